@@ -1,0 +1,221 @@
+// Spatial batch normalisation on NHWC bf16 tensors (rows = N*H*W, columns = channels):
+//   forward (training): per-channel batch mean / inverse std, running-statistic update with a caller-given
+//   factor, then y = act(gamma * xhat + beta [+ residual]);  inference uses the running statistics.
+//   backward: dgamma = sum dy*xhat, dbeta = sum dy, dx = gamma*istd/M * (M*dy - dbeta - xhat*dgamma).
+// Replaces cuDNN BatchNormalizationForwardTraining/Inference/Backward as used by the reference's
+// BNormConv2d and residual operators, including its "add into a copy of x" residual trick
+// (src/operator/conv.rs:494-535,595-608,1601-1644).
+#include "common.cuh"
+
+namespace rb {
+
+// sums[c] += sum x, sums[C+c] += sum x^2 ; optionally of dy and dy*xhat for the backward pass
+__global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                                 const float* __restrict__ mean, const float* __restrict__ istd, long long rows, int C,
+                                 float* __restrict__ sums, int backward) {
+  __shared__ float red0[8][257];
+  __shared__ float red1[8][257];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + tx) * 8;
+  float a0[8], a1[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { a0[j] = 0.f; a1[j] = 0.f; }
+  if (c0 < C) {
+    float mu[8], is[8];
+    if (backward) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { mu[j] = mean[c0 + j]; is[j] = istd[c0 + j]; }
+    }
+    for (long long r = (long long)blockIdx.y * 8 + ty; r < rows; r += (long long)gridDim.y * 8) {
+      float v[8];
+      load8(x + r * C + c0, v);
+      if (!backward) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a0[j] += v[j]; a1[j] += v[j] * v[j]; }
+      } else {
+        float g[8];
+        load8(dy + r * C + c0, g);
+        if (y) {  // ReLU after the normalisation: mask by the forward output
+          float yy[8];
+          load8(y + r * C + c0, yy);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) if (!(yy[j] > 0.f)) g[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { a0[j] += g[j]; a1[j] += g[j] * (v[j] - mu[j]) * is[j]; }
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { red0[ty][tx * 8 + j] = a0[j]; red1[ty][tx * 8 + j] = a1[j]; }
+  __syncthreads();
+  const int c = threadIdx.x;
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) { s0 += red0[k][c]; s1 += red1[k][c]; }
+  const int gc = blockIdx.x * 256 + c;
+  if (gc < C) {
+    atomicAdd(sums + gc, s0);
+    atomicAdd(sums + C + gc, s1);
+  }
+}
+
+// mean/istd from the sums; running statistics: r = (1-f) r + f batch ; sums re-zeroed.
+__global__ void bn_finalize_kernel(float* __restrict__ sums, long long rows, int C, float eps, float factor,
+                                   float* __restrict__ mean, float* __restrict__ istd, float* __restrict__ run_mean,
+                                   float* __restrict__ run_var) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const float m = sums[c] / (float)rows;
+  float var = sums[C + c] / (float)rows - m * m;
+  var = fmaxf(var, 0.f);
+  mean[c] = m;
+  istd[c] = rsqrtf(var + eps);
+  if (run_mean) {
+    const float unbiased = rows > 1 ? var * (float)rows / (float)(rows - 1) : var;
+    run_mean[c] = (1.f - factor) * run_mean[c] + factor * m;
+    run_var[c] = (1.f - factor) * run_var[c] + factor * unbiased;
+  }
+  sums[c] = 0.f;
+  sums[C + c] = 0.f;
+}
+
+__global__ void bn_running_istd_kernel(const float* __restrict__ run_var, float eps, float* __restrict__ istd, int C) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c < C) istd[c] = rsqrtf(run_var[c] + eps);
+}
+
+__global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restrict__ mean,
+                                const float* __restrict__ istd, const float* __restrict__ gamma,
+                                const float* __restrict__ beta, const bf16* __restrict__ residual,
+                                bf16* __restrict__ y, long long rows, int C, int c_valid, int relu) {
+  const int cv = C / 8;
+  const long long total = rows * cv;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c0 = (int)(i % cv) * 8;
+    float v[8], r[8];
+    load8(x + i * 8, v);
+    if (residual) load8(residual + i * 8, r);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j;
+      float o = 0.f;
+      if (c < c_valid) {
+        o = (v[j] - mean[c]) * istd[c] * gamma[c] + beta[c];
+        if (residual) o += r[j];
+        if (relu) o = fmaxf(o, 0.f);
+      }
+      v[j] = o;
+    }
+    store8(y + i * 8, v);
+  }
+}
+
+// sums holds [dbeta | dgamma]; they are also accumulated into the gradient buffers.
+__global__ void bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
+                                    const float* __restrict__ mean, const float* __restrict__ istd,
+                                    const float* __restrict__ gamma, const float* __restrict__ sums,
+                                    bf16* __restrict__ dx, long long rows, int C, int c_valid) {
+  const int cv = C / 8;
+  const long long total = rows * cv;
+  const float invm = 1.f / (float)rows;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c0 = (int)(i % cv) * 8;
+    float v[8], g[8];
+    load8(x + i * 8, v);
+    load8(dy + i * 8, g);
+    if (y) {
+      float yy[8];
+      load8(y + i * 8, yy);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (!(yy[j] > 0.f)) g[j] = 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j;
+      float o = 0.f;
+      if (c < c_valid) {
+        const float xh = (v[j] - mean[c]) * istd[c];
+        o = gamma[c] * istd[c] * (g[j] - invm * (sums[c] + xh * sums[C + c]));
+      }
+      v[j] = o;
+    }
+    store8(dx + i * 8, v);
+  }
+}
+
+__global__ void bn_grad_accum_kernel(float* __restrict__ sums, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                     int C, int c_valid) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  if (c < c_valid) {
+    dbeta[c] += sums[c];
+    dgamma[c] += sums[C + c];
+  }
+  sums[c] = 0.f;
+  sums[C + c] = 0.f;
+}
+
+static inline int grid_for(long long total, int block) {
+  long long g = (total + block - 1) / block;
+  if (g > 148LL * 16) g = 148LL * 16;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" {
+
+// sums: 2*C floats of scratch that must be zero on entry and is zero again on return.
+int rb_bn_fwd_train(const void* x, long long rows, int C, int c_valid, float* sums, float eps, float factor,
+                    float* mean, float* istd, float* run_mean, float* run_var, const float* gamma, const float* beta,
+                    const void* residual, void* y, int relu, cudaStream_t st) {
+  if (C % 8) return -10;
+  dim3 grid((C + 255) / 256, 1);
+  long long gy = rows / 64;
+  if (gy < 1) gy = 1;
+  if (gy > 256) gy = 256;
+  grid.y = (unsigned)gy;
+  bn_reduce_kernel<<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, rows, C, eps, factor, mean, istd, run_mean, run_var);
+  bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, mean, istd, gamma, beta,
+                                                                (const bf16*)residual, (bf16*)y, rows, C, c_valid, relu);
+  return RB_LAUNCH_OK();
+}
+
+int rb_bn_fwd_infer(const void* x, long long rows, int C, int c_valid, float eps, const float* run_mean,
+                    const float* run_var, float* istd_tmp, const float* gamma, const float* beta, const void* residual,
+                    void* y, int relu, cudaStream_t st) {
+  if (C % 8) return -10;
+  bn_running_istd_kernel<<<(C + 127) / 128, 128, 0, st>>>(run_var, eps, istd_tmp, C);
+  bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, run_mean, istd_tmp, gamma, beta,
+                                                                (const bf16*)residual, (bf16*)y, rows, C, c_valid, relu);
+  return RB_LAUNCH_OK();
+}
+
+// y_relu: forward output when a ReLU followed the normalisation (masks dy), else null.
+// dgamma/dbeta are accumulated (the optimizer zeroes them).
+int rb_bn_bwd(const void* x, const void* dy, const void* y_relu, long long rows, int C, int c_valid, float* sums,
+              const float* mean, const float* istd, const float* gamma, float* dgamma, float* dbeta, void* dx,
+              cudaStream_t st) {
+  if (C % 8) return -10;
+  dim3 grid((C + 255) / 256, 1);
+  long long gy = rows / 64;
+  if (gy < 1) gy = 1;
+  if (gy > 256) gy = 256;
+  grid.y = (unsigned)gy;
+  bn_reduce_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y_relu, mean, istd, rows, C, sums,
+                                         1);
+  bn_bwd_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, (const bf16*)dy,
+                                                                    (const bf16*)y_relu, mean, istd, gamma, sums,
+                                                                    (bf16*)dx, rows, C, c_valid);
+  bn_grad_accum_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, dgamma, dbeta, C, c_valid);
+  return RB_LAUNCH_OK();
+}
+
+}  // extern "C"

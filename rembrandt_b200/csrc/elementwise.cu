@@ -1,0 +1,242 @@
+// Small memory-bound helpers around the tensor-core kernels: bias-gradient column sums,
+// the fp32 -> bf16 epilogue of split-K affine layers, dropout, ReLU masking, filter repacking.
+#include "common.cuh"
+
+namespace rb {
+
+// out[c] += sum_r x[r][c]   (bias gradient; replaces cuDNN ConvolutionBackwardBias and the ones-vector
+// gemm of the reference, src/operator/mod.rs:1169,1775-1781)
+__global__ void colsum_kernel(const bf16* __restrict__ x, long long rows, int ld, int cols, float* __restrict__ out) {
+  __shared__ float red[8][257];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c0 = (blockIdx.x * 32 + tx) * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+  if (c0 < ld) {
+    for (long long r = (long long)blockIdx.y * 8 + ty; r < rows; r += (long long)gridDim.y * 8) {
+      float v[8];
+      load8(x + r * ld + c0, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += v[j];
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[ty][tx * 8 + j] = acc[j];
+  __syncthreads();
+  const int c = threadIdx.x;  // 256 columns per block
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) s += red[k][c];
+  const int gc = blockIdx.x * 256 + c;
+  if (gc < cols) atomicAdd(out + gc, s);
+}
+
+// y[r][c] = act(acc[r][c] + bias[c]) for c < n_valid, 0 for padded columns; acc is re-zeroed so the
+// split-K workspace is clean for its next use.
+__global__ void bias_act_kernel(float* __restrict__ acc, long long rows, int ld, int n_valid,
+                                const float* __restrict__ bias, int relu, bf16* __restrict__ y,
+                                const bf16* __restrict__ mask_src, int rezero) {
+  const long long total = rows * (ld / 8);
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int c0 = (int)(i % (ld / 8)) * 8;
+    const long long r = i / (ld / 8);
+    float4* ap = reinterpret_cast<float4*>(acc + r * ld + c0);
+    const float4 a0 = ap[0], a1 = ap[1];
+    float v[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = c0 + j;
+      if (c < n_valid) {
+        if (bias) v[j] += bias[c];
+        if (relu) v[j] = fmaxf(v[j], 0.f);
+      } else {
+        v[j] = 0.f;
+      }
+    }
+    if (mask_src) {
+      float m[8];
+      load8(mask_src + r * ld + c0, m);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (!(m[j] > 0.f)) v[j] = 0.f;
+    }
+    store8(y + r * ld + c0, v);
+    if (rezero) {
+      ap[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+      ap[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+}
+
+// Inverted dropout: y = x * keep / (1 - p), keep = (u >= p), u from Philox(seed, element/4).
+// The mask is never stored; backward regenerates it from the same (seed, stream) pair.
+// (reference: map_dropout / map_dropout_backprop call sites, src/operator/mod.rs:2210-2244)
+__global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const bf16* __restrict__ mask_src,
+                               long long n, float p, uint64_t seed, uint32_t stream) {
+  const float scale = 1.f / (1.f - p);
+  const long long groups = n / 8;
+  for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
+       g += (long long)gridDim.x * blockDim.x) {
+    float v[8];
+    load8(x + g * 8, v);
+    uint32_t r0[4], r1[4];
+    Philox::gen(seed, (uint64_t)g * 2, stream, r0);
+    Philox::gen(seed, (uint64_t)g * 2 + 1, stream, r1);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[j] = (u32_to_unit(r0[j]) >= p) ? v[j] * scale : 0.f;
+      v[4 + j] = (u32_to_unit(r1[j]) >= p) ? v[4 + j] * scale : 0.f;
+    }
+    if (mask_src) {
+      float m[8];
+      load8(mask_src + g * 8, m);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (!(m[j] > 0.f)) v[j] = 0.f;
+    }
+    store8(y + g * 8, v);
+  }
+}
+
+// d *= (y > 0) in place
+__global__ void relu_mask_kernel(bf16* __restrict__ d, const bf16* __restrict__ y, long long n) {
+  const long long groups = n / 8;
+  for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
+       g += (long long)gridDim.x * blockDim.x) {
+    float v[8], m[8];
+    load8(d + g * 8, v);
+    load8(y + g * 8, m);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) if (!(m[j] > 0.f)) v[j] = 0.f;
+    store8(d + g * 8, v);
+  }
+}
+
+// a += b (bf16), optional mask; used to sum branch deltas at fan-out points
+__global__ void add_kernel(bf16* __restrict__ a, const bf16* __restrict__ b, long long n) {
+  const long long groups = n / 8;
+  for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
+       g += (long long)gridDim.x * blockDim.x) {
+    float v[8], w[8];
+    load8(a + g * 8, v);
+    load8(b + g * 8, w);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += w[j];
+    store8(a + g * 8, v);
+  }
+}
+
+__global__ void f32_to_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    y[i] = f2bf(x[i]);
+}
+
+// wt[c][(R-1-r)*S + (S-1-s)][k] = w[k][r*S+s][c]   (k < Kout, c < Cp; padded k are zero)
+// Filters for the data-gradient, which runs as a forward convolution of dY with flipped taps.
+__global__ void pack_dgrad_filters_kernel(const bf16* __restrict__ w, bf16* __restrict__ wt, int Kout, int Kp, int RS,
+                                          int Cp) {
+  const long long total = (long long)Cp * RS * Kp;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int k = (int)(i % Kp);
+    long long t = i / Kp;
+    const int tap = (int)(t % RS);
+    const int c = (int)(t / RS);
+    bf16 v = f2bf(0.f);
+    if (k < Kout) v = w[((long long)k * RS + (RS - 1 - tap)) * Cp + c];
+    wt[i] = v;
+  }
+}
+
+// Zero the entries of a space-to-depth'd first-layer filter gradient that have no counterpart in the
+// original filter: taps (r,s) >= ksize and padded channels.  dw is [Kout][R2*S2][Cp], channel =
+// (dy*f + dx)*cin + ci, original row = R2idx*f + dy.
+__global__ void zero_s2d_structural_kernel(float* __restrict__ dw, int Kout, int R2, int Cp, int f, int cin,
+                                           int ksize) {
+  const long long total = (long long)Kout * R2 * R2 * Cp;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int ch = (int)(i % Cp);
+    long long t = i / Cp;
+    const int tap = (int)(t % (R2 * R2));
+    const int r2 = tap / R2, s2 = tap % R2;
+    bool dead = ch >= f * f * cin;
+    if (!dead) {
+      const int blk = ch / cin;
+      const int dy = blk / f, dx = blk % f;
+      dead = (r2 * f + dy >= ksize) || (s2 * f + dx >= ksize);
+    }
+    if (dead) dw[i] = 0.f;
+  }
+}
+
+static inline int grid_for(long long total, int block) {
+  long long g = (total + block - 1) / block;
+  if (g > 148LL * 16) g = 148LL * 16;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" {
+
+int rb_colsum(const void* x, long long rows, int ld, int cols, float* out, cudaStream_t st) {
+  if (ld % 8) return -10;
+  dim3 grid((ld + 255) / 256, 1);
+  long long gy = rows / 64;
+  if (gy < 1) gy = 1;
+  if (gy > 256) gy = 256;
+  grid.y = (unsigned)gy;
+  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, rows, ld, cols, out);
+  return RB_LAUNCH_OK();
+}
+
+int rb_bias_act(float* acc, long long rows, int ld, int n_valid, const float* bias, int relu, void* y,
+                const void* mask_src, int rezero, cudaStream_t st) {
+  if (ld % 8) return -10;
+  bias_act_kernel<<<grid_for(rows * (ld / 8), 256), 256, 0, st>>>(acc, rows, ld, n_valid, bias, relu, (bf16*)y,
+                                                                 (const bf16*)mask_src, rezero);
+  return RB_LAUNCH_OK();
+}
+
+int rb_dropout(const void* x, void* y, const void* mask_src, long long n, float p, unsigned long long seed,
+               unsigned int stream_id, cudaStream_t st) {
+  if (n % 8) return -10;
+  dropout_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)mask_src, n, p, seed,
+                                                      stream_id);
+  return RB_LAUNCH_OK();
+}
+
+int rb_relu_mask(void* d, const void* y, long long n, cudaStream_t st) {
+  if (n % 8) return -10;
+  relu_mask_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((bf16*)d, (const bf16*)y, n);
+  return RB_LAUNCH_OK();
+}
+
+int rb_add_bf16(void* a, const void* b, long long n, cudaStream_t st) {
+  if (n % 8) return -10;
+  add_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((bf16*)a, (const bf16*)b, n);
+  return RB_LAUNCH_OK();
+}
+
+int rb_f32_to_bf16(const float* x, void* y, long long n, cudaStream_t st) {
+  f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, (bf16*)y, n);
+  return RB_LAUNCH_OK();
+}
+
+int rb_pack_dgrad_filters(const void* w, void* wt, int Kout, int Kp, int RS, int Cp, cudaStream_t st) {
+  pack_dgrad_filters_kernel<<<grid_for((long long)Cp * RS * Kp, 256), 256, 0, st>>>((const bf16*)w, (bf16*)wt, Kout,
+                                                                                   Kp, RS, Cp);
+  return RB_LAUNCH_OK();
+}
+
+int rb_zero_s2d_structural(float* dw, int Kout, int R2, int Cp, int f, int cin, int ksize, cudaStream_t st) {
+  zero_s2d_structural_kernel<<<grid_for((long long)Kout * R2 * R2 * Cp, 256), 256, 0, st>>>(dw, Kout, R2, Cp, f, cin,
+                                                                                           ksize);
+  return RB_LAUNCH_OK();
+}
+
+}  // extern "C"

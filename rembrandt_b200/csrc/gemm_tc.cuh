@@ -1,0 +1,54 @@
+// Parameter block of the persistent tcgen05 GEMM / implicit-GEMM convolution
+// kernel (gemm_tc.cu). One kernel, configured at run time, serves:
+//   conv fprop   A = im2col(X) K-major (TMA im2col)   B = filters K-major
+//   conv dgrad   A = im2col(dY) K-major               B = flipped/transposed filters K-major
+//   conv wgrad   A = dY^T MN-major (tiled)            B = im2col(X) MN-major (TMA im2col)
+//   affine fwd   A = X K-major                        B = W K-major
+//   affine dgrad A = dY K-major                       B = W MN-major
+//   affine wgrad A = dY^T MN-major                    B = X^T MN-major
+// Reference parity: these replace the cuDNN convolution forward / backward-data /
+// backward-filter calls and the cuBLAS sgemm calls of the reference operators
+// (src/operator/mod.rs:1075-1176 affine, :1663-1795 conv).
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace rb {
+
+enum : int { A_TILED_K = 0, A_IM2COL_K = 1, A_TILED_MN = 2 };
+enum : int { B_TILED_K = 0, B_TILED_MN = 1, B_IM2COL_MN = 2, B_TILED_K3 = 3 };
+enum : int { EPI_BF16 = 0, EPI_F32_STORE = 1, EPI_F32_ATOMIC = 2 };
+
+struct alignas(64) GemmTcParams {
+  CUtensorMap tm_a;
+  CUtensorMap tm_b;
+  int a_mode, b_mode;
+  int M, N;            // extent of D in rows / columns (tiles are clipped against these)
+  int bn;              // tile width  (multiple of 32, <= 256)
+  int bk;              // k-block depth (64 or 32)
+  int num_kb;          // k-blocks over the whole reduction
+  int split_k;         // reduction split; > 1 requires EPI_F32_ATOMIC
+  int stages;
+  // convolution geometry (im2col operands)
+  int cv_P, cv_Q;      // output height / width per image
+  int cv_stride;       // traversal stride
+  int cv_lower_h, cv_lower_w;  // lower corner of the base pixel (= -pad)
+  int cv_S;            // filter width (taps are enumerated r*S+s)
+  int cv_cchunks;      // channel chunks of bk per tap (A_IM2COL_K / B_TILED_K3)
+  int wg_ctiles;       // channel tiles of bn per tap (B_IM2COL_MN)
+  int wg_cpad;         // padded input channels: column of D = tap*wg_cpad + channel
+  int n_tiles;         // tiles along N (taps*wg_ctiles for wgrad)
+  // epilogue
+  int epi;
+  int relu;            // EPI_BF16: clamp at zero after the bias
+  int n_valid;         // columns >= n_valid are written as zero (channel padding)
+  int n_store;         // columns >= n_store are not written at all
+  long long ldd;       // row pitch of D in elements
+  void* D;
+  const float* bias;               // optional, indexed by column
+  const __nv_bfloat16* mask_src;   // optional, same layout as D: D is zeroed where mask_src <= 0
+  unsigned int* status;            // error bits (see ptx.cuh)
+};
+
+}  // namespace rb

@@ -1,0 +1,198 @@
+"""Thin, allocation-free Python fronts of the CUDA kernels.
+
+Conventions shared by every function here:
+
+* activations are bf16, NHWC, with the channel count padded (``pad_channels``); padded channels hold zeros;
+* convolution filters are ``[Kout][R*S][Cp]`` (bf16 compute copy, fp32 master/gradient);
+* affine weights are ``[out][in_pad]`` row-major, which is the reference's ``[in,out]`` first-dimension-fastest
+  array (src/operator/mod.rs:1024-1034);
+* every function launches on the current torch stream and writes into caller-provided tensors.
+
+The functions raise ``NativeError`` if a launcher reports a problem; there is no eager fallback.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from .._native import check, ptr, stream_handle
+
+EPI_BF16, EPI_F32_STORE, EPI_F32_ATOMIC = 0, 1, 2
+
+
+def pad_channels(c: int) -> int:
+    """Channel padding rule: a multiple of 64 is kept, anything else is rounded up to a multiple of 32."""
+    if c % 64 == 0:
+        return c
+    return (c + 31) // 32 * 32
+
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def status_word(device=None) -> torch.Tensor:
+    """Per-device uint32 word in which kernels record a bounded wait that ran out (0 = healthy)."""
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev not in _status_words:
+        _status_words[dev] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{dev}")
+    return _status_words[dev]
+
+
+def read_status() -> int:
+    return int(status_word().item())
+
+
+# ------------------------------------------------------------------ GEMM / convolution (tcgen05)
+def gemm_tc(a, a_mn, lda, b, b_mn, ldb, M, N, K, d, ldd, epi=EPI_BF16, bias=None, relu=False, mask_src=None,
+            n_valid=0, n_store=0, split_k=0, bn_cap=0):
+    rc = _native.cuda().rb_gemm_tc(ptr(a), int(a_mn), lda, ptr(b), int(b_mn), ldb, M, N, K, ptr(d), ldd, epi,
+                                   ptr(bias), int(relu), ptr(mask_src), n_valid, n_store, split_k, bn_cap,
+                                   ptr(status_word()), stream_handle())
+    check(rc, "rb_gemm_tc")
+
+
+def conv_fprop_tc(x, N, H, W, Cp, w, Kout, R, S, stride, pad_h, pad_w, P, Q, y, ldy, bias=None, relu=False,
+                  mask_src=None, n_valid=0, n_store=0):
+    rc = _native.cuda().rb_conv_fprop_tc(ptr(x), N, H, W, Cp, ptr(w), Kout, R, S, stride, pad_h, pad_w, P, Q, ptr(y),
+                                         ldy, ptr(bias), int(relu), ptr(mask_src), n_valid, n_store,
+                                         ptr(status_word()), stream_handle())
+    check(rc, "rb_conv_fprop_tc")
+
+
+def conv_wgrad_tc(x, N, H, W, Cp, dy, lddy, Kout, R, S, stride, pad_h, pad_w, P, Q, dw, split_k=0):
+    rc = _native.cuda().rb_conv_wgrad_tc(ptr(x), N, H, W, Cp, ptr(dy), lddy, Kout, R, S, stride, pad_h, pad_w, P, Q,
+                                         ptr(dw), split_k, ptr(status_word()), stream_handle())
+    check(rc, "rb_conv_wgrad_tc")
+
+
+def conv_direct_fwd(x, w, bias, y, N, H, W, Cp, Kout, Kp, R, S, stride, pad_h, pad_w, P, Q, relu):
+    check(_native.cuda().rb_conv_direct_fwd(ptr(x), ptr(w), ptr(bias), ptr(y), N, H, W, Cp, Kout, Kp, R, S, stride,
+                                            pad_h, pad_w, P, Q, int(relu), stream_handle()), "rb_conv_direct_fwd")
+
+
+def conv_direct_dgrad(dy, w, dx, mask_src, N, H, W, Cp, Kout, Kp, R, S, stride, pad_h, pad_w, P, Q):
+    check(_native.cuda().rb_conv_direct_dgrad(ptr(dy), ptr(w), ptr(dx), ptr(mask_src), N, H, W, Cp, Kout, Kp, R, S,
+                                              stride, pad_h, pad_w, P, Q, stream_handle()), "rb_conv_direct_dgrad")
+
+
+def conv_direct_wgrad(x, dy, dw, N, H, W, Cp, Kout, Kp, R, S, stride, pad_h, pad_w, P, Q):
+    check(_native.cuda().rb_conv_direct_wgrad(ptr(x), ptr(dy), ptr(dw), N, H, W, Cp, Kout, Kp, R, S, stride, pad_h,
+                                              pad_w, P, Q, stream_handle()), "rb_conv_direct_wgrad")
+
+
+def pack_dgrad_filters(w16, wt16, Kout, Kp, RS, Cp):
+    check(_native.cuda().rb_pack_dgrad_filters(ptr(w16), ptr(wt16), Kout, Kp, RS, Cp, stream_handle()),
+          "rb_pack_dgrad_filters")
+
+
+def zero_s2d_structural(dw, Kout, R2, Cp, f, cin, ksize):
+    check(_native.cuda().rb_zero_s2d_structural(ptr(dw), Kout, R2, Cp, f, cin, ksize, stream_handle()),
+          "rb_zero_s2d_structural")
+
+
+# ------------------------------------------------------------------ memory-bound operators
+def colsum(x, rows, ld, cols, out):
+    check(_native.cuda().rb_colsum(ptr(x), rows, ld, cols, ptr(out), stream_handle()), "rb_colsum")
+
+
+def bias_act(acc, rows, ld, n_valid, bias, relu, y, mask_src=None, rezero=True):
+    check(_native.cuda().rb_bias_act(ptr(acc), rows, ld, n_valid, ptr(bias), int(relu), ptr(y), ptr(mask_src),
+                                     int(rezero), stream_handle()), "rb_bias_act")
+
+
+def dropout(x, y, n, p, seed, stream_id, mask_src=None):
+    check(_native.cuda().rb_dropout(ptr(x), ptr(y), ptr(mask_src), n, float(p), int(seed) & (2**64 - 1),
+                                    int(stream_id) & 0xFFFFFFFF, stream_handle()), "rb_dropout")
+
+
+def relu_mask(d, y, n):
+    check(_native.cuda().rb_relu_mask(ptr(d), ptr(y), n, stream_handle()), "rb_relu_mask")
+
+
+def add_bf16(a, b, n):
+    check(_native.cuda().rb_add_bf16(ptr(a), ptr(b), n, stream_handle()), "rb_add_bf16")
+
+
+def f32_to_bf16(x, y, n):
+    check(_native.cuda().rb_f32_to_bf16(ptr(x), ptr(y), n, stream_handle()), "rb_f32_to_bf16")
+
+
+def pool_fwd(x, y, idx, N, H, W, C, P, Q, k, stride, pad, is_max, relu):
+    check(_native.cuda().rb_pool_fwd(ptr(x), ptr(y), ptr(idx), N, H, W, C, P, Q, k, stride, pad, int(is_max),
+                                     int(relu), stream_handle()), "rb_pool_fwd")
+
+
+def pool_bwd(dy, idx, y_relu, dx, mask_src, N, H, W, C, P, Q, k, stride, pad, is_max):
+    check(_native.cuda().rb_pool_bwd(ptr(dy), ptr(idx), ptr(y_relu), ptr(dx), ptr(mask_src), N, H, W, C, P, Q, k,
+                                     stride, pad, int(is_max), stream_handle()), "rb_pool_bwd")
+
+
+def lrn_fwd(x, y, pixels, C, size, alpha_eff, beta, k):
+    check(_native.cuda().rb_lrn_fwd(ptr(x), ptr(y), pixels, C, size, alpha_eff, beta, k, stream_handle()),
+          "rb_lrn_fwd")
+
+
+def lrn_bwd(x, dy, dx, mask_src, pixels, C, size, alpha_eff, beta, k):
+    check(_native.cuda().rb_lrn_bwd(ptr(x), ptr(dy), ptr(dx), ptr(mask_src), pixels, C, size, alpha_eff, beta, k,
+                                    stream_handle()), "rb_lrn_bwd")
+
+
+def softmax_ce(logits, B, K, ld, labels, weights, w_scalar, delta, probs=None, loss_sum=None, correct=None,
+               loss_per=None, argmax_out=None, cat_weights=None):
+    check(_native.cuda().rb_softmax_ce(ptr(logits), B, K, ld, ptr(labels), ptr(weights), float(w_scalar), ptr(delta),
+                                       ptr(probs), ptr(loss_sum), ptr(correct), ptr(loss_per), ptr(argmax_out),
+                                       ptr(cat_weights), stream_handle()), "rb_softmax_ce")
+
+
+def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
+    check(_native.cuda().rb_sgd_fused(ptr(w), ptr(g), ptr(v), ptr(w16), n, lr, mu, l2, grad_scale, mode, phase,
+                                      stream_handle()), "rb_sgd_fused")
+
+
+def axpy_shadow(w, v, w16, n, s):
+    check(_native.cuda().rb_axpy_shadow(ptr(w), ptr(v), ptr(w16), n, float(s), stream_handle()), "rb_axpy_shadow")
+
+
+def axpby(x, y, n, a, b):
+    check(_native.cuda().rb_axpby(ptr(x), ptr(y), n, float(a), float(b), stream_handle()), "rb_axpby")
+
+
+def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi_y, lo_x, hi_x, random_crop,
+             random_flip, per_batch, scale, mean_scale, pca_sigma, pca_vals, pca_vecs, seed, step):
+    import ctypes as C_
+    pv = (C_.c_float * 3)(*pca_vals) if pca_vals is not None else None
+    pe = (C_.c_float * 9)(*pca_vecs) if pca_vecs is not None else None
+    check(_native.cuda().rb_input_u8(ptr(src), ptr(mean), ptr(dst), N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y,
+                                     hi_y, lo_x, hi_x, int(random_crop), int(random_flip), int(per_batch),
+                                     float(scale), float(mean_scale), float(pca_sigma),
+                                     C_.cast(pv, C_.c_void_p) if pv is not None else None,
+                                     C_.cast(pe, C_.c_void_p) if pe is not None else None,
+                                     int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF, stream_handle()), "rb_input_u8")
+
+
+def synth_normal(dst, pixels, C, Cp, seed, step):
+    check(_native.cuda().rb_synth_normal(ptr(dst), pixels, C, Cp, int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF,
+                                         stream_handle()), "rb_synth_normal")
+
+
+def synth_labels(labels, n, classes, seed, step):
+    check(_native.cuda().rb_synth_labels(ptr(labels), n, classes, int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF,
+                                         stream_handle()), "rb_synth_labels")
+
+
+def bn_fwd_train(x, rows, C, c_valid, sums, eps, factor, mean, istd, run_mean, run_var, gamma, beta, residual, y,
+                 relu):
+    check(_native.cuda().rb_bn_fwd_train(ptr(x), rows, C, c_valid, ptr(sums), eps, factor, ptr(mean), ptr(istd),
+                                         ptr(run_mean), ptr(run_var), ptr(gamma), ptr(beta), ptr(residual), ptr(y),
+                                         int(relu), stream_handle()), "rb_bn_fwd_train")
+
+
+def bn_fwd_infer(x, rows, C, c_valid, eps, run_mean, run_var, istd_tmp, gamma, beta, residual, y, relu):
+    check(_native.cuda().rb_bn_fwd_infer(ptr(x), rows, C, c_valid, eps, ptr(run_mean), ptr(run_var), ptr(istd_tmp),
+                                         ptr(gamma), ptr(beta), ptr(residual), ptr(y), int(relu), stream_handle()),
+          "rb_bn_fwd_infer")
+
+
+def bn_bwd(x, dy, y_relu, rows, C, c_valid, sums, mean, istd, gamma, dgamma, dbeta, dx):
+    check(_native.cuda().rb_bn_bwd(ptr(x), ptr(dy), ptr(y_relu), rows, C, c_valid, ptr(sums), ptr(mean), ptr(istd),
+                                   ptr(gamma), ptr(dgamma), ptr(dbeta), ptr(dx), stream_handle()), "rb_bn_bwd")
