@@ -1,0 +1,291 @@
+"""Operator configurations and the fluent sequential builder.
+
+Counterpart of the reference's per-operator ``*OperatorConfig`` structs, its ``OperatorConfig`` tagged union
+(src/operator/mod.rs:121-231), the enums next to it (``ActivationFunction``, ``ParamsInit``, ``PoolOperation``,
+``OpPhase``, ``Regularization``; :233-297) and ``SequentialOperatorConfig`` with its ``.data3d().conv2d()...``
+builder methods (src/operator/worker.rs:133-228).
+"""
+from __future__ import annotations
+
+import enum
+from dataclasses import dataclass, field
+from typing import List, Optional, Sequence, Tuple
+
+
+class Act(enum.Enum):
+    IDENTITY = "identity"
+    RECT = "rect"
+    LOGISTIC = "logistic"   # declared by the reference, not implemented there either
+    TANH = "tanh"
+
+    @staticmethod
+    def parse(s: str) -> "Act":
+        s = s.lower()
+        if s in ("relu", "rect"):
+            return Act.RECT
+        if s in ("identity", "none", "linear"):
+            return Act.IDENTITY
+        if s in ("sigmoid", "logistic"):
+            return Act.LOGISTIC
+        if s == "tanh":
+            return Act.TANH
+        raise ValueError(f"unknown activation {s!r}")
+
+
+class OpPhase(enum.Enum):
+    INFERENCE = 0
+    TRAINING = 1
+
+
+class OpCapability(enum.Enum):
+    FORWARD = 0
+    BACKWARD = 1
+
+
+@dataclass
+class ParamsInit:
+    """kind: disabled | uniform (half_range) | normal (std) | xavier | kaiming_fwd"""
+    kind: str = "disabled"
+    half_range: float = 0.0
+    std: float = 0.0
+    mean: float = 0.0
+
+    @staticmethod
+    def uniform(half_range):
+        return ParamsInit("uniform", half_range=half_range)
+
+    @staticmethod
+    def normal(std, mean=0.0):
+        return ParamsInit("normal", std=std, mean=mean)
+
+    @staticmethod
+    def xavier():
+        return ParamsInit("xavier")
+
+    @staticmethod
+    def kaiming():
+        return ParamsInit("kaiming_fwd")
+
+
+class PoolKind(enum.Enum):
+    MAX = "max"
+    AVERAGE = "average"
+
+
+@dataclass
+class BNormMovingAverage:
+    """Running-statistics factor: cumulative 1/(1+t) or exponential f (1.0 at t = 0); conv.rs:52-73."""
+    kind: str = "exponential"
+    factor: float = 0.1
+
+    def at_iter(self, t: int) -> float:
+        if self.kind == "cumulative":
+            return 1.0 / (1.0 + t)
+        return 1.0 if t == 0 else self.factor
+
+
+# ---------------------------------------------------------------------------------------- preprocessing
+@dataclass
+class Preproc:
+    """One stage of the input operator's preprocessing chain (src/operator/mod.rs:491-519).
+
+    kind: crop (crop_width, crop_height, pad) | flip_x | subtract_mean (mean_path or mean array, normalize) |
+    pca_noise (std, eigenvalues, eigenvectors) | scale_bicubic (lower, upper; variable-size input only)
+    """
+    kind: str
+    crop_width: int = 0
+    crop_height: int = 0
+    pad: int = 0
+    mean_path: Optional[str] = None
+    mean: Optional[object] = None
+    normalize: bool = False
+    std: float = 0.0
+    eigenvalues: Sequence[float] = ()
+    eigenvectors: Sequence[float] = ()
+    lower: int = 0
+    upper: int = 0
+
+
+@dataclass
+class Data3dCfg:
+    in_dims: Tuple[int, int, int]            # (W, H, C) as in the reference
+    normalize: bool = False                  # divide bytes by 255
+    preprocs: List[Preproc] = field(default_factory=list)
+    per_batch_draws: bool = False            # one crop offset / flip coin per batch (reference behaviour)
+    scale: Optional[float] = None            # overrides the 1/255 factor when set
+    variable_size: bool = False              # VarData3d: per-sample source shapes (src/operator/input.rs)
+    max_dims: Optional[Tuple[int, int, int]] = None
+
+
+@dataclass
+class Conv2dCfg:
+    conv_size: int
+    conv_stride: int
+    conv_pad: int
+    out_channels: int
+    act: Act = Act.RECT
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
+    bias: bool = True
+
+
+@dataclass
+class AffineCfg:
+    out_channels: int
+    act: Act = Act.IDENTITY
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.xavier())
+
+
+@dataclass
+class Pool2dCfg:
+    pool_size: int
+    pool_stride: int
+    pool_pad: int = 0
+    kind: PoolKind = PoolKind.MAX
+    ceil_mode: bool = False                  # gen-3 floors (mod.rs:2022-2027), gen-1 / .model files ceil
+    act: Act = Act.IDENTITY
+
+
+@dataclass
+class LrnCfg:
+    cross_size: int = 5
+    scale: float = 1e-4                      # alpha, applied to the plain sum of squares over the window
+    power: float = 0.75
+    min_div: float = 2.0
+    alpha_div_n: bool = False                # Caffe / torch divide alpha by the window size
+
+
+@dataclass
+class DropoutCfg:
+    drop_ratio: float = 0.5
+
+
+@dataclass
+class BNormConv2dCfg:
+    conv_size: int
+    conv_stride: int
+    conv_pad: int
+    out_channels: int
+    act: Act = Act.RECT
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
+    bnorm_mov_avg: BNormMovingAverage = field(default_factory=BNormMovingAverage)
+    bnorm_epsilon: float = 1e-5
+
+
+@dataclass
+class StackResConv2dCfg:
+    """Identity basic block: relu(x + bn(conv3x3(relu(bn(conv3x3(x))))))."""
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
+    bnorm_mov_avg: BNormMovingAverage = field(default_factory=BNormMovingAverage)
+    bnorm_epsilon: float = 1e-5
+
+
+@dataclass
+class ProjStackResConv2dCfg:
+    """Projection basic block; stride 2 when the output is half the input size, else 1."""
+    out_channels: int
+    out_hw: Optional[int] = None             # None: halve the spatial size when channels change
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
+    bnorm_mov_avg: BNormMovingAverage = field(default_factory=BNormMovingAverage)
+    bnorm_epsilon: float = 1e-5
+
+
+@dataclass
+class BotResConv2dCfg:
+    """Bottleneck residual block (configuration only, as in the reference: conv.rs:3854-3886)."""
+    bottleneck_channels: int = 0
+    out_channels: int = 0
+
+
+@dataclass
+class SoftmaxKLLossCfg:
+    num_categories: int
+
+
+@dataclass
+class MarginalizedSoftmaxIndLossCfg:
+    num_categories: int
+
+
+@dataclass
+class SplitCfg:
+    """Fan-out marker for the graph container: the activation is shared, branch deltas are summed."""
+    num_out_arms: int = 2
+
+
+OpCfg = object
+
+
+@dataclass
+class NamedOp:
+    name: str
+    cfg: OpCfg
+
+
+class SequentialOperatorConfig:
+    """input operator -> hidden operators -> loss operator, built fluently."""
+
+    def __init__(self):
+        self.input_op: Optional[NamedOp] = None
+        self.hidden_ops: List[NamedOp] = []
+        self.loss_op: Optional[NamedOp] = None
+
+    def _name(self, name, prefix):
+        return name if name else f"{prefix}{len(self.hidden_ops) + 1}"
+
+    def data3d(self, cfg: Data3dCfg, name="data"):
+        self.input_op = NamedOp(name, cfg)
+        return self
+
+    def var_data3d(self, cfg: Data3dCfg, name="data"):
+        cfg.variable_size = True
+        self.input_op = NamedOp(name, cfg)
+        return self
+
+    def conv2d(self, cfg: Conv2dCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "conv"), cfg))
+        return self
+
+    def bnorm_conv2d(self, cfg: BNormConv2dCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "bnconv"), cfg))
+        return self
+
+    def stack_res_conv2d(self, cfg: StackResConv2dCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "res"), cfg))
+        return self
+
+    def proj_stack_res_conv2d(self, cfg: ProjStackResConv2dCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "projres"), cfg))
+        return self
+
+    def bot_res_conv2d(self, cfg, name=None):
+        raise NotImplementedError("bottleneck residual blocks are configuration-only, as in the reference "
+                                  "(src/operator/worker.rs:204-212)")
+
+    def pool2d(self, cfg: Pool2dCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "pool"), cfg))
+        return self
+
+    def lrn(self, cfg: LrnCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "lrn"), cfg))
+        return self
+
+    def dropout(self, cfg: DropoutCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "drop"), cfg))
+        return self
+
+    def affine(self, cfg: AffineCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "fc"), cfg))
+        return self
+
+    def softmax_kl_loss(self, cfg: SoftmaxKLLossCfg, name="loss"):
+        self.loss_op = NamedOp(name, cfg)
+        return self
+
+    def marginalized_softmax_ind_loss(self, cfg: MarginalizedSoftmaxIndLossCfg, name="loss"):
+        self.loss_op = NamedOp(name, cfg)
+        return self
+
+    def validate(self):
+        if self.input_op is None or self.loss_op is None:
+            raise ValueError("a sequential configuration needs an input and a loss operator")
+        return self
