@@ -1,0 +1,130 @@
+"""Comparison baseline: the same models and optimizer on stock PyTorch (cuDNN / cuBLAS kernels, DDP over NCCL).
+
+The reference itself (a 2016 Rust crate over cuDNN v4 and MPI) cannot be built offline, so the number to
+beat is this: torch DDP + cuDNN/cuBLAS, bf16 autocast, channels-last activations, SGD momentum 0.9 with
+weight decay 5e-4, 25 MB gradient buckets, same synthetic input shape and batch per GPU. None of the
+framework's own kernels or engine is on this path.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+class AlexNet(nn.Module):
+    """Ungrouped AlexNet, 227x227 input, one LRN after conv1 (62,378,344 parameters)."""
+
+    def __init__(self, num_classes=1000, lrn2=False):
+        super().__init__()
+        self.conv1 = nn.Conv2d(3, 96, 11, 4)
+        self.conv2 = nn.Conv2d(96, 256, 5, 1, 2)
+        self.conv3 = nn.Conv2d(256, 384, 3, 1, 1)
+        self.conv4 = nn.Conv2d(384, 384, 3, 1, 1)
+        self.conv5 = nn.Conv2d(384, 256, 3, 1, 1)
+        self.fc6 = nn.Linear(9216, 4096)
+        self.fc7 = nn.Linear(4096, 4096)
+        self.fc8 = nn.Linear(4096, num_classes)
+        self.lrn2 = lrn2
+
+    def forward(self, x):
+        x = F.relu(self.conv1(x))
+        x = F.local_response_norm(x, 5, alpha=5e-4, beta=0.75, k=2.0)
+        x = F.max_pool2d(x, 3, 2)
+        x = F.relu(self.conv2(x))
+        if self.lrn2:
+            x = F.local_response_norm(x, 5, alpha=5e-4, beta=0.75, k=2.0)
+        x = F.max_pool2d(x, 3, 2)
+        x = F.relu(self.conv3(x))
+        x = F.relu(self.conv4(x))
+        x = F.relu(self.conv5(x))
+        x = F.max_pool2d(x, 3, 2)
+        x = x.flatten(1)
+        x = F.dropout(F.relu(self.fc6(x)), 0.5, self.training)
+        x = F.dropout(F.relu(self.fc7(x)), 0.5, self.training)
+        return self.fc8(x)
+
+
+class NiN(nn.Module):
+    def __init__(self, num_classes=1000):
+        super().__init__()
+
+        def block(cin, k, s, p, outs):
+            layers = []
+            c = cin
+            for i, o in enumerate(outs):
+                layers += [nn.Conv2d(c, o, k if i == 0 else 1, s if i == 0 else 1, p if i == 0 else 0), nn.ReLU(True)]
+                c = o
+            return nn.Sequential(*layers)
+
+        self.b1 = block(3, 11, 4, 0, (96, 96, 96))
+        self.b2 = block(96, 5, 1, 2, (256, 256, 256))
+        self.b3 = block(256, 3, 1, 1, (384, 384, 384))
+        self.b4 = block(384, 3, 1, 1, (1024, 1024, num_classes))
+
+    def forward(self, x):
+        x = F.max_pool2d(self.b1(x), 3, 2, ceil_mode=True)
+        x = F.max_pool2d(self.b2(x), 3, 2, ceil_mode=True)
+        x = F.max_pool2d(self.b3(x), 3, 2, ceil_mode=True)
+        x = self.b4(F.dropout(x, 0.5, self.training))
+        return F.adaptive_avg_pool2d(x, 1).flatten(1)
+
+
+class LeNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1, self.c2 = nn.Conv2d(1, 20, 5), nn.Conv2d(20, 50, 5)
+        self.f1, self.f2 = nn.Linear(800, 500), nn.Linear(500, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.c1(x)), 2)
+        x = F.max_pool2d(F.relu(self.c2(x)), 2)
+        return self.f2(F.relu(self.f1(x.flatten(1))))
+
+
+class CifarNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1, self.c2, self.c3 = nn.Conv2d(3, 32, 5, 1, 2), nn.Conv2d(32, 32, 5, 1, 2), nn.Conv2d(32, 64, 5, 1, 2)
+        self.f = nn.Linear(576, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.c1(x)), 3, 2)
+        x = F.avg_pool2d(F.relu(self.c2(x)), 3, 2)
+        x = F.avg_pool2d(F.relu(self.c3(x)), 3, 2)
+        return self.f(x.flatten(1))
+
+
+MODELS = {"alexnet": (AlexNet, 227, 3, 1000), "nin": (NiN, 224, 3, 1000), "lenet": (LeNet, 28, 1, 10),
+          "cifar": (CifarNet, 32, 3, 10)}
+
+
+class TorchBaseline:
+    """One data-parallel replica; `step(images_u8, labels)` does input cast, forward, backward, all-reduce, SGD."""
+
+    def __init__(self, model="alexnet", batch=128, world=1, rank=0, device="cuda", lr=0.01, momentum=0.9, wd=5e-4):
+        cls, hw, c, k = MODELS[model]
+        self.hw, self.c, self.k, self.batch = hw, c, k, batch
+        self.device = torch.device(device)
+        torch.manual_seed(0)
+        net = cls().to(self.device).to(memory_format=torch.channels_last)
+        if world > 1:
+            net = torch.nn.parallel.DistributedDataParallel(net, device_ids=[self.device.index], bucket_cap_mb=25,
+                                                            gradient_as_bucket_view=True)
+        self.net = net
+        self.opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=momentum, weight_decay=wd, fused=True)
+        self.loss = None
+
+    def step(self, images_u8, labels):
+        x = images_u8.to(self.device, non_blocking=True)
+        y = labels.to(self.device, non_blocking=True).long()
+        x = (x.float() - 127.5) * (1.0 / 73.9)
+        x = x.contiguous(memory_format=torch.channels_last)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            out = self.net(x)
+            loss = F.cross_entropy(out.float(), y)
+        self.opt.zero_grad(set_to_none=True)
+        loss.backward()
+        self.opt.step()
+        self.loss = loss
+        return loss

@@ -42,7 +42,7 @@ _CUDA_SIGS = {
     # elementwise.cu
     "rb_colsum": [vp, i64, i32, i32, vp, vp],
     "rb_bias_act": [vp, i64, i32, i32, vp, i32, vp, vp, i32, vp],
-    "rb_dropout": [vp, vp, vp, i64, f32, u64, u32, vp],
+    "rb_dropout": [vp, vp, vp, i64, f32, u64, u32, vp, vp],
     "rb_relu_mask": [vp, vp, i64, vp],
     "rb_add_bf16": [vp, vp, i64, vp],
     "rb_f32_to_bf16": [vp, vp, i64, vp],
@@ -55,7 +55,7 @@ _CUDA_SIGS = {
     "rb_axpy_shadow": [vp, vp, vp, i64, f32, vp],
     "rb_axpby": [vp, vp, i64, f32, f32, vp],
     # input_pipeline.cu
-    "rb_input_u8": [vp, vp, vp] + [i32] * 17 + [f32, f32, f32, vp, vp, u64, u32, vp],
+    "rb_input_u8": [vp, vp, vp] + [i32] * 17 + [f32, f32, f32, vp, vp, u64, u32, vp, vp],
     "rb_synth_normal": [vp, i64, i32, i32, u64, u32, vp],
     "rb_synth_labels": [vp, i32, i32, u64, u32, vp],
     # bn.cu
@@ -157,7 +157,11 @@ class NativeError(RuntimeError):
     pass
 
 
+LAUNCH_COUNT = [0]   # launcher calls made through check(); the benchmark reports it per step
+
+
 def check(rc: int, what: str) -> None:
+    LAUNCH_COUNT[0] += 1
     if rc != 0:
         raise NativeError(f"{what}: native launcher returned {rc}")
 

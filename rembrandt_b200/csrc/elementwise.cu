@@ -73,8 +73,10 @@ __global__ void bias_act_kernel(float* __restrict__ acc, long long rows, int ld,
 // The mask is never stored; backward regenerates it from the same (seed, stream) pair.
 // (reference: map_dropout / map_dropout_backprop call sites, src/operator/mod.rs:2210-2244)
 __global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const bf16* __restrict__ mask_src,
-                               long long n, float p, uint64_t seed, uint32_t stream) {
+                               long long n, float p, uint64_t seed, uint32_t stream,
+                               const uint32_t* __restrict__ step_ptr) {
   const float scale = 1.f / (1.f - p);
+  if (step_ptr) seed += *step_ptr;  // device-side step counter: a captured graph draws a new mask per replay
   const long long groups = n / 8;
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
        g += (long long)gridDim.x * blockDim.x) {
@@ -203,10 +205,10 @@ int rb_bias_act(float* acc, long long rows, int ld, int n_valid, const float* bi
 }
 
 int rb_dropout(const void* x, void* y, const void* mask_src, long long n, float p, unsigned long long seed,
-               unsigned int stream_id, cudaStream_t st) {
+               unsigned int stream_id, const unsigned int* step_ptr, cudaStream_t st) {
   if (n % 8) return -10;
   dropout_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)mask_src, n, p, seed,
-                                                      stream_id);
+                                                      stream_id, step_ptr);
   return RB_LAUNCH_OK();
 }
 

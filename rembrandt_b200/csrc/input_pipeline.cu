@@ -30,11 +30,13 @@ struct InputArgs {
   float pca_vecs[9];    // row c, column j
   uint64_t seed;
   uint32_t step;
+  const uint32_t* step_ptr;  // optional device counter added to `step` (keeps captured graphs fresh)
 };
 
 __device__ __forceinline__ void sample_draw(const InputArgs& a, int n, int& oy, int& ox, int& flip, float (&shift)[3]) {
   uint32_t r[4];
-  Philox::gen(a.seed, a.per_batch ? 0ull : (uint64_t)n, a.step, r);
+  const uint32_t step = a.step + (a.step_ptr ? *a.step_ptr : 0u);
+  Philox::gen(a.seed, a.per_batch ? 0ull : (uint64_t)n, step, r);
   if (a.random_crop) {
     oy = a.lo_y + (int)(r[0] % (uint32_t)(a.hi_y - a.lo_y + 1));
     ox = a.lo_x + (int)(r[1] % (uint32_t)(a.hi_x - a.lo_x + 1));
@@ -46,7 +48,7 @@ __device__ __forceinline__ void sample_draw(const InputArgs& a, int n, int& oy, 
   shift[0] = shift[1] = shift[2] = 0.f;
   if (a.pca_sigma > 0.f && a.C == 3) {
     uint32_t q[4];
-    Philox::gen(a.seed ^ 0x5bd1e995ull, (uint64_t)n, a.step, q);
+    Philox::gen(a.seed ^ 0x5bd1e995ull, (uint64_t)n, step, q);
     // Box-Muller: three normals from four uniforms
     const float u0 = fmaxf(u32_to_unit(q[0]), 1e-7f), u1 = u32_to_unit(q[1]);
     const float u2 = fmaxf(u32_to_unit(q[2]), 1e-7f), u3 = u32_to_unit(q[3]);
@@ -139,7 +141,8 @@ extern "C" {
 int rb_input_u8(const void* src, const float* mean, void* dst, int N, int C, int H, int W, int crop_h, int crop_w,
                 int OH, int OW, int Cp, int f, int lo_y, int hi_y, int lo_x, int hi_x, int random_crop,
                 int random_flip, int per_batch, float scale, float mean_scale, float pca_sigma, const float* pca_vals,
-                const float* pca_vecs, unsigned long long seed, unsigned int step, cudaStream_t st) {
+                const float* pca_vecs, unsigned long long seed, unsigned int step, const unsigned int* step_ptr,
+                cudaStream_t st) {
   if (Cp % 8) return -10;
   InputArgs a;
   a.src = (const uint8_t*)src; a.mean = mean; a.dst = (bf16*)dst;
@@ -150,7 +153,7 @@ int rb_input_u8(const void* src, const float* mean, void* dst, int N, int C, int
   a.scale = scale; a.mean_scale = mean_scale; a.pca_sigma = pca_sigma;
   for (int i = 0; i < 3; ++i) a.pca_vals[i] = pca_vals ? pca_vals[i] : 0.f;
   for (int i = 0; i < 9; ++i) a.pca_vecs[i] = pca_vecs ? pca_vecs[i] : 0.f;
-  a.seed = seed; a.step = step;
+  a.seed = seed; a.step = step; a.step_ptr = step_ptr;
   const long long total = (long long)N * OH * OW * (Cp / 8);
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;

@@ -1,0 +1,668 @@
+"""Operator library: one class per layer kind, each with a CUDA path (hand-written kernels, bf16 NHWC) and
+a reference path (plain torch fp32, used on CPU and as the numerical oracle).
+
+Mirrors the reference's ``Operator`` protocol (src/operator/mod.rs:61-99): parameters live in flat
+vectors owned by the network; an operator reads its input activation from the previous operator, writes
+its own output buffer, and on backward accumulates parameter gradients (beta = 1, as cuDNN/cuBLAS are
+called in the reference) and writes the previous operator's delta buffer. Where the previous operator
+ends in a ReLU, the delta is masked by that operator's output in the same kernel that produces it (the
+reference does this as a separate in-place pass at the start of each backward).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+import torch.nn.functional as F
+
+from ..ops import layout
+from ..ops import native_ops as K
+from ..ops.native_ops import pad_channels
+from . import config as C
+
+
+class ParamSeg:
+    """A parameter tensor inside the flat vectors."""
+
+    def __init__(self, name, shape, decay=True, trainable=True):
+        self.name = name
+        self.shape = tuple(shape)
+        self.numel = int(math.prod(shape))
+        self.decay = decay
+        self.trainable = trainable
+        self.offset = -1  # assigned by the network
+
+
+class Op:
+    """Base operator. Shapes are (H, W, C) logical plus the padded channel count `cp`."""
+
+    has_params = False
+
+    def __init__(self, name, cfg):
+        self.name = name
+        self.cfg = cfg
+        self.net = None
+        self.prev: Optional[Op] = None
+        self.out_hwc = None
+        self.out_cp = 0
+        self.has_relu = False
+        self.segs: List[ParamSeg] = []
+        self.out = None    # activation buffer (CUDA path)
+        self.dout = None   # delta w.r.t. `out`, written by the consumer
+
+    # ---- construction
+    def setup(self, net, prev):
+        self.net, self.prev = net, prev
+
+    def alloc(self):
+        h, w, _ = self.out_hwc
+        n = self.net.batch
+        self.out = torch.zeros((n, h, w, self.out_cp), dtype=torch.bfloat16, device=self.net.device)
+        if self.net.training_capable:
+            self.dout = torch.zeros_like(self.out)
+
+    def bind(self):
+        """Called after the flat vectors exist."""
+
+    # ---- parameters
+    def init_params(self, rng):
+        pass
+
+    def encode_params(self) -> list:
+        return []
+
+    def decode_params(self, arrays: list) -> int:
+        return 0
+
+    def state_segs(self) -> List[ParamSeg]:
+        return [s for s in self.segs if s.trainable]
+
+    # ---- execution
+    def forward(self, train: bool, t: int):
+        raise NotImplementedError
+
+    def backward(self):
+        pass
+
+    def ref_forward(self, x, train: bool, t: int):
+        raise NotImplementedError
+
+    # ---- helpers
+    def view(self, seg: ParamSeg, which="params"):
+        return self.net.seg_view(seg, which)
+
+    @property
+    def in_hwc(self):
+        return self.prev.out_hwc
+
+    @property
+    def in_cp(self):
+        return self.prev.out_cp
+
+    def mask_src(self):
+        """Activation to mask the delta of `prev` with, or None."""
+        return self.prev.out if self.prev.has_relu else None
+
+    def wants_prev_delta(self):
+        return self.prev is not None and self.prev.dout is not None and not isinstance(self.prev, DataOp)
+
+
+def _draw(kind: C.ParamsInit, rng, shape, fan_in, fan_out):
+    n = int(math.prod(shape))
+    if kind.kind == "disabled":
+        return torch.zeros(shape)
+    if kind.kind == "uniform":
+        return rng.uniform(n, -kind.half_range, kind.half_range).reshape(shape)
+    if kind.kind == "normal":
+        return rng.normal(n, kind.mean, kind.std).reshape(shape)
+    if kind.kind == "xavier":
+        h = math.sqrt(6.0 / (fan_in + fan_out))
+        return rng.uniform(n, -h, h).reshape(shape)
+    if kind.kind == "kaiming_fwd":
+        return rng.normal(n, 0.0, math.sqrt(2.0 / fan_in)).reshape(shape)
+    raise ValueError(kind.kind)
+
+
+# =============================================================================================== input
+class DataOp(Op):
+    """Fixed-size input operator: u8 staging -> cast / normalise / mean / crop / flip / PCA noise.
+
+    Reference: Data3dOperator (src/operator/mod.rs:386-836). Differences by design: crop offsets and flip
+    coins are drawn per sample unless `per_batch_draws` is set; the crop may extend beyond the image by
+    `pad` pixels (zero fill), which gives the usual pad-and-crop augmentation.
+    """
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        cfg: C.Data3dCfg = self.cfg
+        w, h, c = cfg.in_dims
+        self.src_hwc = (h, w, c)
+        self.crop_h, self.crop_w, self.pad = h, w, 0
+        self.flip = False
+        self.mean = None
+        self.mean_scale = 1.0
+        self.pca = None
+        for p in cfg.preprocs:
+            if p.kind == "crop":
+                self.crop_w, self.crop_h, self.pad = p.crop_width, p.crop_height, p.pad
+            elif p.kind == "flip_x":
+                self.flip = True
+            elif p.kind == "subtract_mean":
+                self.mean = p
+            elif p.kind == "pca_noise":
+                self.pca = p
+            elif p.kind == "scale_bicubic":
+                self.scale_range = (p.lower, p.upper)
+            else:
+                raise ValueError(f"unknown preprocessing stage {p.kind!r}")
+        self.scale = cfg.scale if cfg.scale is not None else (1.0 / 255.0 if cfg.normalize else 1.0)
+        self.out_hwc = (self.crop_h, self.crop_w, c)
+        self.out_cp = pad_channels(c)
+        self.mode = "nhwc"
+        self.f = 1
+        self.extra_pad = 0      # padding absorbed from a space-to-depth'd first convolution
+        self.mean_dev = None
+        self.stage = None
+
+    # layout requests from the first hidden operator
+    def request_s2d(self, f, s2d_hw, conv_pad):
+        self.mode, self.f, self.extra_pad = "s2d", f, conv_pad
+        c = self.out_hwc[2]
+        self.s2d_hw = s2d_hw
+        self.out_cp = pad_channels(f * f * c)
+
+    def request_flat(self):
+        h, w, c = self.out_hwc
+        self.mode, self.f = "flat", max(h, w)
+        self.out_cp = pad_channels(self.f * self.f * c)
+
+    def out_buffer_shape(self):
+        n = self.net.batch
+        if self.mode == "s2d":
+            return (n, self.s2d_hw, self.s2d_hw, self.out_cp)
+        if self.mode == "flat":
+            return (n, 1, 1, self.out_cp)
+        return (n, self.crop_h, self.crop_w, self.out_cp)
+
+    def alloc(self):
+        h, w, c = self.src_hwc
+        dev = self.net.device
+        self.out = torch.zeros(self.out_buffer_shape(), dtype=torch.bfloat16, device=dev)
+        self.stage = torch.zeros((self.net.batch, c, h, w), dtype=torch.uint8, device=dev)
+        if self.mean is not None:
+            m = self.mean.mean
+            if m is None and self.mean.mean_path:
+                from ..utils import blob
+                m = blob.read_array_file(self.mean.mean_path, "f32")
+            m = torch.as_tensor(m, dtype=torch.float32).reshape(c, h, w)
+            self.mean_dev = m.to(dev)
+            self.mean_scale = self.scale if self.mean.normalize or self.cfg.normalize else 1.0
+
+    def load_batch(self, images_u8: torch.Tensor, non_blocking=True):
+        """Copy a [B,C,H,W] uint8 batch (host, ideally pinned, or device) into the staging buffer."""
+        self.stage.copy_(images_u8.reshape(self.stage.shape), non_blocking=non_blocking)
+
+    def forward(self, train, t):
+        h, w, c = self.src_hwc
+        cfg = self.cfg
+        n = self.net.batch
+        if self.mode == "nhwc":
+            oh, ow, f = self.crop_h, self.crop_w, 1
+        elif self.mode == "s2d":
+            oh = ow = self.s2d_hw
+            f = self.f
+        else:
+            oh = ow = 1
+            f = self.f
+        ep = self.extra_pad
+        # a crop window enlarged by the absorbed convolution padding
+        ch, cw = self.crop_h + 2 * ep, self.crop_w + 2 * ep
+        lo_y, hi_y = -(self.pad + ep), h - self.crop_h + self.pad - ep
+        lo_x, hi_x = -(self.pad + ep), w - self.crop_w + self.pad - ep
+        rnd_crop = train and (hi_y > lo_y or hi_x > lo_x)
+        pv = pe = None
+        sigma = 0.0
+        if self.pca is not None and train:
+            sigma, pv, pe = self.pca.std, list(self.pca.eigenvalues), list(self.pca.eigenvectors)
+        K.input_u8(self.stage, self.mean_dev, self.out, n, c, h, w, ch, cw, oh, ow, self.out_cp, f, lo_y, hi_y, lo_x,
+                   hi_x, rnd_crop, train and self.flip, cfg.per_batch_draws, self.scale, self.mean_scale, sigma, pv,
+                   pe, self.net.data_seed, 0, self.net.step_counter)
+
+    def ref_forward(self, x, train, t):
+        """x: [B,C,H,W] uint8 or float. Centre crop / no flip at inference, torch RNG draws when training."""
+        h, w, c = self.src_hwc
+        x = x.float() * self.scale
+        if self.mean is not None:
+            m = torch.as_tensor(self.mean.mean, dtype=torch.float32).reshape(1, c, h, w).to(x.device)
+            x = x - (self.scale if (self.mean.normalize or self.cfg.normalize) else 1.0) * m
+        p = self.pad
+        if p:
+            x = F.pad(x, (p, p, p, p))
+        hh, ww = x.shape[2], x.shape[3]
+        if (hh, ww) != (self.crop_h, self.crop_w):
+            if train:
+                g = self.net.ref_generator
+                oy = int(torch.randint(0, hh - self.crop_h + 1, (1,), generator=g))
+                ox = int(torch.randint(0, ww - self.crop_w + 1, (1,), generator=g))
+            else:
+                oy, ox = (hh - self.crop_h) // 2, (ww - self.crop_w) // 2
+            x = x[:, :, oy:oy + self.crop_h, ox:ox + self.crop_w]
+        if train and self.flip and int(torch.randint(0, 2, (1,), generator=self.net.ref_generator)):
+            x = x.flip(-1)
+        return x
+
+
+# =============================================================================================== conv
+def conv_out(n, k, s, p):
+    return (n + 2 * p - k) // s + 1
+
+
+class Conv2dOp(Op):
+    """Convolution + bias + optional ReLU (src/operator/mod.rs:1366-2003), on the tcgen05 implicit-GEMM kernel."""
+
+    has_params = True
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        cfg = self.cfg
+        h, w, c = prev.out_hwc
+        self.in_c = c
+        k, s, p = cfg.conv_size, cfg.conv_stride, cfg.conv_pad
+        self.P, self.Q = conv_out(h, k, s, p), conv_out(w, k, s, p)
+        self.s2d = False
+        if isinstance(prev, DataOp) and s > 1 and c <= 4 and h == w and prev.mode == "nhwc":
+            f, r2, out_hw, s2d_hw = layout.s2d_geometry(k, s, h + 2 * p)
+            prev.request_s2d(f, s2d_hw, p)
+            self.s2d, self.f, self.r2, self.s2d_hw = True, f, r2, s2d_hw
+        self.cp = prev.out_cp
+        self.out_hwc = (self.P, self.Q, cfg.out_channels)
+        self.out_cp = pad_channels(cfg.out_channels)
+        self.has_relu = cfg.act == C.Act.RECT
+        if cfg.act not in (C.Act.RECT, C.Act.IDENTITY):
+            raise NotImplementedError("only identity and rect activations are implemented (as in the reference)")
+        rs = self.r2 * self.r2 if self.s2d else k * k
+        self.rs = rs
+        self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, rs, self.cp))
+        self.segs = [self.seg_w]
+        self.seg_b = None
+        if getattr(cfg, "bias", True):
+            self.seg_b = ParamSeg(self.name + ".b", (cfg.out_channels,))
+            self.segs.append(self.seg_b)
+        self.wt16 = None
+
+    def alloc(self):
+        super().alloc()
+        if self.net.training_capable and self.wants_prev_delta() and self.cfg.conv_stride == 1:
+            self.wt16 = torch.zeros((self.cp, self.rs, self.out_cp), dtype=torch.bfloat16, device=self.net.device)
+
+    # geometry the kernels see (the s2d form is a stride-1, pad-0 convolution on the rearranged input)
+    def _geom(self):
+        if self.s2d:
+            return self.s2d_hw, self.s2d_hw, self.r2, 1, 0
+        h, w, _ = self.prev.out_hwc
+        return h, w, self.cfg.conv_size, self.cfg.conv_stride, self.cfg.conv_pad
+
+    def forward(self, train, t):
+        h, w, r, s, p = self._geom()
+        ko = self.cfg.out_channels
+        K.conv_fprop_tc(self.prev.out, self.net.batch, h, w, self.cp, self.view(self.seg_w, "params16"), ko, r, r, s,
+                        p, p, self.P, self.Q, self.out, self.out_cp,
+                        bias=self.view(self.seg_b) if self.seg_b else None, relu=self.has_relu, n_valid=ko,
+                        n_store=self.out_cp)
+
+    def backward(self):
+        h, w, r, s, p = self._geom()
+        n, ko = self.net.batch, self.cfg.out_channels
+        rows = n * self.P * self.Q
+        if self.seg_b:
+            K.colsum(self.dout, rows, self.out_cp, ko, self.view(self.seg_b, "grads"))
+        gw = self.view(self.seg_w, "grads")
+        K.conv_wgrad_tc(self.prev.out, n, h, w, self.cp, self.dout, self.out_cp, ko, r, r, s, p, p, self.P, self.Q, gw)
+        if self.s2d:
+            K.zero_s2d_structural(gw, ko, self.r2, self.cp, self.f, self.in_c, self.cfg.conv_size)
+        if self.wants_prev_delta():
+            mask = self.mask_src()
+            w16 = self.view(self.seg_w, "params16")
+            if s == 1:
+                K.pack_dgrad_filters(w16, self.wt16, ko, self.out_cp, r * r, self.cp)
+                K.conv_fprop_tc(self.dout, n, self.P, self.Q, self.out_cp, self.wt16, self.cp, r, r, 1, r - 1 - p,
+                                r - 1 - p, h, w, self.prev.dout, self.cp, mask_src=mask, n_valid=self.in_c,
+                                n_store=self.cp)
+            else:
+                K.conv_direct_dgrad(self.dout, w16, self.prev.dout, mask, n, h, w, self.cp, ko, self.out_cp, r, r, s,
+                                    p, p, self.P, self.Q)
+
+    # ---- parameters in reference layout
+    def _w_ref(self, w_int):
+        k = self.cfg.conv_size
+        if self.s2d:
+            return layout.s2d_weight_from_internal(w_int, self.in_c, k, self.f)
+        return layout.conv_weight_from_internal(w_int, self.in_c, k, k)
+
+    def _w_int(self, w_oihw):
+        if self.s2d:
+            return layout.s2d_weight_to_internal(w_oihw, self.f, self.cp)
+        return layout.conv_weight_to_internal(w_oihw, self.cp)
+
+    def init_params(self, rng):
+        cfg = self.cfg
+        k = cfg.conv_size
+        if cfg.init_weights.kind == "xavier":
+            raise NotImplementedError("Xavier initialisation is not defined for convolutions in the reference "
+                                      "(src/operator/mod.rs:1576-1579)")
+        w = _draw(cfg.init_weights, rng, (cfg.out_channels, self.in_c, k, k), k * k * self.in_c, cfg.out_channels)
+        self.view(self.seg_w).copy_(self._w_int(w))
+        if self.seg_b:
+            self.view(self.seg_b).zero_()
+
+    def encode_params(self):
+        cfg = self.cfg
+        k = cfg.conv_size
+        w = self._w_ref(self.view(self.seg_w).detach().float().cpu())
+        out = [(w.reshape(-1), (k * k * self.in_c, cfg.out_channels))]
+        if self.seg_b:
+            out.append((self.view(self.seg_b).detach().float().cpu(), (1, cfg.out_channels)))
+        return out
+
+    def decode_params(self, arrays):
+        cfg = self.cfg
+        k = cfg.conv_size
+        w = torch.as_tensor(arrays[0][0]).reshape(cfg.out_channels, self.in_c, k, k)
+        self.view(self.seg_w).copy_(self._w_int(w))
+        if self.seg_b:
+            self.view(self.seg_b).copy_(torch.as_tensor(arrays[1][0]).reshape(-1))
+            return 2
+        return 1
+
+    def ref_forward(self, x, train, t):
+        cfg = self.cfg
+        w = self._w_ref(self.view(self.seg_w))
+        b = self.view(self.seg_b) if self.seg_b else None
+        y = F.conv2d(x, w, b, stride=cfg.conv_stride, padding=cfg.conv_pad)
+        return torch.relu(y) if self.has_relu else y
+
+
+# =============================================================================================== affine
+class AffineOp(Op):
+    """Fully connected layer + bias + optional ReLU (src/operator/mod.rs:838-1364).
+
+    Forward and data-gradient split their reduction over many CTAs (the batch gives a single 128-row tile),
+    accumulate in an fp32 workspace with red.add and finish with a small bias/activation kernel.
+    """
+
+    has_params = True
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        cfg = self.cfg
+        if isinstance(prev, DataOp) and prev.mode == "nhwc" and prev.out_hwc[0] == prev.out_hwc[1]:
+            prev.request_flat()
+        h, w, c = prev.out_hwc
+        self.in_hw_c = (h, w, c)
+        if isinstance(prev, DataOp) and prev.mode == "flat":
+            self.in_pixel_cp = c            # flat mode packs pixels tightly, padding only at the end
+            self.k_in = prev.out_cp
+        else:
+            self.in_pixel_cp = prev.out_cp
+            self.k_in = h * w * prev.out_cp
+        self.out_hwc = (1, 1, cfg.out_channels)
+        self.out_cp = pad_channels(cfg.out_channels)
+        self.has_relu = cfg.act == C.Act.RECT
+        self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, self.k_in))
+        self.seg_b = ParamSeg(self.name + ".b", (cfg.out_channels,))
+        self.segs = [self.seg_w, self.seg_b]
+
+    def alloc(self):
+        super().alloc()
+        n = self.net.batch
+        self.ws = torch.zeros((n, self.out_cp), dtype=torch.float32, device=self.net.device)
+        self.ws_in = None
+        if self.net.training_capable and self.wants_prev_delta():
+            self.ws_in = torch.zeros((n, self.k_in), dtype=torch.float32, device=self.net.device)
+
+    @staticmethod
+    def _bn_cap(n_cols, m_tiles=1):
+        target = max(1, 148 // m_tiles)
+        bn = (n_cols + target - 1) // target
+        bn = (bn + 63) // 64 * 64
+        return max(64, min(256, bn))
+
+    def forward(self, train, t):
+        n, ko = self.net.batch, self.cfg.out_channels
+        x = self.prev.out
+        K.gemm_tc(x, 0, self.k_in, self.view(self.seg_w, "params16"), 0, self.k_in, n, ko, self.k_in, self.ws,
+                  self.out_cp, epi=K.EPI_F32_ATOMIC, n_store=self.out_cp, split_k=0, bn_cap=self._bn_cap(ko))
+        K.bias_act(self.ws, n, self.out_cp, ko, self.view(self.seg_b), self.has_relu, self.out)
+
+    def backward(self):
+        n, ko = self.net.batch, self.cfg.out_channels
+        K.colsum(self.dout, n, self.out_cp, ko, self.view(self.seg_b, "grads"))
+        # dW[out][in] += dY^T X : both operands are read "MN-major" straight from their row-major buffers
+        K.gemm_tc(self.dout, 1, self.out_cp, self.prev.out, 1, self.k_in, ko, self.k_in, n,
+                  self.view(self.seg_w, "grads"), self.k_in, epi=K.EPI_F32_ATOMIC, n_store=self.k_in, split_k=1)
+        if self.wants_prev_delta():
+            K.gemm_tc(self.dout, 0, self.out_cp, self.view(self.seg_w, "params16"), 1, self.k_in, n, self.k_in,
+                      ko, self.ws_in, self.k_in, epi=K.EPI_F32_ATOMIC, n_store=self.k_in, split_k=0,
+                      bn_cap=self._bn_cap(self.k_in))
+            K.bias_act(self.ws_in, n, self.k_in, self.k_in, None, False, self.prev.dout, mask_src=self.mask_src())
+
+    def _w_ref(self, w_int):
+        h, w, c = self.in_hw_c
+        o = self.cfg.out_channels
+        tight = w_int[:, : h * w * self.in_pixel_cp] if self.in_pixel_cp == c else w_int
+        return layout.affine_weight_from_internal(tight, c, h, w, self.in_pixel_cp)
+
+    def _w_int(self, w_ref):
+        h, w, c = self.in_hw_c
+        t = layout.affine_weight_to_internal(w_ref, c, h, w, self.in_pixel_cp)
+        out = torch.zeros((w_ref.shape[0], self.k_in), dtype=w_ref.dtype)
+        out[:, : t.shape[1]] = t
+        return out
+
+    def init_params(self, rng):
+        cfg = self.cfg
+        h, w, c = self.in_hw_c
+        fan_in = h * w * c
+        wr = _draw(cfg.init_weights, rng, (cfg.out_channels, fan_in), fan_in, cfg.out_channels)
+        self.view(self.seg_w).copy_(self._w_int(wr))
+        self.view(self.seg_b).zero_()
+
+    def encode_params(self):
+        h, w, c = self.in_hw_c
+        o = self.cfg.out_channels
+        wr = self._w_ref(self.view(self.seg_w).detach().float().cpu())
+        return [(wr.reshape(-1), (h * w * c, o)), (self.view(self.seg_b).detach().float().cpu(), (1, o))]
+
+    def decode_params(self, arrays):
+        h, w, c = self.in_hw_c
+        o = self.cfg.out_channels
+        self.view(self.seg_w).copy_(self._w_int(torch.as_tensor(arrays[0][0]).reshape(o, h * w * c)))
+        self.view(self.seg_b).copy_(torch.as_tensor(arrays[1][0]).reshape(-1))
+        return 2
+
+    def ref_forward(self, x, train, t):
+        wr = self._w_ref(self.view(self.seg_w))
+        y = x.flatten(1) @ wr.t() + self.view(self.seg_b)
+        y = torch.relu(y) if self.has_relu else y
+        return y.reshape(y.shape[0], -1, 1, 1)
+
+
+# =============================================================================================== pool / lrn / dropout
+class Pool2dOp(Op):
+    """Max / average pooling with optional fused ReLU (src/operator/mod.rs:2005-2132; act_func on pool layers
+    appears in examples/imagenet_alexnet.model:38-44)."""
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        cfg = self.cfg
+        h, w, c = prev.out_hwc
+        k, s, p = cfg.pool_size, cfg.pool_stride, cfg.pool_pad
+
+        def out(n):
+            if cfg.ceil_mode:
+                o = -(-(n + 2 * p - k) // s) + 1
+                if (o - 1) * s >= n + p:   # the last window must start inside the image or its left padding
+                    o -= 1
+                return o
+            return (n + 2 * p - k) // s + 1
+
+        self.P, self.Q = out(h), out(w)
+        self.out_hwc = (self.P, self.Q, c)
+        self.out_cp = prev.out_cp
+        self.is_max = cfg.kind == C.PoolKind.MAX
+        self.fused_relu = cfg.act == C.Act.RECT
+        # the output is non-negative if this op or its producer applied a ReLU; consumers then mask by it
+        self.has_relu = self.fused_relu
+        self.idx = None
+
+    def alloc(self):
+        super().alloc()
+        if self.is_max:
+            self.idx = torch.zeros(self.out.shape, dtype=torch.uint8, device=self.net.device)
+
+    def forward(self, train, t):
+        h, w, _ = self.prev.out_hwc
+        cfg = self.cfg
+        K.pool_fwd(self.prev.out, self.out, self.idx, self.net.batch, h, w, self.out_cp, self.P, self.Q, cfg.pool_size,
+                   cfg.pool_stride, cfg.pool_pad, self.is_max, self.fused_relu)
+
+    def backward(self):
+        if not self.wants_prev_delta():
+            return
+        h, w, _ = self.prev.out_hwc
+        cfg = self.cfg
+        K.pool_bwd(self.dout, self.idx, self.out if (self.fused_relu and not self.is_max) else None, self.prev.dout,
+                   self.mask_src(), self.net.batch, h, w, self.out_cp, self.P, self.Q, cfg.pool_size, cfg.pool_stride,
+                   cfg.pool_pad, self.is_max)
+
+    def ref_forward(self, x, train, t):
+        cfg = self.cfg
+        if self.is_max:
+            y = F.max_pool2d(x, cfg.pool_size, cfg.pool_stride, cfg.pool_pad, ceil_mode=cfg.ceil_mode)
+        else:
+            y = F.avg_pool2d(x, cfg.pool_size, cfg.pool_stride, cfg.pool_pad, ceil_mode=cfg.ceil_mode,
+                             count_include_pad=True)
+        return torch.relu(y) if self.fused_relu else y
+
+
+class LrnOp(Op):
+    """Cross-channel local response normalisation (a real one; the reference's is a pass-through stub,
+    src/layer.rs:1846-1899)."""
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        self.out_hwc = prev.out_hwc
+        self.out_cp = prev.out_cp
+        cfg = self.cfg
+        self.alpha_eff = cfg.scale / cfg.cross_size if cfg.alpha_div_n else cfg.scale
+        self.has_relu = False
+
+    def forward(self, train, t):
+        h, w, _ = self.out_hwc
+        cfg = self.cfg
+        K.lrn_fwd(self.prev.out, self.out, self.net.batch * h * w, self.out_cp, cfg.cross_size, self.alpha_eff,
+                  cfg.power, cfg.min_div)
+
+    def backward(self):
+        if not self.wants_prev_delta():
+            return
+        h, w, _ = self.out_hwc
+        cfg = self.cfg
+        K.lrn_bwd(self.prev.out, self.dout, self.prev.dout, self.mask_src(), self.net.batch * h * w, self.out_cp,
+                  cfg.cross_size, self.alpha_eff, cfg.power, cfg.min_div)
+
+    def ref_forward(self, x, train, t):
+        cfg = self.cfg
+        return F.local_response_norm(x, cfg.cross_size, alpha=self.alpha_eff * cfg.cross_size, beta=cfg.power,
+                                     k=cfg.min_div)
+
+
+class DropoutOp(Op):
+    """Inverted dropout with an in-kernel Philox mask (src/operator/mod.rs:2134-2255); inference is a copy."""
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        self.out_hwc = prev.out_hwc
+        self.out_cp = prev.out_cp
+        self.has_relu = False
+        self.stream_id = net.next_stream_id()
+        self._t = 0
+
+    def forward(self, train, t):
+        n = self.out.numel()
+        self._t = t
+        if train:
+            K.dropout(self.prev.out, self.out, n, self.cfg.drop_ratio, self.net.dropout_seed, self.stream_id,
+                      step_ptr=self.net.step_counter)
+        else:
+            self.out.copy_(self.prev.out)
+
+    def backward(self):
+        if not self.wants_prev_delta():
+            return
+        K.dropout(self.dout, self.prev.dout, self.dout.numel(), self.cfg.drop_ratio, self.net.dropout_seed,
+                  self.stream_id, mask_src=self.mask_src(), step_ptr=self.net.step_counter)
+
+    def ref_forward(self, x, train, t):
+        if not train:
+            return x
+        p = self.cfg.drop_ratio
+        keep = (torch.rand(x.shape, generator=self.net.ref_generator) >= p).to(x.dtype)
+        return x * keep / (1.0 - p)
+
+
+# =============================================================================================== loss
+class SoftmaxKLLossOp(Op):
+    """Softmax + cross-entropy head with per-sample weights (src/operator/loss.rs:20-262)."""
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        self.k = self.cfg.num_categories
+        h, w, c = prev.out_hwc
+        if h * w * c != self.k:
+            raise ValueError(f"loss expects {self.k} inputs, previous operator produces {h * w * c}")
+        self.out_hwc = prev.out_hwc
+        self.out_cp = prev.out_cp
+        self.cat_weights = None
+
+    def alloc(self):
+        dev = self.net.device
+        n = self.net.batch
+        self.labels = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.weights = None
+        self.loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.correct = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.argmax = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.loss_per = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.probs = None
+
+    def load_labels(self, labels, non_blocking=True):
+        self.labels.copy_(labels.reshape(-1), non_blocking=non_blocking)
+
+    def load_weights(self, weights):
+        if self.weights is None:
+            self.weights = torch.zeros(self.net.batch, dtype=torch.float32, device=self.net.device)
+        self.weights.copy_(weights)
+
+    def forward(self, train, t):
+        delta = self.prev.dout if (train and self.prev.dout is not None) else None
+        K.softmax_ce(self.prev.out, self.net.batch, self.k, self.out_cp, self.labels, self.weights,
+                     self.net.sample_weight, delta, probs=self.probs, loss_sum=self.loss_sum, correct=self.correct,
+                     loss_per=self.loss_per, argmax_out=self.argmax, cat_weights=self.cat_weights)
+
+    def ref_loss(self, logits, labels, weights=None):
+        """Returns (weighted loss sum, number correct, argmax)."""
+        logits = logits.flatten(1)
+        lp = F.log_softmax(logits, dim=1)
+        nll = -lp.gather(1, labels.long().reshape(-1, 1)).squeeze(1)
+        w = weights if weights is not None else torch.full_like(nll, self.net.sample_weight)
+        am = logits.argmax(1)
+        return (w * nll).sum(), int((am == labels.long()).sum()), am
+
+
+class MarginalizedSoftmaxIndLossOp(SoftmaxKLLossOp):
+    """Softmax head whose gradient is weighted per category (src/operator/loss.rs:264-407)."""
+
+    def set_category_weights(self, cw):
+        self.cat_weights = torch.as_tensor(cw, dtype=torch.float32, device=self.net.device)

@@ -18,6 +18,7 @@ from .. import _native
 from .._native import check, ptr, stream_handle
 
 EPI_BF16, EPI_F32_STORE, EPI_F32_ATOMIC = 0, 1, 2
+LAUNCHES = _native.LAUNCH_COUNT
 
 
 def pad_channels(c: int) -> int:
@@ -100,9 +101,9 @@ def bias_act(acc, rows, ld, n_valid, bias, relu, y, mask_src=None, rezero=True):
                                      int(rezero), stream_handle()), "rb_bias_act")
 
 
-def dropout(x, y, n, p, seed, stream_id, mask_src=None):
+def dropout(x, y, n, p, seed, stream_id, mask_src=None, step_ptr=None):
     check(_native.cuda().rb_dropout(ptr(x), ptr(y), ptr(mask_src), n, float(p), int(seed) & (2**64 - 1),
-                                    int(stream_id) & 0xFFFFFFFF, stream_handle()), "rb_dropout")
+                                    int(stream_id) & 0xFFFFFFFF, ptr(step_ptr), stream_handle()), "rb_dropout")
 
 
 def relu_mask(d, y, n):
@@ -158,7 +159,7 @@ def axpby(x, y, n, a, b):
 
 
 def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi_y, lo_x, hi_x, random_crop,
-             random_flip, per_batch, scale, mean_scale, pca_sigma, pca_vals, pca_vecs, seed, step):
+             random_flip, per_batch, scale, mean_scale, pca_sigma, pca_vals, pca_vecs, seed, step, step_ptr=None):
     import ctypes as C_
     pv = (C_.c_float * 3)(*pca_vals) if pca_vals is not None else None
     pe = (C_.c_float * 9)(*pca_vecs) if pca_vecs is not None else None
@@ -167,7 +168,8 @@ def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi
                                      float(scale), float(mean_scale), float(pca_sigma),
                                      C_.cast(pv, C_.c_void_p) if pv is not None else None,
                                      C_.cast(pe, C_.c_void_p) if pe is not None else None,
-                                     int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF, stream_handle()), "rb_input_u8")
+                                     int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF, ptr(step_ptr), stream_handle()),
+          "rb_input_u8")
 
 
 def synth_normal(dst, pixels, C, Cp, seed, step):

@@ -1,0 +1,111 @@
+"""The CUDA execution path of the network container against its own CPU reference path (GPU only)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from rembrandt_b200.models import zoo
+from rembrandt_b200.models.config import (Act, AffineCfg, Conv2dCfg, Data3dCfg, DropoutCfg, LrnCfg, ParamsInit,
+                                          Pool2dCfg, PoolKind, SequentialOperatorConfig, SoftmaxKLLossCfg)
+from rembrandt_b200.models.net import Net
+from rembrandt_b200.ops import native_ops as K
+from rembrandt_b200.optim.sgd import Momentum
+from rembrandt_b200.optim.stepper import SgdStepper
+
+
+def small_cfg(first_stride=1, hw=20):
+    k = ParamsInit.kaiming()
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((hw, hw, 3), normalize=True))
+    if first_stride > 1:
+        cfg.conv2d(Conv2dCfg(7, first_stride, 0, 24, Act.RECT, k), "conv1")
+    else:
+        cfg.conv2d(Conv2dCfg(3, 1, 1, 24, Act.RECT, k), "conv1")
+    cfg.lrn(LrnCfg(5, 1e-2, 0.75, 2.0), "rnorm1")
+    cfg.pool2d(Pool2dCfg(3, 2, 0, PoolKind.MAX), "pool1")
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 40, Act.IDENTITY, k), "conv2")
+    cfg.pool2d(Pool2dCfg(2, 2, 0, PoolKind.AVERAGE, act=Act.RECT), "pool2")
+    cfg.conv2d(Conv2dCfg(1, 1, 0, 64, Act.RECT, k), "conv3")
+    cfg.affine(AffineCfg(48, Act.RECT, ParamsInit.xavier()), "fc1")
+    cfg.dropout(DropoutCfg(0.0), "drop")
+    cfg.affine(AffineCfg(10, Act.IDENTITY, ParamsInit.xavier()), "fc2")
+    return cfg.softmax_kl_loss(SoftmaxKLLossCfg(10))
+
+
+def run_pair(cfg_fn, batch, hw):
+    g = Net(cfg_fn(), batch, device="cuda", seed=(3, 4))
+    c = Net(cfg_fn(), batch, device="cpu", seed=(3, 4))
+    assert torch.equal(g.params.cpu(), c.params.detach()), "same seed must give the same parameters"
+    # the reference path must see the bf16-rounded weights the kernels use
+    with torch.no_grad():
+        c.params.copy_(g.params16.float().cpu())
+    torch.manual_seed(0)
+    x = torch.randint(0, 256, (batch, 3, hw, hw), dtype=torch.uint8)
+    y = torch.randint(0, 10, (batch,))
+    g.load_batch(x.cuda(), y.cuda().int())
+    c.load_batch(x, y)
+    g.forward(True)
+    g.backward()
+    c.forward(True)
+    c.backward()
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    return g, c
+
+
+@pytest.mark.parametrize("stride,hw", [(1, 20), (2, 31)])
+def test_forward_backward_matches_reference_path(stride, hw):
+    g, c = run_pair(lambda: small_cfg(stride, hw), 6, hw)
+    gl, gc = g.read_stats()
+    cl, cc = c.read_stats()
+    assert abs(gl - cl) < 3e-2 * max(1.0, abs(cl)), (gl, cl)
+    gg, cg = g.grads.cpu(), c.grads
+    for seg in g.segs:
+        a = gg[seg.offset: seg.offset + seg.numel]
+        b = cg[seg.offset: seg.offset + seg.numel]
+        scale = float(b.abs().max().clamp_min(1e-6))
+        err = float((a - b).abs().max())
+        assert err < 6e-2 * scale, f"{seg.name}: max err {err:.4g} vs scale {scale:.4g}"
+
+
+def test_training_reduces_loss_and_matches_cpu_trajectory():
+    cfg_fn = lambda: small_cfg(1, 20)
+    g = Net(cfg_fn(), 16, device="cuda", seed=(5, 6))
+    st = SgdStepper(g, Momentum.UPDATE, 0.9, 5e-4)
+    torch.manual_seed(1)
+    x = torch.randint(0, 256, (16, 3, 20, 20), dtype=torch.uint8).cuda()
+    y = torch.randint(0, 10, (16,)).int().cuda()
+    losses = []
+    for t in range(30):
+        g.load_batch(x, y)
+        g.forward(True, t)
+        g.backward()
+        st.step(0.05)
+        losses.append(g.read_stats()[0])
+    assert losses[-1] < 0.5 * losses[0], losses
+    assert float(g.grads.abs().max()) == 0.0, "the fused step must leave the gradients zeroed"
+    assert K.read_status() == 0
+
+
+def test_checkpoint_blob_round_trip_on_device():
+    g = Net(zoo.lenet(), 8, device="cuda", seed=(7, 8))
+    blob = g.encode_params()
+    p0 = g.params.clone()
+    g.params.zero_()
+    g.decode_params(blob)
+    assert torch.equal(g.params, p0)
+    assert torch.equal(g.params16, p0.bfloat16())
+
+
+def test_alexnet_and_nin_build_and_step():
+    for fn, hw, b in ((zoo.alexnet, 227, 8), (zoo.nin, 224, 4)):
+        net = Net(fn(scale=1.0 / 255.0), b, device="cuda")
+        x = torch.randint(0, 256, (b, 3, hw, hw), dtype=torch.uint8).cuda()
+        y = torch.randint(0, 1000, (b,)).int().cuda()
+        net.load_batch(x, y)
+        net.forward(True)
+        net.backward()
+        loss, _ = net.read_stats()
+        assert 5.0 < loss < 9.0, loss   # ~ln(1000) at random initialisation
+        assert torch.isfinite(net.grads).all()
+        assert K.read_status() == 0
+    assert Net(zoo.alexnet(), 2, device="cpu").params_len == 62378344
