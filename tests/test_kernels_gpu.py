@@ -202,14 +202,15 @@ def test_conv_wgrad_tc(case):
     close(layout.conv_weight_from_internal(dw2, C, R, R), ref, rtol=2e-2)
 
 
-def test_conv_s2d_first_layer_matches_strided_conv():
-    """11x11 stride-4 convolution on 3 channels == 3x3 stride-1 convolution on the space-to-depth input."""
+@pytest.mark.parametrize("ks,st,HW", [(11, 4, 67), (7, 2, 31), (5, 2, 20)])
+def test_conv_s2d_first_layer_matches_strided_conv(ks, st, HW):
+    """A strided k x k convolution on 3 channels == a stride-1 convolution on the space-to-depth input."""
     torch.manual_seed(8)
-    N, C, HW, Ko, ks, st = 2, 3, 67, 96, 11, 4
+    N, C, Ko = 2, 3, 96
     f, r2, out_hw, s2d_hw = layout.s2d_geometry(ks, st, HW)
     cp2 = K.pad_channels(f * f * C)
     x = bf(torch.randn(N, C, HW, HW, device=DEV))
-    w = bf(torch.randn(Ko, C, ks, ks, device=DEV) / 19.0)
+    w = bf(torch.randn(Ko, C, ks, ks, device=DEV) / math.sqrt(C * ks * ks))
     b = torch.randn(Ko, device=DEV)
     xi = layout.s2d_input(x, f, s2d_hw, cp2)
     wi = layout.s2d_weight_to_internal(w, f, cp2).bfloat16()

