@@ -219,3 +219,62 @@ int rb_bn_bwd(const void* x, const void* dy, const void* y_relu, long long rows,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Allocation-free variant (declared and documented in bn_noalloc.h).
+#include "bn_noalloc.h"
+
+namespace rb {
+// Scratch for the per-channel sums: part of the library's device image, one copy per GPU.
+static __device__ __align__(256) float g_bn_noalloc_scratch[2 * RB_BN_NOALLOC_MAX_CHANNELS];
+constexpr int kMaxDevices = 64;
+// Device address of the array above, per device. The array's name is only a host-side handle; kernels
+// must be given the address that cudaGetSymbolAddress returns for the device they run on.
+static float* g_bn_noalloc_ptr[kMaxDevices] = {nullptr};
+}  // namespace rb
+
+extern "C" {
+
+int rb_bn_fwd_train_noalloc(const void* x, long long rows, int C, int c_valid, float eps, float factor, float* mean,
+                            float* istd, float* run_mean, float* run_var, const float* gamma, const float* beta,
+                            const void* residual, void* y, int relu, cudaStream_t stream) {
+  if (C % 8) return RB_BN_NOALLOC_E_CHANNEL_ALIGN;
+  if (C > RB_BN_NOALLOC_MAX_CHANNELS) return RB_BN_NOALLOC_E_TOO_MANY_CHANNELS;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return RB_BN_NOALLOC_E_DEVICE;
+  if (g_bn_noalloc_ptr[dev] == nullptr) {
+    // first call on this device: resolve the array's device address (the device is current here)
+    float* p = nullptr;
+    if (cudaGetSymbolAddress((void**)&p, g_bn_noalloc_scratch) != cudaSuccess || p == nullptr)
+      return RB_BN_NOALLOC_E_SYMBOL;
+    g_bn_noalloc_ptr[dev] = p;
+  }
+  float* sums = g_bn_noalloc_ptr[dev];
+  // the array keeps whatever the previous call left: clear the part this call accumulates into
+  if (cudaMemsetAsync(sums, 0, sizeof(float) * 2 * (size_t)C, stream) != cudaSuccess) return RB_BN_NOALLOC_E_LAUNCH;
+  dim3 grid((C + 255) / 256, 1);
+  long long gy = rows / 64;
+  if (gy < 1) gy = 1;
+  if (gy > 256) gy = 256;
+  grid.y = (unsigned)gy;
+  bn_reduce_kernel<<<grid, 256, 0, stream>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, rows, C, eps, factor, mean, istd, run_mean, run_var);
+  bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, stream>>>((const bf16*)x, mean, istd, gamma, beta,
+                                                                    (const bf16*)residual, (bf16*)y, rows, C, c_valid,
+                                                                    relu);
+  return cudaGetLastError() == cudaSuccess ? RB_BN_NOALLOC_OK : RB_BN_NOALLOC_E_LAUNCH;
+}
+
+const char* rb_bn_noalloc_strerror(int code) {
+  switch (code) {
+    case RB_BN_NOALLOC_OK: return "ok";
+    case RB_BN_NOALLOC_E_CHANNEL_ALIGN: return "channel count must be a multiple of 8";
+    case RB_BN_NOALLOC_E_TOO_MANY_CHANNELS: return "channel count exceeds RB_BN_NOALLOC_MAX_CHANNELS (4096)";
+    case RB_BN_NOALLOC_E_DEVICE: return "current CUDA device could not be determined or its index is >= 64";
+    case RB_BN_NOALLOC_E_SYMBOL: return "cudaGetSymbolAddress failed for the built-in scratch array";
+    case RB_BN_NOALLOC_E_LAUNCH: return "a kernel launch or the scratch-clearing memset failed";
+    default: return "unknown code";
+  }
+}
+
+}  // extern "C"

@@ -40,6 +40,8 @@ def _parse_decls():
 
 def test_every_launcher_is_declared_with_matching_types():
     decls = _parse_decls()
+    # the allocation-free entry point is bound by its own test straight from the C symbol
+    decls = {k: v for k, v in decls.items() if not k.endswith("_noalloc")}
     table = dict(_native._CUDA_SIGS)
     # launchers bound by other modules through _native.register carry their own tables
     from rembrandt_b200.parallel import p2p_kernels
