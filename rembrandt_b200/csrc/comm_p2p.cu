@@ -1,0 +1,478 @@
+// Communication kernels that move data between GPUs themselves: peer-to-peer loads / stores / reductions
+// over NVLink (and NVSwitch multimem instructions where a multicast mapping exists), fused with the maths
+// that follows the exchange.
+//
+//   allreduce_sgd   gradient all-reduce + 1/N + SGD momentum / weight decay + bf16 weight refresh in one
+//                   kernel. Two-shot: rank r reduces shard r of the bucket from every peer's gradient
+//                   buffer, applies the optimizer to its shard of the fp32 master weights (master and
+//                   momentum are therefore sharded), and stores the new bf16 weights into every peer's
+//                   compute copy. One-shot (small buckets): every rank reduces the whole bucket itself.
+//                   op = 1 turns it into a plain in-place fp32 average (exact parameter sync, benchmarks).
+//   publish / gossip_mix   a rank publishes a snapshot of its parameters; a peer pulls it through NVLink and
+//                   applies x <- x - alpha (x - x_peer) in one pass (pair / pull gossip).
+//   push_add / push_finalize   push gossip: vectors are red.add'ed into the target's accumulator.
+//   elastic_pull / elastic_apply   elastic averaging against a centre held by rank 0.
+//
+// Replaces the reference's ring all-reduce (src/arch_new.rs:554-573), its MPI all-reduce through host memory
+// (src/worker/allreduce_dist.rs:211-241) and its gossip / elastic-averaging workers (src/operator/comm.rs:125-296,
+// src/worker/gossip_*.rs, src/worker/elasticserver_dist.rs).
+//
+// Cross-GPU ordering uses per-bucket flag words in peer-visible memory carrying an epoch number; every wait
+// on a flag is bounded (globaltimer deadline) and a wait that runs out sets RB_STATUS_PEER_TIMEOUT in the
+// status word, skips the data movement that depended on it and lets the kernel finish normally.
+// No TMA is used here at all.
+#include "common.cuh"
+#include "ptx.cuh"
+#include "sgd_rules.cuh"
+
+namespace rb {
+
+constexpr int MAX_RANKS = 8;
+constexpr uint64_t PEER_WAIT_NS = 3000000000ull;  // 3 s
+
+struct ArSgdArgs {
+  float* grads[MAX_RANKS];     // peer-visible buffers, identical layout on every rank
+  bf16* w16[MAX_RANKS];        // peer-visible bf16 compute weights (op 0)
+  float* w32[MAX_RANKS];       // optional: peer-visible fp32 masters to keep replicated (op 0)
+  uint32_t* flags[MAX_RANKS];  // peer-visible flag pads: [slot][phase 0/1][source rank]
+  float* w;                    // local master weights
+  float* v;                    // local momentum
+  const float* mc_grads;       // multimem (NVSwitch multicast) address of the gradient buffer, or null
+  bf16* mc_w16;                // multimem address of the bf16 weights, or null
+  uint32_t* epoch_ptr;         // local: last completed epoch of this slot
+  unsigned int* block_counter; // local, zero between launches
+  unsigned int* status;
+  long long off, n, decay_len;
+  int rank, world, slot, one_shot, op;
+  float avg_scale;             // op 1: result = sum * avg_scale
+  SgdHyper h;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// true once *p has reached `epoch` (wrap-around safe); false after the deadline
+__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch) {
+  if ((int32_t)(ld_acquire_sys(p) - epoch) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if ((int32_t)(ld_acquire_sys(p) - epoch) >= 0) return true;
+    if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > PEER_WAIT_NS) return false;
+  }
+}
+__device__ __forceinline__ float4 ld_f4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 mm_ld_reduce_f4(const float* p) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mm_st_f4(void* p, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w) : "memory");
+}
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+  return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+__device__ __forceinline__ uint32_t* flag_at(uint32_t* pad, int slot, int phase, int src) {
+  return pad + ((slot * 2 + phase) * MAX_RANKS + src);
+}
+
+// All threads of the block return the same verdict.
+__device__ __forceinline__ bool start_barrier(uint32_t* const* flags, int rank, int world, int slot, uint32_t epoch,
+                                              unsigned int* status) {
+  if (blockIdx.x == 0 && threadIdx.x < world) {
+    __threadfence_system();
+    st_release_sys(flag_at(flags[threadIdx.x], slot, 0, rank), epoch);
+  }
+  int ok = 1;
+  if (threadIdx.x < world) ok = wait_epoch(flag_at(flags[rank], slot, 0, threadIdx.x), epoch) ? 1 : 0;
+  ok = __syncthreads_and(ok);
+  if (!ok && threadIdx.x == 0) atomicOr(status, RB_STATUS_PEER_TIMEOUT);
+  return ok != 0;
+}
+
+// Called by every thread after its data movement. The last block to arrive tells every peer that this rank
+// is done with the epoch and waits until every peer has said the same, so that when the kernel ends nobody
+// still reads this rank's buffers and every store of a peer into this rank's memory has landed.
+__device__ __forceinline__ void end_barrier(uint32_t* const* flags, int rank, int world, int slot, uint32_t epoch,
+                                            unsigned int* block_counter, uint32_t* epoch_ptr, unsigned int* status) {
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  if (threadIdx.x < world) st_release_sys(flag_at(flags[threadIdx.x], slot, 1, rank), epoch);
+  int ok = 1;
+  if (threadIdx.x < world) ok = wait_epoch(flag_at(flags[rank], slot, 1, threadIdx.x), epoch) ? 1 : 0;
+  ok = __syncthreads_and(ok);
+  if (threadIdx.x == 0) {
+    if (!ok) atomicOr(status, RB_STATUS_PEER_TIMEOUT);
+    *block_counter = 0u;
+    *epoch_ptr = epoch;
+    __threadfence();
+  }
+}
+
+__global__ void __launch_bounds__(512) allreduce_sgd_kernel(const __grid_constant__ ArSgdArgs a) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
+  const bool ready = start_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.status);
+  if (ready) {
+    long long s0 = 0, s1 = a.n;
+    if (!a.one_shot) {
+      long long per = (a.n + a.world - 1) / a.world;
+      per = (per + 7) / 8 * 8;
+      s0 = min(a.n, (long long)a.rank * per);
+      s1 = min(a.n, s0 + per);
+    }
+    const long long stride = (long long)gridDim.x * blockDim.x * 8;
+    for (long long i = s0 + ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < s1; i += stride) {
+      const long long e = a.off + i;
+      float4 g0, g1;
+      if (a.mc_grads) {
+        g0 = mm_ld_reduce_f4(a.mc_grads + e);
+        g1 = mm_ld_reduce_f4(a.mc_grads + e + 4);
+      } else {
+        g0 = ld_f4(a.grads[0] + e);
+        g1 = ld_f4(a.grads[0] + e + 4);
+#pragma unroll
+        for (int p = 1; p < MAX_RANKS; ++p) {
+          if (p < a.world) {
+            g0 = add4(g0, ld_f4(a.grads[p] + e));
+            g1 = add4(g1, ld_f4(a.grads[p] + e + 4));
+          }
+        }
+      }
+      if (a.op == 1) {
+        // plain average, written back to every rank's buffer in place
+        const float s = a.avg_scale;
+        g0 = make_float4(g0.x * s, g0.y * s, g0.z * s, g0.w * s);
+        g1 = make_float4(g1.x * s, g1.y * s, g1.z * s, g1.w * s);
+        if (a.mc_grads) {
+          mm_st_f4(const_cast<float*>(a.mc_grads) + e, g0);
+          mm_st_f4(const_cast<float*>(a.mc_grads) + e + 4, g1);
+        } else {
+#pragma unroll
+          for (int p = 0; p < MAX_RANKS; ++p) {
+            if (p < a.world) {
+              *reinterpret_cast<float4*>(a.grads[p] + e) = g0;
+              *reinterpret_cast<float4*>(a.grads[p] + e + 4) = g1;
+            }
+          }
+        }
+        continue;
+      }
+      SgdHyper h = a.h;
+      if (e >= a.decay_len) h.l2 = 0.f;
+      float4 w0 = *reinterpret_cast<float4*>(a.w + e), w1 = *reinterpret_cast<float4*>(a.w + e + 4);
+      float4 v0 = *reinterpret_cast<float4*>(a.v + e), v1 = *reinterpret_cast<float4*>(a.v + e + 4);
+      sgd_elem(w0.x, g0.x, v0.x, h); sgd_elem(w0.y, g0.y, v0.y, h);
+      sgd_elem(w0.z, g0.z, v0.z, h); sgd_elem(w0.w, g0.w, v0.w, h);
+      sgd_elem(w1.x, g1.x, v1.x, h); sgd_elem(w1.y, g1.y, v1.y, h);
+      sgd_elem(w1.z, g1.z, v1.z, h); sgd_elem(w1.w, g1.w, v1.w, h);
+      *reinterpret_cast<float4*>(a.w + e) = w0;
+      *reinterpret_cast<float4*>(a.w + e + 4) = w1;
+      *reinterpret_cast<float4*>(a.v + e) = v0;
+      *reinterpret_cast<float4*>(a.v + e + 4) = v1;
+      uint4 packed;
+      {
+        __nv_bfloat162 b0 = __floats2bfloat162_rn(w0.x, w0.y), b1 = __floats2bfloat162_rn(w0.z, w0.w);
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(w1.x, w1.y), b3 = __floats2bfloat162_rn(w1.z, w1.w);
+        packed.x = *reinterpret_cast<uint32_t*>(&b0);
+        packed.y = *reinterpret_cast<uint32_t*>(&b1);
+        packed.z = *reinterpret_cast<uint32_t*>(&b2);
+        packed.w = *reinterpret_cast<uint32_t*>(&b3);
+      }
+      if (a.one_shot) {
+        *reinterpret_cast<uint4*>(a.w16[a.rank] + e) = packed;
+      } else if (a.mc_w16) {
+        mm_st_f4(a.mc_w16 + e, make_float4(__uint_as_float(packed.x), __uint_as_float(packed.y),
+                                           __uint_as_float(packed.z), __uint_as_float(packed.w)));
+      } else {
+#pragma unroll
+        for (int p = 0; p < MAX_RANKS; ++p)
+          if (p < a.world) *reinterpret_cast<uint4*>(a.w16[p] + e) = packed;
+      }
+      if (!a.one_shot && a.w32[0]) {
+#pragma unroll
+        for (int p = 0; p < MAX_RANKS; ++p) {
+          if (p < a.world && p != a.rank) {
+            *reinterpret_cast<float4*>(a.w32[p] + e) = w0;
+            *reinterpret_cast<float4*>(a.w32[p] + e + 4) = w1;
+          }
+        }
+      }
+    }
+  }
+  end_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.block_counter, a.epoch_ptr, a.status);
+}
+
+// ------------------------------------------------------------------------------------------ gossip
+struct MixArgs {
+  uint32_t* flags[MAX_RANKS];
+  float* w;               // local parameters (updated in place)
+  bf16* w16;              // local bf16 copy (refreshed), may be null
+  float* pub_local;       // local published snapshots: two buffers of `n` back to back
+  const float* pub_peer;  // the peer's published snapshots (same layout), P2P address
+  float* acc_target;      // push gossip: the target's accumulator (P2P) / own accumulator in finalize
+  float* count_target;    // push gossip: the target's receive counter
+  uint32_t* epoch_ptr;
+  unsigned int* block_counter;
+  unsigned int* status;
+  long long n;
+  int rank, world, slot, peer;
+  int wait_peer;          // 1: wait until the peer has published this epoch (synchronous gossip)
+  float alpha;            // mixing weight: x <- (1-alpha) x + alpha x_peer
+  float w_self;           // push gossip: weight of the own vector
+};
+
+// pub[epoch & 1] <- w, then tell every peer that epoch is published. Before overwriting the buffer last used
+// two epochs ago, wait until every peer has reported being done with that epoch.
+__global__ void __launch_bounds__(512) publish_kernel(const __grid_constant__ MixArgs a) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
+  int ok = 1;
+  if (epoch > 2u && threadIdx.x < a.world && threadIdx.x != a.rank)
+    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 1, threadIdx.x), epoch - 2u) ? 1 : 0;
+  ok = __syncthreads_and(ok);
+  if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
+  float* dst = a.pub_local + (size_t)(epoch & 1u) * a.n;
+  const long long n4 = a.n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x)
+    reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(a.w)[i];
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 0, a.rank), epoch);
+    if (threadIdx.x == 0) *a.block_counter = 0u;  // epoch_ptr advances in the mix kernel that follows
+  }
+}
+
+// x <- (1 - alpha) x + alpha x_peer, reading the peer's published snapshot of this epoch over NVLink.
+__global__ void __launch_bounds__(512) gossip_mix_kernel(const __grid_constant__ MixArgs a) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
+  int ok = 1;
+  if (a.wait_peer && a.peer != a.rank && threadIdx.x == 0)
+    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, a.peer), epoch) ? 1 : 0;
+  ok = __syncthreads_and(ok);
+  if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
+  // An asynchronous puller takes whichever snapshot the peer published last (nothing yet: no mixing). Blocks
+  // sample the peer's epoch independently, so an asynchronous pull may combine two consecutive snapshots.
+  __shared__ uint32_t s_pe;
+  if (threadIdx.x == 0)
+    s_pe = a.wait_peer ? epoch : ld_acquire_sys(flag_at(a.flags[a.rank], a.slot, 0, a.peer));
+  __syncthreads();
+  const uint32_t pe = s_pe;
+  if (ok && a.peer != a.rank && pe != 0u) {
+    const float* src = a.pub_peer + (size_t)(pe & 1u) * a.n;
+    const long long n4 = a.n / 4;
+    const float al = a.alpha, be = 1.f - a.alpha;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+      const float4 p = ld_f4(src + i * 4);
+      float4 x = reinterpret_cast<float4*>(a.w)[i];
+      x = make_float4(be * x.x + al * p.x, be * x.y + al * p.y, be * x.z + al * p.z, be * x.w + al * p.w);
+      reinterpret_cast<float4*>(a.w)[i] = x;
+      if (a.w16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(a.w16)[i] = o;
+      }
+    }
+  }
+  // last block: report "done with this epoch" to every peer and advance the local epoch
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {
+    if (threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 1, a.rank), epoch);
+    if (threadIdx.x == 0) {
+      *a.block_counter = 0u;
+      *a.epoch_ptr = epoch;
+    }
+  }
+}
+
+// Push gossip, step 1: add this rank's published snapshot into the target's accumulator and count it.
+__global__ void __launch_bounds__(512) push_add_kernel(const __grid_constant__ MixArgs a) {
+  const long long n4 = a.n / 4;
+  if (a.peer != a.rank) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+      const float4 x = reinterpret_cast<const float4*>(a.w)[i];
+      asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.acc_target + i * 4), "f"(x.x), "f"(x.y),
+                   "f"(x.z), "f"(x.w) : "memory");
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(a.count_target, 1.f);
+  }
+}
+
+// Push gossip, step 2 (after a barrier): x <- (w_self x + acc) / (w_self + count); accumulator cleared.
+__global__ void __launch_bounds__(512) push_finalize_kernel(const __grid_constant__ MixArgs a) {
+  const float cnt = *reinterpret_cast<volatile float*>(a.count_target);
+  const float inv = 1.f / (a.w_self + cnt);
+  const long long n4 = a.n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    float4 x = reinterpret_cast<float4*>(a.w)[i];
+    const float4 s = reinterpret_cast<float4*>(a.acc_target)[i];
+    if (cnt > 0.f) {
+      x = make_float4((a.w_self * x.x + s.x) * inv, (a.w_self * x.y + s.y) * inv, (a.w_self * x.z + s.z) * inv,
+                      (a.w_self * x.w + s.w) * inv);
+      reinterpret_cast<float4*>(a.w)[i] = x;
+      reinterpret_cast<float4*>(a.acc_target)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (a.w16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(a.w16)[i] = o;
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    *a.count_target = 0.f;
+    *a.block_counter = 0u;
+  }
+}
+
+// Elastic averaging, client side: read the centre (rank 0's memory), move toward it, and add the opposite
+// pull into the centre's delta accumulator:  x <- x - beta (x - c) ;  delta_centre += beta (x - c).
+__global__ void __launch_bounds__(512) elastic_pull_kernel(const __grid_constant__ MixArgs a) {
+  const long long n4 = a.n / 4;
+  const float be = a.alpha;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 c = ld_f4(a.pub_peer + i * 4);
+    float4 x = reinterpret_cast<float4*>(a.w)[i];
+    const float4 d = make_float4(be * (x.x - c.x), be * (x.y - c.y), be * (x.z - c.z), be * (x.w - c.w));
+    x = make_float4(x.x - d.x, x.y - d.y, x.z - d.z, x.w - d.w);
+    reinterpret_cast<float4*>(a.w)[i] = x;
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a.acc_target + i * 4), "f"(d.x), "f"(d.y),
+                 "f"(d.z), "f"(d.w) : "memory");
+    if (a.w16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(a.w16)[i] = o;
+    }
+  }
+}
+
+// Elastic averaging, centre side (rank 0): centre += delta ; delta = 0.
+__global__ void elastic_apply_kernel(float* __restrict__ center, float* __restrict__ delta, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    center[i] += delta[i];
+    delta[i] = 0.f;
+  }
+}
+
+// Cross-GPU barrier as a kernel of one block (orders the kernels before it on every rank's stream against
+// the kernels after it on every other rank's stream).
+struct BarrierArgs {
+  uint32_t* flags[MAX_RANKS];
+  uint32_t* epoch_ptr;
+  unsigned int* status;
+  int rank, world, slot;
+};
+__global__ void barrier_kernel(const __grid_constant__ BarrierArgs a) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
+  __threadfence_system();
+  if (threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 0, a.rank), epoch);
+  int ok = 1;
+  if (threadIdx.x < a.world) ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch) ? 1 : 0;
+  ok = __syncthreads_and(ok);
+  if (threadIdx.x == 0) {
+    if (!ok) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
+    *a.epoch_ptr = epoch;
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" {
+
+// Host-side mirror of ArSgdArgs with plain pointers (filled through ctypes).
+int rb_allreduce_sgd_p2p(const void* args, int blocks, cudaStream_t st) {
+  const ArSgdArgs* a = reinterpret_cast<const ArSgdArgs*>(args);
+  if (a->world < 1 || a->world > MAX_RANKS || (a->n % 8) || (a->off % 8)) return -10;
+  if (blocks < 1) blocks = 1;
+  allreduce_sgd_kernel<<<blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_publish_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4) return -10;
+  publish_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_gossip_mix_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4) return -10;
+  gossip_mix_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_push_add_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4) return -10;
+  push_add_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_push_finalize(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4) return -10;
+  push_finalize_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_elastic_pull_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4) return -10;
+  elastic_pull_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_elastic_apply(float* center, float* delta, long long n, cudaStream_t st) {
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  if (blocks < 1) blocks = 1;
+  elastic_apply_kernel<<<(int)blocks, 256, 0, st>>>(center, delta, n);
+  return RB_LAUNCH_OK();
+}
+
+int rb_barrier_p2p(const void* args, cudaStream_t st) {
+  const BarrierArgs* a = reinterpret_cast<const BarrierArgs*>(args);
+  barrier_kernel<<<1, 32, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+}  // extern "C"

@@ -3,58 +3,19 @@
 // The reference does this as 6-8 saxpy/sscal launches per tensor (regularize / accumulate_grads /
 // update_params / reset, src/operator/mod.rs:1178-1363 and src/opt/sgd/new.rs:358-495).
 //
-// Momentum rules (src/opt/sgd/new.rs:377-463), g' = grad_scale * g + l2 * w :
-//   0 Zero             v = -lr g'            w += v
-//   1 Update           v = mu v - lr g'      w += v
-//   2 UpdateNesterov   w is stored at the look-ahead point w + mu v:
-//                      w -= mu v_old ; v = mu v_old - lr g' ; w += v ; w += mu v
-//   3 Gradient         v = mu v + g'         w -= lr v
-//   4 GradientNesterov v = mu v + g'         w -= lr g' + lr mu v
-//   5 GradDecay        w -= lr g' ; g = mu g'   (gen-2 rule, src/opt_new.rs:321-327; no velocity buffer)
-// phase bits: 1 = regularise + accumulate into v, 2 = apply to w (and refresh the bf16 copy), 4 = zero g.
+// The rules themselves are in sgd_rules.cuh.
 #include "common.cuh"
+#include "sgd_rules.cuh"
 
 namespace rb {
 
-struct SgdArgs {
+struct SgdArgs : SgdHyper {
   float* w;
   float* g;
   float* v;
   bf16* w16;   // optional
   long long n;
-  float lr, mu, l2, grad_scale;
-  int mode, phase;
 };
-
-__device__ __forceinline__ void sgd_elem(float& w, float& g, float& v, const SgdArgs& a) {
-  const bool acc = a.phase & 1, upd = a.phase & 2, zero = a.phase & 4;
-  float gp = a.grad_scale * g + a.l2 * w;
-  switch (a.mode) {
-    case 0:
-    case 1:
-      if (acc) v = (a.mode == 0 ? 0.f : a.mu * v) - a.lr * gp;
-      if (upd) w += v;
-      break;
-    case 2:
-      if (acc) { w -= a.mu * v; v = a.mu * v - a.lr * gp; }
-      if (upd) w += v + a.mu * v;
-      break;
-    case 3:
-      if (acc) v = a.mu * v + gp;
-      if (upd) w -= a.lr * v;
-      break;
-    case 4:
-      // the update needs g', so regularisation is recomputed when the phases are split
-      if (acc) v = a.mu * v + gp;
-      if (upd) w -= a.lr * gp + a.lr * a.mu * v;
-      break;
-    case 5:
-      if (upd) w -= a.lr * gp;
-      g = a.mu * gp;
-      break;
-  }
-  if (zero && a.mode != 5) g = 0.f;
-}
 
 __global__ void sgd_fused_kernel(SgdArgs a) {
   const long long n4 = a.n / 4;
@@ -116,7 +77,9 @@ extern "C" {
 int rb_sgd_fused(float* w, float* g, float* v, void* w16, long long n, float lr, float mu, float l2, float grad_scale,
                  int mode, int phase, cudaStream_t st) {
   if (n <= 0) return 0;
-  SgdArgs a{w, g, v, (bf16*)w16, n, lr, mu, l2, grad_scale, mode, phase};
+  SgdArgs a;
+  a.lr = lr; a.mu = mu; a.l2 = l2; a.grad_scale = grad_scale; a.mode = mode; a.phase = phase;
+  a.w = w; a.g = g; a.v = v; a.w16 = (bf16*)w16; a.n = n;
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;

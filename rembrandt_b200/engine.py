@@ -84,10 +84,10 @@ class StepEngine:
         self.net.input_op.stage.copy_(self._stage_imgs[slot], non_blocking=True)
         self.net.loss_op.labels.copy_(self._stage_lbls[slot], non_blocking=True)
 
-    def _fwd_bwd(self, train=True):
+    def _fwd_bwd(self, train=True, hook=None):
         self.net.forward(train, None)
         if train:
-            self.net.backward()
+            self.net.backward(hook)
         if self.is_cuda:
             self.net.step_counter.add_(1)
 
@@ -97,7 +97,7 @@ class StepEngine:
         lr = self.lr
         communicate = c.num_workers() > 1 and (self.iter % max(1, o.comm_interval) == 0)
         if o.sync_order == SyncOrder.SYNC_GRADS_THEN_STEP:
-            if communicate and hasattr(c, "fused_grads_step"):
+            if self._overlapped():
                 c.fused_grads_step(st, lr)
             else:
                 if communicate:
@@ -121,6 +121,11 @@ class StepEngine:
         else:
             raise ValueError(o.sync_order)
 
+    def _overlapped(self) -> bool:
+        o, c = self.opt, self.comm
+        return (c.num_workers() > 1 and hasattr(c, "on_op_backward") and
+                o.sync_order == SyncOrder.SYNC_GRADS_THEN_STEP and max(1, o.comm_interval) == 1)
+
     def _graph_safe_update(self) -> bool:
         c = self.comm
         return c.num_workers() <= 1 or getattr(c, "graph_safe", False)
@@ -129,12 +134,17 @@ class StepEngine:
         """Forward + backward (+ update when this batch completes a minibatch) on the compute stream."""
         key = (last_of_iteration, self.lr if last_of_iteration else 0.0)
         full = last_of_iteration and self._graph_safe_update()
+        hook = None
+        if last_of_iteration and self._overlapped():
+            # the exchange of a gradient bucket starts from inside backward, as soon as the bucket is complete
+            self.comm.prepare(self.stepper, self.lr)
+            hook = self.comm.on_op_backward
         if self.use_graph:
             g = self._graphs.get(key)
             if g is None:
                 # first use of this configuration runs eagerly (allocations, lazy init); the second captures
                 before = K.LAUNCHES[0]
-                self._fwd_bwd()
+                self._fwd_bwd(hook=hook)
                 if full:
                     self._update()
                 self.launches_per_step = K.LAUNCHES[0] - before
@@ -144,7 +154,7 @@ class StepEngine:
                     torch.cuda.current_stream().synchronize()
                     g = torch.cuda.CUDAGraph()
                     with torch.cuda.graph(g, stream=torch.cuda.current_stream()):
-                        self._fwd_bwd()
+                        self._fwd_bwd(hook=hook)
                         if full:
                             self._update()
                     self._graphs[key] = g
@@ -153,7 +163,7 @@ class StepEngine:
                 self._update()
         else:
             before = K.LAUNCHES[0]
-            self._fwd_bwd()
+            self._fwd_bwd(hook=hook)
             if last_of_iteration:
                 self._update()
             self.launches_per_step = K.LAUNCHES[0] - before

@@ -252,10 +252,14 @@ class Net:
         self._cpu_logits = x.detach()
         return None
 
-    def backward(self):
+    def backward(self, hook=None):
+        """Backward in reverse operator order. `hook(i)` is called after operator i has produced its parameter
+        gradients (the communication backends start a bucket's exchange from it)."""
         if self.is_cuda:
-            for op in reversed(self.ops[1:-1]):
-                op.backward()
+            for i in range(len(self.ops) - 2, 0, -1):
+                self.ops[i].backward()
+                if hook is not None:
+                    hook(i)
             return
         self._cpu_loss.backward()
         self._cpu_loss = None

@@ -1,0 +1,451 @@
+"""Communication backends whose data path is our own CUDA kernels over peer-visible (symmetric) memory.
+
+``torch.distributed`` (NCCL) is used for plumbing only: rendezvous, exchange of memory handles through
+``torch.distributed._symmetric_memory``, the broadcast of the shared seed and tiny host-side statistics. The
+gradient all-reduce, the optimizer step that follows it, and the gossip / elastic parameter mixes are single
+kernels from ``csrc/comm_p2p.cu`` that load from and store to the other GPUs' memory directly.
+
+``FusedAllreduceSgdComm`` additionally overlaps the exchange with the backward pass: the flat gradient vector
+is cut into buckets (25 MB by default) in the order backward produces them; as soon as the operators of a
+bucket have run, the bucket's fused kernel is launched on a separate stream while backward continues.
+Master weights and momentum are sharded over the ranks by that kernel (rank r owns shard r of every bucket);
+``gather_master`` re-assembles full fp32 vectors when a checkpoint needs them.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native_ops as K
+from .._native import check
+from ..utils.rng import XorShift128Plus
+from . import p2p_kernels as PK
+from .comm import AllreduceComm, CommWorker, GossipConfig
+
+ALIGN = 64
+
+
+class SymmetricArena:
+    """Peer-visible device tensors (one allocation per name) and their per-rank addresses."""
+
+    def __init__(self, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self._symm = symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(self.group)
+        self.world = dist.get_world_size(self.group)
+        self.tensors, self.handles = {}, {}
+        try:
+            symm_mem.enable_symm_mem_for_group(self.group.group_name)
+        except Exception:
+            pass
+
+    def alloc(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        dev = torch.device("cuda", torch.cuda.current_device())
+        t = self._symm.empty(int(numel), dtype=dtype, device=dev)
+        t.zero_()
+        h = self._symm.rendezvous(t, self.group.group_name)
+        self.tensors[name], self.handles[name] = t, h
+        return t
+
+    def ptrs(self, name: str) -> List[int]:
+        return [int(p) for p in self.handles[name].buffer_ptrs]
+
+    def multicast_ptr(self, name: str) -> int:
+        try:
+            return int(self.handles[name].multicast_ptr or 0)
+        except Exception:
+            return 0
+
+    def barrier(self, name: str):
+        self.handles[name].barrier()
+
+
+def _fill_ptrs(arr, ptrs):
+    for i in range(PK.MAX_RANKS):
+        arr[i] = ptrs[i] if i < len(ptrs) else None
+
+
+class _P2PBase:
+    """State shared by the kernel-driven backends: arena, flag pad, per-slot epoch counters."""
+
+    def _init_p2p(self, group, num_slots=256):
+        self.arena = SymmetricArena(group)
+        self.num_slots = num_slots
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.flags = self.arena.alloc("flags", num_slots * 2 * PK.MAX_RANKS, torch.int32)
+        self.epochs = torch.zeros(num_slots, dtype=torch.int32, device=dev)
+        self.counters = torch.zeros(num_slots, dtype=torch.int32, device=dev)
+        self.status = K.status_word()
+        torch.cuda.synchronize()
+        dist.barrier(self.arena.group)
+
+    def _flag_ptrs(self):
+        return self.arena.ptrs("flags")
+
+    def _barrier_kernel(self, slot, stream):
+        a = PK.BarrierArgs()
+        _fill_ptrs(a.flags, self._flag_ptrs())
+        a.epoch_ptr = self.epochs[slot:].data_ptr()
+        a.status = self.status.data_ptr()
+        a.rank, a.world, a.slot = self.rank, self.world, slot
+        check(PK.fn("rb_barrier_p2p")(C.byref(a), stream.cuda_stream), "rb_barrier_p2p")
+
+
+class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
+    name = "fused_allreduce_sgd"
+    graph_safe = True
+
+    def __init__(self, group=None, bucket_bytes: int = 25 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 48,
+                 one_shot_bytes: int = 256 << 10, replicate_master: bool = False, use_multimem: Optional[bool] = None):
+        AllreduceComm.__init__(self, group)
+        self._init_p2p(group)
+        self.bucket_elems = bucket_bytes // 4 // ALIGN * ALIGN
+        self.min_bucket_elems = min_bucket_bytes // 4
+        self.one_shot_elems = one_shot_bytes // 4
+        self.blocks = blocks
+        self.replicate_master = replicate_master
+        if use_multimem is None:
+            use_multimem = os.environ.get("RB_MULTIMEM", "0") == "1"
+        self.use_multimem = use_multimem
+        self.engine = None
+        self.launches = []        # [(trigger op index, off, n, slot)]
+        self._by_trigger = {}
+        self._hyper = None
+        self.kernel_launches_per_step = 0
+
+    # the network asks us where its flat vectors should live
+    def flat_allocator(self, name, n, dtype):
+        if name in ("grads", "params16") or (name == "params" and self.replicate_master):
+            return self.arena.alloc(name, n, dtype)
+        return torch.zeros(n, dtype=dtype, device=torch.device("cuda", torch.cuda.current_device()))
+
+    def attach(self, engine):
+        self.engine = engine
+        net = engine.net
+        self.net = net
+        self.comm_stream = torch.cuda.Stream(net.device, priority=-1)
+        self._ready = torch.cuda.Event()
+        self._done = torch.cuda.Event()
+        self._plan(net)
+        self.mc_grads = self.arena.multicast_ptr("grads") if self.use_multimem else 0
+        self.mc_w16 = self.arena.multicast_ptr("params16") if self.use_multimem else 0
+
+    # ---- bucket plan: ranges of the flat vectors in the order backward completes them
+    def _plan(self, net):
+        ops = net.ops
+        pending, pending_elems = [], 0
+        slot = 0
+        self.launches = []
+        for idx in range(len(ops) - 2, 0, -1):
+            op = ops[idx]
+            for s in op.segs:
+                n = (s.numel + ALIGN - 1) // ALIGN * ALIGN
+                pending.append((s.offset, s.offset + n))
+                pending_elems += n
+            last = idx == 1
+            if pending and (pending_elems >= self.min_bucket_elems or last):
+                for lo, hi in self._merge(pending):
+                    o = lo
+                    while o < hi:
+                        n = min(self.bucket_elems, hi - o)
+                        self.launches.append((idx, o, n, slot))
+                        slot += 1
+                        o += n
+                pending, pending_elems = [], 0
+        if slot > self.num_slots:
+            raise RuntimeError("too many gradient buckets for the flag pad")
+        self._by_trigger = {}
+        for rec in self.launches:
+            self._by_trigger.setdefault(rec[0], []).append(rec)
+
+    @staticmethod
+    def _merge(ranges):
+        out = []
+        for lo, hi in sorted(ranges):
+            if out and out[-1][1] == lo:
+                out[-1] = (out[-1][0], hi)
+            else:
+                out.append((lo, hi))
+        return out
+
+    def shard_bounds(self, n):
+        per = (n + self.world - 1) // self.world
+        per = (per + 7) // 8 * 8
+        return [(min(n, r * per), min(n, r * per + per)) for r in range(self.world)]
+
+    # ---- per-step protocol driven by the engine
+    def prepare(self, stepper, lr):
+        self.kernel_launches_per_step = 0
+        self._hyper = (float(lr), stepper.mu, stepper.l2, 1.0 / self.world, stepper.mode)
+
+    def on_op_backward(self, op_index):
+        recs = self._by_trigger.get(op_index)
+        if not recs:
+            return
+        cur = torch.cuda.current_stream()
+        self._ready.record(cur)
+        self.comm_stream.wait_event(self._ready)
+        for _, off, n, slot in recs:
+            self._launch(off, n, slot, op=0)
+
+    def fused_grads_step(self, stepper, lr):
+        """Everything was launched from the backward hooks; join the communication stream."""
+        self._done.record(self.comm_stream)
+        torch.cuda.current_stream().wait_event(self._done)
+
+    def _launch(self, off, n, slot, op, buf="grads", scale=None):
+        net = self.net
+        a = PK.ArSgdArgs()
+        _fill_ptrs(a.grads, self.arena.ptrs(buf))
+        _fill_ptrs(a.w16, self.arena.ptrs("params16") if op == 0 else [])
+        _fill_ptrs(a.w32, self.arena.ptrs("params") if (op == 0 and self.replicate_master) else [])
+        _fill_ptrs(a.flags, self._flag_ptrs())
+        a.w, a.v = net.params.data_ptr(), net.mom.data_ptr()
+        a.mc_grads = (self.mc_grads or None) if buf == "grads" else None
+        a.mc_w16 = self.mc_w16 or None
+        a.epoch_ptr = self.epochs[slot:].data_ptr()
+        a.block_counter = self.counters[slot:].data_ptr()
+        a.status = self.status.data_ptr()
+        a.off, a.n, a.decay_len = off, n, net.decay_len
+        a.rank, a.world, a.slot = self.rank, self.world, slot
+        a.one_shot = 1 if (op == 0 and n <= self.one_shot_elems) else 0
+        a.op = op
+        a.avg_scale = scale if scale is not None else 1.0 / self.world
+        if op == 0:
+            lr, mu, l2, gs, mode = self._hyper
+            a.h.lr, a.h.mu, a.h.l2, a.h.grad_scale, a.h.mode, a.h.phase = lr, mu, l2, gs, mode, 3
+        blocks = max(1, min(self.blocks, (n // 8 + 511) // 512))
+        with torch.cuda.stream(self.comm_stream):
+            check(PK.fn("rb_allreduce_sgd_p2p")(C.byref(a), blocks, self.comm_stream.cuda_stream),
+                  "rb_allreduce_sgd_p2p")
+            if op == 0:
+                # every peer has finished reading this bucket when the kernel ends
+                net.grads[off:off + n].zero_()
+        self.bytes_moved += n * 4
+        self.kernel_launches_per_step += 1
+
+    # ---- whole-vector operations
+    def allreduce_average(self, flat):
+        """In-place average of the symmetric gradient buffer with the P2P kernel; other tensors use NCCL."""
+        if self.world <= 1:
+            return
+        if flat.data_ptr() == self.net.grads.data_ptr():
+            cur = torch.cuda.current_stream()
+            self._ready.record(cur)
+            self.comm_stream.wait_event(self._ready)
+            off = 0
+            slot = self.num_slots - 1
+            total = flat.numel() // 8 * 8
+            while off < total:
+                n = min(self.bucket_elems, total - off)
+                self._launch(off, n, slot, op=1)
+                off += n
+            self._done.record(self.comm_stream)
+            cur.wait_event(self._done)
+        else:
+            super().allreduce_average(flat)
+
+    def gather_master(self):
+        """Make the fp32 master weights and momentum complete on every rank (owners broadcast their shards)."""
+        if self.world <= 1 or self.replicate_master:
+            return
+        net = self.net
+        torch.cuda.synchronize()
+        for _, off, n, _slot in self.launches:
+            if n <= self.one_shot_elems:
+                continue
+            for r, (s0, s1) in enumerate(self.shard_bounds(n)):
+                if s1 > s0:
+                    dist.broadcast(net.params[off + s0: off + s1], r, group=self.group)
+                    dist.broadcast(net.mom[off + s0: off + s1], r, group=self.group)
+        torch.cuda.synchronize()
+
+    def exact_sync(self, flat):
+        # replicas hold identical bf16 weights by construction; assembling the master is what a checkpoint needs
+        self.gather_master()
+
+
+class GossipP2PComm(CommWorker, _P2PBase):
+    """Pair gossip (shared-seed permutation, synchronous) or pull gossip (random peer) through one kernel that
+    reads the peer's published parameter snapshot over NVLink and mixes it in: x <- x - alpha (x - x_peer)."""
+    name = "gossip_p2p"
+    graph_safe = False
+
+    def __init__(self, group=None, mode: str = "pair", alpha: float = 0.5, seed=(17, 29), blocks: int = 96,
+                 cfg: GossipConfig = GossipConfig()):
+        CommWorker.__init__(self, group)
+        self._init_p2p(group, num_slots=8)
+        self.mode, self.alpha, self.blocks, self.cfg = mode, alpha, blocks, cfg
+        self.rng = XorShift128Plus(seed[0] + (0 if mode == "pair" else 1000003 * self.rank), seed[1])
+        self.pub = None
+        self._last_peer = None
+        self.net = None
+
+    def attach(self, engine):
+        self.net = engine.net
+        self.pub = self.arena.alloc("pub", 2 * self.net.flat_len, torch.float32)
+
+    def _peer(self, repeat):
+        if repeat and self._last_peer is not None:
+            return self._last_peer
+        if self.mode == "pair":
+            # the shared-seed permutation of the reference: rank r sends to perm[r], so r receives from the
+            # rank whose target it is -- here r pulls from that rank
+            perm = self.rng.permutation(self.world)
+            peer = perm.index(self.rank)
+        else:
+            peer = self.rng.below(self.world)
+        self._last_peer = peer
+        return peer
+
+    def sync_params(self, flat, repeat=False):
+        if self.world <= 1:
+            return
+        net = self.net
+        is_params = flat.data_ptr() == net.params.data_ptr()
+        peer = self._peer(repeat)
+        st = torch.cuda.current_stream()
+        a = PK.MixArgs()
+        _fill_ptrs(a.flags, self._flag_ptrs())
+        a.w = flat.data_ptr()
+        a.w16 = net.params16.data_ptr() if is_params else None
+        a.pub_local = self.pub.data_ptr()
+        a.pub_peer = self.arena.ptrs("pub")[peer]
+        slot = 0 if is_params else 1
+        a.epoch_ptr = self.epochs[slot:].data_ptr()
+        a.block_counter = self.counters[slot:].data_ptr()
+        a.status = self.status.data_ptr()
+        a.n = flat.numel() // 4 * 4
+        a.rank, a.world, a.slot, a.peer = self.rank, self.world, slot, peer
+        a.wait_peer = 1 if self.mode == "pair" else 0
+        a.alpha, a.w_self = self.alpha, 1.0
+        check(PK.fn("rb_publish_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_publish_p2p")
+        check(PK.fn("rb_gossip_mix_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_gossip_mix_p2p")
+        self.bytes_moved += a.n * 4
+
+    def allreduce_average(self, flat):
+        CommWorker.exact_sync(self, flat)
+
+
+class ElasticP2PComm(CommWorker, _P2PBase):
+    """Elastic averaging with the centre in rank 0's memory: clients read it and add their pull to it with
+    peer-to-peer loads and reductions; rank 0 folds the accumulated pulls into the centre."""
+    name = "elastic_p2p"
+    graph_safe = False
+
+    def __init__(self, group=None, beta: Optional[float] = None, blocks: int = 96):
+        CommWorker.__init__(self, group)
+        self._init_p2p(group, num_slots=8)
+        self.beta = beta if beta is not None else 0.8 / max(1, self.world)
+        self.blocks = blocks
+        self.net = None
+
+    def attach(self, engine):
+        self.net = engine.net
+        n = self.net.flat_len
+        self.center = self.arena.alloc("center", n, torch.float32)
+        self.delta = self.arena.alloc("delta", n, torch.float32)
+
+    def first_one_way_sync(self, flat):
+        if self.world > 1:
+            dist.broadcast(flat, 0, group=self.group)
+        self.center.copy_(flat)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+
+    def sync_params(self, flat, repeat=False):
+        if self.world <= 1:
+            return
+        net = self.net
+        st = torch.cuda.current_stream()
+        a = PK.MixArgs()
+        _fill_ptrs(a.flags, self._flag_ptrs())
+        a.w = flat.data_ptr()
+        a.w16 = net.params16.data_ptr() if flat.data_ptr() == net.params.data_ptr() else None
+        a.pub_peer = self.arena.ptrs("center")[0]
+        a.acc_target = self.arena.ptrs("delta")[0]
+        a.status = self.status.data_ptr()
+        a.n = flat.numel() // 4 * 4
+        a.rank, a.world = self.rank, self.world
+        a.alpha = self.beta
+        check(PK.fn("rb_elastic_pull_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_elastic_pull_p2p")
+        self._barrier_kernel(2, st)
+        if self.rank == 0:
+            check(PK.fn("rb_elastic_apply")(self.center.data_ptr(), self.delta.data_ptr(), a.n, st.cuda_stream),
+                  "rb_elastic_apply")
+        self._barrier_kernel(3, st)
+        self.bytes_moved += a.n * 8
+
+    def exact_sync(self, flat):
+        if self.world <= 1:
+            return
+        if self.rank == 0:
+            flat.copy_(self.center)
+        dist.broadcast(flat, 0, group=self.group)
+
+    allreduce_average = CommWorker.exact_sync
+
+
+class PushGossipP2PComm(CommWorker, _P2PBase):
+    """Push gossip: every rank adds its vector into a random target's accumulator with peer-to-peer reductions;
+    after a barrier each rank keeps (w_self * own + received) / (w_self + count)."""
+    name = "gossip_push_p2p"
+    graph_safe = False
+
+    def __init__(self, group=None, seed=(41, 43), blocks: int = 96):
+        CommWorker.__init__(self, group)
+        self._init_p2p(group, num_slots=8)
+        self.rng = XorShift128Plus(seed[0] + 7919 * self.rank, seed[1])
+        self.blocks = blocks
+        self.net = None
+
+    def attach(self, engine):
+        self.net = engine.net
+        self.acc = self.arena.alloc("acc", self.net.flat_len, torch.float32)
+        self.count = self.arena.alloc("count", ALIGN, torch.float32)
+
+    def sync_params(self, flat, repeat=False):
+        if self.world <= 1:
+            return
+        net = self.net
+        target = self.rng.below(self.world)
+        st = torch.cuda.current_stream()
+        a = PK.MixArgs()
+        _fill_ptrs(a.flags, self._flag_ptrs())
+        a.w = flat.data_ptr()
+        a.w16 = net.params16.data_ptr() if flat.data_ptr() == net.params.data_ptr() else None
+        a.acc_target = self.arena.ptrs("acc")[target]
+        a.count_target = self.arena.ptrs("count")[target]
+        a.block_counter = self.counters[4:].data_ptr()
+        a.status = self.status.data_ptr()
+        a.n = flat.numel() // 4 * 4
+        a.rank, a.world, a.peer = self.rank, self.world, target
+        a.w_self = 2.0 if target == self.rank else 1.0
+        check(PK.fn("rb_push_add_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_push_add_p2p")
+        self._barrier_kernel(2, st)
+        a.acc_target = self.acc.data_ptr()
+        a.count_target = self.count.data_ptr()
+        check(PK.fn("rb_push_finalize")(C.byref(a), self.blocks, st.cuda_stream), "rb_push_finalize")
+        self._barrier_kernel(3, st)
+        self.bytes_moved += a.n * 4
+
+    allreduce_average = CommWorker.exact_sync
+
+
+def make(name: str, **kw) -> CommWorker:
+    if name == "fused_allreduce_sgd":
+        return FusedAllreduceSgdComm(**kw)
+    if name == "gossip_p2p":
+        return GossipP2PComm(**kw)
+    if name == "gossip_pull_p2p":
+        return GossipP2PComm(mode="pull", **kw)
+    if name == "gossip_push_p2p":
+        return PushGossipP2PComm(**kw)
+    if name == "elastic_p2p":
+        return ElasticP2PComm(**kw)
+    raise ValueError(name)

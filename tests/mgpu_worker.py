@@ -1,0 +1,175 @@
+"""Multi-GPU test worker, launched by tests/test_multigpu.py through torch.distributed.run (one rank per GPU).
+
+Each case checks a kernel-driven communication backend against the same exchange done with library
+collectives (NCCL) or a closed-form expectation, and exits non-zero on a mismatch.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from rembrandt_b200.api import default_opt, model_config
+from rembrandt_b200.engine import StepEngine
+from rembrandt_b200.models.net import Net
+from rembrandt_b200.ops import native_ops as K
+from rembrandt_b200.parallel import comm as comm_mod
+from rembrandt_b200.parallel import p2p
+
+
+def batches(rank, steps, batch, hw, ch, classes):
+    g = torch.Generator().manual_seed(100 + rank)
+    return [(torch.randint(0, 256, (batch, ch, hw, hw), dtype=torch.uint8, generator=g).pin_memory(),
+             torch.randint(0, classes, (batch,), dtype=torch.int32, generator=g).pin_memory()) for _ in range(steps)]
+
+
+def case_fused_allreduce_sgd(rank, world, use_graph):
+    """Fused P2P all-reduce + SGD (overlapped with backward) == NCCL all-reduce + separate optimizer step."""
+    batch, steps = 8, 5
+    cfg = lambda: model_config("cifar", augment=False)
+    fused = p2p.FusedAllreduceSgdComm(min_bucket_bytes=64 << 10, bucket_bytes=128 << 10, one_shot_bytes=16 << 10)
+    net_a = Net(cfg(), batch, device="cuda", seed=(11, 12), flat_allocator=fused.flat_allocator)
+    eng_a = StepEngine(net_a, default_opt(batch, fused.name), fused, use_graph=use_graph)
+    base = comm_mod.AllreduceComm()
+    net_b = Net(cfg(), batch, device="cuda", seed=(11, 12))
+    eng_b = StepEngine(net_b, default_opt(batch, base.name), base, use_graph=False)
+    assert torch.equal(net_a.params, net_b.params)
+    assert len(fused.launches) >= 3, fused.launches
+    data = batches(rank, steps, batch, 32, 3, 10)
+    for x, y in data:
+        for eng in (eng_a, eng_b):
+            eng.feed(x, y)
+            eng.step()
+    la, lb = eng_a.flush(), eng_b.flush()
+    torch.cuda.synchronize()
+    assert K.read_status() == 0, "a bounded wait ran out"
+    assert abs(la[0] - lb[0]) < 2e-2 * max(1.0, abs(lb[0])), (la, lb)
+    a16, b16 = net_a.params16.float(), net_b.params16.float()
+    rel = float((a16 - b16).norm() / b16.norm())
+    assert rel < 2e-3, f"bf16 weights differ: rel {rel}"
+    # sharded master: after gathering, the fp32 master equals the baseline's
+    fused.gather_master()
+    rel = float((net_a.params - net_b.params).norm() / net_b.params.norm())
+    assert rel < 1e-4, f"fp32 master differs after gather: rel {rel}"
+    assert float(net_a.grads.abs().max()) == 0.0
+    # every rank holds the same weights
+    mine = net_a.params16.float().clone()
+    ref = mine.clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(mine, ref), "replicas diverged"
+
+
+def case_p2p_allreduce(rank, world):
+    """The plain in-place average (op 1) of the gradient buffer against NCCL, two-shot and multi-bucket."""
+    fused = p2p.FusedAllreduceSgdComm(bucket_bytes=1 << 20)
+    net = Net(model_config("lenet"), 4, device="cuda", seed=(1, 2), flat_allocator=fused.flat_allocator)
+    StepEngine(net, default_opt(4, fused.name), fused, use_graph=False)
+    torch.manual_seed(rank)
+    net.grads.copy_(torch.randn_like(net.grads))
+    ref = net.grads.clone()
+    dist.all_reduce(ref)
+    ref /= world
+    fused.allreduce_average(net.grads)
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    n = net.grads.numel() // 8 * 8
+    assert torch.allclose(net.grads[:n], ref[:n], rtol=1e-5, atol=1e-6)
+
+
+def _param_engine(comm):
+    net = Net(model_config("lenet"), 4, device="cuda", seed=(1, 2))
+    eng = StepEngine(net, default_opt(4, comm.name), comm, use_graph=False)
+    return net, eng
+
+
+def case_gossip_pair(rank, world):
+    comm = p2p.GossipP2PComm(mode="pair", alpha=0.5, seed=(17, 29))
+    oracle = comm_mod.PairGossipComm(seed=(17, 29))
+    net, _ = _param_engine(comm)
+    for rnd in range(4):
+        torch.manual_seed(1000 * rnd + rank)
+        net.params.copy_(torch.randn_like(net.params))
+        expect = net.params.clone()
+        oracle.sync_params(expect)
+        comm.sync_params(net.params)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(net.params[:n], expect[:n], rtol=1e-6, atol=1e-6), f"round {rnd}"
+        assert torch.equal(net.params16[:n], net.params[:n].bfloat16())
+
+
+def case_elastic(rank, world):
+    comm = p2p.ElasticP2PComm(beta=0.25)
+    oracle = comm_mod.ElasticComm(beta=0.25)
+    net, _ = _param_engine(comm)
+    torch.manual_seed(7)
+    start = torch.randn_like(net.params)
+    net.params.copy_(start)
+    expect = start.clone()
+    comm.first_one_way_sync(net.params)
+    oracle.first_one_way_sync(expect)
+    for rnd in range(3):
+        torch.manual_seed(50 * rnd + rank)
+        noise = torch.randn_like(net.params) * 0.1
+        net.params.add_(noise)
+        expect.add_(noise)
+        comm.sync_params(net.params)
+        oracle.sync_params(expect)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(net.params[:n], expect[:n], rtol=1e-5, atol=1e-5), f"round {rnd}"
+    if rank == 0:
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(comm.center[:n], oracle.center[:n], rtol=1e-5, atol=1e-5)
+
+
+def case_push(rank, world):
+    comm = p2p.PushGossipP2PComm(seed=(41, 43))
+    oracle = comm_mod.PushGossipComm(seed=(41, 43))
+    net, _ = _param_engine(comm)
+    for rnd in range(4):
+        torch.manual_seed(300 * rnd + rank)
+        net.params.copy_(torch.randn_like(net.params))
+        expect = net.params.clone()
+        oracle.sync_params(expect)
+        comm.sync_params(net.params)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(net.params[:n], expect[:n], rtol=1e-5, atol=1e-5), f"round {rnd}"
+
+
+def main():
+    case = sys.argv[1]
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    try:
+        if case == "fused_eager":
+            case_fused_allreduce_sgd(rank, world, False)
+        elif case == "fused_graph":
+            case_fused_allreduce_sgd(rank, world, True)
+        elif case == "p2p_allreduce":
+            case_p2p_allreduce(rank, world)
+        elif case == "gossip_pair":
+            case_gossip_pair(rank, world)
+        elif case == "elastic":
+            case_elastic(rank, world)
+        elif case == "push":
+            case_push(rank, world)
+        else:
+            raise SystemExit(f"unknown case {case}")
+        torch.cuda.synchronize()
+        dist.barrier()
+        if rank == 0:
+            print(f"case {case}: ok on {world} ranks")
+    finally:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
