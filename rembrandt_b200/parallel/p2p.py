@@ -39,10 +39,6 @@ class SymmetricArena:
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
         self.tensors, self.handles = {}, {}
-        try:
-            symm_mem.enable_symm_mem_for_group(self.group.group_name)
-        except Exception:
-            pass
 
     def alloc(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         dev = torch.device("cuda", torch.cuda.current_device())
