@@ -1,0 +1,138 @@
+"""Shared driver of the training entry points.
+
+The reference's tools hard-code their configuration in ``main()`` (no argument parsing anywhere); the entry
+points here keep those values as defaults and expose them as flags. Multi-GPU runs are launched with
+``python -m torch.distributed.run --nproc-per-node N -m rembrandt_b200.cli.<tool> ...`` (one rank per GPU).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..data import (AsyncQueueDataIter, BatchIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
+                    compute_mean, open_data_file, partition_shard)
+from ..engine import StepEngine
+from ..models.net import Net
+from ..optim.sgd import (CheckpointBehavior, Momentum, SgdOptConfig, StepSizeReference, StepSizeSchedule, SyncOrder)
+from ..parallel import comm as comm_mod
+from ..trainer import ExperimentConfig, SgdOpt
+
+MOMENTA = {"zero": Momentum.ZERO, "update": Momentum.UPDATE, "nesterov": Momentum.UPDATE_NESTEROV,
+           "gradient": Momentum.GRADIENT, "gradient_nesterov": Momentum.GRADIENT_NESTEROV,
+           "grad_decay": Momentum.GRAD_DECAY}
+ORDERS = {o.value: o for o in SyncOrder}
+
+
+def base_parser(desc, **defaults):
+    ap = argparse.ArgumentParser(description=desc)
+    ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    ap.add_argument("--batch", type=int, default=defaults.get("batch", 64))
+    ap.add_argument("--minibatch", type=int, default=defaults.get("minibatch", 0), help="0 = batch")
+    ap.add_argument("--lr", type=float, default=defaults.get("lr", 0.01))
+    ap.add_argument("--momentum", choices=sorted(MOMENTA), default=defaults.get("momentum", "nesterov"))
+    ap.add_argument("--mu", type=float, default=defaults.get("mu", 0.9))
+    ap.add_argument("--l2", type=float, default=defaults.get("l2", 5e-4))
+    ap.add_argument("--iters", type=int, default=defaults.get("iters", 200))
+    ap.add_argument("--display-iters", type=int, default=defaults.get("display_iters", 50))
+    ap.add_argument("--checkpoint-iters", type=int, default=defaults.get("checkpoint_iters", 0))
+    ap.add_argument("--save-iters", type=int, default=0)
+    ap.add_argument("--valid-iters", type=int, default=defaults.get("valid_iters", 0))
+    ap.add_argument("--checkpoint-dir", default=None)
+    ap.add_argument("--comm", default=defaults.get("comm", "auto"))
+    ap.add_argument("--sync-order", choices=sorted(ORDERS), default=None)
+    ap.add_argument("--comm-interval", type=int, default=1)
+    ap.add_argument("--data", default=None, help=".data descriptor; synthetic data when absent")
+    ap.add_argument("--synthetic-size", type=int, default=4096)
+    ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--straggler-ranks", type=int, nargs="*", default=[])
+    ap.add_argument("--straggler-max-delay-ms", type=int, default=0)
+    ap.add_argument("--report-port", type=int, default=0, help="serve a live loss report on this port")
+    return ap
+
+
+def init_distributed(device: str):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world > 1 and not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if device == "cuda":
+            local = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        else:
+            dist.init_process_group("gloo")
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    return rank, world
+
+
+def make_comm(name, device, world):
+    if world <= 1:
+        return comm_mod.NullComm()
+    if name == "auto":
+        name = "fused_allreduce_sgd" if device == "cuda" else "allreduce"
+    return comm_mod.make_comm(name)
+
+
+def default_order(comm_name):
+    if "gossip" in comm_name:
+        return SyncOrder.STEP_THEN_SYNC_PARAMS
+    if "elastic" in comm_name:
+        return SyncOrder.SYNC_PARAMS_THEN_STEP
+    return SyncOrder.SYNC_GRADS_THEN_STEP
+
+
+def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None, valid_source=None):
+    rank, world = init_distributed(args.device)
+    device = torch.device(args.device, int(os.environ.get("LOCAL_RANK", "0")) if args.device == "cuda" else None) \
+        if args.device == "cuda" else torch.device("cpu")
+    worker = make_comm(args.comm, args.device, world)
+    seed = worker.broadcast_seed((args.seed, args.seed * 7919 + 13))
+    dims = model_cfg.input_op.cfg.in_dims
+    classes = model_cfg.loss_op.cfg.num_categories
+    if source is None:
+        source = (open_data_file(args.data, "train") if args.data else
+                  SyntheticDataSource(args.synthetic_size, dims, classes, seed=args.seed, separable=True))
+        if valid_source is None and args.valid_iters:
+            valid_source = (open_data_file(args.data, "valid") if args.data else
+                            SyntheticDataSource(max(256, args.synthetic_size // 8), dims, classes, seed=args.seed + 1,
+                                                separable=True))
+    minibatch = args.minibatch or args.batch
+    opt = SgdOptConfig(minibatch_size=minibatch, step_size=schedule or StepSizeSchedule.constant(args.lr),
+                       momentum=MOMENTA[args.momentum], mu=args.mu, l2_reg_coef=args.l2,
+                       sync_order=ORDERS[args.sync_order] if args.sync_order else default_order(worker.name),
+                       comm_interval=args.comm_interval, checkpoint=CheckpointBehavior.DISCARD,
+                       display_iters=args.display_iters, checkpoint_iters=args.checkpoint_iters,
+                       save_iters=args.save_iters or args.checkpoint_iters, valid_iters=args.valid_iters,
+                       checkpoint_dir=args.checkpoint_dir, max_iters=args.iters)
+    net = Net(model_cfg, args.batch, device=device, seed=seed, minibatch_size=minibatch,
+              flat_allocator=getattr(worker, "flat_allocator", None))
+    if rank == 0:
+        print(net.describe())
+    engine = StepEngine(net, opt, worker, use_graph=not args.no_graph)
+    train_iter = BatchIter(AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world),
+                                                                   seed=(args.seed + rank, 99))),
+                           args.batch, dims)
+    valid_iter = None
+    if valid_source is not None:
+        valid_iter = BatchIter(CyclicSampleDataIter(partition_shard(valid_source, rank, world)), args.batch, dims)
+    report = None
+    if args.report_port and rank == 0:
+        from ..utils.report import ReportServer
+        report = ReportServer(port=args.report_port)
+    sgd = SgdOpt(opt, engine, ExperimentConfig(args.straggler_ranks, args.straggler_max_delay_ms), report=report)
+    history = sgd.train(_repeat(train_iter), valid_iter, max_iters=args.iters)
+    if valid_iter is not None and args.valid_iters:
+        sgd.validate(valid_iter, args.valid_iters, engine.iter)
+    if dist.is_initialized():
+        dist.barrier()
+        dist.destroy_process_group()
+    return sgd
+
+
+def _repeat(it):
+    while True:
+        for x in it:
+            yield x

@@ -1,0 +1,136 @@
+"""Sample codecs and host-side augmentation (src/data/codec.rs, src/data/augment.rs, src/caffe_proto.proto).
+
+* ``Array3dDataCodec``   NdArray record -> uint8 array;
+* ``FakeJpegDataCodec``  returns a zero 256x256x3 image whatever the bytes (the reference's fake for I/O tests);
+* ``JpegDataCodec``      real decode through Pillow when it is installed (the reference uses turbojpeg with an
+                         stb fallback), grey -> RGB, HWC -> planar;
+* ``decode_caffe_datum`` hand-written reader of the Caffe ``Datum`` protobuf message (fields 1-7);
+* host preprocs: transpose CWH <-> WHC, random / centre crop, random flip.
+"""
+from __future__ import annotations
+
+import io
+from typing import Optional, Tuple
+
+import numpy as np
+
+from ..utils import blob
+
+
+class Array3dDataCodec:
+    def decode(self, value: bytes) -> np.ndarray:
+        recs, _ = blob.decode_records(value, "u8", count=1)
+        data, dims, _ = recs[0]
+        return data.reshape(tuple(reversed(dims)))
+
+
+class FakeJpegDataCodec:
+    def decode(self, value: bytes) -> np.ndarray:
+        return np.zeros((3, 256, 256), dtype=np.uint8)
+
+
+class JpegDataCodec:
+    def __init__(self):
+        try:
+            from PIL import Image  # noqa: F401
+            self._ok = True
+        except Exception:
+            self._ok = False
+
+    def decode(self, value: bytes) -> np.ndarray:
+        if not self._ok:
+            raise RuntimeError("no JPEG decoder available (Pillow is not installed)")
+        from PIL import Image
+        img = Image.open(io.BytesIO(value)).convert("RGB")
+        return np.ascontiguousarray(np.asarray(img, dtype=np.uint8).transpose(2, 0, 1))
+
+
+def _varint(buf: bytes, pos: int) -> Tuple[int, int]:
+    out, shift = 0, 0
+    while True:
+        b = buf[pos]
+        pos += 1
+        out |= (b & 0x7F) << shift
+        if not b & 0x80:
+            return out, pos
+        shift += 7
+
+
+def decode_caffe_datum(buf: bytes) -> dict:
+    """Fields: 1 channels, 2 height, 3 width, 4 data (bytes), 5 label, 6 float_data (repeated), 7 encoded."""
+    out = {"channels": 0, "height": 0, "width": 0, "data": b"", "label": 0, "float_data": [], "encoded": False}
+    names = {1: "channels", 2: "height", 3: "width", 5: "label"}
+    pos = 0
+    while pos < len(buf):
+        key, pos = _varint(buf, pos)
+        field, wire = key >> 3, key & 7
+        if wire == 0:
+            v, pos = _varint(buf, pos)
+            if field in names:
+                out[names[field]] = v
+            elif field == 7:
+                out["encoded"] = bool(v)
+        elif wire == 2:
+            n, pos = _varint(buf, pos)
+            chunk = buf[pos:pos + n]
+            pos += n
+            if field == 4:
+                out["data"] = bytes(chunk)
+            elif field == 6:
+                out["float_data"].extend(np.frombuffer(chunk, dtype="<f4").tolist())
+        elif wire == 5:
+            if field == 6:
+                out["float_data"].append(float(np.frombuffer(buf[pos:pos + 4], dtype="<f4")[0]))
+            pos += 4
+        elif wire == 1:
+            pos += 8
+        else:
+            raise ValueError(f"unsupported wire type {wire}")
+    return out
+
+
+def datum_to_sample(d: dict, jpeg: Optional[JpegDataCodec] = None):
+    if d["encoded"]:
+        return (jpeg or JpegDataCodec()).decode(d["data"]), d["label"]
+    arr = np.frombuffer(d["data"], dtype=np.uint8).reshape(d["channels"], d["height"], d["width"])
+    return arr, d["label"]
+
+
+# ---- host-side preprocessing (the GPU input kernel is the fast path; these serve CPU pipelines)
+def transpose_cwh_to_whc(img_chw: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(img_chw.transpose(1, 2, 0))
+
+
+def transpose_whc_to_cwh(img_hwc: np.ndarray) -> np.ndarray:
+    return np.ascontiguousarray(img_hwc.transpose(2, 0, 1))
+
+
+class RandomCropPreproc:
+    def __init__(self, crop_w, crop_h, seed=0):
+        self.cw, self.ch, self.rng = crop_w, crop_h, np.random.default_rng(seed)
+
+    def __call__(self, sample):
+        img, label = sample
+        _, h, w = img.shape
+        oy, ox = int(self.rng.integers(0, h - self.ch + 1)), int(self.rng.integers(0, w - self.cw + 1))
+        return img[:, oy:oy + self.ch, ox:ox + self.cw], label
+
+
+class CenterCropPreproc:
+    def __init__(self, crop_w, crop_h):
+        self.cw, self.ch = crop_w, crop_h
+
+    def __call__(self, sample):
+        img, label = sample
+        _, h, w = img.shape
+        oy, ox = (h - self.ch) // 2, (w - self.cw) // 2
+        return img[:, oy:oy + self.ch, ox:ox + self.cw], label
+
+
+class RandomFlipXPreproc:
+    def __init__(self, seed=0):
+        self.rng = np.random.default_rng(seed)
+
+    def __call__(self, sample):
+        img, label = sample
+        return (img[:, :, ::-1] if self.rng.integers(0, 2) else img), label

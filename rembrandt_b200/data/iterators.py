@@ -1,0 +1,276 @@
+"""Shards, sample iterators and asynchronous prefetching, after the reference's data API
+(src/data/mod.rs:23-809): a *shard* is an indexable range of a source; an *iterator* yields samples;
+asynchronous wrappers move the work to threads.
+
+* ``RangeDataShard`` / ``partition_shard``  contiguous (balanced) part of a source for one rank;
+* ``SequentialSampleIter``, ``RandomSampleDataIter`` (uniform with replacement), ``CyclicSampleDataIter``;
+* ``TransformDataIter``                     applies a host-side transform per sample;
+* ``AsyncQueueDataIter``                    one prefetch thread, bounded queue (256 by default);
+* ``AsyncPoolDataIter``                     N transform threads, original order restored;
+* ``ParallelJoinDataIter``                  N independent producers, unordered;
+* ``BatchIter``                             packs samples into pinned uint8 / int32 batch tensors.
+"""
+from __future__ import annotations
+
+import queue
+import threading
+from typing import Callable, Iterable, Iterator, List, Optional
+
+import numpy as np
+import torch
+
+from ..utils.rng import XorShift128Plus, cyclic_partition_range, partition_range
+
+
+class RangeDataShard:
+    def __init__(self, source, lo: int = 0, hi: Optional[int] = None):
+        self.source, self.lo, self.hi = source, lo, len(source) if hi is None else hi
+
+    def __len__(self):
+        return self.hi - self.lo
+
+    def __getitem__(self, i):
+        if not 0 <= i < len(self):
+            raise IndexError(i)
+        return self.source[self.lo + i]
+
+
+class RangeWrapDataShard:
+    """A shard made of up to two pieces of the source (wrap-around partitions, src/util.rs:23-41)."""
+
+    def __init__(self, source, pieces):
+        self.source, self.pieces = source, list(pieces)
+        self._len = sum(b - a for a, b in self.pieces)
+
+    def __len__(self):
+        return self._len
+
+    def __getitem__(self, i):
+        for a, b in self.pieces:
+            if i < b - a:
+                return self.source[a + i]
+            i -= b - a
+        raise IndexError
+
+
+def partition_shard(source, rank: int, world: int) -> RangeDataShard:
+    lo, hi = partition_range(len(source), world, rank)
+    return RangeDataShard(source, lo, hi)
+
+
+def cyclic_partition_shard(source, rank: int, world: int, shift: int) -> RangeWrapDataShard:
+    return RangeWrapDataShard(source, cyclic_partition_range(len(source), world, rank, shift))
+
+
+class SequentialSampleIter:
+    def __init__(self, shard):
+        self.shard = shard
+
+    def __iter__(self):
+        for i in range(len(self.shard)):
+            yield self.shard[i]
+
+
+class RandomSampleDataIter:
+    """Uniform sampling with replacement; one pass yields len(shard) samples."""
+
+    def __init__(self, shard, seed=(1, 2)):
+        self.shard, self.rng = shard, XorShift128Plus(*seed)
+
+    def __iter__(self):
+        n = len(self.shard)
+        for _ in range(n):
+            yield self.shard[self.rng.below(n)]
+
+
+class CyclicSampleDataIter:
+    """Endless sequential passes (validation in the reference iterates a fixed number of samples off this)."""
+
+    def __init__(self, shard):
+        self.shard, self.pos = shard, 0
+
+    def __iter__(self):
+        n = len(self.shard)
+        while True:
+            yield self.shard[self.pos]
+            self.pos = (self.pos + 1) % n
+
+
+class TransformDataIter:
+    def __init__(self, inner: Iterable, transform: Callable):
+        self.inner, self.transform = inner, transform
+
+    def __iter__(self):
+        for s in self.inner:
+            yield self.transform(s)
+
+
+_END = object()
+
+
+class AsyncQueueDataIter:
+    """One producer thread fills a bounded queue; iteration can be restarted (each `iter()` starts a new pass and
+    waits for the previous producer to acknowledge the stop request)."""
+
+    def __init__(self, inner: Iterable, capacity: int = 256):
+        self.inner, self.capacity = inner, capacity
+        self._thread = None
+        self._stop = None
+
+    def _produce(self, q, stop):
+        try:
+            for s in self.inner:
+                while not stop.is_set():
+                    try:
+                        q.put(s, timeout=0.05)
+                        break
+                    except queue.Full:
+                        continue
+                if stop.is_set():
+                    return
+            q.put(_END)
+        except BaseException as e:  # surface producer failures to the consumer
+            q.put(e)
+
+    def __iter__(self):
+        self.close()
+        q = queue.Queue(self.capacity)
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._produce, args=(q, self._stop), daemon=True)
+        self._thread.start()
+        while True:
+            item = q.get()
+            if item is _END:
+                return
+            if isinstance(item, BaseException):
+                raise item
+            yield item
+
+    def close(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=5)
+            self._thread = None
+
+
+class AsyncPoolDataIter:
+    """N worker threads apply `transform`; results come out in the order of the inner iterator."""
+
+    def __init__(self, inner: Iterable, transform: Callable, num_workers: int = 4, window: int = 64):
+        self.inner, self.transform, self.num_workers, self.window = inner, transform, num_workers, window
+
+    def __iter__(self):
+        tasks: "queue.Queue" = queue.Queue(self.window)
+        results = {}
+        cond = threading.Condition()
+        failure: List[BaseException] = []
+
+        def work():
+            while True:
+                item = tasks.get()
+                if item is _END:
+                    return
+                idx, s = item
+                try:
+                    r = self.transform(s)
+                except BaseException as e:
+                    r = e
+                with cond:
+                    results[idx] = r
+                    cond.notify_all()
+
+        workers = [threading.Thread(target=work, daemon=True) for _ in range(self.num_workers)]
+        for w in workers:
+            w.start()
+        submitted = 0
+        emitted = 0
+        it = iter(self.inner)
+        done = False
+        try:
+            while True:
+                while not done and submitted - emitted < self.window:
+                    try:
+                        tasks.put((submitted, next(it)))
+                        submitted += 1
+                    except StopIteration:
+                        done = True
+                if emitted == submitted and done:
+                    return
+                with cond:
+                    while emitted not in results:
+                        cond.wait(timeout=0.1)
+                    r = results.pop(emitted)
+                emitted += 1
+                if isinstance(r, BaseException):
+                    raise r
+                yield r
+        finally:
+            for _ in workers:
+                tasks.put(_END)
+
+
+class ParallelJoinDataIter:
+    """N independent producers (each with its own inner iterator) feeding one queue; order is arbitrary."""
+
+    def __init__(self, inners: List[Iterable], capacity: int = 256):
+        self.inners, self.capacity = inners, capacity
+
+    def __iter__(self):
+        q: "queue.Queue" = queue.Queue(self.capacity)
+        stop = threading.Event()
+
+        def produce(inner):
+            try:
+                for s in inner:
+                    while not stop.is_set():
+                        try:
+                            q.put(s, timeout=0.05)
+                            break
+                        except queue.Full:
+                            continue
+                    if stop.is_set():
+                        return
+            finally:
+                q.put(_END)
+
+        threads = [threading.Thread(target=produce, args=(i,), daemon=True) for i in self.inners]
+        for t in threads:
+            t.start()
+        live = len(threads)
+        try:
+            while live:
+                item = q.get()
+                if item is _END:
+                    live -= 1
+                    continue
+                yield item
+        finally:
+            stop.set()
+
+
+class BatchIter:
+    """Packs (image [C,H,W] uint8, label) samples into batch tensors; pinned when CUDA is available so that the
+    engine's host-to-device copies are asynchronous. A pool of `depth` buffers is cycled."""
+
+    def __init__(self, inner: Iterable, batch: int, dims, depth: int = 4, drop_last: bool = True):
+        w, h, c = dims
+        self.inner, self.batch, self.drop_last = inner, batch, drop_last
+        pin = torch.cuda.is_available()
+        self.imgs = [torch.zeros((batch, c, h, w), dtype=torch.uint8) for _ in range(depth)]
+        self.lbls = [torch.zeros(batch, dtype=torch.int32) for _ in range(depth)]
+        if pin:
+            self.imgs = [t.pin_memory() for t in self.imgs]
+            self.lbls = [t.pin_memory() for t in self.lbls]
+
+    def __iter__(self):
+        k, slot = 0, 0
+        for img, label in self.inner:
+            self.imgs[slot][k].copy_(torch.from_numpy(np.ascontiguousarray(img)).reshape(self.imgs[slot][k].shape))
+            self.lbls[slot][k] = int(label)
+            k += 1
+            if k == self.batch:
+                yield self.imgs[slot], self.lbls[slot]
+                slot = (slot + 1) % len(self.imgs)
+                k = 0
+        if k and not self.drop_last:
+            yield self.imgs[slot][:k], self.lbls[slot][:k]

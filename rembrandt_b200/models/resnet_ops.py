@@ -118,7 +118,8 @@ class _BnConv:
         w = layout.conv_weight_from_internal(self.v(self.seg_w), self.in_c, self.k, self.k)
         y = F.conv2d(x, w, None, stride=self.s, padding=self.p)
         g, b = self.v(self.seg_g)[: self.ko], self.v(self.seg_b)[: self.ko]
-        rm, rv = self.v(self.seg_rm).detach()[: self.ko], self.v(self.seg_rv).detach()[: self.ko]
+        # `.data` views: running statistics are updated in place without touching autograd's version counter
+        rm, rv = self.v(self.seg_rm).data[: self.ko], self.v(self.seg_rv).data[: self.ko]
         if train:
             rm2, rv2 = rm.clone(), rv.clone()
             y = F.batch_norm(y, rm2, rv2, g, b, training=True, momentum=self.mov_avg.at_iter(t), eps=self.eps)

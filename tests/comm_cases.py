@@ -1,0 +1,181 @@
+"""Per-rank bodies of the CPU communication tests (top-level functions so that spawn can pickle them)."""
+import time
+
+import torch
+import torch.distributed as dist
+
+from rembrandt_b200.parallel import comm as C
+from rembrandt_b200.utils.rng import XorShift128Plus
+
+
+def _vec(rank, n=257, rnd=0):
+    g = torch.Generator().manual_seed(100 * rnd + rank)
+    return torch.randn(n, generator=g)
+
+
+def _all(world, n=257, rnd=0):
+    return [_vec(r, n, rnd) for r in range(world)]
+
+
+def allreduce(rank, world):
+    c = C.AllreduceComm()
+    x = _vec(rank)
+    c.allreduce_average(x)
+    assert torch.allclose(x, sum(_all(world)) / world, atol=1e-6)
+    assert c.allreduce_stats([1.0, float(rank)]) == [float(world), float(sum(range(world)))]
+    assert c.broadcast_seed((rank + 5, rank + 9)) == (5, 9)
+
+
+def pair_gossip(rank, world):
+    c = C.PairGossipComm(seed=(17, 29))
+    shadow = XorShift128Plus(17, 29)
+    for rnd in range(5):
+        x = _vec(rank, rnd=rnd)
+        c.sync_params(x)
+        perm = shadow.permutation(world)
+        src = perm.index(rank)                     # the rank that sends to me
+        every = _all(world, rnd=rnd)
+        expect = every[rank] if src == rank and perm[rank] == rank else 0.5 * (every[rank] + every[src])
+        if src == rank:
+            expect = every[rank]
+        assert torch.allclose(x, expect, atol=1e-6), f"round {rnd}"
+    # repeat=True reuses the partners of the previous round (params and grads mixed with the same peer)
+    x, y = _vec(rank, rnd=50), _vec(rank, rnd=51)
+    c.sync_params(x)
+    c.sync_params(y, repeat=True)
+    perm = shadow.permutation(world)
+    src = perm.index(rank)
+    if src != rank:
+        assert torch.allclose(y, 0.5 * (_vec(rank, rnd=51) + _vec(src, rnd=51)), atol=1e-6)
+
+
+def pull_gossip(rank, world, rounds):
+    c = C.PullGossipComm(seed=(31, 37), cfg=C.GossipConfig(num_rounds=rounds))
+    shadows = [XorShift128Plus(31 + 1000003 * r, 37) for r in range(world)]
+    for rnd in range(4):
+        x = _vec(rank, rnd=rnd)
+        c.sync_params(x)
+        every = _all(world, rnd=rnd)
+        peers = [[s.below(world) for _ in range(rounds)] for s in shadows][rank]
+        expect = (every[rank] + sum(every[p] for p in peers)) / (rounds + 1)
+        assert torch.allclose(x, expect, atol=1e-6), f"round {rnd}"
+
+
+def push_gossip(rank, world):
+    c = C.PushGossipComm(seed=(41, 43))
+    shadows = [XorShift128Plus(41 + 7919 * r, 43) for r in range(world)]
+    for rnd in range(5):
+        x = _vec(rank, rnd=rnd)
+        c.sync_params(x)
+        every = _all(world, rnd=rnd)
+        targets = [s.below(world) for s in shadows]
+        received = [every[r] for r in range(world) if targets[r] == rank and r != rank]
+        w_self = 2.0 if targets[rank] == rank else 1.0
+        expect = every[rank] if not received else (w_self * every[rank] + sum(received)) / (w_self + len(received))
+        assert torch.allclose(x, expect, atol=1e-6), f"round {rnd}"
+
+
+def elastic(rank, world):
+    beta = 0.8 / world
+    c = C.ElasticComm()
+    assert abs(c.beta - beta) < 1e-12
+    x = _vec(rank)
+    c.first_one_way_sync(x)
+    center = _vec(0)
+    assert torch.allclose(x, center)               # everybody starts from rank 0's parameters
+    xs = [center.clone() for _ in range(world)]
+    for rnd in range(3):
+        noise = [_vec(r, rnd=10 + rnd) * 0.1 for r in range(world)]
+        x += noise[rank]
+        xs = [a + n for a, n in zip(xs, noise)]
+        c.sync_params(x)
+        pulls = [beta * (a - center) for a in xs]
+        xs = [a - p for a, p in zip(xs, pulls)]
+        center = center + sum(pulls)
+        assert torch.allclose(x, xs[rank], atol=1e-6)
+        if rank == 0:
+            assert torch.allclose(c.center, center, atol=1e-6)
+    y = torch.zeros_like(x)
+    c.exact_sync(y)
+    assert torch.allclose(y, center, atol=1e-6)    # exact sync broadcasts the centre
+
+
+def hierarchical(rank, world):
+    c = C.GroupAllreduceGossipComm(group_size=2, seed=(53, 59))
+    x = _vec(rank)
+    c.sync_params(x)
+    every = _all(world)
+    g0 = rank // 2 * 2
+    members = [r for r in range(g0, min(world, g0 + 2))]
+    group_mean = sum(every[r] for r in members) / len(members)
+    shadows = [XorShift128Plus(53 + 1000003 * r, 59) for r in range(world)]
+    peer = [s.below(world) for s in shadows][rank]
+    pg0 = peer // 2 * 2
+    pmem = [r for r in range(pg0, min(world, pg0 + 2))]
+    peer_mean = sum(every[r] for r in pmem) / len(pmem)
+    assert torch.allclose(x, 0.5 * (group_mean + peer_mean), atol=1e-6)
+
+
+def exact_sync(rank, world):
+    for cls in (C.PairGossipComm, C.PullGossipComm, C.PushGossipComm):
+        x = _vec(rank)
+        cls().exact_sync(x)
+        assert torch.allclose(x, sum(_all(world)) / world, atol=1e-6)
+
+
+# ---- failure injection on the host: a rank that raises, never joins, or arrives late
+def rank_raises_before_collective(rank, world):
+    if rank == 1:
+        raise RuntimeError("injected failure on rank 1")
+    x = _vec(rank)
+    C.AllreduceComm().allreduce_average(x)         # the survivors' collective must end with an error, not hang
+
+
+def rank_never_joins(rank, world):
+    if rank == world - 1:
+        time.sleep(6)                              # misses the collective; the process-group timeout is shorter
+        return
+    C.AllreduceComm().allreduce_average(_vec(rank))
+
+
+def straggler_is_tolerated(rank, world):
+    c = C.AllreduceComm()
+    for rnd in range(3):
+        if rank == 0:
+            time.sleep(0.3)                        # delayed, not dead: results are unchanged
+        x = _vec(rank, rnd=rnd)
+        c.allreduce_average(x)
+        assert torch.allclose(x, sum(_all(world, rnd=rnd)) / world, atol=1e-6)
+
+
+def dp_training_matches_single_process(rank, world):
+    """Data-parallel SGD over `world` ranks == one process on the concatenated batch (mean gradient)."""
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.sgd import Momentum, SgdOptConfig, StepSizeSchedule
+
+    def opt(mb):
+        return SgdOptConfig(minibatch_size=mb, step_size=StepSizeSchedule.constant(0.05), momentum=Momentum.UPDATE,
+                            mu=0.9, l2_reg_coef=1e-3)
+    per = 8
+    comm = C.AllreduceComm()
+    seed = comm.broadcast_seed((rank + 3, 7))
+    net = Net(zoo.lenet(), per, device="cpu", seed=seed, minibatch_size=per)
+    eng = StepEngine(net, opt(per), comm)
+    g = torch.Generator().manual_seed(5)
+    steps = [(torch.randint(0, 256, (per * world, 1, 28, 28), dtype=torch.uint8, generator=g),
+              torch.randint(0, 10, (per * world,), dtype=torch.int32, generator=g)) for _ in range(3)]
+    for x, y in steps:
+        eng.feed(x[rank * per:(rank + 1) * per], y[rank * per:(rank + 1) * per])
+        eng.step()
+    if rank == 0:
+        big = Net(zoo.lenet(), per * world, device="cpu", seed=seed, minibatch_size=per * world)
+        beng = StepEngine(big, opt(per * world))
+        for x, y in steps:
+            beng.feed(x, y)
+            beng.step()
+        assert torch.allclose(net.params.detach(), big.params.detach(), atol=2e-6)
+    ref = net.params.detach().clone()
+    dist.broadcast(ref, 0)
+    assert torch.equal(ref, net.params.detach()), "replicas diverged"

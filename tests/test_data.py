@@ -1,0 +1,128 @@
+"""Dataset readers, shards, iterators and codecs (CPU)."""
+import struct
+
+import numpy as np
+import pytest
+import torch
+
+from rembrandt_b200.data import (AsyncPoolDataIter, AsyncQueueDataIter, BatchIter, Cifar10DataSource,
+                                 CyclicSampleDataIter, MnistDataSource, ParallelJoinDataIter, RandomSampleDataIter,
+                                 RangeDataShard, SequentialSampleIter, SyntheticDataSource, TransformDataIter,
+                                 compute_mean, cyclic_partition_shard, partition_shard)
+from rembrandt_b200.data import codecs
+from rembrandt_b200.utils import blob
+
+
+def write_idx(path, arr):
+    with open(path, "wb") as f:
+        f.write(bytes([0, 0, 0x08, arr.ndim]))
+        for d in arr.shape:
+            f.write(struct.pack(">I", d))
+        f.write(arr.tobytes())
+
+
+def test_mnist_idx_reader(tmp_path):
+    rng = np.random.default_rng(0)
+    imgs = rng.integers(0, 256, (7, 5, 6), dtype=np.uint8)          # 7 images of height 5, width 6
+    lbls = rng.integers(0, 10, (7,), dtype=np.uint8)
+    write_idx(tmp_path / "img", imgs)
+    write_idx(tmp_path / "lbl", lbls)
+    src = MnistDataSource(str(tmp_path / "img"), str(tmp_path / "lbl"))
+    assert len(src) == 7 and src.dims == (6, 5, 1)
+    x, y = src[3]
+    assert x.shape == (1, 5, 6) and np.array_equal(x[0], imgs[3]) and y == lbls[3]
+    (tmp_path / "bad").write_bytes(b"\x01\x02\x03")
+    with pytest.raises(ValueError):
+        MnistDataSource(str(tmp_path / "bad"), str(tmp_path / "lbl"))
+
+
+def test_cifar_reader_and_mean(tmp_path):
+    rng = np.random.default_rng(1)
+    recs = rng.integers(0, 256, (5, 3073), dtype=np.uint8)
+    recs[:, 0] %= 10
+    (tmp_path / "c.bin").write_bytes(recs.tobytes())
+    src = Cifar10DataSource(str(tmp_path / "c.bin"))
+    assert len(src) == 5 and src.dims == (32, 32, 3)
+    x, y = src[2]
+    assert y == recs[2, 0] and np.array_equal(x.reshape(-1), recs[2, 1:])
+    imgs, lbls = src.batch(1, 3)
+    assert np.array_equal(lbls, recs[1:4, 0]) and np.array_equal(imgs[0].reshape(-1), recs[1, 1:])
+    mean = compute_mean(src)
+    assert np.allclose(mean.reshape(-1), recs[:, 1:].astype(np.float64).mean(0), atol=1e-4)
+    (tmp_path / "short.bin").write_bytes(b"\x00" * 100)
+    with pytest.raises(ValueError):
+        Cifar10DataSource(str(tmp_path / "short.bin"))
+
+
+def test_synthetic_source_is_a_pure_function_of_seed_and_index():
+    a, b = SyntheticDataSource(10, (8, 8, 3), 5, seed=3), SyntheticDataSource(10, (8, 8, 3), 5, seed=3)
+    c = SyntheticDataSource(10, (8, 8, 3), 5, seed=4)
+    assert np.array_equal(a[7][0], b[7][0]) and a[7][1] == b[7][1]
+    assert not np.array_equal(a[7][0], c[7][0])
+    assert a[0][0].shape == (3, 8, 8) and a[0][0].dtype == np.uint8
+
+
+def test_shards_partition_the_source():
+    src = list(range(10))
+    shards = [partition_shard(src, r, 3) for r in range(3)]
+    assert [list(SequentialSampleIter(s)) for s in shards] == [[0, 1, 2, 3], [4, 5, 6], [7, 8, 9]]
+    wrap = cyclic_partition_shard(src, 0, 2, 7)
+    assert list(SequentialSampleIter(wrap)) == [7, 8, 9, 0, 1]
+    with pytest.raises(IndexError):
+        RangeDataShard(src, 2, 4)[5]
+
+
+def test_iterators():
+    shard = RangeDataShard(list(range(20)))
+    r1 = list(RandomSampleDataIter(shard, seed=(1, 2)))
+    assert len(r1) == 20 and r1 == list(RandomSampleDataIter(shard, seed=(1, 2))) and set(r1) <= set(range(20))
+    cyc = iter(CyclicSampleDataIter(RangeDataShard([1, 2, 3])))
+    assert [next(cyc) for _ in range(7)] == [1, 2, 3, 1, 2, 3, 1]
+    assert list(TransformDataIter(SequentialSampleIter(shard), lambda v: v + 1))[:3] == [1, 2, 3]
+    aq = AsyncQueueDataIter(SequentialSampleIter(shard), capacity=4)
+    assert list(aq) == list(range(20))
+    assert list(aq) == list(range(20))                               # restartable
+    assert list(AsyncPoolDataIter(range(50), lambda v: v * 2, num_workers=4, window=8)) == [2 * v for v in range(50)]
+    assert sorted(ParallelJoinDataIter([range(0, 5), range(5, 9)])) == list(range(9))
+
+
+def test_async_iterators_surface_producer_errors():
+    def bad():
+        yield 1
+        raise RuntimeError("decode failed")
+    with pytest.raises(RuntimeError, match="decode failed"):
+        list(AsyncQueueDataIter(bad()))
+
+    def boom(v):
+        if v == 3:
+            raise ValueError("bad sample")
+        return v
+    with pytest.raises(ValueError, match="bad sample"):
+        list(AsyncPoolDataIter(range(6), boom, 2))
+
+
+def test_batch_iter_packs_samples():
+    src = SyntheticDataSource(10, (4, 4, 1), 3, seed=0)
+    batches = list(BatchIter(SequentialSampleIter(RangeDataShard(src)), 4, src.dims, depth=2))
+    assert len(batches) == 2
+    x, y = batches[1]
+    assert x.shape == (4, 1, 4, 4) and x.dtype == torch.uint8 and y.dtype == torch.int32
+    assert np.array_equal(x[1].numpy(), src[5][0]) and int(y[1]) == src[5][1]
+
+
+def test_codecs_and_caffe_datum():
+    img = np.arange(24, dtype=np.uint8).reshape(2, 3, 4)             # [c][h][w]
+    rec = blob.encode_record(img.reshape(-1), (4, 3, 2), dtype="u8")
+    assert np.array_equal(codecs.Array3dDataCodec().decode(rec), img)
+    assert codecs.FakeJpegDataCodec().decode(b"whatever").shape == (3, 256, 256)
+    # hand-assembled Datum: channels=2, height=3, width=4, data, label=7
+    msg = b"\x08\x02\x10\x03\x18\x04" + b"\x22" + bytes([24]) + img.tobytes() + b"\x28\x07"
+    d = codecs.decode_caffe_datum(msg)
+    assert (d["channels"], d["height"], d["width"], d["label"], d["encoded"]) == (2, 3, 4, 7, False)
+    x, y = codecs.datum_to_sample(d)
+    assert np.array_equal(x, img) and y == 7
+    assert np.array_equal(codecs.transpose_whc_to_cwh(codecs.transpose_cwh_to_whc(img)), img)
+    crop, _ = codecs.CenterCropPreproc(2, 1)((img, 0))
+    assert np.array_equal(crop, img[:, 1:2, 1:3])
+    rc, _ = codecs.RandomCropPreproc(2, 2, seed=1)((img, 0))
+    assert rc.shape == (2, 2, 2)

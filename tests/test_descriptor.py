@@ -1,0 +1,121 @@
+"""The shipped .model / .data descriptors parse as they are, and the networks they describe have the
+reference's parameter counts (CPU)."""
+import os
+
+import pytest
+
+from rembrandt_b200.models import descriptor, zoo
+from rembrandt_b200.models import config as C
+from rembrandt_b200.models.net import Net
+
+EX = "/root/reference/examples"
+have_ref = os.path.isdir(EX)
+
+LENET_MODEL = """
+[[layer]]
+name = "data"
+type = "data"
+raw_width = 28
+raw_height = 28
+crop_width = 28
+crop_height = 28
+channels = 1
+[[layer]]
+name = "conv1"
+type = "conv2d"
+conv_size = 5
+conv_stride = 1
+conv_pad = 2
+out_channels = 16
+act_func = "rect"
+init_weights = { kind = "normal", mean = 0.0, std = 0.01 }
+[[layer]]
+name = "pool1"
+pool_size = 2
+pool_stride = 2
+pool_pad = 0
+[[layer]]
+names = ["fc1a", "fc1b"]
+out_channels = 50
+act_func = "relu"
+[[layer]]
+names = ["drop1a", "drop1b"]
+type = "dropout"
+drop_ratio = 0.1
+[[layer]]
+name = "fc2"
+inputs = ["drop1a", "drop1b"]
+type = "fully_conn"
+out_channels = 10
+act_func = "identity"
+[[layer]]
+name = "loss"
+type = "softmax_loss"
+num_categories = 10
+[opt]
+minibatch_size = 64
+init_step_size = 0.01
+momentum = 0.9
+l2_reg_coef = 0.0005
+annealing_policy = { kind = "step", step_iters = 200000, decay = 0.1 }
+"""
+
+
+def test_inline_descriptor_with_irregularities():
+    d = descriptor.parse_model(LENET_MODEL)
+    kinds = [type(o.cfg).__name__ for o in d.config.hidden_ops]
+    assert kinds == ["Conv2dCfg", "Pool2dCfg", "AffineCfg", "DropoutCfg", "AffineCfg"]
+    pool = d.config.hidden_ops[1].cfg
+    assert pool.kind == C.PoolKind.MAX and pool.ceil_mode            # type and kind inferred
+    fc1 = d.config.hidden_ops[2].cfg
+    assert fc1.out_channels == 100 and fc1.act == C.Act.RECT         # towers merged, "relu" accepted
+    assert d.opt.minibatch_size == 64 and d.opt.mu == 0.9 and d.opt.l2_reg_coef == 5e-4
+    assert d.opt.step_size.at_iter(0) == 0.01 and abs(d.opt.step_size.at_iter(200000) - 0.001) < 1e-12
+    net = Net(d.config, 2, device="cpu")
+    assert net.params_len == (16 * 25 + 16) + (14 * 14 * 16 * 100 + 100) + (100 * 10 + 10)
+
+
+@pytest.mark.skipif(not have_ref, reason="reference examples not mounted")
+@pytest.mark.parametrize("name,params", [("mnist_lenet", (16 * 25 + 16) + (14 * 14 * 16 * 100 + 100) + 1010),
+                                         ("imagenet_nin", 7595176), ("imagenet_alexnet", None)])
+def test_shipped_models_parse(name, params):
+    d = descriptor.load_model(f"{EX}/{name}.model", use_crop=False)
+    net = Net(d.config, 1, device="cpu")
+    if params is not None:
+        assert net.params_len == params
+    if name == "imagenet_alexnet":
+        # ungrouped towers: 96/256/384/384/256 convs, two LRN layers, ReLU on pool layers as written
+        convs = [o.cfg.out_channels for o in d.config.hidden_ops if isinstance(o.cfg, C.Conv2dCfg)]
+        assert convs == [96, 256, 384, 384, 256]
+        assert sum(isinstance(o.cfg, C.LrnCfg) for o in d.config.hidden_ops) == 2
+        pools = [o.cfg for o in d.config.hidden_ops if isinstance(o.cfg, C.Pool2dCfg)]
+        assert [p.act for p in pools] == [C.Act.RECT, C.Act.IDENTITY, C.Act.RECT]
+        assert net.params_len == 62378344
+        assert d.opt.minibatch_size == 64
+    if name == "imagenet_nin":
+        sizes = [op.out_hwc[0] for op in net.ops if type(op).__name__ == "Pool2dOp"]
+        assert sizes == [27, 13, 6, 1]                                # ceil-mode pooling, global average
+
+
+@pytest.mark.skipif(not have_ref, reason="reference examples not mounted")
+def test_shipped_data_files_parse():
+    m = descriptor.load_data(f"{EX}/mnist.data")
+    assert m["train"].source == "mnist" and m["train"].normalize and m["valid"].labels_path.endswith("t10k-labels-idx1-ubyte")
+    i = descriptor.load_data(f"{EX}/imagenet.data")
+    assert i["train"].source == "lmdb_caffe" and i["train"].mean_path.endswith(".ndarray")
+
+
+def test_template_parameter_counts():
+    assert Net(zoo.lenet(), 1, device="cpu").params_len == 431080
+    assert Net(zoo.cifar_krizh26(augment=False), 1, device="cpu").params_len == 85098
+    assert Net(zoo.nin(), 1, device="cpu").params_len == 7595176
+    assert Net(zoo.alexnet(), 1, device="cpu").params_len == 62378344
+
+
+def test_bad_descriptors_are_rejected():
+    with pytest.raises(descriptor.DescriptorError):
+        descriptor.parse_model("[opt]\nmomentum = 0.9\n")
+    with pytest.raises(descriptor.DescriptorError):
+        descriptor.parse_model('[[layer]]\nname = "x"\nfoo = 1\n')
+    with pytest.raises(descriptor.DescriptorError):
+        descriptor.parse_data("[dataset.train]\ndata_path = 'x'\n")

@@ -1,0 +1,182 @@
+"""The reference (CPU) execution path against an independently written torch model, the internal parameter
+layouts against the reference's blob layout, and checkpoint / resume (CPU)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from rembrandt_b200.models import zoo
+from rembrandt_b200.models.config import (Act, AffineCfg, BNormConv2dCfg, Conv2dCfg, Data3dCfg, ParamsInit, Pool2dCfg,
+                                          PoolKind, ProjStackResConv2dCfg, SequentialOperatorConfig, SoftmaxKLLossCfg,
+                                          StackResConv2dCfg)
+from rembrandt_b200.models.net import Net
+from rembrandt_b200.ops import layout
+from rembrandt_b200.utils import blob, checkpoint as ckpt
+
+
+class TorchLeNet(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.c1, self.c2 = nn.Conv2d(1, 20, 5), nn.Conv2d(20, 50, 5)
+        self.f1, self.f2 = nn.Linear(800, 500), nn.Linear(500, 10)
+
+    def forward(self, x):
+        x = F.max_pool2d(F.relu(self.c1(x)), 2)
+        x = F.max_pool2d(F.relu(self.c2(x)), 2)
+        return self.f2(F.relu(self.f1(x.flatten(1))))
+
+
+def load_blob_into_torch(model, blob_bytes):
+    """The blob stores, per layer, weights as (fan_in, out) first-dimension-fastest = torch's own memory order."""
+    recs, _ = blob.decode_records(blob_bytes)
+    mods = [model.c1, model.c2, model.f1, model.f2]
+    for m, (w, wd, _), (b, bd, _) in zip(mods, recs[0::2], recs[1::2]):
+        assert wd == (m.weight[0].numel(), m.weight.shape[0]) and bd == (1, m.bias.numel())
+        with torch.no_grad():
+            m.weight.copy_(torch.from_numpy(w).reshape(m.weight.shape))
+            m.bias.copy_(torch.from_numpy(b))
+
+
+def test_lenet_matches_an_independent_torch_model_through_the_blob():
+    net = Net(zoo.lenet(), 5, device="cpu", seed=(1, 2))
+    with torch.no_grad():
+        for op in net.hidden_ops:      # non-zero biases make the check stricter
+            if op.has_params:
+                op.view(op.seg_b).normal_(0, 0.1)
+    model = TorchLeNet()
+    load_blob_into_torch(model, net.encode_params())
+    x = torch.randint(0, 256, (5, 1, 28, 28), dtype=torch.uint8)
+    y = torch.randint(0, 10, (5,))
+    net.load_batch(x, y)
+    net.forward(True)
+    net.backward()
+    loss, _ = net.read_stats()
+    ref = F.cross_entropy(model(x.float() / 255.0), y, reduction="sum") / 5
+    ref.backward()
+    assert abs(loss - float(ref)) < 1e-5
+    # gradients, compared in the reference layout
+    conv1 = net.hidden_ops[0]
+    g = layout.conv_weight_from_internal(conv1.view(conv1.seg_w, "grads"), 1, 5, 5)
+    assert torch.allclose(g, model.c1.weight.grad, atol=1e-6)
+    fc1 = net.hidden_ops[4]
+    gf = fc1._w_ref(fc1.view(fc1.seg_w, "grads"))
+    assert torch.allclose(gf, model.f1.weight.grad, atol=1e-6)
+
+
+def test_strided_first_layer_reference_path_equals_plain_conv():
+    cfg = (SequentialOperatorConfig().data3d(Data3dCfg((23, 23, 3), normalize=True))
+           .conv2d(Conv2dCfg(7, 2, 0, 8, Act.RECT, ParamsInit.kaiming()), "conv1")
+           .pool2d(Pool2dCfg(9, 1, 0, PoolKind.AVERAGE), "gap")
+           .affine(AffineCfg(4, Act.IDENTITY, ParamsInit.xavier()), "fc")
+           .softmax_kl_loss(SoftmaxKLLossCfg(4)))
+    net = Net(cfg, 3, device="cpu", seed=(4, 4))
+    conv = net.hidden_ops[0]
+    assert conv.s2d                                                    # stored in space-to-depth layout ...
+    recs, _ = blob.decode_records(net.encode_params())
+    assert recs[0][1] == (7 * 7 * 3, 8)                                # ... but written as a 7x7x3 filter bank
+    w = torch.from_numpy(recs[0][0]).reshape(8, 3, 7, 7)
+    x = torch.randint(0, 256, (3, 3, 23, 23), dtype=torch.uint8)
+    out = conv.ref_forward(x.float() / 255.0, False, 0)
+    assert torch.allclose(out, torch.relu(F.conv2d(x.float() / 255.0, w, None, stride=2)), atol=1e-5)
+
+
+def test_params_blob_round_trip_is_byte_exact_for_every_template():
+    for fn in (zoo.lenet, lambda: zoo.cifar_krizh26(augment=False), zoo.resnet20_cifar, zoo.mnist_fc2):
+        a = Net(fn(), 2, device="cpu", seed=(5, 6))
+        b = Net(fn(), 2, device="cpu", seed=(7, 8))
+        raw = a.encode_params()
+        assert raw != b.encode_params()
+        b.decode_params(raw)
+        assert b.encode_params() == raw
+        assert torch.equal(a.params.detach(), b.params.detach())
+
+
+def test_state_blob_carries_momentum():
+    a = Net(zoo.lenet(), 2, device="cpu", seed=(5, 6))
+    with torch.no_grad():
+        a.mom.normal_()
+        # padded entries of the momentum never become non-zero in training
+        for op in a.hidden_ops:
+            for s in op.segs:
+                pass
+    b = Net(zoo.lenet(), 2, device="cpu", seed=(9, 9))
+    b.decode_state(a.encode_state())
+    assert torch.equal(a.params.detach(), b.params.detach())
+    for op_a, op_b in zip(a.hidden_ops, b.hidden_ops):
+        if op_a.has_params:
+            assert op_a.encode_params()[0][0].equal(op_b.encode_params()[0][0])
+
+
+def test_residual_blocks_run_and_have_resnet_parameter_layout():
+    k = ParamsInit.kaiming()
+    cfg = (SequentialOperatorConfig().data3d(Data3dCfg((16, 16, 3), normalize=True))
+           .bnorm_conv2d(BNormConv2dCfg(3, 1, 1, 8, Act.RECT, k), "stem")
+           .stack_res_conv2d(StackResConv2dCfg(k), "res1")
+           .proj_stack_res_conv2d(ProjStackResConv2dCfg(16, None, k), "res2")
+           .pool2d(Pool2dCfg(8, 1, 0, PoolKind.AVERAGE), "gap")
+           .affine(AffineCfg(5, Act.IDENTITY, ParamsInit.xavier()), "fc")
+           .softmax_kl_loss(SoftmaxKLLossCfg(5)))
+    net = Net(cfg, 4, device="cpu", seed=(2, 3))
+    # W + 4*Cout per normalised conv: stem 1, identity block 2, projection block 3
+    expect = (3 * 9 * 8 + 32) + 2 * (8 * 9 * 8 + 32) + (8 * 9 * 16 + 64) + (16 * 9 * 16 + 64) + (8 * 16 + 64) + 16 * 5 + 5
+    assert net.params_len == expect
+    assert net.ops[3].out_hwc == (8, 8, 16)                            # projection halves the spatial size
+    x = torch.randint(0, 256, (4, 3, 16, 16), dtype=torch.uint8)
+    y = torch.randint(0, 5, (4,))
+    net.load_batch(x, y)
+    net.forward(True)
+    net.backward()
+    assert torch.isfinite(net.grads).all() and float(net.grads.abs().sum()) > 0
+    stem = net.hidden_ops[0].u
+    assert float(net.seg_view(stem.seg_rm).abs().sum()) > 0            # running statistics were updated
+    assert float(net.seg_view(stem.seg_rm, "grads").abs().sum()) == 0  # and never receive gradients
+    assert not stem.seg_g.decay and stem.seg_w.decay                    # L2 skips the normalisation parameters
+
+
+def test_checkpoint_directory_layout_and_resume(tmp_path):
+    d = str(tmp_path / "ck")
+    net = Net(zoo.lenet(), 2, device="cpu", seed=(1, 1))
+    assert ckpt.can_rollback(d) is None
+    ckpt.checkpoint_state(net, d, rank=0)
+    p100 = ckpt.checkpoint_params(net, 100, d)
+    with torch.no_grad():
+        net.params.add_(1.0)
+    ckpt.checkpoint_params(net, 200, d)
+    assert sorted(os.listdir(d)) == ["checkpoint", "checkpoint.0", "params.latest.blob", "params.t_100.blob",
+                                     "params.t_200.blob", "state.latest.blob.0"]
+    assert open(os.path.join(d, "checkpoint")).read() == "200\n"
+    assert open(os.path.join(d, "checkpoint.0")).read() == "100\n"
+    assert os.readlink(os.path.join(d, "params.latest.blob")) == "params.t_200.blob"
+    assert ckpt.can_rollback(d, 0) == 200 and ckpt.can_rollback(d, 1) is None
+    other = Net(zoo.lenet(), 2, device="cpu", seed=(3, 3))
+    assert ckpt.rollback_params(other, d, 100) == 100
+    assert other.encode_params() == open(p100, "rb").read()
+    assert ckpt.rollback_params(other, d) == 200
+    with pytest.raises(ValueError):
+        ckpt.rollback_params(other, d, 300)
+    # a truncated state blob is reported, not silently accepted
+    path = os.path.join(d, "state.latest.blob.0")
+    raw = open(path, "rb").read()
+    open(path, "wb").write(raw[: len(raw) // 2])
+    with pytest.raises(blob.BlobError):
+        ckpt.rollback_state(other, d, 0)
+
+
+def test_gen1_binary_checkpoint_index_is_readable(tmp_path):
+    import struct
+    (tmp_path / "checkpoint").write_bytes(struct.pack("<Q", 4242))
+    assert ckpt.latest_iteration(str(tmp_path)) == 4242
+
+
+def test_reshape_conv_out_channels():
+    net = Net(zoo.lenet(), 2, device="cpu", seed=(1, 1))
+    raw = net.encode_params()
+    small = ckpt.reshape_conv_out_channels(raw, {0: 12})
+    recs, _ = blob.decode_records(small)
+    full, _ = blob.decode_records(raw)
+    assert recs[0][1] == (25, 12) and recs[1][1] == (1, 12)
+    assert np.array_equal(recs[0][0], full[0][0][: 25 * 12])
+    assert recs[2][1] == full[2][1]

@@ -1,0 +1,159 @@
+"""The training loop on CPU: the MNIST-shaped softmax-regression configuration, sync orders, gradient
+accumulation, CSV traces, checkpoint + resume, validation, straggler injection."""
+import csv
+import os
+
+import pytest
+import torch
+
+from rembrandt_b200.data import BatchIter, CyclicSampleDataIter, RandomSampleDataIter, RangeDataShard, SyntheticDataSource
+from rembrandt_b200.engine import StepEngine
+from rembrandt_b200.models import zoo
+from rembrandt_b200.models.net import Net
+from rembrandt_b200.optim.sgd import (InitBehavior, Momentum, SgdOptConfig, StepSizeReference, StepSizeSchedule, SyncOrder)
+from rembrandt_b200.trainer import ExperimentConfig, SgdOpt
+
+
+def mnist_shape_batches(seed, batch=64, steps=100):
+    g = torch.Generator().manual_seed(seed)
+    for _ in range(steps):
+        yield (torch.rand(batch, 1, 28, 28, generator=g).mul(255).to(torch.uint8),
+               torch.randint(0, 10, (batch,), generator=g, dtype=torch.int32))
+
+
+def make(cfg_fn=zoo.mnist_fc1, batch=64, **opt_kw):
+    opt_kw.setdefault("minibatch_size", batch)
+    opt_kw.setdefault("step_size", StepSizeSchedule.constant(0.01))
+    opt_kw.setdefault("momentum", Momentum.UPDATE)
+    opt_kw.setdefault("display_iters", 0)
+    opt = SgdOptConfig(**opt_kw)
+    net = Net(cfg_fn(), batch, device="cpu", seed=(0, 0), minibatch_size=opt.minibatch_size)
+    return opt, StepEngine(net, opt), net
+
+
+def test_mnist_shape_softmax_regression_100_steps_seed0():
+    """Input [64,784] uniform, labels uniform 0..9, affine 784->10 + softmax CE, SGD lr 0.01 momentum 0.9, 100 steps:
+    labels carry no signal, so the loss must stay near ln(10) while the plumbing runs end to end."""
+    opt, eng, net = make()
+    sgd = SgdOpt(opt, eng, quiet=True)
+    losses = []
+    for x, y in mnist_shape_batches(0):
+        eng.feed(x, y)
+        losses.append(eng.step()[0])
+    assert eng.iter == 100 and net.t == 100
+    assert all(1.9 < l < 2.9 for l in losses), (min(losses), max(losses))
+    assert float(net.mom.abs().sum()) > 0 and float(net.grads.abs().sum()) == 0
+
+
+def test_learns_separable_data_and_validates():
+    src = SyntheticDataSource(512, (28, 28, 1), 10, seed=1, separable=True)
+    opt, eng, net = make(batch=32, step_size=StepSizeSchedule.constant(0.05), valid_iters=4, display_iters=10)
+    sgd = SgdOpt(opt, eng, quiet=True)
+    train = BatchIter(RandomSampleDataIter(RangeDataShard(src), seed=(3, 4)), 32, src.dims)
+    hist = sgd.train(train, None, max_iters=60)
+    assert hist[-1][1] < 0.5 * hist[0][1] and hist[-1][2] > 0.9
+    loss, acc = sgd.validate(BatchIter(CyclicSampleDataIter(RangeDataShard(src)), 32, src.dims), 4)
+    assert acc > 0.9 and loss < 0.7
+
+
+@pytest.mark.parametrize("order", list(SyncOrder))
+def test_sync_orders_agree_on_a_single_worker(order):
+    """With one worker nothing is exchanged, so every order must give the same parameters."""
+    ref_opt, ref_eng, ref_net = make(sync_order=SyncOrder.SYNC_GRADS_THEN_STEP)
+    opt, eng, net = make(sync_order=order)
+    for x, y in mnist_shape_batches(5, steps=5):
+        for e in (ref_eng, eng):
+            e.feed(x, y)
+            e.step()
+    assert torch.allclose(net.params.detach(), ref_net.params.detach(), atol=1e-7)
+
+
+def test_gradient_accumulation_equals_one_large_batch():
+    opt_a, eng_a, net_a = make(batch=64, minibatch_size=64)
+    opt_b, eng_b, net_b = make(batch=16, minibatch_size=64)
+    assert eng_b.accum == 4
+    x, y = next(mnist_shape_batches(9))
+    eng_a.feed(x, y)
+    eng_a.step()
+    for i in range(4):
+        eng_b.feed(x[16 * i:16 * i + 16], y[16 * i:16 * i + 16])
+        eng_b.step()
+    assert eng_b.iter == 1 and net_b.t == 4
+    assert torch.allclose(net_a.params.detach(), net_b.params.detach(), atol=1e-6)
+
+
+def test_trace_csv_checkpoint_and_resume(tmp_path):
+    d = str(tmp_path / "run")
+    common = dict(checkpoint_iters=4, save_iters=4, checkpoint_dir=d)
+    opt, eng, net = make(batch=16, **common)
+    sgd = SgdOpt(opt, eng, quiet=True)
+    sgd.train(mnist_shape_batches(1, 16, 8), None, max_iters=8)
+    sgd.trace.close()
+    rows = list(csv.reader(open(os.path.join(d, "trace_sgd.0.log"))))
+    assert rows[0] == ["t", "event", "loss", "error", "elapsed"]
+    assert [r[1] for r in rows[1:]].count("step") == 8
+    assert open(os.path.join(d, "checkpoint")).read() == "8\n"
+    assert os.path.exists(os.path.join(d, "params.t_4.blob")) and os.path.exists(os.path.join(d, "state.latest.blob.0"))
+    # an uninterrupted 12-iteration run ...
+    opt_u, eng_u, net_u = make(batch=16)
+    SgdOpt(opt_u, eng_u, quiet=True).train(mnist_shape_batches(1, 16, 12), None, max_iters=12)
+    # ... equals resuming from the checkpoint at 8 and running 4 more on the same data stream
+    opt_r, eng_r, net_r = make(batch=16, **common)
+    sgd_r = SgdOpt(opt_r, eng_r, quiet=True)
+    stream = mnist_shape_batches(1, 16, 12)
+    for _ in range(8):
+        next(stream)
+    sgd_r.train(stream, None, max_iters=12)
+    assert eng_r.iter == 12
+    assert torch.allclose(net_r.params.detach(), net_u.params.detach(), atol=1e-6)
+    # a second run in the same directory does not overwrite the first trace
+    assert os.path.exists(os.path.join(d, "trace_sgd.0.log.1"))
+
+
+def test_resume_from_a_given_iteration(tmp_path):
+    d = str(tmp_path / "run")
+    opt, eng, net = make(batch=16, checkpoint_iters=2, save_iters=2, checkpoint_dir=d)
+    SgdOpt(opt, eng, quiet=True).train(mnist_shape_batches(2, 16, 4), None, max_iters=4)
+    opt2, eng2, net2 = make(batch=16, checkpoint_dir=d, init=InitBehavior.RESUME_FROM, resume_t=2)
+    sgd2 = SgdOpt(opt2, eng2, quiet=True)
+    assert sgd2._init_or_resume() == 2
+    assert net2.encode_params() == open(os.path.join(d, "params.t_2.blob"), "rb").read()
+
+
+def test_step_size_reference_checkpoint_freezes_the_rate_between_checkpoints():
+    sched = StepSizeSchedule.anneal1(0.1, 3, 0.01)
+    opt, eng, net = make(batch=16, step_size=sched, step_ref=StepSizeReference.CHECKPOINT, checkpoint_iters=4)
+    sgd = SgdOpt(opt, eng, quiet=True)
+    seen = []
+    orig = eng._update
+
+    def spy():
+        seen.append(eng.lr)
+        orig()
+    eng._update = spy
+    sgd.train(mnist_shape_batches(3, 16, 8), None, max_iters=8)
+    assert seen[:4] == [0.1] * 4 and seen[5:] == [0.01] * 3       # changes only after the checkpoint at t = 4
+
+
+def test_straggler_injection_only_delays():
+    opt, eng, net = make(batch=16)
+    opt2, eng2, net2 = make(batch=16)
+    SgdOpt(opt, eng, ExperimentConfig([0], 5), quiet=True).train(mnist_shape_batches(4, 16, 5), None, max_iters=5)
+    SgdOpt(opt2, eng2, quiet=True).train(mnist_shape_batches(4, 16, 5), None, max_iters=5)
+    assert torch.equal(net.params.detach(), net2.params.detach())
+
+
+def test_nesterov_prelookahead_and_report_hook():
+    class Rep:
+        def __init__(self):
+            self.t = []
+
+        def update_training(self, t, loss, acc):
+            self.t.append(t)
+
+        def update_validation(self, *a):
+            pass
+    opt, eng, net = make(batch=16, momentum=Momentum.UPDATE_NESTEROV, display_iters=2)
+    rep = Rep()
+    SgdOpt(opt, eng, report=rep, quiet=True).train(mnist_shape_batches(6, 16, 6), None, max_iters=6)
+    assert rep.t == [2, 4, 6]
