@@ -1,0 +1,81 @@
+"""bench-conv: time the implicit-GEMM convolution kernels on given or built-in shapes and report achieved
+TFLOP/s (counterpart of the reference's tools/bench-cudnn.rs, which timed cuDNN on NIN / AlexNet-shaped
+convolutions). Timing uses CUDA events after warm-up; `--pass` selects fprop / dgrad / wgrad.
+
+    python -m rembrandt_b200.cli.bench_conv --shape alexnet_conv2 --batch 128 --pass all
+"""
+import argparse
+import json
+
+import torch
+
+from ..ops import native_ops as K
+from ..utils.timing import time_fn
+
+SHAPES = {
+    # name: (C, H, W, Kout, R, stride, pad)
+    "alexnet_conv1_s2d": (48, 57, 57, 96, 3, 1, 0),
+    "alexnet_conv2": (96, 27, 27, 256, 5, 1, 2),
+    "alexnet_conv3": (256, 13, 13, 384, 3, 1, 1),
+    "alexnet_conv4": (384, 13, 13, 384, 3, 1, 1),
+    "alexnet_conv5": (384, 13, 13, 256, 3, 1, 1),
+    "nin_cccp1": (96, 54, 54, 96, 1, 1, 0),
+    "nin_conv2": (96, 27, 27, 256, 5, 1, 2),
+    "nin_cccp3": (256, 27, 27, 256, 1, 1, 0),
+    "nin_conv3": (256, 13, 13, 384, 3, 1, 1),
+    "nin_conv4": (384, 6, 6, 1024, 3, 1, 1),
+    "nin_cccp7": (1024, 6, 6, 1024, 1, 1, 0),
+}
+
+
+def run(name, batch, passes, iters, warmup):
+    C, H, W, Ko, R, s, p = SHAPES[name]
+    Cp, Kp = K.pad_channels(C), K.pad_channels(Ko)
+    P, Q = (H + 2 * p - R) // s + 1, (W + 2 * p - R) // s + 1
+    dev = "cuda"
+    x = torch.randn(batch, H, W, Cp, device=dev).bfloat16()
+    w = (torch.randn(Ko, R * R, Cp, device=dev) * 0.05).bfloat16()
+    wt = torch.zeros(Cp, R * R, Kp, device=dev, dtype=torch.bfloat16)
+    K.pack_dgrad_filters(w, wt, Ko, Kp, R * R, Cp)
+    b = torch.zeros(Ko, device=dev)
+    y = torch.zeros(batch, P, Q, Kp, device=dev, dtype=torch.bfloat16)
+    dy = torch.randn(batch, P, Q, Kp, device=dev).bfloat16()
+    dx = torch.zeros_like(x)
+    dw = torch.zeros(Ko, R * R, Cp, device=dev)
+    flops = 2.0 * batch * P * Q * Ko * R * R * C
+    out = {"shape": name, "batch": batch, "gflop": flops / 1e9}
+    fns = {
+        "fprop": lambda: K.conv_fprop_tc(x, batch, H, W, Cp, w, Ko, R, R, s, p, p, P, Q, y, Kp, bias=b, relu=True,
+                                         n_valid=Ko, n_store=Kp),
+        "dgrad": lambda: K.conv_fprop_tc(dy, batch, P, Q, Kp, wt, Cp, R, R, 1, R - 1 - p, R - 1 - p, H, W, dx, Cp,
+                                         mask_src=x, n_valid=C, n_store=Cp),
+        "wgrad": lambda: K.conv_wgrad_tc(x, batch, H, W, Cp, dy, Kp, Ko, R, R, s, p, p, P, Q, dw),
+    }
+    for name_, fn in fns.items():
+        if passes != "all" and passes != name_:
+            continue
+        if name_ == "dgrad" and s != 1:
+            continue
+        ms = time_fn(fn, iters, warmup)
+        out[name_ + "_ms"] = round(ms, 4)
+        out[name_ + "_tflops"] = round(flops / ms / 1e9, 1)
+    torch.cuda.synchronize()
+    out["status"] = K.read_status()
+    return out
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__)
+    ap.add_argument("--shape", default="all", choices=["all"] + sorted(SHAPES))
+    ap.add_argument("--batch", type=int, default=128)
+    ap.add_argument("--pass", dest="passes", default="all", choices=["all", "fprop", "dgrad", "wgrad"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    args = ap.parse_args(argv)
+    names = sorted(SHAPES) if args.shape == "all" else [args.shape]
+    for n in names:
+        print(json.dumps(run(n, args.batch, args.passes, args.iters, args.warmup)))
+
+
+if __name__ == "__main__":
+    main()
