@@ -6,30 +6,36 @@ namespace rb {
 
 // out[c] += sum_r x[r][c]   (bias gradient; replaces cuDNN ConvolutionBackwardBias and the ones-vector
 // gemm of the reference, src/operator/mod.rs:1169,1775-1781)
-__global__ void colsum_kernel(const bf16* __restrict__ x, long long rows, int ld, int cols, float* __restrict__ out) {
-  __shared__ float red[8][257];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int c0 = (blockIdx.x * 32 + tx) * 8;
+__global__ void colsum_kernel(const bf16* __restrict__ x, long long rows, int ld, int cols, float* __restrict__ out,
+                              int tpr) {
+  // tpr threads (8 columns each) per row, 256 / tpr rows per pass: narrow matrices keep all lanes busy
+  __shared__ float red[256 * 8];
+  const int rpp = 256 / tpr;
+  const int tx = threadIdx.x % tpr, ty = threadIdx.x / tpr;
+  const int c0 = (blockIdx.x * tpr + tx) * 8;
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-  if (c0 < ld) {
-    for (long long r = (long long)blockIdx.y * 8 + ty; r < rows; r += (long long)gridDim.y * 8) {
+  if (ty < rpp && c0 < ld) {
+    for (long long r = (long long)blockIdx.y * rpp + ty; r < rows; r += (long long)gridDim.y * rpp) {
       float v[8];
       load8(x + r * ld + c0, v);
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] += v[j];
     }
   }
+  const int width = tpr * 8;
+  if (ty < rpp) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) red[ty][tx * 8 + j] = acc[j];
+    for (int j = 0; j < 8; ++j) red[ty * width + tx * 8 + j] = acc[j];
+  }
   __syncthreads();
-  const int c = threadIdx.x;  // 256 columns per block
-  float s = 0.f;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) s += red[k][c];
-  const int gc = blockIdx.x * 256 + c;
-  if (gc < cols) atomicAdd(out + gc, s);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float sum = 0.f;
+    for (int k = 0; k < rpp; ++k) sum += red[k * width + c];
+    const int gc = blockIdx.x * width + c;
+    if (gc < cols) atomicAdd(out + gc, sum);
+  }
 }
 
 // y[r][c] = act(acc[r][c] + bias[c]) for c < n_valid, 0 for padded columns; acc is re-zeroed so the
@@ -187,12 +193,16 @@ extern "C" {
 
 int rb_colsum(const void* x, long long rows, int ld, int cols, float* out, cudaStream_t st) {
   if (ld % 8) return -10;
-  dim3 grid((ld + 255) / 256, 1);
-  long long gy = rows / 64;
+  const int groups = ld / 8;
+  const int tpr = groups < 32 ? groups : 32;
+  const int rpp = 256 / tpr;
+  dim3 grid((groups + tpr - 1) / tpr, 1);
+  long long gy = rows / (rpp * 4);
   if (gy < 1) gy = 1;
-  if (gy > 256) gy = 256;
+  const long long cap = (148LL * 8) / grid.x > 1 ? (148LL * 8) / grid.x : 1;
+  if (gy > cap) gy = cap;
   grid.y = (unsigned)gy;
-  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, rows, ld, cols, out);
+  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, rows, ld, cols, out, tpr);
   return RB_LAUNCH_OK();
 }
 

@@ -1,9 +1,20 @@
 // Persistent, warp-specialised tcgen05 GEMM / implicit-GEMM convolution for sm_100a.
 //
 //   warp 0      TMA producer (one elected lane): tiled or im2col loads into a ring of smem stages
-//   warp 1      MMA issuer (one elected lane): tcgen05.mma, fp32 accumulators in TMEM (2 x 256 columns,
-//               so the epilogue of tile i overlaps the main loop of tile i+1); owns TMEM alloc/dealloc
-//   warps 2..5  epilogue: tcgen05.ld -> bias / ReLU / mask -> bf16 stores, or fp32 store / red.add (split-K)
+//   warp 1      MMA issuer (one elected lane): tcgen05.mma, fp32 accumulators in TMEM; owns TMEM alloc/dealloc
+//   warps 2..9  epilogue: tcgen05.ld -> bias / ReLU / mask -> swizzled smem -> TMA store (bf16), or fp32
+//               store / red.add (split-K). Two warps share each TMEM lane quarter and alternate column slabs:
+//               with one warp per scheduler the epilogue is bound by instruction latency, not bandwidth.
+//
+// The kernel is bound by the bytes it must bring into shared memory per MMA (measured: ~30 GB/s per SM of
+// TMA fill against a tensor pipe that could consume several times that), so the tile shape is chosen to cut
+// those bytes:
+//   * a work item may cover two 128-row sub-tiles (mt = 2) that share one B stage and use two accumulators;
+//   * when the whole B panel (every k-block of the filter bank) fits in shared memory and the CTA only ever
+//     needs that one panel, it is loaded once per CTA and stays resident (b_resident) while A streams;
+//   * split-K (fp32 red.add epilogue) spreads long reductions over all SMs.
+// With two accumulator sets in TMEM the epilogue of work item i overlaps the main loop of item i+1; a
+// 256 x 256 item needs all 512 columns and runs without that overlap.
 //
 // Every mbarrier wait is bounded; on a timeout the CTA raises an abort flag, records
 // RB_STATUS_MBAR_TIMEOUT in the status word, drains its outstanding TMA copies (bounded),
@@ -11,14 +22,17 @@
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
 #include "common.cuh"
+#include <stdlib.h>
 
 namespace rb {
 
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;   // producer warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
 constexpr int MAX_STAGES = 8;
-constexpr int TILE_SMEM_BYTES = 192 * 1024;
-constexpr int GEMM_SMEM_BYTES = TILE_SMEM_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+constexpr int TILE_SMEM_BYTES = 192 * 1024;   // B panel (if resident) + stage ring
+constexpr int STAGING_BYTES = 32 * 1024;      // epilogue: 8 warps x one slab of 32 rows x 128 B
+constexpr int GEMM_SMEM_BYTES = TILE_SMEM_BYTES + STAGING_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 struct SharedCtl {
@@ -26,6 +40,8 @@ struct SharedCtl {
   uint64_t empty[MAX_STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t b_full;
+  uint64_t mask_bar[EPI_WARPS];
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -38,23 +54,71 @@ __device__ __forceinline__ bool ctl_wait(SharedCtl* ctl, uint64_t* bar, uint32_t
   return false;
 }
 
+// base pixel (w, h, n) of output position `pix` for the im2col tensor maps
+__device__ __forceinline__ void pixel_coords(const GemmTcParams& p, int pix, int& w, int& h, int& n) {
+  const int pq = p.cv_P * p.cv_Q;
+  n = pix / pq;
+  const int r2 = pix - n * pq;
+  const int pp = r2 / p.cv_Q;
+  const int qq = r2 - pp * p.cv_Q;
+  w = qq * p.cv_stride + p.cv_lower_w;
+  h = pp * p.cv_stride + p.cv_lower_h;
+}
+
+__device__ __forceinline__ void load_b(const GemmTcParams& p, uint8_t* sb, uint64_t* bar, int kb, int n0, int b_tap,
+                                       int b_c0) {
+  if (p.b_mode == B_TILED_K) {
+    tma_load_2d(sb, &p.tm_b, bar, kb * p.bk, n0);
+  } else if (p.b_mode == B_TILED_K3) {
+    const int tap = kb / p.cv_cchunks;
+    const int cc = kb - tap * p.cv_cchunks;
+    tma_load_3d(sb, &p.tm_b, bar, cc * p.bk, tap, n0);
+  } else if (p.b_mode == B_TILED_MN) {
+    for (int j = 0; j < p.bn_load / 64; ++j) tma_load_2d(sb + j * p.bk * 128, &p.tm_b, bar, n0 + 64 * j, kb * p.bk);
+  } else {  // B_IM2COL_MN
+    int w, h, n_img;
+    pixel_coords(p, kb * p.bk, w, h, n_img);
+    if (p.wg_taps > 1) {
+      // several filter taps side by side in one column tile: they share the A (dY) stage
+      const int apt = p.wg_cw / 64;  // 64-column atoms per tap
+      for (int t = 0; t < p.wg_taps; ++t) {
+        const int tap = min(b_tap + t, p.wg_ntaps - 1);   // slots past the last tap reload it; the epilogue skips them
+        const int r = tap / p.cv_S;
+        const int sx = tap - r * p.cv_S;
+        for (int j = 0; j < apt; ++j)
+          tma_load_im2col_4d(sb + (t * apt + j) * p.bk * 128, &p.tm_b, bar, 64 * j, w, h, n_img, (uint16_t)sx,
+                             (uint16_t)r);
+      }
+    } else {
+      const int r = b_tap / p.cv_S;
+      const int sx = b_tap - r * p.cv_S;
+      for (int j = 0; j < p.bn_load / 64; ++j)
+        tma_load_im2col_4d(sb + j * p.bk * 128, &p.tm_b, bar, b_c0 + 64 * j, w, h, n_img, (uint16_t)sx, (uint16_t)r);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // tiles start on a 1024-byte boundary (swizzle atoms); control block follows the tiles
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(tiles + TILE_SMEM_BYTES);
+  uint8_t* staging = tiles + TILE_SMEM_BYTES;
+  SharedCtl* ctl = reinterpret_cast<SharedCtl*>(staging + STAGING_BYTES);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const int a_bytes = BM * p.bk * 2;
-  const int b_bytes = p.bn * p.bk * 2;
-  const int stage_bytes = a_bytes + b_bytes;
+  const int mt = p.mt;
+  const int a_bytes = BM * p.bk * 2;            // one 128-row sub-tile
+  const int b_bytes = p.bn_load * p.bk * 2;
+  const int panel_bytes = p.b_resident ? p.num_kb * b_bytes : 0;
+  const int stage_bytes = mt * a_bytes + (p.b_resident ? 0 : b_bytes);
+  uint8_t* ring = tiles + panel_bytes;
   const int stages = p.stages;
 
-  const int m_tiles = (p.M + BM - 1) / BM;
+  const int m_items = (p.M + BM * mt - 1) / (BM * mt);
   const int n_tiles = p.n_tiles;
-  const int num_work = m_tiles * n_tiles * p.split_k;
+  const int num_work = m_items * n_tiles * p.split_k;
   const int kb_per_split = (p.num_kb + p.split_k - 1) / p.split_k;
 
   if (threadIdx.x == 0) {
@@ -64,12 +128,16 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->acc_full[a], 1);
-      mbar_init(&ctl->acc_empty[a], 4);
+      mbar_init(&ctl->acc_empty[a], EPI_WARPS);
     }
+    mbar_init(&ctl->b_full, 1);
+    for (int w = 0; w < EPI_WARPS; ++w) mbar_init(&ctl->mask_bar[w], 1);
     ctl->abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&p.tm_a);
     tma_prefetch_desc(&p.tm_b);
+    if (p.epi == EPI_BF16) tma_prefetch_desc(&p.tm_d);
+    if (p.epi == EPI_BF16 && p.mask_src) tma_prefetch_desc(&p.tm_mask);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, 512);
@@ -87,75 +155,60 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       uint32_t ph = 0;
       int issued = 0;
       bool ok = true;
+      if (p.b_resident && blockIdx.x < num_work) {
+        // the one B panel this CTA will ever need: all k-blocks, loaded once
+        mbar_expect_tx(&ctl->b_full, (uint32_t)panel_bytes);
+        for (int kb = 0; kb < p.num_kb; ++kb) load_b(p, tiles + kb * b_bytes, &ctl->b_full, kb, 0, 0, 0);
+      }
       for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const int z = work / (m_tiles * n_tiles);
-        const int rem = work - z * (m_tiles * n_tiles);
-        const int tn = rem / m_tiles;
-        const int tm = rem - tn * m_tiles;
-        const int m0 = tm * BM;
+        const int z = work / (m_items * n_tiles);
+        const int rem = work - z * (m_items * n_tiles);
+        const int tn = rem / m_items;
+        const int tm = rem - tn * m_items;
+        const int m0 = tm * BM * mt;
         const int kb0 = z * kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + kb_per_split);
 
-        // geometry that is fixed for the tile
-        int a_w = 0, a_h = 0, a_n = 0;
+        // geometry that is fixed for the work item
+        int a_w[2] = {0, 0}, a_h[2] = {0, 0}, a_n[2] = {0, 0};
         if (p.a_mode == A_IM2COL_K) {
-          const int pq = p.cv_P * p.cv_Q;
-          a_n = m0 / pq;
-          const int r2 = m0 - a_n * pq;
-          const int pp = r2 / p.cv_Q;
-          const int qq = r2 - pp * p.cv_Q;
-          a_w = qq * p.cv_stride + p.cv_lower_w;
-          a_h = pp * p.cv_stride + p.cv_lower_h;
+          for (int j = 0; j < mt; ++j) pixel_coords(p, m0 + j * BM, a_w[j], a_h[j], a_n[j]);
         }
         int b_tap = 0, b_c0 = 0, n0 = tn * p.bn;
         if (p.b_mode == B_IM2COL_MN) {
-          b_tap = tn / p.wg_ctiles;
-          b_c0 = (tn - b_tap * p.wg_ctiles) * p.bn;
+          if (p.wg_taps > 1) {
+            b_tap = tn * p.wg_taps;
+          } else {
+            b_tap = tn / p.wg_ctiles;
+            b_c0 = (tn - b_tap * p.wg_ctiles) * p.bn;
+          }
         }
 
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ctl_wait(ctl, &ctl->empty[s], ph ^ 1u, p.status)) { ok = false; break; }
-          uint8_t* sa = tiles + s * stage_bytes;
-          uint8_t* sb = sa + a_bytes;
+          uint8_t* sa = ring + s * stage_bytes;
+          uint8_t* sb = sa + mt * a_bytes;
           mbar_expect_tx(&ctl->full[s], (uint32_t)stage_bytes);
-          // ---- A ----
-          if (p.a_mode == A_TILED_K) {
-            tma_load_2d(sa, &p.tm_a, &ctl->full[s], kb * p.bk, m0);
-          } else if (p.a_mode == A_IM2COL_K) {
-            const int tap = kb / p.cv_cchunks;
-            const int cc = kb - tap * p.cv_cchunks;
-            const int r = tap / p.cv_S;
-            const int sx = tap - r * p.cv_S;
-            tma_load_im2col_4d(sa, &p.tm_a, &ctl->full[s], cc * p.bk, a_w, a_h, a_n, (uint16_t)sx, (uint16_t)r);
-          } else {  // A_TILED_MN: two boxes of 64 rows(M) x bk
-            tma_load_2d(sa, &p.tm_a, &ctl->full[s], m0, kb * p.bk);
-            tma_load_2d(sa + p.bk * 128, &p.tm_a, &ctl->full[s], m0 + 64, kb * p.bk);
+          // ---- A: one load group per sub-tile ----
+          for (int j = 0; j < mt; ++j) {
+            uint8_t* saj = sa + j * a_bytes;
+            const int mj = m0 + j * BM;
+            if (p.a_mode == A_TILED_K) {
+              tma_load_2d(saj, &p.tm_a, &ctl->full[s], kb * p.bk, mj);
+            } else if (p.a_mode == A_IM2COL_K) {
+              const int tap = kb / p.cv_cchunks;
+              const int cc = kb - tap * p.cv_cchunks;
+              const int r = tap / p.cv_S;
+              const int sx = tap - r * p.cv_S;
+              tma_load_im2col_4d(saj, &p.tm_a, &ctl->full[s], cc * p.bk, a_w[j], a_h[j], a_n[j], (uint16_t)sx,
+                                 (uint16_t)r);
+            } else {  // A_TILED_MN: two boxes of 64 rows(M) x bk
+              tma_load_2d(saj, &p.tm_a, &ctl->full[s], mj, kb * p.bk);
+              tma_load_2d(saj + p.bk * 128, &p.tm_a, &ctl->full[s], mj + 64, kb * p.bk);
+            }
           }
           // ---- B ----
-          if (p.b_mode == B_TILED_K) {
-            tma_load_2d(sb, &p.tm_b, &ctl->full[s], kb * p.bk, n0);
-          } else if (p.b_mode == B_TILED_K3) {
-            const int tap = kb / p.cv_cchunks;
-            const int cc = kb - tap * p.cv_cchunks;
-            tma_load_3d(sb, &p.tm_b, &ctl->full[s], cc * p.bk, tap, n0);
-          } else if (p.b_mode == B_TILED_MN) {
-            for (int j = 0; j < p.bn / 64; ++j)
-              tma_load_2d(sb + j * p.bk * 128, &p.tm_b, &ctl->full[s], n0 + 64 * j, kb * p.bk);
-          } else {  // B_IM2COL_MN
-            const int pix = kb * p.bk;
-            const int pq = p.cv_P * p.cv_Q;
-            const int n_img = pix / pq;
-            const int r2 = pix - n_img * pq;
-            const int pp = r2 / p.cv_Q;
-            const int qq = r2 - pp * p.cv_Q;
-            const int w = qq * p.cv_stride + p.cv_lower_w;
-            const int h = pp * p.cv_stride + p.cv_lower_h;
-            const int r = b_tap / p.cv_S;
-            const int sx = b_tap - r * p.cv_S;
-            for (int j = 0; j < p.bn / 64; ++j)
-              tma_load_im2col_4d(sb + j * p.bk * 128, &p.tm_b, &ctl->full[s], b_c0 + 64 * j, w, h, n_img,
-                                 (uint16_t)sx, (uint16_t)r);
-          }
+          if (!p.b_resident) load_b(p, sb, &ctl->full[s], kb, n0, b_tap, b_c0);
           ++issued;
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
@@ -170,6 +223,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           --ds;
           mbar_wait_bounded(&ctl->full[ds], dph, 100000000ull);
         }
+        if (p.b_resident) mbar_wait_bounded(&ctl->b_full, 0u, 100000000ull);
       }
     }
   } else if (warp == 1) {
@@ -190,57 +244,68 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       const uint32_t a_adv = a_mn ? (2048u >> 4) : (32u >> 4);  // per 16-deep MMA, in 16-byte units
       const uint32_t b_adv = b_mn ? (2048u >> 4) : (32u >> 4);
       const int kk_steps = p.bk / 16;
+      const uint32_t set_cols = (uint32_t)(mt * p.acc_stride);
 
       int s = 0;
       uint32_t ph = 0;
       int acc = 0;
       uint32_t acc_ph = 0;
       bool ok = true;
+      if (p.b_resident && blockIdx.x < num_work) ok = ctl_wait(ctl, &ctl->b_full, 0u, p.status);
       for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const int z = work / (m_tiles * n_tiles);
+        const int z = work / (m_items * n_tiles);
         const int kb0 = z * kb_per_split;
         const int kb1 = min(p.num_kb, kb0 + kb_per_split);
         if (!ctl_wait(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + (uint32_t)acc * 256u;
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * set_cols;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!ctl_wait(ctl, &ctl->full[s], ph, p.status)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t sa = smem_u32(tiles + s * stage_bytes);
-          const uint32_t sb = sa + (uint32_t)a_bytes;
-          const uint64_t da = make_smem_desc(sa, a_lbo, a_sbo, a_lay);
+          const uint32_t sa = smem_u32(ring + s * stage_bytes);
+          const uint32_t sb = p.b_resident ? smem_u32(tiles + kb * b_bytes) : sa + (uint32_t)(mt * a_bytes);
           const uint64_t db = make_smem_desc(sb, b_lbo, b_sbo, b_lay);
-          for (int kk = 0; kk < kk_steps; ++kk) {
-            tc_mma_f16(d_tmem, da + (uint64_t)(a_adv * kk), db + (uint64_t)(b_adv * kk), idesc,
-                       (kb > kb0 || kk > 0) ? 1u : 0u);
+          for (int j = 0; j < mt; ++j) {
+            const uint64_t da = make_smem_desc(sa + (uint32_t)(j * a_bytes), a_lbo, a_sbo, a_lay);
+            for (int kk = 0; kk < kk_steps; ++kk) {
+              tc_mma_f16(d_tmem + (uint32_t)(j * p.acc_stride), da + (uint64_t)(a_adv * kk),
+                         db + (uint64_t)(b_adv * kk), idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+            }
           }
           tc_commit(&ctl->empty[s]);  // stage is free once these MMAs have read it
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
         if (!ok) break;
         tc_commit(&ctl->acc_full[acc]);
-        if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+        if (++acc == p.acc_bufs) { acc = 0; acc_ph ^= 1u; }
       }
     }
   } else {
     // ------------------------------ epilogue ------------------------------
     const int lane_base = (warp & 3) * 32;  // TMEM lanes this warp may read
+    const uint32_t set_cols = (uint32_t)(mt * p.acc_stride);
+    const int col_half = (warp - 2) >> 2;        // which of the two warps of this lane quarter
+    uint8_t* stg = staging + (warp - 2) * 4096;  // one 32-row x 128-byte slab buffer per warp
+    const bool has_bias = p.bias != nullptr;
+    uint64_t* mbar_m = &ctl->mask_bar[warp - 2];
+    uint32_t mask_ph = 0;
+    const float act_lo = p.relu ? 0.f : -INFINITY;
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-      const int z = work / (m_tiles * n_tiles);
-      const int rem = work - z * (m_tiles * n_tiles);
-      const int tn = rem / m_tiles;
-      const int tm = rem - tn * m_tiles;
-      (void)z;
+      const int z = work / (m_items * n_tiles);
+      const int rem = work - z * (m_items * n_tiles);
+      const int tn = rem / m_items;
+      const int tm = rem - tn * m_items;
       if (!ctl_wait(ctl, &ctl->acc_full[acc], acc_ph, p.status)) { ok = false; break; }
       tc_fence_after();
-      const int row = tm * BM + lane_base + lane;
-      const bool row_ok = row < p.M;
       int col0;        // first column of D this tile writes
       int col_limit;   // tile-local bound on stored columns
-      if (p.b_mode == B_IM2COL_MN) {
+      if (p.b_mode == B_IM2COL_MN && p.wg_taps > 1) {
+        col0 = 0;            // columns are mapped per 32-column chunk below
+        col_limit = p.bn;
+      } else if (p.b_mode == B_IM2COL_MN) {
         const int tap = tn / p.wg_ctiles;
         const int c0 = (tn - tap * p.wg_ctiles) * p.bn;
         col0 = tap * p.wg_cpad + c0;
@@ -249,48 +314,113 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         col0 = tn * p.bn;
         col_limit = min(p.bn, p.n_store - col0);
       }
-      const uint32_t t_addr = tmem_base + (uint32_t)acc * 256u + ((uint32_t)lane_base << 16);
-      for (int c = 0; c < p.bn; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32(t_addr + (uint32_t)c, v);
-        tmem_ld_wait();
-        if (!row_ok || c >= col_limit) continue;
-        const int gcol = col0 + c;
+      for (int j = 0; j < mt; ++j) {
+        const int row0 = tm * BM * mt + j * BM + lane_base;   // first row of this warp's 32-row band
+        const int row = row0 + lane;
+        const bool row_ok = row < p.M;
+        const uint32_t t_addr =
+            tmem_base + (uint32_t)acc * set_cols + (uint32_t)(j * p.acc_stride) + ((uint32_t)lane_base << 16);
         if (p.epi == EPI_BF16) {
-          __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(p.D) + (size_t)row * p.ldd + gcol;
-          const __nv_bfloat16* mrow = p.mask_src ? p.mask_src + (size_t)row * p.ldd + gcol : nullptr;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            float f[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int n = gcol + q * 8 + j;
-              float x = __uint_as_float(v[q * 8 + j]);
-              if (n < p.n_valid) {
-                if (p.bias) x += __ldg(p.bias + n);
-                if (p.relu) x = fmaxf(x, 0.f);
-              } else {
-                x = 0.f;
+          // 64-column slabs: TMEM -> registers -> bias / ReLU / mask -> swizzled shared memory -> TMA store.
+          // Each warp owns a 4 KB slab buffer and issues its own stores, so no cross-warp sync is needed.
+          for (int c = col_half * 64; c < p.bn && col0 + c < p.n_store; c += 128) {
+            uint8_t* buf = stg;
+            if (lane == 0) tma_store_wait_read<0>();   // the store that last used this buffer has read it
+            __syncwarp();
+            const int gcol = col0 + c;
+            uint4 mreg[8];
+            if (p.mask_src) {
+              // the mask slab arrives through TMA into the slab buffer (same box and swizzle as the output),
+              // is copied to registers, and the buffer is then reused for the output
+              if (lane == 0) {
+                mbar_expect_tx(mbar_m, 4096u);
+                tma_load_2d(buf, &p.tm_mask, mbar_m, gcol, row0);
               }
-              f[j] = x;
-            }
-            if (mrow) {
-              const uint4 mv = *reinterpret_cast<const uint4*>(mrow + q * 8);
-              const __nv_bfloat162* m2 = reinterpret_cast<const __nv_bfloat162*>(&mv);
+              if (!mbar_wait_bounded(mbar_m, mask_ph, WAIT_LIMIT_NS)) {
+                ctl->abort_flag = 1;
+                if (p.status) atomicOr(p.status, RB_STATUS_MBAR_TIMEOUT);
+              }
+              mask_ph ^= 1u;
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const float2 mf = __bfloat1622float2(m2[j]);
-                if (!(mf.x > 0.f)) f[2 * j] = 0.f;
-                if (!(mf.y > 0.f)) f[2 * j + 1] = 0.f;
+              for (int ch = 0; ch < 8; ++ch)
+                mreg[ch] = *reinterpret_cast<const uint4*>(buf + lane * 128 + ((ch ^ (lane & 7)) * 16));
+              __syncwarp();
+            }
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+              uint32_t v[32];
+              tmem_ld_32x32(t_addr + (uint32_t)(c + half * 32), v);
+              tmem_ld_wait();
+              const int nbase = gcol + half * 32;
+              const bool fast = nbase + 32 <= p.n_valid;   // no padded column in this 32-column group
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                float f[8];
+                if (fast) {
+                  // one warp per scheduler runs this, so instruction count matters: vector bias loads, no
+                  // per-element tests (ReLU is a max against 0 or -inf)
+                  float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+                  if (has_bias) {
+                    b0 = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q * 8));
+                    b1 = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q * 8 + 4));
+                  }
+                  f[0] = fmaxf(__uint_as_float(v[q * 8 + 0]) + b0.x, act_lo);
+                  f[1] = fmaxf(__uint_as_float(v[q * 8 + 1]) + b0.y, act_lo);
+                  f[2] = fmaxf(__uint_as_float(v[q * 8 + 2]) + b0.z, act_lo);
+                  f[3] = fmaxf(__uint_as_float(v[q * 8 + 3]) + b0.w, act_lo);
+                  f[4] = fmaxf(__uint_as_float(v[q * 8 + 4]) + b1.x, act_lo);
+                  f[5] = fmaxf(__uint_as_float(v[q * 8 + 5]) + b1.y, act_lo);
+                  f[6] = fmaxf(__uint_as_float(v[q * 8 + 6]) + b1.z, act_lo);
+                  f[7] = fmaxf(__uint_as_float(v[q * 8 + 7]) + b1.w, act_lo);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < 8; ++e) {
+                    const int n = nbase + q * 8 + e;
+                    float x = 0.f;
+                    if (n < p.n_valid) x = fmaxf(__uint_as_float(v[q * 8 + e]) + (has_bias ? __ldg(p.bias + n) : 0.f), act_lo);
+                    f[e] = x;
+                  }
+                }
+                if (p.mask_src) {
+                  const uint4 mv = mreg[half * 4 + q];
+                  const __nv_bfloat162* m2 = reinterpret_cast<const __nv_bfloat162*>(&mv);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 mf = __bfloat1622float2(m2[e]);
+                    if (!(mf.x > 0.f)) f[2 * e] = 0.f;
+                    if (!(mf.y > 0.f)) f[2 * e + 1] = 0.f;
+                  }
+                }
+                uint4 o;
+                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                // 128-byte swizzle: 16-byte chunk index XOR (row mod 8), the layout the store's tensor map expects
+                const int chunk = (half * 4 + q) ^ (lane & 7);
+                *reinterpret_cast<uint4*>(buf + lane * 128 + chunk * 16) = o;
               }
             }
-            uint4 o;
-            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
-            *reinterpret_cast<uint4*>(drow + q * 8) = o;
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && row0 < p.M) {
+              tma_store_2d(&p.tm_d, buf, gcol, row0);
+              tma_store_commit();
+            }
           }
-        } else {
+          continue;
+        }
+        for (int c = col_half * 32; c < p.bn; c += 64) {
+          uint32_t v[32];
+          tmem_ld_32x32(t_addr + (uint32_t)c, v);
+          tmem_ld_wait();
+          if (!row_ok || c >= col_limit || (p.dbg & 1)) continue;
+          int gcol = col0 + c;
+          if (p.b_mode == B_IM2COL_MN && p.wg_taps > 1) {
+            const int t = c / p.wg_cw, cc = c - t * p.wg_cw;
+            const int tap = tn * p.wg_taps + t;
+            if (tap >= p.wg_ntaps || cc >= p.wg_cpad) continue;
+            gcol = tap * p.wg_cpad + cc;
+          }
           float* drow = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + gcol;
           if (p.epi == EPI_F32_STORE) {
 #pragma unroll
@@ -313,8 +443,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&ctl->acc_empty[acc]);
-      if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+      if (++acc == p.acc_bufs) { acc = 0; acc_ph ^= 1u; }
     }
+    if (lane == 0) tma_store_wait_all<0>();   // every output store has completed before the CTA exits
   }
 
   tc_fence_before();
@@ -406,42 +537,113 @@ static int make_map_im2col(CUtensorMap* m, const void* ptr, int N, int H, int W,
   return 0;
 }
 
-static int pick_stages(int bn, int bk) {
-  const int stage = (BM + bn) * bk * 2;
-  int s = TILE_SMEM_BYTES / stage;
-  if (s > MAX_STAGES) s = MAX_STAGES;
-  return s;
+// Output map of the bf16 epilogue: columns [0, n_store) x rows [0, M), 64 x 32 boxes, 128-byte swizzle.
+static int make_map_out(CUtensorMap* m, void* D, int n_store, int M, long long ldd) {
+  return make_map_2d(m, D, (uint64_t)n_store, (uint64_t)M, (uint64_t)ldd, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-static int launch(GemmTcParams& p, cudaStream_t stream, int max_ctas) {
-  const int m_tiles = (p.M + BM - 1) / BM;
-  const int work = m_tiles * p.n_tiles * p.split_k;
-  if (work <= 0) return 0;
-  p.stages = pick_stages(p.bn, p.bk);
+// ---- tile-shape planning -----------------------------------------------------------------------------------
+// Cost model in "rows": the kernel is bound by the 128-byte rows it fills into shared memory per k-block
+// (see the header comment), so an item costs about k-blocks x (rows of A + rows of B) plus its epilogue, and a
+// launch costs rounds x item (persistent CTAs, one per SM). The planner picks sub-tiles per item (mt),
+// the reduction split and B residency to minimise that.
+struct Plan {
+  int mt, split, resident;
+  double cost;
+};
+
+static bool split_ok(int s, int num_kb) { return s == 1 || (s - 1) * ((num_kb + s - 1) / s) < num_kb; }
+
+static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights) {
+  const int a_bytes = BM * p.bk * 2, b_bytes = p.bn_load * p.bk * 2;
+  const double epi_elem = (p.epi == EPI_BF16) ? 1.2 : 1.6;
+  Plan best{1, 1, 0, 1e300};
+  // test hooks: RB_GEMM_FORCE_MT=1|2 and RB_GEMM_FORCE_RESIDENT=0|1 restrict the search (ignored when infeasible)
+  const char* e_mt = getenv("RB_GEMM_FORCE_MT");
+  const char* e_res = getenv("RB_GEMM_FORCE_RESIDENT");
+  const int force_mt = e_mt ? atoi(e_mt) : 0, force_res = e_res ? atoi(e_res) : -1;
+  for (int pass = 0; pass < 2 && best.cost >= 1e299; ++pass)
+  for (int mt = 1; mt <= 2; ++mt) {
+    if (pass == 0 && force_mt && mt != force_mt) continue;
+    if (mt == 2 && p.M <= BM) continue;
+    const int acc_stride = p.bn > 128 ? 256 : 128;
+    const int acc_bufs = (2 * mt * acc_stride <= 512) ? 2 : 1;
+    const int m_items = (p.M + BM * mt - 1) / (BM * mt);
+    const long long tiles = (long long)m_items * p.n_tiles;
+    const int max_split = allow_split ? (p.num_kb / 8 > 64 ? 64 : (p.num_kb / 8 < 1 ? 1 : p.num_kb / 8)) : 1;
+    for (int s = (fixed_split > 0 ? fixed_split : 1); s <= (fixed_split > 0 ? fixed_split : max_split); ++s) {
+      if (!split_ok(s, p.num_kb)) continue;
+      for (int res = 0; res <= 1; ++res) {
+        if (pass == 0 && force_res >= 0 && res != force_res) continue;
+        const long long panel = (long long)p.num_kb * b_bytes;
+        if (res) {
+          if (!b_is_weights || p.n_tiles != 1 || s != 1 || panel > 112 * 1024) continue;
+          if ((TILE_SMEM_BYTES - panel) / (mt * a_bytes) < 3) continue;
+        } else if (TILE_SMEM_BYTES / (mt * a_bytes + b_bytes) < 2) {
+          continue;
+        }
+        const int kbs = (p.num_kb + s - 1) / s;
+        const double rows_kb = mt * BM + (res ? 0 : p.bn_load);
+        const double mainloop = kbs * rows_kb * (p.bk / 64.0);
+        const double epi = mt * p.bn * epi_elem;
+        const double item = acc_bufs == 2 ? (mainloop > epi ? mainloop : epi) + 0.15 * epi : mainloop + epi;
+        const long long rounds = (tiles * s + g_num_sms - 1) / g_num_sms;
+        const double cost = rounds * item + (res ? (double)p.num_kb * p.bn_load * (p.bk / 64.0) : 0.0);
+        if (cost < best.cost * 0.97) best = Plan{mt, s, res, cost};
+      }
+    }
+  }
+  return best;
+}
+
+static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights, cudaStream_t stream) {
+  if (p.M <= 0 || p.n_tiles <= 0 || p.num_kb <= 0) return 0;
+  const Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
+  if (pl.cost >= 1e299) return -3;
+  p.mt = pl.mt;
+  p.split_k = pl.split;
+  p.b_resident = pl.resident;
+  p.acc_stride = p.bn > 128 ? 256 : 128;
+  p.acc_bufs = (2 * p.mt * p.acc_stride <= 512) ? 2 : 1;
+  { const char* e = getenv("RB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
+  const int a_bytes = BM * p.bk * 2, b_bytes = p.bn_load * p.bk * 2;
+  const int panel = p.b_resident ? p.num_kb * b_bytes : 0;
+  const int stage = p.mt * a_bytes + (p.b_resident ? 0 : b_bytes);
+  p.stages = (TILE_SMEM_BYTES - panel) / stage;
+  if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
   if (p.stages < 2) return -3;
-  int grid = work < g_num_sms ? work : g_num_sms;
-  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+  const int m_items = (p.M + BM * p.mt - 1) / (BM * p.mt);
+  const long long work = (long long)m_items * p.n_tiles * p.split_k;
+  const int grid = work < g_num_sms ? (int)work : g_num_sms;
   gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
-}
-
-// choose a reduction split so that about one wave of CTAs is busy
-static int pick_split(int tiles, int num_kb, int min_kb_per_split) {
-  if (tiles >= g_num_sms) return 1;
-  int s = g_num_sms / tiles;
-  int max_s = num_kb / min_kb_per_split;
-  if (max_s < 1) max_s = 1;
-  if (s > max_s) s = max_s;
-  if (s < 1) s = 1;
-  // every split must own at least one k-block
-  while (s > 1 && (s - 1) * ((num_kb + s - 1) / s) >= num_kb) --s;
-  return s;
 }
 
 static int round_bn(int n, int cap) {
   int bn = ((n + 31) / 32) * 32;
   if (bn > cap) bn = cap;
   return bn;
+}
+
+// Tile width for `n` output columns: among 1..4 column tiles (width a multiple of `gran`, at most 256), the one
+// whose plan is cheapest. `setup(p, bn)` must fill the fields that depend on the width.
+template <class Setup>
+static int pick_bn(GemmTcParams& p, int n, int gran, bool allow_split, int fixed_split, bool b_is_weights,
+                   Setup setup) {
+  int best_bn = 0;
+  double best_cost = 1e300;
+  for (int nt = 1; nt <= 4; ++nt) {
+    int bn = (n + nt - 1) / nt;
+    const int g = (nt > 1 && gran < 64) ? 64 : gran;   // the bf16 epilogue stores 64-column slabs
+    bn = (bn + g - 1) / g * g;
+    if (bn > 256 || bn == best_bn) continue;
+    setup(p, bn);
+    const Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
+    if (pl.cost < best_cost * 0.97) { best_cost = pl.cost; best_bn = bn; }
+  }
+  if (best_bn == 0) best_bn = 256;
+  setup(p, best_bn);
+  return best_bn;
 }
 
 }  // namespace rb
@@ -467,7 +669,8 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
   p.bk = (!any_mn && (K % 64 != 0) && (K % 32 == 0)) ? 32 : 64;
   if (bn_cap <= 0) bn_cap = 256;
   p.bn = round_bn(N, bn_cap);
-  if (b_mn) p.bn = ((p.bn + 63) / 64) * 64;
+  if (b_mn || (epi == EPI_BF16 && N > p.bn)) p.bn = ((p.bn + 63) / 64) * 64;
+  p.bn_load = p.bn;
   p.M = M;
   p.N = N;
   p.num_kb = (K + p.bk - 1) / p.bk;
@@ -489,12 +692,6 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
     rc = make_map_2d(&p.tm_b, B, K, N, ldb, p.bk, p.bn, ksw);
   }
   if (rc) return rc;
-  const int tiles = ((M + BM - 1) / BM) * p.n_tiles;
-  if (epi != EPI_F32_ATOMIC) split_k = 1;
-  else if (split_k <= 0) split_k = pick_split(tiles, p.num_kb, 4);
-  if (split_k > p.num_kb) split_k = p.num_kb;
-  while (split_k > 1 && (split_k - 1) * ((p.num_kb + split_k - 1) / split_k) >= p.num_kb) --split_k;
-  p.split_k = split_k;
   p.epi = epi;
   p.relu = relu;
   p.n_valid = n_valid > 0 ? n_valid : N;
@@ -504,7 +701,16 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
   p.bias = bias;
   p.mask_src = reinterpret_cast<const __nv_bfloat16*>(mask_src);
   p.status = status;
-  return launch(p, stream, 0);
+  if (epi == EPI_BF16) {
+    rc = make_map_out(&p.tm_d, D, p.n_store, M, ldd);
+    if (rc) return rc;
+    if (mask_src) rc = make_map_out(&p.tm_mask, const_cast<void*>(mask_src), p.n_store, M, ldd);
+    if (rc) return rc;
+  }
+  if (epi != EPI_F32_ATOMIC) split_k = 1;
+  if (split_k > p.num_kb) split_k = p.num_kb;
+  while (split_k > 1 && !split_ok(split_k, p.num_kb)) --split_k;
+  return launch(p, epi == EPI_F32_ATOMIC && split_k <= 0, split_k > 0 ? split_k : 0, !b_mn, stream);
 }
 
 // Convolution forward (also used for stride-1 data-grad with flipped filters).
@@ -521,12 +727,16 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   if (Cp % 32 != 0) return -10;
   if ((n_store > 0 ? n_store : Kout) % 32 != 0 || ldy % 8 != 0) return -11;
   const CUtensorMapSwizzle ksw = p.bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
-  p.bn = round_bn(n_store > 0 ? n_store : Kout, 256);
+  const int n_cols = n_store > 0 ? n_store : Kout;
   p.M = N * P * Q;
   p.N = Kout;
   p.cv_cchunks = Cp / p.bk;
   p.num_kb = R * S * p.cv_cchunks;
-  p.n_tiles = ((n_store > 0 ? n_store : Kout) + p.bn - 1) / p.bn;
+  p.epi = EPI_BF16;
+  pick_bn(p, n_cols, 32, false, 1, true, [n_cols](GemmTcParams& q, int bn) {
+    q.bn = q.bn_load = bn;
+    q.n_tiles = (n_cols + bn - 1) / bn;
+  });
   p.a_mode = A_IM2COL_K;
   p.b_mode = B_TILED_K3;
   p.cv_P = P;
@@ -542,7 +752,6 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   if (rc) return rc;
   rc = make_map_3d(&p.tm_b, w, Cp, (uint64_t)R * S, Kout, Cp, (uint64_t)R * S * Cp, p.bk, 1, p.bn, ksw);
   if (rc) return rc;
-  p.split_k = 1;
   p.epi = EPI_BF16;
   p.relu = relu;
   p.n_valid = n_valid > 0 ? n_valid : Kout;
@@ -552,12 +761,15 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   p.bias = bias;
   p.mask_src = reinterpret_cast<const __nv_bfloat16*>(mask_src);
   p.status = status;
-  return launch(p, stream, 0);
+  rc = make_map_out(&p.tm_d, y, p.n_store, p.M, ldy);
+  if (rc) return rc;
+  if (mask_src) rc = make_map_out(&p.tm_mask, const_cast<void*>(mask_src), p.n_store, p.M, ldy);
+  if (rc) return rc;
+  return launch(p, false, 1, true, stream);
 }
 
 // Convolution weight-grad:  dw[Kout][R*S][Cp] (fp32) (+)= sum over pixels dy[pix][k] * x[pix shifted by tap][c].
-//   accumulate = 0 requires dw to have been zeroed when the reduction is split (the library reports the
-//   split it would use through rb_conv_wgrad_split so that callers can zero only when needed).
+//   The result is always accumulated into dw (red.add), so dw holds zeros or the running gradient on entry.
 int rb_conv_wgrad_tc(const void* x, int N, int H, int W, int Cp, const void* dy, long long lddy, int Kout, int R,
                      int S, int stride, int pad_h, int pad_w, int P, int Q, float* dw, int split_k,
                      unsigned int* status, cudaStream_t stream) {
@@ -566,17 +778,58 @@ int rb_conv_wgrad_tc(const void* x, int N, int H, int W, int Cp, const void* dy,
   GemmTcParams p;
   memset(&p, 0, sizeof(p));
   p.bk = 64;
-  int bn = ((Cp + 63) / 64) * 64;
-  if (bn > 256) bn = 256;
-  if (Cp > 256 && Cp % 256 != 0 && Cp % 128 == 0) bn = 128;
-  p.bn = bn;
   p.M = Kout;
   p.N = R * S * Cp;
   const long long pixels = (long long)N * P * Q;
   p.num_kb = (int)((pixels + p.bk - 1) / p.bk);
-  p.wg_ctiles = (Cp + p.bn - 1) / p.bn;
   p.wg_cpad = Cp;
-  p.n_tiles = R * S * p.wg_ctiles;
+  p.epi = EPI_F32_ATOMIC;
+  if (split_k > p.num_kb) split_k = p.num_kb;
+  while (split_k > 1 && !split_ok(split_k, p.num_kb)) --split_k;
+  const int taps = R * S;
+  p.wg_ntaps = taps;
+  const bool auto_split = split_k <= 0;
+  const int fixed = split_k > 0 ? split_k : 0;
+  // candidates: (a) one tap per tile, 1..4 channel tiles; (b) several taps side by side when a tap is narrow
+  double best_cost = 1e300;
+  int best_bn = 0, best_taps = 1;
+  auto setup = [Cp, taps](GemmTcParams& q, int bn, int T) {
+    q.bn = q.bn_load = bn;
+    q.wg_taps = T;
+    if (T > 1) {
+      q.wg_cw = bn / T;
+      q.wg_ctiles = 1;
+      q.n_tiles = (taps + T - 1) / T;
+    } else {
+      q.wg_cw = bn;
+      q.wg_ctiles = (Cp + bn - 1) / bn;
+      q.n_tiles = taps * q.wg_ctiles;
+    }
+  };
+  for (int nt = 1; nt <= 4; ++nt) {
+    int bn = (Cp + nt - 1) / nt;
+    bn = (bn + 63) / 64 * 64;
+    if (bn > 256) continue;
+    setup(p, bn, 1);
+    const Plan pl = plan_shape(p, auto_split, fixed, false);
+    if (pl.cost < best_cost * 0.97) { best_cost = pl.cost; best_bn = bn; best_taps = 1; }
+  }
+  const int cw = (Cp + 63) / 64 * 64;
+  for (int T = 2; T * cw <= 256 && T <= taps; ++T) {
+    setup(p, T * cw, T);
+    const Plan pl = plan_shape(p, auto_split, fixed, false);
+    // a tile with idle tap slots still pays for them: scale by the slots actually computed
+    const double waste = (double)(p.n_tiles * T) / taps;
+    if (pl.cost * waste < best_cost * 0.97) { best_cost = pl.cost * waste; best_bn = T * cw; best_taps = T; }
+  }
+  {  // test hook: RB_GEMM_FORCE_TAPS=T takes the T-taps-per-tile candidate when it is feasible
+    const char* e = getenv("RB_GEMM_FORCE_TAPS");
+    const int T = e ? atoi(e) : 0;
+    if (T == 1 && best_taps != 1) { best_taps = 1; best_bn = cw > 256 ? 256 : cw; }
+    if (T > 1 && T * cw <= 256 && T <= taps) { best_taps = T; best_bn = T * cw; }
+  }
+  if (best_bn == 0) return -3;
+  setup(p, best_bn, best_taps);
   p.a_mode = A_TILED_MN;
   p.b_mode = B_IM2COL_MN;
   p.cv_P = P;
@@ -592,18 +845,15 @@ int rb_conv_wgrad_tc(const void* x, int N, int H, int W, int Cp, const void* dy,
   rc = make_map_im2col(&p.tm_b, x, N, H, W, Cp, -pad_h, -pad_w, upper_h, upper_w, stride, 64, p.bk,
                        CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc) return rc;
-  const int tiles = ((Kout + BM - 1) / BM) * p.n_tiles;
-  if (split_k <= 0) split_k = pick_split(tiles, p.num_kb, 8);
-  if (split_k > p.num_kb) split_k = p.num_kb;
-  while (split_k > 1 && (split_k - 1) * ((p.num_kb + split_k - 1) / split_k) >= p.num_kb) --split_k;
-  p.split_k = split_k;
   p.epi = EPI_F32_ATOMIC;
   p.n_valid = p.N;
   p.n_store = p.N;
   p.ldd = (long long)R * S * Cp;
   p.D = dw;
   p.status = status;
-  return launch(p, stream, 0);
+  if (split_k > p.num_kb) split_k = p.num_kb;
+  while (split_k > 1 && !split_ok(split_k, p.num_kb)) --split_k;
+  return launch(p, split_k <= 0, split_k > 0 ? split_k : 0, false, stream);
 }
 
 int rb_num_sms() {

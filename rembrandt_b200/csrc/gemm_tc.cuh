@@ -23,19 +23,29 @@ enum : int { EPI_BF16 = 0, EPI_F32_STORE = 1, EPI_F32_ATOMIC = 2 };
 struct alignas(64) GemmTcParams {
   CUtensorMap tm_a;
   CUtensorMap tm_b;
+  CUtensorMap tm_mask; // EPI_BF16 with mask_src: same geometry as tm_d over the mask tensor (epilogue TMA loads)
+  CUtensorMap tm_d;    // EPI_BF16: output map for the TMA stores of the epilogue (box 64 columns x 32 rows)
   int a_mode, b_mode;
   int M, N;            // extent of D in rows / columns (tiles are clipped against these)
   int bn;              // tile width  (multiple of 32, <= 256)
+  int bn_load;         // rows of B brought in per k-block (= bn; kept separate from the MMA width)
   int bk;              // k-block depth (64 or 32)
   int num_kb;          // k-blocks over the whole reduction
   int split_k;         // reduction split; > 1 requires EPI_F32_ATOMIC
   int stages;
+  int mt;              // 128-row sub-tiles per work item (1 or 2): they share one B stage
+  int b_resident;      // 1: the whole B panel (all k-blocks) is loaded once per CTA and stays in shared memory
+  int acc_stride;      // TMEM columns between the accumulators of the sub-tiles (128 or 256)
+  int acc_bufs;        // accumulator sets in TMEM (2 = epilogue overlaps the next main loop, 1 = no overlap)
   // convolution geometry (im2col operands)
   int cv_P, cv_Q;      // output height / width per image
   int cv_stride;       // traversal stride
   int cv_lower_h, cv_lower_w;  // lower corner of the base pixel (= -pad)
   int cv_S;            // filter width (taps are enumerated r*S+s)
   int cv_cchunks;      // channel chunks of bk per tap (A_IM2COL_K / B_TILED_K3)
+  int wg_taps;         // filter taps per column tile (B_IM2COL_MN; > 1 only when one tap's channels fit 128 columns)
+  int wg_cw;           // columns reserved per tap inside a tile (multiple of 64)
+  int wg_ntaps;        // R*S
   int wg_ctiles;       // channel tiles of bn per tap (B_IM2COL_MN)
   int wg_cpad;         // padded input channels: column of D = tap*wg_cpad + channel
   int n_tiles;         // tiles along N (taps*wg_ctiles for wgrad)
@@ -49,6 +59,7 @@ struct alignas(64) GemmTcParams {
   const float* bias;               // optional, indexed by column
   const __nv_bfloat16* mask_src;   // optional, same layout as D: D is zeroed where mask_src <= 0
   unsigned int* status;            // error bits (see ptx.cuh)
+  int dbg;                         // timing experiments only: 1 = epilogue skips its global stores
 };
 
 }  // namespace rb

@@ -102,6 +102,68 @@ __global__ void input_kernel(InputArgs a) {
   }
 }
 
+// Row-staged variant: one block per (sample, output row). The f source rows of every channel are read with
+// coalesced byte loads, converted (scale, mean, lighting shift, crop / flip / zero padding) into shared memory
+// as floats, then written out as 16-byte channel groups. The per-sample random draw is computed once per block.
+__global__ void __launch_bounds__(256) input_rows_kernel(InputArgs a) {
+  extern __shared__ float srow[];  // [f][C][seg_w]
+  __shared__ int s_draw[3];
+  __shared__ float s_shift[3];
+  const int n = blockIdx.x / a.OH, Y = blockIdx.x % a.OH;
+  if (threadIdx.x == 0) {
+    int oy, ox, flip;
+    float shift[3];
+    sample_draw(a, n, oy, ox, flip, shift);
+    s_draw[0] = oy; s_draw[1] = ox; s_draw[2] = flip;
+    s_shift[0] = shift[0]; s_shift[1] = shift[1]; s_shift[2] = shift[2];
+  }
+  __syncthreads();
+  const int oy = s_draw[0], ox = s_draw[1], flip = s_draw[2];
+  const int seg_w = a.OW * a.f;
+  const int per_row = a.C * seg_w;
+  const int total_in = a.f * per_row;
+  const uint8_t* img = a.src + (long long)n * a.C * a.H * a.W;
+  for (int i = threadIdx.x; i < total_in; i += blockDim.x) {
+    const int dy = i / per_row;
+    const int r = i - dy * per_row;
+    const int c = r / seg_w;
+    const int xc = r - c * seg_w;
+    const int y = Y * a.f + dy;
+    float v = 0.f;
+    if (y < a.crop_h && xc < a.crop_w) {
+      const int cx = flip ? a.crop_w - 1 - xc : xc;
+      const int sy = oy + y, sx = ox + cx;
+      if (sy >= 0 && sy < a.H && sx >= 0 && sx < a.W) {
+        const long long si = ((long long)c * a.H + sy) * a.W + sx;
+        v = (float)img[si] * a.scale;
+        if (a.mean) v -= a.mean_scale * a.mean[si];
+        if (c < 3) v += s_shift[c];
+      }
+    }
+    srow[i] = v;
+  }
+  __syncthreads();
+  const int groups = a.Cp / 8;
+  const int ff = a.f * a.f;
+  bf16* drow = a.dst + ((long long)n * a.OH + Y) * a.OW * a.Cp;
+  for (int i = threadIdx.x; i < a.OW * groups; i += blockDim.x) {
+    const int X = i / groups, g = i - X * groups;
+    float out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int ch = g * 8 + j;
+      const int blk = ch / a.C, c = ch - blk * a.C;
+      float v = 0.f;
+      if (blk < ff) {
+        const int dy = blk / a.f, dx = blk - dy * a.f;
+        v = srow[(dy * a.C + c) * seg_w + X * a.f + dx];
+      }
+      out[j] = v;
+    }
+    store8(drow + (long long)i * 8, out);
+  }
+}
+
 // Synthetic N(0,1) activations (bf16, padded channels zero) and uniform labels, generated on the device.
 __global__ void synth_normal_kernel(bf16* __restrict__ dst, long long pixels, int C, int Cp, uint64_t seed,
                                     uint32_t step) {
@@ -158,7 +220,12 @@ int rb_input_u8(const void* src, const float* mean, void* dst, int N, int C, int
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
-  input_kernel<<<(int)blocks, 256, 0, st>>>(a);
+  const size_t row_smem = (size_t)f * C * OW * f * sizeof(float);
+  if (row_smem <= 40 * 1024 && (long long)N * OH < 0x7FFFFFFF) {
+    input_rows_kernel<<<N * OH, 256, row_smem, st>>>(a);
+  } else {
+    input_kernel<<<(int)blocks, 256, 0, st>>>(a);
+  }
   return RB_LAUNCH_OK();
 }
 

@@ -8,14 +8,14 @@
 
 namespace rb {
 
+template <typename IT>
 __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ idx, int N,
                                    int H, int W, int C, int P, int Q, int k, int stride, int pad, int relu) {
   const int cv = C / 8;
-  const long long total = (long long)N * P * Q * cv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
+  const IT total = (IT)N * P * Q * cv;
+  for (IT i = (IT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IT)gridDim.x * blockDim.x) {
     const int c8 = (int)(i % cv);
-    long long t = i / cv;
+    IT t = i / cv;
     const int q = (int)(t % Q); t /= Q;
     const int p = (int)(t % P);
     const int n = (int)(t / P);
@@ -51,15 +51,15 @@ __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict_
 }
 
 // dx[n,h,w,c] = sum over windows covering (h,w) whose recorded argmax is (h,w) of dy.
+template <typename IT>
 __global__ void maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ idx, bf16* __restrict__ dx,
                                    const bf16* __restrict__ mask_src, int N, int H, int W, int C, int P, int Q,
                                    int k, int stride, int pad) {
   const int cv = C / 8;
-  const long long total = (long long)N * H * W * cv;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
+  const IT total = (IT)N * H * W * cv;
+  for (IT i = (IT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IT)gridDim.x * blockDim.x) {
     const int c8 = (int)(i % cv);
-    long long t = i / cv;
+    IT t = i / cv;
     const int w = (int)(t % W); t /= W;
     const int h = (int)(t % H);
     const int n = (int)(t / H);
@@ -99,15 +99,15 @@ __global__ void maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* _
   }
 }
 
+template <typename IT>
 __global__ void avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int N, int H, int W, int C, int P,
                                    int Q, int k, int stride, int pad, int relu) {
   const int cv = C / 8;
-  const long long total = (long long)N * P * Q * cv;
+  const IT total = (IT)N * P * Q * cv;
   const float inv = 1.f / (float)(k * k);
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
+  for (IT i = (IT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IT)gridDim.x * blockDim.x) {
     const int c8 = (int)(i % cv);
-    long long t = i / cv;
+    IT t = i / cv;
     const int q = (int)(t % Q); t /= Q;
     const int p = (int)(t % P);
     const int n = (int)(t / P);
@@ -137,16 +137,16 @@ __global__ void avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict_
 }
 
 // y_relu: optional forward output; when given, dy is masked by (y > 0) first (pool with fused ReLU).
+template <typename IT>
 __global__ void avgpool_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y_relu,
                                    bf16* __restrict__ dx, const bf16* __restrict__ mask_src, int N, int H, int W,
                                    int C, int P, int Q, int k, int stride, int pad) {
   const int cv = C / 8;
-  const long long total = (long long)N * H * W * cv;
+  const IT total = (IT)N * H * W * cv;
   const float inv = 1.f / (float)(k * k);
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
-       i += (long long)gridDim.x * blockDim.x) {
+  for (IT i = (IT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IT)gridDim.x * blockDim.x) {
     const int c8 = (int)(i % cv);
-    long long t = i / cv;
+    IT t = i / cv;
     const int w = (int)(t % W); t /= W;
     const int h = (int)(t % H);
     const int n = (int)(t / H);
@@ -201,12 +201,16 @@ int rb_pool_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, i
                 int pad, int is_max, int relu, cudaStream_t st) {
   if (C % 8) return -10;
   const long long total = (long long)N * P * Q * (C / 8);
-  if (is_max)
-    maxpool_fwd_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, P, Q,
-                                                            k, stride, pad, relu);
-  else
-    avgpool_fwd_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, N, H, W, C, P, Q, k, stride,
-                                                            pad, relu);
+  const bool small = (long long)N * (H > P ? H : P) * (W > Q ? W : Q) * C < 0x7FFFFFFFll;  // 32-bit index math
+#define RB_POOL_FWD(IT)                                                                                              \
+  if (is_max)                                                                                                        \
+    maxpool_fwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, \
+                                                                P, Q, k, stride, pad, relu);                         \
+  else                                                                                                               \
+    avgpool_fwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, N, H, W, C, P, Q, k,       \
+                                                                stride, pad, relu);
+  if (small) { RB_POOL_FWD(unsigned int) } else { RB_POOL_FWD(long long) }
+#undef RB_POOL_FWD
   return RB_LAUNCH_OK();
 }
 
@@ -214,12 +218,18 @@ int rb_pool_bwd(const void* dy, const void* idx, const void* y_relu, void* dx, c
                 int W, int C, int P, int Q, int k, int stride, int pad, int is_max, cudaStream_t st) {
   if (C % 8) return -10;
   const long long total = (long long)N * H * W * (C / 8);
-  if (is_max)
-    maxpool_bwd_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const uint8_t*)idx, (bf16*)dx,
-                                                            (const bf16*)mask_src, N, H, W, C, P, Q, k, stride, pad);
-  else
-    avgpool_bwd_kernel<<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const bf16*)y_relu, (bf16*)dx,
-                                                            (const bf16*)mask_src, N, H, W, C, P, Q, k, stride, pad);
+  const bool small = (long long)N * (H > P ? H : P) * (W > Q ? W : Q) * C < 0x7FFFFFFFll;
+#define RB_POOL_BWD(IT)                                                                                               \
+  if (is_max)                                                                                                         \
+    maxpool_bwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const uint8_t*)idx, (bf16*)dx,      \
+                                                                (const bf16*)mask_src, N, H, W, C, P, Q, k, stride,   \
+                                                                pad);                                                 \
+  else                                                                                                                \
+    avgpool_bwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const bf16*)y_relu, (bf16*)dx,      \
+                                                                (const bf16*)mask_src, N, H, W, C, P, Q, k, stride,   \
+                                                                pad);
+  if (small) { RB_POOL_BWD(unsigned int) } else { RB_POOL_BWD(long long) }
+#undef RB_POOL_BWD
   return RB_LAUNCH_OK();
 }
 

@@ -36,7 +36,7 @@ def status_ok():
 
 # ----------------------------------------------------------------------------- GEMM
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 512), (200, 96, 96), (77, 32, 64), (384, 512, 1024), (128, 1024, 160)])
-def test_gemm_kmajor_bf16_epilogue(M, N, K_):
+def test_gemm_kmajor_bf16_epilogue(M, N, K_, tile_mode):
     torch.manual_seed(0)
     a = bf(torch.randn(M, K_, device=DEV))
     b = bf(torch.randn(N, K_, device=DEV))
@@ -76,7 +76,7 @@ def test_gemm_b_mn_major(M, N, K_):
 
 
 @pytest.mark.parametrize("M,N,K_,split", [(256, 384, 128, 1), (96, 200, 1000, 0), (4096, 1024, 128, 1)])
-def test_gemm_both_mn_major_atomic(M, N, K_, split):
+def test_gemm_both_mn_major_atomic(M, N, K_, split, tile_mode):
     """dW[M][N] += dY^T X with dY [K][M], X [K][N]: the affine weight-gradient form (fp32 accumulate)."""
     torch.manual_seed(3)
     Np = (N + 31) // 32 * 32
@@ -128,8 +128,20 @@ def _conv_setup(N, C, H, W, Ko, R, stride, pad, seed=0):
     return Cp, Kp, x, w, b, P, Q
 
 
+@pytest.fixture(params=["auto", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3"])
+def tile_mode(request, monkeypatch):
+    """Force the kernel's tile-shape planner through each of its modes (two sub-tiles per item, resident B)."""
+    mode = request.param
+    if mode != "auto":
+        monkeypatch.setenv("RB_GEMM_FORCE_MT", "2" if "mt2" in mode else "1")
+        monkeypatch.setenv("RB_GEMM_FORCE_RESIDENT", "1" if "resident" in mode else "0")
+        if "taps" in mode:
+            monkeypatch.setenv("RB_GEMM_FORCE_TAPS", mode[-1])
+    return mode
+
+
 @pytest.mark.parametrize("case", CONV_CASES)
-def test_conv_fprop_tc(case):
+def test_conv_fprop_tc(case, tile_mode):
     N, C, H, W, Ko, R, stride, pad = case
     Cp, Kp, x, w, b, P, Q = _conv_setup(*case)
     xi = layout.to_nhwc_padded(x, Cp)
@@ -148,7 +160,7 @@ def test_conv_fprop_tc(case):
 
 
 @pytest.mark.parametrize("case", [c for c in CONV_CASES if c[6] == 1])
-def test_conv_dgrad_tc(case):
+def test_conv_dgrad_tc(case, tile_mode):
     N, C, H, W, Ko, R, stride, pad = case
     Cp, Kp, x, w, b, P, Q = _conv_setup(*case, seed=5)
     dy = bf(torch.randn(N, Ko, P, Q, device=DEV))
@@ -183,7 +195,7 @@ def test_conv_direct_dgrad_strided():
 
 
 @pytest.mark.parametrize("case", CONV_CASES)
-def test_conv_wgrad_tc(case):
+def test_conv_wgrad_tc(case, tile_mode):
     N, C, H, W, Ko, R, stride, pad = case
     Cp, Kp, x, w, b, P, Q = _conv_setup(*case, seed=7)
     dy = bf(torch.randn(N, Ko, P, Q, device=DEV))
