@@ -203,6 +203,8 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    last_result = [None]
+
     def timed(fn, steps):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -210,7 +212,7 @@ def main():
             e0.record(stream)
         for i in range(steps):
             fn(i)
-        finish()
+        last_result[0] = finish()
         with torch.cuda.stream(stream):
             e1.record(stream)
         barrier()
@@ -241,6 +243,7 @@ def main():
         from rembrandt_b200.ops import native_ops as K
         l0 = K.LAUNCHES[0]
     ms_dev = timed(resident_step, args.steps)
+    last_loss = last_result[0]
     if args.impl == "ours":
         engine.hold_input = False
         launches = engine.launches_per_step * args.steps
@@ -268,6 +271,7 @@ def main():
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "note": "pinned uint8 batch + int32 labels copied every step; loss read back with a one-step lag"},
             "gpu_launches": launches,
+            "final_loss": last_loss[0] if isinstance(last_loss, tuple) else last_loss,
             "clocks": clocks,
         }
         print(json.dumps(out))

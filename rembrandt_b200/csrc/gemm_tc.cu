@@ -136,7 +136,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     mbar_fence_init();
     tma_prefetch_desc(&p.tm_a);
     tma_prefetch_desc(&p.tm_b);
-    if (p.epi == EPI_BF16) tma_prefetch_desc(&p.tm_d);
+    tma_prefetch_desc(&p.tm_d);
     if (p.epi == EPI_BF16 && p.mask_src) tma_prefetch_desc(&p.tm_mask);
   }
   if (warp == 1) {
@@ -316,8 +316,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       }
       for (int j = 0; j < mt; ++j) {
         const int row0 = tm * BM * mt + j * BM + lane_base;   // first row of this warp's 32-row band
-        const int row = row0 + lane;
-        const bool row_ok = row < p.M;
         const uint32_t t_addr =
             tmem_base + (uint32_t)acc * set_cols + (uint32_t)(j * p.acc_stride) + ((uint32_t)lane_base << 16);
         if (p.epi == EPI_BF16) {
@@ -413,7 +411,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           uint32_t v[32];
           tmem_ld_32x32(t_addr + (uint32_t)c, v);
           tmem_ld_wait();
-          if (!row_ok || c >= col_limit || (p.dbg & 1)) continue;
+          if (c >= col_limit || (p.dbg & 1)) continue;
           int gcol = col0 + c;
           if (p.b_mode == B_IM2COL_MN && p.wg_taps > 1) {
             const int t = c / p.wg_cw, cc = c - t * p.wg_cw;
@@ -421,22 +419,21 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
             if (tap >= p.wg_ntaps || cc >= p.wg_cpad) continue;
             gcol = tap * p.wg_cpad + cc;
           }
-          float* drow = reinterpret_cast<float*>(p.D) + (size_t)row * p.ldd + gcol;
-          if (p.epi == EPI_F32_STORE) {
+          // fp32 output: 32-column chunk -> swizzled slab buffer -> one TMA store (overwrite) or TMA reduce-add
+          // (accumulate / split-K) per warp, instead of eight 16-byte red instructions per thread
+          if (lane == 0) tma_store_wait_read<0>();
+          __syncwarp();
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              float4 o = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]),
-                                     __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
-              *reinterpret_cast<float4*>(drow + 4 * q) = o;
-            }
-          } else {
-#pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(drow + 4 * q),
-                           "f"(__uint_as_float(v[4 * q])), "f"(__uint_as_float(v[4 * q + 1])),
-                           "f"(__uint_as_float(v[4 * q + 2])), "f"(__uint_as_float(v[4 * q + 3]))
-                           : "memory");
-            }
+          for (int q = 0; q < 8; ++q) {
+            const uint4 o = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            *reinterpret_cast<uint4*>(stg + lane * 128 + ((q ^ (lane & 7)) * 16)) = o;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && row0 < p.M) {
+            if (p.epi == EPI_F32_STORE) tma_store_2d(&p.tm_d, stg, gcol, row0);
+            else tma_reduce_add_2d(&p.tm_d, stg, gcol, row0);
+            tma_store_commit();
           }
         }
       }
@@ -540,6 +537,18 @@ static int make_map_im2col(CUtensorMap* m, const void* ptr, int N, int H, int W,
 // Output map of the bf16 epilogue: columns [0, n_store) x rows [0, M), 64 x 32 boxes, 128-byte swizzle.
 static int make_map_out(CUtensorMap* m, void* D, int n_store, int M, long long ldd) {
   return make_map_2d(m, D, (uint64_t)n_store, (uint64_t)M, (uint64_t)ldd, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// fp32 output map: 32-column x 32-row boxes (128-byte rows), 128-byte swizzle; used by TMA store / reduce-add.
+static int make_map_out_f32(CUtensorMap* m, void* D, long long n_cols, int M, long long ldd) {
+  cuuint64_t dims[2] = {(cuuint64_t)n_cols, (cuuint64_t)M};
+  cuuint64_t strides[1] = {(cuuint64_t)ldd * 4};
+  cuuint32_t box[2] = {32, 32};
+  cuuint32_t es[2] = {1, 1};
+  CUresult r = g_encode_tiled(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, D, dims, strides, box, es,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(300 + (int)r);
 }
 
 // ---- tile-shape planning -----------------------------------------------------------------------------------
@@ -706,6 +715,9 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
     if (rc) return rc;
     if (mask_src) rc = make_map_out(&p.tm_mask, const_cast<void*>(mask_src), p.n_store, M, ldd);
     if (rc) return rc;
+  } else {
+    rc = make_map_out_f32(&p.tm_d, D, p.n_store, M, ldd);
+    if (rc) return rc;
   }
   if (epi != EPI_F32_ATOMIC) split_k = 1;
   if (split_k > p.num_kb) split_k = p.num_kb;
@@ -850,6 +862,8 @@ int rb_conv_wgrad_tc(const void* x, int N, int H, int W, int Cp, const void* dy,
   p.n_store = p.N;
   p.ldd = (long long)R * S * Cp;
   p.D = dw;
+  rc = make_map_out_f32(&p.tm_d, dw, p.ldd, Kout, p.ldd);
+  if (rc) return rc;
   p.status = status;
   if (split_k > p.num_kb) split_k = p.num_kb;
   while (split_k > 1 && !split_ok(split_k, p.num_kb)) --split_k;

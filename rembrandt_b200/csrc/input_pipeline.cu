@@ -120,45 +120,52 @@ __global__ void __launch_bounds__(256) input_rows_kernel(InputArgs a) {
   __syncthreads();
   const int oy = s_draw[0], ox = s_draw[1], flip = s_draw[2];
   const int seg_w = a.OW * a.f;
-  const int per_row = a.C * seg_w;
-  const int total_in = a.f * per_row;
   const uint8_t* img = a.src + (long long)n * a.C * a.H * a.W;
-  for (int i = threadIdx.x; i < total_in; i += blockDim.x) {
-    const int dy = i / per_row;
-    const int r = i - dy * per_row;
-    const int c = r / seg_w;
-    const int xc = r - c * seg_w;
+  // phase 1: one (source row, channel) line at a time, threads stride along x: no per-element divisions
+  for (int line = 0; line < a.f * a.C; ++line) {
+    const int dy = line / a.C, c = line - dy * a.C;
     const int y = Y * a.f + dy;
-    float v = 0.f;
-    if (y < a.crop_h && xc < a.crop_w) {
-      const int cx = flip ? a.crop_w - 1 - xc : xc;
-      const int sy = oy + y, sx = ox + cx;
-      if (sy >= 0 && sy < a.H && sx >= 0 && sx < a.W) {
-        const long long si = ((long long)c * a.H + sy) * a.W + sx;
-        v = (float)img[si] * a.scale;
-        if (a.mean) v -= a.mean_scale * a.mean[si];
-        if (c < 3) v += s_shift[c];
+    const int sy = oy + y;
+    const bool row_in = y < a.crop_h && sy >= 0 && sy < a.H;
+    const long long rbase = ((long long)c * a.H + sy) * a.W;
+    const float sh = c < 3 ? s_shift[c] : 0.f;
+    float* dstl = srow + line * seg_w;
+    for (int xc = threadIdx.x; xc < seg_w; xc += blockDim.x) {
+      float v = 0.f;
+      if (row_in && xc < a.crop_w) {
+        const int sx = ox + (flip ? a.crop_w - 1 - xc : xc);
+        if (sx >= 0 && sx < a.W) {
+          v = (float)img[rbase + sx] * a.scale;
+          if (a.mean) v -= a.mean_scale * a.mean[rbase + sx];
+          v += sh;
+        }
       }
+      dstl[xc] = v;
     }
-    srow[i] = v;
+  }
+  // channel -> offset of its source line in shared memory (or -1 for padded channels), built once per block
+  __shared__ int s_tab[512];
+  const int ff = a.f * a.f;
+  for (int ch = threadIdx.x; ch < a.Cp && ch < 512; ch += blockDim.x) {
+    const int blk = ch / a.C, c = ch - blk * a.C;
+    int off = -1;
+    if (blk < ff) {
+      const int dy = blk / a.f, dx = blk - dy * a.f;
+      off = (dy * a.C + c) * seg_w + dx;
+    }
+    s_tab[ch] = off;
   }
   __syncthreads();
   const int groups = a.Cp / 8;
-  const int ff = a.f * a.f;
   bf16* drow = a.dst + ((long long)n * a.OH + Y) * a.OW * a.Cp;
   for (int i = threadIdx.x; i < a.OW * groups; i += blockDim.x) {
     const int X = i / groups, g = i - X * groups;
+    const int xoff = X * a.f;
     float out[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const int ch = g * 8 + j;
-      const int blk = ch / a.C, c = ch - blk * a.C;
-      float v = 0.f;
-      if (blk < ff) {
-        const int dy = blk / a.f, dx = blk - dy * a.f;
-        v = srow[(dy * a.C + c) * seg_w + X * a.f + dx];
-      }
-      out[j] = v;
+      const int off = s_tab[g * 8 + j];
+      out[j] = off >= 0 ? srow[off + xoff] : 0.f;
     }
     store8(drow + (long long)i * 8, out);
   }
@@ -221,7 +228,7 @@ int rb_input_u8(const void* src, const float* mean, void* dst, int N, int C, int
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
   const size_t row_smem = (size_t)f * C * OW * f * sizeof(float);
-  if (row_smem <= 40 * 1024 && (long long)N * OH < 0x7FFFFFFF) {
+  if (row_smem <= 40 * 1024 && Cp <= 512 && (long long)N * OH < 0x7FFFFFFF) {
     input_rows_kernel<<<N * OH, 256, row_smem, st>>>(a);
   } else {
     input_kernel<<<(int)blocks, 256, 0, st>>>(a);

@@ -56,6 +56,7 @@ class Net:
         self.training_capable = training
         self.minibatch_size = int(minibatch_size or batch_size)
         self.sample_weight = 1.0 / self.minibatch_size
+        self.accumulate = self.minibatch_size > self.batch   # gradients of several batches are summed per iteration
         self.shared_seed = tuple(seed)
         self.data_seed = (seed[0] * 0x9E3779B97F4A7C15 + 1) & (2**63 - 1)
         self.dropout_seed = (seed[1] * 0xD1B54A32D192ED03 + 7) & (2**62 - 1)

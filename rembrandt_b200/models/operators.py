@@ -439,8 +439,10 @@ class AffineOp(Op):
         n, ko = self.net.batch, self.cfg.out_channels
         K.colsum(self.dout, n, self.out_cp, ko, self.view(self.seg_b, "grads"))
         # dW[out][in] += dY^T X : both operands are read "MN-major" straight from their row-major buffers
+        # one pass over the batch: overwrite when this is the only micro-batch of the iteration, else accumulate
+        epi = K.EPI_F32_ATOMIC if self.net.accumulate else K.EPI_F32_STORE
         K.gemm_tc(self.dout, 1, self.out_cp, self.prev.out, 1, self.k_in, ko, self.k_in, n,
-                  self.view(self.seg_w, "grads"), self.k_in, epi=K.EPI_F32_ATOMIC, n_store=self.k_in, split_k=1)
+                  self.view(self.seg_w, "grads"), self.k_in, epi=epi, n_store=self.k_in, split_k=1)
         if self.wants_prev_delta():
             K.gemm_tc(self.dout, 0, self.out_cp, self.view(self.seg_w, "params16"), 1, self.k_in, n, self.k_in,
                       ko, self.ws_in, self.k_in, epi=K.EPI_F32_ATOMIC, n_store=self.k_in, split_k=0,
