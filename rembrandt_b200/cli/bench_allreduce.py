@@ -59,7 +59,7 @@ def main(argv=None):
     ap.add_argument("--sizes-mb", type=float, nargs="*", default=[1, 4, 16, 25, 64, 256])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--blocks", type=int, default=48)
+    ap.add_argument("--blocks", type=int, default=148)
     ap.add_argument("--multimem", type=int, default=-1, help="1/0 force; -1 = RB_MULTIMEM")
     args = ap.parse_args(argv)
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -127,7 +127,15 @@ __device__ __forceinline__ void end_barrier(uint32_t* const* flags, int rank, in
   }
 }
 
-__global__ void __launch_bounds__(512) allreduce_sgd_kernel(const __grid_constant__ ArSgdArgs a) {
+// Thread blocks are small (128 threads, <= 85 registers) on purpose: the kernel runs on its own stream while the
+// backward pass's GEMM CTAs (one per SM, most of the register file and all of the shared memory) are resident,
+// and only a block this size fits beside them. Each thread owns groups of 4 consecutive elements; per sweep it
+// keeps up to 8 remote 16-byte loads in flight (U groups x (world-1) peers) before it consumes any, because an
+// NVLink round trip takes microseconds and throughput is bytes in flight / latency.
+constexpr int AR_THREADS = 128;
+constexpr int AR_SLOTS = 8;
+
+__global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __grid_constant__ ArSgdArgs a) {
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
   const bool ready = start_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.status);
   if (ready) {
@@ -138,81 +146,99 @@ __global__ void __launch_bounds__(512) allreduce_sgd_kernel(const __grid_constan
       s0 = min(a.n, (long long)a.rank * per);
       s1 = min(a.n, s0 + per);
     }
-    const long long stride = (long long)gridDim.x * blockDim.x * 8;
-    for (long long i = s0 + ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < s1; i += stride) {
-      const long long e = a.off + i;
-      float4 g0, g1;
-      if (a.mc_grads) {
-        g0 = mm_ld_reduce_f4(a.mc_grads + e);
-        g1 = mm_ld_reduce_f4(a.mc_grads + e + 4);
-      } else {
-        g0 = ld_f4(a.grads[0] + e);
-        g1 = ld_f4(a.grads[0] + e + 4);
+    const int peers = a.world - 1;
+    int U = peers > 0 ? AR_SLOTS / peers : 4;
+    U = U > 4 ? 4 : (U < 1 ? 1 : U);
+    const long long gthreads = (long long)gridDim.x * blockDim.x;
+    const long long sweep = gthreads * 4 * U;
+    const long long tid4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    for (long long base = s0; base < s1; base += sweep) {
+      float4 ga[4], wa[4], va[4];
+      // own (or switch-reduced) contribution; the local master / momentum loads go out in the same wave
 #pragma unroll
-        for (int p = 1; p < MAX_RANKS; ++p) {
-          if (p < a.world) {
-            g0 = add4(g0, ld_f4(a.grads[p] + e));
-            g1 = add4(g1, ld_f4(a.grads[p] + e + 4));
+      for (int u = 0; u < 4; ++u) {
+        const long long i = base + (long long)u * gthreads * 4 + tid4;
+        if (u < U && i < s1) {
+          ga[u] = a.mc_grads ? mm_ld_reduce_f4(a.mc_grads + a.off + i) : ld_f4(a.grads[a.rank] + a.off + i);
+          if (a.op == 0) {
+            wa[u] = ld_f4(a.w + a.off + i);
+            va[u] = ld_f4(a.v + a.off + i);
           }
         }
       }
-      if (a.op == 1) {
-        // plain average, written back to every rank's buffer in place
-        const float s = a.avg_scale;
-        g0 = make_float4(g0.x * s, g0.y * s, g0.z * s, g0.w * s);
-        g1 = make_float4(g1.x * s, g1.y * s, g1.z * s, g1.w * s);
-        if (a.mc_grads) {
-          mm_st_f4(const_cast<float*>(a.mc_grads) + e, g0);
-          mm_st_f4(const_cast<float*>(a.mc_grads) + e + 4, g1);
+      if (!a.mc_grads && peers > 0) {
+        // all remote loads of the sweep first (peers visited in rotated order so that ranks do not all hit
+        // the same GPU at once), then the sums, in that same fixed order: run-to-run deterministic
+        float4 t[AR_SLOTS];
+#pragma unroll
+        for (int sl = 0; sl < AR_SLOTS; ++sl) {
+          const int u = sl / peers, po = sl - u * peers;
+          const long long i = base + (long long)u * gthreads * 4 + tid4;
+          if (u < U && i < s1) {
+            int peer = a.rank + 1 + po;
+            if (peer >= a.world) peer -= a.world;
+            t[sl] = ld_f4(a.grads[peer] + a.off + i);
+          }
+        }
+#pragma unroll
+        for (int sl = 0; sl < AR_SLOTS; ++sl) {
+          const int u = sl / peers;
+          const long long i = base + (long long)u * gthreads * 4 + tid4;
+          if (u < U && i < s1) {
+#pragma unroll
+            for (int uu = 0; uu < 4; ++uu)
+              if (uu == u) ga[uu] = add4(ga[uu], t[sl]);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const long long i = base + (long long)u * gthreads * 4 + tid4;
+        if (u >= U || i >= s1) continue;
+        const long long e = a.off + i;
+        float4 g = ga[u];
+        if (a.op == 1) {
+          // plain average, written back to every rank's buffer in place
+          const float s = a.avg_scale;
+          g = make_float4(g.x * s, g.y * s, g.z * s, g.w * s);
+          if (a.mc_grads) {
+            mm_st_f4(const_cast<float*>(a.mc_grads) + e, g);
+          } else {
+#pragma unroll
+            for (int p = 0; p < MAX_RANKS; ++p)
+              if (p < a.world) *reinterpret_cast<float4*>(a.grads[p] + e) = g;
+          }
+          continue;
+        }
+        SgdHyper h = a.h;
+        if (e >= a.decay_len) h.l2 = 0.f;
+        float4 w = wa[u], v = va[u];
+        sgd_elem(w.x, g.x, v.x, h);
+        sgd_elem(w.y, g.y, v.y, h);
+        sgd_elem(w.z, g.z, v.z, h);
+        sgd_elem(w.w, g.w, v.w, h);
+        *reinterpret_cast<float4*>(a.w + e) = w;
+        *reinterpret_cast<float4*>(a.v + e) = v;
+        uint2 packed;
+        {
+          __nv_bfloat162 b0 = __floats2bfloat162_rn(w.x, w.y), b1 = __floats2bfloat162_rn(w.z, w.w);
+          packed.x = *reinterpret_cast<uint32_t*>(&b0);
+          packed.y = *reinterpret_cast<uint32_t*>(&b1);
+        }
+        if (a.one_shot) {
+          *reinterpret_cast<uint2*>(a.w16[a.rank] + e) = packed;
+        } else if (a.mc_w16) {
+          asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(a.mc_w16 + e),
+                       "f"(__uint_as_float(packed.x)), "f"(__uint_as_float(packed.y)) : "memory");
         } else {
 #pragma unroll
-          for (int p = 0; p < MAX_RANKS; ++p) {
-            if (p < a.world) {
-              *reinterpret_cast<float4*>(a.grads[p] + e) = g0;
-              *reinterpret_cast<float4*>(a.grads[p] + e + 4) = g1;
-            }
-          }
+          for (int p = 0; p < MAX_RANKS; ++p)
+            if (p < a.world) *reinterpret_cast<uint2*>(a.w16[p] + e) = packed;
         }
-        continue;
-      }
-      SgdHyper h = a.h;
-      if (e >= a.decay_len) h.l2 = 0.f;
-      float4 w0 = *reinterpret_cast<float4*>(a.w + e), w1 = *reinterpret_cast<float4*>(a.w + e + 4);
-      float4 v0 = *reinterpret_cast<float4*>(a.v + e), v1 = *reinterpret_cast<float4*>(a.v + e + 4);
-      sgd_elem(w0.x, g0.x, v0.x, h); sgd_elem(w0.y, g0.y, v0.y, h);
-      sgd_elem(w0.z, g0.z, v0.z, h); sgd_elem(w0.w, g0.w, v0.w, h);
-      sgd_elem(w1.x, g1.x, v1.x, h); sgd_elem(w1.y, g1.y, v1.y, h);
-      sgd_elem(w1.z, g1.z, v1.z, h); sgd_elem(w1.w, g1.w, v1.w, h);
-      *reinterpret_cast<float4*>(a.w + e) = w0;
-      *reinterpret_cast<float4*>(a.w + e + 4) = w1;
-      *reinterpret_cast<float4*>(a.v + e) = v0;
-      *reinterpret_cast<float4*>(a.v + e + 4) = v1;
-      uint4 packed;
-      {
-        __nv_bfloat162 b0 = __floats2bfloat162_rn(w0.x, w0.y), b1 = __floats2bfloat162_rn(w0.z, w0.w);
-        __nv_bfloat162 b2 = __floats2bfloat162_rn(w1.x, w1.y), b3 = __floats2bfloat162_rn(w1.z, w1.w);
-        packed.x = *reinterpret_cast<uint32_t*>(&b0);
-        packed.y = *reinterpret_cast<uint32_t*>(&b1);
-        packed.z = *reinterpret_cast<uint32_t*>(&b2);
-        packed.w = *reinterpret_cast<uint32_t*>(&b3);
-      }
-      if (a.one_shot) {
-        *reinterpret_cast<uint4*>(a.w16[a.rank] + e) = packed;
-      } else if (a.mc_w16) {
-        mm_st_f4(a.mc_w16 + e, make_float4(__uint_as_float(packed.x), __uint_as_float(packed.y),
-                                           __uint_as_float(packed.z), __uint_as_float(packed.w)));
-      } else {
+        if (!a.one_shot && a.w32[0]) {
 #pragma unroll
-        for (int p = 0; p < MAX_RANKS; ++p)
-          if (p < a.world) *reinterpret_cast<uint4*>(a.w16[p] + e) = packed;
-      }
-      if (!a.one_shot && a.w32[0]) {
-#pragma unroll
-        for (int p = 0; p < MAX_RANKS; ++p) {
-          if (p < a.world && p != a.rank) {
-            *reinterpret_cast<float4*>(a.w32[p] + e) = w0;
-            *reinterpret_cast<float4*>(a.w32[p] + e + 4) = w1;
-          }
+          for (int p = 0; p < MAX_RANKS; ++p)
+            if (p < a.world && p != a.rank) *reinterpret_cast<float4*>(a.w32[p] + e) = w;
         }
       }
     }
@@ -422,7 +448,7 @@ int rb_allreduce_sgd_p2p(const void* args, int blocks, cudaStream_t st) {
   const ArSgdArgs* a = reinterpret_cast<const ArSgdArgs*>(args);
   if (a->world < 1 || a->world > MAX_RANKS || (a->n % 8) || (a->off % 8)) return -10;
   if (blocks < 1) blocks = 1;
-  allreduce_sgd_kernel<<<blocks, 512, 0, st>>>(*a);
+  allreduce_sgd_kernel<<<blocks, AR_THREADS, 0, st>>>(*a);
   return RB_LAUNCH_OK();
 }
 

@@ -96,7 +96,7 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
     name = "fused_allreduce_sgd"
     graph_safe = True
 
-    def __init__(self, group=None, bucket_bytes: int = 25 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 48,
+    def __init__(self, group=None, bucket_bytes: int = 25 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 296,
                  one_shot_bytes: int = 256 << 10, replicate_master: bool = False, use_multimem: Optional[bool] = None):
         AllreduceComm.__init__(self, group)
         self._init_p2p(group)
@@ -215,7 +215,8 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         if op == 0:
             lr, mu, l2, gs, mode = self._hyper
             a.h.lr, a.h.mu, a.h.l2, a.h.grad_scale, a.h.mode, a.h.phase = lr, mu, l2, gs, mode, 3
-        blocks = max(1, min(self.blocks, (n // 8 + 511) // 512))
+        work = n if a.one_shot else (n + self.world - 1) // self.world
+        blocks = max(1, min(self.blocks, (work // 4 + 127) // 128))
         with torch.cuda.stream(self.comm_stream):
             check(PK.fn("rb_allreduce_sgd_p2p")(C.byref(a), blocks, self.comm_stream.cuda_stream),
                   "rb_allreduce_sgd_p2p")
