@@ -58,6 +58,7 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index=0):
+        # an int, or a comma-separated list of local GPU indices (every GPU of a multi-rank run)
         self.gpu_index = gpu_index
         self.proc = None
         self.lines = []
@@ -84,7 +85,7 @@ class ClockSampler:
             self.proc.wait(timeout=2)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, per_gpu = [], [], set(), {}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines:
             parts = [p.strip() for p in ln.split(",")]
@@ -93,13 +94,15 @@ class ClockSampler:
             try:
                 sm.append(float(parts[1]))
                 mx.append(float(parts[2]))
+                per_gpu.setdefault(parts[0], []).append(float(parts[1]))
             except ValueError:
                 continue
             for nm, val in zip(names, parts[5:9]):
                 if val.lower() == "active":
                     reasons.add(nm)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "sm_mhz_slowest_gpu": min(statistics.median(v) for v in per_gpu.values()) if per_gpu else None,
+                "gpus_sampled": len(per_gpu), "samples": len(sm), "reasons": sorted(reasons)}
 
 
 def main():
@@ -235,7 +238,7 @@ def main():
         resident_step(i)
     finish()
 
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(",".join(str(i) for i in range(world)) if world > 1 else local_rank)
     if rank == 0:
         sampler.start()
         time.sleep(0.15)

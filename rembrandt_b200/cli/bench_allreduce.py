@@ -4,10 +4,12 @@ by the separate fused-SGD kernel. Device-timed (CUDA events), max over ranks; re
 
     python -m torch.distributed.run --nproc-per-node 8 -m rembrandt_b200.cli.bench_allreduce --sizes-mb 1 4 16 25 64 256
 
-Roofline of the fused kernel (two-shot, sharded optimizer): each GPU pulls (N-1)/N * S bytes of fp32 gradients
-and pushes (N-1)/N * S/2 bytes of bf16 weights; the two directions are independent, so the bound is
-(N-1)/N * S / link_bandwidth with the measured 770 GB/s per direction. With NVSwitch multimem reductions the
-inbound side shrinks to S/N and the bound is the outbound (N-1)/N * S of gradient reads served to the switch.
+Roofline of the fused exchange (two-shot, sharded optimizer): every GPU sends (N-1)/N * S bytes of fp32 gradients
+(its contribution to the other ranks' shards) and (N-1)/N * S/2 bytes of new bf16 weights (its shard, to every
+peer), and receives as much; both travel in the same direction of its links, so the bound is
+1.5 * (N-1)/N * S / link_bandwidth with the measured 770 GB/s per direction (multimem.st broadcasts the weights
+through the switch and shrinks the outbound weight term to S/2N). The plain all-reduce (op 1) moves fp32 both ways:
+2 * (N-1)/N * S / link_bandwidth.
 """
 import argparse
 import json
@@ -75,6 +77,10 @@ def main(argv=None):
     comm._ready, comm._done = torch.cuda.Event(), torch.cuda.Event()
     comm.mc_grads = comm.arena.multicast_ptr("grads") if comm.use_multimem else 0
     comm.mc_w16 = comm.arena.multicast_ptr("params16") if comm.use_multimem else 0
+    comm.launches = [(0, 0, max_n, 0)]
+    comm.one_shot_elems = 0
+    comm.setup_stage(avg_elems=max_n)
+    comm._avg_cap = max_n
     comm._hyper = (0.01, 0.9, 5e-4, 1.0 / world, 1)
     net.grads.normal_()
     rows = []
@@ -82,7 +88,7 @@ def main(argv=None):
         n = int(mb * (1 << 20) / 4) // 512 * 512
         fused = lambda: comm._launch(0, n, 0, op=0)
         t_fused = timed(fused, args.iters, args.warmup)
-        plain = lambda: comm._launch(0, n, 1, op=1)
+        plain = lambda: comm._launch(0, n, comm.num_slots - 1, op=1)
         t_plain = timed(plain, args.iters, args.warmup)
 
         def nccl():
@@ -91,7 +97,7 @@ def main(argv=None):
         t_nccl = timed(nccl, args.iters, args.warmup)
         s = n * 4.0
         busbw = lambda ms: s / (ms * 1e-3) * 2 * (world - 1) / world / 1e9
-        bound_ms = (world - 1) / world * s / (LINK_GBS * 1e9) * 1e3
+        bound_ms = 1.5 * (world - 1) / world * s / (LINK_GBS * 1e9) * 1e3
         rows.append({"bucket_mb": mb, "n_gpus": world, "multimem": bool(comm.mc_grads),
                      "fused_allreduce_sgd_ms": round(t_fused, 4), "fused_busbw_gbs": round(busbw(t_fused), 1),
                      "fused_fraction_of_roofline": round(bound_ms / t_fused, 3),

@@ -35,6 +35,7 @@ struct ArSgdArgs {
   bf16* w16[MAX_RANKS];        // peer-visible bf16 compute weights (op 0)
   float* w32[MAX_RANKS];       // optional: peer-visible fp32 masters to keep replicated (op 0)
   uint32_t* flags[MAX_RANKS];  // peer-visible flag pads: [slot][phase 0/1][source rank]
+  float* stage[MAX_RANKS];     // peer-visible staging: per bucket, `world` slots (one per source rank) of shard length
   float* w;                    // local master weights
   float* v;                    // local momentum
   const float* mc_grads;       // multimem (NVSwitch multicast) address of the gradient buffer, or null
@@ -42,8 +43,9 @@ struct ArSgdArgs {
   uint32_t* epoch_ptr;         // local: last completed epoch of this slot
   unsigned int* block_counter; // local, zero between launches
   unsigned int* status;
-  long long off, n, decay_len;
-  int rank, world, slot, one_shot, op;
+  uint32_t* wait_ok;           // local: verdict of ar_wait_kernel for this slot (null: the reducing kernel waits itself)
+  long long off, n, decay_len, stage_off;
+  int rank, world, slot, one_shot, op, zero_grads;
   float avg_scale;             // op 1: result = sum * avg_scale
   SgdHyper h;
 };
@@ -127,36 +129,113 @@ __device__ __forceinline__ void end_barrier(uint32_t* const* flags, int rank, in
   }
 }
 
-// Thread blocks are small (128 threads, <= 85 registers) on purpose: the kernel runs on its own stream while the
+// Thread blocks are small (128 threads, <= 85 registers) on purpose: the kernels run on their own stream while the
 // backward pass's GEMM CTAs (one per SM, most of the register file and all of the shared memory) are resident,
-// and only a block this size fits beside them. Each thread owns groups of 4 consecutive elements; per sweep it
-// keeps up to 8 remote 16-byte loads in flight (U groups x (world-1) peers) before it consumes any, because an
-// NVLink round trip takes microseconds and throughput is bytes in flight / latency.
+// and only a block this size fits beside them. With so few threads a design that PULLS gradients from peers is
+// latency bound (a remote load takes ~2 us; 148 x 128 threads x 64 B in flight is ~0.5 TB/s at best and far less
+// once the loads compete with local ones for registers), whereas remote STORES are posted and saturate the link
+// from any grid. So the exchange is push based:
+//   ar_push_kernel        rank r copies shard p of its gradients into slot r of peer p's staging buffer
+//                         (local loads, remote stores), zeroes what it read, and raises phase-0 flags;
+//   allreduce_sgd_kernel  waits for every peer's phase-0 flag, sums its own shard with the N-1 staged copies
+//                         (all local loads), applies 1/N + SGD to its shard of master/momentum and stores the
+//                         new bf16 weights into every peer (remote stores, or one multimem.st).
+// With a multimem mapping of the gradient buffer the push is skipped and the second kernel fetches the sum with
+// multimem.ld_reduce (the switch does the N-way read).
 constexpr int AR_THREADS = 128;
 constexpr int AR_SLOTS = 8;
 
+__device__ __forceinline__ long long shard_len(long long n, int world) {
+  long long per = (n + world - 1) / world;
+  return (per + 7) / 8 * 8;
+}
+
+__global__ void __launch_bounds__(AR_THREADS, 6) ar_push_kernel(const __grid_constant__ ArSgdArgs a) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
+  const int peers = a.world - 1;
+  const long long per = a.one_shot ? a.n : shard_len(a.n, a.world);
+  const uint32_t per4 = (uint32_t)(per / 4);
+  const uint32_t total4 = per4 * (uint32_t)peers;
+  const uint32_t gthreads = gridDim.x * blockDim.x;
+  float* g = a.grads[a.rank] + a.off;
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (uint32_t base = blockIdx.x * blockDim.x + threadIdx.x; base < total4; base += gthreads * 4u) {
+    float4 t[4];
+    float* dstp[4];
+    float* srcp[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const uint32_t j = base + (uint32_t)u * gthreads;
+      dstp[u] = nullptr;
+      if (j < total4) {
+        const uint32_t po = j / per4, k = j - po * per4;
+        int peer = a.rank + 1 + (int)po;
+        if (peer >= a.world) peer -= a.world;
+        const long long si = (a.one_shot ? 0 : (long long)peer * per) + (long long)k * 4;
+        if (si < a.n) {
+          srcp[u] = g + si;
+          t[u] = ld_f4(srcp[u]);
+          dstp[u] = a.stage[peer] + a.stage_off + (long long)a.rank * per + (long long)k * 4;
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (dstp[u]) {
+        *reinterpret_cast<float4*>(dstp[u]) = t[u];
+        // in one-shot mode the own copy is still needed by the reducing kernel, which zeroes it itself
+        if (a.zero_grads && !a.one_shot) *reinterpret_cast<float4*>(srcp[u]) = zero;
+      }
+    }
+  }
+  // last block: every store of this rank into the peers' staging has been fenced; tell them
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last) {
+    __threadfence_system();
+    if (threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 0, a.rank), epoch);
+    if (threadIdx.x == 0) {
+      *a.block_counter = 0u;
+      __threadfence();
+    }
+  }
+}
+
 __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __grid_constant__ ArSgdArgs a) {
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
-  const bool ready = start_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.status);
+  bool ready;
+  if (a.wait_ok) {
+    ready = *reinterpret_cast<volatile uint32_t*>(a.wait_ok) == epoch;
+  } else if (a.mc_grads) {
+    ready = start_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.status);
+  } else {
+    int ok = 1;
+    if (threadIdx.x < a.world) ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch) ? 1 : 0;
+    ok = __syncthreads_and(ok);
+    if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
+    ready = ok != 0;
+  }
   if (ready) {
-    long long s0 = 0, s1 = a.n;
+    long long s0 = 0, s1 = a.n, per = a.n;
     if (!a.one_shot) {
-      long long per = (a.n + a.world - 1) / a.world;
-      per = (per + 7) / 8 * 8;
+      per = shard_len(a.n, a.world);
       s0 = min(a.n, (long long)a.rank * per);
       s1 = min(a.n, s0 + per);
     }
     const int peers = a.world - 1;
-    int U = peers > 0 ? AR_SLOTS / peers : 4;
-    U = U > 4 ? 4 : (U < 1 ? 1 : U);
+    const int U = (peers <= 3) ? 2 : 1;   // groups of 4 elements per thread and sweep: U * (3 + peers) loads in flight
     const long long gthreads = (long long)gridDim.x * blockDim.x;
     const long long sweep = gthreads * 4 * U;
     const long long tid4 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const float* stage = a.stage[a.rank] + a.stage_off;
+    const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
     for (long long base = s0; base < s1; base += sweep) {
-      float4 ga[4], wa[4], va[4];
-      // own (or switch-reduced) contribution; the local master / momentum loads go out in the same wave
+      float4 ga[2], wa[2], va[2];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const long long i = base + (long long)u * gthreads * 4 + tid4;
         if (u < U && i < s1) {
           ga[u] = a.mc_grads ? mm_ld_reduce_f4(a.mc_grads + a.off + i) : ld_f4(a.grads[a.rank] + a.off + i);
@@ -167,32 +246,28 @@ __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __gr
         }
       }
       if (!a.mc_grads && peers > 0) {
-        // all remote loads of the sweep first (peers visited in rotated order so that ranks do not all hit
-        // the same GPU at once), then the sums, in that same fixed order: run-to-run deterministic
+        // staged copies of the peers, summed in a fixed order (run-to-run deterministic)
         float4 t[AR_SLOTS];
 #pragma unroll
         for (int sl = 0; sl < AR_SLOTS; ++sl) {
-          const int u = sl / peers, po = sl - u * peers;
+          const int u = (peers <= 3) ? sl / 4 : 0, po = (peers <= 3) ? (sl & 3) : sl;
           const long long i = base + (long long)u * gthreads * 4 + tid4;
-          if (u < U && i < s1) {
+          t[sl] = zero;
+          if (po < peers && i < s1) {
             int peer = a.rank + 1 + po;
             if (peer >= a.world) peer -= a.world;
-            t[sl] = ld_f4(a.grads[peer] + a.off + i);
+            t[sl] = ld_f4(stage + (long long)peer * per + (i - s0));
           }
         }
-#pragma unroll
-        for (int sl = 0; sl < AR_SLOTS; ++sl) {
-          const int u = sl / peers;
-          const long long i = base + (long long)u * gthreads * 4 + tid4;
-          if (u < U && i < s1) {
-#pragma unroll
-            for (int uu = 0; uu < 4; ++uu)
-              if (uu == u) ga[uu] = add4(ga[uu], t[sl]);
-          }
+        if (peers <= 3) {
+          ga[0] = add4(ga[0], add4(add4(t[0], t[1]), t[2]));
+          ga[1] = add4(ga[1], add4(add4(t[4], t[5]), t[6]));
+        } else {
+          ga[0] = add4(ga[0], add4(add4(add4(t[0], t[1]), add4(t[2], t[3])), add4(add4(t[4], t[5]), t[6])));
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 2; ++u) {
         const long long i = base + (long long)u * gthreads * 4 + tid4;
         if (u >= U || i >= s1) continue;
         const long long e = a.off + i;
@@ -210,6 +285,7 @@ __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __gr
           }
           continue;
         }
+        if (a.zero_grads) *reinterpret_cast<float4*>(a.grads[a.rank] + e) = zero;
         SgdHyper h = a.h;
         if (e >= a.decay_len) h.l2 = 0.f;
         float4 w = wa[u], v = va[u];
@@ -244,6 +320,25 @@ __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __gr
     }
   }
   end_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.block_counter, a.epoch_ptr, a.status);
+}
+
+// The wait for the peers' phase-0 flags as a kernel of its own (one warp): the reducing kernel that follows in
+// stream order then never spins, so its blocks do not sit on SMs that the backward pass's GEMM CTAs need.
+// With a multimem gradient mapping there is no push kernel, so this kernel also announces the rank.
+__global__ void ar_wait_kernel(const __grid_constant__ ArSgdArgs a) {
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
+  if (a.mc_grads && threadIdx.x < a.world) {
+    __threadfence_system();
+    st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 0, a.rank), epoch);
+  }
+  int ok = 1;
+  if (threadIdx.x < a.world) ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch) ? 1 : 0;
+  ok = __all_sync(0xffffffffu, ok);
+  if (threadIdx.x == 0) {
+    if (!ok) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
+    *a.wait_ok = ok ? epoch : 0u;
+    __threadfence();
+  }
 }
 
 // ------------------------------------------------------------------------------------------ gossip
@@ -437,6 +532,35 @@ __global__ void barrier_kernel(const __grid_constant__ BarrierArgs a) {
   }
 }
 
+
+// Link probe: what one direction of the NVLink fabric gives to SM-issued traffic, as a function of how many
+// 16-byte accesses each thread keeps in flight. mode 0 = load from `src` (sum kept in a register), 1 = store a
+// constant to `dst`, 2 = copy src -> dst. Which of the two pointers is a peer's memory is the caller's choice.
+template <int UNROLL>
+__global__ void __launch_bounds__(512) link_probe_kernel(const float* __restrict__ src, float* __restrict__ dst,
+                                                         float* __restrict__ sink, long long n4, int mode) {
+  const long long gthreads = (long long)gridDim.x * blockDim.x;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (long long base = tid; base < n4; base += gthreads * UNROLL) {
+    float4 t[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = base + (long long)u * gthreads;
+      if (mode != 1 && i < n4) t[u] = ld_f4(src + i * 4);
+      else t[u] = make_float4(1.f, 2.f, 3.f, 4.f);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const long long i = base + (long long)u * gthreads;
+      if (i >= n4) continue;
+      if (mode == 0) acc = add4(acc, t[u]);
+      else *reinterpret_cast<float4*>(dst + i * 4) = t[u];
+    }
+  }
+  if (mode == 0 && acc.x + acc.y + acc.z + acc.w == 1.2345e-30f) sink[0] = acc.x;
+}
+
 }  // namespace rb
 
 using namespace rb;
@@ -448,7 +572,25 @@ int rb_allreduce_sgd_p2p(const void* args, int blocks, cudaStream_t st) {
   const ArSgdArgs* a = reinterpret_cast<const ArSgdArgs*>(args);
   if (a->world < 1 || a->world > MAX_RANKS || (a->n % 8) || (a->off % 8)) return -10;
   if (blocks < 1) blocks = 1;
+  if (!a->mc_grads && a->world > 1 && !a->stage[a->rank]) return -11;
   allreduce_sgd_kernel<<<blocks, AR_THREADS, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_allreduce_wait_p2p(const void* args, cudaStream_t st) {
+  const ArSgdArgs* a = reinterpret_cast<const ArSgdArgs*>(args);
+  if (a->world < 1 || a->world > MAX_RANKS || !a->wait_ok) return -10;
+  ar_wait_kernel<<<1, 32, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+// First half of the push-based exchange (not needed with a multimem gradient mapping or on one rank).
+int rb_allreduce_push_p2p(const void* args, int blocks, cudaStream_t st) {
+  const ArSgdArgs* a = reinterpret_cast<const ArSgdArgs*>(args);
+  if (a->world < 2 || a->world > MAX_RANKS || (a->n % 8) || (a->off % 8) || (a->stage_off % 4)) return -10;
+  if (!a->stage[a->rank] || a->n / 4 * (a->world - 1) >= (1ll << 31)) return -11;
+  if (blocks < 1) blocks = 1;
+  ar_push_kernel<<<blocks, AR_THREADS, 0, st>>>(*a);
   return RB_LAUNCH_OK();
 }
 
@@ -498,6 +640,21 @@ int rb_elastic_apply(float* center, float* delta, long long n, cudaStream_t st) 
 int rb_barrier_p2p(const void* args, cudaStream_t st) {
   const BarrierArgs* a = reinterpret_cast<const BarrierArgs*>(args);
   barrier_kernel<<<1, 32, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_link_probe(const float* src, float* dst, float* sink, long long n, int mode, int unroll, int blocks,
+                  int threads, cudaStream_t st) {
+  if (n % 4 || threads < 32 || threads > 512 || blocks < 1 || mode < 0 || mode > 2) return -10;
+  const long long n4 = n / 4;
+  switch (unroll) {
+    case 1: link_probe_kernel<1><<<blocks, threads, 0, st>>>(src, dst, sink, n4, mode); break;
+    case 2: link_probe_kernel<2><<<blocks, threads, 0, st>>>(src, dst, sink, n4, mode); break;
+    case 4: link_probe_kernel<4><<<blocks, threads, 0, st>>>(src, dst, sink, n4, mode); break;
+    case 8: link_probe_kernel<8><<<blocks, threads, 0, st>>>(src, dst, sink, n4, mode); break;
+    case 16: link_probe_kernel<16><<<blocks, threads, 0, st>>>(src, dst, sink, n4, mode); break;
+    default: return -10;
+  }
   return RB_LAUNCH_OK();
 }
 

@@ -158,9 +158,20 @@ class AllreduceComm(CommWorker):
 
 def _exchange(flat: torch.Tensor, send_to: int, recv_from: int, rank: int, group) -> Optional[torch.Tensor]:
     """Send `flat` to one peer and receive a vector from another (either may be this rank)."""
+    recv = torch.empty_like(flat) if recv_from != rank else None
+    if dist.get_backend(group) == "nccl":
+        # one collective over the whole group: point-to-point calls between pairs that have not talked before
+        # set up a connection per pair, in an order that differs between ranks of a long cycle
+        world = dist.get_world_size(group)
+        n = flat.numel()
+        in_split = [n if (r == send_to and send_to != rank) else 0 for r in range(world)]
+        out_split = [n if (r == recv_from and recv_from != rank) else 0 for r in range(world)]
+        src = flat if send_to != rank else flat[:0]
+        dst = recv if recv is not None else flat[:0]
+        dist.all_to_all_single(dst, src.contiguous(), out_split, in_split, group=group)
+        return recv
     if send_to == rank and recv_from == rank:
         return None
-    recv = torch.empty_like(flat) if recv_from != rank else None
     ops = []
     if send_to != rank:
         ops.append(dist.P2POp(dist.isend, flat, send_to, group))

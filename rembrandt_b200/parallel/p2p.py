@@ -96,7 +96,7 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
     name = "fused_allreduce_sgd"
     graph_safe = True
 
-    def __init__(self, group=None, bucket_bytes: int = 25 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 296,
+    def __init__(self, group=None, bucket_bytes: int = 25 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 148,
                  one_shot_bytes: int = 256 << 10, replicate_master: bool = False, use_multimem: Optional[bool] = None):
         AllreduceComm.__init__(self, group)
         self._init_p2p(group)
@@ -108,6 +108,13 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         if use_multimem is None:
             use_multimem = os.environ.get("RB_MULTIMEM", "0") == "1"
         self.use_multimem = use_multimem
+        # overlap=False launches every bucket after backward instead of from inside it; split_wait puts the wait
+        # for the peers into a one-warp kernel so that the reducing kernel's blocks never spin on an SM
+        self.overlap = os.environ.get("RB_COMM_OVERLAP", "1") == "1"
+        self.split_wait = os.environ.get("RB_COMM_SPLIT_WAIT", "1") == "1"
+        self.blocks = int(os.environ.get("RB_COMM_BLOCKS", self.blocks))
+        self.wait_ok = torch.zeros(self.num_slots, dtype=torch.int32,
+                                   device=torch.device("cuda", torch.cuda.current_device()))
         self.engine = None
         self.launches = []        # [(trigger op index, off, n, slot)]
         self._by_trigger = {}
@@ -130,6 +137,27 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         self._plan(net)
         self.mc_grads = self.arena.multicast_ptr("grads") if self.use_multimem else 0
         self.mc_w16 = self.arena.multicast_ptr("params16") if self.use_multimem else 0
+        self.setup_stage()
+
+    def _shard_len(self, n):
+        per = (n + self.world - 1) // self.world
+        return (per + 7) // 8 * 8
+
+    def setup_stage(self, avg_elems: Optional[int] = None):
+        """Staging memory of the push-based exchange: per bucket, one slot per source rank of the length a rank
+        reduces (its shard, or the whole bucket for one-shot buckets); one more region for `allreduce_average`."""
+        self._stage_off = {}
+        off = 0
+        for _, _o, n, slot in self.launches:
+            per = n if n <= self.one_shot_elems else self._shard_len(n)
+            self._stage_off[slot] = off
+            off += self.world * per
+        avg = self.bucket_elems if avg_elems is None else avg_elems
+        self._stage_off[self.num_slots - 1] = off
+        off += self.world * self._shard_len(avg) + 64
+        self._avg_cap = avg
+        if self.world > 1 and not self.mc_grads:
+            self.arena.alloc("stage", off, torch.float32)
 
     # ---- bucket plan: ranges of the flat vectors in the order backward completes them
     def _plan(self, net):
@@ -181,7 +209,7 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
 
     def on_op_backward(self, op_index):
         recs = self._by_trigger.get(op_index)
-        if not recs:
+        if not recs or not self.overlap:
             return
         cur = torch.cuda.current_stream()
         self._ready.record(cur)
@@ -191,6 +219,11 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
 
     def fused_grads_step(self, stepper, lr):
         """Everything was launched from the backward hooks; join the communication stream."""
+        if not self.overlap:
+            self._ready.record(torch.cuda.current_stream())
+            self.comm_stream.wait_event(self._ready)
+            for _, off, n, slot in self.launches:
+                self._launch(off, n, slot, op=0)
         self._done.record(self.comm_stream)
         torch.cuda.current_stream().wait_event(self._done)
 
@@ -204,6 +237,15 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         a.w, a.v = net.params.data_ptr(), net.mom.data_ptr()
         a.mc_grads = (self.mc_grads or None) if buf == "grads" else None
         a.mc_w16 = self.mc_w16 or None
+        push = self.world > 1 and not a.mc_grads
+        if push:
+            if buf != "grads":
+                raise ValueError("the push exchange stages the gradient buffer only")
+            _fill_ptrs(a.stage, self.arena.ptrs("stage"))
+            a.stage_off = self._stage_off[slot]
+            if slot == self.num_slots - 1 and n > self._avg_cap:
+                raise ValueError("bucket larger than the staging region")
+        a.zero_grads = 1 if (op == 0 and push) else 0
         a.epoch_ptr = self.epochs[slot:].data_ptr()
         a.block_counter = self.counters[slot:].data_ptr()
         a.status = self.status.data_ptr()
@@ -216,12 +258,24 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
             lr, mu, l2, gs, mode = self._hyper
             a.h.lr, a.h.mu, a.h.l2, a.h.grad_scale, a.h.mode, a.h.phase = lr, mu, l2, gs, mode, 3
         work = n if a.one_shot else (n + self.world - 1) // self.world
-        blocks = max(1, min(self.blocks, (work // 4 + 127) // 128))
+        blocks = max(1, min(self.blocks, (work // 8 + 127) // 128))
         with torch.cuda.stream(self.comm_stream):
+            if push:
+                pwork = (n if a.one_shot else self._shard_len(n)) * (self.world - 1)
+                pblocks = max(1, min(self.blocks, (pwork // 16 + 127) // 128))
+                check(PK.fn("rb_allreduce_push_p2p")(C.byref(a), pblocks, self.comm_stream.cuda_stream),
+                      "rb_allreduce_push_p2p")
+                self.kernel_launches_per_step += 1
+            if self.split_wait and self.world > 1:
+                a.wait_ok = self.wait_ok[slot:].data_ptr()
+                check(PK.fn("rb_allreduce_wait_p2p")(C.byref(a), self.comm_stream.cuda_stream),
+                      "rb_allreduce_wait_p2p")
+                self.kernel_launches_per_step += 1
             check(PK.fn("rb_allreduce_sgd_p2p")(C.byref(a), blocks, self.comm_stream.cuda_stream),
                   "rb_allreduce_sgd_p2p")
-            if op == 0:
-                # every peer has finished reading this bucket when the kernel ends
+            if op == 0 and not push:
+                # every peer has finished reading this bucket when the kernel ends; the push kernels zero
+                # what they read themselves
                 net.grads[off:off + n].zero_()
         self.bytes_moved += n * 4
         self.kernel_launches_per_step += 1

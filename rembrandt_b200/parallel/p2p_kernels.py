@@ -7,6 +7,8 @@ MAX_RANKS = 8
 
 SIGS = {
     "rb_allreduce_sgd_p2p": [vp, i32, vp],
+    "rb_allreduce_push_p2p": [vp, i32, vp],
+    "rb_allreduce_wait_p2p": [vp, vp],
     "rb_publish_p2p": [vp, i32, vp],
     "rb_gossip_mix_p2p": [vp, i32, vp],
     "rb_push_add_p2p": [vp, i32, vp],
@@ -14,6 +16,7 @@ SIGS = {
     "rb_elastic_pull_p2p": [vp, i32, vp],
     "rb_elastic_apply": [vp, vp, i64, vp],
     "rb_barrier_p2p": [vp, vp],
+    "rb_link_probe": [vp, vp, vp, i64, i32, i32, i32, i32, vp],
 }
 
 
@@ -23,10 +26,10 @@ class SgdHyper(C.Structure):
 
 class ArSgdArgs(C.Structure):
     _fields_ = [("grads", vp * MAX_RANKS), ("w16", vp * MAX_RANKS), ("w32", vp * MAX_RANKS),
-                ("flags", vp * MAX_RANKS), ("w", vp), ("v", vp), ("mc_grads", vp), ("mc_w16", vp),
-                ("epoch_ptr", vp), ("block_counter", vp), ("status", vp), ("off", i64), ("n", i64),
-                ("decay_len", i64), ("rank", i32), ("world", i32), ("slot", i32), ("one_shot", i32), ("op", i32),
-                ("avg_scale", f32), ("h", SgdHyper)]
+                ("flags", vp * MAX_RANKS), ("stage", vp * MAX_RANKS), ("w", vp), ("v", vp), ("mc_grads", vp),
+                ("mc_w16", vp), ("epoch_ptr", vp), ("block_counter", vp), ("status", vp), ("wait_ok", vp), ("off", i64),
+                ("n", i64), ("decay_len", i64), ("stage_off", i64), ("rank", i32), ("world", i32), ("slot", i32),
+                ("one_shot", i32), ("op", i32), ("zero_grads", i32), ("avg_scale", f32), ("h", SgdHyper)]
 
 
 class MixArgs(C.Structure):

@@ -38,3 +38,12 @@ def _run(case, nproc=None, timeout=240):
 @pytest.mark.parametrize("case", ["p2p_allreduce", "fused_eager", "fused_graph", "gossip_pair", "elastic", "push"])
 def test_p2p_backend(case):
     _run(case)
+
+
+@pytest.mark.parametrize("case", ["p2p_allreduce", "fused_graph", "gossip_pair"])
+def test_p2p_backend_all_gpus(case):
+    """The same cases on every GPU of the box (8 ranks: one staged slot / one peer flag per rank in use)."""
+    n = torch.cuda.device_count()
+    if n <= 4:
+        pytest.skip("covered by test_p2p_backend")
+    _run(case, nproc=n)
