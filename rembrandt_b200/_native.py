@@ -56,6 +56,7 @@ _CUDA_SIGS = {
     "rb_axpby": [vp, vp, i64, f32, f32, vp],
     # input_pipeline.cu
     "rb_input_u8": [vp, vp, vp] + [i32] * 17 + [f32, f32, f32, vp, vp, u64, u32, vp, vp],
+    "rb_var_input_u8": [vp, vp, vp, vp, i64] + [i32] * 14 + [f32, vp, f32, vp, vp, u64, u32, vp, vp],
     "rb_synth_normal": [vp, i64, i32, i32, u64, u32, vp],
     "rb_synth_labels": [vp, i32, i32, u64, u32, vp],
     # bn.cu

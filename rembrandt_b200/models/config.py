@@ -114,7 +114,8 @@ class Data3dCfg:
     per_batch_draws: bool = False            # one crop offset / flip coin per batch (reference behaviour)
     scale: Optional[float] = None            # overrides the 1/255 factor when set
     variable_size: bool = False              # VarData3d: per-sample source shapes (src/operator/input.rs)
-    max_dims: Optional[Tuple[int, int, int]] = None
+    max_dims: Optional[Tuple[int, int, int]] = None   # largest (W, H, C) a variable-size sample may have
+    channel_mean: Optional[Sequence[float]] = None    # variable-size input: per-channel mean (after scaling)
 
 
 @dataclass

@@ -71,6 +71,8 @@ class Net:
         prev = None
         for no in named:
             cls = table.get(type(no.cfg))
+            if isinstance(no.cfg, C.Data3dCfg) and no.cfg.variable_size:
+                cls = O.VarDataOp
             if cls is None:
                 raise NotImplementedError(f"no operator for configuration {type(no.cfg).__name__}")
             op = cls(no.name, no.cfg)

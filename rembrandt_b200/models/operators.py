@@ -253,6 +253,175 @@ class DataOp(Op):
         return x
 
 
+class VarDataOp(DataOp):
+    """Variable-size input operator: every sample has its own width / height (up to `max_dims`).
+
+    Reference: VarData3dOperator (src/operator/input.rs:49-538) with its ScaleBicubic -> Crop -> FlipX -> PCA-noise
+    chain. Here the whole chain is one kernel (csrc/var_input.cu) that interpolates only the pixels of the crop
+    window. Training draws, per sample: the target length of the shorter side in [lower, upper], the crop offset
+    and the flip coin; inference uses `lower`, the centred crop and no flip (input.rs:318-321, 428-431).
+    A batch is a list of uint8 [C, h, w] tensors, or a pair (padded uint8 [B, C*maxH*maxW], int32 [B, 2] of (w, h)).
+    """
+
+    def setup(self, net, prev):
+        cfg: C.Data3dCfg = self.cfg
+        md = cfg.max_dims or cfg.in_dims
+        Op.setup(self, net, prev)
+        mw, mh, c = md
+        self.max_hwc = (mh, mw, c)
+        self.src_hwc = (mh, mw, c)
+        self.crop_h, self.crop_w, self.pad = mh, mw, 0
+        self.flip, self.pca, self.mean = False, None, None
+        self.scale_range = (0, 0)
+        for p in cfg.preprocs:
+            if p.kind == "crop":
+                self.crop_w, self.crop_h = p.crop_width, p.crop_height
+            elif p.kind == "flip_x":
+                self.flip = True
+            elif p.kind == "pca_noise":
+                self.pca = p
+            elif p.kind == "scale_bicubic":
+                self.scale_range = (int(p.lower), int(p.upper))
+            else:
+                raise ValueError(f"variable-size input does not support the stage {p.kind!r}")
+        if c > 4:
+            raise ValueError("variable-size input handles up to 4 channels")
+        self.scale = cfg.scale if cfg.scale is not None else (1.0 / 255.0 if cfg.normalize else 1.0)
+        self.channel_mean = list(cfg.channel_mean) if cfg.channel_mean is not None else [0.0] * c
+        self.out_hwc = (self.crop_h, self.crop_w, c)
+        self.out_cp = pad_channels(c)
+        self.mode, self.f, self.extra_pad = "nhwc", 1, 0
+        self.mean_dev = None
+        self.stage = None
+
+    def request_flat(self):
+        raise ValueError("a variable-size input cannot feed an affine operator directly")
+
+    def alloc(self):
+        mh, mw, c = self.max_hwc
+        dev = self.net.device
+        n = self.net.batch
+        self.in_stride = c * mh * mw
+        self.out = torch.zeros(self.out_buffer_shape(), dtype=torch.bfloat16, device=dev)
+        self.stage = torch.zeros((n, self.in_stride), dtype=torch.uint8, device=dev)
+        self.shapes = torch.ones((n, 2), dtype=torch.int32, device=dev)
+        self.draws = torch.zeros((n, 4), dtype=torch.int32, device=dev)
+
+    @staticmethod
+    def pack(images, in_stride):
+        """List of uint8 [C, h, w] tensors -> (padded [B, in_stride] uint8, [B, 2] int32 of (w, h)) on the host."""
+        padded = torch.zeros((len(images), in_stride), dtype=torch.uint8)
+        shapes = torch.zeros((len(images), 2), dtype=torch.int32)
+        for i, im in enumerate(images):
+            c, h, w = im.shape
+            if c * h * w > in_stride:
+                raise ValueError(f"sample {i} ({w}x{h}) exceeds the configured maximum")
+            padded[i, : c * h * w] = im.reshape(-1)
+            shapes[i, 0], shapes[i, 1] = w, h
+        return padded, shapes
+
+    def load_batch(self, images, non_blocking=True):
+        if isinstance(images, (list,)) or (isinstance(images, tuple) and images[0].dim() == 3):
+            images = self.pack(list(images), self.in_stride)
+        padded, shapes = images
+        self.stage.copy_(padded.reshape(self.stage.shape), non_blocking=non_blocking)
+        self.shapes.copy_(shapes.reshape(self.shapes.shape).int(), non_blocking=non_blocking)
+
+    def forward(self, train, t):
+        mh, mw, c = self.max_hwc
+        cfg = self.cfg
+        if self.mode == "s2d":
+            oh = ow = self.s2d_hw
+        else:
+            oh, ow = self.crop_h, self.crop_w
+        pv = pe = None
+        sigma = 0.0
+        if self.pca is not None and train:
+            sigma, pv, pe = self.pca.std, list(self.pca.eigenvalues), list(self.pca.eigenvectors)
+        K.var_input_u8(self.stage, self.shapes, self.out, self.draws, self.in_stride, self.net.batch, c, self.crop_h,
+                       self.crop_w, self.out_cp, self.f, self.extra_pad, oh, ow, self.scale_range[0],
+                       self.scale_range[1], train, self.flip, cfg.per_batch_draws, self.scale, self.channel_mean,
+                       sigma, pv, pe, self.net.data_seed, 0, self.net.step_counter)
+
+    # ---- plain-torch restatement (one sample), the oracle of the kernel
+    @staticmethod
+    def scaled_dims(w, h, sdim):
+        if sdim <= 0:
+            return w, h
+        f32 = torch.float32
+        if w <= h:
+            return sdim, int(torch.round(torch.tensor(sdim, dtype=f32) / torch.tensor(w, dtype=f32) * h))
+        return int(torch.round(torch.tensor(sdim, dtype=f32) / torch.tensor(h, dtype=f32) * w)), sdim
+
+    @staticmethod
+    def ref_sample(img, sdim, ox, oy, flip, crop_w, crop_h):
+        """img: [C, h, w] (any dtype). Returns float32 [C, crop_h, crop_w]: Catmull-Rom rescale so that the shorter
+        side is `sdim` (0 = none), window at (ox, oy) of the rescaled image, zeros outside it, optional flip."""
+        img = img.float()
+        c, h, w = img.shape
+        rw, rh = VarDataOp.scaled_dims(w, h, sdim)
+        xs = torch.arange(crop_w)
+        X = ox + (crop_w - 1 - xs if flip else xs)
+        Y = oy + torch.arange(crop_h)
+        inside = ((Y >= 0) & (Y < rh))[:, None] & ((X >= 0) & (X < rw))[None, :]
+        if (rw, rh) == (w, h):
+            out = img[:, Y.clamp(0, h - 1)][:, :, X.clamp(0, w - 1)]
+            return out * inside
+
+        def taps(P, src, dst):
+            f = (P.float() + 0.5) * (torch.tensor(float(src)) / torch.tensor(float(dst))) - 0.5
+            fl = torch.floor(f)
+            t = f - fl
+            t2, t3 = t * t, t * t * t
+            wts = torch.stack([-0.5 * t3 + t2 - 0.5 * t, 1.5 * t3 - 2.5 * t2 + 1.0, -1.5 * t3 + 2.0 * t2 + 0.5 * t,
+                               0.5 * t3 - 0.5 * t2], 1)                         # [n, 4]
+            idx = (fl.long()[:, None] - 1 + torch.arange(4)[None, :]).clamp(0, src - 1)
+            return wts, idx
+
+        wx, xi = taps(X, w, rw)
+        wy, yi = taps(Y, h, rh)
+        rows = img[:, yi.reshape(-1)].reshape(c, crop_h, 4, w)                 # [C, ch, 4, w]
+        cols = rows[:, :, :, xi.reshape(-1)].reshape(c, crop_h, 4, crop_w, 4)  # [C, ch, 4(j), cw, 4(k)]
+        horiz = (cols * wx[None, None, None]).sum(-1)                           # [C, ch, 4, cw]
+        out = (horiz * wy[None, :, :, None]).sum(2)
+        return out.clamp(0.0, 255.0) * inside
+
+    def ref_forward(self, x, train, t):
+        if isinstance(x, tuple) and not (x[0].dim() == 3):
+            padded, shapes = x
+            images = []
+            c = self.max_hwc[2]
+            for i in range(padded.shape[0]):
+                w, h = int(shapes[i, 0]), int(shapes[i, 1])
+                images.append(padded[i, : c * h * w].reshape(c, h, w))
+        else:
+            images = list(x)
+        g = self.net.ref_generator
+        outs = []
+        lo, hi = self.scale_range
+        mean = torch.tensor(self.channel_mean, dtype=torch.float32).reshape(-1, 1, 1)
+        for im in images:
+            c, h, w = im.shape
+            sdim = (int(torch.randint(lo, hi + 1, (1,), generator=g)) if train else lo) if lo > 0 else 0
+            rw, rh = self.scaled_dims(w, h, sdim)
+            if train and rw > self.crop_w:
+                ox = int(torch.randint(0, rw - self.crop_w + 1, (1,), generator=g))
+            else:
+                ox = (rw - self.crop_w) // 2
+            if train and rh > self.crop_h:
+                oy = int(torch.randint(0, rh - self.crop_h + 1, (1,), generator=g))
+            else:
+                oy = (rh - self.crop_h) // 2
+            flip = bool(train and self.flip and int(torch.randint(0, 2, (1,), generator=g)))
+            v = self.ref_sample(im, sdim, ox, oy, flip, self.crop_w, self.crop_h)
+            xs = torch.arange(self.crop_w)
+            X = ox + (self.crop_w - 1 - xs if flip else xs)
+            Y = oy + torch.arange(self.crop_h)
+            inside = ((Y >= 0) & (Y < rh))[:, None] & ((X >= 0) & (X < rw))[None, :]
+            outs.append((v * self.scale - mean) * inside)
+        return torch.stack(outs)
+
+
 # =============================================================================================== conv
 def conv_out(n, k, s, p):
     return (n + 2 * p - k) // s + 1

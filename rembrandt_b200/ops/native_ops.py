@@ -172,6 +172,21 @@ def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi
           "rb_input_u8")
 
 
+def var_input_u8(src, shapes, dst, draws, in_stride, N, C, crop_h, crop_w, Cp, f, ep, OH, OW, scale_lower, scale_upper,
+                 train, random_flip, per_batch, scale, mean, pca_sigma, pca_vals, pca_vecs, seed, step, step_ptr=None):
+    """Variable-size input: bicubic rescale + crop + flip + mean + lighting noise in one kernel (csrc/var_input.cu)."""
+    import ctypes as C_
+    mv = (C_.c_float * 4)(*(list(mean) + [0.0] * 4)[:4]) if mean is not None else None
+    pv = (C_.c_float * 3)(*pca_vals) if pca_vals is not None else None
+    pe = (C_.c_float * 9)(*pca_vecs) if pca_vecs is not None else None
+    cast = lambda a: C_.cast(a, C_.c_void_p) if a is not None else None
+    check(_native.cuda().rb_var_input_u8(ptr(src), ptr(shapes), ptr(dst), ptr(draws), int(in_stride), N, C, crop_h,
+                                         crop_w, Cp, f, ep, OH, OW, scale_lower, scale_upper, int(train),
+                                         int(random_flip), int(per_batch), float(scale), cast(mv), float(pca_sigma),
+                                         cast(pv), cast(pe), int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF,
+                                         ptr(step_ptr), stream_handle()), "rb_var_input_u8")
+
+
 def synth_normal(dst, pixels, C, Cp, seed, step):
     check(_native.cuda().rb_synth_normal(ptr(dst), pixels, C, Cp, int(seed) & (2**64 - 1), int(step) & 0xFFFFFFFF,
                                          stream_handle()), "rb_synth_normal")
