@@ -213,6 +213,12 @@ class SplitCfg:
     num_out_arms: int = 2
 
 
+@dataclass
+class JoinCfg:
+    """Fan-in for the graph container: the arms (same shape) are summed; every arm receives the output's delta."""
+    num_in_arms: int = 2
+
+
 OpCfg = object
 
 
@@ -290,3 +296,84 @@ class SequentialOperatorConfig:
         if self.input_op is None or self.loss_op is None:
             raise ValueError("a sequential configuration needs an input and a loss operator")
         return self
+
+
+class GraphOperatorConfig:
+    """A directed acyclic graph of named operators (src/operator/worker.rs:479-596).
+
+    Every node names its inputs. `linearize()` inserts a Split node wherever an output feeds more than one consumer
+    (as the reference's builder does) and orders the nodes by a depth-first topological sort that starts from the
+    loss; the network container then runs them forward in that order and backward in the reverse order.
+    The reference stops at the sorted configuration (its `into_worker` is unimplemented); here the graph runs.
+    """
+
+    def __init__(self):
+        self.nodes = {}          # name -> (cfg, [input names]) in insertion order
+        self.input_name: Optional[str] = None
+        self.loss_name: Optional[str] = None
+
+    def input(self, name: str, cfg: Data3dCfg):
+        self.nodes[name] = (cfg, [])
+        self.input_name = name
+        return self
+
+    def op(self, name: str, cfg: OpCfg, inputs):
+        if name in self.nodes:
+            raise ValueError(f"duplicate operator name {name!r}")
+        self.nodes[name] = (cfg, [inputs] if isinstance(inputs, str) else list(inputs))
+        return self
+
+    def loss(self, name: str, cfg: OpCfg, inp: str):
+        self.op(name, cfg, [inp])
+        self.loss_name = name
+        return self
+
+    def validate(self):
+        if self.input_name is None or self.loss_name is None:
+            raise ValueError("a graph configuration needs an input and a loss operator")
+        for name, (cfg, ins) in self.nodes.items():
+            for i in ins:
+                if i not in self.nodes:
+                    raise ValueError(f"operator {name!r} reads the unknown operator {i!r}")
+            if isinstance(cfg, JoinCfg) and len(ins) != cfg.num_in_arms:
+                raise ValueError(f"join {name!r} expects {cfg.num_in_arms} inputs, has {len(ins)}")
+            if not isinstance(cfg, JoinCfg) and name != self.input_name and len(ins) != 1:
+                raise ValueError(f"operator {name!r} needs exactly one input")
+        return self
+
+    def linearize(self):
+        """[(name, cfg, [producer keys])] in execution order. A producer key is an operator name, or
+        "<split name>:<arm>" for one arm of an inserted Split."""
+        self.validate()
+        consumers = {}
+        for name, (_cfg, ins) in self.nodes.items():
+            for i in ins:
+                consumers.setdefault(i, []).append(name)
+        nodes = {}
+        rename = {}               # (consumer, producer) -> producer key
+        for name, (cfg, ins) in self.nodes.items():
+            nodes[name] = [cfg, list(ins)]
+        for prod, cons in consumers.items():
+            if len(cons) > 1:
+                split = f"{prod}__split"
+                nodes[split] = [SplitCfg(len(cons)), [prod]]
+                for arm, c in enumerate(cons):
+                    rename[(c, prod)] = f"{split}:{arm}"
+        for name, (_cfg, ins) in nodes.items():
+            if not isinstance(_cfg, SplitCfg):
+                nodes[name][1] = [rename.get((name, i), i) for i in ins]
+        order, state = [], {}
+
+        def visit(name):
+            if state.get(name) == 2:
+                return
+            if state.get(name) == 1:
+                raise ValueError(f"the operator graph has a cycle through {name!r}")
+            state[name] = 1
+            for key in nodes[name][1]:
+                visit(key.split(":")[0])
+            state[name] = 2
+            order.append(name)
+
+        visit(self.loss_name)
+        return [(n, nodes[n][0], nodes[n][1]) for n in order]

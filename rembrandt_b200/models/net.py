@@ -41,6 +41,8 @@ def _op_table():
         C.BNormConv2dCfg: R.BNormConv2dOp,
         C.StackResConv2dCfg: R.StackResConv2dOp,
         C.ProjStackResConv2dCfg: R.ProjStackResConv2dOp,
+        C.SplitCfg: O.SplitOp,
+        C.JoinCfg: O.JoinOp,
     }
 
 
@@ -66,19 +68,30 @@ class Net:
         self._flat_allocator = flat_allocator
 
         table = _op_table()
-        named = [cfg.input_op] + list(cfg.hidden_ops) + [cfg.loss_op]
+        if isinstance(cfg, C.GraphOperatorConfig):
+            entries = cfg.linearize()
+        else:
+            named = [cfg.input_op] + list(cfg.hidden_ops) + [cfg.loss_op]
+            entries = [(no.name, no.cfg, [named[i - 1].name] if i else []) for i, no in enumerate(named)]
         self.ops: List[O.Op] = []
-        prev = None
-        for no in named:
-            cls = table.get(type(no.cfg))
-            if isinstance(no.cfg, C.Data3dCfg) and no.cfg.variable_size:
+        produced = {}            # producer key -> operator (or one arm of a split)
+        for name, ocfg, ins in entries:
+            cls = table.get(type(ocfg))
+            if isinstance(ocfg, C.Data3dCfg) and ocfg.variable_size:
                 cls = O.VarDataOp
             if cls is None:
-                raise NotImplementedError(f"no operator for configuration {type(no.cfg).__name__}")
-            op = cls(no.name, no.cfg)
-            op.setup(self, prev)
+                raise NotImplementedError(f"no operator for configuration {type(ocfg).__name__}")
+            op = cls(name, ocfg)
+            op.input_keys = list(ins)
+            prevs = [produced[k] for k in ins]
+            op.setup(self, prevs if isinstance(op, O.JoinOp) else (prevs[0] if prevs else None))
             self.ops.append(op)
-            prev = op
+            produced[name] = op
+            if isinstance(op, O.SplitOp):
+                for arm in op.arms:
+                    produced[arm.name] = arm
+        if not isinstance(self.ops[0], O.DataOp):
+            raise ValueError("the first operator in execution order must be the input operator")
         self.input_op: O.DataOp = self.ops[0]
         self.hidden_ops = self.ops[1:-1]
         self.loss_op: O.SoftmaxKLLossOp = self.ops[-1]
@@ -245,9 +258,15 @@ class Net:
         images, labels, weights = self._cpu_batch
         ctx = torch.enable_grad() if train else torch.no_grad()
         with ctx:
+            vals = {}
             x = images
             for op in self.ops[:-1]:
+                if op.input_keys:
+                    ins = [vals[k.split(":")[0]] for k in op.input_keys]
+                    x = ins if isinstance(op, O.JoinOp) else ins[0]
                 x = op.ref_forward(x, train, t)
+                vals[op.name] = x
+            x = vals[self.loss_op.input_keys[0].split(":")[0]] if self.loss_op.input_keys else x
             loss, correct, am = self.loss_op.ref_loss(x, labels, weights)
         self._cpu_loss = loss if train else None
         self._cpu_stats[0] += float(loss.detach())

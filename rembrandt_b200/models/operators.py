@@ -422,6 +422,83 @@ class VarDataOp(DataOp):
         return torch.stack(outs)
 
 
+# =============================================================================================== graph plumbing
+class _SplitArm:
+    """One arm of a Split as its consumer sees it: the shared activation and a delta buffer of its own."""
+
+    def __init__(self, split, index):
+        self.split, self.index = split, index
+        self.name = f"{split.name}:{index}"
+        self.dout = None
+
+    out = property(lambda self: self.split.prev.out)
+    out_hwc = property(lambda self: self.split.out_hwc)
+    out_cp = property(lambda self: self.split.out_cp)
+    # the consumer masks its delta with the shared activation when the producer ends in a ReLU
+    has_relu = property(lambda self: self.split.prev.has_relu)
+
+
+class SplitOp(Op):
+    """Fan-out: the activation is shared (no copy), the arms' deltas are summed on backward
+    (src/operator/mod.rs:301-384)."""
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        self.out_hwc, self.out_cp = prev.out_hwc, prev.out_cp
+        self.arms = [_SplitArm(self, i) for i in range(self.cfg.num_out_arms)]
+
+    def alloc(self):
+        if self.net.training_capable:
+            for a in self.arms:
+                a.dout = torch.zeros_like(self.prev.out)
+
+    def forward(self, train, t):
+        pass
+
+    def backward(self):
+        if not self.wants_prev_delta():
+            return
+        d = self.prev.dout
+        d.copy_(self.arms[0].dout)
+        for a in self.arms[1:]:
+            K.add_bf16(d, a.dout, d.numel())
+
+    def ref_forward(self, x, train, t):
+        return x
+
+
+class JoinOp(Op):
+    """Fan-in by summation: out = sum of the arms; every arm receives the output's delta."""
+
+    def setup(self, net, prev):
+        prevs = list(prev)
+        Op.setup(self, net, prevs[0])
+        self.prevs = prevs
+        for p in prevs[1:]:
+            if p.out_hwc != prevs[0].out_hwc:
+                raise ValueError(f"join {self.name!r}: arm shapes differ ({p.out_hwc} vs {prevs[0].out_hwc})")
+        self.out_hwc, self.out_cp = prevs[0].out_hwc, prevs[0].out_cp
+
+    def forward(self, train, t):
+        self.out.copy_(self.prevs[0].out)
+        for p in self.prevs[1:]:
+            K.add_bf16(self.out, p.out, self.out.numel())
+
+    def backward(self):
+        for p in self.prevs:
+            if p.dout is None or isinstance(p, DataOp):
+                continue
+            p.dout.copy_(self.dout)
+            if p.has_relu:
+                K.relu_mask(p.dout, p.out, p.dout.numel())
+
+    def ref_forward(self, xs, train, t):
+        out = xs[0]
+        for x in xs[1:]:
+            out = out + x
+        return out
+
+
 # =============================================================================================== conv
 def conv_out(n, k, s, p):
     return (n + 2 * p - k) // s + 1
