@@ -7,19 +7,30 @@
 
 namespace rb {
 
-__global__ void softmax_ce_kernel(const bf16* __restrict__ logits, int B, int K, int ld,
+// Rows are (sample, head) pairs: a sample carries L heads of K logits each, head l at columns [l K, (l+1) K) of its
+// row of `ld` columns (L = 1 is the plain softmax head; L > 1 the k-step look-ahead heads). `mask` (optional,
+// [B L][K] bytes) marks the admissible categories: the others get probability zero and the rest is renormalised
+// (the legal-move masks of the reference's gen-2 softmax head). A head whose label is negative is skipped: zero
+// delta, no loss. Accuracy and arg-max are those of head 0.
+// `soft` (optional, [B L][K] floats) replaces the one-hot target by a distribution q (a teacher's probabilities):
+// delta = w (p - q), loss = -sum_k q_k log p_k; accuracy then compares with the label as before.
+__global__ void softmax_ce_kernel(const bf16* __restrict__ logits, int B, int K, int ld, int L,
                                   const int* __restrict__ labels, const float* __restrict__ weights, float w_scalar,
                                   bf16* __restrict__ delta, float* __restrict__ probs, float* __restrict__ loss_sum,
                                   int* __restrict__ correct, float* __restrict__ loss_per, int* __restrict__ argmax_out,
-                                  const float* __restrict__ cat_weights) {
+                                  const float* __restrict__ cat_weights, const uint8_t* __restrict__ mask,
+                                  const float* __restrict__ soft) {
   const int warps_per_block = blockDim.x >> 5;
-  const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  if (b >= B) return;
-  const bf16* row = logits + (long long)b * ld;
+  if (r >= B * L) return;
+  const int b = r / L, l = r - b * L;
+  const bf16* row = logits + (long long)b * ld + (long long)l * K;
+  const uint8_t* mrow = mask ? mask + (long long)r * K : nullptr;
   float mx = -INFINITY;
   int am = 0;
   for (int k = lane; k < K; k += 32) {
+    if (mrow && !mrow[k]) continue;
     const float v = bf2f(row[k]);
     if (v > mx) { mx = v; am = k; }
   }
@@ -31,33 +42,46 @@ __global__ void softmax_ce_kernel(const bf16* __restrict__ logits, int B, int K,
     if (ov > mx || (ov == mx && oi < am)) { mx = ov; am = oi; }
   }
   float se = 0.f;
-  for (int k = lane; k < K; k += 32) se += __expf(bf2f(row[k]) - mx);
+  for (int k = lane; k < K; k += 32)
+    if (!mrow || mrow[k]) se += __expf(bf2f(row[k]) - mx);
   se = warp_sum(se);
-  const float inv = 1.f / se;
-  const int y = labels[b];
+  const float inv = se > 0.f ? 1.f / se : 0.f;
+  const int y = labels[r];
+  const bool live = soft ? true : (y >= 0 && y < K);
   const float w = weights ? weights[b] : w_scalar;
+  const float* q = soft ? soft + (long long)r * K : nullptr;
+  float soft_loss = 0.f;
+  if (q) {
+    const float lse = mx + __logf(se);
+    for (int k = lane; k < K; k += 32)
+      if ((!mrow || mrow[k]) && q[k] > 0.f) soft_loss -= q[k] * (bf2f(row[k]) - lse);
+    soft_loss = warp_sum(soft_loss);
+  }
   if (delta || probs) {
-    for (int k = lane; k < ld; k += 32) {
+    // the last head also clears the padding columns behind the heads
+    const int kend = (l == L - 1) ? ld - l * K : K;
+    for (int k = lane; k < kend; k += 32) {
       float pk = 0.f;
-      if (k < K) pk = __expf(bf2f(row[k]) - mx) * inv;
-      if (probs && k < K) probs[(long long)b * K + k] = pk;
+      if (k < K && (!mrow || mrow[k])) pk = __expf(bf2f(row[k]) - mx) * inv;
+      if (probs && k < K) probs[(long long)r * K + k] = pk;
       if (delta) {
         float d = 0.f;
-        if (k < K) {
-          d = w * (pk - (k == y ? 1.f : 0.f));
+        if (k < K && live) {
+          d = w * (pk - (q ? q[k] : (k == y ? 1.f : 0.f)));
           if (cat_weights) d *= cat_weights[k];
         }
-        delta[(long long)b * ld + k] = f2bf(d);
+        delta[(long long)b * ld + (long long)l * K + k] = f2bf(d);
       }
     }
   }
   if (lane == 0) {
-    float l = 0.f;
-    if (y >= 0 && y < K) l = -(bf2f(row[y]) - mx - __logf(se));
-    if (loss_per) loss_per[b] = l;
-    if (argmax_out) argmax_out[b] = am;
-    if (loss_sum) atomicAdd(loss_sum, w * l);
-    if (correct && am == y) atomicAdd(correct, 1);
+    float lo = 0.f;
+    if (q) lo = soft_loss;
+    else if (live) lo = -(bf2f(row[y]) - mx - __logf(se));
+    if (loss_per) loss_per[r] = lo;
+    if (argmax_out && l == 0) argmax_out[b] = am;
+    if (loss_sum && live) atomicAdd(loss_sum, w * lo);
+    if (correct && l == 0 && am == y) atomicAdd(correct, 1);
   }
 }
 
@@ -67,13 +91,14 @@ using namespace rb;
 
 extern "C" {
 
-int rb_softmax_ce(const void* logits, int B, int K, int ld, const int* labels, const float* weights, float w_scalar,
-                  void* delta, float* probs, float* loss_sum, int* correct, float* loss_per, int* argmax_out,
-                  const float* cat_weights, cudaStream_t st) {
+int rb_softmax_ce(const void* logits, int B, int K, int ld, int L, const int* labels, const float* weights,
+                  float w_scalar, void* delta, float* probs, float* loss_sum, int* correct, float* loss_per,
+                  int* argmax_out, const float* cat_weights, const void* mask, const float* soft, cudaStream_t st) {
+  if (L < 1 || (long long)L * K > ld) return -10;
   const int wpb = 4;
-  softmax_ce_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>((const bf16*)logits, B, K, ld, labels, weights, w_scalar,
-                                                             (bf16*)delta, probs, loss_sum, correct, loss_per,
-                                                             argmax_out, cat_weights);
+  softmax_ce_kernel<<<(B * L + wpb - 1) / wpb, wpb * 32, 0, st>>>(
+      (const bf16*)logits, B, K, ld, L, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, loss_per,
+      argmax_out, cat_weights, (const uint8_t*)mask, soft);
   return RB_LAUNCH_OK();
 }
 

@@ -145,12 +145,13 @@ __global__ void __launch_bounds__(256) var_input_kernel(const __grid_constant__ 
 
 using namespace rb;
 
-extern "C" int rb_var_input_u8(const void* src, const int* shapes, void* dst, int* draws, long long in_stride, int N,
-                               int C, int crop_h, int crop_w, int Cp, int f, int ep, int OH, int OW, int scale_lower,
-                               int scale_upper, int train, int random_flip, int per_batch, float scale,
-                               const float* mean, float pca_sigma, const float* pca_vals, const float* pca_vecs,
-                               unsigned long long seed, unsigned int step, const unsigned int* step_ptr,
-                               cudaStream_t st) {
+extern "C" {
+
+int rb_var_input_u8(const void* src, const int* shapes, void* dst, int* draws, long long in_stride, int N, int C,
+                    int crop_h, int crop_w, int Cp, int f, int ep, int OH, int OW, int scale_lower, int scale_upper,
+                    int train, int random_flip, int per_batch, float scale, const float* mean, float pca_sigma,
+                    const float* pca_vals, const float* pca_vecs, unsigned long long seed, unsigned int step,
+                    const unsigned int* step_ptr, cudaStream_t st) {
   if (C < 1 || C > 4 || Cp < C || f < 1 || (scale_lower > 0 && scale_upper < scale_lower)) return -10;
   if (f > 1 && f * f * C > Cp) return -10;
   VarInputArgs a;
@@ -169,3 +170,5 @@ extern "C" int rb_var_input_u8(const void* src, const int* shapes, void* dst, in
   var_input_kernel<<<(int)blocks, 256, 0, st>>>(a);
   return RB_LAUNCH_OK();
 }
+
+}  // extern "C"

@@ -203,6 +203,13 @@ class SoftmaxKLLossCfg:
 
 
 @dataclass
+class MultiSoftmaxKLLossCfg:
+    """`num_heads` softmax heads of `num_categories` each (look-ahead targets, src/layer_new.rs:2969-3118)."""
+    num_categories: int
+    num_heads: int = 1
+
+
+@dataclass
 class MarginalizedSoftmaxIndLossCfg:
     num_categories: int
 
@@ -289,6 +296,10 @@ class SequentialOperatorConfig:
         return self
 
     def marginalized_softmax_ind_loss(self, cfg: MarginalizedSoftmaxIndLossCfg, name="loss"):
+        self.loss_op = NamedOp(name, cfg)
+        return self
+
+    def multi_softmax_kl_loss(self, cfg: "MultiSoftmaxKLLossCfg", name="loss"):
         self.loss_op = NamedOp(name, cfg)
         return self
 

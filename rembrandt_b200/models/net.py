@@ -38,6 +38,7 @@ def _op_table():
         C.DropoutCfg: O.DropoutOp,
         C.SoftmaxKLLossCfg: O.SoftmaxKLLossOp,
         C.MarginalizedSoftmaxIndLossCfg: O.MarginalizedSoftmaxIndLossOp,
+        C.MultiSoftmaxKLLossCfg: O.MultiSoftmaxKLLossOp,
         C.BNormConv2dCfg: R.BNormConv2dOp,
         C.StackResConv2dCfg: R.StackResConv2dOp,
         C.ProjStackResConv2dCfg: R.ProjStackResConv2dOp,

@@ -862,27 +862,37 @@ class DropoutOp(Op):
 
 # =============================================================================================== loss
 class SoftmaxKLLossOp(Op):
-    """Softmax + cross-entropy head with per-sample weights (src/operator/loss.rs:20-262)."""
+    """Softmax + cross-entropy head with per-sample weights (src/operator/loss.rs:20-262).
+
+    Optional admissibility masks (`load_mask`): categories whose mask byte is zero get probability zero and the rest
+    is renormalised, as the gen-2 head does for legal moves (src/layer_new.rs:2057-2096).
+    """
+
+    heads = 1
 
     def setup(self, net, prev):
         super().setup(net, prev)
         self.k = self.cfg.num_categories
+        self.heads = int(getattr(self.cfg, "num_heads", 1))
         h, w, c = prev.out_hwc
-        if h * w * c != self.k:
-            raise ValueError(f"loss expects {self.k} inputs, previous operator produces {h * w * c}")
+        if h * w * c != self.k * self.heads:
+            raise ValueError(f"loss expects {self.k * self.heads} inputs, previous operator produces {h * w * c}")
         self.out_hwc = prev.out_hwc
         self.out_cp = prev.out_cp
         self.cat_weights = None
+        self.mask = None
+        self._cpu_mask = None
+        self.soft = None          # target distributions (distillation), [B * heads, K] float32
 
     def alloc(self):
         dev = self.net.device
         n = self.net.batch
-        self.labels = torch.zeros(n, dtype=torch.int32, device=dev)
+        self.labels = torch.zeros(n * self.heads, dtype=torch.int32, device=dev)
         self.weights = None
         self.loss_sum = torch.zeros(1, dtype=torch.float32, device=dev)
         self.correct = torch.zeros(1, dtype=torch.int32, device=dev)
         self.argmax = torch.zeros(n, dtype=torch.int32, device=dev)
-        self.loss_per = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.loss_per = torch.zeros(n * self.heads, dtype=torch.float32, device=dev)
         self.probs = None
 
     def load_labels(self, labels, non_blocking=True):
@@ -893,20 +903,77 @@ class SoftmaxKLLossOp(Op):
             self.weights = torch.zeros(self.net.batch, dtype=torch.float32, device=self.net.device)
         self.weights.copy_(weights)
 
+    def load_mask(self, mask):
+        """mask: [B, K] (or [B, heads, K]), non-zero = admissible; None removes the mask."""
+        if mask is None:
+            self.mask = self._cpu_mask = None
+            return
+        m = (torch.as_tensor(mask) != 0).reshape(self.net.batch * self.heads, self.k)
+        if self.net.is_cuda:
+            if self.mask is None:
+                self.mask = torch.zeros(m.shape, dtype=torch.uint8, device=self.net.device)
+            self.mask.copy_(m.to(torch.uint8))
+        else:
+            self._cpu_mask = m
+
+    def enable_probs(self):
+        """Keep the softmax probabilities of every forward pass (a teacher network's output)."""
+        if self.net.is_cuda and self.probs is None:
+            self.probs = torch.zeros((self.net.batch * self.heads, self.k), dtype=torch.float32,
+                                     device=self.net.device)
+        self.keep_probs = True
+
+    def load_soft_targets(self, q):
+        """q: [B * heads, K] distribution that replaces the one-hot labels; None returns to hard labels."""
+        if q is None:
+            self.soft = None
+            return
+        q = q.reshape(self.net.batch * self.heads, self.k).float()
+        if self.net.is_cuda:
+            # a persistent buffer: captured graphs keep reading the same address
+            if self.soft is None:
+                self.soft = torch.zeros_like(q, device=self.net.device)
+            self.soft.copy_(q, non_blocking=True)
+        else:
+            self.soft = q
+
     def forward(self, train, t):
         delta = self.prev.dout if (train and self.prev.dout is not None) else None
         K.softmax_ce(self.prev.out, self.net.batch, self.k, self.out_cp, self.labels, self.weights,
                      self.net.sample_weight, delta, probs=self.probs, loss_sum=self.loss_sum, correct=self.correct,
-                     loss_per=self.loss_per, argmax_out=self.argmax, cat_weights=self.cat_weights)
+                     loss_per=self.loss_per, argmax_out=self.argmax, cat_weights=self.cat_weights, mask=self.mask,
+                     heads=self.heads, soft=self.soft)
 
     def ref_loss(self, logits, labels, weights=None):
         """Returns (weighted loss sum, number correct, argmax)."""
-        logits = logits.flatten(1)
+        n = logits.shape[0]
+        logits = logits.flatten(1).reshape(n * self.heads, self.k)
+        if self._cpu_mask is not None:
+            logits = logits.masked_fill(~self._cpu_mask, float("-inf"))
+        labels = labels.long().reshape(-1)
+        live = (labels >= 0) & (labels < self.k)
         lp = F.log_softmax(logits, dim=1)
-        nll = -lp.gather(1, labels.long().reshape(-1, 1)).squeeze(1)
-        w = weights if weights is not None else torch.full_like(nll, self.net.sample_weight)
-        am = logits.argmax(1)
-        return (w * nll).sum(), int((am == labels.long()).sum()), am
+        if getattr(self, "keep_probs", False):
+            self.probs = lp.detach().exp()
+        if self.soft is not None:
+            q = self.soft.to(lp.device)
+            nll = -(torch.where(q > 0, q * lp, torch.zeros_like(lp))).sum(1)
+        else:
+            nll = -lp.gather(1, labels.clamp(0, self.k - 1).reshape(-1, 1)).squeeze(1)
+            nll = torch.where(live, nll, torch.zeros_like(nll))
+        if weights is not None:
+            w = weights.reshape(-1, 1).expand(n, self.heads).reshape(-1)
+        else:
+            w = torch.full_like(nll, self.net.sample_weight)
+        am = logits.reshape(n, self.heads, self.k)[:, 0].argmax(1)
+        first = labels.reshape(n, self.heads)[:, 0]
+        return (w * nll).sum(), int((am == first).sum()), am
+
+
+class MultiSoftmaxKLLossOp(SoftmaxKLLossOp):
+    """k-step look-ahead heads: `num_heads` blocks of `num_categories` logits per sample, one label per head
+    (negative = no target for that step); the loss is the sum over heads, accuracy is that of the first head
+    (src/layer_new.rs:2969-3118)."""
 
 
 class MarginalizedSoftmaxIndLossOp(SoftmaxKLLossOp):

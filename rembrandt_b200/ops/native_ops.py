@@ -139,10 +139,14 @@ def lrn_bwd(x, dy, dx, mask_src, pixels, C, size, alpha_eff, beta, k):
 
 
 def softmax_ce(logits, B, K, ld, labels, weights, w_scalar, delta, probs=None, loss_sum=None, correct=None,
-               loss_per=None, argmax_out=None, cat_weights=None):
-    check(_native.cuda().rb_softmax_ce(ptr(logits), B, K, ld, ptr(labels), ptr(weights), float(w_scalar), ptr(delta),
-                                       ptr(probs), ptr(loss_sum), ptr(correct), ptr(loss_per), ptr(argmax_out),
-                                       ptr(cat_weights), stream_handle()), "rb_softmax_ce")
+               loss_per=None, argmax_out=None, cat_weights=None, mask=None, heads=1, soft=None):
+    """`heads` > 1: every sample carries that many blocks of K logits (labels [B, heads], negative = skip).
+    `mask`: uint8 [B * heads, K], zero marks a category that must get probability zero.
+    `soft`: float32 [B * heads, K] target distribution that replaces the one-hot label (distillation)."""
+    check(_native.cuda().rb_softmax_ce(ptr(logits), B, K, ld, int(heads), ptr(labels), ptr(weights), float(w_scalar),
+                                       ptr(delta), ptr(probs), ptr(loss_sum), ptr(correct), ptr(loss_per),
+                                       ptr(argmax_out), ptr(cat_weights), ptr(mask), ptr(soft), stream_handle()),
+          "rb_softmax_ce")
 
 
 def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):

@@ -116,6 +116,9 @@ class SgdOpt:
         if self.rank == 0 and not self.quiet:
             print(msg, file=sys.stderr, flush=True)
 
+    def before_step(self, images, labels):
+        """Hook run before every batch is fed (used by the distillation optimizer)."""
+
     # ------------------------------------------------------------------ training
     def train(self, train_data: Iterable, valid_data: Optional[Iterable] = None, max_iters: Optional[int] = None):
         cfg, eng, net, comm = self.cfg, self.engine, self.net, self.comm
@@ -147,6 +150,7 @@ class SgdOpt:
         while not done:
             for images, labels in train_data:
                 it_before = eng.iter
+                self.before_step(images, labels)
                 eng.feed(images, labels)
                 stats = eng.step()
                 if self.rank in self.experiment.straggler_ranks and self.experiment.straggler_max_delay_ms > 0:

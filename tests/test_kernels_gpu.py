@@ -333,6 +333,40 @@ def test_softmax_ce():
     assert correct.item() == int((logits.argmax(1) == labels.long()).sum())
 
 
+def test_softmax_ce_masks_and_lookahead_heads():
+    torch.manual_seed(13)
+    B, Kc, L = 9, 361, 3
+    ld = K.pad_channels(Kc * L)
+    logits = bf(torch.randn(B, L, Kc, device=DEV) * 2)
+    li = torch.zeros(B, ld, device=DEV, dtype=torch.bfloat16)
+    li[:, :Kc * L] = logits.reshape(B, -1).bfloat16()
+    mask = (torch.rand(B, L, Kc, device=DEV) > 0.3)
+    labels = torch.randint(0, Kc, (B, L), device=DEV)
+    mask.scatter_(2, labels.unsqueeze(-1), True)          # a target is always admissible
+    labels[2, 1] = -1                                      # a head without a target
+    labels[5, 2] = -1
+    w = 0.25
+    delta = torch.full((B, ld), float("nan"), device=DEV, dtype=torch.bfloat16)
+    loss = torch.zeros(1, device=DEV)
+    correct = torch.zeros(1, device=DEV, dtype=torch.int32)
+    am = torch.zeros(B, device=DEV, dtype=torch.int32)
+    K.softmax_ce(li, B, Kc, ld, labels.int().contiguous(), None, w, delta, loss_sum=loss, correct=correct,
+                 argmax_out=am, mask=mask.to(torch.uint8).contiguous(), heads=L)
+    lr = logits.clone().requires_grad_()
+    masked = lr.masked_fill(~mask, float("-inf")).reshape(B * L, Kc)
+    live = labels.reshape(-1) >= 0
+    nll = F.cross_entropy(masked, labels.reshape(-1).clamp_min(0), reduction="none")
+    ref_loss = (nll * live).sum() * w
+    ref_delta = torch.autograd.grad(ref_loss, lr)[0].reshape(B, L * Kc)
+    assert abs(loss.item() - ref_loss.item()) < 2e-3 * max(1.0, abs(ref_loss.item()))
+    close(delta[:, :Kc * L], ref_delta, atol=2e-3)
+    assert (delta[:, Kc * L:].float() == 0).all()
+    assert (delta[:, :Kc * L].float().reshape(B, L, Kc)[~mask] == 0).all()
+    first = masked.reshape(B, L, Kc)[:, 0].argmax(1)
+    assert torch.equal(am.long(), first)
+    assert correct.item() == int((first == labels[:, 0]).sum())
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 5])
 def test_sgd_fused_rules(mode):
     from rembrandt_b200.optim.sgd import reference_step

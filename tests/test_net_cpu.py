@@ -180,3 +180,32 @@ def test_reshape_conv_out_channels():
     assert recs[0][1] == (25, 12) and recs[1][1] == (1, 12)
     assert np.array_equal(recs[0][0], full[0][0][: 25 * 12])
     assert recs[2][1] == full[2][1]
+
+
+def test_masked_and_multi_head_softmax_reference_path():
+    """Admissibility masks renormalise over the allowed categories; look-ahead heads sum their losses."""
+    import torch.nn.functional as F
+    from rembrandt_b200.models import config as C
+    from rembrandt_b200.models.net import Net
+    cfg = C.SequentialOperatorConfig().data3d(C.Data3dCfg((4, 4, 2)))
+    cfg.affine(C.AffineCfg(12)).multi_softmax_kl_loss(C.MultiSoftmaxKLLossCfg(6, 2))
+    net = Net(cfg, 3, device="cpu")
+    x = torch.randint(0, 256, (3, 2, 4, 4), dtype=torch.uint8)
+    labels = torch.tensor([[1, 2], [0, -1], [5, 3]])
+    mask = torch.ones(3, 2, 6, dtype=torch.bool)
+    mask[0, 0, 4] = False
+    mask[2, 1, 0] = False
+    net.loss_op.load_mask(mask)
+    net.load_batch(x, labels)
+    net.forward(True)
+    net.backward()
+    loss, correct = net.read_stats()
+    logits = net._cpu_logits.reshape(3, 2, 6).masked_fill(~mask, float("-inf"))
+    want = 0.0
+    for b in range(3):
+        for l in range(2):
+            if labels[b, l] >= 0:
+                want += float(F.cross_entropy(logits[b, l][None], labels[b, l][None])) / 3
+    assert abs(loss - want) < 1e-4 * max(1.0, abs(want))
+    assert correct == int((logits[:, 0].argmax(1) == labels[:, 0]).sum())
+    assert torch.isfinite(net.grads).all()

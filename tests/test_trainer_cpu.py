@@ -157,3 +157,41 @@ def test_nesterov_prelookahead_and_report_hook():
     rep = Rep()
     SgdOpt(opt, eng, report=rep, quiet=True).train(mnist_shape_batches(6, 16, 6), None, max_iters=6)
     assert rep.t == [2, 4, 6]
+
+
+def test_mimic_training_pulls_student_towards_teacher():
+    """Distillation: the student's output distribution approaches the teacher's on the training batch."""
+    import torch.nn.functional as F
+    from rembrandt_b200.api import default_opt
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.mimic import MimicSgdOpt
+    from rembrandt_b200.parallel.comm import NullComm
+    teacher = Net(zoo.mnist_fc1(), 16, device="cpu", seed=(11, 12), training=False)
+    student = Net(zoo.mnist_fc1(), 16, device="cpu", seed=(21, 22))
+    torch.manual_seed(0)
+    x = torch.randint(0, 256, (16, 1, 28, 28), dtype=torch.uint8)
+    y = torch.randint(0, 10, (16,))
+
+    def kl():
+        outs = []
+        for n in (teacher, student):
+            n.load_batch(x, y)
+            with torch.no_grad():
+                n.forward(False)
+            n.read_stats()
+            outs.append(F.log_softmax(n._cpu_logits.flatten(1), 1))
+        return float((outs[0].exp() * (outs[0] - outs[1])).sum(1).mean())
+
+    before = kl()
+    cfg = default_opt(16, "null")
+    cfg.max_iters = 60
+    cfg.display_iters = 0
+    cfg.checkpoint_iters = 0
+    eng = StepEngine(student, cfg, NullComm(), use_graph=False)
+    eng.set_lr(0.1)
+    opt = MimicSgdOpt(cfg, eng, teacher, quiet=True)
+    opt.train([(x, y)] * 60, max_iters=60)
+    after = kl()
+    assert after < 0.5 * before, (before, after)
