@@ -49,6 +49,7 @@ _CUDA_SIGS = {
     "rb_pack_dgrad_filters": [vp, vp, i32, i32, i32, i32, vp],
     "rb_zero_s2d_structural": [vp, i32, i32, i32, i32, i32, i32, vp],
     # softmax_ce.cu
+    "rb_pointwise_loss": [vp, i32, i32, i32, vp, vp, f32, vp, vp, vp, i32, vp],
     "rb_softmax_ce": [vp, i32, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     # sgd_fused.cu
     "rb_sgd_fused": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, vp],

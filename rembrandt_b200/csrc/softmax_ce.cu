@@ -85,6 +85,47 @@ __global__ void softmax_ce_kernel(const bf16* __restrict__ logits, int B, int K,
   }
 }
 
+// Element-wise regression / binary heads on [B][K] outputs with float targets [B][K]:
+//   mode 0  logistic:  p = sigmoid(x), loss = -(t log p + (1-t) log(1-p)), delta = w (p - t); "correct" counts
+//           samples whose first output lies on the target's side of 0.5
+//   mode 1  L2:        loss = 0.5 (x - t)^2, delta = w (x - t)
+// (the gen-2 logistic indicator head, src/layer_new.rs, and the gen-1 L2LossLayer, src/layer.rs).
+__global__ void pointwise_loss_kernel(const bf16* __restrict__ x, int B, int K, int ld, const float* __restrict__ target,
+                                      const float* __restrict__ weights, float w_scalar, bf16* __restrict__ delta,
+                                      float* __restrict__ loss_sum, int* __restrict__ correct, int mode) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  const float w = weights ? weights[b] : w_scalar;
+  float loss = 0.f;
+  for (int k = lane; k < ld; k += 32) {
+    float d = 0.f;
+    if (k < K) {
+      const float v = bf2f(x[(long long)b * ld + k]), t = target[(long long)b * K + k];
+      if (mode == 0) {
+        // log(1 + exp(-|v|)) form keeps both logs finite
+        const float sp = __logf(1.f + __expf(-fabsf(v)));
+        const float log_p = (v >= 0.f ? 0.f : v) - sp, log_q = (v >= 0.f ? -v : 0.f) - sp;
+        loss -= t * log_p + (1.f - t) * log_q;
+        d = w * (1.f / (1.f + __expf(-v)) - t);
+      } else {
+        loss += 0.5f * (v - t) * (v - t);
+        d = w * (v - t);
+      }
+    }
+    if (delta) delta[(long long)b * ld + k] = f2bf(d);
+  }
+  loss = warp_sum(loss);
+  if (lane == 0) {
+    if (loss_sum) atomicAdd(loss_sum, w * loss);
+    if (correct && mode == 0) {
+      const float v = bf2f(x[(long long)b * ld]), t = target[(long long)b * K];
+      if ((v > 0.f) == (t > 0.5f)) atomicAdd(correct, 1);
+    }
+  }
+}
+
 }  // namespace rb
 
 using namespace rb;
@@ -99,6 +140,15 @@ int rb_softmax_ce(const void* logits, int B, int K, int ld, int L, const int* la
   softmax_ce_kernel<<<(B * L + wpb - 1) / wpb, wpb * 32, 0, st>>>(
       (const bf16*)logits, B, K, ld, L, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, loss_per,
       argmax_out, cat_weights, (const uint8_t*)mask, soft);
+  return RB_LAUNCH_OK();
+}
+
+int rb_pointwise_loss(const void* x, int B, int K, int ld, const float* target, const float* weights, float w_scalar,
+                      void* delta, float* loss_sum, int* correct, int mode, cudaStream_t st) {
+  if (mode < 0 || mode > 1 || K > ld) return -10;
+  const int wpb = 4;
+  pointwise_loss_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>((const bf16*)x, B, K, ld, target, weights, w_scalar,
+                                                                 (bf16*)delta, loss_sum, correct, mode);
   return RB_LAUNCH_OK();
 }
 

@@ -203,6 +203,13 @@ class SoftmaxKLLossCfg:
 
 
 @dataclass
+class PointwiseLossCfg:
+    """Logistic (binary cross-entropy on logits) or L2 head over `num_outputs` outputs with float targets."""
+    num_outputs: int = 1
+    kind: str = "logistic"       # "logistic" | "l2"
+
+
+@dataclass
 class MultiSoftmaxKLLossCfg:
     """`num_heads` softmax heads of `num_categories` each (look-ahead targets, src/layer_new.rs:2969-3118)."""
     num_categories: int
@@ -296,6 +303,10 @@ class SequentialOperatorConfig:
         return self
 
     def marginalized_softmax_ind_loss(self, cfg: MarginalizedSoftmaxIndLossCfg, name="loss"):
+        self.loss_op = NamedOp(name, cfg)
+        return self
+
+    def pointwise_loss(self, cfg: "PointwiseLossCfg", name="loss"):
         self.loss_op = NamedOp(name, cfg)
         return self
 

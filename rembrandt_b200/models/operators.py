@@ -976,6 +976,48 @@ class MultiSoftmaxKLLossOp(SoftmaxKLLossOp):
     (src/layer_new.rs:2969-3118)."""
 
 
+class PointwiseLossOp(SoftmaxKLLossOp):
+    """Heads that compare every output with a float target: logistic (binary cross-entropy on the logit; the gen-2
+    LogisticIndicatorLossLayer, src/layer_new.rs) and L2 (the gen-1 L2LossLayer, src/layer.rs). Targets are loaded
+    with `load_labels` as [B, K] floats (a [B] integer tensor is taken as K = 1 binary labels)."""
+
+    def setup(self, net, prev):
+        Op.setup(self, net, prev)
+        self.k = self.cfg.num_outputs
+        self.heads = 1
+        self.mode = {"logistic": 0, "l2": 1}[self.cfg.kind]
+        h, w, c = prev.out_hwc
+        if h * w * c != self.k:
+            raise ValueError(f"loss expects {self.k} inputs, previous operator produces {h * w * c}")
+        self.out_hwc, self.out_cp = prev.out_hwc, prev.out_cp
+        self.cat_weights = self.mask = self._cpu_mask = self.soft = None
+
+    def alloc(self):
+        super().alloc()
+        self.targets = torch.zeros((self.net.batch, self.k), dtype=torch.float32, device=self.net.device)
+
+    def load_labels(self, labels, non_blocking=True):
+        self.targets.copy_(labels.reshape(self.net.batch, self.k).float(), non_blocking=non_blocking)
+
+    def forward(self, train, t):
+        delta = self.prev.dout if (train and self.prev.dout is not None) else None
+        K.pointwise_loss(self.prev.out, self.net.batch, self.k, self.out_cp, self.targets, self.weights,
+                         self.net.sample_weight, delta, loss_sum=self.loss_sum, correct=self.correct, mode=self.mode)
+
+    def ref_loss(self, logits, labels, weights=None):
+        n = logits.shape[0]
+        x = logits.flatten(1)
+        t = labels.reshape(n, self.k).float()
+        if self.mode == 0:
+            per = F.binary_cross_entropy_with_logits(x, t, reduction="none").sum(1)
+            correct = int(((x[:, 0] > 0) == (t[:, 0] > 0.5)).sum())
+        else:
+            per = 0.5 * ((x - t) ** 2).sum(1)
+            correct = 0
+        w = weights if weights is not None else torch.full_like(per, self.net.sample_weight)
+        return (w * per).sum(), correct, (x[:, 0] > 0).long()
+
+
 class MarginalizedSoftmaxIndLossOp(SoftmaxKLLossOp):
     """Softmax head whose gradient is weighted per category (src/operator/loss.rs:264-407)."""
 

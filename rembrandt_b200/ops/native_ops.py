@@ -149,6 +149,13 @@ def softmax_ce(logits, B, K, ld, labels, weights, w_scalar, delta, probs=None, l
           "rb_softmax_ce")
 
 
+def pointwise_loss(x, B, K, ld, target, weights, w_scalar, delta, loss_sum=None, correct=None, mode=0):
+    """mode 0: logistic (binary cross-entropy on logits), mode 1: L2; targets float32 [B, K]."""
+    check(_native.cuda().rb_pointwise_loss(ptr(x), B, K, ld, ptr(target), ptr(weights), float(w_scalar), ptr(delta),
+                                           ptr(loss_sum), ptr(correct), int(mode), stream_handle()),
+          "rb_pointwise_loss")
+
+
 def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
     check(_native.cuda().rb_sgd_fused(ptr(w), ptr(g), ptr(v), ptr(w16), n, lr, mu, l2, grad_scale, mode, phase,
                                       stream_handle()), "rb_sgd_fused")

@@ -367,6 +367,33 @@ def test_softmax_ce_masks_and_lookahead_heads():
     assert correct.item() == int((first == labels[:, 0]).sum())
 
 
+@pytest.mark.parametrize("mode", [0, 1])
+def test_pointwise_loss(mode):
+    torch.manual_seed(14)
+    B, Kc = 21, 5
+    ld = K.pad_channels(Kc)
+    x = bf(torch.randn(B, Kc, device=DEV) * 4)
+    xi = torch.zeros(B, ld, device=DEV, dtype=torch.bfloat16)
+    xi[:, :Kc] = x.bfloat16()
+    t = (torch.rand(B, Kc, device=DEV) > 0.5).float() if mode == 0 else torch.randn(B, Kc, device=DEV)
+    w = 0.125
+    delta = torch.full((B, ld), float("nan"), device=DEV, dtype=torch.bfloat16)
+    loss = torch.zeros(1, device=DEV)
+    correct = torch.zeros(1, device=DEV, dtype=torch.int32)
+    K.pointwise_loss(xi, B, Kc, ld, t, None, w, delta, loss_sum=loss, correct=correct, mode=mode)
+    xr = x.clone().requires_grad_()
+    if mode == 0:
+        ref = F.binary_cross_entropy_with_logits(xr, t, reduction="sum") * w
+    else:
+        ref = 0.5 * ((xr - t) ** 2).sum() * w
+    ref_delta = torch.autograd.grad(ref, xr)[0]
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
+    close(delta[:, :Kc], ref_delta, atol=2e-3, rtol=1e-2)
+    assert (delta[:, Kc:].float() == 0).all()
+    if mode == 0:
+        assert correct.item() == int(((x[:, 0] > 0) == (t[:, 0] > 0.5)).sum())
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 5])
 def test_sgd_fused_rules(mode):
     from rembrandt_b200.optim.sgd import reference_step

@@ -209,3 +209,25 @@ def test_masked_and_multi_head_softmax_reference_path():
     assert abs(loss - want) < 1e-4 * max(1.0, abs(want))
     assert correct == int((logits[:, 0].argmax(1) == labels[:, 0]).sum())
     assert torch.isfinite(net.grads).all()
+
+
+@pytest.mark.parametrize("kind", ["logistic", "l2"])
+def test_pointwise_heads_reference_path(kind):
+    from rembrandt_b200.models import config as C
+    from rembrandt_b200.models.net import Net
+    cfg = C.SequentialOperatorConfig().data3d(C.Data3dCfg((4, 4, 2)))
+    cfg.affine(C.AffineCfg(3)).pointwise_loss(C.PointwiseLossCfg(3, kind))
+    net = Net(cfg, 5, device="cpu")
+    x = torch.randint(0, 256, (5, 2, 4, 4), dtype=torch.uint8)
+    t = (torch.rand(5, 3) > 0.5).float() if kind == "logistic" else torch.randn(5, 3)
+    net.load_batch(x, t)
+    net.forward(True)
+    net.backward()
+    loss, _ = net.read_stats()
+    z = net._cpu_logits.flatten(1)
+    if kind == "logistic":
+        want = torch.nn.functional.binary_cross_entropy_with_logits(z, t, reduction="sum") / 5
+    else:
+        want = 0.5 * ((z - t) ** 2).sum() / 5
+    assert abs(loss - float(want)) < 1e-4 * max(1.0, abs(float(want)))
+    assert float(net.grads.abs().sum()) > 0
