@@ -343,6 +343,7 @@ def test_softmax_ce_masks_and_lookahead_heads():
     mask = (torch.rand(B, L, Kc, device=DEV) > 0.3)
     labels = torch.randint(0, Kc, (B, L), device=DEV)
     mask.scatter_(2, labels.unsqueeze(-1), True)          # a target is always admissible
+    mask[:, :, 0] = True                                  # so is the stand-in index of a skipped head
     labels[2, 1] = -1                                      # a head without a target
     labels[5, 2] = -1
     w = 0.25
@@ -356,7 +357,7 @@ def test_softmax_ce_masks_and_lookahead_heads():
     masked = lr.masked_fill(~mask, float("-inf")).reshape(B * L, Kc)
     live = labels.reshape(-1) >= 0
     nll = F.cross_entropy(masked, labels.reshape(-1).clamp_min(0), reduction="none")
-    ref_loss = (nll * live).sum() * w
+    ref_loss = torch.where(live, nll, torch.zeros_like(nll)).sum() * w
     ref_delta = torch.autograd.grad(ref_loss, lr)[0].reshape(B, L * Kc)
     assert abs(loss.item() - ref_loss.item()) < 2e-3 * max(1.0, abs(ref_loss.item()))
     close(delta[:, :Kc * L], ref_delta, atol=2e-3)
