@@ -53,6 +53,7 @@ _CUDA_SIGS = {
     "rb_softmax_ce": [vp, i32, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     # sgd_fused.cu
     "rb_sgd_fused": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, vp],
+    "rb_sgd_fused_grid": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, i32, i32, vp],
     "rb_axpy_shadow": [vp, vp, vp, i64, f32, vp],
     "rb_axpby": [vp, vp, i64, f32, f32, vp],
     # input_pipeline.cu

@@ -87,6 +87,21 @@ int rb_sgd_fused(float* w, float* g, float* v, void* w16, long long n, float lr,
   return RB_LAUNCH_OK();
 }
 
+// Same kernel with a caller-chosen grid: blocks of 128 threads fit on an SM next to a resident GEMM CTA, which lets
+// the update of a finished gradient bucket run on a second stream while backward continues.
+int rb_sgd_fused_grid(float* w, float* g, float* v, void* w16, long long n, float lr, float mu, float l2,
+                      float grad_scale, int mode, int phase, int blocks, int threads, cudaStream_t st) {
+  if (n <= 0) return 0;
+  if (blocks < 1 || threads < 32 || threads > 1024 || (threads & 31)) return -10;
+  SgdArgs a;
+  a.lr = lr; a.mu = mu; a.l2 = l2; a.grad_scale = grad_scale; a.mode = mode; a.phase = phase;
+  a.w = w; a.g = g; a.v = v; a.w16 = (bf16*)w16; a.n = n;
+  const long long need = (n / 4 + threads - 1) / threads;
+  if (need < blocks) blocks = need < 1 ? 1 : (int)need;
+  sgd_fused_kernel<<<blocks, threads, 0, st>>>(a);
+  return RB_LAUNCH_OK();
+}
+
 int rb_axpy_shadow(float* w, const float* v, void* w16, long long n, float s, cudaStream_t st) {
   if (n <= 0) return 0;
   long long blocks = (n + 255) / 256;

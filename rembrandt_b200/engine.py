@@ -123,7 +123,7 @@ class StepEngine:
 
     def _overlapped(self) -> bool:
         o, c = self.opt, self.comm
-        return (c.num_workers() > 1 and hasattr(c, "on_op_backward") and
+        return ((c.num_workers() > 1 or getattr(c, "overlap_single", False)) and hasattr(c, "on_op_backward") and
                 o.sync_order == SyncOrder.SYNC_GRADS_THEN_STEP and max(1, o.comm_interval) == 1)
 
     def _graph_safe_update(self) -> bool:

@@ -161,6 +161,12 @@ def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
                                       stream_handle()), "rb_sgd_fused")
 
 
+def sgd_fused_grid(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7, blocks=296, threads=128):
+    """The fused SGD sweep with an explicit grid (small blocks that co-reside with the GEMM CTAs)."""
+    check(_native.cuda().rb_sgd_fused_grid(ptr(w), ptr(g), ptr(v), ptr(w16), n, lr, mu, l2, grad_scale, mode, phase,
+                                           int(blocks), int(threads), stream_handle()), "rb_sgd_fused_grid")
+
+
 def axpy_shadow(w, v, w16, n, s):
     check(_native.cuda().rb_axpy_shadow(ptr(w), ptr(v), ptr(w16), n, float(s), stream_handle()), "rb_axpy_shadow")
 

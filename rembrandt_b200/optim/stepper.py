@@ -30,12 +30,16 @@ class SgdStepper:
             out.append((max(lo, d), hi, 0.0))
         return out
 
-    def step(self, lr: float, grad_scale: float = 1.0, phase: int = 7, lo: int = 0, hi: int = None):
+    def step(self, lr: float, grad_scale: float = 1.0, phase: int = 7, lo: int = 0, hi: int = None, grid=None):
+        """`grid` = (blocks, threads) launches the sweep with small blocks (used when it runs beside backward)."""
         net = self.net
         hi = net.flat_len if hi is None else hi
         for a, b, l2 in self._ranges(lo, hi):
             n = b - a
-            if net.is_cuda:
+            if net.is_cuda and grid is not None:
+                K.sgd_fused_grid(net.params[a:b], net.grads[a:b], net.mom[a:b], net.params16[a:b], n, lr, self.mu,
+                                 l2, grad_scale, self.mode, phase, grid[0], grid[1])
+            elif net.is_cuda:
                 K.sgd_fused(net.params[a:b], net.grads[a:b], net.mom[a:b], net.params16[a:b], n, lr, self.mu, l2,
                             grad_scale, self.mode, phase)
             else:

@@ -141,6 +141,84 @@ class NullComm(CommWorker):
         pass
 
 
+def plan_buckets(net, bucket_elems: int, min_bucket_elems: int, align: int = 64):
+    """Ranges of the flat vectors in the order backward completes them: [(trigger operator index, offset, length)].
+    Operators are visited last to first; their segments are merged into contiguous ranges, flushed once at least
+    `min_bucket_elems` are pending, and cut into pieces of at most `bucket_elems`."""
+    ops = net.ops
+    pending, pending_elems, out = [], 0, []
+
+    def merge(ranges):
+        res = []
+        for lo, hi in sorted(ranges):
+            if res and res[-1][1] == lo:
+                res[-1] = (res[-1][0], hi)
+            else:
+                res.append((lo, hi))
+        return res
+
+    for idx in range(len(ops) - 2, 0, -1):
+        for s in ops[idx].segs:
+            n = (s.numel + align - 1) // align * align
+            pending.append((s.offset, s.offset + n))
+            pending_elems += n
+        if pending and (pending_elems >= min_bucket_elems or idx == 1):
+            for lo, hi in merge(pending):
+                o = lo
+                while o < hi:
+                    n = min(bucket_elems, hi - o)
+                    out.append((idx, o, n))
+                    o += n
+            pending, pending_elems = [], 0
+    return out
+
+
+class LocalOverlapComm(NullComm):
+    """One worker, no exchange -- but the optimizer step of a gradient bucket starts as soon as backward has
+    finished the bucket, on a second stream and with blocks small enough to sit beside the GEMM CTAs, instead of
+    one sweep over all parameters after backward. The update is bound by HBM traffic and the convolutions by
+    shared-memory fill, so the two overlap well."""
+    name = "null"
+    graph_safe = True
+    overlap_single = True
+
+    def __init__(self, bucket_bytes: int = 32 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 296):
+        super().__init__()
+        self.bucket_elems = bucket_bytes // 4 // 64 * 64
+        self.min_bucket_elems = min_bucket_bytes // 4
+        self.blocks = blocks
+        self.kernel_launches_per_step = 0
+
+    def attach(self, engine):
+        self.engine = engine
+        net = engine.net
+        self.side = torch.cuda.Stream(net.device, priority=-1)
+        self._ready, self._done = torch.cuda.Event(), torch.cuda.Event()
+        self._by_trigger = {}
+        for idx, off, n in plan_buckets(net, self.bucket_elems, self.min_bucket_elems):
+            self._by_trigger.setdefault(idx, []).append((off, n))
+
+    def prepare(self, stepper, lr):
+        self._stepper, self._lr = stepper, float(lr)
+        self._forked = False
+
+    def on_op_backward(self, op_index):
+        recs = self._by_trigger.get(op_index)
+        if not recs:
+            return
+        self._forked = True
+        self._ready.record(torch.cuda.current_stream())
+        self.side.wait_event(self._ready)
+        with torch.cuda.stream(self.side):
+            for off, n in recs:
+                self._stepper.step(self._lr, lo=off, hi=off + n, grid=(self.blocks, 128))
+
+    def fused_grads_step(self, stepper, lr):
+        if self._forked:
+            self._done.record(self.side)
+            torch.cuda.current_stream().wait_event(self._done)
+
+
 class AllreduceComm(CommWorker):
     """Library all-reduce of the whole flat vector followed by a 1/N scale."""
     name = "allreduce"

@@ -113,3 +113,29 @@ def test_alexnet_and_nin_build_and_step():
         assert torch.isfinite(net.grads).all()
         assert K.read_status() == 0
     assert Net(zoo.alexnet(), 2, device="cpu").params_len == 62378344
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_overlapped_local_update_equals_single_sweep(use_graph):
+    """The per-bucket optimizer step launched from inside backward gives the same parameters (up to the
+    summation order of split-K gradient reductions, which differs from run to run)."""
+    from rembrandt_b200.api import default_opt, model_config
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.parallel.comm import LocalOverlapComm, NullComm
+    torch.manual_seed(3)
+    xs = [torch.randint(0, 256, (32, 3, 32, 32), dtype=torch.uint8).pin_memory() for _ in range(4)]
+    ys = [torch.randint(0, 10, (32,), dtype=torch.int32).pin_memory() for _ in range(4)]
+    finals = []
+    for comm in (NullComm(), LocalOverlapComm(bucket_bytes=64 << 10, min_bucket_bytes=16 << 10)):
+        net = Net(model_config("cifar"), 32, device="cuda", seed=(9, 9))
+        eng = StepEngine(net, default_opt(32, "null"), comm, use_graph=use_graph)
+        for i in range(4):
+            eng.feed(xs[i], ys[i])
+            eng.step()
+        eng.flush()
+        eng.synchronize()
+        finals.append((net.params.clone(), net.mom.clone(), net.params16.clone()))
+        assert float(net.grads.abs().max()) == 0.0
+    for a, b in zip(*finals):
+        assert torch.allclose(a.float(), b.float(), rtol=1e-3, atol=2e-4)
+    assert K.read_status() == 0
