@@ -121,26 +121,60 @@ __global__ void __launch_bounds__(256) input_rows_kernel(InputArgs a) {
   const int oy = s_draw[0], ox = s_draw[1], flip = s_draw[2];
   const int seg_w = a.OW * a.f;
   const uint8_t* img = a.src + (long long)n * a.C * a.H * a.W;
-  // phase 1: one (source row, channel) line at a time, threads stride along x: no per-element divisions
-  for (int line = 0; line < a.f * a.C; ++line) {
-    const int dy = line / a.C, c = line - dy * a.C;
-    const int y = Y * a.f + dy;
-    const int sy = oy + y;
-    const bool row_in = y < a.crop_h && sy >= 0 && sy < a.H;
-    const long long rbase = ((long long)c * a.H + sy) * a.W;
-    const float sh = c < 3 ? s_shift[c] : 0.f;
-    float* dstl = srow + line * seg_w;
-    for (int xc = threadIdx.x; xc < seg_w; xc += blockDim.x) {
-      float v = 0.f;
-      if (row_in && xc < a.crop_w) {
+  // phase 1: (source row dy, channel c) lines, threads stride along x. No per-element divisions; the loads of two
+  // source rows (up to 8 lines) are issued before any of them is used, because a block moves only a few KB and
+  // what it costs is load latency and instruction count, not bandwidth.
+  const int Cn = a.C < 4 ? a.C : 4;
+  if (a.C <= 4) {
+    for (int dy0 = 0; dy0 < a.f; dy0 += 2) {
+      for (int xc = threadIdx.x; xc < seg_w; xc += blockDim.x) {
         const int sx = ox + (flip ? a.crop_w - 1 - xc : xc);
-        if (sx >= 0 && sx < a.W) {
-          v = (float)img[rbase + sx] * a.scale;
-          if (a.mean) v -= a.mean_scale * a.mean[rbase + sx];
-          v += sh;
+        const bool col_in = xc < a.crop_w && sx >= 0 && sx < a.W;
+        uint8_t px[8];
+        float mu[8];
+        bool ok[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int dy = dy0 + (u >> 2), c = u & 3;
+          const int y = Y * a.f + dy;
+          const int sy = oy + y;
+          ok[u] = dy < a.f && c < Cn && col_in && y < a.crop_h && sy >= 0 && sy < a.H;
+          px[u] = 0;
+          mu[u] = 0.f;
+          if (ok[u]) {
+            const int idx = (c * a.H + sy) * a.W + sx;
+            px[u] = img[idx];
+            if (a.mean) mu[u] = a.mean[idx];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int dy = dy0 + (u >> 2), c = u & 3;
+          if (dy < a.f && c < Cn) {
+            float v = 0.f;
+            if (ok[u]) v = (float)px[u] * a.scale - a.mean_scale * mu[u] + (c < 3 ? s_shift[c] : 0.f);
+            srow[(dy * a.C + c) * seg_w + xc] = v;
+          }
         }
       }
-      dstl[xc] = v;
+    }
+  } else {
+    for (int line = 0; line < a.f * a.C; ++line) {
+      const int dy = line / a.C, c = line - dy * a.C;
+      const int y = Y * a.f + dy;
+      const int sy = oy + y;
+      const bool row_in = y < a.crop_h && sy >= 0 && sy < a.H;
+      const long long rbase = ((long long)c * a.H + sy) * a.W;
+      for (int xc = threadIdx.x; xc < seg_w; xc += blockDim.x) {
+        float v = 0.f;
+        const int sx = ox + (flip ? a.crop_w - 1 - xc : xc);
+        if (row_in && xc < a.crop_w && sx >= 0 && sx < a.W) {
+          v = (float)img[rbase + sx] * a.scale;
+          if (a.mean) v -= a.mean_scale * a.mean[rbase + sx];
+          if (c < 3) v += s_shift[c];
+        }
+        srow[line * seg_w + xc] = v;
+      }
     }
   }
   // channel -> offset of its source line in shared memory (or -1 for padded channels), built once per block
@@ -158,8 +192,9 @@ __global__ void __launch_bounds__(256) input_rows_kernel(InputArgs a) {
   __syncthreads();
   const int groups = a.Cp / 8;
   bf16* drow = a.dst + ((long long)n * a.OH + Y) * a.OW * a.Cp;
+  const int gshift = (groups & (groups - 1)) == 0 ? __ffs(groups) - 1 : -1;
   for (int i = threadIdx.x; i < a.OW * groups; i += blockDim.x) {
-    const int X = i / groups, g = i - X * groups;
+    const int X = gshift >= 0 ? (i >> gshift) : i / groups, g = i - X * groups;
     const int xoff = X * a.f;
     float out[8];
 #pragma unroll

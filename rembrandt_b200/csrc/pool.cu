@@ -4,6 +4,8 @@
 // full window size (padding counted), as cuDNN's AverageCountIncludingPadding does
 // (src/operator/mod.rs:2053-2066). Max pooling records the window offset of the (first) maximum in
 // one byte per output so that the backward pass is an exact gather with no atomics.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace rb {
@@ -184,6 +186,130 @@ __global__ void avgpool_bwd_kernel(const bf16* __restrict__ dy, const bf16* __re
   }
 }
 
+// Row-mapped variants of the two max-pooling kernels: one block per (sample, output row) [forward] or per
+// (sample, input row) [backward], threads stride over (column, channel group of 8). The generic kernels above are
+// bound by instruction issue (three div/mod pairs per element, bf16 -> fp32 conversions, per-channel selects);
+// here the in-row index is split with one multiply-high, window size and stride are template constants for the
+// common cases, and the 8 channels are handled as four packed bf16x2 values: compare / max / masked add are one
+// instruction per pair, with no conversion (max and compare of bf16 values are exact; the backward sum of at
+// most ceil(k/stride)^2 terms is rounded to bf16 per addition instead of once at the end).
+__device__ __forceinline__ uint32_t div_magic(uint32_t x, uint32_t magic) { return __umulhi(x, magic); }
+__device__ __forceinline__ __nv_bfloat162 as_bf2(uint32_t v) { return *reinterpret_cast<__nv_bfloat162*>(&v); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
+template <int KK, int SS>
+__global__ void __launch_bounds__(256) maxpool_fwd_rows_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
+                                                               uint8_t* __restrict__ idx, int H, int W, int C, int P,
+                                                               int Q, int k_rt, int stride_rt, int pad, int relu,
+                                                               uint32_t cv_magic) {
+  const int k = KK ? KK : k_rt, stride = SS ? SS : stride_rt;
+  const int cv = C / 8;
+  const int n = blockIdx.x / P, p = blockIdx.x - n * P;
+  const int h0 = p * stride - pad;
+  const int r_lo = max(0, -h0), r_hi = min(k, H - h0);
+  const bf16* xn = x + (long long)n * H * W * C;
+  const long long orow = ((long long)n * P + p) * Q * C;
+  const uint32_t ninf2 = 0xFF80FF80u;  // two bf16 -inf
+  const __nv_bfloat162 zero2 = as_bf2(0u);
+  for (int j = threadIdx.x; j < Q * cv; j += blockDim.x) {
+    const int q = (int)div_magic((uint32_t)j, cv_magic), c8 = j - q * cv;
+    const int w0 = q * stride - pad;
+    const int s_lo = max(0, -w0), s_hi = min(k, W - w0);
+    uint32_t best[4] = {ninf2, ninf2, ninf2, ninf2};
+    uint32_t bi[4] = {0u, 0u, 0u, 0u};  // two 16-bit window codes per word
+    const bf16* base = xn + (h0 * W + w0) * C + c8 * 8;
+    auto visit = [&](int r, int s_) {
+      const uint4 v = *reinterpret_cast<const uint4*>(base + (r * W + s_) * C);
+      const uint32_t code2 = (uint32_t)(r * k + s_) * 0x00010001u;
+      const uint32_t vv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t gm = __hgt2_mask(as_bf2(vv[e]), as_bf2(best[e]));   // strictly greater: first maximum wins
+        bi[e] = (bi[e] & ~gm) | (code2 & gm);
+        best[e] = (best[e] & ~gm) | (vv[e] & gm);
+      }
+    };
+    if (KK) {
+#pragma unroll
+      for (int r = 0; r < (KK ? KK : 1); ++r) {
+        if (r < r_lo || r >= r_hi) continue;
+#pragma unroll
+        for (int s_ = 0; s_ < (KK ? KK : 1); ++s_) {
+          if (s_ < s_lo || s_ >= s_hi) continue;
+          visit(r, s_);
+        }
+      }
+    } else {
+      for (int r = r_lo; r < r_hi; ++r)
+        for (int s_ = s_lo; s_ < s_hi; ++s_) visit(r, s_);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // an empty window leaves -inf: output 0; with a fused ReLU non-positive maxima become 0 with code 255
+      uint32_t keep = ~__heq2_mask(as_bf2(best[e]), as_bf2(ninf2));
+      if (relu) {
+        const uint32_t pos = __hgt2_mask(as_bf2(best[e]), zero2);
+        bi[e] = (bi[e] & pos) | (0x00FF00FFu & ~pos);
+        keep &= pos;
+      }
+      best[e] &= keep;
+    }
+    const long long o = orow + (long long)j * 8;
+    *reinterpret_cast<uint4*>(y + o) = make_uint4(best[0], best[1], best[2], best[3]);
+    // low bytes of the four 16-bit code pairs -> 8 code bytes
+    *reinterpret_cast<uint2*>(idx + o) = make_uint2(__byte_perm(bi[0], bi[1], 0x6420), __byte_perm(bi[2], bi[3], 0x6420));
+  }
+}
+
+template <int KK, int SS>
+__global__ void __launch_bounds__(256) maxpool_bwd_rows_kernel(const bf16* __restrict__ dy,
+                                                               const uint8_t* __restrict__ idx, bf16* __restrict__ dx,
+                                                               const bf16* __restrict__ mask_src, int H, int W, int C,
+                                                               int P, int Q, int k_rt, int stride_rt, int pad,
+                                                               uint32_t cv_magic) {
+  const int k = KK ? KK : k_rt, stride = SS ? SS : stride_rt;
+  const int cv = C / 8;
+  const int n = blockIdx.x / H, h = blockIdx.x - n * H;
+  // windows p with p*stride - pad <= h <= p*stride - pad + k - 1 (numerators are >= stride - k, so truncating
+  // division agrees with the ceiling wherever max(0, .) does not already decide)
+  const int p_lo = max(0, (h + pad - k + stride) / stride), p_hi = min(P - 1, (h + pad) / stride);
+  const long long xrow = ((long long)n * H + h) * W * C;
+  const bf16* dyn = dy + (long long)n * P * Q * C;
+  const uint8_t* idn = idx + (long long)n * P * Q * C;
+  const __nv_bfloat162 zero2 = as_bf2(0u);
+  for (int j = threadIdx.x; j < W * cv; j += blockDim.x) {
+    const int w = (int)div_magic((uint32_t)j, cv_magic), c8 = j - w * cv;
+    const int q_lo = max(0, (w + pad - k + stride) / stride), q_hi = min(Q - 1, (w + pad) / stride);
+    __nv_bfloat162 acc[4] = {zero2, zero2, zero2, zero2};
+    for (int p = p_lo; p <= p_hi; ++p) {
+      const int r = h - (p * stride - pad);
+      for (int q = q_lo; q <= q_hi; ++q) {
+        const int code = r * k + (w - (q * stride - pad));
+        const int o = (p * Q + q) * C + c8 * 8;
+        const uint2 iv = *reinterpret_cast<const uint2*>(idn + o);
+        const uint32_t pat = (uint32_t)code * 0x01010101u;
+        const uint32_t mlo = __vcmpeq4(iv.x, pat), mhi = __vcmpeq4(iv.y, pat);   // 0xff where the code matches
+        if ((mlo | mhi) == 0u) continue;
+        const uint4 g = *reinterpret_cast<const uint4*>(dyn + o);
+        acc[0] = __hadd2(acc[0], as_bf2(g.x & __byte_perm(mlo, 0u, 0x1100)));
+        acc[1] = __hadd2(acc[1], as_bf2(g.y & __byte_perm(mlo, 0u, 0x3322)));
+        acc[2] = __hadd2(acc[2], as_bf2(g.z & __byte_perm(mhi, 0u, 0x1100)));
+        acc[3] = __hadd2(acc[3], as_bf2(g.w & __byte_perm(mhi, 0u, 0x3322)));
+      }
+    }
+    uint32_t out[4] = {as_u32(acc[0]), as_u32(acc[1]), as_u32(acc[2]), as_u32(acc[3])};
+    const long long xi = xrow + (long long)j * 8;
+    if (mask_src) {
+      const uint4 m = *reinterpret_cast<const uint4*>(mask_src + xi);
+      out[0] &= __hgt2_mask(as_bf2(m.x), zero2);
+      out[1] &= __hgt2_mask(as_bf2(m.y), zero2);
+      out[2] &= __hgt2_mask(as_bf2(m.z), zero2);
+      out[3] &= __hgt2_mask(as_bf2(m.w), zero2);
+    }
+    *reinterpret_cast<uint4*>(dx + xi) = make_uint4(out[0], out[1], out[2], out[3]);
+  }
+}
+
 static inline int grid_for(long long total, int block) {
   long long g = (total + block - 1) / block;
   if (g > 148LL * 16) g = 148LL * 16;
@@ -209,6 +335,20 @@ int rb_pool_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, i
   else                                                                                                               \
     avgpool_fwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, N, H, W, C, P, Q, k,       \
                                                                 stride, pad, relu);
+  const int cv = C / 8;
+  if (is_max && small && !getenv("RB_POOL_GENERIC") && Q * cv >= 64 && Q * cv < 65536 && (long long)N * P < 0x7FFFFFFF) {
+    const int threads = Q * cv >= 256 ? 256 : (Q * cv + 31) / 32 * 32;
+    const uint32_t magic = (uint32_t)((0x100000000ull + cv - 1) / cv);
+#define RB_FWD_ROWS(KK, SS)                                                                                \
+  maxpool_fwd_rows_kernel<KK, SS><<<N * P, threads, 0, st>>>((const bf16*)x, (bf16*)y, (uint8_t*)idx, H, W, C, P, Q, \
+                                                            k, stride, pad, relu, magic)
+    if (k == 3 && stride == 2) RB_FWD_ROWS(3, 2);
+    else if (k == 2 && stride == 2) RB_FWD_ROWS(2, 2);
+    else if (k == 3 && stride == 1) RB_FWD_ROWS(3, 1);
+    else RB_FWD_ROWS(0, 0);
+#undef RB_FWD_ROWS
+    return RB_LAUNCH_OK();
+  }
   if (small) { RB_POOL_FWD(unsigned int) } else { RB_POOL_FWD(long long) }
 #undef RB_POOL_FWD
   return RB_LAUNCH_OK();
@@ -228,6 +368,21 @@ int rb_pool_bwd(const void* dy, const void* idx, const void* y_relu, void* dx, c
     avgpool_bwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const bf16*)y_relu, (bf16*)dx,      \
                                                                 (const bf16*)mask_src, N, H, W, C, P, Q, k, stride,   \
                                                                 pad);
+  const int cv = C / 8;
+  if (is_max && small && !getenv("RB_POOL_GENERIC") && W * cv >= 64 && W * cv < 65536 && (long long)N * H < 0x7FFFFFFF) {
+    const int threads = W * cv >= 256 ? 256 : (W * cv + 31) / 32 * 32;
+    const uint32_t magic = (uint32_t)((0x100000000ull + cv - 1) / cv);
+#define RB_BWD_ROWS(KK, SS)                                                                              \
+  maxpool_bwd_rows_kernel<KK, SS><<<N * H, threads, 0, st>>>((const bf16*)dy, (const uint8_t*)idx, (bf16*)dx,       \
+                                                            (const bf16*)mask_src, H, W, C, P, Q, k, stride, pad, \
+                                                            magic)
+    if (k == 3 && stride == 2) RB_BWD_ROWS(3, 2);
+    else if (k == 2 && stride == 2) RB_BWD_ROWS(2, 2);
+    else if (k == 3 && stride == 1) RB_BWD_ROWS(3, 1);
+    else RB_BWD_ROWS(0, 0);
+#undef RB_BWD_ROWS
+    return RB_LAUNCH_OK();
+  }
   if (small) { RB_POOL_BWD(unsigned int) } else { RB_POOL_BWD(long long) }
 #undef RB_POOL_BWD
   return RB_LAUNCH_OK();

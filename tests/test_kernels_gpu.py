@@ -275,6 +275,37 @@ def test_pool(kind, k, stride, pad, ceil, relu):
     close(layout.from_nhwc_padded(dx, C), gref)
 
 
+@pytest.mark.parametrize("k,stride,pad,ceil,relu,C,H", [(3, 2, 0, False, False, 96, 29), (3, 2, 0, True, True, 96, 29),
+                                                        (3, 2, 1, False, False, 40, 31), (2, 2, 0, False, True, 256, 14),
+                                                        (3, 1, 1, False, False, 64, 17)])
+def test_maxpool_row_mapped_kernels(k, stride, pad, ceil, relu, C, H):
+    """Shapes wide enough for the row-mapped max-pooling kernels (forward and backward), with a ReLU mask."""
+    torch.manual_seed(19)
+    N = 3
+    Cp = K.pad_channels(C)
+    x = bf(torch.randn(N, C, H, H, device=DEV)).requires_grad_()
+    ref = F.max_pool2d(x, k, stride, pad, ceil_mode=ceil)
+    if relu:
+        ref = torch.relu(ref)
+    P = ref.shape[2]
+    assert P * (Cp // 8) >= 64 and H * (Cp // 8) >= 64
+    xi = layout.to_nhwc_padded(x.detach(), Cp)
+    y = torch.full((N, P, P, Cp), float("nan"), device=DEV, dtype=torch.bfloat16)
+    idx = torch.zeros((N, P, P, Cp), device=DEV, dtype=torch.uint8)
+    K.pool_fwd(xi, y, idx, N, H, H, Cp, P, P, k, stride, pad, True, relu)
+    close(layout.from_nhwc_padded(y, C), ref.detach())
+    dy = bf(torch.randn_like(ref))
+    gref = torch.autograd.grad(ref, x, dy)[0]
+    # the producer of the delta masks it with the ReLU'd activation below the pooling layer
+    below = bf(torch.randn(N, C, H, H, device=DEV))
+    gref = gref * (below > 0)
+    dx = torch.full((N, H, H, Cp), float("nan"), device=DEV, dtype=torch.bfloat16)
+    K.pool_bwd(layout.to_nhwc_padded(dy, Cp), idx, y if relu else None, dx, layout.to_nhwc_padded(below, Cp), N, H, H,
+               Cp, P, P, k, stride, pad, True)
+    close(layout.from_nhwc_padded(dx, C), gref)
+    assert (dx[..., C:].float() == 0).all()
+
+
 def test_lrn():
     torch.manual_seed(10)
     N, C, H = 2, 96, 7
