@@ -63,6 +63,8 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--blocks", type=int, default=148)
     ap.add_argument("--multimem", type=int, default=-1, help="1/0 force; -1 = RB_MULTIMEM")
+    ap.add_argument("--bucket-mb", type=float, default=32,
+                    help="also time each size cut into buckets of this size alternating over two streams, as in training")
     args = ap.parse_args(argv)
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -77,9 +79,13 @@ def main(argv=None):
     comm._ready, comm._done = torch.cuda.Event(), torch.cuda.Event()
     comm.mc_grads = comm.arena.multicast_ptr("grads") if comm.use_multimem else 0
     comm.mc_w16 = comm.arena.multicast_ptr("params16") if comm.use_multimem else 0
-    comm.launches = [(0, 0, max_n, 0)]
+    bn = int(args.bucket_mb * (1 << 20) / 4) // 512 * 512
+    # slot 0: the whole vector as one bucket; slots 1..: the same range cut into buckets of --bucket-mb
+    comm.launches = [(0, 0, max_n, 0)] + [(0, o, min(bn, max_n - o), 1 + i) for i, o in enumerate(range(0, max_n, bn))]
     comm.one_shot_elems = 0
     comm.setup_stage(avg_elems=max_n)
+    side = [torch.cuda.Stream(priority=-1), torch.cuda.Stream(priority=-1)]
+    ev_ready, ev_done = torch.cuda.Event(), [torch.cuda.Event(), torch.cuda.Event()]
     comm._avg_cap = max_n
     comm._hyper = (0.01, 0.9, 5e-4, 1.0 / world, 1)
     net.grads.normal_()
@@ -91,6 +97,21 @@ def main(argv=None):
         plain = lambda: comm._launch(0, n, comm.num_slots - 1, op=1)
         t_plain = timed(plain, args.iters, args.warmup)
 
+        def bucketed():
+            cur = torch.cuda.current_stream()
+            ev_ready.record(cur)
+            comm.comm_streams = side
+            for st in side:
+                st.wait_event(ev_ready)
+            for _, o, m, slot in comm.launches[1:]:
+                if o < n:
+                    comm._launch(o, min(m, n - o), slot, op=0)
+            for st, ev in zip(side, ev_done):
+                ev.record(st)
+                cur.wait_event(ev)
+            comm.comm_streams = None
+        t_bucketed = timed(bucketed, args.iters, args.warmup) if n > bn else None
+
         def nccl():
             dist.all_reduce(net.grads[:n])
             K.sgd_fused(net.params[:n], net.grads[:n], net.mom[:n], net.params16[:n], n, 0.01, 0.9, 5e-4, 1.0 / world, 1)
@@ -101,6 +122,8 @@ def main(argv=None):
         rows.append({"bucket_mb": mb, "n_gpus": world, "multimem": bool(comm.mc_grads),
                      "fused_allreduce_sgd_ms": round(t_fused, 4), "fused_busbw_gbs": round(busbw(t_fused), 1),
                      "fused_fraction_of_roofline": round(bound_ms / t_fused, 3),
+                     "fused_bucketed_two_streams_ms": round(t_bucketed, 4) if t_bucketed else None,
+                     "bucketed_fraction_of_roofline": round(bound_ms / t_bucketed, 3) if t_bucketed else None,
                      "p2p_allreduce_only_ms": round(t_plain, 4), "p2p_allreduce_busbw_gbs": round(busbw(t_plain), 1),
                      "nccl_allreduce_plus_sgd_ms": round(t_nccl, 4), "nccl_path_busbw_gbs": round(busbw(t_nccl), 1)})
     torch.cuda.synchronize()

@@ -132,6 +132,12 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         net = engine.net
         self.net = net
         self.comm_stream = torch.cuda.Stream(net.device, priority=-1)
+        # consecutive buckets alternate between two streams, so that the push of bucket k+1 (NVLink bound) runs
+        # while bucket k is reduced and applied (HBM bound)
+        self.comm_streams = [self.comm_stream]
+        if int(os.environ.get("RB_COMM_STREAMS", "2")) > 1:
+            self.comm_streams.append(torch.cuda.Stream(net.device, priority=-1))
+        self._done2 = torch.cuda.Event()
         self._ready = torch.cuda.Event()
         self._done = torch.cuda.Event()
         self._plan(net)
@@ -213,19 +219,23 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
             return
         cur = torch.cuda.current_stream()
         self._ready.record(cur)
-        self.comm_stream.wait_event(self._ready)
+        for s in self.comm_streams:
+            s.wait_event(self._ready)
         for _, off, n, slot in recs:
             self._launch(off, n, slot, op=0)
 
     def fused_grads_step(self, stepper, lr):
-        """Everything was launched from the backward hooks; join the communication stream."""
+        """Everything was launched from the backward hooks; join the communication streams."""
         if not self.overlap:
             self._ready.record(torch.cuda.current_stream())
-            self.comm_stream.wait_event(self._ready)
+            for s in self.comm_streams:
+                s.wait_event(self._ready)
             for _, off, n, slot in self.launches:
                 self._launch(off, n, slot, op=0)
-        self._done.record(self.comm_stream)
-        torch.cuda.current_stream().wait_event(self._done)
+        cur = torch.cuda.current_stream()
+        for s, ev in zip(self.comm_streams, (self._done, self._done2)):
+            ev.record(s)
+            cur.wait_event(ev)
 
     def _launch(self, off, n, slot, op, buf="grads", scale=None):
         net = self.net
@@ -259,19 +269,21 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
             a.h.lr, a.h.mu, a.h.l2, a.h.grad_scale, a.h.mode, a.h.phase = lr, mu, l2, gs, mode, 3
         work = n if a.one_shot else (n + self.world - 1) // self.world
         blocks = max(1, min(self.blocks, (work // 8 + 127) // 128))
-        with torch.cuda.stream(self.comm_stream):
+        streams = getattr(self, "comm_streams", None) or [self.comm_stream]
+        stream = streams[slot % len(streams)] if op == 0 else self.comm_stream
+        with torch.cuda.stream(stream):
             if push:
                 pwork = (n if a.one_shot else self._shard_len(n)) * (self.world - 1)
                 pblocks = max(1, min(self.blocks, (pwork // 16 + 127) // 128))
-                check(PK.fn("rb_allreduce_push_p2p")(C.byref(a), pblocks, self.comm_stream.cuda_stream),
+                check(PK.fn("rb_allreduce_push_p2p")(C.byref(a), pblocks, stream.cuda_stream),
                       "rb_allreduce_push_p2p")
                 self.kernel_launches_per_step += 1
             if self.split_wait and self.world > 1:
                 a.wait_ok = self.wait_ok[slot:].data_ptr()
-                check(PK.fn("rb_allreduce_wait_p2p")(C.byref(a), self.comm_stream.cuda_stream),
+                check(PK.fn("rb_allreduce_wait_p2p")(C.byref(a), stream.cuda_stream),
                       "rb_allreduce_wait_p2p")
                 self.kernel_launches_per_step += 1
-            check(PK.fn("rb_allreduce_sgd_p2p")(C.byref(a), blocks, self.comm_stream.cuda_stream),
+            check(PK.fn("rb_allreduce_sgd_p2p")(C.byref(a), blocks, stream.cuda_stream),
                   "rb_allreduce_sgd_p2p")
             if op == 0 and not push:
                 # every peer has finished reading this bucket when the kernel ends; the push kernels zero
