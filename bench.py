@@ -41,13 +41,20 @@ MODELS = {
 
 
 def read_baseline(model, n):
-    """Published/recorded baseline images/s for (model, n GPUs) from BASELINE.json's `published` table."""
-    try:
-        with open(os.path.join(ROOT, "BASELINE.json")) as f:
-            pub = json.load(f).get("published", {})
-        return pub.get(f"{model}_images_per_s", {}).get(str(n))
-    except Exception:
-        return None
+    """Baseline images/s for (model, n GPUs): a published figure of the reference if BASELINE.json lists one, else
+    the recorded torch-DDP measurement on this hardware (baseline/recorded.json)."""
+    for path, key in ((os.path.join(ROOT, "BASELINE.json"), "published"),
+                      (os.path.join(ROOT, "baseline", "recorded.json"), None)):
+        try:
+            with open(path) as f:
+                tab = json.load(f)
+            tab = tab.get(key, {}) if key else tab
+            v = tab.get(f"{model}_images_per_s", {}).get(str(n))
+            if v:
+                return v
+        except Exception:
+            pass
+    return None
 
 
 class ClockSampler:
