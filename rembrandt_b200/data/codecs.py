@@ -134,3 +134,23 @@ class RandomFlipXPreproc:
     def __call__(self, sample):
         img, label = sample
         return (img[:, :, ::-1] if self.rng.integers(0, 2) else img), label
+
+
+def encode_caffe_datum(data: bytes, channels: int, height: int, width: int, label: int = 0, encoded: bool = False) -> bytes:
+    """Serialise a Caffe ``Datum`` (fields 1-5 and 7); the inverse of `decode_caffe_datum` for tools and tests."""
+    def varint(v):
+        out = bytearray()
+        while True:
+            b = v & 0x7F
+            v >>= 7
+            out.append(b | (0x80 if v else 0))
+            if not v:
+                return bytes(out)
+    msg = bytearray()
+    for field, v in ((1, channels), (2, height), (3, width)):
+        msg += varint(field << 3) + varint(v)
+    msg += varint((4 << 3) | 2) + varint(len(data)) + data
+    msg += varint(5 << 3) + varint(label)
+    if encoded:
+        msg += varint(7 << 3) + varint(1)
+    return bytes(msg)

@@ -136,7 +136,25 @@ def compute_mean(source: DataSource, limit: Optional[int] = None) -> np.ndarray:
     return out.reshape(c, h, w)
 
 
-def open_split(split: DatasetSplit) -> DataSource:
+class _IterableAsSource:
+    """A sequential shard (database cursor) behind the indexable interface; records are materialised on first use."""
+
+    def __init__(self, shard):
+        self._shard, self._items = shard, None
+
+    def _load(self):
+        if self._items is None:
+            self._items = list(self._shard)
+        return self._items
+
+    def __len__(self):
+        return len(self._shard)
+
+    def __getitem__(self, i):
+        return self._load()[i]
+
+
+def open_split(split: DatasetSplit, rank: int = 0, world: int = 1) -> DataSource:
     """Open one `[dataset.<split>]` table of a .data file (src/data_new.rs:296-412)."""
     if split.source == "mnist":
         return MnistDataSource(split.data_path, split.labels_path)
@@ -144,9 +162,19 @@ def open_split(split: DatasetSplit) -> DataSource:
         return Cifar10DataSource(split.data_path)
     if split.source == "synthetic":
         return SyntheticDataSource(10000)
-    if split.source in ("lmdb_caffe", "episodb", "varraydb"):
-        raise NotImplementedError(f"source {split.source!r} needs a database binding that is not part of this "
-                                  "framework (see data/codecs.py for the Caffe Datum record decoder)")
+    if split.source == "lmdb_caffe":
+        from .codecs import JpegDataCodec
+        from .lmdb_reader import LmdbCaffeShard
+        return _IterableAsSource(LmdbCaffeShard(split.data_path, rank, world, codec=JpegDataCodec()))
+    if split.source == "varraydb":
+        from .codecs import JpegDataCodec
+        from .recorddb import VarrayDbShard
+        return VarrayDbShard(split.data_path, split.labels_path, JpegDataCodec(), rank, world)
+    if split.source == "episodb":
+        from .recorddb import EpisodeDataSource
+        dims = tuple(split.frame_dims) if getattr(split, "frame_dims", None) else (19, 19, 1)
+        return EpisodeDataSource(split.data_path, dims, lookahead=getattr(split, "lookahead", 1) or 1, rank=rank,
+                                 world=world)
     raise ValueError(f"unknown data source {split.source!r}")
 
 

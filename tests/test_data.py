@@ -126,3 +126,79 @@ def test_codecs_and_caffe_datum():
     assert np.array_equal(crop, img[:, 1:2, 1:3])
     rc, _ = codecs.RandomCropPreproc(2, 2, seed=1)((img, 0))
     assert rc.shape == (2, 2, 2)
+
+
+def test_lmdb_reader_round_trip_with_depth_and_overflow(tmp_path):
+    """The dependency-free LMDB reader: ordered iteration, get, cursor seek, overflow values, multi-level tree."""
+    import random
+    from rembrandt_b200.data.lmdb_reader import LmdbEnv, write_env
+    rnd = random.Random(5)
+    items = []
+    for i in range(700):
+        key = b"%08d" % i
+        size = rnd.choice([0, 1, 17, 300, 900, 5000, 20000]) if i % 7 == 0 else rnd.randint(1, 200)
+        items.append((key, bytes(rnd.getrandbits(8) for _ in range(size))))
+    for cap in (0, 5):           # natural fan-out, and 5 nodes per page (a tree of depth >= 4)
+        d = tmp_path / f"db{cap}"
+        write_env(str(d), items, max_leaf_nodes=cap)
+        with LmdbEnv(str(d)) as env:
+            assert len(env) == 700
+            if cap:
+                assert env.depth >= 4
+            got = list(env.items())
+            assert got == sorted(items)
+            assert env.get(b"00000123") == dict(items)[b"00000123"]
+            assert env.get(b"00000699") == dict(items)[b"00000699"]
+            assert env.get(b"nope") is None
+            tail = list(env.items(b"00000650"))
+            assert [k for k, _ in tail] == [b"%08d" % i for i in range(650, 700)]
+            assert next(iter(env.items(b"000001235")))[0] == b"00000124"   # seek lands on the next larger key
+
+
+def test_lmdb_caffe_shard_partitions_and_decodes(tmp_path):
+    from rembrandt_b200.data.codecs import encode_caffe_datum
+    from rembrandt_b200.data.lmdb_reader import LmdbCaffeShard, write_env
+    rng = np.random.default_rng(0)
+    imgs = [rng.integers(0, 256, (3, 8, 6), dtype=np.uint8) for _ in range(10)]
+    items = [(b"%08d_img" % i, encode_caffe_datum(imgs[i].tobytes(), 3, 8, 6, label=i * 3)) for i in range(10)]
+    write_env(str(tmp_path / "db"), items)
+    seen = []
+    for rank in range(3):
+        shard = LmdbCaffeShard(str(tmp_path / "db"), rank, 3)
+        for img, label in shard:
+            seen.append(label // 3)
+            assert np.array_equal(img, imgs[label // 3])
+    assert seen == list(range(10))
+
+
+def test_record_stores_shards_and_episode_lookahead(tmp_path):
+    import struct
+    from rembrandt_b200.data.codecs import Array3dDataCodec
+    from rembrandt_b200.data.recorddb import EpisodeDataSource, RecordDb, RecordDbWriter, VarrayDbShard
+    from rembrandt_b200.utils import blob
+    rng = np.random.default_rng(1)
+    imgs = [rng.integers(0, 256, (2, 3 + i % 3, 4), dtype=np.uint8) for i in range(9)]
+    with RecordDbWriter(str(tmp_path / "d")) as wd, RecordDbWriter(str(tmp_path / "l")) as wl:
+        for i, im in enumerate(imgs):
+            wd.append(blob.encode_record(im.reshape(-1), tuple(reversed(im.shape)), dtype="u8"))
+            wl.append(struct.pack("<i", 100 + i))
+    db = RecordDb(str(tmp_path / "d"))
+    assert len(db) == 9
+    got = []
+    for rank in range(2):
+        shard = VarrayDbShard(str(tmp_path / "d"), str(tmp_path / "l"), Array3dDataCodec(), rank, 2)
+        for im, label in shard:
+            assert np.array_equal(im, imgs[label - 100])
+            got.append(label - 100)
+    assert got == list(range(9))
+    # episodes of Go-like frames: label -1 marks a frame without a target
+    labels = [[3, 5, -1, 7], [2, 9]]
+    with RecordDbWriter(str(tmp_path / "e")) as we:
+        for ep in labels:
+            we.append_episode([struct.pack("<i", l) + bytes([l & 0xFF if l >= 0 else 0] * 9) for l in ep])
+    src = EpisodeDataSource(str(tmp_path / "e"), (3, 3, 1), lookahead=3)
+    assert len(src) == 5
+    frame, la = src[0]
+    assert frame.shape == (1, 3, 3) and la == [3, 5, -1]
+    assert src[2][1] == [7, -1, -1]          # the frame after the unlabeled one; its episode ends
+    assert src[3][1] == [2, 9, -1]
