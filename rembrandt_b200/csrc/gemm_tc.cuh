@@ -1,6 +1,7 @@
 // Parameter block of the persistent tcgen05 GEMM / implicit-GEMM convolution
 // kernel (gemm_tc.cu). One kernel, configured at run time, serves:
 //   conv fprop   A = im2col(X) K-major (TMA im2col)   B = filters K-major
+//                or, stride 1: A = column-shifted halo tiles of X (plain tiled TMA, A_HALO_K), see gemm_tc.cu
 //   conv dgrad   A = im2col(dY) K-major               B = flipped/transposed filters K-major
 //   conv wgrad   A = dY^T MN-major (tiled)            B = im2col(X) MN-major (TMA im2col)
 //   affine fwd   A = X K-major                        B = W K-major
@@ -16,7 +17,7 @@
 
 namespace rb {
 
-enum : int { A_TILED_K = 0, A_IM2COL_K = 1, A_TILED_MN = 2 };
+enum : int { A_TILED_K = 0, A_IM2COL_K = 1, A_TILED_MN = 2, A_HALO_K = 3 };
 enum : int { B_TILED_K = 0, B_TILED_MN = 1, B_IM2COL_MN = 2, B_TILED_K3 = 3 };
 enum : int { EPI_BF16 = 0, EPI_F32_STORE = 1, EPI_F32_ATOMIC = 2 };
 
@@ -48,7 +49,17 @@ struct alignas(64) GemmTcParams {
   int wg_ntaps;        // R*S
   int wg_ctiles;       // channel tiles of bn per tap (B_IM2COL_MN)
   int wg_cpad;         // padded input channels: column of D = tap*wg_cpad + channel
+  int a_split, b_split; // K-major operands: TMA boxes (one issuing lane each) per 128-row A sub-tile / per B tile
   int n_tiles;         // tiles along N (taps*wg_ctiles for wgrad)
+  // halo mode (A_HALO_K): a sub-tile is hl_rows output rows of one image at a row pitch of hl_pitch positions
+  int hl_pitch;        // 8..128, a power of two >= Q; hl_rows * hl_pitch = 128
+  int hl_rows;
+  int hl_rtot;         // input rows per A stage = mt * hl_rows + R - 1
+  int hl_groups;       // work items per image = ceil(P / (mt * hl_rows))
+  int hl_R;            // filter height
+  int hl_pad_h, hl_pad_w;
+  int hl_a_stages;     // A stages in shared memory (each hl_a_bytes apart)
+  int hl_a_bytes;
   // epilogue
   int epi;
   int relu;            // EPI_BF16: clamp at zero after the bias

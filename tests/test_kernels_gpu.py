@@ -114,6 +114,8 @@ CONV_CASES = [
     (2, 128, 15, 15, 96, 3, 2, 1),
     (1, 32, 6, 6, 40, 3, 1, 1),
     (130, 32, 8, 8, 32, 5, 1, 2),
+    (1, 32, 40, 40, 64, 3, 1, 1),     # halo mode: row pitch 64 (two output rows per sub-tile)
+    (1, 32, 70, 66, 32, 3, 1, 1),     # halo mode: row pitch 128, non-square
 ]
 
 
@@ -128,11 +130,16 @@ def _conv_setup(N, C, H, W, Ko, R, stride, pad, seed=0):
     return Cp, Kp, x, w, b, P, Q
 
 
-@pytest.fixture(params=["auto", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3"])
+@pytest.fixture(params=["auto", "halo", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3"])
 def tile_mode(request, monkeypatch):
-    """Force the kernel's tile-shape planner through each of its modes (two sub-tiles per item, resident B)."""
+    """Force the kernel's tile-shape planner through each of its modes (two sub-tiles per item, resident B,
+    column-shifted halo tiles for stride-1 convolutions)."""
     mode = request.param
-    if mode != "auto":
+    if mode == "halo":
+        monkeypatch.setenv("RB_GEMM_FORCE_HALO", "1")
+    elif mode != "auto":
+        monkeypatch.setenv("RB_GEMM_FORCE_HALO", "0")
+    if mode not in ("auto", "halo"):
         monkeypatch.setenv("RB_GEMM_FORCE_MT", "2" if "mt2" in mode else "1")
         monkeypatch.setenv("RB_GEMM_FORCE_RESIDENT", "1" if "resident" in mode else "0")
         if "taps" in mode:
