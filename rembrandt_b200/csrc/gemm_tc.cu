@@ -30,6 +30,9 @@
 #include "ptx.cuh"
 #include "common.cuh"
 #include <stdlib.h>
+#include <map>
+#include <mutex>
+#include <tuple>
 
 namespace rb {
 
@@ -788,25 +791,86 @@ static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split,
   return best;
 }
 
-static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights, cudaStream_t stream) {
-  if (p.M <= 0 || p.n_tiles <= 0 || p.num_kb <= 0) return 0;
-  const Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
-  if (pl.cost >= 1e299) return -3;
+// Fill in what follows from a plan; returns the grid size, or 0 when the plan does not fit.
+static int apply_plan(GemmTcParams& p, const Plan& pl) {
   p.mt = pl.mt;
   p.split_k = pl.split;
   p.b_resident = pl.resident;
   p.acc_stride = p.bn > 128 ? 256 : 128;
   p.acc_bufs = (2 * p.mt * p.acc_stride <= 512) ? 2 : 1;
-  { const char* e = getenv("RB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
   const int a_bytes = BM * p.bk * 2, b_bytes = p.bn_load * p.bk * 2;
   const int panel = p.b_resident ? p.num_kb * b_bytes : 0;
   const int stage = p.mt * a_bytes + (p.b_resident ? 0 : b_bytes);
+  if (panel >= TILE_SMEM_BYTES) return 0;
   p.stages = (TILE_SMEM_BYTES - panel) / stage;
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
-  if (p.stages < 2) return -3;
+  if (p.stages < 2) return 0;
+  if (p.mt == 2 && p.M <= BM) return 0;
   const int m_items = (p.M + BM * p.mt - 1) / (BM * p.mt);
   const long long work = (long long)m_items * p.n_tiles * p.split_k;
-  const int grid = work < g_num_sms ? (int)work : g_num_sms;
+  return work < g_num_sms ? (int)work : g_num_sms;
+}
+
+// Shapes whose output is overwritten (bf16 epilogue: forward and data-grad passes) are tuned by measurement the
+// first time they are seen outside a stream capture: every feasible (sub-tiles per item, resident B) choice is
+// timed on the caller's stream with its real operands (the launches are idempotent) and the fastest is cached.
+// The cost model alone mis-ranks them by up to 30 % (it knows rows filled, not wave quantisation or how much of
+// the epilogue is exposed). RB_GEMM_AUTOTUNE=0 turns this off; the force hooks bypass it.
+typedef std::tuple<int, int, int, int, int, int, int, int, int, int> PlanKey;
+static std::map<PlanKey, Plan> g_plan_cache;
+static std::mutex g_plan_mutex;
+
+static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights, cudaStream_t stream) {
+  if (p.M <= 0 || p.n_tiles <= 0 || p.num_kb <= 0) return 0;
+  { const char* e = getenv("RB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
+  Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
+  if (pl.cost >= 1e299) return -3;
+  const char* e_tune = getenv("RB_GEMM_AUTOTUNE");
+  const bool forced = getenv("RB_GEMM_FORCE_MT") || getenv("RB_GEMM_FORCE_RESIDENT");
+  if (p.epi == EPI_BF16 && !forced && !(e_tune && atoi(e_tune) == 0)) {
+    const PlanKey key(p.a_mode, p.b_mode, p.M, p.N, p.num_kb, p.bn, p.bk, p.n_tiles, p.cv_stride, p.mask_src ? 1 : 0);
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    auto it = g_plan_cache.find(key);
+    if (it != g_plan_cache.end()) {
+      pl = it->second;
+    } else {
+      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+      if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+        cudaEvent_t e0, e1;
+        cudaEventCreate(&e0);
+        cudaEventCreate(&e1);
+        float best_ms = 1e30f;
+        Plan best = pl;
+        for (int mt = 1; mt <= 2; ++mt) {
+          for (int res = 0; res <= 1; ++res) {
+            if (res && (!b_is_weights || p.n_tiles != 1)) continue;
+            GemmTcParams q = p;
+            const Plan cand{mt, 1, res, 0.0};
+            const int grid = apply_plan(q, cand);
+            if (grid <= 0 || (res && q.stages < 3)) continue;
+            float ms = 1e30f;
+            bool okc = true;
+            for (int rep = 0; rep < 3 && okc; ++rep) {
+              cudaEventRecord(e0, stream);
+              gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(q);
+              cudaEventRecord(e1, stream);
+              if (cudaEventSynchronize(e1) != cudaSuccess) { okc = false; break; }
+              float t = 0.f;
+              cudaEventElapsedTime(&t, e0, e1);
+              if (rep > 0 && t < ms) ms = t;   // the first run warms the caches
+            }
+            if (okc && ms < best_ms) { best_ms = ms; best = cand; }
+          }
+        }
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        pl = best;
+        g_plan_cache[key] = pl;
+      }
+    }
+  }
+  const int grid = apply_plan(p, pl);
+  if (grid <= 0) return -3;
   gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
