@@ -888,11 +888,13 @@ static int pick_bn(GemmTcParams& p, int n, int gran, bool allow_split, int fixed
                    Setup setup) {
   int best_bn = 0;
   double best_cost = 1e300;
+  const char* e_cap = getenv("RB_GEMM_BN_CAP");   // experiment hook: upper bound on the tile width
+  const int cap = e_cap ? atoi(e_cap) : 256;
   for (int nt = 1; nt <= 4; ++nt) {
     int bn = (n + nt - 1) / nt;
     const int g = (nt > 1 && gran < 64) ? 64 : gran;   // the bf16 epilogue stores 64-column slabs
     bn = (bn + g - 1) / g * g;
-    if (bn > 256 || bn == best_bn) continue;
+    if (bn > 256 || bn > cap || bn == best_bn) continue;
     setup(p, bn);
     const Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
     if (pl.cost < best_cost * 0.97) { best_cost = pl.cost; best_bn = bn; }
@@ -984,14 +986,21 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   if (rc) return rc;
   GemmTcParams p;
   memset(&p, 0, sizeof(p));
-  p.bk = (Cp % 64 == 0) ? 64 : 32;
+  // The TMA unit is bound by rows (requests), not bytes: 64-channel (128-byte) rows halve the rows per MMA. A channel
+  // count such as 96 therefore runs as two 64-channel chunks whose upper half lies outside the tensor and is
+  // zero-filled by the TMA unit (both operands), rather than as three 32-channel chunks: a third more MMA work,
+  // a third fewer loads, and the loads are what binds.
+  {
+    const char* e = getenv("RB_GEMM_BK32");   // test hook: 1 = keep 32-channel chunks for such counts
+    p.bk = (Cp % 64 == 0 || (Cp > 64 && !(e && atoi(e) == 1))) ? 64 : 32;
+  }
   if (Cp % 32 != 0) return -10;
   if ((n_store > 0 ? n_store : Kout) % 32 != 0 || ldy % 8 != 0) return -11;
   const CUtensorMapSwizzle ksw = p.bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   const int n_cols = n_store > 0 ? n_store : Kout;
   p.M = N * P * Q;
   p.N = Kout;
-  p.cv_cchunks = Cp / p.bk;
+  p.cv_cchunks = (Cp + p.bk - 1) / p.bk;
   p.num_kb = R * S * p.cv_cchunks;
   p.epi = EPI_BF16;
   pick_bn(p, n_cols, 32, false, 1, true, [n_cols](GemmTcParams& q, int bn) {

@@ -114,6 +114,8 @@ CONV_CASES = [
     (2, 128, 15, 15, 96, 3, 2, 1),
     (1, 32, 6, 6, 40, 3, 1, 1),
     (130, 32, 8, 8, 32, 5, 1, 2),
+    (2, 64, 14, 14, 96, 3, 1, 1),     # data-grad reduces over 96 channels: a half-empty 64-channel chunk
+    (2, 160, 9, 9, 64, 3, 1, 1),
     (1, 32, 40, 40, 64, 3, 1, 1),     # halo mode: row pitch 64 (two output rows per sub-tile)
     (1, 32, 70, 66, 32, 3, 1, 1),     # halo mode: row pitch 128, non-square
 ]
