@@ -358,6 +358,8 @@ struct MixArgs {
   int wait_peer;          // 1: wait until the peer has published this epoch (synchronous gossip)
   float alpha;            // mixing weight: x <- (1-alpha) x + alpha x_peer
   float w_self;           // push gossip: weight of the own vector
+  int not_last;           // gossip mix: 1 = another pull of the same round follows (keep the epoch, do not report done)
+  int mix_self;           // gossip mix: 1 = a pull that lands on this rank mixes with its own published snapshot
 };
 
 // pub[epoch & 1] <- w, then tell every peer that epoch is published. Before overwriting the buffer last used
@@ -400,7 +402,7 @@ __global__ void __launch_bounds__(512) gossip_mix_kernel(const __grid_constant__
     s_pe = a.wait_peer ? epoch : ld_acquire_sys(flag_at(a.flags[a.rank], a.slot, 0, a.peer));
   __syncthreads();
   const uint32_t pe = s_pe;
-  if (ok && a.peer != a.rank && pe != 0u) {
+  if (ok && (a.peer != a.rank || a.mix_self) && pe != 0u) {
     const float* src = a.pub_peer + (size_t)(pe & 1u) * a.n;
     const long long n4 = a.n / 4;
     const float al = a.alpha, be = 1.f - a.alpha;
@@ -426,10 +428,10 @@ __global__ void __launch_bounds__(512) gossip_mix_kernel(const __grid_constant__
   if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
   __syncthreads();
   if (s_last) {
-    if (threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 1, a.rank), epoch);
+    if (!a.not_last && threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 1, a.rank), epoch);
     if (threadIdx.x == 0) {
       *a.block_counter = 0u;
-      *a.epoch_ptr = epoch;
+      if (!a.not_last) *a.epoch_ptr = epoch;
     }
   }
 }

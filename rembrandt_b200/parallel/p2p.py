@@ -340,10 +340,13 @@ class GossipP2PComm(CommWorker, _P2PBase):
     graph_safe = False
 
     def __init__(self, group=None, mode: str = "pair", alpha: float = 0.5, seed=(17, 29), blocks: int = 96,
-                 cfg: GossipConfig = GossipConfig()):
+                 cfg: GossipConfig = GossipConfig(), synchronous: Optional[bool] = None):
         CommWorker.__init__(self, group)
         self._init_p2p(group, num_slots=8)
         self.mode, self.alpha, self.blocks, self.cfg = mode, alpha, blocks, cfg
+        # synchronous: wait until the peer has published this round's snapshot (always for pair gossip; pull gossip
+        # is asynchronous by default and takes whichever snapshot the peer published last)
+        self.synchronous = (mode == "pair") if synchronous is None else bool(synchronous)
         self.rng = XorShift128Plus(seed[0] + (0 if mode == "pair" else 1000003 * self.rank), seed[1])
         self.pub = None
         self._last_peer = None
@@ -353,43 +356,53 @@ class GossipP2PComm(CommWorker, _P2PBase):
         self.net = engine.net
         self.pub = self.arena.alloc("pub", 2 * self.net.flat_len, torch.float32)
 
-    def _peer(self, repeat):
+    def _peers(self, repeat):
+        """Peers of this exchange: one for pair gossip; `num_rounds` independent draws for pull gossip."""
         if repeat and self._last_peer is not None:
             return self._last_peer
         if self.mode == "pair":
             # the shared-seed permutation of the reference: rank r sends to perm[r], so r receives from the
             # rank whose target it is -- here r pulls from that rank
             perm = self.rng.permutation(self.world)
-            peer = perm.index(self.rank)
+            peers = [perm.index(self.rank)]
         else:
-            peer = self.rng.below(self.world)
-        self._last_peer = peer
-        return peer
+            peers = [self.rng.below(self.world) for _ in range(max(1, self.cfg.num_rounds))]
+        self._last_peer = peers
+        return peers
 
     def sync_params(self, flat, repeat=False):
+        """Pair gossip: x <- (1 - alpha) x + alpha x_peer. Pull gossip: x <- mean of x and the snapshots of
+        `num_rounds` randomly drawn ranks (src/worker/gossip_pull_dist_rdma.rs:517-589), as a running mean:
+        pull k mixes with weight 1 / (k + 1)."""
         if self.world <= 1:
             return
         net = self.net
         is_params = flat.data_ptr() == net.params.data_ptr()
-        peer = self._peer(repeat)
+        peers = self._peers(repeat)
         st = torch.cuda.current_stream()
         a = PK.MixArgs()
         _fill_ptrs(a.flags, self._flag_ptrs())
         a.w = flat.data_ptr()
         a.w16 = net.params16.data_ptr() if is_params else None
         a.pub_local = self.pub.data_ptr()
-        a.pub_peer = self.arena.ptrs("pub")[peer]
         slot = 0 if is_params else 1
         a.epoch_ptr = self.epochs[slot:].data_ptr()
         a.block_counter = self.counters[slot:].data_ptr()
         a.status = self.status.data_ptr()
         a.n = flat.numel() // 4 * 4
-        a.rank, a.world, a.slot, a.peer = self.rank, self.world, slot, peer
-        a.wait_peer = 1 if self.mode == "pair" else 0
-        a.alpha, a.w_self = self.alpha, 1.0
+        a.rank, a.world, a.slot = self.rank, self.world, slot
+        a.wait_peer = 1 if self.synchronous else 0
+        a.mix_self = 0 if self.mode == "pair" else 1
+        a.w_self = 1.0
+        a.peer = peers[0]
         check(PK.fn("rb_publish_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_publish_p2p")
-        check(PK.fn("rb_gossip_mix_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_gossip_mix_p2p")
-        self.bytes_moved += a.n * 4
+        for k, peer in enumerate(peers):
+            a.peer = peer
+            a.pub_peer = self.arena.ptrs("pub")[peer]
+            a.alpha = self.alpha if self.mode == "pair" else 1.0 / (k + 2)
+            a.not_last = 0 if k == len(peers) - 1 else 1
+            check(PK.fn("rb_gossip_mix_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_gossip_mix_p2p")
+            self.bytes_moved += a.n * 4
 
     def allreduce_average(self, flat):
         CommWorker.exact_sync(self, flat)

@@ -36,7 +36,7 @@ class MixArgs(C.Structure):
     _fields_ = [("flags", vp * MAX_RANKS), ("w", vp), ("w16", vp), ("pub_local", vp), ("pub_peer", vp),
                 ("acc_target", vp), ("count_target", vp), ("epoch_ptr", vp), ("block_counter", vp), ("status", vp),
                 ("n", i64), ("rank", i32), ("world", i32), ("slot", i32), ("peer", i32), ("wait_peer", i32),
-                ("alpha", f32), ("w_self", f32)]
+                ("alpha", f32), ("w_self", f32), ("not_last", i32), ("mix_self", i32)]
 
 
 class BarrierArgs(C.Structure):

@@ -101,6 +101,28 @@ def case_gossip_pair(rank, world):
         assert torch.equal(net.params16[:n], net.params[:n].bfloat16())
 
 
+def case_pull_rounds(rank, world):
+    """Pull gossip with three pulls per exchange: the result is the mean of the own vector and the published
+    snapshots of the drawn ranks (a self-draw contributes the own snapshot)."""
+    comm = p2p.GossipP2PComm(mode="pull", seed=(31, 37), cfg=comm_mod.GossipConfig(num_rounds=3), synchronous=True)
+    net, _ = _param_engine(comm)
+    for rnd in range(3):
+        torch.manual_seed(2000 * rnd + rank)
+        net.params.copy_(torch.randn_like(net.params))
+        everyone = [torch.empty_like(net.params) for _ in range(world)]
+        dist.all_gather(everyone, net.params)
+        comm.sync_params(net.params)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        peers = comm._last_peer
+        assert len(peers) == 3
+        expect = (everyone[rank] + sum(everyone[p] for p in peers)) / 4.0
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(net.params[:n], expect[:n], rtol=1e-5, atol=1e-5), f"round {rnd}"
+        assert torch.equal(net.params16[:n], net.params[:n].bfloat16())
+        dist.barrier()
+
+
 def case_elastic(rank, world):
     comm = p2p.ElasticP2PComm(beta=0.25)
     oracle = comm_mod.ElasticComm(beta=0.25)
@@ -157,6 +179,8 @@ def main():
             case_p2p_allreduce(rank, world)
         elif case == "gossip_pair":
             case_gossip_pair(rank, world)
+        elif case == "pull_rounds":
+            case_pull_rounds(rank, world)
         elif case == "elastic":
             case_elastic(rank, world)
         elif case == "push":

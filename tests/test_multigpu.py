@@ -35,7 +35,7 @@ def _run(case, nproc=None, timeout=240):
     assert f"case {case}: ok" in r.stdout
 
 
-@pytest.mark.parametrize("case", ["p2p_allreduce", "fused_eager", "fused_graph", "gossip_pair", "elastic", "push"])
+@pytest.mark.parametrize("case", ["p2p_allreduce", "fused_eager", "fused_graph", "gossip_pair", "pull_rounds", "elastic", "push"])
 def test_p2p_backend(case):
     _run(case)
 
