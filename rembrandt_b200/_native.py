@@ -62,7 +62,7 @@ _CUDA_SIGS = {
     "rb_synth_normal": [vp, i64, i32, i32, u64, u32, vp],
     "rb_synth_labels": [vp, i32, i32, u64, u32, vp],
     # bn.cu
-    "rb_bn_fwd_train": [vp, i64, i32, i32, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp],
+    "rb_bn_fwd_train": [vp, i64, i32, i32, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp],
     "rb_bn_fwd_infer": [vp, i64, i32, i32, f32, vp, vp, vp, vp, vp, vp, vp, i32, vp],
     "rb_bn_bwd": [vp, vp, vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp],
 }

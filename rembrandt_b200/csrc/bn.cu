@@ -61,11 +61,19 @@ __global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restr
 }
 
 // mean/istd from the sums; running statistics: r = (1-f) r + f batch ; sums re-zeroed.
+// With a step counter (`step_ptr`, the network's device-side count of training steps) the factor is derived on
+// the device, so that a captured CUDA graph keeps averaging correctly: avg_kind 1 = cumulative 1 / (1 + t),
+// avg_kind 2 = exponential `factor` with 1 at t = 0; avg_kind 0 (or no counter) uses `factor` as given.
 __global__ void bn_finalize_kernel(float* __restrict__ sums, long long rows, int C, float eps, float factor,
                                    float* __restrict__ mean, float* __restrict__ istd, float* __restrict__ run_mean,
-                                   float* __restrict__ run_var) {
+                                   float* __restrict__ run_var, int avg_kind = 0,
+                                   const unsigned int* __restrict__ step_ptr = nullptr) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
+  if (step_ptr && avg_kind) {
+    const unsigned int t = *step_ptr;
+    factor = avg_kind == 1 ? 1.f / (1.f + (float)t) : (t == 0u ? 1.f : factor);
+  }
   const float m = sums[c] / (float)rows;
   float var = sums[C + c] / (float)rows - m * m;
   var = fmaxf(var, 0.f);
@@ -174,7 +182,8 @@ extern "C" {
 // sums: 2*C floats of scratch that must be zero on entry and is zero again on return.
 int rb_bn_fwd_train(const void* x, long long rows, int C, int c_valid, float* sums, float eps, float factor,
                     float* mean, float* istd, float* run_mean, float* run_var, const float* gamma, const float* beta,
-                    const void* residual, void* y, int relu, cudaStream_t st) {
+                    const void* residual, void* y, int relu, int avg_kind, const unsigned int* step_ptr,
+                    cudaStream_t st) {
   if (C % 8) return -10;
   dim3 grid((C + 255) / 256, 1);
   long long gy = rows / 64;
@@ -182,7 +191,8 @@ int rb_bn_fwd_train(const void* x, long long rows, int C, int c_valid, float* su
   if (gy > 256) gy = 256;
   grid.y = (unsigned)gy;
   bn_reduce_kernel<<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0);
-  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, rows, C, eps, factor, mean, istd, run_mean, run_var);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, rows, C, eps, factor, mean, istd, run_mean, run_var,
+                                                      avg_kind, step_ptr);
   bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, mean, istd, gamma, beta,
                                                                 (const bf16*)residual, (bf16*)y, rows, C, c_valid, relu);
   return RB_LAUNCH_OK();

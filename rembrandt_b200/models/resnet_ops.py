@@ -61,9 +61,11 @@ class _BnConv:
                         self.p, self.p, self.P, self.Q, self.conv_out, self.kp, n_valid=self.ko, n_store=self.kp)
         rows = n * self.P * self.Q
         if train:
-            K.bn_fwd_train(self.conv_out, rows, self.kp, self.ko, self.sums, self.eps, self.mov_avg.at_iter(t),
+            # the factor comes from the device-side step counter, so that graph replays keep averaging correctly
+            kind = 1 if self.mov_avg.kind == "cumulative" else 2
+            K.bn_fwd_train(self.conv_out, rows, self.kp, self.ko, self.sums, self.eps, self.mov_avg.factor,
                            self.mean, self.istd, self.v(self.seg_rm), self.v(self.seg_rv), self.v(self.seg_g),
-                           self.v(self.seg_b), residual, out, relu)
+                           self.v(self.seg_b), residual, out, relu, avg_kind=kind, step_ptr=net.step_counter)
         else:
             K.bn_fwd_infer(self.conv_out, rows, self.kp, self.ko, self.eps, self.v(self.seg_rm), self.v(self.seg_rv),
                            self.istd, self.v(self.seg_g), self.v(self.seg_b), residual, out, relu)

@@ -215,10 +215,12 @@ def synth_labels(labels, n, classes, seed, step):
 
 
 def bn_fwd_train(x, rows, C, c_valid, sums, eps, factor, mean, istd, run_mean, run_var, gamma, beta, residual, y,
-                 relu):
+                 relu, avg_kind=0, step_ptr=None):
+    """avg_kind 1 (cumulative) / 2 (exponential, 1 at step 0) derive the averaging factor from the device-side step
+    counter `step_ptr`, so that a captured graph keeps averaging correctly; 0 uses `factor` as given."""
     check(_native.cuda().rb_bn_fwd_train(ptr(x), rows, C, c_valid, ptr(sums), eps, factor, ptr(mean), ptr(istd),
                                          ptr(run_mean), ptr(run_var), ptr(gamma), ptr(beta), ptr(residual), ptr(y),
-                                         int(relu), stream_handle()), "rb_bn_fwd_train")
+                                         int(relu), int(avg_kind), ptr(step_ptr), stream_handle()), "rb_bn_fwd_train")
 
 
 def bn_fwd_infer(x, rows, C, c_valid, eps, run_mean, run_var, istd_tmp, gamma, beta, residual, y, relu):
