@@ -30,7 +30,7 @@ def _lib():
     vp, i32, i64, f32 = C.c_void_p, C.c_int, C.c_longlong, C.c_float
     lib.rb_bn_fwd_train_noalloc.argtypes = [vp, i64, i32, i32, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]
     lib.rb_bn_fwd_train_noalloc.restype = i32
-    lib.rb_bn_fwd_train.argtypes = [vp, i64, i32, i32, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]
+    lib.rb_bn_fwd_train.argtypes = [vp, i64, i32, i32, vp, f32, f32, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, vp, vp]
     lib.rb_bn_fwd_train.restype = i32
     lib.rb_bn_noalloc_strerror.argtypes = [i32]
     lib.rb_bn_noalloc_strerror.restype = C.c_char_p
@@ -56,12 +56,12 @@ def _run_both(lib, rows, channels, seed, with_residual):
         if which == "noalloc":
             rc = lib.rb_bn_fwd_train_noalloc(x.data_ptr(), rows, channels, channels, 1e-5, 0.1, mean.data_ptr(),
                                              istd.data_ptr(), rm.data_ptr(), rv.data_ptr(), gamma.data_ptr(),
-                                             beta.data_ptr(), rp, y.data_ptr(), 1, stream)
+                                             beta.data_ptr(), rp, y.data_ptr(), 1, 0, None, stream)
         else:
             sums = torch.zeros(2 * channels, device=dev)
             rc = lib.rb_bn_fwd_train(x.data_ptr(), rows, channels, channels, sums.data_ptr(), 1e-5, 0.1,
                                      mean.data_ptr(), istd.data_ptr(), rm.data_ptr(), rv.data_ptr(), gamma.data_ptr(),
-                                     beta.data_ptr(), rp, y.data_ptr(), 1, stream)
+                                     beta.data_ptr(), rp, y.data_ptr(), 1, 0, None, stream)
         assert rc == 0, lib.rb_bn_noalloc_strerror(rc)
         torch.cuda.synchronize()
         outs.append((y.float(), mean, istd, rm, rv))
