@@ -56,3 +56,39 @@ def test_a_straggler_only_delays():
 
 def test_data_parallel_training_equals_single_process_on_the_global_batch():
     run_ranks(2, cases.dp_training_matches_single_process, timeout_s=120)
+
+
+def test_plan_buckets_covers_every_parameter_once_in_backward_order():
+    """Bucket plan of the overlapped exchanges: ranges follow the order backward completes them, cover every
+    parameter segment exactly once and respect the size bounds."""
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.parallel.comm import plan_buckets
+    net = Net(zoo.cifar_krizh26(), 4, device="cpu")
+    plan = plan_buckets(net, bucket_elems=16 * 1024, min_bucket_elems=4 * 1024)
+    covered = []
+    last_trigger = len(net.ops)
+    for idx, off, n in plan:
+        assert 0 < n <= 16 * 1024
+        assert idx <= last_trigger, "triggers must not move towards the loss"
+        last_trigger = idx
+        covered.append((off, off + n))
+    covered.sort()
+    for (a0, a1), (b0, b1) in zip(covered, covered[1:]):
+        assert a1 <= b0, "ranges overlap"
+    for s in net.segs:
+        assert any(lo <= s.offset and s.offset + s.numel <= hi for lo, hi in _merged(covered)), s.name
+    # every range becomes available only after the operator that owns its last-written segment has run backward
+    for idx, off, n in plan:
+        owners = [i for i, op in enumerate(net.ops) for s in op.segs if s.offset < off + n and off < s.offset + s.numel]
+        assert min(owners) >= idx
+
+
+def _merged(ranges):
+    out = []
+    for lo, hi in ranges:
+        if out and out[-1][1] == lo:
+            out[-1] = (out[-1][0], hi)
+        else:
+            out.append((lo, hi))
+    return out
