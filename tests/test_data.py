@@ -202,3 +202,30 @@ def test_record_stores_shards_and_episode_lookahead(tmp_path):
     assert frame.shape == (1, 3, 3) and la == [3, 5, -1]
     assert src[2][1] == [7, -1, -1]          # the frame after the unlabeled one; its episode ends
     assert src[3][1] == [2, 9, -1]
+
+
+def test_data_tools_cli(tmp_path, capsys):
+    import json
+    from rembrandt_b200.cli import data_tools
+    from rembrandt_b200.data.lmdb_reader import write_env
+    from rembrandt_b200.data.codecs import encode_caffe_datum
+    from rembrandt_b200.utils import blob
+    # a CIFAR-10 style file of 7 records (1 label byte + 3072 pixel bytes)
+    rng = np.random.default_rng(2)
+    recs = rng.integers(0, 256, (7, 3073), dtype=np.uint8)
+    (tmp_path / "batch.bin").write_bytes(recs.tobytes())
+    data_tools.main(["cifar10-mean", str(tmp_path / "batch.bin"), str(tmp_path / "mean.ndarray")])
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["samples"] == 7 and out["dims"] == [32, 32, 3]
+    mean = blob.read_array_file(str(tmp_path / "mean.ndarray"), "f32")
+    want = recs[:, 1:].astype(np.float64).mean(0).reshape(3, 32, 32)
+    assert np.allclose(mean, want, atol=1e-3)
+    data_tools.main(["dump-header", str(tmp_path / "mean.ndarray")])
+    hdr = json.loads(capsys.readouterr().out.strip().splitlines()[0])
+    assert hdr["dims"] == [32, 32, 3] and hdr["elements"] == 3072
+    data_tools.main(["load-array", str(tmp_path / "mean.ndarray")])
+    assert json.loads(capsys.readouterr().out.strip())["shape"] == [3, 32, 32]
+    write_env(str(tmp_path / "db"), [(b"%08d" % i, encode_caffe_datum(bytes(12), 3, 2, 2, label=i)) for i in range(4)])
+    data_tools.main(["test-lmdb", str(tmp_path / "db"), "--limit", "2"])
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert json.loads(lines[0])["entries"] == 4 and json.loads(lines[2])["label"] == 1
