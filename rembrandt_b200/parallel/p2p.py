@@ -344,7 +344,7 @@ class GossipP2PComm(CommWorker, _P2PBase):
         CommWorker.__init__(self, group)
         self._init_p2p(group, num_slots=8)
         self.mode, self.alpha, self.blocks, self.cfg = mode, alpha, blocks, cfg
-        # synchronous: wait until the peer has published this round's snapshot (always for pair gossip; pull gossip
+        # synchronous: wait until the peer has published the snapshot of the same exchange (always for pair gossip; pull gossip
         # is asynchronous by default and takes whichever snapshot the peer published last)
         self.synchronous = (mode == "pair") if synchronous is None else bool(synchronous)
         self.rng = XorShift128Plus(seed[0] + (0 if mode == "pair" else 1000003 * self.rank), seed[1])
