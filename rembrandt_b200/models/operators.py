@@ -923,6 +923,23 @@ class SoftmaxKLLossOp(Op):
                                      device=self.net.device)
         self.keep_probs = True
 
+    def sample_categories(self, temperature: float = 1.0, generator=None) -> torch.Tensor:
+        """Draw one category per sample (head 0) from softmax(logits / temperature), restricted to the admissible
+        categories when a mask is loaded: the Boltzmann sampling of the gen-1 softmax head (src/layer.rs, prefix-sum
+        CDF + uniform draw). Call after `forward`; not on the training hot path (plain torch ops)."""
+        n = self.net.batch
+        if self.net.is_cuda:
+            logits = self.prev.out.reshape(n, -1)[:, : self.k].float()
+            mask = None if self.mask is None else self.mask.reshape(n, self.heads, self.k)[:, 0].bool()
+        else:
+            logits = self.net._cpu_logits.flatten(1)[:, : self.k].float()
+            mask = None if self._cpu_mask is None else self._cpu_mask.reshape(n, self.heads, self.k)[:, 0]
+        logits = logits / max(float(temperature), 1e-6)
+        if mask is not None:
+            logits = logits.masked_fill(~mask, float("-inf"))
+        probs = torch.softmax(logits, dim=1)
+        return torch.multinomial(probs, 1, generator=generator).squeeze(1)
+
     def load_soft_targets(self, q):
         """q: [B * heads, K] distribution that replaces the one-hot labels; None returns to hard labels."""
         if q is None:

@@ -1,0 +1,58 @@
+"""SGD loop without the shared checkpoint barrier: every worker checkpoints, validates and continues on its own
+clock, on its own local model (the reference's older ``AsyncSgdOpt``, src/opt/sgd/async.rs, which pre-dates the
+shared ``OptSharedData`` barrier and is no longer compiled there).
+
+Intended for the gossip / elastic backends, whose exchanges tolerate workers that are steps apart. Differences to
+``SgdOpt``: no barrier before or after the checkpoint window, no exact synchronisation of the parameters at a
+checkpoint (each rank writes its own parameter files under ``<checkpoint_dir>/rank<r>``), and the displayed training
+statistics are this rank's alone.
+"""
+from __future__ import annotations
+
+import os
+
+from ..optim.sgd import CheckpointBehavior
+from ..trainer import SgdOpt
+from ..utils import checkpoint as ckpt
+
+
+class _LocalStats:
+    """Stand-in for the shared statistics exchange: a rank reports its own numbers."""
+
+    def sync(self, values):
+        return list(values)
+
+
+class AsyncSgdOpt(SgdOpt):
+    def __init__(self, config, engine, **kw):
+        super().__init__(config, engine, **kw)
+        self.shared = _LocalStats()
+
+    def train(self, train_data, valid_data=None, max_iters=None):
+        comm = self.comm
+        # the barrier calls of the synchronous loop become no-ops for the duration of the run
+        saved = (comm.signal_barrier, comm.wait_barrier, comm.barrier)
+        comm.signal_barrier = lambda: None
+        comm.wait_barrier = lambda: True
+        comm.barrier = lambda: None
+        try:
+            return super().train(train_data, valid_data, max_iters)
+        finally:
+            comm.signal_barrier, comm.wait_barrier, comm.barrier = saved
+
+    def _checkpoint_window(self, t, valid_data, t_start):
+        cfg, eng, net = self.cfg, self.engine, self.net
+        eng.flush()
+        eng.synchronize()
+        if cfg.checkpoint == CheckpointBehavior.DISCARD:
+            net.save_params()
+        if cfg.checkpoint_dir:
+            local_dir = os.path.join(cfg.checkpoint_dir, f"rank{self.rank}")
+            os.makedirs(local_dir, exist_ok=True)
+            if cfg.save_iters and t % cfg.save_iters == 0:
+                ckpt.checkpoint_state(net, local_dir, self.rank)
+            ckpt.checkpoint_params(net, t, local_dir)
+        if valid_data is not None and cfg.valid_iters:
+            self.validate(valid_data, cfg.valid_iters, t, t_start)
+        if cfg.checkpoint == CheckpointBehavior.DISCARD:
+            net.restore_params()

@@ -231,3 +231,26 @@ def test_pointwise_heads_reference_path(kind):
         want = 0.5 * ((z - t) ** 2).sum() / 5
     assert abs(loss - float(want)) < 1e-4 * max(1.0, abs(float(want)))
     assert float(net.grads.abs().sum()) > 0
+
+
+def test_softmax_head_sampling_respects_mask_and_temperature():
+    from rembrandt_b200.models import config as C
+    from rembrandt_b200.models.net import Net
+    cfg = C.SequentialOperatorConfig().data3d(C.Data3dCfg((4, 4, 1)))
+    cfg.affine(C.AffineCfg(6)).softmax_kl_loss(C.SoftmaxKLLossCfg(6))
+    net = Net(cfg, 64, device="cpu")
+    x = torch.randint(0, 256, (64, 1, 4, 4), dtype=torch.uint8)
+    mask = torch.ones(64, 6, dtype=torch.bool)
+    mask[:, 2] = False
+    net.loss_op.load_mask(mask)
+    net.load_batch(x, torch.zeros(64, dtype=torch.long))
+    with torch.no_grad():
+        net.forward(False)
+    g = torch.Generator().manual_seed(0)
+    draws = torch.stack([net.loss_op.sample_categories(1.0, g) for _ in range(20)])
+    assert not (draws == 2).any(), "a masked category must never be drawn"
+    assert draws.unique().numel() > 1
+    # a very low temperature draws the arg-max among the admissible categories
+    cold = net.loss_op.sample_categories(1e-4, g)
+    best = net._cpu_logits.flatten(1).masked_fill(~mask, float("-inf")).argmax(1)
+    assert torch.equal(cold, best)

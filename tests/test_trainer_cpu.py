@@ -195,3 +195,21 @@ def test_mimic_training_pulls_student_towards_teacher():
     opt.train([(x, y)] * 60, max_iters=60)
     after = kl()
     assert after < 0.5 * before, (before, after)
+
+
+def test_async_sgd_opt_checkpoints_locally_without_barriers(tmp_path):
+    """The barrier-free loop trains like the synchronous one on a single worker, never calls a barrier, and
+    writes its checkpoints under a per-rank directory."""
+    from rembrandt_b200.optim.async_sgd import AsyncSgdOpt
+    d = str(tmp_path / "run")
+    opt, eng, net = make(batch=16, checkpoint_iters=4, save_iters=4, checkpoint_dir=d)
+    calls = []
+    eng.comm.barrier = lambda: calls.append("barrier")
+    sgd = AsyncSgdOpt(opt, eng, quiet=True)
+    sgd.train(mnist_shape_batches(1, 16, 8), None, max_iters=8)
+    assert eng.iter == 8 and not calls
+    assert os.path.exists(os.path.join(d, "rank0", "params.t_8.blob"))
+    assert os.path.exists(os.path.join(d, "rank0", "state.latest.blob.0"))
+    opt_s, eng_s, net_s = make(batch=16)
+    SgdOpt(opt_s, eng_s, quiet=True).train(mnist_shape_batches(1, 16, 8), None, max_iters=8)
+    assert torch.allclose(net.params.detach(), net_s.params.detach(), atol=1e-6)
