@@ -2,14 +2,17 @@
 
 ``torch.distributed`` (NCCL) is used for plumbing only: rendezvous, exchange of memory handles through
 ``torch.distributed._symmetric_memory``, the broadcast of the shared seed and tiny host-side statistics. The
-gradient all-reduce, the optimizer step that follows it, and the gossip / elastic parameter mixes are single
-kernels from ``csrc/comm_p2p.cu`` that load from and store to the other GPUs' memory directly.
+gradient exchange, the optimizer step that follows it, and the gossip / elastic parameter mixes are kernels from
+``csrc/comm_p2p.cu`` that load from and store to the other GPUs' memory directly.
 
-``FusedAllreduceSgdComm`` additionally overlaps the exchange with the backward pass: the flat gradient vector
-is cut into buckets (25 MB by default) in the order backward produces them; as soon as the operators of a
-bucket have run, the bucket's fused kernel is launched on a separate stream while backward continues.
-Master weights and momentum are sharded over the ranks by that kernel (rank r owns shard r of every bucket);
-``gather_master`` re-assembles full fp32 vectors when a checkpoint needs them.
+``FusedAllreduceSgdComm`` overlaps the exchange with the backward pass: the flat gradient vector is cut into
+buckets (25 MB by default) in the order backward produces them; as soon as the operators of a bucket have run, the
+bucket's kernels are launched on one of two side streams while backward continues. The exchange is push based
+(posted remote stores saturate NVLink from a grid small enough to sit beside the GEMM CTAs; remote loads do not):
+a push kernel copies shard p of the local gradients into peer p's staging buffer, a one-warp kernel waits for the
+peers' flags, and the reducing kernel sums the staged copies, applies 1/N + SGD to its shard and stores the new
+bf16 weights into every peer. Master weights and momentum are sharded over the ranks by that kernel (rank r owns
+shard r of every bucket); ``gather_master`` re-assembles full fp32 vectors when a checkpoint needs them.
 """
 from __future__ import annotations
 
