@@ -98,6 +98,17 @@ def host():
             lib.rb_blob_write.argtypes = [vp, u64, C.POINTER(C.c_uint8), C.c_uint32, C.POINTER(C.c_uint64), vp,
                                           C.c_uint32]
             lib.rb_blob_write.restype = u64
+            lib.rb_loader_create.argtypes = [vp, vp, u64, u64, u64, C.c_uint32, C.c_uint32, u64, C.c_uint32,
+                                             C.c_uint32, C.POINTER(vp), C.POINTER(vp)]
+            lib.rb_loader_create.restype = vp
+            lib.rb_loader_acquire.argtypes = [vp, C.POINTER(C.c_uint64)]
+            lib.rb_loader_acquire.restype = i32
+            lib.rb_loader_release.argtypes = [vp, i32]
+            lib.rb_loader_release.restype = None
+            lib.rb_loader_destroy.argtypes = [vp]
+            lib.rb_loader_destroy.restype = None
+            lib.rb_loader_sample_index.argtypes = [u64, u64, C.c_uint32, u64, u64]
+            lib.rb_loader_sample_index.restype = u64
             lib.rb_xs_seed.argtypes = [C.POINTER(XorShift), u64, u64]
             lib.rb_xs_seed.restype = None
             lib.rb_xs_next.argtypes = [C.POINTER(XorShift)]

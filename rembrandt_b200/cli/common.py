@@ -48,6 +48,9 @@ def base_parser(desc, **defaults):
     ap.add_argument("--synthetic-size", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--native-loader", type=int, default=0, metavar="THREADS",
+                    help="assemble training batches with this many C++ prefetch threads (shuffled epochs over the "
+                         "rank's shard, pinned ring buffers) instead of the Python iterators")
     ap.add_argument("--straggler-ranks", type=int, nargs="*", default=[])
     ap.add_argument("--straggler-max-delay-ms", type=int, default=0)
     ap.add_argument("--report-port", type=int, default=0, help="serve a live loss report on this port")
@@ -112,9 +115,17 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
     if rank == 0:
         print(net.describe())
     engine = StepEngine(net, opt, worker, use_graph=not args.no_graph)
-    train_iter = BatchIter(AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world),
-                                                                   seed=(args.seed + rank, 99))),
-                           args.batch, dims)
+    if args.native_loader > 0:
+        from ..data.datasets import source_arrays
+        from ..data.native_loader import NativeBatchLoader
+        from ..utils.rng import partition_range
+        imgs, lbls = source_arrays(source)
+        train_iter = NativeBatchLoader(imgs, lbls, args.batch, mode="shuffled", seed=args.seed + rank,
+                                       threads=args.native_loader, shard=partition_range(len(source), world, rank))
+    else:
+        train_iter = BatchIter(AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world),
+                                                                       seed=(args.seed + rank, 99))),
+                               args.batch, dims)
     valid_iter = None
     if valid_source is not None:
         valid_iter = BatchIter(CyclicSampleDataIter(partition_shard(valid_source, rank, world)), args.batch, dims)

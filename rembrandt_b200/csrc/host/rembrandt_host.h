@@ -55,6 +55,18 @@ int rb_cifar_split(const uint8_t* buf, uint64_t len, uint64_t first, uint64_t co
 // Per-pixel mean over u8 images laid out [n][elems]; accumulates in double.
 void rb_mean_u8(const uint8_t* images, uint64_t n, uint64_t elems, float* mean_out);
 
+// ---- prefetching batch loader (batch_loader.cc) -------------------------------------------------------
+// Worker threads assemble batches of `batch` samples (u8 images of `elems` bytes + i32 labels) of the shard [lo, hi)
+// into a ring of `nslots` caller-owned slots; the order of samples depends only on (mode, seed, position):
+// mode 0 cyclic, 1 random with replacement, 2 shuffled epochs. Returns null on bad arguments.
+void* rb_loader_create(const uint8_t* images, const int32_t* labels, uint64_t elems, uint64_t lo, uint64_t hi,
+                       uint32_t batch, uint32_t mode, uint64_t seed, uint32_t threads, uint32_t nslots,
+                       uint8_t** image_slots, int32_t** label_slots);
+int rb_loader_acquire(void* handle, uint64_t* batch_number);   // blocks; slot index, or -1 after destroy
+void rb_loader_release(void* handle, int slot);
+void rb_loader_destroy(void* handle);
+uint64_t rb_loader_sample_index(uint64_t lo, uint64_t hi, uint32_t mode, uint64_t seed, uint64_t pos);
+
 #ifdef __cplusplus
 }
 #endif

@@ -19,6 +19,21 @@ from .. import _native
 from ..models.descriptor import DatasetSplit, load_data
 
 
+def source_arrays(source):
+    """(images uint8 [n, C, H, W], labels int32 [n]) of a whole source, for the native batch loader. MNIST and
+    CIFAR-10 files map directly (no per-sample Python work); any other source is materialised sample by sample."""
+    if hasattr(source, "as_arrays"):
+        return source.as_arrays()
+    n = len(source)
+    first, _ = source[0]
+    imgs = np.empty((n,) + tuple(np.asarray(first).shape), dtype=np.uint8)
+    lbls = np.empty(n, dtype=np.int32)
+    for i in range(n):
+        im, lb = source[i]
+        imgs[i], lbls[i] = im, lb
+    return imgs, lbls
+
+
 class DataSource:
     dims: Tuple[int, int, int]   # (W, H, C) as in the reference
     num_classes: int
@@ -95,6 +110,11 @@ class MnistDataSource(DataSource):
         o = self._ioff + i * w * h
         return self._img.arr[o:o + w * h].reshape(1, h, w), int(self._lbl.arr[self._loff + i])
 
+    def as_arrays(self):
+        w, h, _ = self.dims
+        imgs = self._img.arr[self._ioff:self._ioff + self.n * w * h].reshape(self.n, 1, h, w)   # a view of the mapping
+        return imgs, self._lbl.arr[self._loff:self._loff + self.n].astype(np.int32)
+
 
 class Cifar10DataSource(DataSource):
     """Records of 1 label byte + 3072 planar RGB bytes (src/data_new.rs:797-883)."""
@@ -124,6 +144,9 @@ class Cifar10DataSource(DataSource):
         if rc != 0:
             raise IndexError("record range outside the file")
         return imgs, lbls
+
+    def as_arrays(self):
+        return self.batch(0, self.n)
 
 
 def compute_mean(source: DataSource, limit: Optional[int] = None) -> np.ndarray:

@@ -229,3 +229,37 @@ def test_data_tools_cli(tmp_path, capsys):
     data_tools.main(["test-lmdb", str(tmp_path / "db"), "--limit", "2"])
     lines = capsys.readouterr().out.strip().splitlines()
     assert json.loads(lines[0])["entries"] == 4 and json.loads(lines[2])["label"] == 1
+
+
+@pytest.mark.parametrize("mode,threads", [("cyclic", 1), ("cyclic", 4), ("random", 3), ("shuffled", 4)])
+def test_native_batch_loader_order_is_deterministic_and_sharded(mode, threads):
+    from rembrandt_b200.data.native_loader import NativeBatchLoader
+    n, batch = 103, 8
+    images = (np.arange(n, dtype=np.uint32)[:, None, None, None] * np.ones((1, 2, 3, 3), dtype=np.uint32) % 251).astype(np.uint8)
+    labels = np.arange(n, dtype=np.int32) + 1000
+    lo, hi = 10, 93
+    runs = []
+    for _ in range(2):
+        ld = NativeBatchLoader(images, labels, batch, mode=mode, seed=7, threads=threads, slots=5, shard=(lo, hi),
+                               pin=False, max_batches=40)
+        seen = []
+        for k, (im, lb) in enumerate(ld):
+            idx = lb.numpy() - 1000
+            assert ((idx >= lo) & (idx < hi)).all()
+            assert np.array_equal(im.numpy().reshape(batch, -1)[:, 0], images[idx].reshape(batch, -1)[:, 0])
+            assert [ld.sample_index(k * batch + i) for i in range(batch)] == idx.tolist()
+            seen.append(idx.copy())
+        ld.close()
+        assert len(seen) == 40
+        runs.append(np.concatenate(seen))
+    assert np.array_equal(runs[0], runs[1]), "order must not depend on thread timing"
+    flat = runs[0]
+    if mode == "cyclic":
+        assert np.array_equal(flat, lo + np.arange(flat.size) % (hi - lo))
+    if mode == "shuffled":
+        ep = hi - lo
+        for e in range(flat.size // ep):
+            assert sorted(flat[e * ep:(e + 1) * ep].tolist()) == list(range(lo, hi)), "every epoch is a permutation"
+        assert not np.array_equal(flat[:ep], flat[ep:2 * ep])
+    if mode == "random":
+        assert len(set(flat.tolist())) > (hi - lo) // 2
