@@ -1,25 +1,32 @@
 // Persistent, warp-specialised tcgen05 GEMM / implicit-GEMM convolution for sm_100a.
 //
-//   warp 0      TMA producer (one elected lane): tiled or im2col loads into a ring of smem stages
+//   warp 0      A producer: TMA loads (tiled, im2col, or halo tiles) of the A operand, one lane per box
 //   warp 1      MMA issuer (one elected lane): tcgen05.mma, fp32 accumulators in TMEM; owns TMEM alloc/dealloc
-//   warps 2..9  epilogue: tcgen05.ld -> bias / ReLU / mask -> swizzled smem -> TMA store (bf16), or fp32
-//               store / red.add (split-K). Two warps share each TMEM lane quarter and alternate column slabs:
-//               with one warp per scheduler the epilogue is bound by instruction latency, not bandwidth.
+//   warps 2..9  epilogue: tcgen05.ld -> bias / ReLU / mask -> swizzled smem -> TMA store (bf16), or fp32 TMA
+//               store / reduce-add (split-K, gradient accumulation). Two warps share each TMEM lane quarter and
+//               alternate column slabs: with one warp per scheduler the epilogue is bound by instruction latency.
+//   warp 10     B producer: TMA loads of the B operand, one lane per box (or the resident panel, once)
 //
-// The kernel is bound by the bytes it must bring into shared memory per MMA (measured: ~30 GB/s per SM of
-// TMA fill against a tensor pipe that could consume several times that), so the tile shape is chosen to cut
-// those bytes:
-//   * a work item may cover two 128-row sub-tiles (mt = 2) that share one B stage and use two accumulators;
-//   * when the whole B panel (every k-block of the filter bank) fits in shared memory and the CTA only ever
-//     needs that one panel, it is loaded once per CTA and stays resident (b_resident) while A streams;
-//   * split-K (fp32 red.add epilogue) spreads long reductions over all SMs.
+// What was measured on this kernel and shaped it:
+//   * one thread's TMA loads do not overlap (a box takes ~220 ns whatever its size) while loads issued by different
+//     threads do, so the loads of a stage are spread over two producer warps and over lanes;
+//   * im2col-mode loads cost ~2.8 ns per pixel row per SM and tiled loads 1-1.7 ns per row, independent of the
+//     row's bytes: rows are kept 128 bytes wide (64 channels) even when that means a half-empty, zero-filled chunk;
+//   * a tcgen05.mma (cta_group::1, M = 128, K = 16) costs ~200 cycles however narrow N is, so tiles are as wide as
+//     the layer allows (N <= 256);
+//   * a work item may cover two 128-row sub-tiles (mt = 2) that share one B stage and use two accumulators; when
+//     the whole B panel fits in shared memory and the CTA only ever needs that one panel, it is loaded once per CTA
+//     and stays resident (b_resident); split-K (fp32 reduce-add epilogue) spreads long reductions over all SMs;
+//   * which of these a forward / data-grad launch uses is decided by timing the candidates the first time a shape
+//     is seen (the launches are idempotent), see `launch`.
 //   * stride-1 convolutions can load A as column-shifted halo tiles (A_HALO_K): a sub-tile is hl_rows output rows
 //     of one image laid out at a row pitch of hl_pitch positions (128 rows of the MMA; positions past the image
 //     width or height are computed and dropped by the clipping TMA store). For filter column s the producer
 //     loads ONE tile of (mt * hl_rows + R - 1) input rows x hl_pitch columns starting at column s - pad (plain
 //     tiled TMA, zero fill outside the image); the R filter rows of that column are then descriptor offsets of
 //     r * hl_pitch rows into the same tile (multiples of the swizzle atom), so A is filled S times per item
-//     instead of R * S times. B streams through its own ring, one (r, s, channel chunk) tile per stage.
+//     instead of R * S times. B streams through its own ring, one (r, s, channel chunk) tile per stage. Taken
+//     only when forced (RB_GEMM_FORCE_HALO=1): its padded tiles add MMA work, and MMA issue is what binds there.
 // With two accumulator sets in TMEM the epilogue of work item i overlaps the main loop of item i+1; a
 // 256 x 256 item needs all 512 columns and runs without that overlap.
 //
