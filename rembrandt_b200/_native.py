@@ -98,6 +98,17 @@ def host():
             lib.rb_blob_write.argtypes = [vp, u64, C.POINTER(C.c_uint8), C.c_uint32, C.POINTER(C.c_uint64), vp,
                                           C.c_uint32]
             lib.rb_blob_write.restype = u64
+            lib.rb_lmdb_open.argtypes = [C.c_char_p]
+            lib.rb_lmdb_open.restype = vp
+            for name, res in (("rb_lmdb_entries", u64), ("rb_lmdb_depth", C.c_uint32), ("rb_lmdb_page_size", C.c_uint32)):
+                getattr(lib, name).argtypes = [vp]
+                getattr(lib, name).restype = res
+            lib.rb_lmdb_seek.argtypes = [vp, vp, C.c_uint32]
+            lib.rb_lmdb_seek.restype = i32
+            lib.rb_lmdb_next.argtypes = [vp, C.POINTER(vp), C.POINTER(C.c_uint32), C.POINTER(vp), C.POINTER(u64)]
+            lib.rb_lmdb_next.restype = i32
+            lib.rb_lmdb_close.argtypes = [vp]
+            lib.rb_lmdb_close.restype = None
             lib.rb_loader_create.argtypes = [vp, vp, u64, u64, u64, C.c_uint32, C.c_uint32, u64, C.c_uint32,
                                              C.c_uint32, C.POINTER(vp), C.POINTER(vp)]
             lib.rb_loader_create.restype = vp

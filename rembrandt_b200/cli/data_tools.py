@@ -47,8 +47,8 @@ def load_array(args):
 
 def test_lmdb(args):
     from ..data.codecs import decode_caffe_datum
-    from ..data.lmdb_reader import LmdbEnv
-    with LmdbEnv(args.path) as env:
+    from ..data.lmdb_reader import open_env
+    with open_env(args.path) as env:
         print(json.dumps({"entries": len(env), "depth": env.depth, "page_size": env.psize}))
         for i, (k, v) in enumerate(env.items()):
             if i >= args.limit:

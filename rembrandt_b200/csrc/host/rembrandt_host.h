@@ -67,6 +67,16 @@ void rb_loader_release(void* handle, int slot);
 void rb_loader_destroy(void* handle);
 uint64_t rb_loader_sample_index(uint64_t lo, uint64_t hi, uint32_t mode, uint64_t seed, uint64_t pos);
 
+// ---- read-only LMDB reader (lmdb_reader.cc) ------------------------------------------------------------
+// `path` is the environment directory or its data file. Keys and values point into the memory mapping.
+void* rb_lmdb_open(const char* path);                       // null on failure
+uint64_t rb_lmdb_entries(void* env);
+uint32_t rb_lmdb_depth(void* env);
+uint32_t rb_lmdb_page_size(void* env);
+int rb_lmdb_seek(void* env, const uint8_t* key, uint32_t klen);   // first key >= key (klen 0: first key); 1 if found
+int rb_lmdb_next(void* env, const uint8_t** key, uint32_t* klen, const uint8_t** val, uint64_t* vlen);  // 1, or 0 at end
+void rb_lmdb_close(void* env);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,10 @@
 """Read-only access to LMDB environments (the Caffe image databases the reference reads through its `lmdb`
 bindings: src/data/lmdb_data.rs:50-152, src/data_new.rs:885-997), with no dependency on liblmdb.
 
+Two implementations of the same reader: the C++ cursor in csrc/host/lmdb_reader.cc (`NativeLmdbEnv`, what
+`open_env` returns) and the pure-Python `LmdbEnv` below (the executable description of the format, and the
+cross-check in the tests).
+
 Only what a reader needs is implemented: the newer of the two meta pages, the main database's B+tree (branch and
 leaf pages, overflow pages for large values), ordered iteration, `get` and cursor `seek` (first key >= a given key).
 Sub-databases, duplicate-sorted databases and writing real environments are out of scope; `write_env` produces a
@@ -188,6 +192,59 @@ class LmdbEnv:
         return self.entries
 
 
+class NativeLmdbEnv:
+    """The same interface as `LmdbEnv` over the C++ reader (memory-mapped file, cursor in native code)."""
+
+    def __init__(self, path: str):
+        import ctypes as C
+        from .. import _native
+        self._C = C
+        self._lib = _native.host()
+        self._h = self._lib.rb_lmdb_open(os.fsencode(path))
+        if not self._h:
+            raise LmdbError(f"{path}: not a readable LMDB environment")
+        self.entries = int(self._lib.rb_lmdb_entries(self._h))
+        self.depth = int(self._lib.rb_lmdb_depth(self._h))
+        self.psize = int(self._lib.rb_lmdb_page_size(self._h))
+
+    def close(self):
+        if self._h:
+            self._lib.rb_lmdb_close(self._h)
+            self._h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def __len__(self):
+        return self.entries
+
+    def items(self, start: Optional[bytes] = None) -> Iterator[Tuple[bytes, bytes]]:
+        C = self._C
+        key = start or b""
+        if not self._lib.rb_lmdb_seek(self._h, key, len(key)):
+            return
+        kp, vp_ = C.c_void_p(), C.c_void_p()
+        kl, vl = C.c_uint32(), C.c_uint64()
+        while self._lib.rb_lmdb_next(self._h, C.byref(kp), C.byref(kl), C.byref(vp_), C.byref(vl)):
+            yield C.string_at(kp.value, kl.value), C.string_at(vp_.value, vl.value)
+
+    def get(self, key: bytes) -> Optional[bytes]:
+        for k, v in self.items(key):
+            return v if k == key else None
+        return None
+
+
+def open_env(path: str):
+    """The native reader when the host library is available, else the Python one."""
+    try:
+        return NativeLmdbEnv(path)
+    except (OSError, AttributeError):
+        return LmdbEnv(path)
+
+
 class LmdbCaffeShard:
     """The part [lo, hi) of a Caffe image database that belongs to worker `rank` of `world`: records are decoded
     from `Datum` messages; the cursor is positioned with a seek on the zero-padded record number, as the reference
@@ -195,7 +252,7 @@ class LmdbCaffeShard:
 
     def __init__(self, path: str, rank: int = 0, world: int = 1, codec=None):
         from .codecs import decode_caffe_datum
-        self.env = LmdbEnv(path)
+        self.env = open_env(path)
         self.lo, self.hi = partition_range(len(self.env), world, rank)
         self._decode = decode_caffe_datum
         self.codec = codec

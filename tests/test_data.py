@@ -131,7 +131,7 @@ def test_codecs_and_caffe_datum():
 def test_lmdb_reader_round_trip_with_depth_and_overflow(tmp_path):
     """The dependency-free LMDB reader: ordered iteration, get, cursor seek, overflow values, multi-level tree."""
     import random
-    from rembrandt_b200.data.lmdb_reader import LmdbEnv, write_env
+    from rembrandt_b200.data.lmdb_reader import LmdbEnv, NativeLmdbEnv, write_env
     rnd = random.Random(5)
     items = []
     for i in range(700):
@@ -141,18 +141,19 @@ def test_lmdb_reader_round_trip_with_depth_and_overflow(tmp_path):
     for cap in (0, 5):           # natural fan-out, and 5 nodes per page (a tree of depth >= 4)
         d = tmp_path / f"db{cap}"
         write_env(str(d), items, max_leaf_nodes=cap)
-        with LmdbEnv(str(d)) as env:
-            assert len(env) == 700
-            if cap:
-                assert env.depth >= 4
-            got = list(env.items())
-            assert got == sorted(items)
-            assert env.get(b"00000123") == dict(items)[b"00000123"]
-            assert env.get(b"00000699") == dict(items)[b"00000699"]
-            assert env.get(b"nope") is None
-            tail = list(env.items(b"00000650"))
-            assert [k for k, _ in tail] == [b"%08d" % i for i in range(650, 700)]
-            assert next(iter(env.items(b"000001235")))[0] == b"00000124"   # seek lands on the next larger key
+        for cls in (LmdbEnv, NativeLmdbEnv):     # the Python reader and the C++ cursor must agree
+            with cls(str(d)) as env:
+                assert len(env) == 700
+                if cap:
+                    assert env.depth >= 4
+                got = list(env.items())
+                assert got == sorted(items)
+                assert env.get(b"00000123") == dict(items)[b"00000123"]
+                assert env.get(b"00000699") == dict(items)[b"00000699"]
+                assert env.get(b"nope") is None
+                tail = list(env.items(b"00000650"))
+                assert [k for k, _ in tail] == [b"%08d" % i for i in range(650, 700)]
+                assert next(iter(env.items(b"000001235")))[0] == b"00000124"   # seek lands on the next larger key
 
 
 def test_lmdb_caffe_shard_partitions_and_decodes(tmp_path):
