@@ -141,3 +141,54 @@ def test_overlapped_local_update_equals_single_sweep(use_graph):
     for a, b in zip(*finals):
         assert torch.allclose(a.float(), b.float(), rtol=1e-3, atol=2e-4)
     assert K.read_status() == 0
+
+
+def test_residual_network_matches_reference_path_and_averages_statistics():
+    """Batch-normalised residual blocks (identity + strided projection) on the device against the CPU path:
+    loss, gradients, and the running statistics after two steps (factor 1 at step 0, then 0.1)."""
+    from rembrandt_b200.models.config import (BNormConv2dCfg, ProjStackResConv2dCfg, StackResConv2dCfg)
+    k = ParamsInit.kaiming()
+
+    def cfg_fn():
+        return (SequentialOperatorConfig().data3d(Data3dCfg((16, 16, 3), normalize=True))
+                .bnorm_conv2d(BNormConv2dCfg(3, 1, 1, 32, Act.RECT, k), "stem")
+                .stack_res_conv2d(StackResConv2dCfg(k), "res1")
+                .proj_stack_res_conv2d(ProjStackResConv2dCfg(64, None, k), "res2")
+                .pool2d(Pool2dCfg(8, 1, 0, PoolKind.AVERAGE), "gap")
+                .affine(AffineCfg(10, Act.IDENTITY, ParamsInit.xavier()), "fc")
+                .softmax_kl_loss(SoftmaxKLLossCfg(10)))
+
+    g = Net(cfg_fn(), 8, device="cuda", seed=(3, 4))
+    c = Net(cfg_fn(), 8, device="cpu", seed=(3, 4))
+    with torch.no_grad():
+        c.params.copy_(g.params16.float().cpu())
+    torch.manual_seed(0)
+    for step in range(2):
+        x = torch.randint(0, 256, (8, 3, 16, 16), dtype=torch.uint8)
+        y = torch.randint(0, 10, (8,))
+        g.load_batch(x.cuda(), y.cuda().int())
+        c.load_batch(x, y)
+        g.reset_grads()
+        c.reset_grads()
+        g.forward(True, step)
+        g.backward()
+        c.forward(True, step)
+        c.backward()
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        gl, cl = g.read_stats()[0], c.read_stats()[0]
+        assert abs(gl - cl) < 5e-2 * max(1.0, abs(cl)), (step, gl, cl)
+    gg, cg = g.grads.cpu(), c.grads
+    for seg in g.segs:
+        a, b = gg[seg.offset: seg.offset + seg.numel], cg[seg.offset: seg.offset + seg.numel]
+        if not seg.trainable:
+            continue
+        # bf16 activations and deltas through five normalised convolutions: the error of the deepest layer's
+        # gradient reaches ~13 % in Frobenius norm; a wrong kernel gives order-one errors
+        rel = float((a - b).norm() / b.norm().clamp_min(1e-12))
+        assert rel < 0.2, f"{seg.name}: relative error {rel:.4g}"
+    # running mean / variance of the stem after step 0 (factor 1) and step 1 (factor 0.1)
+    stem_g, stem_c = g.hidden_ops[0].u, c.hidden_ops[0].u
+    for seg_g, seg_c in ((stem_g.seg_rm, stem_c.seg_rm), (stem_g.seg_rv, stem_c.seg_rv)):
+        a, b = g.seg_view(seg_g).float().cpu(), c.seg_view(seg_c).detach()
+        assert torch.allclose(a, b, rtol=5e-2, atol=5e-3), float((a - b).abs().max())
