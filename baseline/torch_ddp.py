@@ -95,16 +95,22 @@ class CifarNet(nn.Module):
         return self.f(x.flatten(1))
 
 
-MODELS = {"alexnet": (AlexNet, 227, 3, 1000), "nin": (NiN, 224, 3, 1000), "lenet": (LeNet, 28, 1, 10),
-          "cifar": (CifarNet, 32, 3, 10)}
+def _resnet18():
+    import torchvision
+    return torchvision.models.resnet18(weights=None, num_classes=1000)
+
+
+# name: (constructor, side of the staged image, channels, classes, side of the random crop fed to the network)
+MODELS = {"alexnet": (AlexNet, 227, 3, 1000, 227), "nin": (NiN, 224, 3, 1000, 224), "lenet": (LeNet, 28, 1, 10, 28),
+          "cifar": (CifarNet, 32, 3, 10, 32), "resnet18": (_resnet18, 256, 3, 1000, 224)}
 
 
 class TorchBaseline:
     """One data-parallel replica; `step(images_u8, labels)` does input cast, forward, backward, all-reduce, SGD."""
 
     def __init__(self, model="alexnet", batch=128, world=1, rank=0, device="cuda", lr=0.01, momentum=0.9, wd=5e-4):
-        cls, hw, c, k = MODELS[model]
-        self.hw, self.c, self.k, self.batch = hw, c, k, batch
+        cls, hw, c, k, crop = MODELS[model]
+        self.hw, self.c, self.k, self.batch, self.crop = hw, c, k, batch, crop
         self.device = torch.device(device)
         torch.manual_seed(0)
         net = cls().to(self.device).to(memory_format=torch.channels_last)
@@ -118,6 +124,11 @@ class TorchBaseline:
     def step(self, images_u8, labels):
         x = images_u8.to(self.device, non_blocking=True)
         y = labels.to(self.device, non_blocking=True).long()
+        if self.crop < self.hw:   # one random crop offset per batch + flip coin, as torchvision pipelines do per sample
+            oy, ox = (int(v) for v in torch.randint(0, self.hw - self.crop + 1, (2,)))
+            x = x[:, :, oy:oy + self.crop, ox:ox + self.crop]
+            if int(torch.randint(0, 2, (1,))):
+                x = x.flip(-1)
         x = (x.float() - 127.5) * (1.0 / 73.9)
         x = x.contiguous(memory_format=torch.channels_last)
         with torch.autocast("cuda", dtype=torch.bfloat16):

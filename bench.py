@@ -37,6 +37,9 @@ MODELS = {
     "nin": (224, 3, 1000, 64),
     "lenet": (28, 1, 10, 128),
     "cifar": (32, 3, 10, 128),
+    # the reference's enabled ImageNet tool trains ResNet-18 at batch 32 per worker (tools/new-dist-train-imagenet.rs):
+    # 256 x 256 staged images, random 224 crop + flip + lighting noise on the GPU
+    "resnet18": (256, 3, 1000, 32),
 }
 
 
