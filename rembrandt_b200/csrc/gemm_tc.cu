@@ -1095,7 +1095,7 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   const int upper_w = (Q - 1) * stride - pad_w - (W - 1);
   p.a_split = pick_box_split("RB_GEMM_A_SPLIT", BM, p.bk, 1);
   p.b_split = pick_box_split("RB_GEMM_B_SPLIT", p.bn, p.bk, 1);
-  if (R == 1 && S == 1 && stride == 1 && pad_h == 0 && pad_w == 0) {
+  if (R == 1 && S == 1 && stride == 1 && pad_h == 0 && pad_w == 0 && P == H && Q == W) {
     // a 1 x 1 convolution is a plain GEMM over the pixel rows: tiled loads, which the TMA unit serves 2-3x faster
     // per row than im2col-mode loads
     p.a_mode = A_TILED_K;

@@ -16,10 +16,19 @@ from typing import List, Optional
 import torch
 import torch.nn.functional as F
 
+import os
+
 from ..ops import layout
 from ..ops import native_ops as K
+from ..ops.conv_strided import dgrad_strided_tc
 from ..ops.native_ops import pad_channels
 from . import config as C
+
+
+def _strided_dgrad_on_tensor_cores() -> bool:
+    """Strided data-grad by output phases on the tensor-core kernel (ops/conv_strided.py) instead of the CUDA-core
+    kernel; RB_STRIDED_DGRAD_TC=0 selects the latter."""
+    return os.environ.get("RB_STRIDED_DGRAD_TC", "1") == "1"
 
 
 class ParamSeg:
@@ -576,8 +585,13 @@ class Conv2dOp(Op):
                                 r - 1 - p, h, w, self.prev.dout, self.cp, mask_src=mask, n_valid=self.in_c,
                                 n_store=self.cp)
             else:
-                K.conv_direct_dgrad(self.dout, w16, self.prev.dout, mask, n, h, w, self.cp, ko, self.out_cp, r, r, s,
-                                    p, p, self.P, self.Q)
+                done = False
+                if _strided_dgrad_on_tensor_cores():
+                    done = dgrad_strided_tc(self.dout, n, self.P, self.Q, self.out_cp, w16, ko, self.cp, self.in_c, r, r,
+                                            s, p, h, w, self.prev.dout, mask)
+                if not done:
+                    K.conv_direct_dgrad(self.dout, w16, self.prev.dout, mask, n, h, w, self.cp, ko, self.out_cp, r, r,
+                                        s, p, p, self.P, self.Q)
 
     # ---- parameters in reference layout
     def _w_ref(self, w_int):

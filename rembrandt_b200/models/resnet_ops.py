@@ -87,8 +87,15 @@ class _BnConv:
                                 self.k - 1 - self.p, self.k - 1 - self.p, self.h, self.w, dx, self.cp, mask_src=mask,
                                 n_valid=self.in_c, n_store=self.cp)
             else:
-                K.conv_direct_dgrad(self.dconv, w16, dx, mask, n, self.h, self.w, self.cp, self.ko, self.kp, self.k,
-                                    self.k, self.s, self.p, self.p, self.P, self.Q)
+                from .operators import _strided_dgrad_on_tensor_cores
+                from ..ops.conv_strided import dgrad_strided_tc
+                done = False
+                if _strided_dgrad_on_tensor_cores():
+                    done = dgrad_strided_tc(self.dconv, n, self.P, self.Q, self.kp, w16, self.ko, self.cp, self.in_c,
+                                            self.k, self.k, self.s, self.p, self.h, self.w, dx, mask)
+                if not done:
+                    K.conv_direct_dgrad(self.dconv, w16, dx, mask, n, self.h, self.w, self.cp, self.ko, self.kp, self.k,
+                                        self.k, self.s, self.p, self.p, self.P, self.Q)
 
     # ---- parameters
     def init_params(self, rng):

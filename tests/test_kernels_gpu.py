@@ -203,6 +203,26 @@ def test_conv_direct_dgrad_strided():
     close(layout.from_nhwc_padded(dx, C), ref)
 
 
+@pytest.mark.parametrize("case", [(2, 32, 15, 15, 48, 3, 2, 1), (2, 64, 16, 16, 64, 1, 2, 0), (3, 32, 12, 14, 32, 3, 2, 1),
+                                  (2, 64, 28, 28, 128, 3, 2, 1)])
+def test_conv_dgrad_strided_by_phases_on_tensor_cores(case):
+    """Strided data-grad as s x s stride-1 sub-convolutions on the tensor-core kernel, with the ReLU mask."""
+    from rembrandt_b200.ops.conv_strided import dgrad_strided_tc
+    N, C, H, W, Ko, R, stride, pad = case
+    Cp, Kp, x, w, b, P, Q = _conv_setup(*case, seed=8)
+    dy = bf(torch.randn(N, Ko, P, Q, device=DEV))
+    mask = bf(torch.randn(N, C, H, W, device=DEV))
+    dx = torch.full((N, H, W, Cp), float("nan"), device=DEV, dtype=torch.bfloat16)
+    wi = layout.conv_weight_to_internal(w, Cp).bfloat16()
+    ok = dgrad_strided_tc(layout.to_nhwc_padded(dy, Kp), N, P, Q, Kp, wi, Ko, Cp, C, R, R, stride, pad, H, W, dx,
+                          layout.to_nhwc_padded(mask, Cp))
+    assert ok
+    status_ok()
+    ref = torch.autograd.grad(F.conv2d(x.requires_grad_(), w, stride=stride, padding=pad), x, dy)[0] * (mask > 0)
+    close(layout.from_nhwc_padded(dx, C), ref)
+    assert (dx[..., C:].float() == 0).all()
+
+
 @pytest.mark.parametrize("case", CONV_CASES)
 def test_conv_wgrad_tc(case, tile_mode):
     N, C, H, W, Ko, R, stride, pad = case

@@ -88,3 +88,25 @@ def test_schedules():
     pol = StepSizeSchedule.from_annealing_policy(0.01, {"kind": "step", "step_iters": 10, "decay": 0.5})
     assert pol.at_iter(25) == 0.01 * 0.25
     assert StepSizeSchedule.from_annealing_policy(0.02, None).at_iter(5) == 0.02
+
+
+import pytest as _pytest
+
+
+@_pytest.mark.parametrize("k,stride,pad,hw", [(3, 2, 1, 15), (3, 2, 1, 16), (1, 2, 0, 14), (7, 2, 3, 21), (5, 3, 2, 17),
+                                              (3, 2, 0, 11), (4, 2, 1, 12)])
+def test_strided_data_grad_phase_decomposition_equals_autograd(k, stride, pad, hw):
+    """The arithmetic of the phase-by-phase strided data-grad (what the tensor-core path computes) against autograd."""
+    import torch
+    import torch.nn.functional as F
+    from rembrandt_b200.ops.conv_strided import dgrad_by_phases_reference, phase_plan
+    torch.manual_seed(k * 100 + stride * 10 + pad)
+    N, C, Ko = 2, 5, 7
+    x = torch.randn(N, C, hw, hw + 1, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(Ko, C, k, k, dtype=torch.float64)
+    y = F.conv2d(x, w, stride=stride, padding=pad)
+    dy = torch.randn_like(y)
+    ref = torch.autograd.grad(y, x, dy)[0]
+    got = dgrad_by_phases_reference(dy, w, hw, hw + 1, stride, pad)
+    assert torch.allclose(got, ref, atol=1e-10), float((got - ref).abs().max())
+    assert len(phase_plan(hw, hw + 1, k, k, stride, pad)) == stride * stride
