@@ -587,8 +587,10 @@ class Conv2dOp(Op):
             else:
                 done = False
                 if _strided_dgrad_on_tensor_cores():
+                    if not hasattr(self, "_sd_cache"):
+                        self._sd_cache = {}
                     done = dgrad_strided_tc(self.dout, n, self.P, self.Q, self.out_cp, w16, ko, self.cp, self.in_c, r, r,
-                                            s, p, h, w, self.prev.dout, mask)
+                                            s, p, h, w, self.prev.dout, mask, cache=self._sd_cache)
                 if not done:
                     K.conv_direct_dgrad(self.dout, w16, self.prev.dout, mask, n, h, w, self.cp, ko, self.out_cp, r, r,
                                         s, p, p, self.P, self.Q)

@@ -91,8 +91,11 @@ class _BnConv:
                 from ..ops.conv_strided import dgrad_strided_tc
                 done = False
                 if _strided_dgrad_on_tensor_cores():
+                    if not hasattr(self, "_sd_cache"):
+                        self._sd_cache = {}
                     done = dgrad_strided_tc(self.dconv, n, self.P, self.Q, self.kp, w16, self.ko, self.cp, self.in_c,
-                                            self.k, self.k, self.s, self.p, self.h, self.w, dx, mask)
+                                            self.k, self.k, self.s, self.p, self.h, self.w, dx, mask,
+                                            cache=self._sd_cache)
                 if not done:
                     K.conv_direct_dgrad(self.dconv, w16, dx, mask, n, self.h, self.w, self.cp, self.ko, self.kp, self.k,
                                         self.k, self.s, self.p, self.p, self.P, self.Q)

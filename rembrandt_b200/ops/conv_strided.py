@@ -71,10 +71,11 @@ def dgrad_by_phases_reference(dy: torch.Tensor, w: torch.Tensor, H: int, W: int,
     return dx
 
 
-def dgrad_strided_tc(dy, n, P, Q, kp, w16, ko, cp, in_c, R, S, stride, pad, H, W, dx, mask=None):
+def dgrad_strided_tc(dy, n, P, Q, kp, w16, ko, cp, in_c, R, S, stride, pad, H, W, dx, mask=None, cache=None):
     """Device path. dy: bf16 [n, P, Q, kp]; w16: bf16 filters [ko][R*S][cp]; dx: bf16 [n, H, W, cp] (overwritten);
     mask: optional bf16 [n, H, W, cp], dx is zeroed where mask <= 0. Returns False when a phase needs a negative
-    padding (the caller then uses the direct kernel)."""
+    padding (the caller then uses the direct kernel). `cache` (a dict owned by the calling operator) keeps the
+    per-phase filter and output buffers between calls, so that a training step allocates nothing here."""
     from . import native_ops as K
     plan = phase_plan(H, W, R, S, stride, pad)
     if any(ph.U and ph.V and (ph.pad_t < 0 or ph.pad_l < 0) for ph in plan):
@@ -87,9 +88,15 @@ def dgrad_strided_tc(dy, n, P, Q, kp, w16, ko, cp, in_c, R, S, stride, pad, H, W
             continue
         # flipped sub-filter in the forward kernel's layout: [output channel = c][tap][input channel = k], k padded
         sub = w4[:, ph.r0::stride, ph.c0::stride, :].flip(1, 2).permute(3, 1, 2, 0).reshape(cp, ph.U * ph.V, ko)
-        wt = torch.zeros((cp, ph.U * ph.V, kp), dtype=torch.bfloat16, device=dy.device)
-        wt[:, :, :ko] = sub
-        tmp = torch.empty((n, ph.Hp, ph.Wp, cp), dtype=torch.bfloat16, device=dy.device)
+        key = (ph.a, ph.b)
+        bufs = cache.get(key) if cache is not None else None
+        if bufs is None:
+            bufs = (torch.zeros((cp, ph.U * ph.V, kp), dtype=torch.bfloat16, device=dy.device),
+                    torch.empty((n, ph.Hp, ph.Wp, cp), dtype=torch.bfloat16, device=dy.device))
+            if cache is not None:
+                cache[key] = bufs
+        wt, tmp = bufs
+        wt[:, :, :ko].copy_(sub)
         K.conv_fprop_tc(dy, n, P, Q, kp, wt, cp, ph.U, ph.V, 1, ph.pad_t, ph.pad_l, ph.Hp, ph.Wp, tmp, cp,
                         n_valid=in_c, n_store=cp)
         view.copy_(tmp)

@@ -110,3 +110,51 @@ def test_strided_data_grad_phase_decomposition_equals_autograd(k, stride, pad, h
     got = dgrad_by_phases_reference(dy, w, hw, hw + 1, stride, pad)
     assert torch.allclose(got, ref, atol=1e-10), float((got - ref).abs().max())
     assert len(phase_plan(hw, hw + 1, k, k, stride, pad)) == stride * stride
+
+
+def test_strided_data_grad_device_path_packing_with_an_emulated_kernel(monkeypatch):
+    """`dgrad_strided_tc` itself (filter slicing / flipping / padding, phase interleave, mask) with the forward kernel
+    replaced by a plain-torch emulation of its contract, so the layout logic is checked without a GPU."""
+    import torch
+    import torch.nn.functional as F
+    from rembrandt_b200.ops import conv_strided, layout
+    from rembrandt_b200.ops import native_ops as K
+
+    def fake_fprop(x, N, H, W, Cp, w, Kout, R, S, stride, pad_h, pad_w, P, Q, y, ldy, bias=None, relu=False,
+                   mask_src=None, n_valid=0, n_store=0):
+        assert stride == 1 and pad_h >= 0 and pad_w >= 0
+        xi = x.float().permute(0, 3, 1, 2)                                     # [N, Cp, H, W]
+        wi = w.float().view(Kout, R, S, Cp).permute(0, 3, 1, 2)                # [Kout, Cp, R, S]
+        need_h, need_w = P + R - 1, Q + S - 1
+        xi = F.pad(xi, (pad_w, max(0, need_w - pad_w - W), pad_h, max(0, need_h - pad_h - H)))[:, :, :need_h, :need_w]
+        out = F.conv2d(xi, wi)                                                 # [N, Kout, P, Q]
+        out[:, n_valid:] = 0
+        y.copy_(out.permute(0, 2, 3, 1).to(y.dtype))
+
+    def fake_mask(d, m, n):
+        d.mul_((m.float() > 0).to(d.dtype))
+
+    monkeypatch.setattr(K, "conv_fprop_tc", fake_fprop)
+    monkeypatch.setattr(K, "relu_mask", fake_mask)
+    torch.manual_seed(4)
+    for (C, Ko, R, stride, pad, H, W) in ((5, 7, 3, 2, 1, 9, 10), (8, 6, 1, 2, 0, 8, 8), (3, 4, 5, 3, 2, 11, 13)):
+        N = 2
+        Cp, Kp = K.pad_channels(C), K.pad_channels(Ko)
+        x = torch.randn(N, C, H, W, requires_grad=True)
+        w = torch.randn(Ko, C, R, R)
+        y = F.conv2d(x, w, stride=stride, padding=pad)
+        dy = torch.randn_like(y)
+        mask = torch.randn(N, C, H, W)
+        ref = torch.autograd.grad(y, x, dy)[0] * (mask > 0)
+        dx = torch.full((N, H, W, Cp), float("nan"))
+        wi = layout.conv_weight_to_internal(w, Cp)
+        cache = {}
+        for _ in range(2):   # the second call reuses the cached per-phase buffers
+            ok = conv_strided.dgrad_strided_tc(layout.to_nhwc_padded(dy, Kp).float(), N, y.shape[2], y.shape[3], Kp, wi,
+                                               Ko, Cp, C, R, R, stride, pad, H, W, dx,
+                                               layout.to_nhwc_padded(mask, Cp).float(), cache=cache)
+            assert ok
+        assert len(cache) == sum(1 for ph in conv_strided.phase_plan(H, W, R, R, stride, pad) if ph.U and ph.V)
+        got = layout.from_nhwc_padded(dx, C)
+        assert torch.allclose(got.float(), ref, atol=2e-2, rtol=2e-2), float((got.float() - ref).abs().max())
+        assert (dx[..., C:] == 0).all()
