@@ -92,3 +92,39 @@ def _merged(ranges):
         else:
             out.append((lo, hi))
     return out
+
+
+def test_exchange_staging_regions_do_not_overlap():
+    """Staging layout of the push-based exchange: every bucket gets `world` slots of the length a rank reduces, and
+    no two regions overlap (checked on the planning code alone, with a stand-in for the symmetric-memory arena)."""
+    import types
+    from rembrandt_b200.parallel import p2p
+
+    class _Arena:
+        def __init__(self):
+            self.allocs = {}
+
+        def alloc(self, name, n, dtype):
+            self.allocs[name] = n
+            return None
+
+    comm = types.SimpleNamespace(world=8, one_shot_elems=64 * 1024, bucket_elems=6 * 1024 * 1024, num_slots=256,
+                                 mc_grads=0, arena=_Arena())
+    comm._shard_len = types.MethodType(p2p.FusedAllreduceSgdComm._shard_len, comm)
+    sizes = [1000 * 64, 6 * 1024 * 1024, 4096, 123 * 64, 6 * 1024 * 1024, 64]
+    comm.launches, off = [], 0
+    for slot, n in enumerate(sizes):
+        comm.launches.append((0, off, n, slot))
+        off += n
+    p2p.FusedAllreduceSgdComm.setup_stage(comm)
+    regions = []
+    for _, _o, n, slot in comm.launches:
+        per = n if n <= comm.one_shot_elems else comm._shard_len(n)
+        assert per % 8 == 0 or n <= comm.one_shot_elems
+        regions.append((comm._stage_off[slot], comm._stage_off[slot] + comm.world * per))
+    regions.append((comm._stage_off[comm.num_slots - 1],
+                    comm._stage_off[comm.num_slots - 1] + comm.world * comm._shard_len(comm.bucket_elems)))
+    regions.sort()
+    for (a0, a1), (b0, b1) in zip(regions, regions[1:]):
+        assert a1 <= b0
+    assert comm.arena.allocs["stage"] >= regions[-1][1]
