@@ -62,11 +62,11 @@ def cyclic_partition_range(n: int, parts: int, idx: int, shift: int):
     Returns one or two (lo, hi) pieces.
     """
     lo, hi = partition_range(n, parts, idx)
-    lo, hi = (lo + shift) % n, (hi + shift) % n
-    if n == 0:
-        return []
-    if lo < hi:
+    if n == 0 or hi == lo:
+        return []            # an empty part stays empty however it is rotated
+    length = hi - lo
+    lo = (lo + shift) % n
+    hi = lo + length
+    if hi <= n:
         return [(lo, hi)]
-    if hi == 0:
-        return [(lo, n)]
-    return [(lo, n), (0, hi)]
+    return [(lo, n), (0, hi - n)]

@@ -1,0 +1,59 @@
+"""Property-based checks (hypothesis) of the host-side building blocks."""
+import numpy as np
+import pytest
+from hypothesis import given, settings, strategies as st
+
+from rembrandt_b200.utils import blob
+from rembrandt_b200.utils.rng import cyclic_partition_range, partition_range
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.lists(st.integers(1, 7), min_size=1, max_size=4), st.sampled_from(["f32", "u8"]), st.integers(0, 2**32 - 1))
+def test_blob_records_round_trip(dims, dtype, seed):
+    rng = np.random.default_rng(seed)
+    n = int(np.prod(dims))
+    data = rng.integers(0, 256, n).astype(np.uint8) if dtype == "u8" else rng.standard_normal(n).astype(np.float32)
+    buf = blob.encode_record(data, tuple(dims), dtype=dtype) + blob.encode_record(data[::-1].copy(), (n,), dtype=dtype)
+    recs, off = blob.decode_records(buf, dtype)
+    assert off == len(buf) and len(recs) == 2
+    assert tuple(recs[0][1]) == tuple(dims) and np.array_equal(recs[0][0], data)
+    assert np.array_equal(recs[1][0], data[::-1])
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.integers(0, 10_000), st.integers(1, 64))
+def test_partition_range_is_a_balanced_contiguous_cover(n, parts):
+    bounds = [partition_range(n, parts, i) for i in range(parts)]
+    assert bounds[0][0] == 0 and bounds[-1][1] == n
+    sizes = []
+    for (lo, hi), (lo2, _hi2) in zip(bounds, bounds[1:] + [(n, n)]):
+        assert lo <= hi and hi == lo2
+        sizes.append(hi - lo)
+    assert max(sizes) - min(sizes) <= 1
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(1, 500), st.integers(1, 8), st.integers(0, 1000))
+def test_cyclic_partition_covers_every_element_once(n, parts, shift):
+    seen = []
+    for i in range(parts):
+        for lo, hi in cyclic_partition_range(n, parts, i, shift):
+            seen.extend(range(lo, hi))
+    assert sorted(seen) == list(range(n))
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.integers(1, 120), st.integers(0, 9), st.integers(0, 2**31 - 1))
+def test_lmdb_readers_agree_on_random_environments(n, cap, seed):
+    import tempfile
+    from rembrandt_b200.data.lmdb_reader import LmdbEnv, NativeLmdbEnv, write_env
+    rng = np.random.default_rng(seed)
+    keys = sorted({bytes(rng.integers(97, 123, int(rng.integers(1, 12))).astype(np.uint8)) for _ in range(n)})
+    items = [(k, bytes(rng.integers(0, 256, int(rng.choice([0, 3, 40, 700, 1500, 9000]))).astype(np.uint8))) for k in keys]
+    with tempfile.TemporaryDirectory() as d:
+        write_env(d, items, max_leaf_nodes=0 if cap < 3 else cap)
+        probe = bytes(rng.integers(97, 123, 3).astype(np.uint8))
+        with LmdbEnv(d) as a, NativeLmdbEnv(d) as b:
+            assert list(a.items()) == items and list(b.items()) == items
+            assert list(a.items(probe)) == list(b.items(probe)) == [kv for kv in items if kv[0] >= probe]
+            assert a.get(keys[0]) == b.get(keys[0]) == items[0][1]
