@@ -57,3 +57,21 @@ def test_lmdb_readers_agree_on_random_environments(n, cap, seed):
             assert list(a.items()) == items and list(b.items()) == items
             assert list(a.items(probe)) == list(b.items(probe)) == [kv for kv in items if kv[0] >= probe]
             assert a.get(keys[0]) == b.get(keys[0]) == items[0][1]
+
+
+@settings(max_examples=40, deadline=None)
+@given(st.integers(1, 5), st.integers(2, 3), st.integers(0, 2), st.integers(5, 13), st.integers(5, 13), st.integers(0, 2**31 - 1))
+def test_strided_data_grad_phases_match_autograd(k, stride, pad, H, W, seed):
+    import torch
+    import torch.nn.functional as F
+    from rembrandt_b200.ops.conv_strided import dgrad_by_phases_reference
+    if pad >= k or H + 2 * pad < k or W + 2 * pad < k:
+        return
+    torch.manual_seed(seed)
+    x = torch.randn(1, 3, H, W, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(4, 3, k, k, dtype=torch.float64)
+    y = F.conv2d(x, w, stride=stride, padding=pad)
+    dy = torch.randn_like(y)
+    ref = torch.autograd.grad(y, x, dy)[0]
+    got = dgrad_by_phases_reference(dy, w, H, W, stride, pad)
+    assert torch.allclose(got, ref, atol=1e-9), float((got - ref).abs().max())
