@@ -121,3 +121,19 @@ def test_bad_descriptors_are_rejected():
         descriptor.parse_model('[[layer]]\nname = "x"\nfoo = 1\n')
     with pytest.raises(descriptor.DescriptorError):
         descriptor.parse_data("[dataset.train]\ndata_path = 'x'\n")
+
+
+def test_example_descriptors_shipped_with_this_framework_build_and_step():
+    """examples/*.model and *.data of this repository parse, build and take a training step on CPU."""
+    import torch
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    md = descriptor.load_model(os.path.join(here, "examples", "mnist_lenet.model"))
+    net = Net(md.config, 4, device="cpu")
+    assert net.params_len == 431080          # 20 / 50 / 500 / 10 LeNet without padding
+    splits = descriptor.load_data(os.path.join(here, "examples", "synthetic_mnist.data"))
+    assert splits["train"].source == "synthetic" and "valid" in splits
+    x = torch.randint(0, 256, (4, 1, 28, 28), dtype=torch.uint8)
+    net.load_batch(x, torch.tensor([1, 2, 3, 4]))
+    net.forward(True)
+    net.backward()
+    assert float(net.grads.abs().sum()) > 0
