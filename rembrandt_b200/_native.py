@@ -52,6 +52,8 @@ _CUDA_SIGS = {
     "rb_pointwise_loss": [vp, i32, i32, i32, vp, vp, f32, vp, vp, vp, i32, vp],
     "rb_softmax_ce": [vp, i32, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     # sgd_fused.cu
+    "rb_tma_probe_tiled": [vp, i64, i32, i32, i32, i32, i32, i32, i64, i32, i32, vp, vp],
+    "rb_tma_probe_conv_stage": [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "rb_sgd_fused": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, vp],
     "rb_sgd_fused_grid": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, i32, i32, vp],
     "rb_axpy_shadow": [vp, vp, vp, i64, f32, vp],
