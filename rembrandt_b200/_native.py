@@ -48,6 +48,10 @@ _CUDA_SIGS = {
     "rb_f32_to_bf16": [vp, vp, i64, vp],
     "rb_pack_dgrad_filters": [vp, vp, i32, i32, i32, i32, vp],
     "rb_zero_s2d_structural": [vp, i32, i32, i32, i32, i32, i32, vp],
+    # activations.cu
+    "rb_act_fwd": [vp, i64, i32, i32, i32, f32, vp],
+    "rb_act_bwd": [vp, vp, i64, i32, i32, i32, f32, vp],
+    "rb_count_above": [vp, i64, i32, f32, vp, vp],
     # softmax_ce.cu
     "rb_pointwise_loss": [vp, i32, i32, i32, vp, vp, f32, vp, vp, vp, i32, vp],
     "rb_softmax_ce": [vp, i32, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],

@@ -15,8 +15,9 @@ from typing import List, Optional, Sequence, Tuple
 class Act(enum.Enum):
     IDENTITY = "identity"
     RECT = "rect"
-    LOGISTIC = "logistic"   # declared by the reference, not implemented there either
+    LOGISTIC = "logistic"   # gen-3 of the reference declares these two without implementing them; gen-1 has them
     TANH = "tanh"
+    BOUNDED_RECT = "bounded_rect"   # min(max(x, 0), ACT_BOUND): the gen-1 clipped ReLU (src/layer.rs:55)
 
     @staticmethod
     def parse(s: str) -> "Act":
@@ -29,7 +30,14 @@ class Act(enum.Enum):
             return Act.LOGISTIC
         if s == "tanh":
             return Act.TANH
+        if s in ("bounded_rect", "boundedrect"):
+            return Act.BOUNDED_RECT
         raise ValueError(f"unknown activation {s!r}")
+
+
+# Upper clip of Act.BOUNDED_RECT. The reference's kernel takes no bound argument and its source is not in the tree,
+# so the value is this framework's choice.
+ACT_BOUND = 6.0
 
 
 class OpPhase(enum.Enum):

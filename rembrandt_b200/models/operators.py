@@ -56,6 +56,7 @@ class Op:
         self.out_hwc = None
         self.out_cp = 0
         self.has_relu = False
+        self.act_kind = 0
         self.segs: List[ParamSeg] = []
         self.out = None    # activation buffer (CUDA path)
         self.dout = None   # delta w.r.t. `out`, written by the consumer
@@ -108,6 +109,36 @@ class Op:
     @property
     def in_cp(self):
         return self.prev.out_cp
+
+    # ---- activations other than ReLU (ReLU is fused into the producing kernel's epilogue and the consumer's mask)
+    def _setup_act(self, act):
+        self.has_relu = act == C.Act.RECT
+        self.act_kind = {C.Act.LOGISTIC: K.ACT_LOGISTIC, C.Act.TANH: K.ACT_TANH,
+                         C.Act.BOUNDED_RECT: K.ACT_BOUNDED_RECT}.get(act, 0)
+
+    def _act_rows(self):
+        h, w, _ = self.out_hwc
+        return self.net.batch * h * w
+
+    def _act_forward(self):
+        if self.act_kind:
+            K.act_fwd(self.out, self._act_rows(), self.out_cp, self.out_hwc[2], self.act_kind, C.ACT_BOUND)
+
+    def _act_backward(self):
+        """Turn the delta w.r.t. the activation into the delta w.r.t. the pre-activation, in place."""
+        if self.act_kind:
+            K.act_bwd(self.dout, self.out, self._act_rows(), self.out_cp, self.out_hwc[2], self.act_kind, C.ACT_BOUND)
+
+    def _ref_act(self, y):
+        if self.has_relu:
+            return torch.relu(y)
+        if self.act_kind == K.ACT_LOGISTIC:
+            return torch.sigmoid(y)
+        if self.act_kind == K.ACT_TANH:
+            return torch.tanh(y)
+        if self.act_kind == K.ACT_BOUNDED_RECT:
+            return y.clamp(0.0, C.ACT_BOUND)
+        return y
 
     def mask_src(self):
         """Activation to mask the delta of `prev` with, or None."""
@@ -533,9 +564,7 @@ class Conv2dOp(Op):
         self.cp = prev.out_cp
         self.out_hwc = (self.P, self.Q, cfg.out_channels)
         self.out_cp = pad_channels(cfg.out_channels)
-        self.has_relu = cfg.act == C.Act.RECT
-        if cfg.act not in (C.Act.RECT, C.Act.IDENTITY):
-            raise NotImplementedError("only identity and rect activations are implemented (as in the reference)")
+        self._setup_act(cfg.act)
         rs = self.r2 * self.r2 if self.s2d else k * k
         self.rs = rs
         self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, rs, self.cp))
@@ -565,11 +594,13 @@ class Conv2dOp(Op):
                         p, p, self.P, self.Q, self.out, self.out_cp,
                         bias=self.view(self.seg_b) if self.seg_b else None, relu=self.has_relu, n_valid=ko,
                         n_store=self.out_cp)
+        self._act_forward()
 
     def backward(self):
         h, w, r, s, p = self._geom()
         n, ko = self.net.batch, self.cfg.out_channels
         rows = n * self.P * self.Q
+        self._act_backward()
         if self.seg_b:
             K.colsum(self.dout, rows, self.out_cp, ko, self.view(self.seg_b, "grads"))
         gw = self.view(self.seg_w, "grads")
@@ -642,7 +673,7 @@ class Conv2dOp(Op):
         w = self._w_ref(self.view(self.seg_w))
         b = self.view(self.seg_b) if self.seg_b else None
         y = F.conv2d(x, w, b, stride=cfg.conv_stride, padding=cfg.conv_pad)
-        return torch.relu(y) if self.has_relu else y
+        return self._ref_act(y)
 
 
 # =============================================================================================== affine
@@ -670,7 +701,7 @@ class AffineOp(Op):
             self.k_in = h * w * prev.out_cp
         self.out_hwc = (1, 1, cfg.out_channels)
         self.out_cp = pad_channels(cfg.out_channels)
-        self.has_relu = cfg.act == C.Act.RECT
+        self._setup_act(cfg.act)
         self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, self.k_in))
         self.seg_b = ParamSeg(self.name + ".b", (cfg.out_channels,))
         self.segs = [self.seg_w, self.seg_b]
@@ -696,9 +727,11 @@ class AffineOp(Op):
         K.gemm_tc(x, 0, self.k_in, self.view(self.seg_w, "params16"), 0, self.k_in, n, ko, self.k_in, self.ws,
                   self.out_cp, epi=K.EPI_F32_ATOMIC, n_store=self.out_cp, split_k=0, bn_cap=self._bn_cap(ko))
         K.bias_act(self.ws, n, self.out_cp, ko, self.view(self.seg_b), self.has_relu, self.out)
+        self._act_forward()
 
     def backward(self):
         n, ko = self.net.batch, self.cfg.out_channels
+        self._act_backward()
         K.colsum(self.dout, n, self.out_cp, ko, self.view(self.seg_b, "grads"))
         # dW[out][in] += dY^T X : both operands are read "MN-major" straight from their row-major buffers
         # one pass over the batch: overwrite when this is the only micro-batch of the iteration, else accumulate
@@ -747,8 +780,7 @@ class AffineOp(Op):
 
     def ref_forward(self, x, train, t):
         wr = self._w_ref(self.view(self.seg_w))
-        y = x.flatten(1) @ wr.t() + self.view(self.seg_b)
-        y = torch.relu(y) if self.has_relu else y
+        y = self._ref_act(x.flatten(1) @ wr.t() + self.view(self.seg_b))
         return y.reshape(y.shape[0], -1, 1, 1)
 
 

@@ -180,7 +180,7 @@ class BNormConv2dOp(_BlockBase):
         self.segs = list(self.u.segs)
         self.out_hwc = (self.u.P, self.u.Q, cfg.out_channels)
         self.out_cp = self.u.kp
-        self.has_relu = cfg.act == C.Act.RECT
+        self._setup_act(cfg.act)
 
     def alloc(self):
         super().alloc()
@@ -188,14 +188,17 @@ class BNormConv2dOp(_BlockBase):
 
     def forward(self, train, t):
         self.u.forward(self.prev.out, self.out, None, self.has_relu, train, t)
+        self._act_forward()
 
     def backward(self):
+        self._act_backward()
         dx = self.prev.dout if self.wants_prev_delta() else None
         # the consumer already masked dout by this operator's ReLU
         self.u.backward(self.prev.out, self.dout, None, dx, self.mask_src())
 
     def ref_forward(self, x, train, t):
-        return self.u.ref(x, None, self.has_relu, train, t)
+        y = self.u.ref(x, None, self.has_relu, train, t)
+        return y if self.has_relu else self._ref_act(y)
 
 
 class StackResConv2dOp(_BlockBase):

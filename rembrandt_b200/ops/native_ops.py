@@ -110,6 +110,26 @@ def relu_mask(d, y, n):
     check(_native.cuda().rb_relu_mask(ptr(d), ptr(y), n, stream_handle()), "rb_relu_mask")
 
 
+ACT_LOGISTIC, ACT_TANH, ACT_BOUNDED_RECT = 1, 2, 3
+
+
+def act_fwd(y, rows, ld, n_valid, kind, bound=0.0):
+    """y = f(y) in place on the first `n_valid` columns of a bf16 [rows][ld] buffer (logistic, tanh, clipped ReLU)."""
+    check(_native.cuda().rb_act_fwd(ptr(y), rows, ld, n_valid, kind, float(bound), stream_handle()), "rb_act_fwd")
+
+
+def act_bwd(d, y, rows, ld, n_valid, kind, bound=0.0):
+    """d *= f'(y) in place, with the slope written in terms of the output y."""
+    check(_native.cuda().rb_act_bwd(ptr(d), ptr(y), rows, ld, n_valid, kind, float(bound), stream_handle()),
+          "rb_act_bwd")
+
+
+def count_above(x, threshold, out):
+    """out[0] (int64, device) += number of elements of the bf16 / fp32 tensor `x` with |x| > threshold."""
+    check(_native.cuda().rb_count_above(ptr(x), x.numel(), int(x.dtype == torch.float32), float(threshold), ptr(out),
+                                        stream_handle()), "rb_count_above")
+
+
 def add_bf16(a, b, n):
     check(_native.cuda().rb_add_bf16(ptr(a), ptr(b), n, stream_handle()), "rb_add_bf16")
 

@@ -254,3 +254,25 @@ def test_softmax_head_sampling_respects_mask_and_temperature():
     cold = net.loss_op.sample_categories(1e-4, g)
     best = net._cpu_logits.flatten(1).masked_fill(~mask, float("-inf")).argmax(1)
     assert torch.equal(cold, best)
+
+
+@pytest.mark.parametrize("act,fn", [(Act.LOGISTIC, torch.sigmoid), (Act.TANH, torch.tanh),
+                                    (Act.BOUNDED_RECT, lambda v: v.clamp(0.0, 6.0))])
+def test_smooth_and_clipped_activations_reference_path(act, fn):
+    cfg = (SequentialOperatorConfig().data3d(Data3dCfg((8, 8, 3), normalize=True))
+           .conv2d(Conv2dCfg(3, 1, 1, 6, act, ParamsInit.kaiming()), "conv1")
+           .affine(AffineCfg(5, act, ParamsInit.xavier()), "fc1")
+           .affine(AffineCfg(4, Act.IDENTITY, ParamsInit.xavier()), "fc2")
+           .softmax_kl_loss(SoftmaxKLLossCfg(4)))
+    net = Net(cfg, 2, device="cpu", seed=(1, 2))
+    conv, fc1, _ = net.hidden_ops
+    recs, _ = blob.decode_records(net.encode_params())
+    w = torch.from_numpy(recs[0][0]).reshape(6, 3, 3, 3)
+    b = torch.from_numpy(recs[1][0]).reshape(6)
+    x = torch.rand(2, 3, 8, 8) * 4 - 2
+    out = conv.ref_forward(x, False, 0)
+    assert torch.allclose(out, fn(F.conv2d(x, w, b, padding=1)), atol=1e-5)
+    w1 = torch.from_numpy(recs[2][0]).reshape(5, -1)
+    b1 = torch.from_numpy(recs[3][0]).reshape(5)
+    assert torch.allclose(fc1.ref_forward(out, False, 0).flatten(1), fn(out.flatten(1) @ w1.t() + b1), atol=1e-5)
+    assert Act.parse("sigmoid") is Act.LOGISTIC and Act.parse("bounded_rect") is Act.BOUNDED_RECT
