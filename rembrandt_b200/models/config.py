@@ -126,6 +126,14 @@ class Data3dCfg:
     channel_mean: Optional[Sequence[float]] = None    # variable-size input: per-channel mean (after scaling)
 
 
+class ConvBackend(enum.Enum):
+    """Which kernels a convolution runs on. The reference's enum of the same name picks a cuDNN algorithm
+    (implicit precomputed GEMM or tiled FFT, src/layer_new.rs:177,837-838); here the choice is between the tcgen05
+    implicit GEMM and the plain CUDA-core kernels kept as its on-device cross-check."""
+    TENSOR_CORE = "tensor_core"
+    DIRECT = "direct"
+
+
 @dataclass
 class Conv2dCfg:
     conv_size: int
@@ -135,12 +143,26 @@ class Conv2dCfg:
     act: Act = Act.RECT
     init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
     bias: bool = True
+    backend: ConvBackend = ConvBackend.TENSOR_CORE
 
 
 @dataclass
 class AffineCfg:
     out_channels: int
     act: Act = Act.IDENTITY
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.xavier())
+    bias: bool = True
+
+
+@dataclass
+class MimicAffineCfg:
+    """Low-rank fully connected block of the first layer generation (MimicAffineLayerConfig, src/layer.rs:817-824):
+    in -> `bottleneck_rank` (no bias, no activation) -> `hidden_channels` (no bias, `hidden_act`) -> `out_channels`
+    (bias). It is a macro: `SequentialOperatorConfig.mimic_affine` expands it into three affine operators."""
+    bottleneck_rank: int
+    hidden_channels: int
+    out_channels: int
+    hidden_act: Act = Act.RECT
     init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.xavier())
 
 
@@ -305,6 +327,13 @@ class SequentialOperatorConfig:
     def affine(self, cfg: AffineCfg, name=None):
         self.hidden_ops.append(NamedOp(self._name(name, "fc"), cfg))
         return self
+
+    def mimic_affine(self, cfg: MimicAffineCfg, name=None):
+        base = self._name(name, "mimic")
+        init = cfg.init_weights
+        self.affine(AffineCfg(cfg.bottleneck_rank, Act.IDENTITY, init, bias=False), base + ".down")
+        self.affine(AffineCfg(cfg.hidden_channels, cfg.hidden_act, init, bias=False), base + ".up")
+        return self.affine(AffineCfg(cfg.out_channels, Act.IDENTITY, init), base + ".out")
 
     def softmax_kl_loss(self, cfg: SoftmaxKLLossCfg, name="loss"):
         self.loss_op = NamedOp(name, cfg)

@@ -565,6 +565,7 @@ class Conv2dOp(Op):
         self.out_hwc = (self.P, self.Q, cfg.out_channels)
         self.out_cp = pad_channels(cfg.out_channels)
         self._setup_act(cfg.act)
+        self.direct = getattr(cfg, "backend", C.ConvBackend.TENSOR_CORE) == C.ConvBackend.DIRECT
         rs = self.r2 * self.r2 if self.s2d else k * k
         self.rs = rs
         self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, rs, self.cp))
@@ -590,6 +591,12 @@ class Conv2dOp(Op):
     def forward(self, train, t):
         h, w, r, s, p = self._geom()
         ko = self.cfg.out_channels
+        if self.direct:
+            K.conv_direct_fwd(self.prev.out, self.view(self.seg_w, "params16"),
+                              self.view(self.seg_b) if self.seg_b else None, self.out, self.net.batch, h, w, self.cp,
+                              ko, self.out_cp, r, r, s, p, p, self.P, self.Q, self.has_relu)
+            self._act_forward()
+            return
         K.conv_fprop_tc(self.prev.out, self.net.batch, h, w, self.cp, self.view(self.seg_w, "params16"), ko, r, r, s,
                         p, p, self.P, self.Q, self.out, self.out_cp,
                         bias=self.view(self.seg_b) if self.seg_b else None, relu=self.has_relu, n_valid=ko,
@@ -604,13 +611,21 @@ class Conv2dOp(Op):
         if self.seg_b:
             K.colsum(self.dout, rows, self.out_cp, ko, self.view(self.seg_b, "grads"))
         gw = self.view(self.seg_w, "grads")
-        K.conv_wgrad_tc(self.prev.out, n, h, w, self.cp, self.dout, self.out_cp, ko, r, r, s, p, p, self.P, self.Q, gw)
+        if self.direct:
+            K.conv_direct_wgrad(self.prev.out, self.dout, gw, n, h, w, self.cp, ko, self.out_cp, r, r, s, p, p, self.P,
+                                self.Q)
+        else:
+            K.conv_wgrad_tc(self.prev.out, n, h, w, self.cp, self.dout, self.out_cp, ko, r, r, s, p, p, self.P,
+                            self.Q, gw)
         if self.s2d:
             K.zero_s2d_structural(gw, ko, self.r2, self.cp, self.f, self.in_c, self.cfg.conv_size)
         if self.wants_prev_delta():
             mask = self.mask_src()
             w16 = self.view(self.seg_w, "params16")
-            if s == 1:
+            if self.direct:
+                K.conv_direct_dgrad(self.dout, w16, self.prev.dout, mask, n, h, w, self.cp, ko, self.out_cp, r, r, s,
+                                    p, p, self.P, self.Q)
+            elif s == 1:
                 K.pack_dgrad_filters(w16, self.wt16, ko, self.out_cp, r * r, self.cp)
                 K.conv_fprop_tc(self.dout, n, self.P, self.Q, self.out_cp, self.wt16, self.cp, r, r, 1, r - 1 - p,
                                 r - 1 - p, h, w, self.prev.dout, self.cp, mask_src=mask, n_valid=self.in_c,
@@ -703,8 +718,8 @@ class AffineOp(Op):
         self.out_cp = pad_channels(cfg.out_channels)
         self._setup_act(cfg.act)
         self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, self.k_in))
-        self.seg_b = ParamSeg(self.name + ".b", (cfg.out_channels,))
-        self.segs = [self.seg_w, self.seg_b]
+        self.seg_b = ParamSeg(self.name + ".b", (cfg.out_channels,)) if getattr(cfg, "bias", True) else None
+        self.segs = [self.seg_w] + ([self.seg_b] if self.seg_b else [])
 
     def alloc(self):
         super().alloc()
@@ -726,13 +741,15 @@ class AffineOp(Op):
         x = self.prev.out
         K.gemm_tc(x, 0, self.k_in, self.view(self.seg_w, "params16"), 0, self.k_in, n, ko, self.k_in, self.ws,
                   self.out_cp, epi=K.EPI_F32_ATOMIC, n_store=self.out_cp, split_k=0, bn_cap=self._bn_cap(ko))
-        K.bias_act(self.ws, n, self.out_cp, ko, self.view(self.seg_b), self.has_relu, self.out)
+        K.bias_act(self.ws, n, self.out_cp, ko, self.view(self.seg_b) if self.seg_b else None, self.has_relu,
+                   self.out)
         self._act_forward()
 
     def backward(self):
         n, ko = self.net.batch, self.cfg.out_channels
         self._act_backward()
-        K.colsum(self.dout, n, self.out_cp, ko, self.view(self.seg_b, "grads"))
+        if self.seg_b:
+            K.colsum(self.dout, n, self.out_cp, ko, self.view(self.seg_b, "grads"))
         # dW[out][in] += dY^T X : both operands are read "MN-major" straight from their row-major buffers
         # one pass over the batch: overwrite when this is the only micro-batch of the iteration, else accumulate
         epi = K.EPI_F32_ATOMIC if self.net.accumulate else K.EPI_F32_STORE
@@ -763,24 +780,31 @@ class AffineOp(Op):
         fan_in = h * w * c
         wr = _draw(cfg.init_weights, rng, (cfg.out_channels, fan_in), fan_in, cfg.out_channels)
         self.view(self.seg_w).copy_(self._w_int(wr))
-        self.view(self.seg_b).zero_()
+        if self.seg_b:
+            self.view(self.seg_b).zero_()
 
     def encode_params(self):
         h, w, c = self.in_hw_c
         o = self.cfg.out_channels
         wr = self._w_ref(self.view(self.seg_w).detach().float().cpu())
-        return [(wr.reshape(-1), (h * w * c, o)), (self.view(self.seg_b).detach().float().cpu(), (1, o))]
+        recs = [(wr.reshape(-1), (h * w * c, o))]
+        if self.seg_b:
+            recs.append((self.view(self.seg_b).detach().float().cpu(), (1, o)))
+        return recs
 
     def decode_params(self, arrays):
         h, w, c = self.in_hw_c
         o = self.cfg.out_channels
         self.view(self.seg_w).copy_(self._w_int(torch.as_tensor(arrays[0][0]).reshape(o, h * w * c)))
+        if not self.seg_b:
+            return 1
         self.view(self.seg_b).copy_(torch.as_tensor(arrays[1][0]).reshape(-1))
         return 2
 
     def ref_forward(self, x, train, t):
         wr = self._w_ref(self.view(self.seg_w))
-        y = self._ref_act(x.flatten(1) @ wr.t() + self.view(self.seg_b))
+        y = x.flatten(1) @ wr.t()
+        y = self._ref_act(y + self.view(self.seg_b) if self.seg_b else y)
         return y.reshape(y.shape[0], -1, 1, 1)
 
 

@@ -9,7 +9,8 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from rembrandt_b200.models import zoo
-from rembrandt_b200.models.config import (Act, AffineCfg, BNormConv2dCfg, Conv2dCfg, Data3dCfg, ParamsInit, Pool2dCfg,
+from rembrandt_b200.models.config import (Act, AffineCfg, BNormConv2dCfg, Conv2dCfg, Data3dCfg, MimicAffineCfg,
+                                          ParamsInit, Pool2dCfg,
                                           PoolKind, ProjStackResConv2dCfg, SequentialOperatorConfig, SoftmaxKLLossCfg,
                                           StackResConv2dCfg)
 from rembrandt_b200.models.net import Net
@@ -276,3 +277,25 @@ def test_smooth_and_clipped_activations_reference_path(act, fn):
     b1 = torch.from_numpy(recs[3][0]).reshape(5)
     assert torch.allclose(fc1.ref_forward(out, False, 0).flatten(1), fn(out.flatten(1) @ w1.t() + b1), atol=1e-5)
     assert Act.parse("sigmoid") is Act.LOGISTIC and Act.parse("bounded_rect") is Act.BOUNDED_RECT
+
+
+def test_mimic_affine_expands_into_a_low_rank_chain():
+    cfg = (SequentialOperatorConfig().data3d(Data3dCfg((6, 6, 2), normalize=True))
+           .mimic_affine(MimicAffineCfg(bottleneck_rank=5, hidden_channels=12, out_channels=4), "m")
+           .softmax_kl_loss(SoftmaxKLLossCfg(4)))
+    net = Net(cfg, 3, device="cpu", seed=(7, 8))
+    assert [op.name for op in net.hidden_ops] == ["m.down", "m.up", "m.out"]
+    recs, _ = blob.decode_records(net.encode_params())
+    # downsample and upsample carry no bias: three weight records and one bias record, as in the reference's layer
+    assert [r[1] for r in recs] == [(72, 5), (5, 12), (12, 4), (1, 4)]
+    wd, wu, wo = (torch.from_numpy(recs[i][0]).reshape(recs[i][1][1], recs[i][1][0]) for i in range(3))
+    b = torch.from_numpy(recs[3][0]).reshape(-1)
+    x = torch.rand(3, 2, 6, 6)
+    y = x
+    for op in net.hidden_ops:
+        y = op.ref_forward(y, False, 0)
+    want = torch.relu(x.flatten(1) @ wd.t() @ wu.t()) @ wo.t() + b
+    assert torch.allclose(y.flatten(1), want, atol=1e-5)
+    other = Net(cfg, 3, device="cpu", seed=(9, 9))
+    other.decode_params(net.encode_params())
+    assert torch.equal(other.params, net.params)

@@ -1,4 +1,5 @@
-"""Logistic / tanh / clipped-ReLU activation kernels and the sparsity counter against fp32 torch (GPU only).
+"""Logistic / tanh / clipped-ReLU activation kernels, the sparsity counter, the low-rank affine block and the
+CUDA-core convolution backend against fp32 torch (GPU only).
 
 Sorted after the other GPU files on purpose: these kernels are elementwise helpers of the older layer generations,
 not part of any benchmarked network.
@@ -9,7 +10,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 from rembrandt_b200.models import config as C
-from rembrandt_b200.models.config import (Act, AffineCfg, Conv2dCfg, Data3dCfg, ParamsInit, Pool2dCfg, PoolKind,
+from rembrandt_b200.models.config import (Act, AffineCfg, Conv2dCfg, Data3dCfg, MimicAffineCfg, ParamsInit, Pool2dCfg,
+                                          PoolKind,
                                           SequentialOperatorConfig, SoftmaxKLLossCfg)
 from rembrandt_b200.models.net import Net
 from rembrandt_b200.ops import native_ops as K
@@ -69,14 +71,37 @@ def _cfg():
             .softmax_kl_loss(SoftmaxKLLossCfg(10)))
 
 
-def test_network_with_smooth_activations_matches_reference_path():
+def _mimic_cfg():
+    k = ParamsInit.kaiming()
+    return (SequentialOperatorConfig().data3d(Data3dCfg((12, 12, 3), normalize=True))
+            .conv2d(Conv2dCfg(3, 1, 1, 32, Act.RECT, k), "conv1")
+            .pool2d(Pool2dCfg(2, 2, 0, PoolKind.MAX), "pool1")
+            .mimic_affine(MimicAffineCfg(bottleneck_rank=64, hidden_channels=96, out_channels=10), "m")
+            .softmax_kl_loss(SoftmaxKLLossCfg(10)))
+
+
+def _direct_cfg():
+    k = ParamsInit.kaiming()
+    d = C.ConvBackend.DIRECT
+    return (SequentialOperatorConfig().data3d(Data3dCfg((13, 13, 3), normalize=True))
+            .conv2d(Conv2dCfg(5, 2, 1, 24, Act.RECT, k, backend=d), "conv1")
+            .conv2d(Conv2dCfg(3, 1, 1, 40, Act.RECT, k, backend=d), "conv2")
+            .conv2d(Conv2dCfg(3, 2, 1, 32, Act.RECT, k, backend=d), "conv3")
+            .affine(AffineCfg(10, Act.IDENTITY, ParamsInit.xavier()), "fc")
+            .softmax_kl_loss(SoftmaxKLLossCfg(10)))
+
+
+@pytest.mark.parametrize("_cfg", [_cfg, _mimic_cfg, _direct_cfg],
+                         ids=["smooth_activations", "low_rank_affine", "direct_conv_backend"])
+def test_network_matches_reference_path(_cfg):
     batch = 8
     g = Net(_cfg(), batch, device="cuda", seed=(3, 4))
     c = Net(_cfg(), batch, device="cpu", seed=(3, 4))
     with torch.no_grad():
         c.params.copy_(g.params16.float().cpu())
     torch.manual_seed(0)
-    x = torch.randint(0, 256, (batch, 3, 12, 12), dtype=torch.uint8)
+    hw = g.input_op.src_hwc[0]
+    x = torch.randint(0, 256, (batch, 3, hw, hw), dtype=torch.uint8)
     y = torch.randint(0, 10, (batch,))
     g.load_batch(x.cuda(), y.cuda().int())
     c.load_batch(x, y)
