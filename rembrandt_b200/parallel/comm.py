@@ -451,7 +451,7 @@ class DownpourServerComm(CommWorker):
 def make_comm(name: str, **kw) -> CommWorker:
     table = {c.name: c for c in (NullComm, AllreduceComm, PairGossipComm, PullGossipComm, PushGossipComm,
                                  GroupAllreduceGossipComm, ElasticComm)}
-    if name in ("fused_allreduce_sgd", "gossip_p2p", "elastic_p2p"):
+    if name == "fused_allreduce_sgd" or name.endswith("_p2p"):
         from . import p2p
         return p2p.make(name, **kw)
     if name not in table:

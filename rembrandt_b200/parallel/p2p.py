@@ -411,6 +411,62 @@ class GossipP2PComm(CommWorker, _P2PBase):
         CommWorker.exact_sync(self, flat)
 
 
+class GroupGossipP2PComm(GossipP2PComm):
+    """Hierarchical exchange on the gossip kernels: the mean over this rank's group of `group_size` consecutive ranks,
+    then every rank pulls the group mean of one uniformly random rank and keeps 0.5 * (pulled + own group mean)
+    (the second version of the reference's scheme, src/worker/gossip_pull_allreduce_dist_rdma_v2.rs:327-384).
+
+    Both phases use the publish + mix kernels of the flat gossip: in phase one a rank pulls the snapshots of its group
+    peers as a running mean (pull k with weight 1 / (k + 2)); in phase two it publishes the group mean and pulls one
+    more snapshot with weight 1/2. Every rank runs both phases, so the epochs of the flag protocol stay in step even
+    for a rank that is alone in its group (its phase one is a single mix that lands on itself and changes nothing).
+    """
+    name = "group_allreduce_gossip_p2p"
+
+    def __init__(self, group=None, group_size: int = 2, seed=(53, 59), blocks: int = 96):
+        super().__init__(group, mode="pull", seed=seed, blocks=blocks, synchronous=True)
+        self.group_size = max(1, min(group_size, self.world))
+        g0 = self.rank // self.group_size * self.group_size
+        self.group_peers = [r for r in range(g0, min(self.world, g0 + self.group_size)) if r != self.rank]
+
+    def _phase(self, a, peers, weights, mix_self, st):
+        a.mix_self = mix_self
+        a.peer = peers[0]
+        check(PK.fn("rb_publish_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_publish_p2p")
+        for k, (peer, alpha) in enumerate(zip(peers, weights)):
+            a.peer = peer
+            a.pub_peer = self.arena.ptrs("pub")[peer]
+            a.alpha = alpha
+            a.not_last = 0 if k == len(peers) - 1 else 1
+            check(PK.fn("rb_gossip_mix_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_gossip_mix_p2p")
+            self.bytes_moved += a.n * 4
+
+    def sync_params(self, flat, repeat=False):
+        if self.world <= 1:
+            return
+        net = self.net
+        is_params = flat.data_ptr() == net.params.data_ptr()
+        if not (repeat and self._last_peer is not None):
+            self._last_peer = [self.rng.below(self.world)]
+        st = torch.cuda.current_stream()
+        a = PK.MixArgs()
+        _fill_ptrs(a.flags, self._flag_ptrs())
+        a.w = flat.data_ptr()
+        a.w16 = net.params16.data_ptr() if is_params else None
+        a.pub_local = self.pub.data_ptr()
+        slot = 0 if is_params else 1
+        a.epoch_ptr = self.epochs[slot:].data_ptr()
+        a.block_counter = self.counters[slot:].data_ptr()
+        a.status = self.status.data_ptr()
+        a.n = flat.numel() // 4 * 4
+        a.rank, a.world, a.slot = self.rank, self.world, slot
+        a.wait_peer = 1
+        a.w_self = 1.0
+        peers = self.group_peers or [self.rank]
+        self._phase(a, peers, [1.0 / (k + 2) for k in range(len(peers))], 0, st)
+        self._phase(a, self._last_peer, [0.5], 1, st)
+
+
 class ElasticP2PComm(CommWorker, _P2PBase):
     """Elastic averaging with the centre in rank 0's memory: clients read it and add their pull to it with
     peer-to-peer loads and reductions; rank 0 folds the accumulated pulls into the centre."""
@@ -527,4 +583,6 @@ def make(name: str, **kw) -> CommWorker:
         return PushGossipP2PComm(**kw)
     if name == "elastic_p2p":
         return ElasticP2PComm(**kw)
+    if name == GroupGossipP2PComm.name:
+        return GroupGossipP2PComm(**kw)
     raise ValueError(name)

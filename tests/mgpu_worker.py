@@ -123,6 +123,32 @@ def case_pull_rounds(rank, world):
         dist.barrier()
 
 
+def case_group_gossip(rank, world, group_size):
+    """Group mean + one pull on the gossip kernels: every rank ends with 0.5 * (own group mean + group mean of the
+    rank it drew), the scheme of the library backend (GroupAllreduceGossipComm)."""
+    comm = p2p.GroupGossipP2PComm(group_size=group_size, seed=(53, 59))
+    net, _ = _param_engine(comm)
+    for rnd in range(4):
+        torch.manual_seed(3000 * rnd + rank)
+        net.params.copy_(torch.randn_like(net.params))
+        everyone = [torch.empty_like(net.params) for _ in range(world)]
+        dist.all_gather(everyone, net.params)
+        comm.sync_params(net.params)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+
+        def group_mean(r):
+            g0 = r // group_size * group_size
+            members = range(g0, min(world, g0 + group_size))
+            return sum(everyone[m] for m in members) / len(members)
+
+        expect = 0.5 * (group_mean(rank) + group_mean(comm._last_peer[0]))
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(net.params[:n], expect[:n], rtol=1e-5, atol=1e-5), f"round {rnd}"
+        assert torch.equal(net.params16[:n], net.params[:n].bfloat16())
+        dist.barrier()
+
+
 def case_elastic(rank, world):
     comm = p2p.ElasticP2PComm(beta=0.25)
     oracle = comm_mod.ElasticComm(beta=0.25)
@@ -181,6 +207,8 @@ def main():
             case_gossip_pair(rank, world)
         elif case == "pull_rounds":
             case_pull_rounds(rank, world)
+        elif case.startswith("group_gossip"):
+            case_group_gossip(rank, world, int(case.rsplit("_", 1)[1]))
         elif case == "elastic":
             case_elastic(rank, world)
         elif case == "push":

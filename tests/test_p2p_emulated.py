@@ -1,0 +1,103 @@
+"""Host-side orchestration of the kernel-driven gossip backends, with the kernels replaced by CPU stand-ins.
+
+The stand-ins implement what the publish / mix kernels are specified to do (snapshot the vector; mix with a peer's
+snapshot of the same epoch), so these tests pin the sequence of launches, peers and weights that the Python side
+issues -- the part that needs no GPU. The kernels themselves are checked against library collectives on GPUs.
+"""
+import types
+
+import pytest
+import torch
+
+from rembrandt_b200.parallel import p2p
+from rembrandt_b200.parallel import p2p_kernels as PK
+from rembrandt_b200.utils.rng import XorShift128Plus
+
+
+class FakeWorld:
+    """All ranks in one process; launches are queued per rank and run phase by phase (publish, then the mixes)."""
+
+    def __init__(self, world, n):
+        self.world, self.n = world, n
+        self.w = [torch.zeros(n) for _ in range(world)]
+        self.queue = [[] for _ in range(world)]
+        self.current = 0
+
+    def fn(self, name):
+        def launch(args_ref, blocks, stream):
+            a = args_ref._obj
+            self.queue[self.current].append((name, a.peer, a.alpha, a.not_last, a.mix_self, a.wait_peer))
+            return 0
+        return launch
+
+    def run(self):
+        phases = []
+        for r in range(self.world):
+            mine, cur = [], None
+            for op in self.queue[r]:
+                if op[0] == "rb_publish_p2p":
+                    cur = []
+                    mine.append(cur)
+                else:
+                    cur.append(op)
+            phases.append(mine)
+        assert len({len(p) for p in phases}) == 1, "every rank must run the same number of publish phases"
+        for ph in range(len(phases[0])):
+            snap = [w.clone() for w in self.w]
+            for r in range(self.world):
+                ops = phases[r][ph]
+                assert ops, "a phase without a mix would never advance the epoch"
+                assert [o[3] for o in ops] == [1] * (len(ops) - 1) + [0], "only the last mix of a phase ends the epoch"
+                for _, peer, alpha, _, mix_self, wait_peer in ops:
+                    assert wait_peer == 1
+                    if peer != r or mix_self:
+                        self.w[r] = (1 - alpha) * self.w[r] + alpha * snap[peer]
+        self.queue = [[] for _ in range(self.world)]
+
+
+def _make(rank, world, group_size, seed, fake):
+    c = object.__new__(p2p.GroupGossipP2PComm)
+    c.rank, c.world, c.group, c.bytes_moved = rank, world, None, 0
+    c.mode, c.alpha, c.blocks, c.synchronous = "pull", 0.5, 8, True
+    c.rng = XorShift128Plus(seed[0] + 1000003 * rank, seed[1])
+    c._last_peer = None
+    c.group_size = max(1, min(group_size, world))
+    g0 = rank // c.group_size * c.group_size
+    c.group_peers = [r for r in range(g0, min(world, g0 + c.group_size)) if r != rank]
+    c.net = types.SimpleNamespace(params=fake.w[rank], params16=torch.zeros(1))
+    c.pub = torch.zeros(1)
+    c.epochs = torch.zeros(4, dtype=torch.int32)
+    c.counters = torch.zeros(4, dtype=torch.int32)
+    c.status = torch.zeros(1, dtype=torch.int32)
+    c.arena = types.SimpleNamespace(ptrs=lambda name: [0] * world)
+    return c
+
+
+@pytest.mark.parametrize("world,group_size", [(2, 1), (2, 2), (4, 2), (5, 3), (8, 4)])
+def test_group_gossip_launch_sequence_gives_group_mean_then_half_pull(monkeypatch, world, group_size):
+    n = 16
+    fake = FakeWorld(world, n)
+    monkeypatch.setattr(PK, "fn", fake.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    comms = [_make(r, world, group_size, (53, 59), fake) for r in range(world)]
+    for rnd in range(3):
+        torch.manual_seed(rnd)
+        start = [torch.randn(n) for _ in range(world)]
+        for r in range(world):
+            fake.w[r] = start[r].clone()
+            comms[r].net.params = fake.w[r]
+        for r in range(world):
+            fake.current = r
+            comms[r].sync_params(fake.w[r])
+        fake.run()
+        gmean = []
+        for r in range(world):
+            g0 = r // group_size * group_size
+            members = range(g0, min(world, g0 + group_size))
+            gmean.append(sum(start[m] for m in members) / len(members))
+        for r in range(world):
+            peer = comms[r]._last_peer[0]
+            assert torch.allclose(fake.w[r], 0.5 * (gmean[r] + gmean[peer]), atol=1e-6), (rnd, r)
+    # the draws are the per-rank streams of the library backend, so both backends pick the same peers
+    ref = XorShift128Plus(53 + 1000003 * 1, 59)
+    assert [ref.below(world) for _ in range(3)][-1] == comms[1]._last_peer[0]
