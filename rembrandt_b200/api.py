@@ -48,7 +48,7 @@ def model_config(model: str, synthetic_norm: bool = True, **kw):
 
 def default_opt(batch: int, comm_name: str = "null", lr: float = 0.01) -> SgdOptConfig:
     order = SyncOrder.SYNC_GRADS_THEN_STEP
-    if comm_name.startswith("gossip") or comm_name == "group_allreduce_gossip":
+    if comm_name.startswith("gossip") or comm_name.startswith("group_allreduce_gossip"):
         order = SyncOrder.STEP_THEN_SYNC_PARAMS
     elif comm_name.startswith("elastic"):
         order = SyncOrder.SYNC_PARAMS_THEN_STEP

@@ -48,6 +48,8 @@ class StepEngine:
             io = net.input_op
             self._stage_imgs = [torch.zeros_like(io.stage) for _ in range(2)]
             self._stage_lbls = [torch.zeros_like(net.loss_op.labels) for _ in range(2)]
+            # variable-size input: the per-sample (w, h) table travels with the padded pixel rows
+            self._stage_shapes = [torch.ones_like(io.shapes) for _ in range(2)] if hasattr(io, "shapes") else None
             self._copy_done = [torch.cuda.Event() for _ in range(2)]
             self._consumed = [torch.cuda.Event() for _ in range(2)]
             self._slot = 0
@@ -59,16 +61,27 @@ class StepEngine:
                 self.comm.attach(self)
 
     # ------------------------------------------------------------------ feeding
-    def feed(self, images_u8: torch.Tensor, labels: torch.Tensor) -> None:
-        """Queue one batch: async H2D into the free staging slot (pinned source for a true async copy)."""
+    def feed(self, images_u8, labels: torch.Tensor) -> None:
+        """Queue one batch: async H2D into the free staging slot (pinned source for a true async copy).
+
+        Fixed-size input: a uint8 [B, C, H, W] tensor. Variable-size input: a list of uint8 [C, h, w] tensors, or the
+        pair (padded uint8 [B, C * maxH * maxW], int32 [B, 2] of (w, h)) that `VarDataOp.pack` makes of such a list."""
         if not self.is_cuda:
             self.net.load_batch(images_u8, labels)
             return
+        shapes = None
+        if self._stage_shapes is not None:
+            io = self.net.input_op
+            if isinstance(images_u8, list) or images_u8[0].dim() == 3:
+                images_u8 = io.pack(list(images_u8), io.in_stride)
+            images_u8, shapes = images_u8
         s = self._slot
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self._consumed[s])
             self._stage_imgs[s].copy_(images_u8.reshape(self._stage_imgs[s].shape), non_blocking=True)
             self._stage_lbls[s].copy_(labels.reshape(-1), non_blocking=True)
+            if shapes is not None:
+                self._stage_shapes[s].copy_(shapes.reshape(self._stage_shapes[s].shape).int(), non_blocking=True)
             self._copy_done[s].record(self.copy_stream)
         self._pending = s
         self._slot ^= 1
@@ -76,13 +89,16 @@ class StepEngine:
     def h2d_bytes_per_step(self) -> int:
         if not self.is_cuda:
             return 0
-        return self._stage_imgs[0].numel() + self._stage_lbls[0].numel() * 4
+        extra = self._stage_shapes[0].numel() * 4 if self._stage_shapes is not None else 0
+        return self._stage_imgs[0].numel() + self._stage_lbls[0].numel() * 4 + extra
 
     # ------------------------------------------------------------------ one batch
     def _bind_inputs(self, slot):
         """Point the input and loss operators at a staging slot (device-to-device, on the compute stream)."""
         self.net.input_op.stage.copy_(self._stage_imgs[slot], non_blocking=True)
         self.net.loss_op.labels.copy_(self._stage_lbls[slot], non_blocking=True)
+        if self._stage_shapes is not None:
+            self.net.input_op.shapes.copy_(self._stage_shapes[slot], non_blocking=True)
 
     def _fwd_bwd(self, train=True, hook=None):
         self.net.forward(train, None)
@@ -233,7 +249,9 @@ class StepEngine:
             net.forward(False)
             return net.read_stats()
         with torch.cuda.stream(self.compute_stream):
-            net.load_batch(images_u8.to(net.device, non_blocking=True), labels.to(net.device, non_blocking=True).int())
+            if self._stage_shapes is None:
+                images_u8 = images_u8.to(net.device, non_blocking=True)
+            net.load_batch(images_u8, labels.to(net.device, non_blocking=True).int())
             net.forward(False)
         self.compute_stream.synchronize()
         return net.read_stats()
