@@ -305,6 +305,8 @@ class PullGossipComm(CommWorker):
         self.rng = XorShift128Plus(seed[0] + 1000003 * self.rank, seed[1])
         self.cfg = cfg
         self._last_table = None
+        # point-to-point operations name their peer by global rank; the peer table holds ranks within `group`
+        self._global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
 
     def draw_table(self, repeat=False):
         if repeat and self._last_table is not None:
@@ -326,10 +328,10 @@ class PullGossipComm(CommWorker):
             ops, recv = [], None
             for r in range(self.world):
                 if table[r][rnd] == self.rank and r != self.rank:
-                    ops.append(dist.P2POp(dist.isend, snapshot, r, self.group))
+                    ops.append(dist.P2POp(dist.isend, snapshot, self._global(r), self.group))
             if src != self.rank:
                 recv = torch.empty_like(flat)
-                ops.append(dist.P2POp(dist.irecv, recv, src, self.group))
+                ops.append(dist.P2POp(dist.irecv, recv, self._global(src), self.group))
             if ops:
                 for w in dist.batch_isend_irecv(ops):
                     w.wait()
@@ -376,28 +378,47 @@ class PushGossipComm(CommWorker):
 
 
 class GroupAllreduceGossipComm(CommWorker):
-    """Hierarchical: all-reduce inside groups of `group_size` ranks, then every rank pulls the vector of a
-    random rank and keeps 0.5 * (pulled + group mean) (the v2 scheme of the reference)."""
+    """Hierarchical: the mean inside groups of `group_size` consecutive ranks, then gossip between groups.
+
+    version 2 (default; gossip_pull_allreduce_dist_rdma_v2.rs:327-384): every rank pulls the group mean of a random
+    rank and keeps 0.5 * (pulled + own group mean).
+    version 1 (gossip_pull_allreduce_dist_rdma.rs:327-402): only the group leaders (first rank of each group) gossip:
+    a leader pulls the group mean of a random leader, keeps 0.5 * (pulled + own) unless it drew itself, and
+    broadcasts the result to its group."""
     name = "group_allreduce_gossip"
 
-    def __init__(self, group=None, group_size=2, seed=(53, 59)):
+    def __init__(self, group=None, group_size=2, seed=(53, 59), version=2):
         super().__init__(group)
+        if version not in (1, 2):
+            raise ValueError("version must be 1 or 2")
         self.group_size = max(1, min(group_size, self.world))
+        self.version = version
         self.subgroup = None
+        self.pull = None
         if self.world > 1:
             for g0 in range(0, self.world, self.group_size):
                 ranks = list(range(g0, min(self.world, g0 + self.group_size)))
                 sg = dist.new_group(ranks)
                 if self.rank in ranks:
                     self.subgroup, self.sub_n = sg, len(ranks)
-        self.pull = PullGossipComm(group, seed) if self.world > 1 else None
+            if version == 2:
+                self.pull = PullGossipComm(group, seed)
+            else:
+                leaders = list(range(0, self.world, self.group_size))
+                leader_group = dist.new_group(leaders)       # collective: every rank creates it, leaders use it
+                self.leader = self.rank // self.group_size * self.group_size
+                if self.rank == self.leader and len(leaders) > 1:
+                    self.pull = PullGossipComm(leader_group, seed)
 
     def sync_params(self, flat, repeat=False):
         if self.world <= 1:
             return
         dist.all_reduce(flat, group=self.subgroup)
         flat.div_(self.sub_n)
-        self.pull.sync_params(flat, repeat)
+        if self.pull is not None:
+            self.pull.sync_params(flat, repeat)
+        if self.version == 1 and self.sub_n > 1:
+            dist.broadcast(flat, self.leader, group=self.subgroup)
 
     allreduce_average = CommWorker.exact_sync
 

@@ -116,6 +116,21 @@ def hierarchical(rank, world):
     assert torch.allclose(x, 0.5 * (group_mean + peer_mean), atol=1e-6)
 
 
+def hierarchical_leaders(rank, world):
+    """Version 1: only the first rank of each group of two gossips; its group follows it."""
+    c = C.GroupAllreduceGossipComm(group_size=2, seed=(53, 59), version=1)
+    every = _all(world)
+    means = [sum(every[r] for r in range(g0, min(world, g0 + 2))) / len(range(g0, min(world, g0 + 2)))
+             for g0 in range(0, world, 2)]
+    shadows = [XorShift128Plus(53 + 1000003 * g, 59) for g in range(len(means))]   # one stream per leader
+    x = _vec(rank)
+    for rnd in range(3):
+        draws = [s.below(len(means)) for s in shadows]
+        c.sync_params(x)
+        means = [0.5 * (means[g] + means[draws[g]]) for g in range(len(means))]
+        assert torch.allclose(x, means[rank // 2], atol=1e-6), (rnd, rank)
+
+
 def exact_sync(rank, world):
     for cls in (C.PairGossipComm, C.PullGossipComm, C.PushGossipComm):
         x = _vec(rank)

@@ -33,6 +33,11 @@ def test_group_allreduce_then_gossip():
     run_ranks(4, cases.hierarchical)
 
 
+@pytest.mark.parametrize("world", [4, 5])
+def test_group_leaders_gossip_and_broadcast(world):
+    run_ranks(world, cases.hierarchical_leaders)
+
+
 def test_exact_sync_is_a_true_mean_for_gossip_backends():
     run_ranks(3, cases.exact_sync)
 
