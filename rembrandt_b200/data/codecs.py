@@ -1,6 +1,9 @@
 """Sample codecs and host-side augmentation (src/data/codec.rs, src/data/augment.rs, src/caffe_proto.proto).
 
 * ``Array3dDataCodec``   NdArray record -> uint8 array;
+* ``Bits3dCodec`` / ``BitsThenBytes3dCodec``  bit-plane samples (Go boards): packed bits expanded to 0 / `scale`,
+                         optionally followed by byte planes (SampleDatumConfig::{Bits3d, BitsThenBytes3d},
+                         src/data_new.rs:22-66);
 * ``FakeJpegDataCodec``  returns a zero 256x256x3 image whatever the bytes (the reference's fake for I/O tests);
 * ``JpegDataCodec``      real decode through Pillow when it is installed (the reference uses turbojpeg with an
                          stb fallback), grey -> RGB, HWC -> planar;
@@ -22,6 +25,69 @@ class Array3dDataCodec:
         recs, _ = blob.decode_records(value, "u8", count=1)
         data, dims, _ = recs[0]
         return data.reshape(tuple(reversed(dims)))
+
+
+BITS_TAG = (0x42, 0x01)   # 'B': the payload of this record is packed bits
+
+
+def encode_bits3d(planes) -> bytes:
+    """Pack a {0,1}-valued [C, H, W] array into a bit record: the NdArray header with dims (W, H, C) and tag 'B',
+    then ceil(W*H*C / 8) bytes, element i (first dimension fastest) in bit i % 8 of byte i // 8.
+
+    The reference's BitArray3d comes from a crate outside its tree, so its byte layout is not known; this layout
+    is this framework's own."""
+    a = np.ascontiguousarray(np.asarray(planes) != 0)
+    c, h, w = a.shape
+    packed = np.packbits(a.reshape(-1), bitorder="little")
+    return b"ND" + bytes(BITS_TAG) + np.uint32(3).tobytes() + np.asarray([w, h, c], dtype="<u8").tobytes() + packed.tobytes()
+
+
+def _decode_bits3d(value: bytes, offset: int, scale: int):
+    if value[offset:offset + 2] != b"ND" or tuple(value[offset + 2:offset + 4]) != BITS_TAG:
+        raise blob.BlobError(f"no bit record at offset {offset}")
+    if int(np.frombuffer(value, "<u4", 1, offset + 4)[0]) != 3:
+        raise blob.BlobError("bit records are three-dimensional")
+    w, h, c = (int(v) for v in np.frombuffer(value, "<u8", 3, offset + 8))
+    n = w * h * c
+    nbytes = (n + 7) // 8
+    start = offset + 32
+    if start + nbytes > len(value):
+        raise blob.BlobError("truncated bit record")
+    bits = np.unpackbits(np.frombuffer(value, np.uint8, nbytes, start), bitorder="little")[:n]
+    return (bits * np.uint8(scale)).reshape(c, h, w), start + nbytes
+
+
+class Bits3dCodec:
+    """Bit planes -> uint8 [C, H, W] holding 0 or `scale`."""
+
+    def __init__(self, scale: int = 255):
+        self.scale = scale
+
+    def decode(self, value: bytes) -> np.ndarray:
+        return _decode_bits3d(value, 0, self.scale)[0]
+
+
+class BitsThenBytes3dCodec:
+    """A bit record followed by a byte record of the same width and height: channels are concatenated, bit planes
+    first (a Go position: stone / liberty planes as bits, then a few byte-valued feature planes)."""
+
+    def __init__(self, scale: int = 255):
+        self.scale = scale
+
+    def decode(self, value: bytes) -> np.ndarray:
+        bits, off = _decode_bits3d(value, 0, self.scale)
+        recs, _ = blob.decode_records(value, "u8", offset=off, count=1)
+        data, dims, _ = recs[0]
+        planes = data.reshape(tuple(reversed(dims)))
+        if planes.shape[1:] != bits.shape[1:]:
+            raise blob.BlobError(f"bit planes {bits.shape} and byte planes {planes.shape} differ in size")
+        return np.concatenate([bits, planes], axis=0)
+
+    @staticmethod
+    def encode(bit_planes, byte_planes) -> bytes:
+        b = np.ascontiguousarray(np.asarray(byte_planes, dtype=np.uint8))
+        c, h, w = b.shape
+        return encode_bits3d(bit_planes) + blob.encode_record(b.reshape(-1), (w, h, c), "u8")
 
 
 class FakeJpegDataCodec:

@@ -955,6 +955,41 @@ class SoftmaxKLLossOp(Op):
         self.mask = None
         self._cpu_mask = None
         self.soft = None          # target distributions (distillation), [B * heads, K] float32
+        self._setup_flat()
+
+    def _setup_flat(self):
+        """A spatial producer (e.g. the 19 x 19 x 1 move plane of a Go network) leaves its outputs pixel-major with
+        padded channels; the head wants one dense row per sample in the reference's order (channel slowest:
+        index = x + W * (y + H * c)). `flat` / `dflat` are that row and its delta; copies in and out are strided
+        device copies into fixed buffers."""
+        h, w, c = self.prev.out_hwc
+        self.spatial = h * w > 1
+        self.flat = self.dflat = None
+        self.ld = pad_channels(h * w * c) if self.spatial else self.prev.out_cp
+
+    def _alloc_flat(self):
+        if self.spatial and self.net.is_cuda:
+            n = self.net.batch
+            self.flat = torch.zeros((n, self.ld), dtype=torch.bfloat16, device=self.net.device)
+            if self.net.training_capable:
+                self.dflat = torch.zeros_like(self.flat)
+
+    def _as_planes(self, buf):
+        h, w, c = self.prev.out_hwc
+        return buf[:, : h * w * c].view(self.net.batch, c, h, w)
+
+    def _logits(self):
+        """(logits buffer, its delta buffer or None) handed to the loss kernel."""
+        if not self.spatial:
+            return self.prev.out, self.prev.dout
+        c = self.prev.out_hwc[2]
+        self._as_planes(self.flat).copy_(self.prev.out[..., :c].permute(0, 3, 1, 2))
+        return self.flat, self.dflat
+
+    def _scatter_delta(self):
+        if self.spatial:
+            c = self.prev.out_hwc[2]
+            self.prev.dout[..., :c].copy_(self._as_planes(self.dflat).permute(0, 2, 3, 1))
 
     def alloc(self):
         dev = self.net.device
@@ -966,6 +1001,7 @@ class SoftmaxKLLossOp(Op):
         self.argmax = torch.zeros(n, dtype=torch.int32, device=dev)
         self.loss_per = torch.zeros(n * self.heads, dtype=torch.float32, device=dev)
         self.probs = None
+        self._alloc_flat()
 
     def load_labels(self, labels, non_blocking=True):
         self.labels.copy_(labels.reshape(-1), non_blocking=non_blocking)
@@ -1001,7 +1037,7 @@ class SoftmaxKLLossOp(Op):
         CDF + uniform draw). Call after `forward`; not on the training hot path (plain torch ops)."""
         n = self.net.batch
         if self.net.is_cuda:
-            logits = self.prev.out.reshape(n, -1)[:, : self.k].float()
+            logits = (self.flat if self.spatial else self.prev.out.reshape(n, -1))[:, : self.k].float()
             mask = None if self.mask is None else self.mask.reshape(n, self.heads, self.k)[:, 0].bool()
         else:
             logits = self.net._cpu_logits.flatten(1)[:, : self.k].float()
@@ -1027,11 +1063,14 @@ class SoftmaxKLLossOp(Op):
             self.soft = q
 
     def forward(self, train, t):
-        delta = self.prev.dout if (train and self.prev.dout is not None) else None
-        K.softmax_ce(self.prev.out, self.net.batch, self.k, self.out_cp, self.labels, self.weights,
+        logits, dbuf = self._logits()
+        delta = dbuf if (train and self.prev.dout is not None) else None
+        K.softmax_ce(logits, self.net.batch, self.k, self.ld, self.labels, self.weights,
                      self.net.sample_weight, delta, probs=self.probs, loss_sum=self.loss_sum, correct=self.correct,
                      loss_per=self.loss_per, argmax_out=self.argmax, cat_weights=self.cat_weights, mask=self.mask,
                      heads=self.heads, soft=self.soft)
+        if delta is not None:
+            self._scatter_delta()
 
     def ref_loss(self, logits, labels, weights=None):
         """Returns (weighted loss sum, number correct, argmax)."""
@@ -1080,6 +1119,7 @@ class PointwiseLossOp(SoftmaxKLLossOp):
             raise ValueError(f"loss expects {self.k} inputs, previous operator produces {h * w * c}")
         self.out_hwc, self.out_cp = prev.out_hwc, prev.out_cp
         self.cat_weights = self.mask = self._cpu_mask = self.soft = None
+        self._setup_flat()
 
     def alloc(self):
         super().alloc()
@@ -1089,9 +1129,12 @@ class PointwiseLossOp(SoftmaxKLLossOp):
         self.targets.copy_(labels.reshape(self.net.batch, self.k).float(), non_blocking=non_blocking)
 
     def forward(self, train, t):
-        delta = self.prev.dout if (train and self.prev.dout is not None) else None
-        K.pointwise_loss(self.prev.out, self.net.batch, self.k, self.out_cp, self.targets, self.weights,
+        logits, dbuf = self._logits()
+        delta = dbuf if (train and self.prev.dout is not None) else None
+        K.pointwise_loss(logits, self.net.batch, self.k, self.ld, self.targets, self.weights,
                          self.net.sample_weight, delta, loss_sum=self.loss_sum, correct=self.correct, mode=self.mode)
+        if delta is not None:
+            self._scatter_delta()
 
     def ref_loss(self, logits, labels, weights=None):
         n = logits.shape[0]

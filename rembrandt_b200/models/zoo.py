@@ -251,8 +251,23 @@ def go_policy_net(planes=32, channels=128, layers=6, num_classes=361):
     return cfg.softmax_kl_loss(SoftmaxKLLossCfg(num_classes))
 
 
+def go_policy_resnet(planes=32, channels=128, blocks=5, num_classes=361):
+    """The residual move-prediction network the reference's Go tool trains (tools/train-gogod.rs:59-158): a
+    batch-normalised 3x3 stem, `blocks` two-convolution residual blocks (moving-average factor 0.01, epsilon 1e-4)
+    and a 3x3 convolution to one plane, whose 19 x 19 outputs are the 361 move logits."""
+    k = ParamsInit.kaiming()
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((19, 19, planes), normalize=True))
+    mov = BNormMovingAverage("exponential", 0.01)
+    cfg.bnorm_conv2d(BNormConv2dCfg(3, 1, 1, channels, Act.RECT, k, mov, 1e-4), "stem")
+    for i in range(blocks):
+        cfg.stack_res_conv2d(StackResConv2dCfg(k, mov, 1e-4), f"res{i + 1}")
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 1, Act.IDENTITY, k), "move")
+    return cfg.softmax_kl_loss(SoftmaxKLLossCfg(num_classes))
+
+
 TEMPLATES = {
     "mnist_fc1": mnist_fc1, "mnist_fc2": mnist_fc2, "lenet": lenet, "cifar_krizh26": cifar_krizh26,
     "alexnet": alexnet, "nin": nin, "vgg_a": vgg_a, "resnet10": resnet10, "resnet18": resnet18,
     "resnet34": resnet34, "resnet20_cifar": resnet20_cifar, "go_policy_net": go_policy_net,
+    "go_policy_resnet": go_policy_resnet,
 }

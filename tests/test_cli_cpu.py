@@ -1,0 +1,41 @@
+"""The command-line entry points run end to end on CPU with tiny settings."""
+import os
+
+import pytest
+
+from rembrandt_b200.cli import (bench_kernels, dist_train_mnist, run_rembrandt, test_dist, train_cifar10, train_gogod,
+                                train_mnist)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TINY = ["--device", "cpu", "--batch", "8", "--iters", "3", "--display-iters", "1", "--synthetic-size", "64"]
+
+
+def test_train_mnist_and_its_distributed_alias():
+    sgd = train_mnist.main(TINY + ["--valid-iters", "0"])
+    assert sgd.engine.iter == 3
+    assert dist_train_mnist.main(TINY + ["--valid-iters", "0", "--model", "fc1"]).engine.iter == 3
+
+
+def test_train_cifar10():
+    assert train_cifar10.main(TINY).engine.iter == 3
+
+
+@pytest.mark.parametrize("arch", ["resnet", "plain"])
+def test_train_gogod(arch):
+    sgd = train_gogod.main(TINY + ["--arch", arch, "--channels", "8", "--blocks", "2", "--planes", "6"])
+    assert sgd.engine.iter == 3
+    assert sgd.engine.net.loss_op.k == 361
+
+
+def test_run_rembrandt_from_descriptors():
+    sgd = run_rembrandt.main(TINY + ["--model-file", os.path.join(ROOT, "examples", "mnist_lenet.model"),
+                                     "--data", os.path.join(ROOT, "examples", "synthetic_mnist.data"),
+                                     "--valid-iters", "1"])
+    assert sgd.engine.iter == 3
+
+
+def test_host_side_probes():
+    res = bench_kernels.main(["--no-device"])
+    assert [r["requested_us"] for r in res["sleep"]] == [1, 10, 100, 1000, 10000]
+    assert all(r["observed_us"] >= r["requested_us"] for r in res["sleep"])
+    assert test_dist.main(["--device", "cpu"]) == (0, 1)

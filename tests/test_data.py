@@ -264,3 +264,20 @@ def test_native_batch_loader_order_is_deterministic_and_sharded(mode, threads):
         assert not np.array_equal(flat[:ep], flat[ep:2 * ep])
     if mode == "random":
         assert len(set(flat.tolist())) > (hi - lo) // 2
+
+
+def test_bit_plane_codecs_round_trip():
+    from rembrandt_b200.data import codecs
+    from rembrandt_b200.utils import blob
+    rng = np.random.default_rng(0)
+    bits = rng.integers(0, 2, (5, 19, 19))
+    planes = rng.integers(0, 256, (3, 19, 19)).astype(np.uint8)
+    rec = codecs.BitsThenBytes3dCodec.encode(bits, planes)
+    assert len(rec) == 32 + (5 * 361 + 7) // 8 + 32 + 3 * 361        # two headers, packed bits, bytes
+    out = codecs.BitsThenBytes3dCodec(255).decode(rec)
+    assert out.shape == (8, 19, 19) and (out[:5] == bits * 255).all() and (out[5:] == planes).all()
+    assert (codecs.Bits3dCodec(7).decode(codecs.encode_bits3d(bits)) == bits * 7).all()
+    with pytest.raises(blob.BlobError):
+        codecs.Bits3dCodec().decode(rec[:40])
+    with pytest.raises(blob.BlobError):
+        codecs.Bits3dCodec().decode(blob.encode_record(planes.reshape(-1), (19, 19, 3), "u8"))   # not a bit record

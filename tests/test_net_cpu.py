@@ -299,3 +299,31 @@ def test_mimic_affine_expands_into_a_low_rank_chain():
     other = Net(cfg, 3, device="cpu", seed=(9, 9))
     other.decode_params(net.encode_params())
     assert torch.equal(other.params, net.params)
+
+
+def test_loss_head_dense_row_of_a_spatial_producer():
+    """The device path hands the loss kernel one dense row per sample in the reference's order (channel slowest);
+    the copies in and out of that row are plain strided copies, checked here on CPU tensors."""
+    import types
+    from rembrandt_b200.models.operators import SoftmaxKLLossOp
+    from rembrandt_b200.ops.native_ops import pad_channels
+    n, h, w, c, cp = 3, 5, 4, 2, 32
+    op = object.__new__(SoftmaxKLLossOp)
+    op.net = types.SimpleNamespace(batch=n, is_cuda=True, training_capable=True, device="cpu")
+    nchw = torch.randn(n, c, h, w).bfloat16()
+    out = torch.zeros(n, h, w, cp, dtype=torch.bfloat16)
+    out[..., :c] = nchw.permute(0, 2, 3, 1)
+    op.prev = types.SimpleNamespace(out=out, dout=torch.zeros_like(out), out_hwc=(h, w, c), out_cp=cp)
+    op._setup_flat()
+    assert op.spatial and op.ld == pad_channels(h * w * c)
+    op._alloc_flat()
+    logits, dbuf = op._logits()
+    assert torch.equal(logits[:, : h * w * c], nchw.flatten(1)) and torch.all(logits[:, h * w * c:] == 0)
+    dbuf.copy_(torch.randn_like(dbuf.float()).bfloat16())
+    op._scatter_delta()
+    assert torch.equal(op.prev.dout[..., :c].permute(0, 3, 1, 2).flatten(1), dbuf[:, : h * w * c])
+    assert torch.all(op.prev.dout[..., c:] == 0)
+    # a 1 x 1 producer is used in place
+    op.prev = types.SimpleNamespace(out=out[:, :1, :1], dout=None, out_hwc=(1, 1, 10), out_cp=cp)
+    op._setup_flat()
+    assert not op.spatial and op.ld == cp and op._logits()[0] is op.prev.out
