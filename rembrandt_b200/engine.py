@@ -24,6 +24,7 @@ from .optim.sgd import Momentum, SgdOptConfig, SyncOrder
 from .optim.stepper import SgdStepper
 from .ops import native_ops as K
 from .parallel.comm import CommWorker, NullComm
+from .utils.trace import span
 
 
 class StepEngine:
@@ -101,14 +102,20 @@ class StepEngine:
             self.net.input_op.shapes.copy_(self._stage_shapes[slot], non_blocking=True)
 
     def _fwd_bwd(self, train=True, hook=None):
-        self.net.forward(train, None)
+        with span("forward"):
+            self.net.forward(train, None)
         if train:
-            self.net.backward(hook)
+            with span("backward"):
+                self.net.backward(hook)
         if self.is_cuda:
             self.net.step_counter.add_(1)
 
     def _update(self):
         """Exchange + optimizer step for one iteration, in the configured order."""
+        with span("update"):
+            self._update_in_order()
+
+    def _update_in_order(self):
         o, c, st, net = self.opt, self.comm, self.stepper, self.net
         lr = self.lr
         communicate = c.num_workers() > 1 and (self.iter % max(1, o.comm_interval) == 0)

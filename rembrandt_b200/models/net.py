@@ -21,6 +21,7 @@ import torch
 
 from ..utils import blob
 from ..utils.rng import XorShift128Plus
+from ..utils.trace import span
 from . import config as C
 from . import operators as O
 
@@ -254,7 +255,8 @@ class Net:
             if t is not None:
                 self.step_counter.fill_(int(t))
             for op in self.ops:
-                op.forward(train, self.t if t is None else t)
+                with span(op.name):
+                    op.forward(train, self.t if t is None else t)
             return None
         t = self.t if t is None else t
         images, labels, weights = self._cpu_batch
@@ -281,7 +283,8 @@ class Net:
         gradients (the communication backends start a bucket's exchange from it)."""
         if self.is_cuda:
             for i in range(len(self.ops) - 2, 0, -1):
-                self.ops[i].backward()
+                with span(self.ops[i].name):
+                    self.ops[i].backward()
                 if hook is not None:
                     hook(i)
             return

@@ -32,8 +32,39 @@ from .comm import AllreduceComm, CommWorker, GossipConfig
 ALIGN = 64
 
 
+GUARD_PATTERN = 0xA5
+
+
+def guard_bytes() -> int:
+    """Size of the guard band on each side of a peer-visible buffer: 256 bytes with RB_ARENA_GUARD=1, else none."""
+    return 256 if os.environ.get("RB_ARENA_GUARD", "0") == "1" else 0
+
+
+def arm_guards(raw: torch.Tensor, guard_elems: int) -> torch.Tensor:
+    """Fill the first and last `guard_elems` elements of `raw` with the guard pattern; returns the payload view."""
+    if guard_elems == 0:
+        return raw
+    b = raw.view(torch.uint8)
+    gb = guard_elems * raw.element_size()
+    b[:gb] = GUARD_PATTERN
+    b[-gb:] = GUARD_PATTERN
+    return raw[guard_elems: raw.numel() - guard_elems]
+
+
+def guards_intact(raw: torch.Tensor, guard_elems: int) -> bool:
+    if guard_elems == 0:
+        return True
+    b = raw.view(torch.uint8)
+    gb = guard_elems * raw.element_size()
+    return bool((b[:gb] == GUARD_PATTERN).all()) and bool((b[-gb:] == GUARD_PATTERN).all())
+
+
 class SymmetricArena:
-    """Peer-visible device tensors (one allocation per name) and their per-rank addresses."""
+    """Peer-visible device tensors (one allocation per name) and their per-rank addresses.
+
+    With RB_ARENA_GUARD=1 every buffer gets a 256-byte band of a fixed pattern before and after its payload; peers
+    address the payload, so a kernel of any rank that writes outside a buffer it was given lands in a band and
+    `damaged()` names the buffer (a debugging aid in place of a memory checker; off by default)."""
 
     def __init__(self, group=None):
         import torch.distributed._symmetric_memory as symm_mem
@@ -42,23 +73,36 @@ class SymmetricArena:
         self.rank = dist.get_rank(self.group)
         self.world = dist.get_world_size(self.group)
         self.tensors, self.handles = {}, {}
+        self._raw, self._guard = {}, {}
 
     def alloc(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
         dev = torch.device("cuda", torch.cuda.current_device())
-        t = self._symm.empty(int(numel), dtype=dtype, device=dev)
-        t.zero_()
-        h = self._symm.rendezvous(t, self.group.group_name)
+        g = guard_bytes() // torch.empty(0, dtype=dtype).element_size()
+        raw = self._symm.empty(int(numel) + 2 * g, dtype=dtype, device=dev)
+        raw.zero_()
+        t = arm_guards(raw, g)
+        h = self._symm.rendezvous(raw, self.group.group_name)
         self.tensors[name], self.handles[name] = t, h
+        self._raw[name], self._guard[name] = raw, g
         return t
 
+    def _payload_offset(self, name: str) -> int:
+        return self._guard[name] * self._raw[name].element_size()
+
     def ptrs(self, name: str) -> List[int]:
-        return [int(p) for p in self.handles[name].buffer_ptrs]
+        off = self._payload_offset(name)
+        return [int(p) + off for p in self.handles[name].buffer_ptrs]
 
     def multicast_ptr(self, name: str) -> int:
         try:
-            return int(self.handles[name].multicast_ptr or 0)
+            mc = int(self.handles[name].multicast_ptr or 0)
         except Exception:
             return 0
+        return mc + self._payload_offset(name) if mc else 0
+
+    def damaged(self) -> List[str]:
+        """Names of this rank's buffers whose guard bands no longer hold the pattern (always empty without guards)."""
+        return [n for n, raw in self._raw.items() if not guards_intact(raw, self._guard[n])]
 
     def barrier(self, name: str):
         self.handles[name].barrier()

@@ -82,6 +82,10 @@ class TraceLog:
             self.file = None
 
 
+class DeviceWaitTimeout(RuntimeError):
+    """A kernel gave up a bounded wait on another rank (its flag never arrived): that rank is gone or stuck."""
+
+
 class SgdOpt:
     def __init__(self, config: SgdOptConfig, engine: StepEngine, experiment: Optional[ExperimentConfig] = None,
                  log_dir: Optional[str] = None, report=None, quiet: bool = False):
@@ -115,6 +119,36 @@ class SgdOpt:
     def _log(self, msg):
         if self.rank == 0 and not self.quiet:
             print(msg, file=sys.stderr, flush=True)
+
+    # ------------------------------------------------------------------ failure detection
+    def _device_status(self) -> int:
+        """The status word in which the kernels record a wait that ran out (0 = healthy). One small device read;
+        called only where the loop has just synchronised anyway."""
+        if not self.engine.is_cuda:
+            return 0
+        from .ops import native_ops as K
+        return K.read_status()
+
+    def _check_device_status(self, t: int) -> None:
+        """The exchange kernels never hang on a missing peer: they give up after a deadline, set a bit in the status
+        word and return, and the step goes on with whatever data was there. The reference panics on any MPI / CUDA
+        error (e.g. src/worker/allreduce_dist.rs:231); here the loop stops at the next display point instead: no
+        collective can be trusted once a peer is gone, so this rank writes its own state beside the regular
+        checkpoints (`state.abort.blob.<rank>`, never over them) and raises."""
+        arena = getattr(self.comm, "arena", None)
+        damaged = arena.damaged() if arena is not None else []
+        if damaged:   # only with RB_ARENA_GUARD=1: some kernel wrote outside a peer-visible buffer
+            raise RuntimeError(f"rank {self.rank}: guard bands of peer-visible buffers overwritten: {damaged}")
+        status = self._device_status()
+        if status == 0:
+            return
+        saved = None
+        if self.cfg.checkpoint_dir:
+            saved = ckpt.checkpoint_state(self.net, self.cfg.checkpoint_dir, self.rank, name="state.abort.blob")
+        self.trace.row(t, "abort", float(status), 0.0, 0.0)
+        self.trace.close()
+        raise DeviceWaitTimeout(f"rank {self.rank}: device status {status:#x} at iteration {t}: a bounded wait on a "
+                                f"peer ran out" + (f"; local state written to {saved}" if saved else ""))
 
     def before_step(self, images, labels):
         """Hook run before every batch is fed (used by the distillation optimizer)."""
@@ -182,6 +216,7 @@ class SgdOpt:
                         ms = dev_t0.elapsed_time(dev_t1)
                         ips = cfg.display_iters * batches_per_iter * net.batch * self.world / (ms / 1e3)
                         dev_t0, dev_t1 = dev_t1, torch.cuda.Event(enable_timing=True)
+                    self._check_device_status(t)
                     sums = self.shared.sync([disp_loss, disp_correct, disp_samples])
                     n = max(1.0, sums[2])
                     avg_loss = sums[0] * batches_per_iter / max(1.0, sums[2] / net.batch)
@@ -215,6 +250,7 @@ class SgdOpt:
         cfg, eng, net, comm = self.cfg, self.engine, self.net, self.comm
         eng.flush()
         eng.synchronize()
+        self._check_device_status(t)
         while not comm.wait_barrier():
             time.sleep(0.001)
         if cfg.checkpoint == CheckpointBehavior.DISCARD:

@@ -45,9 +45,9 @@ def checkpoint_params(net, t: int, directory: str, prefix: str = "params") -> st
     return path
 
 
-def checkpoint_state(net, directory: str, rank: int = 0) -> str:
+def checkpoint_state(net, directory: str, rank: int = 0, name: str = "state.latest.blob") -> str:
     os.makedirs(directory, exist_ok=True)
-    path = os.path.join(directory, f"state.latest.blob.{rank}")
+    path = os.path.join(directory, f"{name}.{rank}")
     _atomic_write(path, net.encode_state())
     return path
 

@@ -62,3 +62,50 @@ def format_op_times(rows) -> str:
         out.append(f"{r['name']:>12s} {r['type']:<22s} {r['fwd_ms']:9.3f} {r['bwd_ms']:9.3f}")
     out.append(f"{'total':>12s} {'':<22s} {sum(r['fwd_ms'] for r in rows):9.3f} {sum(r['bwd_ms'] for r in rows):9.3f}")
     return "\n".join(out)
+
+
+def time_phases(engine, iters: int = 5, warmup: int = 2) -> Dict[str, float]:
+    """Device milliseconds per phase of one eager training step on the batch already loaded into the network:
+    forward, backward (the launches of an overlapped gradient exchange are issued from inside it) and the tail from the
+    end of backward to the end of the update (exchange not hidden behind backward + optimizer step). On several ranks
+    every figure is the maximum over ranks. Call between steps, never inside a graph capture."""
+    import torch.distributed as dist
+
+    net = engine.net
+
+    def one(record):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(4)] if record else None
+        hook = None
+        if engine._overlapped():
+            engine.comm.prepare(engine.stepper, engine.lr)
+            hook = engine.comm.on_op_backward
+        if record:
+            marks[0].record()
+        net.forward(True, None)
+        if record:
+            marks[1].record()
+        net.backward(hook)
+        if record:
+            marks[2].record()
+        net.step_counter.add_(1)
+        engine._update()
+        if record:
+            marks[3].record()
+        return marks
+
+    with torch.cuda.stream(engine.compute_stream):
+        for _ in range(warmup):
+            one(False)
+        acc = [0.0, 0.0, 0.0]
+        for _ in range(iters):
+            m = one(True)
+            m[3].synchronize()
+            for i in range(3):
+                acc[i] += m[i].elapsed_time(m[i + 1])
+    out = torch.tensor([a / iters for a in acc], dtype=torch.float64)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dev = out.cuda() if dist.get_backend() == "nccl" else out
+        dist.all_reduce(dev, op=dist.ReduceOp.MAX)
+        out = dev.cpu()
+    fwd, bwd, tail = (float(v) for v in out)
+    return {"forward_ms": fwd, "backward_ms": bwd, "exchange_update_tail_ms": tail, "step_ms": fwd + bwd + tail}

@@ -101,3 +101,34 @@ def test_group_gossip_launch_sequence_gives_group_mean_then_half_pull(monkeypatc
     # the draws are the per-rank streams of the library backend, so both backends pick the same peers
     ref = XorShift128Plus(53 + 1000003 * 1, 59)
     assert [ref.below(world) for _ in range(3)][-1] == comms[1]._last_peer[0]
+
+
+def test_guard_bands_detect_writes_outside_the_payload(monkeypatch):
+    monkeypatch.setenv("RB_ARENA_GUARD", "1")
+    assert p2p.guard_bytes() == 256
+    for dtype in (torch.float32, torch.int32, torch.bfloat16, torch.uint8):
+        g = p2p.guard_bytes() // torch.empty(0, dtype=dtype).element_size()
+        raw = torch.zeros(100 + 2 * g, dtype=dtype)
+        payload = p2p.arm_guards(raw, g)
+        assert payload.numel() == 100 and payload.data_ptr() == raw.data_ptr() + 256
+        payload.fill_(3)
+        assert p2p.guards_intact(raw, g)
+        raw[g - 1] = 1                      # one element before the payload
+        assert not p2p.guards_intact(raw, g)
+        p2p.arm_guards(raw, g)
+        raw[g + 100] = 1                    # one element after it
+        assert not p2p.guards_intact(raw, g)
+    monkeypatch.setenv("RB_ARENA_GUARD", "0")
+    assert p2p.guard_bytes() == 0
+    raw = torch.zeros(8)
+    assert p2p.arm_guards(raw, 0) is raw and p2p.guards_intact(raw, 0)
+
+
+def test_trace_spans_are_inert_without_cuda(monkeypatch):
+    from rembrandt_b200.utils import trace
+    with trace.span("x"):
+        pass
+    monkeypatch.setattr(trace, "ENABLED", True)
+    with trace.span("forward"):             # no CUDA here: still nothing to push
+        pass
+    assert trace.span("a") is trace.span("b")

@@ -213,3 +213,24 @@ def test_async_sgd_opt_checkpoints_locally_without_barriers(tmp_path):
     opt_s, eng_s, net_s = make(batch=16)
     SgdOpt(opt_s, eng_s, quiet=True).train(mnist_shape_batches(1, 16, 8), None, max_iters=8)
     assert torch.allclose(net.params.detach(), net_s.params.detach(), atol=1e-6)
+
+
+def test_a_device_wait_that_ran_out_stops_the_loop_and_keeps_local_state(tmp_path):
+    """The status word is faked on the host (nothing on a GPU is made to time out): from iteration 6 on it reports a
+    peer timeout; the loop must stop at the next display point, leave the regular checkpoints alone and write this
+    rank's state under its own name."""
+    from rembrandt_b200.trainer import DeviceWaitTimeout
+    opt, eng, net = make(display_iters=4, checkpoint_iters=4, save_iters=4, checkpoint_dir=str(tmp_path))
+    sgd = SgdOpt(opt, eng, quiet=True)
+    sgd._device_status = lambda: 0x2 if eng.iter >= 6 else 0
+    with pytest.raises(DeviceWaitTimeout, match="status 0x2 at iteration 8"):
+        sgd.train(mnist_shape_batches(3, steps=40), max_iters=40)
+    assert eng.iter == 8
+    names = sorted(os.listdir(tmp_path))
+    assert "state.abort.blob.0" in names and "params.t_4.blob" in names and "params.t_8.blob" not in names
+    rows = list(csv.reader(open(os.path.join(tmp_path, "trace_sgd.0.log"))))
+    assert rows[-1][:2] == ["8", "abort"]
+    # the aborted state is a complete state blob: a fresh network can load it
+    other = Net(zoo.mnist_fc1(), 64, device="cpu", seed=(5, 5), minibatch_size=64)
+    other.decode_state(open(os.path.join(tmp_path, "state.abort.blob.0"), "rb").read())
+    assert torch.equal(other.params, net.params)
