@@ -120,6 +120,19 @@ class SgdOpt:
         if self.rank == 0 and not self.quiet:
             print(msg, file=sys.stderr, flush=True)
 
+    def _exchange_rate(self, iters: int, device_ms: float) -> Optional[float]:
+        """GB/s of exchange traffic per rank averaged over the device time of `iters` iterations: the flat vector
+        once per exchange, times 2 (N - 1) / N for the all-reduce backends (the usual bus-bandwidth convention).
+        The exchange overlaps the backward pass, so this is a rate the step sustains, not the speed of the exchange
+        kernels alone (that is what `cli/bench_allreduce.py` measures)."""
+        if self.world <= 1 or device_ms <= 0:
+            return None
+        exchanges = iters / max(1, self.cfg.comm_interval)
+        payload = self.net.flat_len * 4.0 * exchanges
+        if "allreduce" in self.comm.name and "gossip" not in self.comm.name:
+            payload *= 2.0 * (self.world - 1) / self.world
+        return payload / (device_ms * 1e-3) / 1e9
+
     # ------------------------------------------------------------------ failure detection
     def _device_status(self) -> int:
         """The status word in which the kernels record a wait that ran out (0 = healthy). One small device read;
@@ -209,12 +222,13 @@ class SgdOpt:
                 comm.hack_set_step_size(eng.lr)
 
                 if cfg.display_iters and t % cfg.display_iters == 0:
-                    ips = None
+                    ips = bus = None
                     if eng.is_cuda:
                         dev_t1.record(eng.compute_stream)
                         dev_t1.synchronize()
                         ms = dev_t0.elapsed_time(dev_t1)
                         ips = cfg.display_iters * batches_per_iter * net.batch * self.world / (ms / 1e3)
+                        bus = self._exchange_rate(cfg.display_iters, ms)
                         dev_t0, dev_t1 = dev_t1, torch.cuda.Event(enable_timing=True)
                     self._check_device_status(t)
                     sums = self.shared.sync([disp_loss, disp_correct, disp_samples])
@@ -227,7 +241,8 @@ class SgdOpt:
                     wall = time.time() - disp_wall
                     disp_wall = time.time()
                     self._log(f"iter {t} epoch {epoch} step {eng.lr:.6g} loss {avg_loss:.4f} accuracy {acc:.4f} "
-                              f"elapsed {wall:.3f}s" + (f" device {ips:.0f} images/s" if ips else ""))
+                              f"elapsed {wall:.3f}s" + (f" device {ips:.0f} images/s" if ips else "") +
+                              (f" exchange {bus:.1f} GB/s" if bus else ""))
                     disp_loss = disp_correct = disp_samples = 0.0
 
                 if cfg.checkpoint_iters and t % cfg.checkpoint_iters == 0:

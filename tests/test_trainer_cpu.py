@@ -234,3 +234,16 @@ def test_a_device_wait_that_ran_out_stops_the_loop_and_keeps_local_state(tmp_pat
     other = Net(zoo.mnist_fc1(), 64, device="cpu", seed=(5, 5), minibatch_size=64)
     other.decode_state(open(os.path.join(tmp_path, "state.abort.blob.0"), "rb").read())
     assert torch.equal(other.params, net.params)
+
+
+def test_exchange_rate_uses_the_bus_bandwidth_convention():
+    import types
+    opt, eng, net = make()
+    sgd = SgdOpt(opt, eng, quiet=True)
+    assert sgd._exchange_rate(10, 5.0) is None                     # one worker: nothing is exchanged
+    sgd.world = 8
+    sgd.comm = types.SimpleNamespace(name="fused_allreduce_sgd")
+    per_iter = net.flat_len * 4.0
+    assert sgd._exchange_rate(10, 5.0) == pytest.approx(10 * per_iter * 1.75 / 5e-3 / 1e9)
+    sgd.comm = types.SimpleNamespace(name="gossip_p2p")
+    assert sgd._exchange_rate(10, 5.0) == pytest.approx(10 * per_iter / 5e-3 / 1e9)
