@@ -41,8 +41,7 @@ __device__ __forceinline__ void sgd_elem(float& w, float& g, float& v, const Sgd
       if (upd) w -= a.lr * gp + a.lr * a.mu * v;
       break;
     case 5:
-      if (upd) w -= a.lr * gp;
-      g = a.mu * gp;
+      if (upd) { w -= a.lr * gp; g = a.mu * gp; }   // the decay belongs to the applying phase: once per step
       break;
   }
   if (zero && a.mode != 5) g = 0.f;

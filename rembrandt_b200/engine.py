@@ -112,7 +112,8 @@ class StepEngine:
 
     def _update(self):
         """Exchange + optimizer step for one iteration, in the configured order."""
-        with span("update"):
+        # no_grad: on CPU the flat parameter vector is an autograd leaf, and the exchanges mix it in place
+        with span("update"), torch.no_grad():
             self._update_in_order()
 
     def _update_in_order(self):

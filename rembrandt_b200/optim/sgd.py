@@ -181,9 +181,9 @@ def reference_step(w, g, v, lr, mu, l2, grad_scale, mode, phase=7):
         if upd:
             w.sub_(lr * gp + lr * mu * v)
     elif mode == 5:
-        if upd:
+        if upd:   # the decay of the gradient belongs to the applying phase, so that split phases decay it once
             w.sub_(lr * gp)
-        g.copy_(mu * gp)
+            g.copy_(mu * gp)
     else:
         raise ValueError(mode)
     if zero and mode != 5:

@@ -194,3 +194,119 @@ def dp_training_matches_single_process(rank, world):
     ref = net.params.detach().clone()
     dist.broadcast(ref, 0)
     assert torch.equal(ref, net.params.detach()), "replicas diverged"
+
+
+def rules_times_orders(rank, world):
+    """Every momentum rule under every synchronisation order (6 x 4 pairs), two ranks each."""
+    from rembrandt_b200.optim.sgd import Momentum, SyncOrder
+    failures = []
+    for mode in Momentum:
+        for order in SyncOrder:
+            try:
+                _rule_and_order(rank, world, int(mode), order.value)
+            except AssertionError as e:
+                failures.append(str(e))
+    assert not failures, "\n".join(failures)
+
+
+def _rule_and_order(rank, world, mode_value, order_value):
+    """Two data-parallel ranks under one (momentum rule, synchronisation order) pair against a NumPy restatement of
+    that pair which simulates both ranks in one process (gradients from single-process networks, the update rules and
+    the averaging written out with NumPy)."""
+    import numpy as np
+
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.sgd import Momentum, SgdOptConfig, StepSizeSchedule, SyncOrder
+
+    mode, order = Momentum(mode_value), SyncOrder(order_value)
+    lr, mu, l2, per, steps = 0.05, 0.9, 1e-3, 8, 4
+    mu_eff = 0.0 if mode == Momentum.ZERO else mu
+
+    def batch(r, s):
+        g = torch.Generator().manual_seed(1000 * s + r)
+        return (torch.randint(0, 256, (per, 1, 28, 28), dtype=torch.uint8, generator=g),
+                torch.randint(0, 10, (per,), dtype=torch.int32, generator=g))
+
+    opt = SgdOptConfig(minibatch_size=per, step_size=StepSizeSchedule.constant(lr), momentum=mode, mu=mu,
+                       l2_reg_coef=l2, sync_order=order)
+    net = Net(zoo.mnist_fc2(), per, device="cpu", seed=(3, 7), minibatch_size=per)
+    eng = StepEngine(net, opt, C.AllreduceComm())
+    for s in range(steps):
+        eng.feed(*batch(rank, s))
+        eng.step()
+
+    # ---- the restatement: both ranks, NumPy state
+    sims = [Net(zoo.mnist_fc2(), per, device="cpu", seed=(3, 7), minibatch_size=per) for _ in range(world)]
+    d = sims[0].decay_len
+    w = [n.params.detach().numpy().astype(np.float64).copy() for n in sims]
+    v = [np.zeros_like(w[0]) for _ in sims]
+    g = [np.zeros_like(w[0]) for _ in sims]
+    lam = np.zeros_like(w[0])
+    lam[:d] = l2
+    m = int(mode)
+
+    def accumulate(r):
+        gp = g[r] + lam * w[r]
+        if m in (0, 1):
+            v[r] = mu_eff * v[r] - lr * gp
+        elif m == 2:
+            w[r] = w[r] - mu_eff * v[r]
+            v[r] = mu_eff * v[r] - lr * (g[r] + lam * (w[r] + mu_eff * v[r]))   # regulariser sees the stored parameters
+        elif m in (3, 4):
+            v[r] = mu_eff * v[r] + gp
+
+    def apply(r):
+        gp = g[r] + lam * w[r]
+        if m in (0, 1):
+            w[r] = w[r] + v[r]
+        elif m == 2:
+            w[r] = w[r] + v[r] + mu_eff * v[r]
+        elif m == 3:
+            w[r] = w[r] - lr * v[r]
+        elif m == 4:
+            w[r] = w[r] - lr * gp - lr * mu_eff * v[r]
+        elif m == 5:
+            w[r] = w[r] - lr * gp
+        g[r] = mu_eff * gp if m == 5 else np.zeros_like(gp)
+
+    def mean(xs):
+        avg = sum(xs) / len(xs)
+        return [avg.copy() for _ in xs]
+
+    for s in range(steps):
+        for r, n in enumerate(sims):
+            with torch.no_grad():
+                n.params.copy_(torch.from_numpy(w[r]).float())
+                n.grads.zero_()
+            n.load_batch(*batch(r, s))
+            n.forward(True)
+            n.backward()
+            n.read_stats()
+            g[r] = g[r] + n.grads.detach().numpy().astype(np.float64)
+        if order == SyncOrder.SYNC_GRADS_THEN_STEP:
+            g = mean(g)
+            for r in range(world):
+                accumulate(r)
+                apply(r)
+        elif order == SyncOrder.STEP_THEN_SYNC_PARAMS:
+            for r in range(world):
+                accumulate(r)
+                apply(r)
+            w = mean(w)
+        elif order == SyncOrder.SYNC_PARAMS_THEN_STEP:
+            for r in range(world):
+                accumulate(r)
+            w = mean(w)
+            for r in range(world):
+                apply(r)
+        else:
+            w = mean(w)
+            g = mean(g)
+            for r in range(world):
+                accumulate(r)
+                apply(r)
+    got = net.params.detach().numpy().astype(np.float64)
+    err = np.abs(got - w[rank]).max()
+    assert err < 5e-5, f"{mode.name} x {order.name}: rank {rank} differs from the restatement by {err:.3g}"

@@ -63,6 +63,10 @@ def test_data_parallel_training_equals_single_process_on_the_global_batch():
     run_ranks(2, cases.dp_training_matches_single_process, timeout_s=120)
 
 
+def test_every_momentum_rule_under_every_sync_order_matches_a_numpy_restatement():
+    run_ranks(2, cases.rules_times_orders, timeout_s=240)
+
+
 def test_plan_buckets_covers_every_parameter_once_in_backward_order():
     """Bucket plan of the overlapped exchanges: ranges follow the order backward completes them, cover every
     parameter segment exactly once and respect the size bounds."""
