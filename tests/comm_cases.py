@@ -206,10 +206,17 @@ def rules_times_orders(rank, world):
                 _rule_and_order(rank, world, int(mode), order.value)
             except AssertionError as e:
                 failures.append(str(e))
+    # exchanges every second iteration, and two batches per iteration (gradient accumulation), under every order
+    for order in SyncOrder:
+        for interval, accum in ((2, 1), (1, 2), (3, 2)):
+            try:
+                _rule_and_order(rank, world, int(Momentum.UPDATE_NESTEROV), order.value, interval, accum)
+            except AssertionError as e:
+                failures.append(str(e))
     assert not failures, "\n".join(failures)
 
 
-def _rule_and_order(rank, world, mode_value, order_value):
+def _rule_and_order(rank, world, mode_value, order_value, interval=1, accum=1):
     """Two data-parallel ranks under one (momentum rule, synchronisation order) pair against a NumPy restatement of
     that pair which simulates both ranks in one process (gradients from single-process networks, the update rules and
     the averaging written out with NumPy)."""
@@ -221,24 +228,25 @@ def _rule_and_order(rank, world, mode_value, order_value):
     from rembrandt_b200.optim.sgd import Momentum, SgdOptConfig, StepSizeSchedule, SyncOrder
 
     mode, order = Momentum(mode_value), SyncOrder(order_value)
-    lr, mu, l2, per, steps = 0.05, 0.9, 1e-3, 8, 4
+    lr, mu, l2, per, steps = 0.05, 0.9, 1e-3, 8, 4 * accum
     mu_eff = 0.0 if mode == Momentum.ZERO else mu
+    mb = per * accum
 
     def batch(r, s):
         g = torch.Generator().manual_seed(1000 * s + r)
         return (torch.randint(0, 256, (per, 1, 28, 28), dtype=torch.uint8, generator=g),
                 torch.randint(0, 10, (per,), dtype=torch.int32, generator=g))
 
-    opt = SgdOptConfig(minibatch_size=per, step_size=StepSizeSchedule.constant(lr), momentum=mode, mu=mu,
-                       l2_reg_coef=l2, sync_order=order)
-    net = Net(zoo.mnist_fc2(), per, device="cpu", seed=(3, 7), minibatch_size=per)
+    opt = SgdOptConfig(minibatch_size=mb, step_size=StepSizeSchedule.constant(lr), momentum=mode, mu=mu,
+                       l2_reg_coef=l2, sync_order=order, comm_interval=interval)
+    net = Net(zoo.mnist_fc2(), per, device="cpu", seed=(3, 7), minibatch_size=mb)
     eng = StepEngine(net, opt, C.AllreduceComm())
     for s in range(steps):
         eng.feed(*batch(rank, s))
         eng.step()
 
     # ---- the restatement: both ranks, NumPy state
-    sims = [Net(zoo.mnist_fc2(), per, device="cpu", seed=(3, 7), minibatch_size=per) for _ in range(world)]
+    sims = [Net(zoo.mnist_fc2(), per, device="cpu", seed=(3, 7), minibatch_size=mb) for _ in range(world)]
     d = sims[0].decay_len
     w = [n.params.detach().numpy().astype(np.float64).copy() for n in sims]
     v = [np.zeros_like(w[0]) for _ in sims]
@@ -285,8 +293,15 @@ def _rule_and_order(rank, world, mode_value, order_value):
             n.backward()
             n.read_stats()
             g[r] = g[r] + n.grads.detach().numpy().astype(np.float64)
+        if (s + 1) % accum:
+            continue                                   # inside a gradient-accumulation group
+        it = (s + 1) // accum - 1                      # iteration counter before this update
+        if it % interval:
+            mean_now = lambda xs: xs                   # no exchange in this iteration
+        else:
+            mean_now = mean
         if order == SyncOrder.SYNC_GRADS_THEN_STEP:
-            g = mean(g)
+            g = mean_now(g)
             for r in range(world):
                 accumulate(r)
                 apply(r)
@@ -294,19 +309,20 @@ def _rule_and_order(rank, world, mode_value, order_value):
             for r in range(world):
                 accumulate(r)
                 apply(r)
-            w = mean(w)
+            w = mean_now(w)
         elif order == SyncOrder.SYNC_PARAMS_THEN_STEP:
             for r in range(world):
                 accumulate(r)
-            w = mean(w)
+            w = mean_now(w)
             for r in range(world):
                 apply(r)
         else:
-            w = mean(w)
-            g = mean(g)
+            w = mean_now(w)
+            g = mean_now(g)
             for r in range(world):
                 accumulate(r)
                 apply(r)
     got = net.params.detach().numpy().astype(np.float64)
     err = np.abs(got - w[rank]).max()
-    assert err < 5e-5, f"{mode.name} x {order.name}: rank {rank} differs from the restatement by {err:.3g}"
+    assert err < 5e-5, (f"{mode.name} x {order.name} (interval {interval}, {accum} batches per iteration): rank {rank} "
+                        f"differs from the restatement by {err:.3g}")
