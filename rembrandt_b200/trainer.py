@@ -174,7 +174,8 @@ class SgdOpt:
         eng.iter = init_t
         if cfg.momentum == Momentum.UPDATE_NESTEROV:
             eng.stepper.nesterov_lookahead(+1.0)
-        comm.first_one_way_sync(net.params)
+        with torch.no_grad():
+            comm.first_one_way_sync(net.params)
         net.refresh_shadow()
         comm.signal_barrier()
         while not comm.wait_barrier():
@@ -261,6 +262,7 @@ class SgdOpt:
         eng.synchronize()
         return self.history
 
+    @torch.no_grad()   # on CPU the flat parameter vector is an autograd leaf; the averaging mixes it in place
     def _checkpoint_window(self, t, valid_data, t_start):
         cfg, eng, net, comm = self.cfg, self.engine, self.net, self.comm
         eng.flush()

@@ -326,3 +326,74 @@ def _rule_and_order(rank, world, mode_value, order_value, interval=1, accum=1):
     err = np.abs(got - w[rank]).max()
     assert err < 5e-5, (f"{mode.name} x {order.name} (interval {interval}, {accum} batches per iteration): rank {rank} "
                         f"differs from the restatement by {err:.3g}")
+
+
+def gossip_training_loop(rank, world, directory):
+    """The whole training loop on several ranks with pair gossip: checkpoint windows (exact averaging, rank-0
+    parameter blob, per-rank state), validation statistics summed over ranks, both checkpoint behaviours, resume."""
+    import os
+
+    from rembrandt_b200.data import BatchIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource, partition_shard
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.sgd import CheckpointBehavior, Momentum, SgdOptConfig, StepSizeSchedule, SyncOrder
+    from rembrandt_b200.trainer import SgdOpt
+
+    src = SyntheticDataSource(384, (28, 28, 1), 10, seed=1, separable=True)
+    valid_src = SyntheticDataSource(96, (28, 28, 1), 10, seed=2, separable=True)
+
+    def run(behavior, sub, iters, resume=False):
+        d = os.path.join(directory, sub)
+        comm = C.PairGossipComm(seed=(17, 29))
+        seed = comm.broadcast_seed((rank + 40, 5))
+        opt = SgdOptConfig(minibatch_size=16, step_size=StepSizeSchedule.constant(0.05), momentum=Momentum.UPDATE,
+                           mu=0.9, l2_reg_coef=1e-4, sync_order=SyncOrder.STEP_THEN_SYNC_PARAMS, checkpoint=behavior,
+                           display_iters=4, checkpoint_iters=4, save_iters=4, valid_iters=2, checkpoint_dir=d)
+        net = Net(zoo.mnist_fc1(), 16, device="cpu", seed=seed, minibatch_size=16)
+        sgd = SgdOpt(opt, StepEngine(net, opt, comm), quiet=True)
+        train = BatchIter(RandomSampleDataIter(partition_shard(src, rank, world), seed=(9 + rank, 9)), 16, src.dims)
+        valid = BatchIter(CyclicSampleDataIter(partition_shard(valid_src, rank, world)), 16, valid_src.dims)
+
+        def forever():
+            while True:
+                for b in train:
+                    yield b
+        sgd.train(forever(), valid, max_iters=iters)
+        sgd.trace.close()
+        return sgd, net, d
+
+    def gathered(t):
+        out = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(out, t)
+        return out
+
+    # KEEP: after the checkpoint window at the last iteration every rank holds the exact average, which is the blob
+    sgd, net, d = run(CheckpointBehavior.KEEP, "keep", 8)
+    everyone = gathered(net.params.detach())
+    assert all(torch.equal(everyone[0], e) for e in everyone[1:]), "KEEP: replicas must equal the averaged model"
+    dist.barrier()
+    assert net.encode_params() == open(os.path.join(d, "params.t_8.blob"), "rb").read()
+    assert open(os.path.join(d, "checkpoint")).read() == "8\n"
+    assert all(os.path.exists(os.path.join(d, f"state.latest.blob.{r}")) for r in range(world))
+    # validation statistics are summed over ranks: every rank reports the same numbers, over all shards
+    vh = torch.tensor([list(v) for v in sgd.valid_history], dtype=torch.float64)
+    assert vh.shape == (2, 3) and all(torch.equal(vh, o) for o in gathered(vh))
+    # the progress line statistics agree too
+    hist = torch.tensor([list(h) for h in sgd.history], dtype=torch.float64)
+    assert all(torch.equal(hist, o) for o in gathered(hist))
+
+    # DISCARD: the averaged model is written and validated, but every rank continues from its own parameters
+    sgd2, net2, d2 = run(CheckpointBehavior.DISCARD, "discard", 8)
+    mine = gathered(net2.params.detach())
+    assert not torch.equal(mine[0], mine[1]), "DISCARD: replicas keep their own parameters"
+    mean = sum(mine) / world
+    blob_net = Net(zoo.mnist_fc1(), 16, device="cpu", seed=(1, 1), minibatch_size=16)
+    blob_net.decode_params(open(os.path.join(d2, "params.t_8.blob"), "rb").read())
+    assert torch.allclose(blob_net.params.detach(), mean, atol=1e-6), "the blob is the exact mean of the replicas"
+
+    # resume: a second run in the same directory starts at iteration 8 from this rank's own state
+    sgd3, net3, _ = run(CheckpointBehavior.DISCARD, "discard", 12, resume=True)
+    assert sgd3.engine.iter == 12
+    steps = [r for r in open(os.path.join(d2, f"trace_sgd.{rank}.log.1")).read().splitlines() if ",step," in r]
+    assert [int(r.split(",")[0]) for r in steps] == [9, 10, 11, 12]

@@ -67,6 +67,10 @@ def test_every_momentum_rule_under_every_sync_order_matches_a_numpy_restatement(
     run_ranks(2, cases.rules_times_orders, timeout_s=240)
 
 
+def test_gossip_training_loop_checkpoints_validates_and_resumes_on_three_ranks(tmp_path):
+    run_ranks(3, cases.gossip_training_loop, str(tmp_path), timeout_s=240)
+
+
 def test_plan_buckets_covers_every_parameter_once_in_backward_order():
     """Bucket plan of the overlapped exchanges: ranges follow the order backward completes them, cover every
     parameter segment exactly once and respect the size bounds."""
