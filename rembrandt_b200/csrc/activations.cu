@@ -10,19 +10,26 @@
 
 namespace rb {
 
-enum { ACT_LOGISTIC = 1, ACT_TANH = 2, ACT_BOUNDED_RECT = 3 };
+// `param` is the upper clip of the bounded rectifier and the input scale beta of the scaled logistic
+// (sigmoid(beta x), src/layer_new.rs:164,1031-1038); the other kinds ignore it. ACT_RECT exists for the places where
+// a ReLU cannot ride in a GEMM epilogue (after a residual sum that is not followed by batch normalisation).
+enum { ACT_LOGISTIC = 1, ACT_TANH = 2, ACT_BOUNDED_RECT = 3, ACT_RECT = 4, ACT_SCALED_LOGISTIC = 5 };
 
-__device__ __forceinline__ float act_apply(float x, int kind, float bound) {
+__device__ __forceinline__ float act_apply(float x, int kind, float param) {
   if (kind == ACT_LOGISTIC) return 1.f / (1.f + __expf(-x));
   if (kind == ACT_TANH) return tanhf(x);
-  return fminf(fmaxf(x, 0.f), bound);
+  if (kind == ACT_BOUNDED_RECT) return fminf(fmaxf(x, 0.f), param);
+  if (kind == ACT_RECT) return fmaxf(x, 0.f);
+  return 1.f / (1.f + __expf(-param * x));
 }
 
 // derivative written in terms of the OUTPUT y, so that backward needs no copy of the pre-activation
-__device__ __forceinline__ float act_slope(float y, int kind, float bound) {
+__device__ __forceinline__ float act_slope(float y, int kind, float param) {
   if (kind == ACT_LOGISTIC) return y * (1.f - y);
   if (kind == ACT_TANH) return 1.f - y * y;
-  return (y > 0.f && y < bound) ? 1.f : 0.f;
+  if (kind == ACT_BOUNDED_RECT) return (y > 0.f && y < param) ? 1.f : 0.f;
+  if (kind == ACT_RECT) return y > 0.f ? 1.f : 0.f;
+  return param * y * (1.f - y);
 }
 
 // y = f(y) in place on the live columns
@@ -95,13 +102,13 @@ using namespace rb;
 extern "C" {
 
 int rb_act_fwd(void* y, long long rows, int ld, int n_valid, int kind, float bound, cudaStream_t st) {
-  if (ld % 8 || kind < ACT_LOGISTIC || kind > ACT_BOUNDED_RECT) return -10;
+  if (ld % 8 || kind < ACT_LOGISTIC || kind > ACT_SCALED_LOGISTIC) return -10;
   act_fwd_kernel<<<act_grid(rows * (ld / 8), 256), 256, 0, st>>>((bf16*)y, rows, ld, n_valid, kind, bound);
   return RB_LAUNCH_OK();
 }
 
 int rb_act_bwd(void* d, const void* y, long long rows, int ld, int n_valid, int kind, float bound, cudaStream_t st) {
-  if (ld % 8 || kind < ACT_LOGISTIC || kind > ACT_BOUNDED_RECT) return -10;
+  if (ld % 8 || kind < ACT_LOGISTIC || kind > ACT_SCALED_LOGISTIC) return -10;
   act_bwd_kernel<<<act_grid(rows * (ld / 8), 256), 256, 0, st>>>((bf16*)d, (const bf16*)y, rows, ld, n_valid, kind,
                                                                bound);
   return RB_LAUNCH_OK();

@@ -96,6 +96,88 @@ class CyclicSampleDataIter:
             self.pos = (self.pos + 1) % n
 
 
+# ---- the episode-based iterators of the reference's older data API (src/data_new.rs:97-279) ----------------
+def episode_ranges(source):
+    """[first, end) sample ranges of the episodes of `source`; a source without episodes has one per sample."""
+    if hasattr(source, "episode_ranges"):
+        return [r for r in source.episode_ranges() if r[1] > r[0]]
+    return [(i, i + 1) for i in range(len(source))]
+
+
+SampleIterator = SequentialSampleIter   # every sample once, episode by episode (data_new.rs:122-147)
+
+
+class RandomEpisodeIterator:
+    """len(source) draws per pass: a uniformly random episode, then a uniformly random sample of it
+    (data_new.rs:149-230). Long and short games are therefore equally likely to be visited."""
+
+    def __init__(self, source, seed=(1, 2)):
+        self.source, self.rng = source, XorShift128Plus(*seed)
+        self.episodes = episode_ranges(source)
+
+    def __iter__(self):
+        for _ in range(len(self.source)):
+            lo, hi = self.episodes[self.rng.below(len(self.episodes))]
+            yield self.source[lo + self.rng.below(hi - lo)]
+
+
+class CyclicEpisodeIterator:
+    """Walks the episodes in order, again and again, taking one random sample from each, until len(source)
+    samples have been drawn (data_new.rs:232-279)."""
+
+    def __init__(self, source, seed=(1, 2)):
+        self.source, self.rng = source, XorShift128Plus(*seed)
+        self.episodes = episode_ranges(source)
+
+    def __iter__(self):
+        limit, count = len(self.source), 0
+        while count < limit:
+            for lo, hi in self.episodes:
+                yield self.source[lo + self.rng.below(hi - lo)]
+                count += 1
+                if count >= limit:
+                    return
+
+
+class PartitionDataSource(RangeDataShard):
+    """The part of a source that belongs to worker `rank` of `world` (data_new.rs:480-549). Sources with episodes are
+    cut at episode boundaries, so that no game is split between workers."""
+
+    def __init__(self, rank: int, world: int, source):
+        if hasattr(source, "episode_ranges"):
+            eps = episode_ranges(source)
+            e_lo, e_hi = partition_range(len(eps), world, rank)
+            lo = eps[e_lo][0] if e_lo < e_hi else 0
+            hi = eps[e_hi - 1][1] if e_lo < e_hi else 0
+            self._eps = [(a - lo, b - lo) for a, b in eps[e_lo:e_hi]]
+        else:
+            lo, hi = partition_range(len(source), world, rank)
+            self._eps = None
+        super().__init__(source, lo, hi)
+
+    def episode_ranges(self):
+        return list(self._eps) if self._eps is not None else [(i, i + 1) for i in range(len(self))]
+
+
+class AugmentDataSource:
+    """A source whose samples pass through `augment(image, label) -> (image, label)` on the host
+    (data_new.rs:429-478); episodes are those of the inner source."""
+
+    def __init__(self, augment: Callable, inner):
+        self.augment, self.inner = augment, inner
+        if hasattr(inner, "dims"):
+            self.dims = inner.dims
+        if hasattr(inner, "episode_ranges"):
+            self.episode_ranges = inner.episode_ranges
+
+    def __len__(self):
+        return len(self.inner)
+
+    def __getitem__(self, i):
+        image, label = self.inner[i]
+        return self.augment(image, label)
+
+
 class TransformDataIter:
     def __init__(self, inner: Iterable, transform: Callable):
         self.inner, self.transform = inner, transform

@@ -127,10 +127,17 @@ class EpisodeDataSource:
         self.lookahead = lookahead
         e_lo, e_hi = partition_range(len(self.db.episodes), world, rank)
         self._samples: List[Tuple[int, int]] = []      # (record, end of its episode)
+        self._episodes: List[Tuple[int, int]] = []     # per episode: range of its samples in `_samples`
         for first, end in self.db.episodes[e_lo:e_hi]:
+            start = len(self._samples)
             for r in range(int(first), int(end)):
                 if self._label(r) >= 0:
                     self._samples.append((r, int(end)))
+            self._episodes.append((start, len(self._samples)))
+
+    def episode_ranges(self) -> List[Tuple[int, int]]:
+        """[first, end) sample indices of every episode of this shard (frames without a label are not samples)."""
+        return list(self._episodes)
 
     def _label(self, r: int) -> int:
         return struct.unpack_from("<i", self.db[r])[0]

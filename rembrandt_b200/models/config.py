@@ -17,7 +17,8 @@ class Act(enum.Enum):
     RECT = "rect"
     LOGISTIC = "logistic"   # gen-3 of the reference declares these two without implementing them; gen-1 has them
     TANH = "tanh"
-    BOUNDED_RECT = "bounded_rect"   # min(max(x, 0), ACT_BOUND): the gen-1 clipped ReLU (src/layer.rs:55)
+    BOUNDED_RECT = "bounded_rect"   # min(max(x, 0), bound): the gen-1 clipped ReLU (src/layer.rs:55)
+    SCALED_LOGISTIC = "scaled_logistic"   # sigmoid(beta x): gen-2 ScaledSigmoid{beta} (src/layer_new.rs:164)
 
     @staticmethod
     def parse(s: str) -> "Act":
@@ -32,12 +33,16 @@ class Act(enum.Enum):
             return Act.TANH
         if s in ("bounded_rect", "boundedrect"):
             return Act.BOUNDED_RECT
+        if s in ("scaled_sigmoid", "scaled_logistic"):
+            return Act.SCALED_LOGISTIC
         raise ValueError(f"unknown activation {s!r}")
 
 
-# Upper clip of Act.BOUNDED_RECT. The reference's kernel takes no bound argument and its source is not in the tree,
-# so the value is this framework's choice.
+# Default upper clip of Act.BOUNDED_RECT (the reference's kernel takes no bound argument and its source is not in
+# the tree, so the value is this framework's choice) and default beta of Act.SCALED_LOGISTIC. An operator
+# configuration's `act_param` overrides them.
 ACT_BOUND = 6.0
+ACT_BETA = 1.0
 
 
 class OpPhase(enum.Enum):
@@ -144,6 +149,18 @@ class Conv2dCfg:
     init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
     bias: bool = True
     backend: ConvBackend = ConvBackend.TENSOR_CORE
+    act_param: Optional[float] = None
+
+
+@dataclass
+class ResConv2dCfg:
+    """Residual convolution without normalisation: out = act(conv(x) + b + x), stride 1, "same" padding, as many output
+    as input channels (ResidualConv2dLayer of the second layer generation, src/layer_new.rs:1179-1418)."""
+    conv_size: int = 3
+    act: Act = Act.RECT
+    init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.kaiming())
+    bias: bool = True
+    act_param: Optional[float] = None
 
 
 @dataclass
@@ -152,6 +169,7 @@ class AffineCfg:
     act: Act = Act.IDENTITY
     init_weights: ParamsInit = field(default_factory=lambda: ParamsInit.xavier())
     bias: bool = True
+    act_param: Optional[float] = None
 
 
 @dataclass
@@ -294,6 +312,10 @@ class SequentialOperatorConfig:
 
     def conv2d(self, cfg: Conv2dCfg, name=None):
         self.hidden_ops.append(NamedOp(self._name(name, "conv"), cfg))
+        return self
+
+    def res_conv2d(self, cfg: ResConv2dCfg, name=None):
+        self.hidden_ops.append(NamedOp(self._name(name, "resconv"), cfg))
         return self
 
     def bnorm_conv2d(self, cfg: BNormConv2dCfg, name=None):

@@ -33,6 +33,7 @@ def _op_table():
     return {
         C.Data3dCfg: O.DataOp,
         C.Conv2dCfg: O.Conv2dOp,
+        C.ResConv2dCfg: O.ResConv2dOp,
         C.AffineCfg: O.AffineOp,
         C.Pool2dCfg: O.Pool2dOp,
         C.LrnCfg: O.LrnOp,

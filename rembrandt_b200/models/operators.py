@@ -10,6 +10,7 @@ reference does this as a separate in-place pass at the start of each backward).
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import List, Optional
 
@@ -57,6 +58,7 @@ class Op:
         self.out_cp = 0
         self.has_relu = False
         self.act_kind = 0
+        self.act_param = 0.0
         self.segs: List[ParamSeg] = []
         self.out = None    # activation buffer (CUDA path)
         self.dout = None   # delta w.r.t. `out`, written by the consumer
@@ -111,10 +113,13 @@ class Op:
         return self.prev.out_cp
 
     # ---- activations other than ReLU (ReLU is fused into the producing kernel's epilogue and the consumer's mask)
-    def _setup_act(self, act):
+    def _setup_act(self, act, param=None):
         self.has_relu = act == C.Act.RECT
         self.act_kind = {C.Act.LOGISTIC: K.ACT_LOGISTIC, C.Act.TANH: K.ACT_TANH,
-                         C.Act.BOUNDED_RECT: K.ACT_BOUNDED_RECT}.get(act, 0)
+                         C.Act.BOUNDED_RECT: K.ACT_BOUNDED_RECT,
+                         C.Act.SCALED_LOGISTIC: K.ACT_SCALED_LOGISTIC}.get(act, 0)
+        default = C.ACT_BETA if act == C.Act.SCALED_LOGISTIC else C.ACT_BOUND
+        self.act_param = float(default if param is None else param)
 
     def _act_rows(self):
         h, w, _ = self.out_hwc
@@ -122,12 +127,13 @@ class Op:
 
     def _act_forward(self):
         if self.act_kind:
-            K.act_fwd(self.out, self._act_rows(), self.out_cp, self.out_hwc[2], self.act_kind, C.ACT_BOUND)
+            K.act_fwd(self.out, self._act_rows(), self.out_cp, self.out_hwc[2], self.act_kind, self.act_param)
 
     def _act_backward(self):
         """Turn the delta w.r.t. the activation into the delta w.r.t. the pre-activation, in place."""
         if self.act_kind:
-            K.act_bwd(self.dout, self.out, self._act_rows(), self.out_cp, self.out_hwc[2], self.act_kind, C.ACT_BOUND)
+            K.act_bwd(self.dout, self.out, self._act_rows(), self.out_cp, self.out_hwc[2], self.act_kind,
+                      self.act_param)
 
     def _ref_act(self, y):
         if self.has_relu:
@@ -137,7 +143,9 @@ class Op:
         if self.act_kind == K.ACT_TANH:
             return torch.tanh(y)
         if self.act_kind == K.ACT_BOUNDED_RECT:
-            return y.clamp(0.0, C.ACT_BOUND)
+            return y.clamp(0.0, self.act_param)
+        if self.act_kind == K.ACT_SCALED_LOGISTIC:
+            return torch.sigmoid(self.act_param * y)
         return y
 
     def mask_src(self):
@@ -564,7 +572,7 @@ class Conv2dOp(Op):
         self.cp = prev.out_cp
         self.out_hwc = (self.P, self.Q, cfg.out_channels)
         self.out_cp = pad_channels(cfg.out_channels)
-        self._setup_act(cfg.act)
+        self._setup_act(cfg.act, getattr(cfg, "act_param", None))
         self.direct = getattr(cfg, "backend", C.ConvBackend.TENSOR_CORE) == C.ConvBackend.DIRECT
         rs = self.r2 * self.r2 if self.s2d else k * k
         self.rs = rs
@@ -691,6 +699,59 @@ class Conv2dOp(Op):
         return self._ref_act(y)
 
 
+class ResConv2dOp(Conv2dOp):
+    """out = act(conv(x) + b + x): a residual convolution without normalisation (ResidualConv2dLayer,
+    src/layer_new.rs:1179-1418). The convolution and its gradients are those of `Conv2dOp`; the identity path is an
+    elementwise add before the activation in forward and an add into the producer's delta in backward."""
+
+    def setup(self, net, prev):
+        rc = self.cfg
+        h, w, c = prev.out_hwc
+        if rc.conv_size % 2 == 0:
+            raise ValueError("a residual convolution needs an odd filter size (same-size output)")
+        self.res_cfg = rc
+        self.cfg = C.Conv2dCfg(rc.conv_size, 1, rc.conv_size // 2, c, C.Act.IDENTITY, rc.init_weights, rc.bias)
+        super().setup(net, prev)
+        if self.s2d or self.out_cp != prev.out_cp:
+            raise ValueError("a residual convolution cannot be the first hidden operator of a strided input")
+        self._setup_act(rc.act, rc.act_param)     # applied after the sum, not in the convolution's epilogue
+
+    @contextlib.contextmanager
+    def _conv_only(self):
+        """While active, the inherited forward / backward see a plain linear convolution."""
+        saved = (self.has_relu, self.act_kind)
+        self.has_relu, self.act_kind = False, 0
+        try:
+            yield
+        finally:
+            self.has_relu, self.act_kind = saved
+
+    def forward(self, train, t):
+        with self._conv_only():
+            super().forward(train, t)
+        K.add_bf16(self.out, self.prev.out, self.out.numel())
+        if self.has_relu:
+            K.act_fwd(self.out, self._act_rows(), self.out_cp, self.out_hwc[2], K.ACT_RECT, 0.0)
+        else:
+            self._act_forward()
+
+    def backward(self):
+        self._act_backward()          # smooth activations; a ReLU was already applied to dout by the consumer
+        with self._conv_only():
+            super().backward()
+        if self.wants_prev_delta():
+            n = self.dout.numel()
+            K.add_bf16(self.prev.dout, self.dout, n)
+            if self.prev.has_relu:    # the identity path passes through the producer's ReLU as well
+                K.relu_mask(self.prev.dout, self.prev.out, n)
+
+    def ref_forward(self, x, train, t):
+        cfg = self.cfg
+        w = self._w_ref(self.view(self.seg_w))
+        b = self.view(self.seg_b) if self.seg_b else None
+        return self._ref_act(F.conv2d(x, w, b, stride=1, padding=cfg.conv_pad) + x)
+
+
 # =============================================================================================== affine
 class AffineOp(Op):
     """Fully connected layer + bias + optional ReLU (src/operator/mod.rs:838-1364).
@@ -716,7 +777,7 @@ class AffineOp(Op):
             self.k_in = h * w * prev.out_cp
         self.out_hwc = (1, 1, cfg.out_channels)
         self.out_cp = pad_channels(cfg.out_channels)
-        self._setup_act(cfg.act)
+        self._setup_act(cfg.act, getattr(cfg, "act_param", None))
         self.seg_w = ParamSeg(self.name + ".w", (cfg.out_channels, self.k_in))
         self.seg_b = ParamSeg(self.name + ".b", (cfg.out_channels,)) if getattr(cfg, "bias", True) else None
         self.segs = [self.seg_w] + ([self.seg_b] if self.seg_b else [])

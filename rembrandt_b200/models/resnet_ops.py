@@ -180,7 +180,7 @@ class BNormConv2dOp(_BlockBase):
         self.segs = list(self.u.segs)
         self.out_hwc = (self.u.P, self.u.Q, cfg.out_channels)
         self.out_cp = self.u.kp
-        self._setup_act(cfg.act)
+        self._setup_act(cfg.act, getattr(cfg, "act_param", None))
 
     def alloc(self):
         super().alloc()

@@ -110,7 +110,7 @@ def relu_mask(d, y, n):
     check(_native.cuda().rb_relu_mask(ptr(d), ptr(y), n, stream_handle()), "rb_relu_mask")
 
 
-ACT_LOGISTIC, ACT_TANH, ACT_BOUNDED_RECT = 1, 2, 3
+ACT_LOGISTIC, ACT_TANH, ACT_BOUNDED_RECT, ACT_RECT, ACT_SCALED_LOGISTIC = 1, 2, 3, 4, 5
 
 
 def act_fwd(y, rows, ld, n_valid, kind, bound=0.0):

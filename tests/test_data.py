@@ -281,3 +281,43 @@ def test_bit_plane_codecs_round_trip():
         codecs.Bits3dCodec().decode(rec[:40])
     with pytest.raises(blob.BlobError):
         codecs.Bits3dCodec().decode(blob.encode_record(planes.reshape(-1), (19, 19, 3), "u8"))   # not a bit record
+
+
+def test_episode_iterators_partition_and_augment(tmp_path):
+    import struct
+    from collections import Counter
+    from rembrandt_b200.data import (AugmentDataSource, CyclicEpisodeIterator, PartitionDataSource,
+                                     RandomEpisodeIterator, SampleIterator, episode_ranges)
+    from rembrandt_b200.data.recorddb import EpisodeDataSource, RecordDbWriter
+    # three games of 6, 2 and 4 labelled positions (labels double as position ids); one unlabelled frame in game 0
+    games = [[0, 1, 2, -1, 3, 4, 5], [10, 11], [20, 21, 22, 23]]
+    with RecordDbWriter(str(tmp_path / "e")) as we:
+        for ep in games:
+            we.append_episode([struct.pack("<i", l) + bytes(9) for l in ep])
+    src = EpisodeDataSource(str(tmp_path / "e"), (3, 3, 1))
+    assert len(src) == 12 and src.episode_ranges() == [(0, 6), (6, 8), (8, 12)]
+    assert [lab for _, lab in SampleIterator(src)] == [0, 1, 2, 3, 4, 5, 10, 11, 20, 21, 22, 23]
+    # random episodes: each game is drawn about equally often although their lengths differ 3 : 1 : 2
+    it = RandomEpisodeIterator(src, seed=(5, 6))
+    draws = [lab // 10 for _ in range(100) for _, lab in it]
+    c = Counter(draws)
+    assert len(draws) == 1200 and all(330 < c[g] < 470 for g in range(3)), c
+    # cyclic: games in order, one position of each, until len(source) positions
+    cyc = [lab // 10 for _, lab in CyclicEpisodeIterator(src, seed=(7, 8))]
+    assert cyc == [0, 1, 2] * 4
+    # a source without episodes: one episode per sample
+    plain = SyntheticDataSource(5, (4, 4, 1), 3, seed=0)
+    assert episode_ranges(plain) == [(i, i + 1) for i in range(5)]
+    assert len(list(RandomEpisodeIterator(plain))) == 5
+    # partitions cut at game boundaries
+    parts = [PartitionDataSource(r, 2, src) for r in range(2)]
+    assert [len(p) for p in parts] == [8, 4] or [len(p) for p in parts] == [6, 6]
+    assert sorted(lab for p in parts for _, lab in SampleIterator(p)) == sorted(l for g in games for l in g if l >= 0)
+    for p in parts:
+        for lo, hi in p.episode_ranges():
+            assert len({p[i][1] // 10 for i in range(lo, hi)}) == 1     # an episode holds one game
+    assert [len(PartitionDataSource(r, 2, plain)) for r in range(2)] == [3, 2]
+    # host-side augmentation keeps the episode structure
+    aug = AugmentDataSource(lambda im, lab: (im + 1, lab), src)
+    assert len(aug) == 12 and aug.episode_ranges() == src.episode_ranges()
+    assert int(aug[0][0].max()) == 1 and aug[3][1] == 3

@@ -327,3 +327,34 @@ def test_loss_head_dense_row_of_a_spatial_producer():
     op.prev = types.SimpleNamespace(out=out[:, :1, :1], dout=None, out_hwc=(1, 1, 10), out_cp=cp)
     op._setup_flat()
     assert not op.spatial and op.ld == cp and op._logits()[0] is op.prev.out
+
+
+def test_residual_convolution_and_scaled_logistic_reference_path():
+    from rembrandt_b200.models.config import ResConv2dCfg
+    cfg = (SequentialOperatorConfig().data3d(Data3dCfg((8, 8, 3), normalize=True))
+           .conv2d(Conv2dCfg(3, 1, 1, 6, Act.RECT, ParamsInit.kaiming()), "stem")
+           .res_conv2d(ResConv2dCfg(3, Act.RECT), "res1")
+           .res_conv2d(ResConv2dCfg(5, Act.SCALED_LOGISTIC, act_param=2.0), "res2")
+           .pool2d(Pool2dCfg(8, 1, 0, PoolKind.AVERAGE), "gap")
+           .affine(AffineCfg(4, Act.IDENTITY, ParamsInit.xavier()), "fc")
+           .softmax_kl_loss(SoftmaxKLLossCfg(4)))
+    net = Net(cfg, 2, device="cpu", seed=(1, 2))
+    stem, res1, res2 = net.hidden_ops[:3]
+    assert res1.out_hwc == (8, 8, 6) and res2.cfg.conv_pad == 2
+    recs, _ = blob.decode_records(net.encode_params())
+    assert [r[1] for r in recs[:6]] == [(27, 6), (1, 6), (54, 6), (1, 6), (150, 6), (1, 6)]
+    x = torch.rand(2, 3, 8, 8)
+    a = stem.ref_forward(x, False, 0)
+    w1 = torch.from_numpy(recs[2][0]).reshape(6, 6, 3, 3)
+    b = res1.ref_forward(a, False, 0)
+    assert torch.allclose(b, torch.relu(F.conv2d(a, w1, None, padding=1) + a), atol=1e-5)
+    w2 = torch.from_numpy(recs[4][0]).reshape(6, 6, 5, 5)
+    c = res2.ref_forward(b, False, 0)
+    assert torch.allclose(c, torch.sigmoid(2.0 * (F.conv2d(b, w2, None, padding=2) + b)), atol=1e-5)
+    net.load_batch((x * 255).to(torch.uint8), torch.tensor([1, 3]))
+    net.forward(True)
+    net.backward()
+    assert float(net.grads.abs().sum()) > 0
+    with pytest.raises(ValueError):
+        Net(SequentialOperatorConfig().data3d(Data3dCfg((8, 8, 3))).res_conv2d(ResConv2dCfg(4), "bad")
+            .softmax_kl_loss(SoftmaxKLLossCfg(4)), 2, device="cpu")

@@ -17,7 +17,8 @@ from rembrandt_b200.models.net import Net
 from rembrandt_b200.ops import native_ops as K
 
 KINDS = [(K.ACT_LOGISTIC, torch.sigmoid), (K.ACT_TANH, torch.tanh),
-         (K.ACT_BOUNDED_RECT, lambda x: x.clamp(0.0, 1.5))]
+         (K.ACT_BOUNDED_RECT, lambda x: x.clamp(0.0, 1.5)), (K.ACT_RECT, torch.relu),
+         (K.ACT_SCALED_LOGISTIC, lambda x: torch.sigmoid(1.5 * x))]
 
 
 @pytest.mark.parametrize("kind,fn", KINDS)
@@ -40,7 +41,8 @@ def test_activation_forward_and_backward(kind, fn, rows, ld, n_valid):
     # the slope is evaluated at the bf16-rounded output, as the kernel sees it
     yo = got
     slope = {K.ACT_LOGISTIC: yo * (1 - yo), K.ACT_TANH: 1 - yo * yo,
-             K.ACT_BOUNDED_RECT: ((yo > 0) & (yo < 1.5)).float()}[kind]
+             K.ACT_BOUNDED_RECT: ((yo > 0) & (yo < 1.5)).float(), K.ACT_RECT: (yo > 0).float(),
+             K.ACT_SCALED_LOGISTIC: 1.5 * yo * (1 - yo)}[kind]
     want = d.float() * slope
     gd = dd.float().cpu()
     assert torch.all(gd[:, n_valid:] == 0)
@@ -91,8 +93,19 @@ def _direct_cfg():
             .softmax_kl_loss(SoftmaxKLLossCfg(10)))
 
 
-@pytest.mark.parametrize("_cfg", [_cfg, _mimic_cfg, _direct_cfg],
-                         ids=["smooth_activations", "low_rank_affine", "direct_conv_backend"])
+def _res_cfg():
+    k = ParamsInit.kaiming()
+    return (SequentialOperatorConfig().data3d(Data3dCfg((12, 12, 3), normalize=True))
+            .conv2d(Conv2dCfg(3, 1, 1, 32, Act.RECT, k), "stem")
+            .res_conv2d(C.ResConv2dCfg(3, Act.RECT), "res1")
+            .res_conv2d(C.ResConv2dCfg(3, Act.SCALED_LOGISTIC, act_param=2.0), "res2")
+            .pool2d(Pool2dCfg(12, 1, 0, PoolKind.AVERAGE), "gap")
+            .affine(AffineCfg(10, Act.IDENTITY, ParamsInit.xavier()), "fc")
+            .softmax_kl_loss(SoftmaxKLLossCfg(10)))
+
+
+@pytest.mark.parametrize("_cfg", [_cfg, _mimic_cfg, _direct_cfg, _res_cfg],
+                         ids=["smooth_activations", "low_rank_affine", "direct_conv_backend", "residual_convolution"])
 def test_network_matches_reference_path(_cfg):
     batch = 8
     g = Net(_cfg(), batch, device="cuda", seed=(3, 4))
