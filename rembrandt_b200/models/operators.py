@@ -892,6 +892,8 @@ class Pool2dOp(Op):
         self.out_hwc = (self.P, self.Q, c)
         self.out_cp = prev.out_cp
         self.is_max = cfg.kind == C.PoolKind.MAX
+        if cfg.act not in (C.Act.RECT, C.Act.IDENTITY):
+            raise ValueError(f"{self.name}: a pooling operator takes a rect activation or none, not {cfg.act.value}")
         self.fused_relu = cfg.act == C.Act.RECT
         # the output is non-negative if this op or its producer applied a ReLU; consumers then mask by it
         self.has_relu = self.fused_relu

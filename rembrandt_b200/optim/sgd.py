@@ -109,6 +109,21 @@ class StepSizeSchedule:
     def inv(step0, tau):
         return StepSizeSchedule("inv", step0, tau=tau)
 
+    # the second generation's names (src/opt_new.rs:52-106): all piecewise-constant or geometric forms of the above
+    @staticmethod
+    def fixed(lr):
+        return StepSizeSchedule.constant(lr)
+
+    @staticmethod
+    def step_once(lr0, lr0_iters, lr_final):
+        return StepSizeSchedule.anneal1(lr0, lr0_iters, lr_final)
+
+    decay_once = step_once
+
+    @staticmethod
+    def step_twice(lr0, lr0_iters, lr1, lr1_iters, lr_final):
+        return StepSizeSchedule.anneal2(lr0, lr0_iters, lr1, lr1_iters, lr_final)
+
     @staticmethod
     def from_annealing_policy(step0: float, policy: Optional[dict]):
         """`annealing_policy` table of a .model file's [opt] section."""

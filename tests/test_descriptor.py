@@ -137,3 +137,21 @@ def test_example_descriptors_shipped_with_this_framework_build_and_step():
     net.forward(True)
     net.backward()
     assert float(net.grads.abs().sum()) > 0
+
+
+def test_sigmoid_and_tanh_layers_of_a_descriptor_build_and_step():
+    text = LENET_MODEL.replace('act_func = "rect"', 'act_func = "sigmoid"', 1).replace('act_func = "relu"', 'act_func = "tanh"', 1)
+    assert text != LENET_MODEL
+    d = descriptor.parse_model(text)
+    acts = [getattr(o.cfg, "act", None) for o in d.config.hidden_ops]
+    assert C.Act.LOGISTIC in acts
+    net = Net(d.config, 2, device="cpu")
+    import torch
+    net.load_batch(torch.randint(0, 256, (2, 1, 28, 28), dtype=torch.uint8), torch.tensor([1, 2]))
+    net.forward(True)
+    net.backward()
+    assert float(net.grads.abs().sum()) > 0
+    with pytest.raises(ValueError):
+        Net(C.SequentialOperatorConfig().data3d(C.Data3dCfg((8, 8, 1)))
+            .pool2d(C.Pool2dCfg(2, 2, 0, C.PoolKind.MAX, act=C.Act.TANH), "p").softmax_kl_loss(C.SoftmaxKLLossCfg(16)),
+            2, device="cpu")

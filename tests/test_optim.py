@@ -74,6 +74,14 @@ def test_split_phases_equal_the_fused_step(mode):
     assert torch.allclose(w1, w2) and torch.allclose(v1, v2) and float(g2.abs().max()) == 0.0
 
 
+def test_second_generation_schedule_names():
+    s = StepSizeSchedule.step_twice(0.1, 10, 0.01, 20, 0.001)
+    assert [s.at_iter(t) for t in (0, 9, 10, 19, 20, 99)] == [0.1, 0.1, 0.01, 0.01, 0.001, 0.001]
+    assert StepSizeSchedule.decay_once(0.5, 3, 0.05).at_iter(3) == 0.05 and StepSizeSchedule.fixed(0.2).at_iter(7) == 0.2
+    d = StepSizeSchedule.decay(1.0, 0.5, 4)
+    assert [d.at_iter(t) for t in (0, 3, 4, 8)] == [1.0, 1.0, 0.5, 0.25]
+
+
 def test_schedules():
     assert StepSizeSchedule.constant(0.3).at_iter(10**6) == 0.3
     a2 = StepSizeSchedule.anneal2(0.1, 18750, 0.01, 37500, 0.001)
