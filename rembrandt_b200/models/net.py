@@ -51,6 +51,10 @@ def _op_table():
 
 
 class Net:
+    # Tests set this to run the device code path (padded bf16 buffers, kernel fronts) on CPU tensors, with the kernel
+    # fronts replaced by plain-torch stand-ins; it has no other use.
+    device_path_on_cpu = False
+
     def __init__(self, cfg: C.SequentialOperatorConfig, batch_size: int, device="cuda", seed=(0x5EED, 0xC0FFEE),
                  minibatch_size: Optional[int] = None, training: bool = True,
                  flat_allocator: Optional[Callable[[str, int, torch.dtype], torch.Tensor]] = None):
@@ -58,7 +62,7 @@ class Net:
         self.cfg = cfg
         self.batch = int(batch_size)
         self.device = torch.device(device)
-        self.is_cuda = self.device.type == "cuda"
+        self.is_cuda = self.device.type == "cuda" or self.device_path_on_cpu
         self.training_capable = training
         self.minibatch_size = int(minibatch_size or batch_size)
         self.sample_weight = 1.0 / self.minibatch_size

@@ -243,7 +243,7 @@ def resnet20_cifar(num_classes=10, mean=None, augment=True):
 def go_policy_net(planes=32, channels=128, layers=6, num_classes=361):
     """Convolutional move-prediction network on 19x19 bit-plane inputs (tools/train-gogod.rs:56-227)."""
     k = ParamsInit.kaiming()
-    cfg = SequentialOperatorConfig().data3d(Data3dCfg((19, 19, planes)))
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((19, 19, planes), normalize=True))   # planes hold 0 / 255
     cfg.conv2d(Conv2dCfg(5, 1, 2, channels, Act.RECT, k), "conv1")
     for i in range(2, layers):
         cfg.conv2d(Conv2dCfg(3, 1, 1, channels, Act.RECT, k), f"conv{i}")

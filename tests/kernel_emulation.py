@@ -1,0 +1,283 @@
+"""Plain-torch stand-ins for the CUDA kernel fronts of `rembrandt_b200.ops.native_ops`, for CPU tests.
+
+With these patched in and `Net.device_path_on_cpu` set, a network runs its *device* code path -- padded NHWC bf16
+buffers, flat parameter vectors, masks handed from consumer to producer, the launch sequence of every operator -- on
+CPU tensors. Each stand-in restates the contract of one kernel front (what it reads, what it writes, which columns
+are live) with torch operators; none of them is derived from a kernel's code. The kernels themselves are compared
+with fp32 torch on a GPU; what this layer checks is everything between the operators and the kernels.
+
+Covered: convolution (tensor-core fronts and the direct fronts), GEMM, bias / activation epilogues, column sums,
+filter repacking, pooling, softmax cross-entropy (one head, hard labels), pointwise losses, elementwise helpers, the
+input kernel without augmentation, the fused SGD step. Anything else raises, so a test cannot pass by accident.
+"""
+import torch
+import torch.nn.functional as F
+
+from rembrandt_b200.ops import native_ops as K
+from rembrandt_b200.optim.sgd import reference_step
+
+
+def _rows(buf, rows, ld):
+    """View the first rows * ld elements of any buffer as a [rows, ld] matrix."""
+    return buf.reshape(-1)[: rows * ld].view(rows, ld)
+
+
+def _finish(out, y, rows, ldy, bias, relu, mask_src, n_valid, n_store):
+    """Shared epilogue: out is fp32 [rows, n]; writes bf16 y[:, :n_store] with bias / ReLU / mask, dead columns 0."""
+    n = out.shape[1]
+    n_valid = n_valid or n
+    n_store = n_store or n
+    res = torch.zeros(rows, n_store)
+    live = min(n, n_valid, n_store)
+    res[:, :live] = out[:, :live]
+    if bias is not None:
+        res[:, :live] += bias.float()[:live]
+    if relu:
+        res.clamp_(min=0)
+    if mask_src is not None:
+        res *= (_rows(mask_src, rows, ldy)[:, :n_store].float() > 0)
+    _rows(y, rows, ldy)[:, :n_store] = res.to(y.dtype)
+
+
+def conv_fprop_tc(x, N, H, W, Cp, w, Kout, R, S, stride, pad_h, pad_w, P, Q, y, ldy, bias=None, relu=False,
+                  mask_src=None, n_valid=0, n_store=0):
+    xi = x.reshape(-1)[: N * H * W * Cp].view(N, H, W, Cp).float().permute(0, 3, 1, 2)
+    wi = w.reshape(-1)[: Kout * R * S * Cp].view(Kout, R, S, Cp).float().permute(0, 3, 1, 2)
+    need_h, need_w = (P - 1) * stride + R, (Q - 1) * stride + S
+    xi = F.pad(xi, (pad_w, max(0, need_w - pad_w - W), pad_h, max(0, need_h - pad_h - H)))[:, :, :need_h, :need_w]
+    out = F.conv2d(xi, wi, stride=stride).permute(0, 2, 3, 1).reshape(N * P * Q, Kout)
+    _finish(out, y, N * P * Q, ldy, bias, relu, mask_src, n_valid, n_store)
+
+
+def conv_wgrad_tc(x, N, H, W, Cp, dy, lddy, Kout, R, S, stride, pad_h, pad_w, P, Q, dw, split_k=0):
+    xi = x.reshape(-1)[: N * H * W * Cp].view(N, H, W, Cp).float().permute(0, 3, 1, 2)
+    need_h, need_w = (P - 1) * stride + R, (Q - 1) * stride + S
+    xi = F.pad(xi, (pad_w, max(0, need_w - pad_w - W), pad_h, max(0, need_h - pad_h - H)))[:, :, :need_h, :need_w]
+    g = _rows(dy, N * P * Q, lddy)[:, :Kout].float().view(N, P, Q, Kout).permute(0, 3, 1, 2)
+    wz = torch.zeros(Kout, Cp, R, S, requires_grad=True)
+    (F.conv2d(xi, wz, stride=stride) * g).sum().backward()
+    dw.reshape(-1)[: Kout * R * S * Cp].view(Kout, R * S, Cp).add_(wz.grad.permute(0, 2, 3, 1).reshape(Kout, R * S, Cp))
+
+
+def conv_direct_fwd(x, w, bias, y, N, H, W, Cp, Kout, Kp, R, S, stride, pad_h, pad_w, P, Q, relu):
+    conv_fprop_tc(x, N, H, W, Cp, w, Kout, R, S, stride, pad_h, pad_w, P, Q, y, Kp, bias, relu, None, Kout, Kp)
+
+
+def conv_direct_wgrad(x, dy, dw, N, H, W, Cp, Kout, Kp, R, S, stride, pad_h, pad_w, P, Q):
+    conv_wgrad_tc(x, N, H, W, Cp, dy, Kp, Kout, R, S, stride, pad_h, pad_w, P, Q, dw)
+
+
+def conv_direct_dgrad(dy, w, dx, mask_src, N, H, W, Cp, Kout, Kp, R, S, stride, pad_h, pad_w, P, Q):
+    wi = w.reshape(-1)[: Kout * R * S * Cp].view(Kout, R, S, Cp).float().permute(0, 3, 1, 2)
+    g = _rows(dy, N * P * Q, Kp)[:, :Kout].float().view(N, P, Q, Kout).permute(0, 3, 1, 2)
+    need_h, need_w = (P - 1) * stride + R, (Q - 1) * stride + S
+    full = F.conv_transpose2d(g, wi, stride=stride)                      # [N, Cp, need_h, need_w] on the padded grid
+    grid = torch.zeros(N, Cp, max(need_h, pad_h + H), max(need_w, pad_w + W))
+    grid[:, :, :need_h, :need_w] = full
+    res = grid[:, :, pad_h: pad_h + H, pad_w: pad_w + W].permute(0, 2, 3, 1)
+    if mask_src is not None:
+        res = res * (mask_src.reshape(-1)[: N * H * W * Cp].view(N, H, W, Cp).float() > 0)
+    dx.reshape(-1)[: N * H * W * Cp].view(N, H, W, Cp).copy_(res.to(dx.dtype))
+
+
+def pack_dgrad_filters(w16, wt16, Kout, Kp, RS, Cp):
+    w = w16.reshape(-1)[: Kout * RS * Cp].view(Kout, RS, Cp)
+    out = torch.zeros(Cp, RS, Kp, dtype=wt16.dtype)
+    out[:, :, :Kout] = w.flip(1).permute(2, 1, 0)
+    wt16.reshape(-1)[: Cp * RS * Kp].view(Cp, RS, Kp).copy_(out)
+
+
+def zero_s2d_structural(dw, Kout, R2, Cp, f, cin, ksize):
+    raise NotImplementedError("space-to-depth first layers are not emulated: use a stride-1 first convolution")
+
+
+def gemm_tc(a, a_mn, lda, b, b_mn, ldb, M, N, K_, d, ldd, epi=K.EPI_BF16, bias=None, relu=False, mask_src=None,
+            n_valid=0, n_store=0, split_k=0, bn_cap=0):
+    A = _rows(a, K_, lda)[:, :M].float().t() if a_mn else _rows(a, M, lda)[:, :K_].float()
+    B = _rows(b, K_, ldb)[:, :N].float() if b_mn else _rows(b, N, ldb)[:, :K_].float().t()
+    out = A @ B
+    if epi == K.EPI_BF16:
+        _finish(out, d, M, ldd, bias, relu, mask_src, n_valid, n_store)
+        return
+    dst = _rows(d, M, ldd)
+    if epi == K.EPI_F32_STORE:
+        dst[:, : (n_store or N)] = 0
+        dst[:, :N] = out
+    else:
+        dst[:, :N] += out
+
+
+def bias_act(acc, rows, ld, n_valid, bias, relu, y, mask_src=None, rezero=True):
+    _finish(_rows(acc, rows, ld).clone(), y, rows, ld, bias, relu, mask_src, n_valid, ld)
+    if rezero:
+        _rows(acc, rows, ld).zero_()
+
+
+def colsum(x, rows, ld, cols, out):
+    out.reshape(-1)[:cols].add_(_rows(x, rows, ld)[:, :cols].float().sum(0))
+
+
+def relu_mask(d, y, n):
+    flat = d.reshape(-1)[:n]
+    flat.mul_((y.reshape(-1)[:n].float() > 0).to(d.dtype))
+
+
+def add_bf16(a, b, n):
+    flat = a.reshape(-1)[:n]
+    flat.copy_((flat.float() + b.reshape(-1)[:n].float()).to(a.dtype))
+
+
+def f32_to_bf16(x, y, n):
+    y.reshape(-1)[:n].copy_(x.reshape(-1)[:n])
+
+
+_ACT = {
+    K.ACT_LOGISTIC: (torch.sigmoid, lambda y, p: y * (1 - y)),
+    K.ACT_TANH: (torch.tanh, lambda y, p: 1 - y * y),
+    K.ACT_RECT: (torch.relu, lambda y, p: (y > 0).float()),
+}
+
+
+def act_fwd(y, rows, ld, n_valid, kind, bound=0.0):
+    m = _rows(y, rows, ld)
+    v = m[:, :n_valid].float()
+    if kind == K.ACT_BOUNDED_RECT:
+        v = v.clamp(0.0, bound)
+    elif kind == K.ACT_SCALED_LOGISTIC:
+        v = torch.sigmoid(bound * v)
+    else:
+        v = _ACT[kind][0](v)
+    m[:, :n_valid] = v.to(y.dtype)
+    m[:, n_valid:] = 0
+
+
+def act_bwd(d, y, rows, ld, n_valid, kind, bound=0.0):
+    dm, ym = _rows(d, rows, ld), _rows(y, rows, ld)[:, :n_valid].float()
+    if kind == K.ACT_BOUNDED_RECT:
+        slope = ((ym > 0) & (ym < bound)).float()
+    elif kind == K.ACT_SCALED_LOGISTIC:
+        slope = bound * ym * (1 - ym)
+    else:
+        slope = _ACT[kind][1](ym, bound)
+    dm[:, :n_valid] = (dm[:, :n_valid].float() * slope).to(d.dtype)
+    dm[:, n_valid:] = 0
+
+
+def _windows(x, k, stride, pad, P, Q, fill):
+    """x [N, C, H, W] -> [N, C, P, Q, k*k] windows, out-of-image taps hold `fill`."""
+    N, C, H, W = x.shape
+    need_h, need_w = (P - 1) * stride + k, (Q - 1) * stride + k
+    xp = F.pad(x, (pad, max(0, need_w - pad - W), pad, max(0, need_h - pad - H)), value=fill)[:, :, :need_h, :need_w]
+    return xp.unfold(2, k, stride).unfold(3, k, stride).reshape(N, C, P, Q, k * k)
+
+
+def pool_fwd(x, y, idx, N, H, W, C, P, Q, k, stride, pad, is_max, relu):
+    xi = x.reshape(-1)[: N * H * W * C].view(N, H, W, C).float().permute(0, 3, 1, 2)
+    if is_max:
+        win = _windows(xi, k, stride, pad, P, Q, float("-inf"))
+        best, arg = win.max(dim=4)
+        if idx is not None:
+            idx.reshape(-1)[: N * P * Q * C].view(N, P, Q, C).copy_(arg.permute(0, 2, 3, 1).to(torch.uint8))
+    else:
+        best = _windows(xi, k, stride, pad, P, Q, 0.0).sum(4) / (k * k)
+    if relu:
+        best = best.clamp(min=0)
+    y.reshape(-1)[: N * P * Q * C].view(N, P, Q, C).copy_(best.permute(0, 2, 3, 1).to(y.dtype))
+
+
+def pool_bwd(dy, idx, y_relu, dx, mask_src, N, H, W, C, P, Q, k, stride, pad, is_max):
+    g = dy.reshape(-1)[: N * P * Q * C].view(N, P, Q, C).float()
+    if y_relu is not None:
+        g = g * (y_relu.reshape(-1)[: N * P * Q * C].view(N, P, Q, C).float() > 0)
+    need_h, need_w = (P - 1) * stride + k, (Q - 1) * stride + k
+    grid = torch.zeros(N, max(need_h, pad + H), max(need_w, pad + W), C)
+    arg = idx.reshape(-1)[: N * P * Q * C].view(N, P, Q, C).long() if is_max else None
+    for r in range(k):
+        for s in range(k):
+            part = g * (arg == r * k + s) if is_max else g / (k * k)
+            grid[:, r: r + (P - 1) * stride + 1: stride, s: s + (Q - 1) * stride + 1: stride] += part
+    res = grid[:, pad: pad + H, pad: pad + W]
+    if mask_src is not None:
+        res = res * (mask_src.reshape(-1)[: N * H * W * C].view(N, H, W, C).float() > 0)
+    dx.reshape(-1)[: N * H * W * C].view(N, H, W, C).copy_(res.to(dx.dtype))
+
+
+def softmax_ce(logits, B, Kc, ld, labels, weights, w_scalar, delta, probs=None, loss_sum=None, correct=None,
+               loss_per=None, argmax_out=None, cat_weights=None, mask=None, heads=1, soft=None):
+    if heads != 1 or mask is not None or soft is not None or cat_weights is not None:
+        raise NotImplementedError("only one head with hard labels is emulated")
+    x = _rows(logits, B, ld)[:, :Kc].float()
+    lab = labels.reshape(-1)[:B].long()
+    p = torch.softmax(x, 1)
+    w = weights.reshape(-1)[:B].float() if weights is not None else torch.full((B,), float(w_scalar))
+    nll = -torch.log_softmax(x, 1).gather(1, lab.view(-1, 1)).squeeze(1)
+    am = x.argmax(1)
+    if delta is not None:
+        d = p.clone()
+        d[torch.arange(B), lab] -= 1.0
+        dm = _rows(delta, B, ld)
+        dm[:, :Kc] = (d * w.view(-1, 1)).to(delta.dtype)
+        dm[:, Kc:] = 0
+    if probs is not None:
+        probs.reshape(-1)[: B * Kc].view(B, Kc).copy_(p)
+    if loss_sum is not None:
+        loss_sum += (w * nll).sum()
+    if correct is not None:
+        correct += int((am == lab).sum())
+    if loss_per is not None:
+        loss_per.reshape(-1)[:B].copy_(w * nll)
+    if argmax_out is not None:
+        argmax_out.reshape(-1)[:B].copy_(am.int())
+
+
+def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi_y, lo_x, hi_x, random_crop,
+             random_flip, per_batch, scale, mean_scale, pca_sigma, pca_vals, pca_vecs, seed, step, step_ptr=None):
+    if random_crop or random_flip or pca_sigma:
+        raise NotImplementedError("the emulated input kernel does no augmentation")
+    img = src.reshape(-1)[: N * C * H * W].view(N, C, H, W).float() * scale
+    if mean is not None:
+        img = img - mean_scale * mean.reshape(-1)[: C * H * W].view(1, C, H, W).float()
+    oy, ox = (lo_y + hi_y) // 2, (lo_x + hi_x) // 2          # the centred window
+    canvas = torch.zeros(N, C, crop_h, crop_w)
+    ys, xs = max(0, -oy), max(0, -ox)
+    ye, xe = min(crop_h, H - oy), min(crop_w, W - ox)
+    canvas[:, :, ys:ye, xs:xe] = img[:, :, oy + ys: oy + ye, ox + xs: ox + xe]
+    out = torch.zeros(N, OH, OW, Cp)
+    if f == 1:
+        out[..., :C] = canvas.permute(0, 2, 3, 1)
+    elif OH == 1 and OW == 1:
+        # flat mode: the whole image of one sample in one pixel, channel = (y * f + x) * C + c
+        out[:, 0, 0, : crop_h * crop_w * C] = canvas.permute(0, 2, 3, 1).reshape(N, -1)
+    else:
+        raise NotImplementedError("space-to-depth output is not emulated")
+    dst.reshape(-1)[: N * OH * OW * Cp].view(N, OH, OW, Cp).copy_(out.to(dst.dtype))
+
+
+def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
+    reference_step(w[:n], g[:n], v[:n], lr, mu, l2, grad_scale, mode, phase)
+    if w16 is not None:
+        w16[:n].copy_(w[:n])
+
+
+def _unsupported(name):
+    def fn(*a, **k):
+        raise NotImplementedError(f"kernel front {name} has no CPU stand-in")
+    return fn
+
+
+EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fwd, conv_direct_wgrad,
+                                    conv_direct_dgrad, pack_dgrad_filters, zero_s2d_structural, gemm_tc, bias_act,
+                                    colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
+                                    softmax_ce, input_u8, sgd_fused)}
+
+
+def install(monkeypatch):
+    """Patch every kernel front: the emulated ones with their stand-ins, all others with a function that raises."""
+    import types
+    for name, obj in vars(K).items():
+        if name in EMULATED:
+            monkeypatch.setattr(K, name, EMULATED[name])
+        elif isinstance(obj, types.FunctionType) and obj.__module__ == K.__name__ and \
+                name not in ("pad_channels", "status_word", "read_status"):
+            monkeypatch.setattr(K, name, _unsupported(name))
+    monkeypatch.setattr(K, "read_status", lambda: 0)

@@ -1,0 +1,137 @@
+"""The device code path of the operators on CPU tensors, with the kernel fronts replaced by plain-torch stand-ins
+(tests/kernel_emulation.py), against the reference (autograd) path of the same network.
+
+This pins what sits between an operator and its kernels: buffer layouts and paddings, the arguments of every launch,
+which operator masks whose delta, residual and activation bookkeeping, the dense row of a spatial loss input.
+The kernels themselves are compared with fp32 torch on a GPU."""
+import pytest
+import torch
+
+import kernel_emulation
+from rembrandt_b200.models import config as C
+from rembrandt_b200.models import zoo
+from rembrandt_b200.models.config import (Act, AffineCfg, Conv2dCfg, Data3dCfg, MimicAffineCfg, ParamsInit, Pool2dCfg,
+                                          PoolKind, ResConv2dCfg, SequentialOperatorConfig, SoftmaxKLLossCfg)
+from rembrandt_b200.models.net import Net
+
+K_ = ParamsInit.kaiming()
+X_ = ParamsInit.xavier()
+
+
+def _head(cfg, classes=10):
+    return cfg.affine(AffineCfg(classes, Act.IDENTITY, X_), "out").softmax_kl_loss(SoftmaxKLLossCfg(classes))
+
+
+def baseline():
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((14, 14, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 24, Act.RECT, K_), "conv1")
+    cfg.pool2d(Pool2dCfg(3, 2, 0, PoolKind.MAX), "pool1")
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 40, Act.IDENTITY, K_), "conv2")
+    cfg.pool2d(Pool2dCfg(2, 2, 0, PoolKind.AVERAGE, act=Act.RECT), "pool2")
+    cfg.conv2d(Conv2dCfg(1, 1, 0, 64, Act.RECT, K_), "conv3")
+    cfg.affine(AffineCfg(48, Act.RECT, X_), "fc1")
+    return _head(cfg)
+
+
+def strided():
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((15, 15, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 16, Act.RECT, K_), "conv1")
+    cfg.conv2d(Conv2dCfg(3, 2, 1, 24, Act.RECT, K_), "conv2")       # data-grad by stride phases
+    cfg.conv2d(Conv2dCfg(5, 3, 2, 32, Act.RECT, K_), "conv3")
+    return _head(cfg)
+
+
+def smooth():
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((12, 12, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 20, Act.TANH, K_), "conv1")
+    cfg.pool2d(Pool2dCfg(2, 2, 0, PoolKind.MAX), "pool1")
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 24, Act.BOUNDED_RECT, K_, act_param=0.5), "conv2")
+    cfg.affine(AffineCfg(30, Act.LOGISTIC, X_), "fc1")
+    cfg.affine(AffineCfg(20, Act.SCALED_LOGISTIC, X_, act_param=2.0), "fc2")
+    return _head(cfg)
+
+
+def low_rank():
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((12, 12, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 32, Act.RECT, K_), "conv1")
+    cfg.pool2d(Pool2dCfg(2, 2, 0, PoolKind.MAX), "pool1")
+    cfg.mimic_affine(MimicAffineCfg(bottleneck_rank=16, hidden_channels=40, out_channels=10), "m")
+    return cfg.softmax_kl_loss(SoftmaxKLLossCfg(10))
+
+
+def direct():
+    d = C.ConvBackend.DIRECT
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((13, 13, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 24, Act.RECT, K_, backend=d), "conv1")
+    cfg.conv2d(Conv2dCfg(3, 2, 1, 40, Act.RECT, K_, backend=d), "conv2")
+    cfg.conv2d(Conv2dCfg(3, 1, 0, 32, Act.TANH, K_, backend=d, bias=False), "conv3")
+    return _head(cfg)
+
+
+def residual():
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((10, 10, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 32, Act.RECT, K_), "stem")
+    cfg.res_conv2d(ResConv2dCfg(3, Act.RECT), "res1")
+    cfg.res_conv2d(ResConv2dCfg(5, Act.SCALED_LOGISTIC, act_param=2.0), "res2")
+    cfg.res_conv2d(ResConv2dCfg(3, Act.IDENTITY, bias=False), "res3")
+    cfg.pool2d(Pool2dCfg(10, 1, 0, PoolKind.AVERAGE), "gap")
+    return _head(cfg)
+
+
+def flat_input():
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((9, 9, 2), normalize=True))
+    cfg.affine(AffineCfg(24, Act.RECT, X_), "fc1")
+    return _head(cfg)
+
+
+def go_plain():
+    return zoo.go_policy_net(6, 16, 3)
+
+
+CASES = {"baseline": (baseline, 10), "strided": (strided, 10), "smooth": (smooth, 10), "low_rank": (low_rank, 10),
+         "direct": (direct, 10), "residual": (residual, 10), "flat_input": (flat_input, 10), "go_plain": (go_plain, 361)}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_device_path_matches_reference_path(monkeypatch, name):
+    make, classes = CASES[name]
+    kernel_emulation.install(monkeypatch)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    dev = Net(make(), 4, device="cpu", seed=(3, 4))
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    ref = Net(make(), 4, device="cpu", seed=(3, 4))
+    assert dev.is_cuda and not ref.is_cuda
+    assert torch.equal(dev.params, ref.params.detach())
+    with torch.no_grad():                       # both paths see the bf16-rounded weights
+        ref.params.copy_(dev.params16.float())
+    w, h, c = dev.input_op.cfg.in_dims
+    torch.manual_seed(1)
+    x = torch.randint(0, 256, (4, c, h, w), dtype=torch.uint8)
+    y = torch.randint(0, classes, (4,))
+    dev.load_batch(x, y.int())
+    ref.load_batch(x, y)
+    for n in (dev, ref):
+        n.forward(True)
+        n.backward()
+    dl, dc = dev.read_stats()
+    rl, rc = ref.read_stats()
+    assert abs(dl - rl) < 2e-2 * max(1.0, abs(rl)), (dl, rl)
+    biggest = max(float(ref.grads[s.offset: s.offset + s.numel].norm()) for s in dev.segs)
+    for seg in dev.segs:
+        a = dev.grads[seg.offset: seg.offset + seg.numel]
+        b = ref.grads[seg.offset: seg.offset + seg.numel]
+        if float(b.norm()) < 1e-4 * biggest:
+            continue        # e.g. the bias behind a one-channel softmax input: its gradient is a sum that cancels
+        rel = float((a - b).norm() / b.norm())
+        # Activations and deltas are bf16 on the device path and fp32 in the reference path. The rounding noise is
+        # unbiased, so the component of the device gradient along the reference one stays at 1; a wiring mistake
+        # gives errors of order one in both figures. The 361-way softmax over one plane sums deltas that nearly
+        # cancel, which is where the noise is largest.
+        along = float((a * b).sum() / (b * b).sum())
+        assert rel < (0.3 if name == "go_plain" else 0.1), f"{seg.name}: relative error {rel:.4g}"
+        assert abs(along - 1.0) < 0.05, f"{seg.name}: component along the reference gradient {along:.4g}"
+    # padded channels of every activation stay zero (a consumer's filters have live weights there only by accident)
+    for op in dev.ops[:-1]:
+        live = op.out_hwc[2] if dev.input_op.mode != "flat" or op is not dev.input_op else None
+        if live is not None and op.out is not None and op.out.shape[-1] > live:
+            assert float(op.out[..., live:].abs().sum()) == 0.0, f"{op.name}: padded channels are not zero"
