@@ -8,7 +8,7 @@ with fp32 torch on a GPU; what this layer checks is everything between the opera
 
 Covered: convolution (tensor-core fronts and the direct fronts), GEMM, bias / activation epilogues, column sums,
 filter repacking, pooling, softmax cross-entropy (one head, hard labels), pointwise losses, elementwise helpers, the
-input kernel without augmentation, the fused SGD step. Anything else raises, so a test cannot pass by accident.
+input kernel without augmentation, batch normalisation, the fused SGD step. Anything else raises, so a test cannot pass by accident.
 """
 import torch
 import torch.nn.functional as F
@@ -253,6 +253,58 @@ def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi
     dst.reshape(-1)[: N * OH * OW * Cp].view(N, OH, OW, Cp).copy_(out.to(dst.dtype))
 
 
+def _bn_apply(x, rows, C, c_valid, mean, istd, gamma, beta, residual, y, relu):
+    xm = _rows(x, rows, C)[:, :c_valid].float()
+    out = (xm - mean[:c_valid]) * istd[:c_valid] * gamma.reshape(-1)[:c_valid].float() + beta.reshape(-1)[:c_valid].float()
+    if residual is not None:
+        out = out + _rows(residual, rows, C)[:, :c_valid].float()
+    if relu:
+        out = out.clamp(min=0)
+    ym = _rows(y, rows, C)
+    ym[:, :c_valid] = out.to(y.dtype)
+    ym[:, c_valid:] = 0
+
+
+def bn_fwd_train(x, rows, C, c_valid, sums, eps, factor, mean, istd, run_mean, run_var, gamma, beta, residual, y,
+                 relu, avg_kind=0, step_ptr=None):
+    xm = _rows(x, rows, C).float()
+    m = xm.mean(0)
+    var = xm.var(0, unbiased=False)
+    mean.reshape(-1)[:C].copy_(m)
+    istd.reshape(-1)[:C].copy_(torch.rsqrt(var + eps))
+    if avg_kind:
+        t = int(step_ptr.reshape(-1)[0])
+        factor = 1.0 / (1.0 + t) if avg_kind == 1 else (1.0 if t == 0 else factor)
+    if run_mean is not None:
+        unbiased = var * rows / (rows - 1) if rows > 1 else var
+        rm, rv = run_mean.reshape(-1)[:C], run_var.reshape(-1)[:C]
+        rm.copy_((1 - factor) * rm + factor * m)
+        rv.copy_((1 - factor) * rv + factor * unbiased)
+    _bn_apply(x, rows, C, c_valid, mean.reshape(-1)[:C].float(), istd.reshape(-1)[:C].float(), gamma, beta, residual,
+              y, relu)
+
+
+def bn_fwd_infer(x, rows, C, c_valid, eps, run_mean, run_var, istd_tmp, gamma, beta, residual, y, relu):
+    istd_tmp.reshape(-1)[:C].copy_(torch.rsqrt(run_var.reshape(-1)[:C].float() + eps))
+    _bn_apply(x, rows, C, c_valid, run_mean.reshape(-1)[:C].float(), istd_tmp.reshape(-1)[:C].float(), gamma, beta,
+              residual, y, relu)
+
+
+def bn_bwd(x, dy, y_relu, rows, C, c_valid, sums, mean, istd, gamma, dgamma, dbeta, dx):
+    g = _rows(dy, rows, C)[:, :c_valid].float()
+    if y_relu is not None:
+        g = g * (_rows(y_relu, rows, C)[:, :c_valid].float() > 0)
+    m, s = mean.reshape(-1)[:c_valid].float(), istd.reshape(-1)[:c_valid].float()
+    xhat = (_rows(x, rows, C)[:, :c_valid].float() - m) * s
+    db, dg = g.sum(0), (g * xhat).sum(0)
+    dbeta.reshape(-1)[:c_valid].add_(db)
+    dgamma.reshape(-1)[:c_valid].add_(dg)
+    res = gamma.reshape(-1)[:c_valid].float() * s / rows * (rows * g - db - xhat * dg)
+    dm = _rows(dx, rows, C)
+    dm[:, :c_valid] = res.to(dx.dtype)
+    dm[:, c_valid:] = 0
+
+
 def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
     reference_step(w[:n], g[:n], v[:n], lr, mu, l2, grad_scale, mode, phase)
     if w16 is not None:
@@ -268,7 +320,7 @@ def _unsupported(name):
 EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fwd, conv_direct_wgrad,
                                     conv_direct_dgrad, pack_dgrad_filters, zero_s2d_structural, gemm_tc, bias_act,
                                     colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
-                                    softmax_ce, input_u8, sgd_fused)}
+                                    softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd)}
 
 
 def install(monkeypatch):
