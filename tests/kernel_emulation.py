@@ -7,8 +7,9 @@ are live) with torch operators; none of them is derived from a kernel's code. Th
 with fp32 torch on a GPU; what this layer checks is everything between the operators and the kernels.
 
 Covered: convolution (tensor-core fronts and the direct fronts), GEMM, bias / activation epilogues, column sums,
-filter repacking, pooling, softmax cross-entropy (one head, hard labels), pointwise losses, elementwise helpers, the
-input kernel without augmentation, batch normalisation, the fused SGD step. Anything else raises, so a test cannot pass by accident.
+filter repacking, pooling, local response normalisation, softmax cross-entropy (heads, masks, soft targets), pointwise
+losses, elementwise helpers, the input kernel without augmentation (plain, flat and space-to-depth output), batch
+normalisation, dropout with ratio zero, the fused SGD step. Anything else raises, so a test cannot pass by accident.
 """
 import torch
 import torch.nn.functional as F
@@ -88,7 +89,15 @@ def pack_dgrad_filters(w16, wt16, Kout, Kp, RS, Cp):
 
 
 def zero_s2d_structural(dw, Kout, R2, Cp, f, cin, ksize):
-    raise NotImplementedError("space-to-depth first layers are not emulated: use a stride-1 first convolution")
+    """Entries of a space-to-depth'd first-layer filter gradient with no counterpart in the original filter."""
+    g = dw.reshape(-1)[: Kout * R2 * R2 * Cp].view(Kout, R2, R2, Cp)
+    ch = torch.arange(Cp)
+    blk = ch // cin
+    dy, dx = blk // f, blk % f
+    for r2 in range(R2):
+        for s2 in range(R2):
+            dead = (ch >= f * f * cin) | (r2 * f + dy >= ksize) | (s2 * f + dx >= ksize)
+            g[:, r2, s2, dead] = 0
 
 
 def gemm_tc(a, a_mn, lda, b, b_mn, ldb, M, N, K_, d, ldd, epi=K.EPI_BF16, bias=None, relu=False, mask_src=None,
@@ -204,30 +213,93 @@ def pool_bwd(dy, idx, y_relu, dx, mask_src, N, H, W, C, P, Q, k, stride, pad, is
 
 def softmax_ce(logits, B, Kc, ld, labels, weights, w_scalar, delta, probs=None, loss_sum=None, correct=None,
                loss_per=None, argmax_out=None, cat_weights=None, mask=None, heads=1, soft=None):
-    if heads != 1 or mask is not None or soft is not None or cat_weights is not None:
-        raise NotImplementedError("only one head with hard labels is emulated")
-    x = _rows(logits, B, ld)[:, :Kc].float()
-    lab = labels.reshape(-1)[:B].long()
-    p = torch.softmax(x, 1)
+    """`heads` blocks of Kc logits per sample; a negative label switches its head off; masked categories get
+    probability zero; `soft` replaces the one-hot target. Accuracy and arg-max are those of the first head."""
+    if cat_weights is not None:
+        raise NotImplementedError("per-category gradient weights are not emulated")
+    L = heads
+    x = _rows(logits, B, ld)[:, : L * Kc].float().reshape(B * L, Kc)
+    if mask is not None:
+        x = x.masked_fill(mask.reshape(B * L, Kc) == 0, float("-inf"))
+    lab = labels.reshape(-1)[: B * L].long()
+    live = (lab >= 0) & (lab < Kc)
+    lp = torch.log_softmax(x, 1)
+    p = lp.exp()
     w = weights.reshape(-1)[:B].float() if weights is not None else torch.full((B,), float(w_scalar))
-    nll = -torch.log_softmax(x, 1).gather(1, lab.view(-1, 1)).squeeze(1)
-    am = x.argmax(1)
+    w = w.view(B, 1).expand(B, L).reshape(-1)
+    if soft is not None:
+        q = soft.reshape(B * L, Kc).float()
+        nll = -torch.where(q > 0, q * lp, torch.zeros_like(lp)).sum(1)
+        target = q
+    else:
+        nll = torch.where(live, -lp.gather(1, lab.clamp(0, Kc - 1).view(-1, 1)).squeeze(1), torch.zeros(B * L))
+        target = torch.zeros(B * L, Kc)
+        target[live, lab[live]] = 1.0
+    am = x.reshape(B, L, Kc)[:, 0].argmax(1)
     if delta is not None:
-        d = p.clone()
-        d[torch.arange(B), lab] -= 1.0
+        d = (p - target) * w.view(-1, 1)
+        if soft is None:
+            d = d * live.view(-1, 1)
         dm = _rows(delta, B, ld)
-        dm[:, :Kc] = (d * w.view(-1, 1)).to(delta.dtype)
-        dm[:, Kc:] = 0
+        dm[:, : L * Kc] = d.reshape(B, L * Kc).to(delta.dtype)
+        dm[:, L * Kc:] = 0
     if probs is not None:
-        probs.reshape(-1)[: B * Kc].view(B, Kc).copy_(p)
+        probs.reshape(-1)[: B * L * Kc].view(B * L, Kc).copy_(p)
     if loss_sum is not None:
         loss_sum += (w * nll).sum()
     if correct is not None:
-        correct += int((am == lab).sum())
+        correct += int((am == lab.view(B, L)[:, 0]).sum())
     if loss_per is not None:
-        loss_per.reshape(-1)[:B].copy_(w * nll)
+        loss_per.reshape(-1)[: B * L].copy_(w * nll)
     if argmax_out is not None:
         argmax_out.reshape(-1)[:B].copy_(am.int())
+
+
+def pointwise_loss(x, B, Kc, ld, target, weights, w_scalar, delta, loss_sum=None, correct=None, mode=0):
+    z = _rows(x, B, ld)[:, :Kc].float()
+    t = target.reshape(B, Kc).float()
+    w = weights.reshape(-1)[:B].float() if weights is not None else torch.full((B,), float(w_scalar))
+    if mode == 0:
+        per = F.binary_cross_entropy_with_logits(z, t, reduction="none").sum(1)
+        d = torch.sigmoid(z) - t
+        hits = int(((z[:, 0] > 0) == (t[:, 0] > 0.5)).sum())
+    else:
+        per = 0.5 * ((z - t) ** 2).sum(1)
+        d = z - t
+        hits = 0
+    if delta is not None:
+        dm = _rows(delta, B, ld)
+        dm[:, :Kc] = (d * w.view(-1, 1)).to(delta.dtype)
+        dm[:, Kc:] = 0
+    if loss_sum is not None:
+        loss_sum += (w * per).sum()
+    if correct is not None:
+        correct += hits
+
+
+def lrn_fwd(x, y, pixels, C, size, alpha_eff, beta, k):
+    xm = _rows(x, pixels, C).float()
+    sq = F.pad((xm * xm).unsqueeze(1), (size // 2, (size - 1) // 2)).unfold(2, size, 1).sum(3).squeeze(1)
+    _rows(y, pixels, C).copy_((xm * (k + alpha_eff * sq) ** (-beta)).to(y.dtype))
+
+
+def lrn_bwd(x, dy, dx, mask_src, pixels, C, size, alpha_eff, beta, k):
+    xm = _rows(x, pixels, C).float().requires_grad_(True)
+    sq = F.pad((xm * xm).unsqueeze(1), (size // 2, (size - 1) // 2)).unfold(2, size, 1).sum(3).squeeze(1)
+    out = xm * (k + alpha_eff * sq) ** (-beta)
+    (g,) = torch.autograd.grad(out, xm, _rows(dy, pixels, C).float())
+    if mask_src is not None:
+        g = g * (_rows(mask_src, pixels, C).float() > 0)
+    _rows(dx, pixels, C).copy_(g.to(dx.dtype))
+
+
+def dropout(x, y, n, p, seed, stream_id, mask_src=None, step_ptr=None):
+    if p != 0.0:
+        raise NotImplementedError("only a drop ratio of zero is emulated (the mask comes from an in-kernel generator)")
+    v = x.reshape(-1)[:n].float()
+    if mask_src is not None:
+        v = v * (mask_src.reshape(-1)[:n].float() > 0)
+    y.reshape(-1)[:n].copy_(v.to(y.dtype))
 
 
 def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi_y, lo_x, hi_x, random_crop,
@@ -249,7 +321,12 @@ def input_u8(src, mean, dst, N, C, H, W, crop_h, crop_w, OH, OW, Cp, f, lo_y, hi
         # flat mode: the whole image of one sample in one pixel, channel = (y * f + x) * C + c
         out[:, 0, 0, : crop_h * crop_w * C] = canvas.permute(0, 2, 3, 1).reshape(N, -1)
     else:
-        raise NotImplementedError("space-to-depth output is not emulated")
+        # space-to-depth: output pixel (Y, X) holds the f x f block of source pixels, channel = (dy * f + dx) * C + c
+        big = torch.zeros(N, C, OH * f, OW * f)
+        hh, ww = min(crop_h, OH * f), min(crop_w, OW * f)
+        big[:, :, :hh, :ww] = canvas[:, :, :hh, :ww]
+        blocks = big.view(N, C, OH, f, OW, f).permute(0, 2, 4, 3, 5, 1).reshape(N, OH, OW, f * f * C)
+        out[..., : f * f * C] = blocks
     dst.reshape(-1)[: N * OH * OW * Cp].view(N, OH, OW, Cp).copy_(out.to(dst.dtype))
 
 
@@ -320,7 +397,8 @@ def _unsupported(name):
 EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fwd, conv_direct_wgrad,
                                     conv_direct_dgrad, pack_dgrad_filters, zero_s2d_structural, gemm_tc, bias_act,
                                     colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
-                                    softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd)}
+                                    softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd,
+                                    pointwise_loss, lrn_fwd, lrn_bwd, dropout)}
 
 
 def install(monkeypatch):

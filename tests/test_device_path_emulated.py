@@ -103,9 +103,21 @@ def bn_blocks():
     return _head(cfg)
 
 
+def alexnet_like():
+    from rembrandt_b200.models.config import DropoutCfg, LrnCfg
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((23, 23, 3), normalize=True))
+    cfg.conv2d(Conv2dCfg(7, 2, 0, 24, Act.RECT, K_), "conv1")                  # strided first layer: space-to-depth input
+    cfg.lrn(LrnCfg(5, 1e-2, 0.75, 2.0), "rnorm1")
+    cfg.pool2d(Pool2dCfg(3, 2, 0, PoolKind.MAX), "pool1")
+    cfg.conv2d(Conv2dCfg(3, 1, 1, 40, Act.RECT, K_), "conv2")
+    cfg.affine(AffineCfg(48, Act.RECT, X_), "fc1")
+    cfg.dropout(DropoutCfg(0.0), "drop")
+    return _head(cfg)
+
+
 CASES = {"baseline": (baseline, 10), "strided": (strided, 10), "smooth": (smooth, 10), "low_rank": (low_rank, 10),
          "direct": (direct, 10), "residual": (residual, 10), "flat_input": (flat_input, 10), "go_plain": (go_plain, 361), "go_residual": (go_residual, 361),
-         "bn_blocks": (bn_blocks, 10)}
+         "bn_blocks": (bn_blocks, 10), "alexnet_like": (alexnet_like, 10)}
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
@@ -151,6 +163,85 @@ def test_device_path_matches_reference_path(monkeypatch, name):
             assert abs(along - 1.0) < 0.05, f"{seg.name}: component along the reference gradient {along:.4g}"
     # padded channels of every activation stay zero (a consumer's filters have live weights there only by accident)
     for op in dev.ops[:-1]:
-        live = op.out_hwc[2] if dev.input_op.mode != "flat" or op is not dev.input_op else None
+        live = op.out_hwc[2] if dev.input_op.mode == "nhwc" or op is not dev.input_op else None
         if live is not None and op.out is not None and op.out.shape[-1] > live:
             assert float(op.out[..., live:].abs().sum()) == 0.0, f"{op.name}: padded channels are not zero"
+
+
+def _pair(monkeypatch, make, batch=4):
+    kernel_emulation.install(monkeypatch)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    dev = Net(make(), batch, device="cpu", seed=(3, 4))
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    ref = Net(make(), batch, device="cpu", seed=(3, 4))
+    with torch.no_grad():
+        ref.params.copy_(dev.params16.float())
+    return dev, ref
+
+
+def _grads_agree(dev, ref, tol=0.1):
+    for seg in dev.segs:
+        a = dev.grads[seg.offset: seg.offset + seg.numel]
+        b = ref.grads[seg.offset: seg.offset + seg.numel]
+        rel = float((a - b).norm() / b.norm().clamp_min(1e-12))
+        assert rel < tol, f"{seg.name}: relative error {rel:.4g}"
+
+
+def test_masked_look_ahead_heads_and_soft_targets_on_the_device_path(monkeypatch):
+    from rembrandt_b200.models.config import MultiSoftmaxKLLossCfg
+
+    def make():
+        cfg = SequentialOperatorConfig().data3d(Data3dCfg((8, 8, 2), normalize=True))
+        cfg.conv2d(Conv2dCfg(3, 1, 1, 16, Act.RECT, K_), "conv1")
+        cfg.affine(AffineCfg(3 * 7, Act.IDENTITY, X_), "out")
+        return cfg.multi_softmax_kl_loss(MultiSoftmaxKLLossCfg(7, 3))
+
+    dev, ref = _pair(monkeypatch, make)
+    torch.manual_seed(2)
+    x = torch.randint(0, 256, (4, 2, 8, 8), dtype=torch.uint8)
+    labels = torch.tensor([[1, 2, -1], [0, 6, 3], [5, -1, -1], [2, 2, 2]])
+    mask = torch.rand(4, 3, 7) > 0.3
+    mask.scatter_(2, labels.clamp(min=0).unsqueeze(2), True)          # a target is always admissible
+    for n in (dev, ref):
+        n.loss_op.load_mask(mask)
+        n.load_batch(x, labels.int() if n is dev else labels)
+        n.forward(True)
+        n.backward()
+    dl, dc = dev.read_stats()
+    rl, rc = ref.read_stats()
+    assert abs(dl - rl) < 2e-2 * max(1.0, abs(rl)) and dc == rc
+    _grads_agree(dev, ref)
+    # distillation targets in place of the labels
+    q = torch.softmax(torch.randn(12, 7), 1) * mask.reshape(12, 7)
+    q = q / q.sum(1, keepdim=True)
+    for n in (dev, ref):
+        n.grads.zero_()
+        n.loss_op.load_soft_targets(q)
+        n.forward(True)
+        n.backward()
+    assert abs(dev.read_stats()[0] - ref.read_stats()[0]) < 2e-2 * max(1.0, abs(rl))
+    _grads_agree(dev, ref)
+
+
+@pytest.mark.parametrize("kind", ["logistic", "l2"])
+def test_pointwise_heads_on_the_device_path(monkeypatch, kind):
+    from rembrandt_b200.models.config import PointwiseLossCfg
+
+    def make():
+        cfg = SequentialOperatorConfig().data3d(Data3dCfg((6, 6, 2), normalize=True))
+        cfg.conv2d(Conv2dCfg(3, 1, 1, 8, Act.RECT, K_), "conv1")
+        cfg.conv2d(Conv2dCfg(3, 1, 1, 1, Act.IDENTITY, K_), "plane")             # a spatial input to the head: 36 outputs
+        return cfg.pointwise_loss(PointwiseLossCfg(36, kind))
+
+    dev, ref = _pair(monkeypatch, make)
+    torch.manual_seed(3)
+    x = torch.randint(0, 256, (4, 2, 6, 6), dtype=torch.uint8)
+    t = (torch.rand(4, 36) > 0.5).float() if kind == "logistic" else torch.randn(4, 36)
+    for n in (dev, ref):
+        n.load_batch(x, t)
+        n.forward(True)
+        n.backward()
+    dl, _ = dev.read_stats()
+    rl, _ = ref.read_stats()
+    assert abs(dl - rl) < 2e-2 * max(1.0, abs(rl)), (dl, rl)
+    _grads_agree(dev, ref)
