@@ -115,9 +115,14 @@ def alexnet_like():
     return _head(cfg)
 
 
+def graph_residual():
+    from test_graph_net import residual_graph
+    return residual_graph()
+
+
 CASES = {"baseline": (baseline, 10), "strided": (strided, 10), "smooth": (smooth, 10), "low_rank": (low_rank, 10),
          "direct": (direct, 10), "residual": (residual, 10), "flat_input": (flat_input, 10), "go_plain": (go_plain, 361), "go_residual": (go_residual, 361),
-         "bn_blocks": (bn_blocks, 10), "alexnet_like": (alexnet_like, 10)}
+         "bn_blocks": (bn_blocks, 10), "alexnet_like": (alexnet_like, 10), "graph_residual": (graph_residual, 10)}
 
 
 @pytest.mark.parametrize("name", sorted(CASES))
