@@ -79,6 +79,12 @@ class BlobRecord(C.Structure):
                 ("data_offset", C.c_uint64), ("num_elems", C.c_uint64), ("next_offset", C.c_uint64)]
 
 
+class Datum(C.Structure):
+    _fields_ = [("channels", C.c_int32), ("height", C.c_int32), ("width", C.c_int32), ("label", C.c_int32),
+                ("encoded", C.c_int32), ("data_offset", C.c_uint64), ("data_len", C.c_uint64),
+                ("float_count", C.c_uint64)]
+
+
 class XorShift(C.Structure):
     _fields_ = [("s", C.c_uint64 * 2)]
 
@@ -115,6 +121,12 @@ def host():
             lib.rb_lmdb_next.restype = i32
             lib.rb_lmdb_close.argtypes = [vp]
             lib.rb_lmdb_close.restype = None
+            lib.rb_datum_parse.argtypes = [vp, u64, C.POINTER(Datum)]
+            lib.rb_datum_parse.restype = i32
+            lib.rb_datum_floats.argtypes = [vp, u64, vp, u64]
+            lib.rb_datum_floats.restype = u64
+            lib.rb_bits_unpack.argtypes = [vp, u64, u64, C.c_uint8, vp]
+            lib.rb_bits_unpack.restype = i32
             lib.rb_loader_create.argtypes = [vp, vp, u64, u64, u64, C.c_uint32, C.c_uint32, u64, C.c_uint32,
                                              C.c_uint32, C.POINTER(vp), C.POINTER(vp)]
             lib.rb_loader_create.restype = vp

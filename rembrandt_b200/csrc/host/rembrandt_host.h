@@ -77,6 +77,20 @@ int rb_lmdb_seek(void* env, const uint8_t* key, uint32_t klen);   // first key >
 int rb_lmdb_next(void* env, const uint8_t** key, uint32_t* klen, const uint8_t** val, uint64_t* vlen);  // 1, or 0 at end
 void rb_lmdb_close(void* env);
 
+// ---- per-sample decoders (sample_codecs.cc) ------------------------------------------------------------
+// Caffe `Datum` message (fields: 1 channels, 2 height, 3 width, 4 data, 5 label, 6 float_data, 7 encoded).
+typedef struct {
+  int32_t channels, height, width, label, encoded;
+  uint64_t data_offset, data_len;   // the `data` bytes inside the message (not copied)
+  uint64_t float_count;             // number of float_data values, packed or not
+} rb_datum;
+// 0, or negative: -1 truncated varint, -2 a field runs past the message, -3 packed floats of odd size, -4 wire type.
+int rb_datum_parse(const uint8_t* buf, uint64_t len, rb_datum* out);
+// Copies up to `cap` float_data values in message order; returns how many were written.
+uint64_t rb_datum_floats(const uint8_t* buf, uint64_t len, float* out, uint64_t cap);
+// Bit i of the packed stream (bit i % 8 of byte i / 8) -> out[i] = scale or 0. -1 if the stream is too short.
+int rb_bits_unpack(const uint8_t* packed, uint64_t packed_len, uint64_t nbits, uint8_t scale, uint8_t* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -117,6 +117,53 @@ static void test_readers() {
   CHECK(std::abs(mean[5] - 0.5f * (images[5] + images[3072 + 5])) < 1e-4f);
 }
 
+static void test_sample_codecs() {
+  // Datum: channels 3, height 2, width 2, data 12 bytes, label 7, two unpacked floats, one packed pair, encoded
+  std::vector<uint8_t> msg = {0x08, 3, 0x10, 2, 0x18, 2, 0x22, 12};
+  for (int i = 0; i < 12; ++i) msg.push_back((uint8_t)(i * 11));
+  msg.insert(msg.end(), {0x28, 7});
+  const float f[4] = {1.5f, -2.f, 0.25f, 8.f};
+  for (int i = 0; i < 2; ++i) {
+    msg.push_back(0x35);
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(&f[i]);
+    msg.insert(msg.end(), b, b + 4);
+  }
+  msg.insert(msg.end(), {0x32, 8});
+  const uint8_t* b2 = reinterpret_cast<const uint8_t*>(&f[2]);
+  msg.insert(msg.end(), b2, b2 + 8);
+  msg.insert(msg.end(), {0x38, 1});
+  rb_datum d;
+  CHECK(rb_datum_parse(msg.data(), msg.size(), &d) == 0);
+  CHECK(d.channels == 3 && d.height == 2 && d.width == 2 && d.label == 7 && d.encoded == 1);
+  CHECK(d.data_len == 12 && msg[d.data_offset + 1] == 11 && d.float_count == 4);
+  float got[4] = {0, 0, 0, 0};
+  CHECK(rb_datum_floats(msg.data(), msg.size(), got, 4) == 4);
+  for (int i = 0; i < 4; ++i) CHECK(got[i] == f[i]);
+  CHECK(rb_datum_floats(msg.data(), msg.size(), got, 3) == 3);   // a short output array is respected
+  // every truncation either parses as a shorter message or is rejected; exact-size copies let ASan see overreads
+  for (uint64_t len = 0; len < msg.size(); ++len) {
+    std::vector<uint8_t> cut(msg.begin(), msg.begin() + len);
+    const int rc = rb_datum_parse(cut.data(), len, &d);
+    CHECK(rc <= 0);
+    if (rc == 0) CHECK(d.data_offset + d.data_len <= len);
+    rb_datum_floats(cut.data(), len, got, 4);
+  }
+  const uint8_t huge_len[] = {0x22, 0xFF, 0xFF, 0xFF, 0xFF, 0xFF, 0xFF, 0xFF, 0xFF, 0xFF, 0x01};
+  CHECK(rb_datum_parse(huge_len, sizeof(huge_len), &d) == -2);
+  const uint8_t endless[] = {0x08, 0x80, 0x80, 0x80, 0x80, 0x80, 0x80, 0x80, 0x80, 0x80, 0x80, 0x80};
+  CHECK(rb_datum_parse(endless, sizeof(endless), &d) == -1);
+  const uint8_t group[] = {0x0B};
+  CHECK(rb_datum_parse(group, sizeof(group), &d) == -4);
+  // bit planes
+  const uint8_t packed[2] = {0xA5, 0x03};
+  std::vector<uint8_t> out(10);
+  CHECK(rb_bits_unpack(packed, 2, 10, 255, out.data()) == 0);
+  const uint8_t want[10] = {255, 0, 255, 0, 0, 255, 0, 255, 255, 255};
+  CHECK(std::memcmp(out.data(), want, 10) == 0);
+  CHECK(rb_bits_unpack(packed, 1, 10, 255, out.data()) == -1);
+  CHECK(rb_bits_unpack(packed, 0, 0, 1, out.data()) == 0);
+}
+
 static void test_loader(uint32_t mode, uint32_t threads, uint32_t nslots) {
   const uint64_t n = 97, elems = 33;
   const uint32_t batch = 8;
@@ -197,6 +244,7 @@ int main(int argc, char** argv) {
   test_blob();
   test_rng_and_partition();
   test_readers();
+  test_sample_codecs();
   for (uint32_t mode = 0; mode < 3; ++mode) {
     test_loader(mode, 1, 2);
     test_loader(mode, 4, 3);

@@ -53,8 +53,12 @@ def _decode_bits3d(value: bytes, offset: int, scale: int):
     start = offset + 32
     if start + nbytes > len(value):
         raise blob.BlobError("truncated bit record")
-    bits = np.unpackbits(np.frombuffer(value, np.uint8, nbytes, start), bitorder="little")[:n]
-    return (bits * np.uint8(scale)).reshape(c, h, w), start + nbytes
+    from .. import _native
+    out = np.empty(n, dtype=np.uint8)
+    packed = np.frombuffer(value, np.uint8, nbytes, start)
+    if n and _native.host().rb_bits_unpack(packed.ctypes.data, nbytes, n, int(scale) & 0xFF, out.ctypes.data) != 0:
+        raise blob.BlobError("truncated bit record")
+    return out.reshape(c, h, w), start + nbytes
 
 
 class Bits3dCodec:
@@ -123,7 +127,29 @@ def _varint(buf: bytes, pos: int) -> Tuple[int, int]:
 
 
 def decode_caffe_datum(buf: bytes) -> dict:
-    """Fields: 1 channels, 2 height, 3 width, 4 data (bytes), 5 label, 6 float_data (repeated), 7 encoded."""
+    """Fields: 1 channels, 2 height, 3 width, 4 data (bytes), 5 label, 6 float_data (repeated), 7 encoded.
+    Parsed by the C++ runtime (csrc/host/sample_codecs.cc); `decode_caffe_datum_py` is the same reader in Python,
+    kept as its cross-check."""
+    import ctypes as C_
+    from .. import _native
+    lib = _native.host()
+    d = _native.Datum()
+    raw = np.frombuffer(buf, dtype=np.uint8)
+    rc = lib.rb_datum_parse(raw.ctypes.data if len(buf) else None, len(buf), C_.byref(d))
+    if rc != 0:
+        raise ValueError({-1: "truncated varint", -2: "a field runs past the end of the message",
+                          -3: "packed float_data of odd size", -4: "unsupported wire type"}.get(rc, f"error {rc}"))
+    floats = []
+    if d.float_count:
+        arr = np.empty(int(d.float_count), dtype="<f4")
+        n = lib.rb_datum_floats(raw.ctypes.data, len(buf), arr.ctypes.data, int(d.float_count))
+        floats = arr[: int(n)].tolist()
+    return {"channels": d.channels, "height": d.height, "width": d.width,
+            "data": bytes(buf[d.data_offset: d.data_offset + d.data_len]), "label": d.label, "float_data": floats,
+            "encoded": bool(d.encoded)}
+
+
+def decode_caffe_datum_py(buf: bytes) -> dict:
     out = {"channels": 0, "height": 0, "width": 0, "data": b"", "label": 0, "float_data": [], "encoded": False}
     names = {1: "channels", 2: "height", 3: "width", 5: "label"}
     pos = 0

@@ -75,3 +75,41 @@ def test_strided_data_grad_phases_match_autograd(k, stride, pad, H, W, seed):
     ref = torch.autograd.grad(y, x, dy)[0]
     got = dgrad_by_phases_reference(dy, w, H, W, stride, pad)
     assert torch.allclose(got, ref, atol=1e-9), float((got - ref).abs().max())
+
+
+@settings(max_examples=120, deadline=None)
+@given(st.integers(0, 4), st.integers(0, 300), st.integers(0, 300), st.binary(max_size=64), st.integers(0, 2**31 - 1),
+       st.lists(st.floats(-1e3, 1e3, width=32), max_size=5), st.booleans(), st.booleans())
+def test_datum_decoders_agree_on_well_formed_messages(c, h, w, data, label, floats, encoded, packed):
+    from rembrandt_b200.data import codecs
+    msg = codecs.encode_caffe_datum(data, c, h, w, label, encoded)
+    fl = np.asarray(floats, dtype="<f4")
+    if len(fl):
+        if packed:
+            msg += bytes([6 << 3 | 2, 4 * len(fl)]) + fl.tobytes()
+        else:
+            msg += b"".join(bytes([6 << 3 | 5]) + fl[i:i + 1].tobytes() for i in range(len(fl)))
+    a, b = codecs.decode_caffe_datum(msg), codecs.decode_caffe_datum_py(msg)
+    assert a == b
+    assert a["data"] == data and a["label"] == label and a["float_data"] == fl.tolist()
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.binary(max_size=48))
+def test_native_datum_parser_never_reads_outside_arbitrary_bytes(junk):
+    """Arbitrary bytes either parse (then the data field lies inside the message) or are rejected with ValueError."""
+    from rembrandt_b200.data import codecs
+    try:
+        d = codecs.decode_caffe_datum(junk)
+    except ValueError:
+        return
+    assert len(d["data"]) <= len(junk)
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.integers(1, 5), st.integers(1, 9), st.integers(1, 9), st.integers(1, 255), st.integers(0, 2**31 - 1))
+def test_bit_planes_round_trip(c, h, w, scale, seed):
+    from rembrandt_b200.data import codecs
+    bits = np.random.default_rng(seed).integers(0, 2, (c, h, w))
+    out = codecs.Bits3dCodec(scale).decode(codecs.encode_bits3d(bits))
+    assert out.dtype == np.uint8 and (out == bits * scale).all()
