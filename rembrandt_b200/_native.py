@@ -130,6 +130,9 @@ def host():
             lib.rb_loader_create.argtypes = [vp, vp, u64, u64, u64, C.c_uint32, C.c_uint32, u64, C.c_uint32,
                                              C.c_uint32, C.POINTER(vp), C.POINTER(vp)]
             lib.rb_loader_create.restype = vp
+            lib.rb_loader_create_lmdb.argtypes = [C.c_char_p, u64, u64, u64, C.c_uint32, C.c_uint32, u64, C.c_uint32,
+                                                  C.c_uint32, C.POINTER(vp), C.POINTER(vp), C.POINTER(C.c_int32)]
+            lib.rb_loader_create_lmdb.restype = vp
             lib.rb_loader_acquire.argtypes = [vp, C.POINTER(C.c_uint64)]
             lib.rb_loader_acquire.restype = i32
             lib.rb_loader_release.argtypes = [vp, i32]

@@ -119,9 +119,20 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
         from ..data.datasets import source_arrays
         from ..data.native_loader import NativeBatchLoader
         from ..utils.rng import partition_range
-        imgs, lbls = source_arrays(source)
-        train_iter = NativeBatchLoader(imgs, lbls, args.batch, mode="shuffled", seed=args.seed + rank,
-                                       threads=args.native_loader, shard=partition_range(len(source), world, rank))
+        shard = partition_range(len(source), world, rank)
+        w, h, c = dims
+        train_iter = None
+        if getattr(source, "lmdb_path", None):
+            try:   # raw image records: pixels go from the memory-mapped database to the pinned slots in C++
+                train_iter = NativeBatchLoader.from_caffe_lmdb(source.lmdb_path, (c, h, w), args.batch, mode="shuffled",
+                                                               seed=args.seed + rank, threads=args.native_loader,
+                                                               shard=shard)
+            except RuntimeError:
+                train_iter = None          # encoded (JPEG) records need the Python decoder
+        if train_iter is None:
+            imgs, lbls = source_arrays(source)
+            train_iter = NativeBatchLoader(imgs, lbls, args.batch, mode="shuffled", seed=args.seed + rank,
+                                           threads=args.native_loader, shard=shard)
     else:
         train_iter = BatchIter(AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world),
                                                                        seed=(args.seed + rank, 99))),

@@ -28,8 +28,12 @@ inline uint64_t mix64(uint64_t x) {   // splitmix64 finaliser
 }
 
 struct Loader {
-  const uint8_t* images;
-  const int32_t* labels;
+  const uint8_t* images = nullptr;
+  const int32_t* labels = nullptr;
+  // gather form: one pointer per sample instead of one contiguous array (records of a memory-mapped database)
+  std::vector<const uint8_t*> sample_ptrs;
+  std::vector<int32_t> sample_labels;
+  void* owned_env = nullptr;   // LMDB environment kept open for the lifetime of the loader
   uint64_t elems, lo, hi, seed;
   uint32_t batch, nslots, mode;
   std::vector<uint8_t*> img_slots;
@@ -71,8 +75,13 @@ struct Loader {
   void fill(uint32_t slot, uint64_t b) {
     for (uint32_t i = 0; i < batch; ++i) {
       const uint64_t idx = sample_index(b * batch + i);
-      std::memcpy(img_slots[slot] + (uint64_t)i * elems, images + idx * elems, elems);
-      lbl_slots[slot][i] = labels ? labels[idx] : 0;
+      if (sample_ptrs.empty()) {
+        std::memcpy(img_slots[slot] + (uint64_t)i * elems, images + idx * elems, elems);
+        lbl_slots[slot][i] = labels ? labels[idx] : 0;
+      } else {
+        std::memcpy(img_slots[slot] + (uint64_t)i * elems, sample_ptrs[idx], elems);
+        lbl_slots[slot][i] = sample_labels[idx];
+      }
     }
   }
 
@@ -121,6 +130,53 @@ void* rb_loader_create(const uint8_t* images, const int32_t* labels, uint64_t el
   return L;
 }
 
+// A loader over the raw (not encoded) images of a Caffe database: the environment is walked once at creation, every
+// `Datum` is parsed in place, and the workers copy pixel bytes straight from the memory mapping into the slots.
+// Records [lo, hi) in key order form the shard. `elems` must equal channels * height * width of every record.
+// On failure returns null and stores a reason in *error: 1 cannot open, 2 malformed record, 3 encoded or wrong size,
+// 4 bad arguments.
+void* rb_loader_create_lmdb(const char* path, uint64_t elems, uint64_t lo, uint64_t hi, uint32_t batch, uint32_t mode,
+                            uint64_t seed, uint32_t threads, uint32_t nslots, uint8_t** image_slots,
+                            int32_t** label_slots, int32_t* error) {
+  int32_t dummy;
+  if (!error) error = &dummy;
+  *error = 4;
+  if (!path || batch == 0 || nslots < 2 || threads == 0 || mode > 2 || !image_slots || !label_slots) return nullptr;
+  void* env = rb_lmdb_open(path);
+  if (!env) { *error = 1; return nullptr; }
+  Loader* L = new Loader();
+  L->owned_env = env;
+  const uint64_t total = rb_lmdb_entries(env);
+  if (hi > total) hi = total;
+  const uint8_t *k, *v;
+  uint32_t kl;
+  uint64_t vl, n = 0;
+  bool ok = hi > lo && rb_lmdb_seek(env, nullptr, 0) == 1;
+  *error = ok ? 0 : 4;
+  while (ok && n < hi && rb_lmdb_next(env, &k, &kl, &v, &vl)) {
+    if (n++ < lo) continue;
+    rb_datum d;
+    if (rb_datum_parse(v, vl, &d) != 0) { *error = 2; ok = false; break; }
+    if (d.encoded || d.data_len != elems) { *error = 3; ok = false; break; }
+    L->sample_ptrs.push_back(v + d.data_offset);
+    L->sample_labels.push_back(d.label);
+  }
+  if (ok && L->sample_ptrs.size() != hi - lo) { *error = 2; ok = false; }
+  if (!ok) {
+    rb_lmdb_close(env);
+    delete L;
+    return nullptr;
+  }
+  L->elems = elems; L->lo = 0; L->hi = L->sample_ptrs.size(); L->seed = seed;
+  L->batch = batch; L->nslots = nslots; L->mode = mode;
+  L->img_slots.assign(image_slots, image_slots + nslots);
+  L->lbl_slots.assign(label_slots, label_slots + nslots);
+  L->state.assign(nslots, 0);
+  L->slot_batch.assign(nslots, 0);
+  for (uint32_t t = 0; t < threads; ++t) L->workers.emplace_back([L] { L->run(); });
+  return L;
+}
+
 // Blocks until the next batch (in order) is ready; returns its slot, which stays valid until it is released.
 int rb_loader_acquire(void* handle, uint64_t* batch_number) {
   Loader* L = static_cast<Loader*>(handle);
@@ -153,6 +209,7 @@ void rb_loader_destroy(void* handle) {
   L->cv_free.notify_all();
   L->cv_ready.notify_all();
   for (auto& t : L->workers) t.join();
+  if (L->owned_env) rb_lmdb_close(L->owned_env);
   delete L;
 }
 

@@ -62,6 +62,11 @@ void rb_mean_u8(const uint8_t* images, uint64_t n, uint64_t elems, float* mean_o
 void* rb_loader_create(const uint8_t* images, const int32_t* labels, uint64_t elems, uint64_t lo, uint64_t hi,
                        uint32_t batch, uint32_t mode, uint64_t seed, uint32_t threads, uint32_t nslots,
                        uint8_t** image_slots, int32_t** label_slots);
+// The same loader over the raw images of a Caffe LMDB environment (records [lo, hi) in key order, pixel bytes copied
+// straight from the memory mapping). *error: 1 cannot open, 2 malformed record, 3 encoded or wrong size, 4 arguments.
+void* rb_loader_create_lmdb(const char* path, uint64_t elems, uint64_t lo, uint64_t hi, uint32_t batch, uint32_t mode,
+                            uint64_t seed, uint32_t threads, uint32_t nslots, uint8_t** image_slots,
+                            int32_t** label_slots, int32_t* error);
 int rb_loader_acquire(void* handle, uint64_t* batch_number);   // blocks; slot index, or -1 after destroy
 void rb_loader_release(void* handle, int slot);
 void rb_loader_destroy(void* handle);

@@ -237,6 +237,15 @@ static void test_lmdb(const char* path, uint64_t expected) {
   CHECK(rb_lmdb_seek(env, (const uint8_t*)beyond.data(), (uint32_t)beyond.size()) == 0);
   CHECK(rb_lmdb_next(env, &k, &kl, &v, &vl) == 0);
   rb_lmdb_close(env);
+  // the values of this environment are not image records: the database-backed loader must refuse it cleanly
+  std::vector<uint8_t> slot_a(64), slot_b(64);
+  std::vector<int32_t> lab_a(4), lab_b(4);
+  uint8_t* ip[2] = {slot_a.data(), slot_b.data()};
+  int32_t* lp[2] = {lab_a.data(), lab_b.data()};
+  int32_t err = 0;
+  CHECK(rb_loader_create_lmdb(path, 16, 0, expected, 4, 0, 1, 2, 2, ip, lp, &err) == nullptr);
+  CHECK(err == 2 || err == 3);
+  CHECK(rb_loader_create_lmdb("/nonexistent/environment", 16, 0, 8, 4, 0, 1, 2, 2, ip, lp, &err) == nullptr && err == 1);
   std::printf("lmdb: %llu entries, byte sum %llu\n", (unsigned long long)count, (unsigned long long)bytes);
 }
 

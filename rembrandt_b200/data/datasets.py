@@ -176,6 +176,12 @@ class _IterableAsSource:
     def __getitem__(self, i):
         return self._load()[i]
 
+    @property
+    def dims(self):
+        """(W, H, C) of the records, read off the first one."""
+        c, h, w = np.asarray(self._load()[0][0]).shape
+        return (w, h, c)
+
 
 def open_split(split: DatasetSplit, rank: int = 0, world: int = 1) -> DataSource:
     """Open one `[dataset.<split>]` table of a .data file (src/data_new.rs:296-412)."""
@@ -188,7 +194,9 @@ def open_split(split: DatasetSplit, rank: int = 0, world: int = 1) -> DataSource
     if split.source == "lmdb_caffe":
         from .codecs import JpegDataCodec
         from .lmdb_reader import LmdbCaffeShard
-        return _IterableAsSource(LmdbCaffeShard(split.data_path, rank, world, codec=JpegDataCodec()))
+        src = _IterableAsSource(LmdbCaffeShard(split.data_path, rank, world, codec=JpegDataCodec()))
+        src.lmdb_path = split.data_path      # lets the native loader read the environment without Python per sample
+        return src
     if split.source == "varraydb":
         from .codecs import JpegDataCodec
         from .recorddb import VarrayDbShard

@@ -39,3 +39,17 @@ def test_host_side_probes():
     assert [r["requested_us"] for r in res["sleep"]] == [1, 10, 100, 1000, 10000]
     assert all(r["observed_us"] >= r["requested_us"] for r in res["sleep"])
     assert test_dist.main(["--device", "cpu"]) == (0, 1)
+
+
+def test_training_from_a_caffe_database_through_the_native_loader(tmp_path):
+    import numpy as np
+    from rembrandt_b200.data.codecs import encode_caffe_datum
+    from rembrandt_b200.data.lmdb_reader import write_env
+    rng = np.random.default_rng(0)
+    items = [(b"%08d" % i, encode_caffe_datum(rng.integers(0, 256, 3 * 32 * 32, dtype=np.uint8).tobytes(), 3, 32, 32,
+                                              label=i % 10)) for i in range(64)]
+    (tmp_path / "db").mkdir()
+    write_env(str(tmp_path / "db"), items)
+    (tmp_path / "c.data").write_text(f'[dataset.train]\nsource = "lmdb_caffe"\ndata_path = "{tmp_path / "db"}"\n')
+    sgd = train_cifar10.main(TINY + ["--data", str(tmp_path / "c.data"), "--native-loader", "2"])
+    assert sgd.engine.iter == 3

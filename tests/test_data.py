@@ -321,3 +321,34 @@ def test_episode_iterators_partition_and_augment(tmp_path):
     aug = AugmentDataSource(lambda im, lab: (im + 1, lab), src)
     assert len(aug) == 12 and aug.episode_ranges() == src.episode_ranges()
     assert int(aug[0][0].max()) == 1 and aug[3][1] == 3
+
+
+def test_native_loader_over_a_caffe_database(tmp_path):
+    from rembrandt_b200.data.codecs import encode_caffe_datum
+    from rembrandt_b200.data.lmdb_reader import write_env
+    from rembrandt_b200.data.native_loader import NativeBatchLoader
+    rng = np.random.default_rng(4)
+    imgs = rng.integers(0, 256, (37, 3, 5, 4), dtype=np.uint8)
+    items = [(b"%08d" % i, encode_caffe_datum(imgs[i].tobytes(), 3, 5, 4, label=100 + i)) for i in range(37)]
+    write_env(str(tmp_path), items, max_leaf_nodes=5)
+    ld = NativeBatchLoader.from_caffe_lmdb(str(tmp_path), (3, 5, 4), batch=6, mode="cyclic", threads=3, pin=False,
+                                           max_batches=13)
+    seen = []
+    for x, y in ld:
+        assert x.shape == (6, 3, 5, 4)
+        for j in range(6):
+            i = int(y[j]) - 100
+            assert np.array_equal(x[j].numpy(), imgs[i])
+            seen.append(i)
+    ld.close()
+    assert seen == [k % 37 for k in range(78)]
+    # a shard of records 10 .. 19, shuffled epochs: every record of the shard once per epoch
+    ld = NativeBatchLoader.from_caffe_lmdb(str(tmp_path), (3, 5, 4), batch=5, mode="shuffled", seed=3, threads=2,
+                                           shard=(10, 20), pin=False, max_batches=4)
+    got = [int(v) - 100 for _, y in ld for v in y]
+    ld.close()
+    assert sorted(got[:10]) == list(range(10, 20)) and sorted(got[10:]) == list(range(10, 20))
+    with pytest.raises(RuntimeError, match="not of the given shape"):
+        NativeBatchLoader.from_caffe_lmdb(str(tmp_path), (3, 5, 5), batch=2, pin=False)
+    with pytest.raises(RuntimeError, match="cannot open"):
+        NativeBatchLoader.from_caffe_lmdb(str(tmp_path / "missing"), (3, 5, 4), batch=2, pin=False)
