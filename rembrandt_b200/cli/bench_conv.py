@@ -25,6 +25,13 @@ SHAPES = {
     "nin_conv3": (256, 13, 13, 384, 3, 1, 1),
     "nin_conv4": (384, 6, 6, 1024, 3, 1, 1),
     "nin_cccp7": (1024, 6, 6, 1024, 1, 1, 0),
+    # the small board-game shapes the reference's tool also times (tools/bench-cudnn.rs:10-60: 8 x 8 boards at batch
+    # 1024, 19 x 19 Go boards at batch 8) and the 128-channel Go layers of tools/train-gogod.rs
+    "board8_conv1": (12, 8, 8, 16, 5, 1, 2),
+    "board8_conv2": (16, 8, 8, 6, 3, 1, 1),
+    "go19_conv1": (16, 19, 19, 16, 5, 1, 2),
+    "go19_hidden": (16, 19, 19, 16, 3, 1, 1),
+    "go19_res128": (128, 19, 19, 128, 3, 1, 1),
 }
 
 
