@@ -55,8 +55,8 @@ def read_baseline(model, n):
             v = tab.get(f"{model}_images_per_s", {}).get(str(n))
             if v:
                 return v
-        except Exception:
-            pass
+        except (OSError, ValueError, AttributeError):
+            pass      # no such file, or not the JSON layout expected: try the next source
     return None
 
 
@@ -80,8 +80,8 @@ class ClockSampler:
                  "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
-        except Exception:
-            self.proc = None
+        except OSError:
+            self.proc = None      # no nvidia-smi on this machine
 
     def _read(self):
         for line in self.proc.stdout:
@@ -93,7 +93,7 @@ class ClockSampler:
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
-        except Exception:
+        except subprocess.TimeoutExpired:
             self.proc.kill()
         sm, mx, reasons, per_gpu = [], [], set(), {}
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]

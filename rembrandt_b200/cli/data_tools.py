@@ -58,8 +58,8 @@ def test_lmdb(args):
                 d = decode_caffe_datum(v)
                 row.update({"channels": d["channels"], "height": d["height"], "width": d["width"], "label": d["label"],
                             "encoded": d["encoded"]})
-            except Exception:
-                pass
+            except ValueError:
+                pass      # not a Datum message: report the key and size only
             print(json.dumps(row))
 
 

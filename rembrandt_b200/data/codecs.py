@@ -104,7 +104,7 @@ class JpegDataCodec:
         try:
             from PIL import Image  # noqa: F401
             self._ok = True
-        except Exception:
+        except ImportError:
             self._ok = False
 
     def decode(self, value: bytes) -> np.ndarray:

@@ -96,8 +96,8 @@ class SymmetricArena:
     def multicast_ptr(self, name: str) -> int:
         try:
             mc = int(self.handles[name].multicast_ptr or 0)
-        except Exception:
-            return 0
+        except (AttributeError, RuntimeError):
+            return 0      # this torch build / this fabric has no multicast object for the allocation
         return mc + self._payload_offset(name) if mc else 0
 
     def damaged(self) -> List[str]:
