@@ -250,3 +250,99 @@ def test_pointwise_heads_on_the_device_path(monkeypatch, kind):
     rl, _ = ref.read_stats()
     assert abs(dl - rl) < 2e-2 * max(1.0, abs(rl)), (dl, rl)
     _grads_agree(dev, ref)
+
+
+# ---- random small networks: geometry (odd sizes, strides, paddings, ceil-mode pooling) and channel padding --------
+from hypothesis import HealthCheck, given, settings, strategies as st
+
+
+@st.composite
+def _random_net(draw):
+    hw = draw(st.integers(7, 15))
+    c = draw(st.integers(1, 4))
+    layers = []
+    size = hw
+    first = True
+    for _ in range(draw(st.integers(1, 4))):
+        kind = draw(st.sampled_from(["conv", "conv", "pool", "res", "lrn"]))
+        if kind == "conv":
+            k = draw(st.sampled_from([1, 3, 5]))
+            s = 1 if first else draw(st.sampled_from([1, 1, 2]))     # the space-to-depth first layer has its own case
+            p = draw(st.integers(0, k // 2))
+            if size + 2 * p < k:
+                continue
+            out = draw(st.sampled_from([5, 8, 16, 24, 33]))
+            act = draw(st.sampled_from([Act.RECT, Act.RECT, Act.IDENTITY, Act.TANH]))
+            layers.append(("conv", (k, s, p, out, act, draw(st.booleans()))))
+            size = (size + 2 * p - k) // s + 1
+            first = False
+        elif kind == "pool" and not first and size >= 3:
+            k = draw(st.sampled_from([2, 3]))
+            p = draw(st.integers(0, 1)) if k == 3 else 0
+            is_max = draw(st.booleans())
+            relu = draw(st.booleans())
+            layers.append(("pool", (k, 2, p, is_max, relu)))
+            o = -(-(size + 2 * p - k) // 2) + 1
+            if (o - 1) * 2 >= size + p:
+                o -= 1
+            size = o
+        elif kind == "res" and not first:
+            layers.append(("res", (draw(st.sampled_from([1, 3])), draw(st.sampled_from([Act.RECT, Act.IDENTITY])))))
+        elif kind == "lrn" and not first:
+            layers.append(("lrn", ()))
+        if size < 2:
+            break
+    if first:
+        layers.insert(0, ("conv", (3, 1, 1, 8, Act.RECT, True)))
+    return hw, c, layers, draw(st.integers(2, 3)), draw(st.integers(0, 2**16))
+
+
+def _build_random(hw, c, layers):
+    from rembrandt_b200.models.config import LrnCfg
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((hw, hw, c), normalize=True))
+    for i, (kind, a) in enumerate(layers):
+        if kind == "conv":
+            k, s, p, out, act, bias = a
+            cfg.conv2d(Conv2dCfg(k, s, p, out, act, K_, bias=bias), f"conv{i}")
+        elif kind == "pool":
+            k, s, p, is_max, relu = a
+            cfg.pool2d(Pool2dCfg(k, s, p, PoolKind.MAX if is_max else PoolKind.AVERAGE,
+                                 act=Act.RECT if relu else Act.IDENTITY), f"pool{i}")
+        elif kind == "res":
+            cfg.res_conv2d(ResConv2dCfg(a[0], a[1]), f"res{i}")
+        else:
+            cfg.lrn(LrnCfg(3, 1e-2, 0.75, 2.0), f"lrn{i}")
+    return _head(cfg, 6)
+
+
+@settings(max_examples=60, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture,
+                                                                 HealthCheck.too_slow])
+@given(_random_net())
+def test_random_networks_on_the_device_path(monkeypatch, spec):
+    hw, c, layers, batch, seed = spec
+    kernel_emulation.install(monkeypatch)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    dev = Net(_build_random(hw, c, layers), batch, device="cpu", seed=(seed, 4))
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    ref = Net(_build_random(hw, c, layers), batch, device="cpu", seed=(seed, 4))
+    with torch.no_grad():
+        ref.params.copy_(dev.params16.float())
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randint(0, 256, (batch, c, hw, hw), dtype=torch.uint8, generator=g)
+    y = torch.randint(0, 6, (batch,), generator=g)
+    dev.load_batch(x, y.int())
+    ref.load_batch(x, y)
+    for n in (dev, ref):
+        n.forward(True)
+        n.backward()
+    dl, rl = dev.read_stats()[0], ref.read_stats()[0]
+    assert abs(dl - rl) < 3e-2 * max(1.0, abs(rl)), (layers, dl, rl)
+    a, b = dev.grads, ref.grads
+    # over the whole gradient vector the rounding noise averages out; a geometry or masking mistake does not
+    along = float((a * b).sum() / (b * b).sum().clamp_min(1e-20))
+    rel = float((a - b).norm() / b.norm().clamp_min(1e-12))
+    assert abs(along - 1.0) < 0.05 and rel < 0.15, (layers, along, rel)
+    for op in dev.ops[1:-1]:
+        live = op.out_hwc[2]
+        if op.out.shape[-1] > live:
+            assert float(op.out[..., live:].abs().sum()) == 0.0, f"{op.name}: padded channels are not zero"
