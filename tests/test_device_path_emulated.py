@@ -346,3 +346,32 @@ def test_random_networks_on_the_device_path(monkeypatch, spec):
         live = op.out_hwc[2]
         if op.out.shape[-1] > live:
             assert float(op.out[..., live:].abs().sum()) == 0.0, f"{op.name}: padded channels are not zero"
+
+
+def test_lenet_trains_on_the_emulated_device_path(monkeypatch):
+    """Forward, backward and the fused optimizer step (fp32 master, bf16 compute copy) of the device path train the
+    convolutional LeNet to full accuracy on separable synthetic digits."""
+    from rembrandt_b200.data import BatchIter, RandomSampleDataIter, RangeDataShard, SyntheticDataSource
+    from rembrandt_b200.optim.sgd import Momentum
+    from rembrandt_b200.optim.stepper import SgdStepper
+    kernel_emulation.install(monkeypatch)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    net = Net(zoo.lenet(pad=2), 32, device="cpu", seed=(0, 0), minibatch_size=32)
+    stepper = SgdStepper(net, Momentum.UPDATE, 0.9, 5e-4)
+    src = SyntheticDataSource(1024, (28, 28, 1), 10, seed=1, separable=True)
+    batches = BatchIter(RandomSampleDataIter(RangeDataShard(src), seed=(3, 4)), 32, src.dims)
+    correct, seen = [], 0
+    while seen < 80:
+        for x, y in batches:
+            net.load_batch(x, y.int())
+            net.forward(True)
+            net.backward()
+            stepper.step(0.02)
+            net.step_counter.add_(1)
+            correct.append(net.read_stats()[1])
+            assert torch.equal(net.params16, net.params.bfloat16())      # the optimizer keeps the compute copy fresh
+            assert float(net.grads.abs().sum()) == 0.0                   # ... and zeroes the gradients
+            seen += 1
+            if seen >= 80:
+                break
+    assert sum(correct[-10:]) == 320, correct[-10:]
