@@ -315,7 +315,7 @@ def _build_random(hw, c, layers):
     return _head(cfg, 6)
 
 
-@settings(max_examples=80, deadline=None, suppress_health_check=[HealthCheck.function_scoped_fixture,
+@settings(max_examples=80, deadline=None, derandomize=True, suppress_health_check=[HealthCheck.function_scoped_fixture,
                                                                  HealthCheck.too_slow, HealthCheck.filter_too_much])
 @given(_random_net())
 def test_random_networks_on_the_device_path(monkeypatch, spec):
