@@ -1139,6 +1139,11 @@ class SoftmaxKLLossOp(Op):
         """Returns (weighted loss sum, number correct, argmax)."""
         n = logits.shape[0]
         logits = logits.flatten(1).reshape(n * self.heads, self.k)
+        if self.cat_weights is not None and logits.requires_grad:
+            # per-category weights act on the gradient only (as in the kernel): delta[b, k] *= cw[k]
+            cw = self.cat_weights.to(logits.device).reshape(1, -1)
+            logits = logits * 1.0
+            logits.register_hook(lambda g: g * cw)
         if self._cpu_mask is not None:
             logits = logits.masked_fill(~self._cpu_mask, float("-inf"))
         labels = labels.long().reshape(-1)

@@ -215,8 +215,6 @@ def softmax_ce(logits, B, Kc, ld, labels, weights, w_scalar, delta, probs=None, 
                loss_per=None, argmax_out=None, cat_weights=None, mask=None, heads=1, soft=None):
     """`heads` blocks of Kc logits per sample; a negative label switches its head off; masked categories get
     probability zero; `soft` replaces the one-hot target. Accuracy and arg-max are those of the first head."""
-    if cat_weights is not None:
-        raise NotImplementedError("per-category gradient weights are not emulated")
     L = heads
     x = _rows(logits, B, ld)[:, : L * Kc].float().reshape(B * L, Kc)
     if mask is not None:
@@ -240,6 +238,8 @@ def softmax_ce(logits, B, Kc, ld, labels, weights, w_scalar, delta, probs=None, 
         d = (p - target) * w.view(-1, 1)
         if soft is None:
             d = d * live.view(-1, 1)
+        if cat_weights is not None:
+            d = d * cat_weights.reshape(1, Kc).float()         # per-category weights act on the gradient only
         dm = _rows(delta, B, ld)
         dm[:, : L * Kc] = d.reshape(B, L * Kc).to(delta.dtype)
         dm[:, L * Kc:] = 0

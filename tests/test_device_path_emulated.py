@@ -385,3 +385,32 @@ def test_lenet_trains_on_the_emulated_device_path(monkeypatch):
             if seen >= 80:
                 break
     assert sum(correct[-10:]) == 320, correct[-10:]
+
+
+def test_per_category_gradient_weights_on_both_paths(monkeypatch):
+    from rembrandt_b200.models.config import MarginalizedSoftmaxIndLossCfg
+
+    def make():
+        cfg = SequentialOperatorConfig().data3d(Data3dCfg((6, 6, 2), normalize=True))
+        cfg.conv2d(Conv2dCfg(3, 1, 1, 8, Act.RECT, K_), "conv1")
+        cfg.affine(AffineCfg(5, Act.IDENTITY, X_), "out")
+        return cfg.marginalized_softmax_ind_loss(MarginalizedSoftmaxIndLossCfg(5))
+
+    dev, ref = _pair(monkeypatch, make)
+    cw = torch.tensor([1.0, 0.0, 2.5, 0.5, 1.0])
+    torch.manual_seed(5)
+    x = torch.randint(0, 256, (4, 2, 6, 6), dtype=torch.uint8)
+    y = torch.tensor([0, 2, 3, 4])
+    plain = []
+    for weights in (None, cw):
+        for n in (dev, ref):
+            n.grads.zero_()
+            if weights is not None:
+                n.loss_op.set_category_weights(weights)
+            n.load_batch(x, y.int() if n is dev else y)
+            n.forward(True)
+            n.backward()
+            n.read_stats()
+        _grads_agree(dev, ref)
+        plain.append(ref.grads.clone())
+    assert not torch.allclose(plain[0], plain[1])      # the weights do change the gradient
