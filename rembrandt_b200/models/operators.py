@@ -298,6 +298,12 @@ class DataOp(Op):
             x = x[:, :, oy:oy + self.crop_h, ox:ox + self.crop_w]
         if train and self.flip and int(torch.randint(0, 2, (1,), generator=self.net.ref_generator)):
             x = x.flip(-1)
+        if train and self.pca is not None and c == 3 and self.pca.std > 0:
+            # lighting noise: per sample, shift[c] = sum_j alpha_j * eigenvalue_j * eigenvector[c][j], alpha ~ N(0, std)
+            al = torch.randn(x.shape[0], 3, generator=self.net.ref_generator) * self.pca.std
+            vals = torch.tensor(list(self.pca.eigenvalues), dtype=torch.float32)
+            vecs = torch.tensor(list(self.pca.eigenvectors), dtype=torch.float32).reshape(3, 3)
+            x = x + ((al * vals) @ vecs.t()).reshape(-1, 3, 1, 1)
         return x
 
 

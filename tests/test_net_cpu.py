@@ -358,3 +358,22 @@ def test_residual_convolution_and_scaled_logistic_reference_path():
     with pytest.raises(ValueError):
         Net(SequentialOperatorConfig().data3d(Data3dCfg((8, 8, 3))).res_conv2d(ResConv2dCfg(4), "bad")
             .softmax_kl_loss(SoftmaxKLLossCfg(4)), 2, device="cpu")
+
+
+def test_lighting_noise_on_the_reference_path():
+    from rembrandt_b200.models.config import Preproc
+    vecs = [0.5, 0.1, 0.0, 0.2, 0.7, 0.0, 0.1, 0.3, 1.0]
+    cfg = (SequentialOperatorConfig()
+           .data3d(Data3dCfg((6, 6, 3), normalize=True,
+                             preprocs=[Preproc("pca_noise", std=0.1, eigenvalues=[0.2, 0.02, 0.004], eigenvectors=vecs)]))
+           .affine(AffineCfg(4, Act.IDENTITY, ParamsInit.xavier()), "fc").softmax_kl_loss(SoftmaxKLLossCfg(4)))
+    net = Net(cfg, 3, device="cpu", seed=(1, 2))
+    x = torch.randint(0, 256, (3, 3, 6, 6), dtype=torch.uint8)
+    clean = net.input_op.ref_forward(x, False, 0)
+    noisy = net.input_op.ref_forward(x, True, 0)
+    shift = noisy - clean
+    # one shift per sample and channel, the same for every pixel; it lies in the span of the scaled eigenvectors
+    assert torch.allclose(shift, shift[:, :, :1, :1].expand_as(shift), atol=1e-6) and float(shift.abs().max()) > 0
+    basis = torch.tensor(vecs).reshape(3, 3) * torch.tensor([0.2, 0.02, 0.004])
+    alpha = torch.linalg.solve(basis, shift[:, :, 0, 0].t())
+    assert float(alpha.abs().max()) < 1.0                 # alphas of a N(0, 0.1) draw
