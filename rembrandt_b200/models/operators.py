@@ -288,16 +288,26 @@ class DataOp(Op):
         if p:
             x = F.pad(x, (p, p, p, p))
         hh, ww = x.shape[2], x.shape[3]
+        g = self.net.ref_generator
+        n = x.shape[0]
+        draws = 1 if self.cfg.per_batch_draws else n       # one offset / coin per batch (reference) or per sample
         if (hh, ww) != (self.crop_h, self.crop_w):
             if train:
-                g = self.net.ref_generator
-                oy = int(torch.randint(0, hh - self.crop_h + 1, (1,), generator=g))
-                ox = int(torch.randint(0, ww - self.crop_w + 1, (1,), generator=g))
+                oys = torch.randint(0, hh - self.crop_h + 1, (draws,), generator=g).tolist()
+                oxs = torch.randint(0, ww - self.crop_w + 1, (draws,), generator=g).tolist()
             else:
-                oy, ox = (hh - self.crop_h) // 2, (ww - self.crop_w) // 2
-            x = x[:, :, oy:oy + self.crop_h, ox:ox + self.crop_w]
-        if train and self.flip and int(torch.randint(0, 2, (1,), generator=self.net.ref_generator)):
-            x = x.flip(-1)
+                oys, oxs = [(hh - self.crop_h) // 2], [(ww - self.crop_w) // 2]
+            if len(oys) == 1:
+                x = x[:, :, oys[0]:oys[0] + self.crop_h, oxs[0]:oxs[0] + self.crop_w]
+            else:
+                x = torch.stack([x[i, :, oy:oy + self.crop_h, ox:ox + self.crop_w]
+                                 for i, (oy, ox) in enumerate(zip(oys, oxs))])
+        if train and self.flip:
+            coins = torch.randint(0, 2, (draws,), generator=g).bool()
+            if draws == 1:
+                x = x.flip(-1) if bool(coins[0]) else x
+            else:
+                x = torch.where(coins.reshape(n, 1, 1, 1), x.flip(-1), x)
         if train and self.pca is not None and c == 3 and self.pca.std > 0:
             # lighting noise: per sample, shift[c] = sum_j alpha_j * eigenvalue_j * eigenvector[c][j], alpha ~ N(0, std)
             al = torch.randn(x.shape[0], 3, generator=self.net.ref_generator) * self.pca.std

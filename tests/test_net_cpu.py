@@ -377,3 +377,23 @@ def test_lighting_noise_on_the_reference_path():
     basis = torch.tensor(vecs).reshape(3, 3) * torch.tensor([0.2, 0.02, 0.004])
     alpha = torch.linalg.solve(basis, shift[:, :, 0, 0].t())
     assert float(alpha.abs().max()) < 1.0                 # alphas of a N(0, 0.1) draw
+
+
+@pytest.mark.parametrize("per_batch", [True, False])
+def test_crop_and_flip_draws_per_batch_or_per_sample_on_the_reference_path(per_batch):
+    from rembrandt_b200.models.config import Preproc
+    pre = [Preproc("crop", crop_width=5, crop_height=5), Preproc("flip_x")]
+    cfg = (SequentialOperatorConfig().data3d(Data3dCfg((12, 12, 1), preprocs=pre, per_batch_draws=per_batch))
+           .affine(AffineCfg(4, Act.IDENTITY, ParamsInit.xavier()), "fc").softmax_kl_loss(SoftmaxKLLossCfg(4)))
+    net = Net(cfg, 16, device="cpu", seed=(1, 2))
+    # every pixel encodes its own position, so the crop window and the flip of each sample can be read back
+    img = (torch.arange(12).reshape(1, 12) + 12 * torch.arange(12).reshape(12, 1)).to(torch.uint8)
+    x = img.reshape(1, 1, 12, 12).repeat(16, 1, 1, 1)
+    out = net.input_op.ref_forward(x, True, 0)
+    assert out.shape == (16, 1, 5, 5)
+    corners = {(int(o[0, 0, 0]), int(o[0, 0, 4])) for o in out}
+    assert (len(corners) == 1) == per_batch, corners
+    for o in out:
+        row = o[0, 0].long() % 12
+        assert torch.equal(row, torch.arange(int(row[0]), int(row[0]) + 5)) or \
+            torch.equal(row, torch.arange(int(row[0]), int(row[0]) - 5, -1))
