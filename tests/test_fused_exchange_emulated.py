@@ -1,0 +1,292 @@
+"""Host side of the fused gradient exchange + optimizer step (`FusedAllreduceSgdComm`) with all ranks in one process.
+
+The three kernels are replaced by stand-ins that restate their contracts on CPU tensors -- push: rank r copies shard p
+of a bucket of its gradients into slot r of peer p's staging buffer and zeroes what it read; wait: nothing to do here;
+reduce: a rank sums its shard with the staged copies, applies 1/N and the optimizer rule to its shard of master and
+momentum, and stores the new bf16 weights into every rank. What is under test is everything the Python side decides:
+the bucket plan, shard bounds, staging offsets, one-shot buckets, which buffers each launch names, the launch order
+from the backward hooks. The result must equal a plain mean of the gradients followed by the optimizer step."""
+import ctypes as C
+import types
+
+import pytest
+import torch
+
+import kernel_emulation
+from rembrandt_b200.models import zoo
+from rembrandt_b200.models.net import Net
+from rembrandt_b200.optim.sgd import Momentum, reference_step
+from rembrandt_b200.optim.stepper import SgdStepper
+from rembrandt_b200.parallel import p2p
+from rembrandt_b200.parallel import p2p_kernels as PK
+
+
+class _Registry:
+    """Resolves raw addresses in an argument block back to the CPU tensors they point into."""
+
+    def __init__(self):
+        self.tensors = []
+
+    def add(self, t):
+        self.tensors.append(t)
+        return t
+
+    def view(self, ptr, dtype):
+        for t in self.tensors:
+            lo = t.data_ptr()
+            if t.dtype == dtype and lo <= ptr < lo + t.numel() * t.element_size():
+                return t.reshape(-1)[(ptr - lo) // t.element_size():]
+        raise KeyError(f"address {ptr:#x} belongs to no registered {dtype} tensor")
+
+
+class _Arena:
+    def __init__(self, shared, reg, rank, world):
+        self.shared, self.reg, self.rank, self.world = shared, reg, rank, world
+        self.group = None
+
+    def alloc(self, name, numel, dtype):
+        t = self.reg.add(torch.zeros(int(numel), dtype=dtype))
+        self.shared.setdefault(name, {})[self.rank] = t
+        return t
+
+    def ptrs(self, name):
+        return [self.shared[name][r].data_ptr() for r in range(self.world)]
+
+    def multicast_ptr(self, name):
+        return 0
+
+    def damaged(self):
+        return []
+
+
+class _Stream:
+    cuda_stream = 0
+
+    def wait_event(self, ev):
+        pass
+
+    def synchronize(self):
+        pass
+
+
+class _Event:
+    def record(self, stream=None):
+        pass
+
+    def wait(self, stream=None):
+        pass
+
+
+class _Ctx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def _shard_len(n, world):
+    per = (n + world - 1) // world
+    return (per + 7) // 8 * 8
+
+
+class World:
+    def __init__(self, monkeypatch, world, make_cfg, batch, mode, **comm_kw):
+        self.world, self.reg, self.shared, self.queue = world, _Registry(), {}, [[] for _ in range(world)]
+        self.current = 0
+        kernel_emulation.install(monkeypatch)
+        monkeypatch.setattr(Net, "device_path_on_cpu", True)
+        monkeypatch.setattr(torch.cuda, "Stream", lambda *a, **k: _Stream())
+        monkeypatch.setattr(torch.cuda, "Event", lambda *a, **k: _Event())
+        monkeypatch.setattr(torch.cuda, "stream", lambda s: _Ctx())
+        monkeypatch.setattr(torch.cuda, "current_stream", lambda *a: _Stream())
+        monkeypatch.setattr(PK, "fn", self._fn)
+        self.comms, self.nets, self.steppers = [], [], []
+        for r in range(world):
+            c = object.__new__(p2p.FusedAllreduceSgdComm)
+            c.rank, c.world, c.group, c.bytes_moved, c.step_size, c.iter = r, world, None, 0, 0.0, 0
+            c.arena = _Arena(self.shared, self.reg, r, world)
+            c.num_slots = 256
+            c.flags = c.arena.alloc("flags", 256 * 2 * PK.MAX_RANKS, torch.int32)
+            c.epochs = self.reg.add(torch.zeros(256, dtype=torch.int32))
+            c.counters = self.reg.add(torch.zeros(256, dtype=torch.int32))
+            c.status = self.reg.add(torch.zeros(1, dtype=torch.int32))
+            c.wait_ok = self.reg.add(torch.zeros(256, dtype=torch.int32))
+            c.bucket_elems = comm_kw.get("bucket_bytes", 64 << 10) // 4 // p2p.ALIGN * p2p.ALIGN
+            c.min_bucket_elems = comm_kw.get("min_bucket_bytes", 16 << 10) // 4
+            c.one_shot_elems = comm_kw.get("one_shot_bytes", 4 << 10) // 4
+            c.blocks, c.replicate_master, c.use_multimem = 8, comm_kw.get("replicate_master", False), False
+            c.overlap, c.split_wait = comm_kw.get("overlap", True), comm_kw.get("split_wait", True)
+            c.engine, c.launches, c._by_trigger, c._hyper, c.kernel_launches_per_step = None, [], {}, None, 0
+
+            def allocator(name, n, dtype, c=c):
+                if name in ("grads", "params16") or (name == "params" and c.replicate_master):
+                    return c.arena.alloc(name, n, dtype)
+                return self.reg.add(torch.zeros(n, dtype=dtype))
+            net = Net(make_cfg(), batch, device="cpu", seed=(5, 6), flat_allocator=allocator)
+            c.attach(types.SimpleNamespace(net=net))
+            self.comms.append(c)
+            self.nets.append(net)
+            self.steppers.append(SgdStepper(net, mode, 0.9, 1e-3))
+        monkeypatch.setattr(Net, "device_path_on_cpu", False)
+
+    # ---- kernel stand-ins: queue now, run when every rank has issued its launches
+    def _fn(self, name):
+        def launch(ref, *rest):
+            self.queue[self.current].append((name, PK.ArSgdArgs.from_buffer_copy(ref._obj)))
+            return 0
+        return launch
+
+    def _f32(self, ptr):
+        return self.reg.view(ptr, torch.float32)
+
+    def _push(self, a):
+        r, n, W = a.rank, a.n, a.world
+        per = n if a.one_shot else _shard_len(n, W)
+        g = self._f32(a.grads[r])[a.off:]
+        for p in range(W):
+            if p == r:
+                continue
+            si = 0 if a.one_shot else p * per
+            ln = min(per, n - si)
+            if ln <= 0:
+                continue
+            self._f32(a.stage[p])[a.stage_off + r * per: a.stage_off + r * per + ln] = g[si: si + ln]
+            if a.zero_grads and not a.one_shot:
+                g[si: si + ln] = 0
+
+    def _reduce(self, a):
+        r, n, W = a.rank, a.n, a.world
+        per = n if a.one_shot else _shard_len(n, W)
+        s0 = 0 if a.one_shot else min(n, r * per)
+        s1 = n if a.one_shot else min(n, s0 + per)
+        if s1 <= s0:
+            return
+        grads = self._f32(a.grads[r])
+        g = grads[a.off + s0: a.off + s1].clone()
+        stage = self._f32(a.stage[r])[a.stage_off:]
+        for k in range(1, W):
+            peer = (r + k) % W
+            g += stage[peer * per: peer * per + (s1 - s0)]
+        lo, hi = a.off + s0, a.off + s1
+        if a.op == 1:
+            for p in range(W):
+                self._f32(a.grads[p])[lo:hi] = g * a.avg_scale
+            return
+        if a.zero_grads:
+            grads[lo:hi] = 0
+        w, v = self._f32(a.w), self._f32(a.v)
+        cut = min(max(a.decay_len, lo), hi)
+        for x0, x1, l2 in ((lo, cut, a.h.l2), (cut, hi, 0.0)):
+            if x1 > x0:
+                reference_step(w[x0:x1], g[x0 - lo: x1 - lo], v[x0:x1], a.h.lr, a.h.mu, l2, a.h.grad_scale, a.h.mode,
+                               a.h.phase)
+        targets = [r] if a.one_shot else range(W)
+        for p in targets:
+            self.reg.view(a.w16[p], torch.bfloat16)[lo:hi] = w[lo:hi].bfloat16()
+        if not a.one_shot and a.w32[0]:
+            for p in range(W):
+                if p != r:
+                    self._f32(a.w32[p])[lo:hi] = w[lo:hi]
+
+    def run_queued(self):
+        per_rank = []
+        for q in self.queue:
+            groups, cur = [], None
+            for name, a in q:          # one group per bucket: [push] [wait] reduce
+                if cur is None:
+                    cur = {}
+                cur[name] = a
+                if name == "rb_allreduce_sgd_p2p":
+                    groups.append(cur)
+                    cur = None
+            assert cur is None, "a bucket's launches must end with the reducing kernel"
+            per_rank.append(groups)
+        assert len({len(g) for g in per_rank}) == 1
+        for k in range(len(per_rank[0])):
+            slots = {per_rank[r][k]["rb_allreduce_sgd_p2p"].slot for r in range(self.world)}
+            assert len(slots) == 1, "ranks must exchange the same bucket at the same position of their streams"
+            for r in range(self.world):
+                if "rb_allreduce_push_p2p" in per_rank[r][k]:
+                    self._push(per_rank[r][k]["rb_allreduce_push_p2p"])
+            for r in range(self.world):
+                self._reduce(per_rank[r][k]["rb_allreduce_sgd_p2p"])
+        self.queue = [[] for _ in range(self.world)]
+        return len(per_rank[0])
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+@pytest.mark.parametrize("mode", [Momentum.UPDATE, Momentum.UPDATE_NESTEROV, Momentum.GRADIENT])
+@pytest.mark.parametrize("overlap", [True, False])
+def test_bucketed_push_exchange_equals_mean_gradient_then_step(monkeypatch, world, mode, overlap):
+    W = World(monkeypatch, world, lambda: zoo.cifar_krizh26(augment=False), 4, mode, overlap=overlap,
+              min_bucket_bytes=1 << 10, one_shot_bytes=16 << 10)
+    net0 = W.nets[0]
+    n = net0.flat_len
+    assert len(W.comms[0].launches) >= 4
+    assert any(rec[2] <= W.comms[0].one_shot_elems for rec in W.comms[0].launches), "no one-shot bucket in the plan"
+    expect_w = net0.params.clone()
+    expect_v = torch.zeros(n)
+    lr = 0.05
+    for step in range(3):
+        gs = []
+        for r in range(world):
+            g = torch.Generator().manual_seed(100 * step + r)
+            grad = torch.randn(n, generator=g)
+            W.nets[r].grads.copy_(grad)
+            gs.append(grad)
+        for r in range(world):
+            W.current = r
+            c, net = W.comms[r], W.nets[r]
+            c.prepare(W.steppers[r], lr)
+            for i in range(len(net.ops) - 2, 0, -1):       # the hooks backward would call
+                c.on_op_backward(i)
+            c.fused_grads_step(W.steppers[r], lr)
+        buckets = W.run_queued()
+        assert buckets == len(W.comms[0].launches)
+        mean = sum(gs) / world
+        d = net0.decay_len
+        reference_step(expect_w[:d], mean[:d].clone(), expect_v[:d], lr, 0.9, 1e-3, 1.0, int(mode), 3)
+        reference_step(expect_w[d:], mean[d:].clone(), expect_v[d:], lr, 0.9, 0.0, 1.0, int(mode), 3)
+        for r in range(world):
+            net, c = W.nets[r], W.comms[r]
+            assert float(net.grads.abs().sum()) == 0.0, "gradients must be zero after the exchange"
+            # 1/N times a sum in the kernel's order against a mean formed here: the fp32 values differ in the last
+            # bit, which now and then lands on the other side of a bf16 rounding boundary
+            got, want = net.params16.float(), expect_w.bfloat16().float()
+            off_by = (got - want).abs()
+            assert float((off_by > want.abs() * 2.0 ** -6 + 1e-6).sum()) == 0, f"step {step}, rank {r}: bf16 weights"
+            assert float((off_by > 0).float().mean()) < 1e-2, f"step {step}, rank {r}: too many rounding differences"
+            # the fp32 master is sharded: a rank owns shard r of every large bucket and all of the one-shot ones
+            for _, off, ln, _slot in c.launches:
+                if ln <= c.one_shot_elems:
+                    lo, hi = off, off + ln
+                else:
+                    s0, s1 = c.shard_bounds(ln)[r]
+                    lo, hi = off + s0, off + s1
+                assert torch.allclose(net.params[lo:hi], expect_w[lo:hi], atol=1e-6)
+                assert torch.allclose(net.mom[lo:hi], expect_v[lo:hi], atol=1e-6)
+    # every parameter is covered by exactly one bucket, and every bucket's shards tile it
+    covered = torch.zeros(n, dtype=torch.int32)
+    for _, off, ln, _slot in W.comms[0].launches:
+        covered[off: off + ln] += 1
+        bounds = W.comms[0].shard_bounds(ln)
+        assert bounds[0][0] == 0 and bounds[-1][1] == ln and all(a[1] == b[0] for a, b in zip(bounds, bounds[1:]))
+    live = sum(((s.numel + p2p.ALIGN - 1) // p2p.ALIGN * p2p.ALIGN) for s in net0.segs)
+    assert int(covered.sum()) == live and int(covered.max()) == 1
+
+
+def test_in_place_average_of_the_gradient_buffer(monkeypatch):
+    W = World(monkeypatch, 4, lambda: zoo.cifar_krizh26(augment=False), 4, Momentum.UPDATE)
+    n = W.nets[0].flat_len
+    gs = [torch.randn(n, generator=torch.Generator().manual_seed(r)) for r in range(4)]
+    for r in range(4):
+        W.nets[r].grads.copy_(gs[r])
+    for r in range(4):
+        W.current = r
+        W.comms[r].allreduce_average(W.nets[r].grads)
+    W.run_queued()
+    mean = sum(gs) / 4
+    total = n // 8 * 8
+    for r in range(4):
+        assert torch.allclose(W.nets[r].grads[:total], mean[:total], atol=1e-6)
