@@ -290,3 +290,26 @@ def test_in_place_average_of_the_gradient_buffer(monkeypatch):
     total = n // 8 * 8
     for r in range(4):
         assert torch.allclose(W.nets[r].grads[:total], mean[:total], atol=1e-6)
+
+
+def test_replicated_master_keeps_full_fp32_weights_on_every_rank(monkeypatch):
+    W = World(monkeypatch, 3, lambda: zoo.cifar_krizh26(augment=False), 4, Momentum.UPDATE, replicate_master=True,
+              split_wait=False, min_bucket_bytes=1 << 10, one_shot_bytes=16 << 10)
+    n = W.nets[0].flat_len
+    expect_w, expect_v = W.nets[0].params.clone(), torch.zeros(n)
+    gs = [torch.randn(n, generator=torch.Generator().manual_seed(7 + r)) for r in range(3)]
+    for r in range(3):
+        W.nets[r].grads.copy_(gs[r])
+        W.current = r
+        W.comms[r].prepare(W.steppers[r], 0.1)
+        for i in range(len(W.nets[r].ops) - 2, 0, -1):
+            W.comms[r].on_op_backward(i)
+        W.comms[r].fused_grads_step(W.steppers[r], 0.1)
+    assert all(name != "rb_allreduce_wait_p2p" for q in W.queue for name, _ in q)     # the reducing kernel waits itself
+    W.run_queued()
+    d = W.nets[0].decay_len
+    mean = sum(gs) / 3
+    reference_step(expect_w[:d], mean[:d].clone(), expect_v[:d], 0.1, 0.9, 1e-3, 1.0, 1, 3)
+    reference_step(expect_w[d:], mean[d:].clone(), expect_v[d:], 0.1, 0.9, 0.0, 1.0, 1, 3)
+    for r in range(3):
+        assert torch.allclose(W.nets[r].params, expect_w, atol=1e-6), f"rank {r}: master not replicated"
