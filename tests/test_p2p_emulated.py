@@ -132,3 +132,71 @@ def test_trace_spans_are_inert_without_cuda(monkeypatch):
     with trace.span("forward"):             # no CUDA here: still nothing to push
         pass
     assert trace.span("a") is trace.span("b")
+
+
+def _make_flat(rank, world, mode, seed, fake, rounds=1, alpha=0.5):
+    from rembrandt_b200.parallel.comm import GossipConfig
+    c = object.__new__(p2p.GossipP2PComm)
+    c.rank, c.world, c.group, c.bytes_moved = rank, world, None, 0
+    c.mode, c.alpha, c.blocks, c.cfg = mode, alpha, 8, GossipConfig(num_rounds=rounds)
+    c.synchronous = True
+    c.rng = XorShift128Plus(seed[0] + (0 if mode == "pair" else 1000003 * rank), seed[1])
+    c._last_peer = None
+    c.net = types.SimpleNamespace(params=fake.w[rank], params16=torch.zeros(1))
+    c.pub = torch.zeros(1)
+    c.epochs = torch.zeros(4, dtype=torch.int32)
+    c.counters = torch.zeros(4, dtype=torch.int32)
+    c.status = torch.zeros(1, dtype=torch.int32)
+    c.arena = types.SimpleNamespace(ptrs=lambda name: [0] * world)
+    return c
+
+
+@pytest.mark.parametrize("world", [2, 5, 8])
+def test_pair_gossip_launches_follow_the_shared_permutation(monkeypatch, world):
+    n = 12
+    fake = FakeWorld(world, n)
+    monkeypatch.setattr(PK, "fn", fake.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    comms = [_make_flat(r, world, "pair", (17, 29), fake, alpha=0.25) for r in range(world)]
+    shadow = XorShift128Plus(17, 29)
+    for rnd in range(4):
+        torch.manual_seed(10 + rnd)
+        start = [torch.randn(n) for _ in range(world)]
+        for r in range(world):
+            fake.w[r] = start[r].clone()
+            comms[r].net.params = fake.w[r]
+            fake.current = r
+            comms[r].sync_params(fake.w[r])
+        fake.run()
+        perm = shadow.permutation(world)
+        for r in range(world):
+            src = perm.index(r)                      # the rank whose target r is
+            want = start[r] if src == r else 0.75 * start[r] + 0.25 * start[src]
+            assert torch.allclose(fake.w[r], want, atol=1e-6), (rnd, r)
+
+
+@pytest.mark.parametrize("rounds", [1, 3])
+def test_pull_gossip_launches_average_own_vector_and_drawn_snapshots(monkeypatch, rounds):
+    world, n = 6, 12
+    fake = FakeWorld(world, n)
+    monkeypatch.setattr(PK, "fn", fake.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    comms = [_make_flat(r, world, "pull", (31, 37), fake, rounds=rounds) for r in range(world)]
+    for rnd in range(3):
+        torch.manual_seed(20 + rnd)
+        start = [torch.randn(n) for _ in range(world)]
+        for r in range(world):
+            fake.w[r] = start[r].clone()
+            comms[r].net.params = fake.w[r]
+            fake.current = r
+            comms[r].sync_params(fake.w[r])
+        fake.run()
+        for r in range(world):
+            peers = comms[r]._last_peer
+            assert len(peers) == rounds
+            want = (start[r] + sum(start[p] for p in peers)) / (rounds + 1)
+            assert torch.allclose(fake.w[r], want, atol=1e-6), (rnd, r, peers)
+    again = comms[0]._last_peer
+    fake.current = 0
+    comms[0].sync_params(fake.w[0], repeat=True)      # `repeat` reuses the drawn peers (parameters, then gradients)
+    assert comms[0]._last_peer == again
