@@ -41,7 +41,11 @@ def base_parser(desc, **defaults):
     ap.add_argument("--save-iters", type=int, default=0)
     ap.add_argument("--valid-iters", type=int, default=defaults.get("valid_iters", 0))
     ap.add_argument("--checkpoint-dir", default=None)
-    ap.add_argument("--comm", default=defaults.get("comm", "auto"))
+    ap.add_argument("--comm", default=defaults.get("comm", "auto"),
+                    help="exchange backend: auto (fused_allreduce_sgd on GPUs, allreduce on CPU ranks) | kernel backends "
+                         "fused_allreduce_sgd, gossip_p2p, gossip_pull_p2p, gossip_push_p2p, group_allreduce_gossip_p2p, "
+                         "elastic_p2p | library backends allreduce, gossip_pair, gossip_pull, gossip_push, "
+                         "group_allreduce_gossip, elastic | null")
     ap.add_argument("--sync-order", choices=sorted(ORDERS), default=None)
     ap.add_argument("--comm-interval", type=int, default=1)
     ap.add_argument("--data", default=None, help=".data descriptor; synthetic data when absent")
