@@ -53,3 +53,19 @@ def test_training_from_a_caffe_database_through_the_native_loader(tmp_path):
     (tmp_path / "c.data").write_text(f'[dataset.train]\nsource = "lmdb_caffe"\ndata_path = "{tmp_path / "db"}"\n')
     sgd = train_cifar10.main(TINY + ["--data", str(tmp_path / "c.data"), "--native-loader", "2"])
     assert sgd.engine.iter == 3
+
+
+@pytest.mark.parametrize("comm", ["allreduce", "gossip_pair", "elastic"])
+def test_distributed_tool_on_two_cpu_ranks(comm):
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "rembrandt_b200.cli.dist_train_mnist", *TINY, "--model", "fc1",
+           "--comm", comm, "--iters", "4", "--display-iters", "2", "--valid-iters", "0"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    assert "iter 4 " in r.stderr
