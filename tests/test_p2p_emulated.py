@@ -200,3 +200,159 @@ def test_pull_gossip_launches_average_own_vector_and_drawn_snapshots(monkeypatch
     fake.current = 0
     comms[0].sync_params(fake.w[0], repeat=True)      # `repeat` reuses the drawn peers (parameters, then gradients)
     assert comms[0]._last_peer == again
+
+
+# ---- push gossip and elastic averaging: launches separated by barrier kernels, buffers named by raw addresses ------
+class PtrWorld:
+    """All ranks in one process. Launches are queued per rank and run stage by stage, a stage ending at each barrier
+    launch; addresses in the argument blocks are resolved back to the CPU tensors registered here."""
+
+    def __init__(self, world, n):
+        self.world, self.n = world, n
+        self.tensors, self.shared = [], {}
+        self.queue = [[] for _ in range(world)]
+        self.current = 0
+
+    def reg(self, t):
+        self.tensors.append(t)
+        return t
+
+    def view(self, ptr):
+        for t in self.tensors:
+            lo = t.data_ptr()
+            if lo <= ptr < lo + t.numel() * 4:
+                return t.reshape(-1)[(ptr - lo) // 4:]
+        raise KeyError(hex(ptr))
+
+    def arena(self, rank):
+        def alloc(name, numel, dtype):
+            t = self.reg(torch.zeros(int(numel), dtype=dtype))
+            self.shared.setdefault(name, {})[rank] = t
+            return t
+        return types.SimpleNamespace(alloc=alloc, ptrs=lambda name: [self.shared[name][r].data_ptr()
+                                                                     for r in range(self.world)])
+
+    def fn(self, name):
+        def launch(*args):
+            a = args[0]
+            if hasattr(a, "_obj"):
+                a = type(a._obj).from_buffer_copy(a._obj)
+            self.queue[self.current].append((name, a, args[1:]))
+            return 0
+        return launch
+
+    def run(self):
+        stages = []
+        for q in self.queue:
+            mine, cur = [], []
+            for item in q:
+                if item[0] == "rb_barrier_p2p":
+                    mine.append(cur)
+                    cur = []
+                else:
+                    cur.append(item)
+            assert not cur, "every exchange must end with a barrier"
+            stages.append(mine)
+        assert len({len(s) for s in stages}) == 1
+        for k in range(len(stages[0])):
+            for r in range(self.world):
+                for name, a, rest in stages[r][k]:
+                    getattr(self, "_" + name)(a, rest)
+        self.queue = [[] for _ in range(self.world)]
+
+    def _rb_push_add_p2p(self, a, rest):
+        if a.peer != a.rank:
+            self.view(a.acc_target)[: a.n] += self.view(a.w)[: a.n]
+            self.view(a.count_target)[0] += 1.0
+
+    def _rb_push_finalize(self, a, rest):
+        cnt = float(self.view(a.count_target)[0])
+        if cnt > 0:
+            w, acc = self.view(a.w)[: a.n], self.view(a.acc_target)[: a.n]
+            w.copy_((a.w_self * w + acc) / (a.w_self + cnt))
+            acc.zero_()
+        self.view(a.count_target)[0] = 0.0
+
+    def _rb_elastic_pull_p2p(self, a, rest):
+        w, c = self.view(a.w)[: a.n], self.view(a.pub_peer)[: a.n]
+        d = a.alpha * (w - c)
+        w.sub_(d)
+        self.view(a.acc_target)[: a.n] += d
+
+    def _rb_elastic_apply(self, center_ptr, rest):
+        delta_ptr, n = rest[0], rest[1]
+        c, d = self.view(center_ptr)[:n], self.view(delta_ptr)[:n]
+        c.add_(d)
+        d.zero_()
+
+
+def _bare(cls, pw, rank, world):
+    c = object.__new__(cls)
+    c.rank, c.world, c.group, c.bytes_moved, c.blocks = rank, world, None, 0, 8
+    c.arena = pw.arena(rank)
+    c.flags = c.arena.alloc("flags", 64, torch.int32)
+    c.epochs = torch.zeros(8, dtype=torch.int32)
+    c.counters = torch.zeros(8, dtype=torch.int32)
+    c.status = torch.zeros(1, dtype=torch.int32)
+    w = pw.reg(torch.zeros(pw.n))
+    c.net = types.SimpleNamespace(params=w, params16=torch.zeros(1), flat_len=pw.n)
+    return c, w
+
+
+def test_push_gossip_launches_give_the_count_normalised_mean(monkeypatch):
+    world, n = 5, 16
+    pw = PtrWorld(world, n)
+    monkeypatch.setattr(PK, "fn", pw.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    comms, ws = [], []
+    for r in range(world):
+        c, w = _bare(p2p.PushGossipP2PComm, pw, r, world)
+        c.rng = XorShift128Plus(41 + 7919 * r, 43)
+        c.attach(types.SimpleNamespace(net=c.net))
+        comms.append(c)
+        ws.append(w)
+    shadows = [XorShift128Plus(41 + 7919 * r, 43) for r in range(world)]
+    for rnd in range(4):
+        torch.manual_seed(30 + rnd)
+        start = [torch.randn(n) for _ in range(world)]
+        targets = [s.below(world) for s in shadows]
+        for r in range(world):
+            ws[r].copy_(start[r])
+            pw.current = r
+            comms[r].sync_params(ws[r])
+        pw.run()
+        for r in range(world):
+            received = [start[s] for s in range(world) if targets[s] == r and s != r]
+            w_self = 2.0 if targets[r] == r else 1.0
+            want = (w_self * start[r] + sum(received)) / (w_self + len(received)) if received else start[r]
+            assert torch.allclose(ws[r], want, atol=1e-6), (rnd, r, targets)
+            assert float(comms[r].acc.abs().sum()) == 0.0 and float(comms[r].count[0]) == 0.0
+
+
+def test_elastic_averaging_launches_move_clients_and_centre_toward_each_other(monkeypatch):
+    world, n, beta = 4, 16, 0.2
+    pw = PtrWorld(world, n)
+    monkeypatch.setattr(PK, "fn", pw.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    comms, ws = [], []
+    for r in range(world):
+        c, w = _bare(p2p.ElasticP2PComm, pw, r, world)
+        c.beta = beta
+        c.attach(types.SimpleNamespace(net=c.net))
+        comms.append(c)
+        ws.append(w)
+    torch.manual_seed(40)
+    centre = torch.randn(n)
+    comms[0].center.copy_(centre)
+    for rnd in range(3):
+        start = [torch.randn(n) for _ in range(world)]
+        for r in range(world):
+            ws[r].copy_(start[r])
+            pw.current = r
+            comms[r].sync_params(ws[r])
+        pw.run()
+        for r in range(world):      # every client mixes with the same centre snapshot
+            assert torch.allclose(ws[r], start[r] - beta * (start[r] - centre), atol=1e-6), (rnd, r)
+        centre = centre + sum(beta * (start[r] - centre) for r in range(world))
+        assert torch.allclose(comms[0].center, centre, atol=1e-5)
+        assert float(comms[0].delta.abs().sum()) == 0.0
