@@ -6,6 +6,10 @@ dump-array3d-header.rs, load-array3d.rs, test-lmdb.rs, test-varraydb.rs):
     python -m rembrandt_b200.cli.data_tools load-array    <file.ndarray> [--dtype f32|u8]
     python -m rembrandt_b200.cli.data_tools test-lmdb     <env dir or data.mdb> [--limit N]
     python -m rembrandt_b200.cli.data_tools test-recorddb <prefix> [--limit N]
+    python -m rembrandt_b200.cli.data_tools make-lmdb     <data_batch.bin> <out dir> [--limit N]
+
+`make-lmdb` writes the images of a CIFAR-10 binary file as a Caffe image database (keys "%08d", values raw `Datum`
+messages), which is what the `lmdb_caffe` source and the native database loader read.
 """
 import argparse
 import json
@@ -71,6 +75,23 @@ def test_recorddb(args):
         print(json.dumps({"record": i, "bytes": len(db[i])}))
 
 
+def make_lmdb(args):
+    import os
+    from ..data.codecs import encode_caffe_datum
+    from ..data.datasets import Cifar10DataSource
+    from ..data.lmdb_reader import write_env
+    src = Cifar10DataSource(args.data)
+    n = len(src) if not args.limit else min(args.limit, len(src))
+    items = []
+    for i in range(n):
+        img, label = src[i]
+        c, h, w = img.shape
+        items.append((b"%08d" % i, encode_caffe_datum(np.ascontiguousarray(img).tobytes(), c, h, w, int(label))))
+    os.makedirs(args.out, exist_ok=True)
+    write_env(args.out, items)
+    print(json.dumps({"records": n, "out": args.out}))
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -81,6 +102,8 @@ def main(argv=None):
     p.set_defaults(fn=test_lmdb)
     p = sub.add_parser("test-recorddb"); p.add_argument("prefix"); p.add_argument("--limit", type=int, default=5)
     p.set_defaults(fn=test_recorddb)
+    p = sub.add_parser("make-lmdb"); p.add_argument("data"); p.add_argument("out")
+    p.add_argument("--limit", type=int, default=0); p.set_defaults(fn=make_lmdb)
     args = ap.parse_args(argv)
     args.fn(args)
     return 0

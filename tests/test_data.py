@@ -352,3 +352,25 @@ def test_native_loader_over_a_caffe_database(tmp_path):
         NativeBatchLoader.from_caffe_lmdb(str(tmp_path), (3, 5, 5), batch=2, pin=False)
     with pytest.raises(RuntimeError, match="cannot open"):
         NativeBatchLoader.from_caffe_lmdb(str(tmp_path / "missing"), (3, 5, 4), batch=2, pin=False)
+
+
+def test_make_lmdb_tool_round_trips_a_cifar_file(tmp_path, capsys):
+    import json
+    from rembrandt_b200.cli import data_tools
+    from rembrandt_b200.data.lmdb_reader import LmdbCaffeShard
+    from rembrandt_b200.data.native_loader import NativeBatchLoader
+    rng = np.random.default_rng(6)
+    recs = rng.integers(0, 256, (9, 3073), dtype=np.uint8)
+    recs[:, 0] %= 10
+    (tmp_path / "batch.bin").write_bytes(recs.tobytes())
+    data_tools.main(["make-lmdb", str(tmp_path / "batch.bin"), str(tmp_path / "db")])
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["records"] == 9
+    got = list(LmdbCaffeShard(str(tmp_path / "db")))
+    assert len(got) == 9
+    for i, (img, label) in enumerate(got):
+        assert label == int(recs[i, 0]) and np.array_equal(img.reshape(-1), recs[i, 1:])
+    ld = NativeBatchLoader.from_caffe_lmdb(str(tmp_path / "db"), (3, 32, 32), batch=3, mode="cyclic", pin=False,
+                                           max_batches=3)
+    labels = [int(v) for _, y in ld for v in y]
+    ld.close()
+    assert labels == [int(v) for v in recs[:, 0]]
