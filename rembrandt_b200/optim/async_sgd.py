@@ -44,6 +44,7 @@ class AsyncSgdOpt(SgdOpt):
         cfg, eng, net = self.cfg, self.engine, self.net
         eng.flush()
         eng.synchronize()
+        self._check_device_status(t)
         if cfg.checkpoint == CheckpointBehavior.DISCARD:
             net.save_params()
         if cfg.checkpoint_dir:
