@@ -382,6 +382,27 @@ def bn_bwd(x, dy, y_relu, rows, C, c_valid, sums, mean, istd, gamma, dgamma, dbe
     dm[:, c_valid:] = 0
 
 
+def var_input_u8(src, shapes, dst, draws, in_stride, N, C, crop_h, crop_w, Cp, f, ep, OH, OW, scale_lower, scale_upper,
+                 train, random_flip, per_batch, scale, mean, pca_sigma, pca_vals, pca_vecs, seed, step, step_ptr=None):
+    """Inference form only (shorter side rescaled to `scale_lower`, centred crop, no flip), plain NHWC output; the
+    rescale itself is the operator's own one-sample restatement, which the kernel is compared with on a GPU."""
+    from rembrandt_b200.models.operators import VarDataOp
+    if train or f != 1 or ep != 0:
+        raise NotImplementedError("only the inference form with plain NHWC output is emulated")
+    out = torch.zeros(N, OH, OW, Cp)
+    mu = torch.tensor(list(mean), dtype=torch.float32).reshape(-1, 1, 1)
+    for i in range(N):
+        w, h = int(shapes[i, 0]), int(shapes[i, 1])
+        im = src.reshape(N, in_stride)[i, : C * h * w].view(C, h, w)
+        rw, rh = VarDataOp.scaled_dims(w, h, scale_lower)
+        ox, oy = (rw - crop_w) // 2, (rh - crop_h) // 2
+        v = VarDataOp.ref_sample(im, scale_lower, ox, oy, False, crop_w, crop_h)
+        X, Y = ox + torch.arange(crop_w), oy + torch.arange(crop_h)
+        inside = ((Y >= 0) & (Y < rh))[:, None] & ((X >= 0) & (X < rw))[None, :]
+        out[i, :, :, :C] = ((v * scale - mu) * inside).permute(1, 2, 0)
+    dst.reshape(-1)[: N * OH * OW * Cp].view(N, OH, OW, Cp).copy_(out.to(dst.dtype))
+
+
 def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
     reference_step(w[:n], g[:n], v[:n], lr, mu, l2, grad_scale, mode, phase)
     if w16 is not None:
@@ -398,7 +419,7 @@ EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fw
                                     conv_direct_dgrad, pack_dgrad_filters, zero_s2d_structural, gemm_tc, bias_act,
                                     colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
                                     softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd,
-                                    pointwise_loss, lrn_fwd, lrn_bwd, dropout)}
+                                    pointwise_loss, lrn_fwd, lrn_bwd, dropout, var_input_u8)}
 
 
 def install(monkeypatch):

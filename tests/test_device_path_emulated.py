@@ -414,3 +414,26 @@ def test_per_category_gradient_weights_on_both_paths(monkeypatch):
         _grads_agree(dev, ref)
         plain.append(ref.grads.clone())
     assert not torch.allclose(plain[0], plain[1])      # the weights do change the gradient
+
+
+def test_variable_size_input_on_the_device_path(monkeypatch):
+    """Packing of ragged images, the size table and the arguments of the variable-size input launch (inference form)."""
+    from test_var_input import _batch, _var_cfg
+    dev, ref = _pair(monkeypatch, lambda: _var_cfg(32, 36, 48, flip=False))
+    imgs = _batch(4)
+    labels = torch.tensor([1, 2, 3, 4])
+    dev.load_batch(imgs, labels.int())
+    ref.load_batch(imgs, labels)
+    dev.forward(False)
+    ref.forward(False)
+    dl, rl = dev.read_stats()[0], ref.read_stats()[0]
+    assert abs(dl - rl) < 2e-2 * max(1.0, abs(rl)), (dl, rl)
+    want = ref.input_op.ref_forward(imgs, False, 0)                       # [N, C, 32, 32]
+    got = dev.input_op.out[..., :3].permute(0, 3, 1, 2).float()
+    assert torch.allclose(got, want, atol=1e-2)
+    assert float(dev.input_op.out[..., 3:].abs().sum()) == 0.0
+    # the packed form gives the same result
+    from rembrandt_b200.models.operators import VarDataOp
+    dev.load_batch(VarDataOp.pack(imgs, dev.input_op.in_stride), labels.int())
+    dev.forward(False)
+    assert abs(dev.read_stats()[0] - dl) < 1e-6
