@@ -1,0 +1,108 @@
+"""The CUDA branch of `StepEngine` (double-buffered staging, lagged statistics, gradient accumulation, the update in
+the configured order) on CPU tensors: streams and events are replaced by inert stand-ins, the kernel fronts by the
+plain-torch ones of tests/kernel_emulation.py. The result is compared with the CPU branch of the same engine."""
+import pytest
+import torch
+
+import kernel_emulation
+from rembrandt_b200.engine import StepEngine
+from rembrandt_b200.models import zoo
+from rembrandt_b200.models.net import Net
+from rembrandt_b200.optim.sgd import Momentum, SgdOptConfig, StepSizeSchedule
+from rembrandt_b200.trainer import SgdOpt
+
+
+class _Stream:
+    cuda_stream = 0
+
+    def wait_event(self, ev):
+        pass
+
+    def synchronize(self):
+        pass
+
+
+class _Event:
+    def __init__(self, *a, **k):
+        pass
+
+    def record(self, stream=None):
+        pass
+
+    def synchronize(self):
+        pass
+
+    def elapsed_time(self, other):
+        return 1.0
+
+
+class _Ctx:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def _device_engine(monkeypatch, cfg_fn, batch, opt):
+    kernel_emulation.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "Stream", lambda *a, **k: _Stream())
+    monkeypatch.setattr(torch.cuda, "Event", _Event)
+    monkeypatch.setattr(torch.cuda, "stream", lambda s: _Ctx())
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a: _Stream())
+    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda self, *a, **k: self)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    net = Net(cfg_fn(), batch, device="cpu", seed=(2, 3), minibatch_size=opt.minibatch_size)
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    return StepEngine(net, opt, use_graph=False), net
+
+
+def _batches(n, batch):
+    g = torch.Generator().manual_seed(11)
+    return [(torch.randint(0, 256, (batch, 1, 28, 28), dtype=torch.uint8, generator=g),
+             torch.randint(0, 10, (batch,), dtype=torch.int32, generator=g)) for _ in range(n)]
+
+
+@pytest.mark.parametrize("accum", [1, 2])
+@pytest.mark.parametrize("mode", [Momentum.UPDATE, Momentum.UPDATE_NESTEROV])
+def test_device_branch_of_the_engine_matches_the_cpu_branch(monkeypatch, accum, mode):
+    batch = 8
+    opt = SgdOptConfig(minibatch_size=batch * accum, step_size=StepSizeSchedule.constant(0.01), momentum=mode, mu=0.9,
+                       l2_reg_coef=1e-3, display_iters=0)
+    cpu_net = Net(zoo.lenet(pad=2), batch, device="cpu", seed=(2, 3), minibatch_size=batch * accum)
+    cpu_eng = StepEngine(cpu_net, opt)
+    dev_eng, dev_net = _device_engine(monkeypatch, lambda: zoo.lenet(pad=2), batch, opt)
+    assert dev_eng.is_cuda and dev_eng.accum == accum
+    with torch.no_grad():                      # both start from the bf16-rounded weights
+        cpu_net.params.copy_(dev_net.params16.float())
+        dev_net.params.copy_(dev_net.params16.float())
+    data = _batches(6, batch)
+    dev_stats, cpu_stats = [], []
+    for x, y in data:
+        dev_eng.feed(x, y)
+        s = dev_eng.step()
+        if s is not None:
+            dev_stats.append(s)
+        cpu_eng.feed(x, y)
+        cpu_stats.append(cpu_eng.step())
+    dev_stats.append(dev_eng.flush())
+    assert dev_eng.iter == cpu_eng.iter == 6 // accum and dev_net.t == 6
+    # statistics arrive one step late on the device branch, and are the same numbers
+    assert len(dev_stats) == len(cpu_stats) == 6
+    for (dl, dc), (cl, cc) in zip(dev_stats, cpu_stats):
+        assert abs(dl - cl) < 3e-2 * max(1.0, abs(cl)), (dl, cl)
+    rel = float((dev_net.params - cpu_net.params.detach()).norm() / cpu_net.params.detach().norm())
+    assert rel < 6e-2, rel     # six steps of bf16 compute against fp32; a wiring mistake is of order one
+    assert torch.equal(dev_net.params16, dev_net.params.bfloat16())
+    assert dev_eng.h2d_bytes_per_step() == batch * 28 * 28 + batch * 4 and dev_eng.d2h_bytes_per_step() == 8
+
+
+def test_training_loop_on_the_device_branch(monkeypatch):
+    """`SgdOpt.train` over the device branch: display points, device-timed throughput, checkpoint window."""
+    opt = SgdOptConfig(minibatch_size=8, step_size=StepSizeSchedule.constant(0.05), momentum=Momentum.UPDATE, mu=0.9,
+                       display_iters=2, checkpoint_iters=4)
+    eng, net = _device_engine(monkeypatch, zoo.mnist_fc1, 8, opt)
+    sgd = SgdOpt(opt, eng, quiet=True)
+    hist = sgd.train(iter(_batches(8, 8)), None, max_iters=8)
+    assert eng.iter == 8 and [h[0] for h in hist] == [2, 4, 6, 8]
+    assert all(0.0 < h[1] < 10.0 for h in hist)
