@@ -76,6 +76,9 @@ class _Event:
     def wait(self, stream=None):
         pass
 
+    def synchronize(self):
+        pass
+
 
 class _Ctx:
     def __enter__(self):
@@ -313,3 +316,41 @@ def test_replicated_master_keeps_full_fp32_weights_on_every_rank(monkeypatch):
     reference_step(expect_w[d:], mean[d:].clone(), expect_v[d:], 0.1, 0.9, 0.0, 1.0, 1, 3)
     for r in range(3):
         assert torch.allclose(W.nets[r].params, expect_w, atol=1e-6), f"rank {r}: master not replicated"
+
+
+def test_data_parallel_engines_over_the_fused_exchange_equal_one_process_on_the_global_batch(monkeypatch):
+    """Two step engines on their device branch, gradients exchanged from the backward hooks through the emulated push /
+    reduce kernels, against one CPU engine that sees both ranks' batches as one."""
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.optim.sgd import SgdOptConfig, StepSizeSchedule
+    world, batch = 2, 4
+    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda self, *a, **k: self)
+    W = World(monkeypatch, world, zoo.lenet, batch, Momentum.UPDATE, min_bucket_bytes=1 << 10, one_shot_bytes=16 << 10)
+    opt = SgdOptConfig(minibatch_size=batch, step_size=StepSizeSchedule.constant(0.01), momentum=Momentum.UPDATE, mu=0.9,
+                       l2_reg_coef=1e-3, display_iters=0)
+    engines = [StepEngine(W.nets[r], opt, W.comms[r], use_graph=False) for r in range(world)]
+    assert all(e._overlapped() for e in engines)
+    big_opt = SgdOptConfig(minibatch_size=world * batch, step_size=StepSizeSchedule.constant(0.01),
+                           momentum=Momentum.UPDATE, mu=0.9, l2_reg_coef=1e-3, display_iters=0)
+    big = Net(zoo.lenet(), world * batch, device="cpu", seed=(5, 6), minibatch_size=world * batch)
+    with torch.no_grad():
+        big.params.copy_(W.nets[0].params16.float())
+        for n in W.nets:
+            n.params.copy_(n.params16.float())
+    big_eng = StepEngine(big, big_opt)
+    g = torch.Generator().manual_seed(3)
+    for step in range(4):
+        x = torch.randint(0, 256, (world * batch, 1, 28, 28), dtype=torch.uint8, generator=g)
+        y = torch.randint(0, 10, (world * batch,), dtype=torch.int32, generator=g)
+        for r in range(world):
+            W.current = r
+            engines[r].feed(x[r * batch:(r + 1) * batch], y[r * batch:(r + 1) * batch])
+            engines[r].step()
+        assert W.run_queued() == len(W.comms[0].launches)
+        big_eng.feed(x, y)
+        big_eng.step()
+    assert torch.equal(W.nets[0].params16, W.nets[1].params16), "replicas must hold identical compute weights"
+    want = big.params.detach()
+    got = W.nets[0].params16.float()
+    rel = float((got - want).norm() / want.norm())
+    assert rel < 2e-2, rel
