@@ -51,7 +51,7 @@ class FakeWorld:
                 for _, peer, alpha, _, mix_self, wait_peer in ops:
                     assert wait_peer == 1
                     if peer != r or mix_self:
-                        self.w[r] = (1 - alpha) * self.w[r] + alpha * snap[peer]
+                        self.w[r].copy_((1 - alpha) * self.w[r] + alpha * snap[peer])     # in place: callers hold it
         self.queue = [[] for _ in range(self.world)]
 
 
@@ -356,3 +356,72 @@ def test_elastic_averaging_launches_move_clients_and_centre_toward_each_other(mo
         centre = centre + sum(beta * (start[r] - centre) for r in range(world))
         assert torch.allclose(comms[0].center, centre, atol=1e-5)
         assert float(comms[0].delta.abs().sum()) == 0.0
+
+
+def test_two_device_branch_engines_with_pair_gossip(monkeypatch):
+    """Step locally, then mix parameters with the partner of the shared permutation: two engines on their device
+    branch with the kernel backend against two CPU engines mixed by hand."""
+    import kernel_emulation
+    from test_engine_emulated import _Ctx, _Event, _Stream
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.sgd import Momentum, SgdOptConfig, StepSizeSchedule, SyncOrder
+    world, batch = 2, 4
+    kernel_emulation.install(monkeypatch)
+    monkeypatch.setattr(torch.cuda, "Stream", lambda *a, **k: _Stream())
+    monkeypatch.setattr(torch.cuda, "Event", _Event)
+    monkeypatch.setattr(torch.cuda, "stream", lambda s: _Ctx())
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda *a: _Stream())
+    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda self, *a, **k: self)
+    opt = SgdOptConfig(minibatch_size=batch, step_size=StepSizeSchedule.constant(0.01), momentum=Momentum.UPDATE, mu=0.9,
+                       sync_order=SyncOrder.STEP_THEN_SYNC_PARAMS, display_iters=0)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    dev_nets = [Net(zoo.mnist_fc2(), batch, device="cpu", seed=(5, 6)) for _ in range(world)]
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    cpu_nets = [Net(zoo.mnist_fc2(), batch, device="cpu", seed=(5, 6)) for _ in range(world)]
+    fake = FakeWorld(world, dev_nets[0].flat_len)
+    monkeypatch.setattr(PK, "fn", fake.fn)
+    comms = []
+    for r in range(world):
+        fake.w[r] = dev_nets[r].params
+        c = _make_flat(r, world, "pair", (17, 29), fake)
+        c.net = dev_nets[r]
+        c.iter, c.step_size = 0, 0.0
+        c.attach = lambda engine: None
+        comms.append(c)
+        with torch.no_grad():
+            dev_nets[r].params.copy_(dev_nets[r].params16.float())
+            cpu_nets[r].params.copy_(dev_nets[r].params16.float())
+    dev_engs = [StepEngine(dev_nets[r], opt, comms[r], use_graph=False) for r in range(world)]
+    cpu_engs = [StepEngine(cpu_nets[r], SgdOptConfig(minibatch_size=batch, step_size=StepSizeSchedule.constant(0.01),
+                                                     momentum=Momentum.UPDATE, mu=0.9, display_iters=0))
+                for r in range(world)]
+    shadow = XorShift128Plus(17, 29)
+    g = torch.Generator().manual_seed(9)
+    mixed = 0
+    for step in range(6):
+        for r in range(world):
+            x = torch.randint(0, 256, (batch, 1, 28, 28), dtype=torch.uint8, generator=g)
+            y = torch.randint(0, 10, (batch,), dtype=torch.int32, generator=g)
+            fake.current = r
+            dev_engs[r].feed(x, y)
+            dev_engs[r].step()
+            cpu_engs[r].feed(x, y)
+            cpu_engs[r].step()
+        fake.run()
+        for n in dev_nets:
+            n.refresh_shadow()      # what the engine does after the exchange; here the exchange ran late
+        perm = shadow.permutation(world)
+        with torch.no_grad():
+            before = [n.params.detach().clone() for n in cpu_nets]
+            for r in range(world):
+                src = perm.index(r)
+                if src != r:
+                    cpu_nets[r].params.copy_(0.5 * before[r] + 0.5 * before[src])
+                    mixed += 1
+    assert mixed > 0, "the permutations never paired the two ranks"
+    for r in range(world):
+        want = cpu_nets[r].params.detach()
+        rel = float((dev_nets[r].params - want).norm() / want.norm())
+        assert rel < 3e-2, (r, rel)
