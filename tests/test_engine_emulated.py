@@ -106,3 +106,33 @@ def test_training_loop_on_the_device_branch(monkeypatch):
     hist = sgd.train(iter(_batches(8, 8)), None, max_iters=8)
     assert eng.iter == 8 and [h[0] for h in hist] == [2, 4, 6, 8]
     assert all(0.0 < h[1] < 10.0 for h in hist)
+
+
+def test_distillation_on_the_device_branch(monkeypatch):
+    """Teacher inference on the compute stream, its probabilities as soft targets of the student's fused head."""
+    from rembrandt_b200.optim.mimic import MimicSgdOpt
+    opt = SgdOptConfig(minibatch_size=16, step_size=StepSizeSchedule.constant(0.1), momentum=Momentum.UPDATE, mu=0.9,
+                       display_iters=0)
+    eng, student = _device_engine(monkeypatch, zoo.mnist_fc1, 16, opt)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    teacher = Net(zoo.mnist_fc1(), 16, device="cpu", seed=(11, 12), training=False)
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    torch.manual_seed(0)
+    x = torch.randint(0, 256, (16, 1, 28, 28), dtype=torch.uint8)
+    y = torch.randint(0, 10, (16,), dtype=torch.int32)
+
+    def kl():
+        outs = []
+        for n in (teacher, student):
+            n.loss_op.enable_probs()
+            n.load_batch(x, y)
+            n.forward(False)
+            n.read_stats()
+            outs.append(n.loss_op.probs.clone().clamp_min(1e-12))
+        q, p = outs
+        return float((q * (q.log() - p.log())).sum(1).mean())
+
+    before = kl()
+    MimicSgdOpt(opt, eng, teacher, quiet=True).train([(x, y)] * 60, max_iters=60)
+    after = kl()
+    assert after < 0.5 * before, (before, after)
