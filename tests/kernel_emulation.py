@@ -387,14 +387,20 @@ def var_input_u8(src, shapes, dst, draws, in_stride, N, C, crop_h, crop_w, Cp, f
     """Inference form only (shorter side rescaled to `scale_lower`, centred crop, no flip), plain NHWC output; the
     rescale itself is the operator's own one-sample restatement, which the kernel is compared with on a GPU."""
     from rembrandt_b200.models.operators import VarDataOp
-    if train or f != 1 or ep != 0:
-        raise NotImplementedError("only the inference form with plain NHWC output is emulated")
+    if f != 1 or ep != 0:
+        raise NotImplementedError("only plain NHWC output is emulated")
+    # the training form draws scale, crop offset and flip from an in-kernel generator: emulated only where nothing is
+    # left to draw (one scale, no flip, no noise, and -- checked per sample below -- no room to move the crop)
+    if train and (scale_lower != scale_upper or random_flip or pca_sigma):
+        raise NotImplementedError("the random draws of the training form are not emulated")
     out = torch.zeros(N, OH, OW, Cp)
     mu = torch.tensor(list(mean), dtype=torch.float32).reshape(-1, 1, 1)
     for i in range(N):
         w, h = int(shapes[i, 0]), int(shapes[i, 1])
         im = src.reshape(N, in_stride)[i, : C * h * w].view(C, h, w)
         rw, rh = VarDataOp.scaled_dims(w, h, scale_lower)
+        if train and (rw > crop_w or rh > crop_h):
+            raise NotImplementedError("the random crop offset of the training form is not emulated")
         ox, oy = (rw - crop_w) // 2, (rh - crop_h) // 2
         v = VarDataOp.ref_sample(im, scale_lower, ox, oy, False, crop_w, crop_h)
         X, Y = ox + torch.arange(crop_w), oy + torch.arange(crop_h)

@@ -136,3 +136,38 @@ def test_distillation_on_the_device_branch(monkeypatch):
     MimicSgdOpt(opt, eng, teacher, quiet=True).train([(x, y)] * 60, max_iters=60)
     after = kl()
     assert after < 0.5 * before, (before, after)
+
+
+@pytest.mark.parametrize("as_list", [True, False])
+def test_variable_size_batches_through_the_engine(monkeypatch, as_list):
+    """The per-sample size table travels through the staging slots with the pixels: the loss of an engine step equals
+    a direct evaluation of the same batch with the weights the engine had before the step."""
+    from test_var_input import _var_cfg
+    from rembrandt_b200.models.operators import VarDataOp
+    opt = SgdOptConfig(minibatch_size=4, step_size=StepSizeSchedule.constant(0.01), momentum=Momentum.UPDATE, mu=0.9,
+                       display_iters=0)
+    eng, net = _device_engine(monkeypatch, lambda: _var_cfg(32, 32, 32, flip=False), 4, opt)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    direct = Net(_var_cfg(32, 32, 32, flip=False), 4, device="cpu", seed=(2, 3), minibatch_size=4)
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    labels = torch.tensor([0, 3, 5, 7], dtype=torch.int32)
+    seen = []
+    for seed in (9, 10):
+        g = torch.Generator().manual_seed(seed)
+        order = [0, 1, 2, 3] if seed == 9 else [3, 1, 0, 2]            # the second batch has another size table
+        imgs = [torch.randint(0, 256, (3, 32 + 8 * i, 32 + 8 * i), dtype=torch.uint8, generator=g) for i in order]
+        with torch.no_grad():
+            direct.params.copy_(net.params)
+            direct.params16.copy_(net.params16)
+        eng.feed(imgs if as_list else VarDataOp.pack(imgs, net.input_op.in_stride), labels)
+        stats = eng.step()
+        if stats is not None:
+            seen.append(stats[0])
+        direct.load_batch(imgs, labels)
+        direct.read_stats()
+        direct.forward(True)
+        want = direct.read_stats()[0]
+        if seed == 10:
+            seen.append(eng.flush()[0])
+            assert abs(seen[-1] - want) < 1e-5 * max(1.0, abs(want)), (seen, want)
+    assert eng.h2d_bytes_per_step() == 4 * net.input_op.in_stride + 4 * 4 + 4 * 2 * 4
