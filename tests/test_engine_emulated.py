@@ -171,3 +171,17 @@ def test_variable_size_batches_through_the_engine(monkeypatch, as_list):
             seen.append(eng.flush()[0])
             assert abs(seen[-1] - want) < 1e-5 * max(1.0, abs(want)), (seen, want)
     assert eng.h2d_bytes_per_step() == 4 * net.input_op.in_stride + 4 * 4 + 4 * 2 * 4
+
+
+def test_phase_timing_helper_runs_the_three_phases(monkeypatch):
+    from rembrandt_b200.utils.timing import time_phases
+    opt = SgdOptConfig(minibatch_size=8, step_size=StepSizeSchedule.constant(0.01), momentum=Momentum.UPDATE, mu=0.9,
+                       display_iters=0)
+    eng, net = _device_engine(monkeypatch, zoo.mnist_fc1, 8, opt)
+    x, y = _batches(1, 8)[0]
+    net.load_batch(x, y)
+    before = net.params.clone()
+    out = time_phases(eng, iters=2, warmup=1)
+    # the inert events report 1 ms between any two marks
+    assert out == {"forward_ms": 1.0, "backward_ms": 1.0, "exchange_update_tail_ms": 1.0, "step_ms": 3.0}
+    assert not torch.equal(net.params, before) and int(net.step_counter) == 3
