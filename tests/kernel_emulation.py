@@ -415,6 +415,16 @@ def sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7):
         w16[:n].copy_(w[:n])
 
 
+def sgd_fused_grid(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase=7, blocks=296, threads=128):
+    sgd_fused(w, g, v, w16, n, lr, mu, l2, grad_scale, mode, phase)
+
+
+def axpy_shadow(w, v, w16, n, s):
+    w[:n].add_(v[:n], alpha=s)
+    if w16 is not None:
+        w16[:n].copy_(w[:n])
+
+
 def _unsupported(name):
     def fn(*a, **k):
         raise NotImplementedError(f"kernel front {name} has no CPU stand-in")
@@ -425,7 +435,8 @@ EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fw
                                     conv_direct_dgrad, pack_dgrad_filters, zero_s2d_structural, gemm_tc, bias_act,
                                     colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
                                     softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd,
-                                    pointwise_loss, lrn_fwd, lrn_bwd, dropout, var_input_u8)}
+                                    pointwise_loss, lrn_fwd, lrn_bwd, dropout, var_input_u8, sgd_fused_grid,
+                                    axpy_shadow)}
 
 
 def install(monkeypatch):

@@ -185,3 +185,25 @@ def test_phase_timing_helper_runs_the_three_phases(monkeypatch):
     # the inert events report 1 ms between any two marks
     assert out == {"forward_ms": 1.0, "backward_ms": 1.0, "exchange_update_tail_ms": 1.0, "step_ms": 3.0}
     assert not torch.equal(net.params, before) and int(net.step_counter) == 3
+
+
+def test_overlapped_local_update_equals_one_sweep_after_backward(monkeypatch):
+    """The per-bucket optimizer launches from the backward hooks cover every parameter exactly once."""
+    from rembrandt_b200.parallel.comm import LocalOverlapComm
+    opt = SgdOptConfig(minibatch_size=8, step_size=StepSizeSchedule.constant(0.02), momentum=Momentum.UPDATE_NESTEROV,
+                       mu=0.9, l2_reg_coef=1e-3, display_iters=0)
+    plain, net_a = _device_engine(monkeypatch, lambda: zoo.lenet(pad=2), 8, opt)
+    monkeypatch.setattr(Net, "device_path_on_cpu", True)
+    net_b = Net(zoo.lenet(pad=2), 8, device="cpu", seed=(2, 3), minibatch_size=8)
+    monkeypatch.setattr(Net, "device_path_on_cpu", False)
+    comm = LocalOverlapComm(bucket_bytes=64 << 10, min_bucket_bytes=4 << 10)
+    overlapped = StepEngine(net_b, opt, comm, use_graph=False)
+    assert overlapped._overlapped() and len(comm._by_trigger) >= 2
+    for eng in (plain, overlapped):
+        eng.stepper.nesterov_lookahead(+1.0)
+    for x, y in _batches(4, 8):
+        for eng in (plain, overlapped):
+            eng.feed(x, y)
+            eng.step()
+    assert torch.allclose(net_a.params, net_b.params, atol=1e-6)
+    assert torch.equal(net_a.params16, net_b.params16) and float(net_b.grads.abs().sum()) == 0.0
