@@ -43,7 +43,7 @@ struct ArSgdArgs {
   uint32_t* epoch_ptr;         // local: last completed epoch of this slot
   unsigned int* block_counter; // local, zero between launches
   unsigned int* status;
-  uint32_t* wait_ok;           // local: verdict of ar_wait_kernel for this slot (null: the reducing kernel waits itself)
+  uint32_t* wait_ok;           // local: outcome of ar_wait_kernel for this slot (null: the reducing kernel waits itself)
   long long off, n, decay_len, stage_off;
   int rank, world, slot, one_shot, op, zero_grads;
   float avg_scale;             // op 1: result = sum * avg_scale
@@ -91,7 +91,7 @@ __device__ __forceinline__ uint32_t* flag_at(uint32_t* pad, int slot, int phase,
   return pad + ((slot * 2 + phase) * MAX_RANKS + src);
 }
 
-// All threads of the block return the same verdict.
+// All threads of the block return the same answer.
 __device__ __forceinline__ bool start_barrier(uint32_t* const* flags, int rank, int world, int slot, uint32_t epoch,
                                               unsigned int* status) {
   if (blockIdx.x == 0 && threadIdx.x < world) {
