@@ -374,3 +374,43 @@ def test_make_lmdb_tool_round_trips_a_cifar_file(tmp_path, capsys):
     labels = [int(v) for _, y in ld for v in y]
     ld.close()
     assert labels == [int(v) for v in recs[:, 0]]
+
+
+def test_jpeg_records_decode_through_the_database_shards(tmp_path):
+    """Encoded (JPEG) image records of a Caffe database and of a record store, decoded through Pillow: planar RGB out,
+    grey images replicated to three channels."""
+    PIL = pytest.importorskip("PIL.Image")
+    import io
+    import struct
+    from rembrandt_b200.data.codecs import JpegDataCodec, encode_caffe_datum
+    from rembrandt_b200.data.lmdb_reader import LmdbCaffeShard, write_env
+    from rembrandt_b200.data.recorddb import RecordDbWriter, VarrayDbShard
+    rng = np.random.default_rng(8)
+
+    def jpeg(arr, mode):
+        buf = io.BytesIO()
+        PIL.fromarray(arr, mode).save(buf, format="JPEG", quality=95)
+        return buf.getvalue()
+    # smooth images survive JPEG closely enough to be recognised
+    ramp = np.linspace(0, 255, 24 * 20).reshape(24, 20)
+    colour = np.stack([ramp, ramp[::-1], ramp * 0.5], axis=2).astype(np.uint8)
+    grey = ramp.astype(np.uint8)
+    blobs = [jpeg(colour, "RGB"), jpeg(grey, "L")]
+    codec = JpegDataCodec()
+    out = codec.decode(blobs[0])
+    assert out.shape == (3, 24, 20) and np.abs(out.astype(int) - colour.transpose(2, 0, 1).astype(int)).mean() < 6
+    g3 = codec.decode(blobs[1])
+    assert g3.shape == (3, 24, 20) and np.array_equal(g3[0], g3[1]) and np.abs(g3[0].astype(int) - grey).mean() < 4
+    # Caffe database with encoded records
+    (tmp_path / "db").mkdir()
+    write_env(str(tmp_path / "db"), [(b"%08d" % i, encode_caffe_datum(b, 3, 24, 20, label=5 + i, encoded=True))
+                                     for i, b in enumerate(blobs)])
+    got = list(LmdbCaffeShard(str(tmp_path / "db"), codec=codec))
+    assert [lab for _, lab in got] == [5, 6] and got[0][0].shape == (3, 24, 20)
+    # record store (value blobs + little-endian labels)
+    with RecordDbWriter(str(tmp_path / "d")) as wd, RecordDbWriter(str(tmp_path / "l")) as wl:
+        for i, b in enumerate(blobs):
+            wd.append(b)
+            wl.append(struct.pack("<i", 40 + i))
+    rows = list(VarrayDbShard(str(tmp_path / "d"), str(tmp_path / "l"), codec))
+    assert [lab for _, lab in rows] == [40, 41] and np.array_equal(rows[1][0], g3)
