@@ -8,7 +8,8 @@ from .common import base_parser, run_training
 def main(argv=None):
     ap = base_parser(__doc__, batch=64, lr=0.01, momentum="update", l2=5e-4, iters=100, display_iters=20)
     ap.add_argument("--model", default="alexnet",
-                    choices=["alexnet", "nin", "vgg_a", "resnet10", "resnet18", "resnet34"])
+                    choices=["alexnet", "nin", "vgg_a", "resnet10", "resnet18", "resnet34", "resnet18_var",
+                             "resnet34_var"])
     ap.add_argument("--model-file", default=None)
     args = ap.parse_args(argv)
     schedule = None
@@ -19,6 +20,8 @@ def main(argv=None):
             schedule = d.opt.step_size
     elif args.model in ("alexnet", "nin"):
         cfg = getattr(zoo, args.model)(scale=1.0 / 255.0)
+    elif args.model.endswith("_var"):
+        cfg = getattr(zoo, args.model)()
     else:
         cfg = getattr(zoo, args.model)(mean=None)
     return run_training(args, cfg, schedule or StepSizeSchedule.decay(args.lr, 0.1, 200000))

@@ -385,6 +385,8 @@ class VarDataOp(DataOp):
         return padded, shapes
 
     def load_batch(self, images, non_blocking=True):
+        if isinstance(images, torch.Tensor) and images.dim() == 4:
+            images = list(images)                       # a batch of equally sized images
         if isinstance(images, (list,)) or (isinstance(images, tuple) and images[0].dim() == 3):
             images = self.pack(list(images), self.in_stride)
         padded, shapes = images
@@ -482,7 +484,14 @@ class VarDataOp(DataOp):
             X = ox + (self.crop_w - 1 - xs if flip else xs)
             Y = oy + torch.arange(self.crop_h)
             inside = ((Y >= 0) & (Y < rh))[:, None] & ((X >= 0) & (X < rw))[None, :]
-            outs.append((v * self.scale - mean) * inside)
+            v = v * self.scale - mean
+            if train and self.pca is not None and c == 3 and self.pca.std > 0:
+                # lighting noise, one draw per image (as in the fixed-size operator)
+                al = torch.randn(3, generator=g) * self.pca.std
+                vals = torch.tensor(list(self.pca.eigenvalues), dtype=torch.float32)
+                vecs = torch.tensor(list(self.pca.eigenvectors), dtype=torch.float32).reshape(3, 3)
+                v = v + (vecs @ (al * vals)).reshape(3, 1, 1)
+            outs.append(v * inside)
         return torch.stack(outs)
 
 

@@ -164,19 +164,29 @@ def vgg_a(num_classes=1000, in_hw=224, raw_hw=256, mean=None):
     return cfg.softmax_kl_loss(SoftmaxKLLossCfg(num_classes))
 
 
-def _imagenet_resnet(blocks, num_classes, in_hw, raw_hw, mean, pca, ema):
+def _imagenet_resnet(blocks, num_classes, in_hw, raw_hw, mean, pca, ema, variable=None):
+    """`variable` = (shorter-side lower, upper, largest width / height accepted) switches to the variable-size input
+    operator: every image is rescaled so that its shorter side has a length drawn in [lower, upper], then cropped."""
     k = ParamsInit.kaiming()
     mov = BNormMovingAverage("exponential", ema)
     pre = []
-    if mean is not None:
-        pre.append(Preproc("subtract_mean", mean=mean))
-    src = in_hw
-    if raw_hw and raw_hw > in_hw:
-        src = raw_hw
-        pre += [Preproc("flip_x"), Preproc("crop", crop_width=in_hw, crop_height=in_hw)]
-    if pca:
-        pre.append(Preproc("pca_noise", std=0.1, eigenvalues=PCA_EIGVALS, eigenvectors=PCA_EIGVECS))
-    cfg = SequentialOperatorConfig().data3d(Data3dCfg((src, src, 3), normalize=True, preprocs=pre))
+    noise = [Preproc("pca_noise", std=0.1, eigenvalues=PCA_EIGVALS, eigenvectors=PCA_EIGVECS)] if pca else []
+    if variable is not None:
+        lower, upper, max_hw = variable
+        pre = [Preproc("scale_bicubic", lower=lower, upper=upper),
+               Preproc("crop", crop_width=in_hw, crop_height=in_hw), Preproc("flip_x")] + noise
+        cfg = SequentialOperatorConfig().var_data3d(
+            Data3dCfg((max_hw, max_hw, 3), normalize=True, preprocs=pre, max_dims=(max_hw, max_hw, 3),
+                      channel_mean=list(mean) if mean is not None else None))
+    else:
+        if mean is not None:
+            pre.append(Preproc("subtract_mean", mean=mean))
+        src = in_hw
+        if raw_hw and raw_hw > in_hw:
+            src = raw_hw
+            pre += [Preproc("flip_x"), Preproc("crop", crop_width=in_hw, crop_height=in_hw)]
+        pre += noise
+        cfg = SequentialOperatorConfig().data3d(Data3dCfg((src, src, 3), normalize=True, preprocs=pre))
     cfg.bnorm_conv2d(BNormConv2dCfg(7, 2, 3, 64, Act.RECT, k, mov), "conv1")
     cfg.pool2d(Pool2dCfg(3, 2, 1, PoolKind.MAX), "pool1")
     ch = 64
@@ -207,6 +217,20 @@ def resnet18(num_classes=1000, in_hw=224, raw_hw=256, mean=None, pca=True, ema=0
 def resnet34(num_classes=1000, in_hw=224, raw_hw=256, mean=None, pca=True, ema=0.1):
     """ResNet-34 (src/templates/resnet.rs:208-365)."""
     return _imagenet_resnet((3, 4, 6, 3), num_classes, in_hw, raw_hw, mean, pca, ema)
+
+
+def resnet18_var(num_classes=1000, in_hw=224, scale=(256, 480), max_hw=640, channel_mean=None, pca=True, ema=0.1):
+    """ResNet-18 on images of any size: shorter side rescaled (bicubic) to a length drawn in `scale`, crop `in_hw`,
+    flip, lighting noise; moving-average factor 0.1, epsilon 1e-5, Xavier classifier
+    (src/templates/resnet_new.rs:58-212). `channel_mean` is an optional per-channel mean in [0, 1] units."""
+    return _imagenet_resnet((2, 2, 2, 2), num_classes, in_hw, None, channel_mean, pca, ema,
+                            variable=(scale[0], scale[1], max_hw))
+
+
+def resnet34_var(num_classes=1000, in_hw=224, scale=(256, 480), max_hw=640, channel_mean=None, pca=True, ema=0.1):
+    """ResNet-34 with the variable-size input chain (src/templates/resnet_new.rs:214-376)."""
+    return _imagenet_resnet((3, 4, 6, 3), num_classes, in_hw, None, channel_mean, pca, ema,
+                            variable=(scale[0], scale[1], max_hw))
 
 
 def resnet10(num_classes=1000, in_hw=224, raw_hw=256, mean=None):
@@ -268,6 +292,6 @@ def go_policy_resnet(planes=32, channels=128, blocks=5, num_classes=361):
 TEMPLATES = {
     "mnist_fc1": mnist_fc1, "mnist_fc2": mnist_fc2, "lenet": lenet, "cifar_krizh26": cifar_krizh26,
     "alexnet": alexnet, "nin": nin, "vgg_a": vgg_a, "resnet10": resnet10, "resnet18": resnet18,
-    "resnet34": resnet34, "resnet20_cifar": resnet20_cifar, "go_policy_net": go_policy_net,
-    "go_policy_resnet": go_policy_resnet,
+    "resnet34": resnet34, "resnet18_var": resnet18_var, "resnet34_var": resnet34_var,
+    "resnet20_cifar": resnet20_cifar, "go_policy_net": go_policy_net, "go_policy_resnet": go_policy_resnet,
 }

@@ -69,3 +69,13 @@ def test_distributed_tool_on_two_cpu_ranks(comm):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     assert "iter 4 " in r.stderr
+
+
+def test_variable_size_template_through_the_imagenet_tool(monkeypatch):
+    from rembrandt_b200.cli import train_imagenet
+    from rembrandt_b200.models import zoo
+    full = zoo.resnet18_var
+    monkeypatch.setattr(zoo, "resnet18_var", lambda: full(num_classes=10, in_hw=32, scale=(36, 40), max_hw=48))
+    sgd = train_imagenet.main(["--device", "cpu", "--batch", "2", "--iters", "2", "--display-iters", "1",
+                               "--synthetic-size", "8", "--model", "resnet18_var"])
+    assert sgd.engine.iter == 2

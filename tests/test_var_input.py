@@ -134,3 +134,21 @@ def test_var_input_space_to_depth_feeds_strided_conv():
     cpu.forward(False)
     lg, lc = gpu.read_stats()[0], cpu.read_stats()[0]
     assert abs(lg - lc) < 0.03 * max(1.0, abs(lc)), (lg, lc)
+
+
+def test_variable_size_resnet_template_builds_and_steps_on_cpu():
+    from rembrandt_b200.models import zoo
+    cfg = zoo.resnet18_var(num_classes=7, in_hw=32, scale=(36, 48), max_hw=64, channel_mean=(0.4, 0.5, 0.6))
+    net = Net(cfg, 2, device="cpu", seed=(1, 2))
+    assert isinstance(net.input_op, VarDataOp) and net.input_op.scale_range == (36, 48)
+    assert net.input_op.flip and net.input_op.pca is not None
+    fixed = Net(zoo.resnet18(num_classes=7, in_hw=32, raw_hw=40), 2, device="cpu", seed=(1, 2))
+    assert net.params_len == fixed.params_len                 # the same network behind a different input operator
+    g = torch.Generator().manual_seed(0)
+    imgs = [torch.randint(0, 256, (3, 40, 64), dtype=torch.uint8, generator=g),
+            torch.randint(0, 256, (3, 57, 38), dtype=torch.uint8, generator=g)]
+    net.load_batch(imgs, torch.tensor([1, 5]))
+    net.forward(True)
+    net.backward()
+    loss, _ = net.read_stats()
+    assert 0.5 < loss < 6.0 and torch.isfinite(net.grads).all() and float(net.grads.abs().sum()) > 0
