@@ -16,7 +16,8 @@ from ..data import (AsyncQueueDataIter, BatchIter, CyclicSampleDataIter, RandomS
                     compute_mean, open_data_file, partition_shard)
 from ..engine import StepEngine
 from ..models.net import Net
-from ..optim.sgd import (CheckpointBehavior, Momentum, SgdOptConfig, StepSizeReference, StepSizeSchedule, SyncOrder)
+from ..optim.sgd import (CheckpointBehavior, InitBehavior, Momentum, SgdOptConfig, StepSizeReference, StepSizeSchedule,
+                         SyncOrder)
 from ..parallel import comm as comm_mod
 from ..trainer import ExperimentConfig, SgdOpt
 
@@ -40,7 +41,12 @@ def base_parser(desc, **defaults):
     ap.add_argument("--checkpoint-iters", type=int, default=defaults.get("checkpoint_iters", 0))
     ap.add_argument("--save-iters", type=int, default=0)
     ap.add_argument("--valid-iters", type=int, default=defaults.get("valid_iters", 0))
-    ap.add_argument("--checkpoint-dir", default=None)
+    ap.add_argument("--checkpoint-dir", default=None,
+                    help="checkpoints and traces go here; a run started in a directory that holds a checkpoint resumes")
+    ap.add_argument("--resume-from", type=int, default=None, metavar="T",
+                    help="start from the parameter file of iteration T in --checkpoint-dir instead of the latest state")
+    ap.add_argument("--keep-averaged", action="store_true",
+                    help="continue from the averaged model after a checkpoint (default: every rank keeps its own)")
     ap.add_argument("--comm", default=defaults.get("comm", "auto"),
                     help="exchange backend: auto (fused_allreduce_sgd on GPUs, allreduce on CPU ranks) | kernel backends "
                          "fused_allreduce_sgd, gossip_p2p, gossip_pull_p2p, gossip_push_p2p, group_allreduce_gossip_p2p, "
@@ -110,7 +116,10 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
     opt = SgdOptConfig(minibatch_size=minibatch, step_size=schedule or StepSizeSchedule.constant(args.lr),
                        momentum=MOMENTA[args.momentum], mu=args.mu, l2_reg_coef=args.l2,
                        sync_order=ORDERS[args.sync_order] if args.sync_order else default_order(worker.name),
-                       comm_interval=args.comm_interval, checkpoint=CheckpointBehavior.DISCARD,
+                       comm_interval=args.comm_interval,
+                       checkpoint=CheckpointBehavior.KEEP if args.keep_averaged else CheckpointBehavior.DISCARD,
+                       init=InitBehavior.RESUME_FROM if args.resume_from is not None else InitBehavior.INIT_OR_RESUME,
+                       resume_t=args.resume_from or 0,
                        display_iters=args.display_iters, checkpoint_iters=args.checkpoint_iters,
                        save_iters=args.save_iters or args.checkpoint_iters, valid_iters=args.valid_iters,
                        checkpoint_dir=args.checkpoint_dir, max_iters=args.iters)

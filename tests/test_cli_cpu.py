@@ -79,3 +79,16 @@ def test_variable_size_template_through_the_imagenet_tool(monkeypatch):
     sgd = train_imagenet.main(["--device", "cpu", "--batch", "2", "--iters", "2", "--display-iters", "1",
                                "--synthetic-size", "8", "--model", "resnet18_var"])
     assert sgd.engine.iter == 2
+
+
+def test_tool_resumes_from_the_latest_state_or_a_given_iteration(tmp_path):
+    d = str(tmp_path / "run")
+    args = TINY + ["--valid-iters", "0", "--model", "fc1", "--checkpoint-dir", d, "--checkpoint-iters", "2"]
+    first = train_mnist.main(args + ["--iters", "4"])
+    assert first.engine.iter == 4 and os.path.exists(os.path.join(d, "params.t_4.blob"))
+    again = train_mnist.main(args + ["--iters", "6"])                      # picks up at 4
+    rows = open(os.path.join(d, "trace_sgd.0.log.1")).read().splitlines()
+    assert again.engine.iter == 6 and [r.split(",")[0] for r in rows[1:] if ",step," in r] == ["5", "6"]
+    from_two = train_mnist.main(args + ["--iters", "3", "--resume-from", "2"])
+    rows = open(os.path.join(d, "trace_sgd.0.log.2")).read().splitlines()
+    assert from_two.engine.iter == 3 and [r.split(",")[0] for r in rows[1:] if ",step," in r] == ["3"]
