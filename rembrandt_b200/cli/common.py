@@ -54,6 +54,8 @@ def base_parser(desc, **defaults):
                          "group_allreduce_gossip, elastic | null")
     ap.add_argument("--sync-order", choices=sorted(ORDERS), default=None)
     ap.add_argument("--comm-interval", type=int, default=1)
+    ap.add_argument("--step-ref", choices=["local", "checkpoint"], default="local",
+                    help="checkpoint: the step size is re-evaluated only at checkpoints")
     ap.add_argument("--data", default=None, help=".data descriptor; synthetic data when absent")
     ap.add_argument("--synthetic-size", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=1234)
@@ -116,7 +118,7 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
     opt = SgdOptConfig(minibatch_size=minibatch, step_size=schedule or StepSizeSchedule.constant(args.lr),
                        momentum=MOMENTA[args.momentum], mu=args.mu, l2_reg_coef=args.l2,
                        sync_order=ORDERS[args.sync_order] if args.sync_order else default_order(worker.name),
-                       comm_interval=args.comm_interval,
+                       comm_interval=args.comm_interval, step_ref=StepSizeReference(args.step_ref),
                        checkpoint=CheckpointBehavior.KEEP if args.keep_averaged else CheckpointBehavior.DISCARD,
                        init=InitBehavior.RESUME_FROM if args.resume_from is not None else InitBehavior.INIT_OR_RESUME,
                        resume_t=args.resume_from or 0,
