@@ -92,3 +92,15 @@ def test_tool_resumes_from_the_latest_state_or_a_given_iteration(tmp_path):
     from_two = train_mnist.main(args + ["--iters", "3", "--resume-from", "2"])
     rows = open(os.path.join(d, "trace_sgd.0.log.2")).read().splitlines()
     assert from_two.engine.iter == 3 and [r.split(",")[0] for r in rows[1:] if ",step," in r] == ["3"]
+
+
+@pytest.mark.parametrize("tool", ["train_mnist", "dist_train_mnist", "train_cifar10", "train_imagenet",
+                                  "dist_train_imagenet", "train_gogod", "run_rembrandt", "bench_conv", "bench_gemm",
+                                  "bench_allreduce", "bench_link", "bench_tma", "bench_kernels", "data_tools",
+                                  "test_dist"])
+def test_every_tool_imports_and_prints_its_help(tool, capsys):
+    import importlib
+    mod = importlib.import_module(f"rembrandt_b200.cli.{tool}")
+    with pytest.raises(SystemExit) as e:
+        mod.main(["--help"])
+    assert e.value.code == 0 and "usage:" in capsys.readouterr().out
