@@ -139,6 +139,23 @@ def test_example_descriptors_shipped_with_this_framework_build_and_step():
     assert float(net.grads.abs().sum()) > 0
 
 
+def test_cifar_example_descriptor_with_an_optimizer_section():
+    import torch
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    md = descriptor.load_model(os.path.join(here, "examples", "cifar10_krizh26.model"))
+    net = Net(md.config, 2, device="cpu")
+    assert [o.out_hwc for o in net.ops[1:8]] == [(32, 32, 32), (16, 16, 32), (16, 16, 32), (8, 8, 32), (8, 8, 64),
+                                                 (4, 4, 64), (1, 1, 10)]
+    assert net.params_len == (75 * 32 + 32) + (800 * 32 + 32) + (800 * 64 + 64) + (1024 * 10 + 10)
+    assert md.opt.minibatch_size == 128 and md.opt.mu == 0.9
+    assert [md.opt.step_size.at_iter(t) for t in (0, 40000, 60000)] == pytest.approx([0.01, 0.001, 0.0001])
+    assert "valid" in descriptor.load_data(os.path.join(here, "examples", "synthetic_cifar10.data"))
+    net.load_batch(torch.randint(0, 256, (2, 3, 32, 32), dtype=torch.uint8), torch.tensor([1, 2]))
+    net.forward(True)
+    net.backward()
+    assert float(net.grads.abs().sum()) > 0
+
+
 def test_sigmoid_and_tanh_layers_of_a_descriptor_build_and_step():
     text = LENET_MODEL.replace('act_func = "rect"', 'act_func = "sigmoid"', 1).replace('act_func = "relu"', 'act_func = "tanh"', 1)
     assert text != LENET_MODEL
