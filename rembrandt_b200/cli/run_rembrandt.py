@@ -12,17 +12,28 @@ def main(argv=None):
     ap = base_parser(__doc__, batch=64, lr=0.01, momentum="update", l2=5e-4, iters=200, display_iters=50,
                      valid_iters=4)
     ap.add_argument("--model-file", default="examples/mnist_lenet.model")
+    first, _ = ap.parse_known_args(argv)
+    d = descriptor.load_model(first.model_file)
+    schedule = None
+    if d.opt is not None:
+        # the optimizer section of the model file provides the defaults; flags on the command line still win
+        schedule = d.opt.step_size
+        ap.set_defaults(minibatch=d.opt.minibatch_size, mu=d.opt.mu, l2=d.opt.l2_reg_coef, lr=d.opt.step_size.at_iter(0))
     args = ap.parse_args(argv)
-    d = descriptor.load_model(args.model_file)
-    schedule = d.opt.step_size if d.opt is not None else None
+    if args.minibatch and args.minibatch % args.batch:
+        args.batch = args.minibatch if args.minibatch < args.batch else args.batch
+        args.minibatch = args.minibatch // args.batch * args.batch
     source = valid = None
     if args.data:
         splits = load_data(args.data)
         if "train" not in splits:
             raise SystemExit(f"{args.data}: missing train data source")
-        source = open_split(splits["train"])
         held_out = next((s for s in ("valid", "test") if s in splits), None)   # gen-1 files call the split "test"
-        valid = open_split(splits[held_out]) if held_out and args.valid_iters else None
+        if splits["train"].source != "synthetic":      # synthetic splits take their shape from the model: see run_training
+            source = open_split(splits["train"])
+            valid = open_split(splits[held_out]) if held_out and args.valid_iters else None
+        else:
+            args.data = None
     return run_training(args, d.config, schedule, source=source, valid_source=valid)
 
 

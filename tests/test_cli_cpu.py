@@ -104,3 +104,18 @@ def test_every_tool_imports_and_prints_its_help(tool, capsys):
     with pytest.raises(SystemExit) as e:
         mod.main(["--help"])
     assert e.value.code == 0 and "usage:" in capsys.readouterr().out
+
+
+def test_run_rembrandt_takes_optimizer_defaults_from_the_model_file():
+    sgd = run_rembrandt.main(["--device", "cpu", "--batch", "16", "--iters", "2", "--display-iters", "1",
+                              "--synthetic-size", "64", "--valid-iters", "0",
+                              "--model-file", os.path.join(ROOT, "examples", "cifar10_krizh26.model"),
+                              "--data", os.path.join(ROOT, "examples", "synthetic_cifar10.data")])
+    assert sgd.cfg.minibatch_size == 128 and sgd.cfg.mu == 0.9 and sgd.cfg.l2_reg_coef == 5e-4
+    assert sgd.engine.accum == 8 and sgd.engine.iter == 2
+    assert sgd.cfg.step_size.at_iter(0) == 0.01 and abs(sgd.cfg.step_size.at_iter(60000) - 1e-4) < 1e-12
+    # a flag on the command line wins over the file
+    sgd = run_rembrandt.main(["--device", "cpu", "--batch", "8", "--minibatch", "8", "--iters", "1", "--display-iters", "1",
+                              "--synthetic-size", "64", "--valid-iters", "0", "--l2", "0.0",
+                              "--model-file", os.path.join(ROOT, "examples", "cifar10_krizh26.model")])
+    assert sgd.cfg.minibatch_size == 8 and sgd.cfg.l2_reg_coef == 0.0
