@@ -13,7 +13,7 @@ import torch
 import torch.distributed as dist
 
 from ..data import (AsyncQueueDataIter, BatchIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
-                    compute_mean, open_data_file, partition_shard)
+                    compute_mean, open_data_file, open_split, partition_shard)
 from ..engine import StepEngine
 from ..models.net import Net
 from ..optim.sgd import (CheckpointBehavior, InitBehavior, Momentum, SgdOptConfig, StepSizeReference, StepSizeSchedule,
@@ -110,10 +110,21 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
     if source is None:
         source = (open_data_file(args.data, "train") if args.data else
                   SyntheticDataSource(args.synthetic_size, dims, classes, seed=args.seed, separable=True))
-        if valid_source is None and args.valid_iters:
-            valid_source = (open_data_file(args.data, "valid") if args.data else
-                            SyntheticDataSource(max(256, args.synthetic_size // 8), dims, classes, seed=args.seed + 1,
-                                                separable=True))
+    if valid_source is None and args.valid_iters:
+        if args.data:
+            from ..data.datasets import load_data
+            splits = load_data(args.data)
+            held_out = next((s for s in ("valid", "test") if s in splits), None)
+            valid_source = open_split(splits[held_out]) if held_out else None
+        else:
+            valid_source = SyntheticDataSource(max(256, args.synthetic_size // 8), dims, classes, seed=args.seed + 1,
+                                               separable=True)
+    # a `source = "synthetic"` split of a .data file has no shape of its own: give it the model's
+    def fit(src, seed_):
+        if isinstance(src, SyntheticDataSource) and (tuple(src.dims) != tuple(dims) or src.num_classes != classes):
+            return SyntheticDataSource(len(src), dims, classes, seed=seed_, separable=True)
+        return src
+    source, valid_source = fit(source, args.seed), fit(valid_source, args.seed + 1)
     minibatch = args.minibatch or args.batch
     opt = SgdOptConfig(minibatch_size=minibatch, step_size=schedule or StepSizeSchedule.constant(args.lr),
                        momentum=MOMENTA[args.momentum], mu=args.mu, l2_reg_coef=args.l2,

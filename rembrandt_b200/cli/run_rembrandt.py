@@ -29,11 +29,8 @@ def main(argv=None):
         if "train" not in splits:
             raise SystemExit(f"{args.data}: missing train data source")
         held_out = next((s for s in ("valid", "test") if s in splits), None)   # gen-1 files call the split "test"
-        if splits["train"].source != "synthetic":      # synthetic splits take their shape from the model: see run_training
-            source = open_split(splits["train"])
-            valid = open_split(splits[held_out]) if held_out and args.valid_iters else None
-        else:
-            args.data = None
+        source = open_split(splits["train"])         # a synthetic split is given the model's shape by run_training
+        valid = open_split(splits[held_out]) if held_out and args.valid_iters else None
     return run_training(args, d.config, schedule, source=source, valid_source=valid)
 
 

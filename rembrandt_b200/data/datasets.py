@@ -190,7 +190,8 @@ def open_split(split: DatasetSplit, rank: int = 0, world: int = 1) -> DataSource
     if split.source == "cifar10":
         return Cifar10DataSource(split.data_path)
     if split.source == "synthetic":
-        return SyntheticDataSource(10000)
+        return SyntheticDataSource(getattr(split, "size", 10000), getattr(split, "dims", None) or (28, 28, 1),
+                                   getattr(split, "num_classes", 10), separable=True)
     if split.source == "lmdb_caffe":
         from .codecs import JpegDataCodec
         from .lmdb_reader import LmdbCaffeShard

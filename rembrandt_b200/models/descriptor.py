@@ -162,6 +162,10 @@ class DatasetSplit:
     labels2_path: Optional[str] = None
     mean_path: Optional[str] = None
     normalize: bool = False
+    # for `source = "synthetic"` (no counterpart in the reference): image size (W, H, C), classes, number of samples
+    dims: Optional[tuple] = None
+    num_classes: int = 10
+    size: int = 10000
 
 
 def parse_data(text: str) -> Dict[str, DatasetSplit]:
@@ -171,7 +175,9 @@ def parse_data(text: str) -> Dict[str, DatasetSplit]:
         if "source" not in tbl:
             raise DescriptorError(f"dataset.{split} has no source")
         out[split] = DatasetSplit(tbl["source"], tbl.get("data_path"), tbl.get("labels_path"),
-                                  tbl.get("labels2_path"), tbl.get("mean_path"), bool(tbl.get("normalize", False)))
+                                  tbl.get("labels2_path"), tbl.get("mean_path"), bool(tbl.get("normalize", False)),
+                                  tuple(tbl["dims"]) if "dims" in tbl else None, int(tbl.get("num_classes", 10)),
+                                  int(tbl.get("size", 10000)))
     return out
 
 

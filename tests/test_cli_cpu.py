@@ -119,3 +119,9 @@ def test_run_rembrandt_takes_optimizer_defaults_from_the_model_file():
                               "--synthetic-size", "64", "--valid-iters", "0", "--l2", "0.0",
                               "--model-file", os.path.join(ROOT, "examples", "cifar10_krizh26.model")])
     assert sgd.cfg.minibatch_size == 8 and sgd.cfg.l2_reg_coef == 0.0
+
+
+def test_synthetic_split_of_a_data_file_takes_the_shape_of_the_model():
+    sgd = train_cifar10.main(TINY + ["--data", os.path.join(ROOT, "examples", "synthetic_cifar10.data"),
+                                     "--valid-iters", "1"])
+    assert sgd.engine.iter == 3 and len(sgd.valid_history) == 1
