@@ -12,7 +12,7 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..data import (AsyncQueueDataIter, BatchIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
+from ..data import (AsyncQueueDataIter, BatchIter, RaggedBatchIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
                     compute_mean, open_data_file, open_split, partition_shard)
 from ..engine import StepEngine
 from ..models.net import Net
@@ -141,7 +141,8 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
     if rank == 0:
         print(net.describe())
     engine = StepEngine(net, opt, worker, use_graph=not args.no_graph)
-    if args.native_loader > 0:
+    ragged = bool(getattr(model_cfg.input_op.cfg, "variable_size", False))    # images of different sizes
+    if args.native_loader > 0 and not ragged:
         from ..data.datasets import source_arrays
         from ..data.native_loader import NativeBatchLoader
         from ..utils.rng import partition_range
@@ -160,12 +161,16 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
             train_iter = NativeBatchLoader(imgs, lbls, args.batch, mode="shuffled", seed=args.seed + rank,
                                            threads=args.native_loader, shard=shard)
     else:
-        train_iter = BatchIter(AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world),
-                                                                       seed=(args.seed + rank, 99))),
-                               args.batch, dims)
+        samples = AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world), seed=(args.seed + rank, 99)))
+        if ragged:
+            train_iter = RaggedBatchIter(samples, args.batch, model_cfg.input_op.cfg.max_dims or dims)
+        else:
+            train_iter = BatchIter(samples, args.batch, dims)
     valid_iter = None
     if valid_source is not None:
-        valid_iter = BatchIter(CyclicSampleDataIter(partition_shard(valid_source, rank, world)), args.batch, dims)
+        vs = CyclicSampleDataIter(partition_shard(valid_source, rank, world))
+        valid_iter = (RaggedBatchIter(vs, args.batch, model_cfg.input_op.cfg.max_dims or dims) if ragged else
+                      BatchIter(vs, args.batch, dims))
     report = None
     if args.report_port and rank == 0:
         from ..utils.report import ReportServer

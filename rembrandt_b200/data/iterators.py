@@ -356,3 +356,35 @@ class BatchIter:
                 k = 0
         if k and not self.drop_last:
             yield self.imgs[slot][:k], self.lbls[slot][:k]
+
+
+class RaggedBatchIter:
+    """Packs samples of different sizes (image [C,h,w] uint8, label) for the variable-size input operator: a batch is
+    ((padded uint8 [B, C * maxH * maxW], int32 [B, 2] of (w, h)), labels int32 [B]); every image is stored densely at
+    the start of its row. Buffers are pinned when CUDA is available and cycled like `BatchIter`'s."""
+
+    def __init__(self, inner: Iterable, batch: int, max_dims, depth: int = 4):
+        mw, mh, c = max_dims
+        self.inner, self.batch, self.max_hw, self.c = inner, batch, (mh, mw), c
+        self.stride = c * mh * mw
+        pin = torch.cuda.is_available()
+        mk = (lambda t: t.pin_memory()) if pin else (lambda t: t)
+        self.imgs = [mk(torch.zeros((batch, self.stride), dtype=torch.uint8)) for _ in range(depth)]
+        self.shapes = [mk(torch.ones((batch, 2), dtype=torch.int32)) for _ in range(depth)]
+        self.lbls = [mk(torch.zeros(batch, dtype=torch.int32)) for _ in range(depth)]
+
+    def __iter__(self):
+        k, slot = 0, 0
+        for img, label in self.inner:
+            a = torch.from_numpy(np.ascontiguousarray(img))
+            c, h, w = a.shape
+            if c != self.c or h > self.max_hw[0] or w > self.max_hw[1]:
+                raise ValueError(f"sample of {w} x {h} x {c} exceeds the configured maximum")
+            self.imgs[slot][k, : c * h * w].copy_(a.reshape(-1))
+            self.shapes[slot][k, 0], self.shapes[slot][k, 1] = w, h
+            self.lbls[slot][k] = int(label)
+            k += 1
+            if k == self.batch:
+                yield (self.imgs[slot], self.shapes[slot]), self.lbls[slot]
+                slot = (slot + 1) % len(self.imgs)
+                k = 0

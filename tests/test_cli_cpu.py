@@ -125,3 +125,35 @@ def test_synthetic_split_of_a_data_file_takes_the_shape_of_the_model():
     sgd = train_cifar10.main(TINY + ["--data", os.path.join(ROOT, "examples", "synthetic_cifar10.data"),
                                      "--valid-iters", "1"])
     assert sgd.engine.iter == 3 and len(sgd.valid_history) == 1
+
+
+def test_ragged_images_train_through_the_common_driver():
+    """Samples of different sizes reach the variable-size input operator as (padded rows, size table) batches."""
+    import numpy as np
+    from rembrandt_b200.cli.common import base_parser, run_training
+    from rembrandt_b200.data import RaggedBatchIter
+    from rembrandt_b200.models import zoo
+
+    class Ragged:
+        dims = (48, 48, 3)
+
+        def __len__(self):
+            return 24
+
+        def __getitem__(self, i):
+            rng = np.random.default_rng(i)
+            h, w = 36 + (i * 5) % 12, 36 + (i * 7) % 12
+            return rng.integers(0, 256, (3, h, w), dtype=np.uint8), i % 10
+
+    batches = list(RaggedBatchIter([Ragged()[i] for i in range(6)], 3, (48, 48, 3)))
+    (padded, shapes), labels = batches[1]
+    assert padded.shape == (3, 3 * 48 * 48) and shapes.tolist() == [[Ragged()[i][0].shape[2], Ragged()[i][0].shape[1]]
+                                                                   for i in (3, 4, 5)]
+    assert labels.tolist() == [3, 4, 5]
+    img = Ragged()[4][0]
+    assert np.array_equal(padded[1, : img.size].numpy(), img.reshape(-1))
+    args = base_parser("ragged").parse_args(["--device", "cpu", "--batch", "3", "--iters", "2", "--display-iters", "1",
+                                             "--valid-iters", "1"])
+    cfg = zoo.resnet18_var(num_classes=10, in_hw=32, scale=(36, 40), max_hw=48)
+    sgd = run_training(args, cfg, source=Ragged(), valid_source=Ragged())
+    assert sgd.engine.iter == 2 and len(sgd.valid_history) == 1
