@@ -157,3 +157,30 @@ def test_ragged_images_train_through_the_common_driver():
     cfg = zoo.resnet18_var(num_classes=10, in_hw=32, scale=(36, 40), max_hw=48)
     sgd = run_training(args, cfg, source=Ragged(), valid_source=Ragged())
     assert sgd.engine.iter == 2 and len(sgd.valid_history) == 1
+
+
+def test_imagenet_tool_on_a_jpeg_record_store_of_ragged_images(tmp_path, monkeypatch):
+    """The data path of the reference's enabled ImageNet binary: a record store of JPEG images of different sizes with
+    little-endian labels, the variable-size ResNet-18, gradients synchronised then stepped."""
+    PIL = pytest.importorskip("PIL.Image")
+    import io
+    import struct
+    import numpy as np
+    from rembrandt_b200.cli import dist_train_imagenet
+    from rembrandt_b200.data.recorddb import RecordDbWriter
+    from rembrandt_b200.models import zoo
+    rng = np.random.default_rng(1)
+    with RecordDbWriter(str(tmp_path / "imgs")) as wd, RecordDbWriter(str(tmp_path / "lbls")) as wl:
+        for i in range(12):
+            h, w = 36 + (i * 5) % 12, 36 + (i * 7) % 12
+            buf = io.BytesIO()
+            PIL.fromarray(rng.integers(0, 256, (h, w, 3), dtype=np.uint8), "RGB").save(buf, format="JPEG")
+            wd.append(buf.getvalue())
+            wl.append(struct.pack("<i", i % 10))
+    (tmp_path / "in.data").write_text(f'[dataset.train]\nsource = "varraydb"\ndata_path = "{tmp_path / "imgs"}"\n'
+                                      f'labels_path = "{tmp_path / "lbls"}"\n')
+    full = zoo.resnet18_var
+    monkeypatch.setattr(zoo, "resnet18_var", lambda: full(num_classes=10, in_hw=32, scale=(36, 40), max_hw=48))
+    sgd = dist_train_imagenet.main(["--device", "cpu", "--batch", "2", "--minibatch", "4", "--iters", "2",
+                                    "--display-iters", "1", "--model", "resnet18_var", "--data", str(tmp_path / "in.data")])
+    assert sgd.engine.iter == 2 and sgd.engine.accum == 2
