@@ -8,7 +8,8 @@ from .common import base_parser, run_training
 def main(argv=None):
     ap = base_parser(__doc__, batch=64, lr=0.01, momentum="update", l2=5e-4, iters=100, display_iters=20)
     ap.add_argument("--model", default="alexnet",
-                    choices=["alexnet", "nin", "vgg_a", "resnet10", "resnet18", "resnet34", "resnet18_var",
+                    choices=["alexnet", "nin", "vgg_a", "vgg_a_avgpool", "resnet10", "resnet18", "resnet20", "resnet34",
+                             "resnet18_var",
                              "resnet34_var"])
     ap.add_argument("--model-file", default=None)
     args = ap.parse_args(argv)

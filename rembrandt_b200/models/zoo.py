@@ -141,9 +141,8 @@ def _nin_final_hw(in_hw):
     return hw
 
 
-def vgg_a(num_classes=1000, in_hw=224, raw_hw=256, mean=None):
-    """VGG-A: 8 conv3x3 + 3 fc, dropout 0.5, Kaiming conv init, U(+-0.01) fc (src/templates/vgg.rs:50-260)."""
-    k, u = ParamsInit.kaiming(), ParamsInit.uniform(0.01)
+def _vgg_a_trunk(in_hw, raw_hw, mean):
+    k = ParamsInit.kaiming()
     pre = []
     if mean is not None:
         pre.append(Preproc("subtract_mean", mean=mean))
@@ -151,13 +150,29 @@ def vgg_a(num_classes=1000, in_hw=224, raw_hw=256, mean=None):
     if raw_hw and raw_hw > in_hw:
         src = raw_hw
         pre += [Preproc("flip_x"), Preproc("crop", crop_width=in_hw, crop_height=in_hw)]
-    cfg = SequentialOperatorConfig().data3d(Data3dCfg((src, src, 3), preprocs=pre))
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((src, src, 3), normalize=True, preprocs=pre))
     i = 0
     for ch, reps in ((64, 1), (128, 1), (256, 2), (512, 2), (512, 2)):
         for _ in range(reps):
             i += 1
             cfg.conv2d(Conv2dCfg(3, 1, 1, ch, Act.RECT, k), f"conv{i}")
         cfg.pool2d(Pool2dCfg(2, 2, 0, PoolKind.MAX), f"pool{i}")
+    return cfg
+
+
+def vgg_a_avgpool(num_classes=1000, in_hw=256, mean=None):
+    """The VGG-A convolutions followed by a global average pool and one classifier layer instead of the three fully
+    connected ones (tools/train-imagenet.rs:270-468; 256 x 256 input, 8 x 8 average pool)."""
+    cfg = _vgg_a_trunk(in_hw, None, mean)
+    cfg.pool2d(Pool2dCfg(in_hw // 32, 1, 0, PoolKind.AVERAGE), "global_pool")
+    cfg.affine(AffineCfg(num_classes, Act.IDENTITY, ParamsInit.xavier()), "fc")
+    return cfg.softmax_kl_loss(SoftmaxKLLossCfg(num_classes))
+
+
+def vgg_a(num_classes=1000, in_hw=224, raw_hw=256, mean=None):
+    """VGG-A: 8 conv3x3 + 3 fc, dropout 0.5, Kaiming conv init, U(+-0.01) fc (src/templates/vgg.rs:50-260)."""
+    u = ParamsInit.uniform(0.01)
+    cfg = _vgg_a_trunk(in_hw, raw_hw, mean)
     cfg.affine(AffineCfg(4096, Act.RECT, u), "fc6").dropout(DropoutCfg(0.5), "drop6")
     cfg.affine(AffineCfg(4096, Act.RECT, u), "fc7").dropout(DropoutCfg(0.5), "drop7")
     cfg.affine(AffineCfg(num_classes, Act.IDENTITY, u), "fc8")
@@ -233,6 +248,12 @@ def resnet34_var(num_classes=1000, in_hw=224, scale=(256, 480), max_hw=640, chan
                             variable=(scale[0], scale[1], max_hw))
 
 
+def resnet20(num_classes=1000, in_hw=224, raw_hw=256, mean=None, pca=True, ema=0.1):
+    """The 20-layer ImageNet variant of the reference's tool: 2 / 2 / 2 / 3 basic blocks
+    (tools/train-imagenet.rs:731-876)."""
+    return _imagenet_resnet((2, 2, 2, 3), num_classes, in_hw, raw_hw, mean, pca, ema)
+
+
 def resnet10(num_classes=1000, in_hw=224, raw_hw=256, mean=None):
     """ResNet-10 (tools/train-imagenet.rs)."""
     return _imagenet_resnet((1, 1, 1, 1), num_classes, in_hw, raw_hw, mean, False, 0.1)
@@ -291,7 +312,8 @@ def go_policy_resnet(planes=32, channels=128, blocks=5, num_classes=361):
 
 TEMPLATES = {
     "mnist_fc1": mnist_fc1, "mnist_fc2": mnist_fc2, "lenet": lenet, "cifar_krizh26": cifar_krizh26,
-    "alexnet": alexnet, "nin": nin, "vgg_a": vgg_a, "resnet10": resnet10, "resnet18": resnet18,
+    "alexnet": alexnet, "nin": nin, "vgg_a": vgg_a, "vgg_a_avgpool": vgg_a_avgpool, "resnet10": resnet10,
+    "resnet18": resnet18, "resnet20": resnet20,
     "resnet34": resnet34, "resnet18_var": resnet18_var, "resnet34_var": resnet34_var,
     "resnet20_cifar": resnet20_cifar, "go_policy_net": go_policy_net, "go_policy_resnet": go_policy_resnet,
 }

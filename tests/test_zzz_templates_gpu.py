@@ -18,6 +18,8 @@ CASES = [
     ("cifar_krizh26", lambda: zoo.cifar_krizh26(), (3, 32, 32), 10, 8),
     ("resnet20_cifar", lambda: zoo.resnet20_cifar(), (3, 32, 32), 10, 4),
     ("vgg_a", lambda: zoo.vgg_a(), (3, 256, 256), 1000, 2),
+    ("vgg_a_avgpool", lambda: zoo.vgg_a_avgpool(), (3, 256, 256), 1000, 2),
+    ("resnet20", lambda: zoo.resnet20(), (3, 256, 256), 1000, 2),
     ("resnet10", lambda: zoo.resnet10(), (3, 256, 256), 1000, 2),
     ("resnet34", lambda: zoo.resnet34(), (3, 256, 256), 1000, 2),
 ]
