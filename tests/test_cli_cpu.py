@@ -96,7 +96,7 @@ def test_tool_resumes_from_the_latest_state_or_a_given_iteration(tmp_path):
 
 @pytest.mark.parametrize("tool", ["train_mnist", "dist_train_mnist", "train_cifar10", "train_imagenet",
                                   "dist_train_imagenet", "train_gogod", "run_rembrandt", "bench_conv", "bench_gemm",
-                                  "bench_allreduce", "bench_link", "bench_tma", "bench_kernels", "data_tools",
+                                  "bench_allreduce", "bench_link", "bench_tma", "bench_kernels", "bench_loader", "data_tools",
                                   "test_dist"])
 def test_every_tool_imports_and_prints_its_help(tool, capsys):
     import importlib
@@ -184,3 +184,11 @@ def test_imagenet_tool_on_a_jpeg_record_store_of_ragged_images(tmp_path, monkeyp
     sgd = dist_train_imagenet.main(["--device", "cpu", "--batch", "2", "--minibatch", "4", "--iters", "2",
                                     "--display-iters", "1", "--model", "resnet18_var", "--data", str(tmp_path / "in.data")])
     assert sgd.engine.iter == 2 and sgd.engine.accum == 2
+
+
+def test_loader_benchmark_runs_and_the_native_loader_wins():
+    from rembrandt_b200.cli import bench_loader
+    rows = bench_loader.main(["--shape", "3", "32", "32", "--samples", "512", "--batch", "32", "--batches", "16",
+                              "--threads", "2"])
+    by = {r["loader"]: r["images_per_s"] for r in rows}
+    assert by["native x2"] > by["python iterators"] > 0
