@@ -60,9 +60,10 @@ def base_parser(desc, **defaults):
     ap.add_argument("--synthetic-size", type=int, default=4096)
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--native-loader", type=int, default=0, metavar="THREADS",
+    ap.add_argument("--native-loader", type=int, default=-1, metavar="THREADS",
                     help="assemble training batches with this many C++ prefetch threads (shuffled epochs over the "
-                         "rank's shard, pinned ring buffers) instead of the Python iterators")
+                         "rank's shard, pinned ring buffers) instead of the Python iterators; 0 = Python iterators; "
+                         "default: 2 threads for sources that map to arrays (MNIST, CIFAR-10 files), else Python")
     ap.add_argument("--straggler-ranks", type=int, nargs="*", default=[])
     ap.add_argument("--straggler-max-delay-ms", type=int, default=0)
     ap.add_argument("--report-port", type=int, default=0, help="serve a live loss report on this port")
@@ -142,6 +143,8 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
         print(net.describe())
     engine = StepEngine(net, opt, worker, use_graph=not args.no_graph)
     ragged = bool(getattr(model_cfg.input_op.cfg, "variable_size", False))    # images of different sizes
+    if args.native_loader < 0:      # the Python chain assembles ~18 000 samples/s whatever their size: too slow for one GPU
+        args.native_loader = 2 if hasattr(source, "as_arrays") and not ragged else 0
     if args.native_loader > 0 and not ragged:
         from ..data.datasets import source_arrays
         from ..data.native_loader import NativeBatchLoader

@@ -192,3 +192,24 @@ def test_loader_benchmark_runs_and_the_native_loader_wins():
                               "--threads", "2"])
     by = {r["loader"]: r["images_per_s"] for r in rows}
     assert by["native x2"] > by["python iterators"] > 0
+
+
+def test_array_backed_sources_use_the_native_loader_by_default(tmp_path, monkeypatch):
+    import numpy as np
+    from rembrandt_b200.data import native_loader
+    rng = np.random.default_rng(3)
+    recs = rng.integers(0, 256, (64, 3073), dtype=np.uint8)
+    recs[:, 0] %= 10
+    (tmp_path / "batch.bin").write_bytes(recs.tobytes())
+    (tmp_path / "c.data").write_text(f'[dataset.train]\nsource = "cifar10"\ndata_path = "{tmp_path / "batch.bin"}"\n')
+    made = []
+    real = native_loader.NativeBatchLoader.__init__
+
+    def spy(self, *a, **k):
+        made.append(k.get("threads"))
+        return real(self, *a, **k)
+    monkeypatch.setattr(native_loader.NativeBatchLoader, "__init__", spy)
+    assert train_cifar10.main(TINY + ["--data", str(tmp_path / "c.data")]).engine.iter == 3
+    assert made == [2]
+    assert train_cifar10.main(TINY + ["--data", str(tmp_path / "c.data"), "--native-loader", "0"]).engine.iter == 3
+    assert made == [2]
