@@ -59,6 +59,37 @@ def measure(shape, samples, batch, batches, threads_list):
     return rows
 
 
+def measure_lmdb(shape, samples, batch, batches, threads_list):
+    """The same comparison over a Caffe image database written to a temporary directory: the C++ loader reading the
+    memory-mapped environment against the Python cursor + `Datum` decode (`LmdbCaffeShard`)."""
+    import tempfile
+    from ..data.codecs import encode_caffe_datum
+    from ..data.lmdb_reader import LmdbCaffeShard, write_env
+    rng = np.random.default_rng(0)
+    c, h, w = shape
+    per_image = c * h * w
+    rows = []
+    with tempfile.TemporaryDirectory() as d:
+        write_env(d, [(b"%08d" % i, encode_caffe_datum(rng.integers(0, 256, per_image, dtype=np.uint8).tobytes(), c, h, w,
+                                                       label=i % 1000)) for i in range(samples)])
+        for threads in threads_list:
+            ld = NativeBatchLoader.from_caffe_lmdb(d, (c, h, w), batch, mode="shuffled", threads=threads, slots=6, pin=False)
+            for _ in range(3):
+                next(ld)
+            t0 = time.perf_counter()
+            for _ in range(batches):
+                next(ld)
+            dt = time.perf_counter() - t0
+            ld.close()
+            rows.append({"loader": f"native lmdb x{threads}", "images_per_s": batches * batch / dt,
+                         "gb_per_s": batches * batch * per_image / dt / 1e9})
+        t0 = time.perf_counter()
+        n = sum(1 for _ in LmdbCaffeShard(d))
+        dt = time.perf_counter() - t0
+        rows.append({"loader": "python lmdb cursor", "images_per_s": n / dt, "gb_per_s": n * per_image / dt / 1e9})
+    return rows
+
+
 def _forever(it):
     while True:
         for x in it:
@@ -72,8 +103,10 @@ def main(argv=None):
     ap.add_argument("--batch", type=int, default=128)
     ap.add_argument("--batches", type=int, default=64)
     ap.add_argument("--threads", type=int, nargs="+", default=[1, 2, 4, 8])
+    ap.add_argument("--lmdb", action="store_true", help="read the samples from a Caffe image database instead of arrays")
     args = ap.parse_args(argv)
-    rows = measure(args.shape, args.samples, args.batch, args.batches, args.threads)
+    fn = measure_lmdb if args.lmdb else measure
+    rows = fn(args.shape, args.samples, args.batch, args.batches, args.threads)
     for r in rows:
         print(f"{r['loader']:<18s} {r['images_per_s']:12.0f} images/s {r['gb_per_s']:8.2f} GB/s")
     print(json.dumps({"shape": args.shape, "batch": args.batch, "rows": rows}))

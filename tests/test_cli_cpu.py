@@ -192,6 +192,9 @@ def test_loader_benchmark_runs_and_the_native_loader_wins():
                               "--threads", "2"])
     by = {r["loader"]: r["images_per_s"] for r in rows}
     assert by["native x2"] > by["python iterators"] > 0
+    rows = bench_loader.main(["--lmdb", "--shape", "3", "16", "16", "--samples", "256", "--batch", "32", "--batches", "8",
+                              "--threads", "2"])
+    assert {r["loader"] for r in rows} == {"native lmdb x2", "python lmdb cursor"}
 
 
 def test_array_backed_sources_use_the_native_loader_by_default(tmp_path, monkeypatch):
