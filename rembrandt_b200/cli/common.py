@@ -12,7 +12,7 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..data import (AsyncQueueDataIter, BatchIter, RaggedBatchIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
+from ..data import (AsyncPoolDataIter, AsyncQueueDataIter, BatchIter, RaggedBatchIter, RandomIndexIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
                     compute_mean, open_data_file, open_split, partition_shard)
 from ..engine import StepEngine
 from ..models.net import Net
@@ -64,6 +64,8 @@ def base_parser(desc, **defaults):
                     help="assemble training batches with this many C++ prefetch threads (shuffled epochs over the "
                          "rank's shard, pinned ring buffers) instead of the Python iterators; 0 = Python iterators; "
                          "default: 2 threads for sources that map to arrays (MNIST, CIFAR-10 files), else Python")
+    ap.add_argument("--decode-threads", type=int, default=1,
+                    help="decode samples (JPEG records, database cursors) on this many Python threads, order preserved")
     ap.add_argument("--straggler-ranks", type=int, nargs="*", default=[])
     ap.add_argument("--straggler-max-delay-ms", type=int, default=0)
     ap.add_argument("--report-port", type=int, default=0, help="serve a live loss report on this port")
@@ -164,7 +166,12 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
             train_iter = NativeBatchLoader(imgs, lbls, args.batch, mode="shuffled", seed=args.seed + rank,
                                            threads=args.native_loader, shard=shard)
     else:
-        samples = AsyncQueueDataIter(RandomSampleDataIter(partition_shard(source, rank, world), seed=(args.seed + rank, 99)))
+        shard = partition_shard(source, rank, world)
+        if args.decode_threads > 1:    # e.g. JPEG records: the decoder releases the interpreter lock, so threads scale
+            samples = AsyncPoolDataIter(RandomIndexIter(len(shard), seed=(args.seed + rank, 99)), shard.__getitem__,
+                                        num_workers=args.decode_threads)
+        else:
+            samples = AsyncQueueDataIter(RandomSampleDataIter(shard, seed=(args.seed + rank, 99)))
         if ragged:
             train_iter = RaggedBatchIter(samples, args.batch, model_cfg.input_op.cfg.max_dims or dims)
         else:

@@ -3,6 +3,6 @@ from .datasets import (Cifar10DataSource, DataSource, MnistDataSource, Synthetic
                        open_data_file, open_split)
 from .iterators import (AsyncPoolDataIter, AsyncQueueDataIter, AugmentDataSource, BatchIter,  # noqa: F401
                         CyclicEpisodeIterator, CyclicSampleDataIter, ParallelJoinDataIter, PartitionDataSource,
-                        RaggedBatchIter, RandomEpisodeIterator, RandomSampleDataIter, RangeDataShard, RangeWrapDataShard,
+                        RaggedBatchIter, RandomEpisodeIterator, RandomIndexIter, RandomSampleDataIter, RangeDataShard, RangeWrapDataShard,
                         SampleIterator, SequentialSampleIter, TransformDataIter, cyclic_partition_shard,
                         episode_ranges, partition_shard)

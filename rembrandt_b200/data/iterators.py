@@ -83,6 +83,19 @@ class RandomSampleDataIter:
             yield self.shard[self.rng.below(n)]
 
 
+class RandomIndexIter:
+    """The index stream of `RandomSampleDataIter` without the samples (uniform with replacement, len(shard) per pass):
+    fed to `AsyncPoolDataIter` with `shard.__getitem__` as the transform, it decodes samples on several threads while
+    keeping the order of the draws."""
+
+    def __init__(self, n: int, seed=(1, 2)):
+        self.n, self.rng = n, XorShift128Plus(*seed)
+
+    def __iter__(self):
+        for _ in range(self.n):
+            yield self.rng.below(self.n)
+
+
 class CyclicSampleDataIter:
     """Endless sequential passes (validation in the reference iterates a fixed number of samples off this)."""
 

@@ -184,6 +184,11 @@ def test_imagenet_tool_on_a_jpeg_record_store_of_ragged_images(tmp_path, monkeyp
     sgd = dist_train_imagenet.main(["--device", "cpu", "--batch", "2", "--minibatch", "4", "--iters", "2",
                                     "--display-iters", "1", "--model", "resnet18_var", "--data", str(tmp_path / "in.data")])
     assert sgd.engine.iter == 2 and sgd.engine.accum == 2
+    # the same run with the JPEG decode spread over three threads draws the same samples in the same order
+    again = dist_train_imagenet.main(["--device", "cpu", "--batch", "2", "--minibatch", "4", "--iters", "2",
+                                      "--display-iters", "1", "--model", "resnet18_var", "--data", str(tmp_path / "in.data"),
+                                      "--decode-threads", "3"])
+    assert [h[1] for h in again.history] == pytest.approx([h[1] for h in sgd.history], rel=1e-5)
 
 
 def test_loader_benchmark_runs_and_the_native_loader_wins():
