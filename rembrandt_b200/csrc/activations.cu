@@ -39,8 +39,13 @@ __global__ void act_fwd_kernel(bf16* __restrict__ y, long long rows, int ld, int
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
        g += (long long)gridDim.x * blockDim.x) {
     const int c0 = (int)(g % gpr) * 8;
-    if (c0 >= n_valid) continue;
     float v[8];
+    if (c0 >= n_valid) {  // a group that lies wholly in the padding: written as zeros, never left as it was
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      store8(y + g * 8, v);
+      continue;
+    }
     load8(y + g * 8, v);
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = (c0 + j < n_valid) ? act_apply(v[j], kind, bound) : 0.f;
@@ -56,8 +61,13 @@ __global__ void act_bwd_kernel(bf16* __restrict__ d, const bf16* __restrict__ y,
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
        g += (long long)gridDim.x * blockDim.x) {
     const int c0 = (int)(g % gpr) * 8;
-    if (c0 >= n_valid) continue;
     float v[8], o[8];
+    if (c0 >= n_valid) {  // padded columns of the delta must come out zero whatever came in
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+      store8(d + g * 8, v);
+      continue;
+    }
     load8(d + g * 8, v);
     load8(y + g * 8, o);
 #pragma unroll
