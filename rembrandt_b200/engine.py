@@ -119,7 +119,9 @@ class StepEngine:
     def _update_in_order(self):
         o, c, st, net = self.opt, self.comm, self.stepper, self.net
         lr = self.lr
-        communicate = c.num_workers() > 1 and (self.iter % max(1, o.comm_interval) == 0)
+        # the reference counts the iteration before it tests the interval (src/opt/sgd/new.rs:372,402): exchanges
+        # happen at iterations k, 2k, ...
+        communicate = c.num_workers() > 1 and ((self.iter + 1) % max(1, o.comm_interval) == 0)
         if o.sync_order == SyncOrder.SYNC_GRADS_THEN_STEP:
             if self._overlapped():
                 c.fused_grads_step(st, lr)

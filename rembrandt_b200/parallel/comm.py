@@ -250,11 +250,13 @@ def _exchange(flat: torch.Tensor, send_to: int, recv_from: int, rank: int, group
         return recv
     if send_to == rank and recv_from == rank:
         return None
+    # point-to-point operations name their peer by global rank; `send_to` / `recv_from` are ranks within `group`
+    to_global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
     ops = []
     if send_to != rank:
-        ops.append(dist.P2POp(dist.isend, flat, send_to, group))
+        ops.append(dist.P2POp(dist.isend, flat, to_global(send_to), group))
     if recv_from != rank:
-        ops.append(dist.P2POp(dist.irecv, recv, recv_from, group))
+        ops.append(dist.P2POp(dist.irecv, recv, to_global(recv_from), group))
     for w in dist.batch_isend_irecv(ops):
         w.wait()
     return recv
@@ -350,6 +352,7 @@ class PushGossipComm(CommWorker):
     def __init__(self, group=None, seed=(41, 43)):
         super().__init__(group)
         self.rng = XorShift128Plus(seed[0] + 7919 * self.rank, seed[1])
+        self._global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
 
     def sync_params(self, flat, repeat=False):
         if self.world <= 1:
@@ -359,10 +362,10 @@ class PushGossipComm(CommWorker):
         dist.all_gather_object(targets, target, group=self.group)
         senders = [r for r in range(self.world) if targets[r] == self.rank and r != self.rank]
         bufs = [torch.empty_like(flat) for _ in senders]
-        ops = [dist.P2POp(dist.irecv, b, r, self.group) for b, r in zip(bufs, senders)]
+        ops = [dist.P2POp(dist.irecv, b, self._global(r), self.group) for b, r in zip(bufs, senders)]
         snapshot = flat.clone()
         if target != self.rank:
-            ops.append(dist.P2POp(dist.isend, snapshot, target, self.group))
+            ops.append(dist.P2POp(dist.isend, snapshot, self._global(target), self.group))
         if ops:
             for w in dist.batch_isend_irecv(ops):
                 w.wait()

@@ -270,11 +270,19 @@ class SgdOpt:
         self._check_device_status(t)
         while not comm.wait_barrier():
             time.sleep(0.001)
+        # a backend that shards the fp32 master (fused all-reduce + SGD) holds only this rank's shard up to date:
+        # the snapshot, the state blob and the restore below all need the complete vector
+        if hasattr(comm, "gather_master"):
+            comm.gather_master()
+        # the training loop keeps Nesterov parameters at the look-ahead point w + mu v; the reference takes the
+        # extra momentum off before the update and puts it back after the checkpoint window
+        # (src/opt/sgd/new.rs:360-369,623-634), so blobs hold the plain w and a resumed run applies it once
+        nesterov = cfg.momentum == Momentum.UPDATE_NESTEROV
+        if nesterov:
+            eng.stepper.nesterov_lookahead(-1.0)
         if cfg.checkpoint == CheckpointBehavior.DISCARD:
             net.save_params()
         if cfg.checkpoint_dir and cfg.save_iters and t % cfg.save_iters == 0:
-            if hasattr(comm, "gather_master"):
-                comm.gather_master()
             ckpt.checkpoint_state(net, cfg.checkpoint_dir, self.rank)
         comm.exact_sync(net.params)
         net.refresh_shadow()
@@ -284,6 +292,8 @@ class SgdOpt:
             self.validate(valid_data, cfg.valid_iters, t, t_start)
         if cfg.checkpoint == CheckpointBehavior.DISCARD:
             net.restore_params()
+        if nesterov:
+            eng.stepper.nesterov_lookahead(+1.0)
         comm.barrier()
 
     # ------------------------------------------------------------------ validation

@@ -295,7 +295,7 @@ def _rule_and_order(rank, world, mode_value, order_value, interval=1, accum=1):
             g[r] = g[r] + n.grads.detach().numpy().astype(np.float64)
         if (s + 1) % accum:
             continue                                   # inside a gradient-accumulation group
-        it = (s + 1) // accum - 1                      # iteration counter before this update
+        it = (s + 1) // accum                          # the iteration is counted before the interval is tested
         if it % interval:
             mean_now = lambda xs: xs                   # no exchange in this iteration
         else:

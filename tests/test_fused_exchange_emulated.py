@@ -354,3 +354,68 @@ def test_data_parallel_engines_over_the_fused_exchange_equal_one_process_on_the_
     got = W.nets[0].params16.float()
     rel = float((got - want).norm() / want.norm())
     assert rel < 2e-2, rel
+
+
+@pytest.mark.parametrize("rule", [Momentum.UPDATE, Momentum.UPDATE_NESTEROV])
+def test_checkpoint_window_leaves_sharded_replicas_as_they_were(monkeypatch, tmp_path, rule):
+    """The master is sharded: between gathers a rank's fp32 vector is current only in its own shard. A checkpoint
+    window (snapshot, exact synchronisation, blob, restore) must assemble the master before it snapshots, or the
+    restore would write stale weights over the live compute copy. After the window every rank's bf16 weights are what
+    they were, identical across ranks, and every rank holds the complete fp32 master."""
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.optim.sgd import CheckpointBehavior, SgdOptConfig, StepSizeSchedule
+    from rembrandt_b200.trainer import SgdOpt
+    world, batch = 2, 4
+    monkeypatch.setattr(torch.Tensor, "pin_memory", lambda self, *a, **k: self)
+    W = World(monkeypatch, world, zoo.lenet, batch, rule, min_bucket_bytes=1 << 10, one_shot_bytes=16 << 10)
+    opt = SgdOptConfig(minibatch_size=batch, step_size=StepSizeSchedule.constant(0.01), momentum=rule, mu=0.9,
+                       l2_reg_coef=1e-3, display_iters=0, checkpoint=CheckpointBehavior.DISCARD,
+                       checkpoint_dir=str(tmp_path), save_iters=1, checkpoint_iters=1)
+    engines = [StepEngine(W.nets[r], opt, W.comms[r], use_graph=False) for r in range(world)]
+    with torch.no_grad():
+        for n in W.nets:
+            n.params.copy_(n.params16.float())
+    g = torch.Generator().manual_seed(11)
+    for step in range(3):
+        for r in range(world):
+            W.current = r
+            x = torch.randint(0, 256, (batch, 1, 28, 28), dtype=torch.uint8, generator=g)
+            y = torch.randint(0, 10, (batch,), dtype=torch.int32, generator=g)
+            engines[r].feed(x, y)
+            engines[r].step()
+        W.run_queued()
+    assert not torch.equal(W.nets[0].params, W.nets[1].params), "the masters should be sharded (each stale elsewhere)"
+
+    gathered = set()
+
+    def gather(comm):          # owners hand their shards of master and momentum to everybody (all ranks live here)
+        # the windows of the ranks run one after the other here, not in lockstep: only the first gather of a window
+        # sees every rank in the same state, so the later ones (a no-op between identical replicas) are skipped
+        if comm.rank in gathered:
+            return
+        gathered.add(comm.rank)
+        for _, off, n, _slot in comm.launches:
+            if n <= comm.one_shot_elems:
+                continue
+            for r, (s0, s1) in enumerate(comm.shard_bounds(n)):
+                for dst in W.nets:
+                    dst.params[off + s0: off + s1] = W.nets[r].params[off + s0: off + s1]
+                    dst.mom[off + s0: off + s1] = W.nets[r].mom[off + s0: off + s1]
+
+    before16 = [n.params16.clone() for n in W.nets]
+    for r in range(world):
+        c = W.comms[r]
+        monkeypatch.setattr(c, "gather_master", lambda c=c: gather(c), raising=False)
+        monkeypatch.setattr(c, "barrier", lambda: None, raising=False)
+        monkeypatch.setattr(c, "signal_barrier", lambda: None, raising=False)
+        monkeypatch.setattr(c, "allreduce_stats", lambda v: list(v), raising=False)
+        monkeypatch.setattr(engines[r], "flush", lambda: None)
+        monkeypatch.setattr(engines[r], "synchronize", lambda: None)
+        sgd = SgdOpt(opt, engines[r], quiet=True)
+        monkeypatch.setattr(sgd, "_check_device_status", lambda t: None)
+        sgd._checkpoint_window(3, None, 0.0)
+    assert torch.equal(W.nets[0].params16, W.nets[1].params16)
+    for r in range(world):
+        assert torch.equal(W.nets[r].params16, before16[r]), f"rank {r}: the window changed the live compute weights"
+    # both now hold the assembled master (taking the Nesterov look-ahead off and putting it back rounds in fp32)
+    assert torch.allclose(W.nets[0].params, W.nets[1].params, atol=1e-6)

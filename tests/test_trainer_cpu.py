@@ -82,9 +82,10 @@ def test_gradient_accumulation_equals_one_large_batch():
     assert torch.allclose(net_a.params.detach(), net_b.params.detach(), atol=1e-6)
 
 
-def test_trace_csv_checkpoint_and_resume(tmp_path):
+@pytest.mark.parametrize("rule", [Momentum.UPDATE, Momentum.UPDATE_NESTEROV])
+def test_trace_csv_checkpoint_and_resume(tmp_path, rule):
     d = str(tmp_path / "run")
-    common = dict(checkpoint_iters=4, save_iters=4, checkpoint_dir=d)
+    common = dict(checkpoint_iters=4, save_iters=4, checkpoint_dir=d, momentum=rule)
     opt, eng, net = make(batch=16, **common)
     sgd = SgdOpt(opt, eng, quiet=True)
     sgd.train(mnist_shape_batches(1, 16, 8), None, max_iters=8)
@@ -95,7 +96,7 @@ def test_trace_csv_checkpoint_and_resume(tmp_path):
     assert open(os.path.join(d, "checkpoint")).read() == "8\n"
     assert os.path.exists(os.path.join(d, "params.t_4.blob")) and os.path.exists(os.path.join(d, "state.latest.blob.0"))
     # an uninterrupted 12-iteration run ...
-    opt_u, eng_u, net_u = make(batch=16)
+    opt_u, eng_u, net_u = make(batch=16, momentum=rule)
     SgdOpt(opt_u, eng_u, quiet=True).train(mnist_shape_batches(1, 16, 12), None, max_iters=12)
     # ... equals resuming from the checkpoint at 8 and running 4 more on the same data stream
     opt_r, eng_r, net_r = make(batch=16, **common)
