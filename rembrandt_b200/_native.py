@@ -24,9 +24,14 @@ f32 = C.c_float
 
 _CUDA_SIGS = {
     # gemm_tc.cu
-    "rb_gemm_tc": [vp, i32, i64, vp, i32, i64, i32, i32, i32, vp, i64, i32, vp, i32, vp, i32, i32, i32, i32, vp, vp],
+    "rb_gemm_tc": [vp, i32, i64, vp, i32, i64, i32, i32, i32, vp, i64, i32, vp, i32, vp, i32, i32, i32, i32, vp, i64,
+                   vp, vp],
     "rb_conv_fprop_tc": [vp, i32, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, i64, vp, i32, vp,
-                         i32, i32, vp, vp],
+                         i32, i32, vp, i64, vp, vp],
+    "rb_gemm_set_option": [vp, i32],
+    "rb_gemm_get_option": [vp, vp],
+    "rb_gemm_tune_mode": [i32],
+    "rb_gemm_clear_plans": [],
     "rb_conv_wgrad_tc": [vp, i32, i32, i32, i32, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp],
     "rb_num_sms": [],
     # conv_direct.cu
@@ -56,8 +61,6 @@ _CUDA_SIGS = {
     "rb_pointwise_loss": [vp, i32, i32, i32, vp, vp, f32, vp, vp, vp, i32, vp],
     "rb_softmax_ce": [vp, i32, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     # sgd_fused.cu
-    "rb_tma_probe_tiled": [vp, i64, i32, i32, i32, i32, i32, i32, i64, i32, i32, vp, vp],
-    "rb_tma_probe_conv_stage": [vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp],
     "rb_sgd_fused": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, vp],
     "rb_sgd_fused_grid": [vp, vp, vp, vp, i64, f32, f32, f32, f32, i32, i32, i32, i32, vp],
     "rb_axpy_shadow": [vp, vp, vp, i64, f32, vp],

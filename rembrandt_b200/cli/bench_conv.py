@@ -35,11 +35,17 @@ SHAPES = {
 }
 
 
-def run(name, batch, passes, iters, warmup):
+def run(name, batch, passes, iters, warmup, tune=True):
     C, H, W, Ko, R, s, p = SHAPES[name]
     Cp, Kp = K.pad_channels(C), K.pad_channels(Ko)
     P, Q = (H + 2 * p - R) // s + 1, (W + 2 * p - R) // s + 1
     dev = "cuda"
+    if tune:
+        # what a network does when it is built: the tile plans of the two overwrite-mode passes are measured once
+        K.tune_conv(batch, H, W, Cp, Ko, R, R, s, p, p, P, Q, Kp, relu=True, has_bias=True, n_valid=Ko, n_store=Kp)
+        if s == 1:
+            K.tune_conv(batch, P, Q, Kp, Cp, R, R, 1, R - 1 - p, R - 1 - p, H, W, Cp, has_mask=True, n_valid=C,
+                        n_store=Cp)
     x = torch.randn(batch, H, W, Cp, device=dev).bfloat16()
     w = (torch.randn(Ko, R * R, Cp, device=dev) * 0.05).bfloat16()
     wt = torch.zeros(Cp, R * R, Kp, device=dev, dtype=torch.bfloat16)
@@ -78,10 +84,11 @@ def main(argv=None):
     ap.add_argument("--pass", dest="passes", default="all", choices=["all", "fprop", "dgrad", "wgrad"])
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-tune", action="store_true", help="take the cost model's tile plans instead of measured ones")
     args = ap.parse_args(argv)
     names = sorted(SHAPES) if args.shape == "all" else [args.shape]
     for n in names:
-        print(json.dumps(run(n, args.batch, args.passes, args.iters, args.warmup)))
+        print(json.dumps(run(n, args.batch, args.passes, args.iters, args.warmup, tune=not args.no_tune)))
 
 
 if __name__ == "__main__":

@@ -28,7 +28,12 @@
 namespace rb {
 
 constexpr int MAX_RANKS = 8;
-constexpr uint64_t PEER_WAIT_NS = 3000000000ull;  // 3 s
+constexpr uint64_t PEER_WAIT_NS = 3000000000ull;  // default limit of a wait on a peer: 3 s
+
+// Every argument block carries `wait_ns`, the limit of each wait on a peer in this launch; 0 takes the default.
+__device__ __forceinline__ uint64_t wait_limit(long long wait_ns) {
+  return wait_ns > 0 ? (uint64_t)wait_ns : PEER_WAIT_NS;
+}
 
 struct ArSgdArgs {
   float* grads[MAX_RANKS];     // peer-visible buffers, identical layout on every rank
@@ -48,6 +53,7 @@ struct ArSgdArgs {
   int rank, world, slot, one_shot, op, zero_grads;
   float avg_scale;             // op 1: result = sum * avg_scale
   SgdHyper h;
+  long long wait_ns;           // limit of each wait on a peer, ns (0: the 3 s default)
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
@@ -59,13 +65,13 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 // true once *p has reached `epoch` (wrap-around safe); false after the deadline
-__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch) {
+__device__ __forceinline__ bool wait_epoch(const uint32_t* p, uint32_t epoch, uint64_t limit_ns) {
   if ((int32_t)(ld_acquire_sys(p) - epoch) >= 0) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (true) {
     if ((int32_t)(ld_acquire_sys(p) - epoch) >= 0) return true;
-    if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > PEER_WAIT_NS) return false;
+    if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > limit_ns) return false;
   }
 }
 __device__ __forceinline__ float4 ld_f4(const float* p) {
@@ -93,13 +99,13 @@ __device__ __forceinline__ uint32_t* flag_at(uint32_t* pad, int slot, int phase,
 
 // All threads of the block return the same answer.
 __device__ __forceinline__ bool start_barrier(uint32_t* const* flags, int rank, int world, int slot, uint32_t epoch,
-                                              unsigned int* status) {
+                                              unsigned int* status, uint64_t limit_ns) {
   if (blockIdx.x == 0 && threadIdx.x < world) {
     __threadfence_system();
     st_release_sys(flag_at(flags[threadIdx.x], slot, 0, rank), epoch);
   }
   int ok = 1;
-  if (threadIdx.x < world) ok = wait_epoch(flag_at(flags[rank], slot, 0, threadIdx.x), epoch) ? 1 : 0;
+  if (threadIdx.x < world) ok = wait_epoch(flag_at(flags[rank], slot, 0, threadIdx.x), epoch, limit_ns) ? 1 : 0;
   ok = __syncthreads_and(ok);
   if (!ok && threadIdx.x == 0) atomicOr(status, RB_STATUS_PEER_TIMEOUT);
   return ok != 0;
@@ -109,7 +115,8 @@ __device__ __forceinline__ bool start_barrier(uint32_t* const* flags, int rank, 
 // is done with the epoch and waits until every peer has said the same, so that when the kernel ends nobody
 // still reads this rank's buffers and every store of a peer into this rank's memory has landed.
 __device__ __forceinline__ void end_barrier(uint32_t* const* flags, int rank, int world, int slot, uint32_t epoch,
-                                            unsigned int* block_counter, uint32_t* epoch_ptr, unsigned int* status) {
+                                            unsigned int* block_counter, uint32_t* epoch_ptr, unsigned int* status,
+                                            uint64_t limit_ns) {
   __shared__ int s_last;
   __threadfence_system();
   __syncthreads();
@@ -119,7 +126,7 @@ __device__ __forceinline__ void end_barrier(uint32_t* const* flags, int rank, in
   __threadfence_system();
   if (threadIdx.x < world) st_release_sys(flag_at(flags[threadIdx.x], slot, 1, rank), epoch);
   int ok = 1;
-  if (threadIdx.x < world) ok = wait_epoch(flag_at(flags[rank], slot, 1, threadIdx.x), epoch) ? 1 : 0;
+  if (threadIdx.x < world) ok = wait_epoch(flag_at(flags[rank], slot, 1, threadIdx.x), epoch, limit_ns) ? 1 : 0;
   ok = __syncthreads_and(ok);
   if (threadIdx.x == 0) {
     if (!ok) atomicOr(status, RB_STATUS_PEER_TIMEOUT);
@@ -210,10 +217,11 @@ __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __gr
   if (a.wait_ok) {
     ready = *reinterpret_cast<volatile uint32_t*>(a.wait_ok) == epoch;
   } else if (a.mc_grads) {
-    ready = start_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.status);
+    ready = start_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.status, wait_limit(a.wait_ns));
   } else {
     int ok = 1;
-    if (threadIdx.x < a.world) ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch) ? 1 : 0;
+    if (threadIdx.x < a.world)
+      ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch, wait_limit(a.wait_ns)) ? 1 : 0;
     ok = __syncthreads_and(ok);
     if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
     ready = ok != 0;
@@ -319,7 +327,7 @@ __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __gr
       }
     }
   }
-  end_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.block_counter, a.epoch_ptr, a.status);
+  end_barrier(a.flags, a.rank, a.world, a.slot, epoch, a.block_counter, a.epoch_ptr, a.status, wait_limit(a.wait_ns));
 }
 
 // The wait for the peers' phase-0 flags as a kernel of its own (one warp): the reducing kernel that follows in
@@ -332,7 +340,8 @@ __global__ void ar_wait_kernel(const __grid_constant__ ArSgdArgs a) {
     st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 0, a.rank), epoch);
   }
   int ok = 1;
-  if (threadIdx.x < a.world) ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch) ? 1 : 0;
+  if (threadIdx.x < a.world)
+    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch, wait_limit(a.wait_ns)) ? 1 : 0;
   ok = __all_sync(0xffffffffu, ok);
   if (threadIdx.x == 0) {
     if (!ok) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
@@ -360,6 +369,11 @@ struct MixArgs {
   float w_self;           // push gossip: weight of the own vector
   int not_last;           // gossip mix: 1 = another pull of the same round follows (keep the epoch, do not report done)
   int mix_self;           // gossip mix: 1 = a pull that lands on this rank mixes with its own published snapshot
+  long long wait_ns;      // limit of each wait on a peer, ns (0: the 3 s default)
+  unsigned long long* gate;   // asynchronous push gossip: the target's (push) or the own (fold) gate word;
+                              // asynchronous elastic averaging: the centre's lock word
+  int* ticket;            // local: what the `begin` kernel of an asynchronous exchange decided for the kernel that follows
+  unsigned int* skipped;  // local counter of exchanges given up because the centre stayed busy (may be null)
 };
 
 // pub[epoch & 1] <- w, then tell every peer that epoch is published. Before overwriting the buffer last used
@@ -368,7 +382,7 @@ __global__ void __launch_bounds__(512) publish_kernel(const __grid_constant__ Mi
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
   int ok = 1;
   if (epoch > 2u && threadIdx.x < a.world && threadIdx.x != a.rank)
-    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 1, threadIdx.x), epoch - 2u) ? 1 : 0;
+    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 1, threadIdx.x), epoch - 2u, wait_limit(a.wait_ns)) ? 1 : 0;
   ok = __syncthreads_and(ok);
   if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
   float* dst = a.pub_local + (size_t)(epoch & 1u) * a.n;
@@ -392,7 +406,7 @@ __global__ void __launch_bounds__(512) gossip_mix_kernel(const __grid_constant__
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
   int ok = 1;
   if (a.wait_peer && a.peer != a.rank && threadIdx.x == 0)
-    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, a.peer), epoch) ? 1 : 0;
+    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, a.peer), epoch, wait_limit(a.wait_ns)) ? 1 : 0;
   ok = __syncthreads_and(ok);
   if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
   // An asynchronous puller takes whichever snapshot the peer published last (nothing yet: no mixing). Blocks
@@ -513,6 +527,196 @@ __global__ void elastic_apply_kernel(float* __restrict__ center, float* __restri
   }
 }
 
+
+// --------------------------------------------------------------------------- asynchronous push gossip
+// The reference's asynchronous push gossip (src/worker/gossip_dist.rs:474-593 passive receiver, :883-976 active
+// side) has no barrier anywhere: a rank sends its vector to a random target whenever it gets there; a receiver
+// thread on the target accumulates whole vectors as they arrive and counts them; at its own exchange a rank pauses
+// its receiver, keeps (w_self x + received) / (w_self + count) -- or its own x when nothing arrived -- and
+// resumes. Ranks may be any number of iterations apart.
+//
+// Here the receiver thread is the target's memory: every rank owns two accumulators acc[0], acc[1] with a count
+// each, and a 64-bit gate word  [ epoch : 32 | pushes in flight into acc[1] : 16 | into acc[0] : 16 ].
+//   push_begin (one thread)   registers at the TARGET's gate with a compare-and-swap: reads the epoch, adds one to
+//                             the in-flight field of acc[epoch & 1]; the buffer index goes to the local ticket
+//   push_add   (grid)         red.add of the own vector into the target's acc[ticket] over NVLink; the last block
+//                             fences, adds 1 to that accumulator's count and takes the registration off the gate
+//   fold_begin (one thread)   adds 1 to the OWN gate's epoch (later pushes go to the other accumulator), then waits
+//                             -- bounded -- until the pushes still in flight into the closed accumulator are done:
+//                             a wait for transfers already under way, never for another rank to reach a round
+//   fold       (grid)         x <- (w_self x + acc[closed]) / (w_self + count[closed]) if count > 0; clears both
+// A push that registers after the epoch moved lands in the other accumulator and is folded one exchange later,
+// which is what a late message does in the reference.
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long atom_cas_sys_u64(unsigned long long* p, unsigned long long cmp,
+                                                               unsigned long long val) {
+  unsigned long long old;
+  asm volatile("atom.acq_rel.sys.global.cas.b64 %0, [%1], %2, %3;" : "=l"(old) : "l"(p), "l"(cmp), "l"(val) : "memory");
+  return old;
+}
+__device__ __forceinline__ unsigned long long atom_add_sys_u64(unsigned long long* p, unsigned long long val) {
+  unsigned long long old;
+  asm volatile("atom.acq_rel.sys.global.add.u64 %0, [%1], %2;" : "=l"(old) : "l"(p), "l"(val) : "memory");
+  return old;
+}
+__device__ __forceinline__ void red_add_sys_f4(float* p, float4 x) {
+  asm volatile("red.relaxed.sys.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(x.x), "f"(x.y), "f"(x.z),
+               "f"(x.w) : "memory");
+}
+constexpr int GATE_CAS_TRIES = 4096;
+
+// ticket: 0 / 1 = accumulator to push into, -1 = nothing to push (target is this rank, or registration failed)
+__global__ void push_begin_kernel(const __grid_constant__ MixArgs a) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  int buf = -1;
+  if (a.peer != a.rank) {
+    unsigned long long seen = ld_acquire_sys_u64(a.gate);
+    for (int t = 0; t < GATE_CAS_TRIES; ++t) {
+      const int b = (int)((seen >> 32) & 1ull);
+      const unsigned long long want = seen + (1ull << (16 * b));
+      const unsigned long long old = atom_cas_sys_u64(a.gate, seen, want);
+      if (old == seen) { buf = b; break; }
+      seen = old;
+    }
+    if (buf < 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);   // the gate changed under every one of the tries
+  }
+  *a.ticket = buf;
+  __threadfence();
+}
+
+__global__ void __launch_bounds__(512) push_add_async_kernel(const __grid_constant__ MixArgs a) {
+  const int buf = *reinterpret_cast<volatile int*>(a.ticket);
+  if (buf < 0) return;
+  float* acc = a.acc_target + (size_t)buf * a.n;
+  const long long n4 = a.n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x)
+    red_add_sys_f4(acc + i * 4, reinterpret_cast<const float4*>(a.w)[i]);
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.f32 [%0], %1;" ::"l"(a.count_target + buf), "f"(1.f) : "memory");
+    atom_add_sys_u64(a.gate, 0ull - (1ull << (16 * buf)));   // the registration comes off after the count is in
+    *a.block_counter = 0u;
+    __threadfence();
+  }
+}
+
+// ticket: 0 / 1 = accumulator that was closed and is safe to fold, -1 = a push into it never finished (not folded)
+__global__ void fold_begin_kernel(const __grid_constant__ MixArgs a) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const unsigned long long old = atom_add_sys_u64(a.gate, 1ull << 32);
+  const int closed = (int)((old >> 32) & 1ull);
+  const uint64_t limit = wait_limit(a.wait_ns), t0 = globaltimer_ns();
+  bool ok = true;
+  uint32_t spins = 0;
+  while (((ld_acquire_sys_u64(a.gate) >> (16 * closed)) & 0xffffull) != 0ull) {
+    if ((++spins & 63u) == 0u && globaltimer_ns() - t0 > limit) { ok = false; break; }
+  }
+  if (!ok) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
+  *a.ticket = ok ? closed : -1;
+  __threadfence();
+}
+
+__global__ void __launch_bounds__(512) fold_kernel(const __grid_constant__ MixArgs a) {
+  const int buf = *reinterpret_cast<volatile int*>(a.ticket);
+  const float cnt = buf >= 0 ? *reinterpret_cast<volatile float*>(a.count_target + buf) : 0.f;
+  if (cnt > 0.f) {
+    float* acc = a.acc_target + (size_t)buf * a.n;
+    const float inv = 1.f / (a.w_self + cnt), ws = a.w_self;
+    const long long n4 = a.n / 4;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
+         i += (long long)gridDim.x * blockDim.x) {
+      float4 x = reinterpret_cast<float4*>(a.w)[i];
+      const float4 s = reinterpret_cast<float4*>(acc)[i];
+      x = make_float4((ws * x.x + s.x) * inv, (ws * x.y + s.y) * inv, (ws * x.z + s.z) * inv, (ws * x.w + s.w) * inv);
+      reinterpret_cast<float4*>(a.w)[i] = x;
+      reinterpret_cast<float4*>(acc)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a.w16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+        uint2 o;
+        o.x = *reinterpret_cast<uint32_t*>(&lo);
+        o.y = *reinterpret_cast<uint32_t*>(&hi);
+        reinterpret_cast<uint2*>(a.w16)[i] = o;
+      }
+    }
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    if (buf >= 0) a.count_target[buf] = 0.f;
+    *a.block_counter = 0u;
+    __threadfence();
+  }
+}
+
+// ------------------------------------------------------------------- asynchronous elastic averaging
+// The reference's parameter server serves one client at a time, each with the centre as it is at that moment, and
+// clients may be any number of iterations apart (src/worker/elasticserver_dist.rs:249-255,667-715); its one-sided
+// form guards the centre with a compare-and-swap state word (src/worker/elasticserver_dist_rdma.rs:74-104,565-649).
+// Here the centre lives in rank 0's memory with a lock word beside it:
+//   elastic_begin (one thread)  compare-and-swap 0 -> rank + 1 on the centre's lock, retried for at most `wait_ns`;
+//                               a client that does not get the lock in time gives this exchange up (counted in
+//                               `skipped`, no error: the centre was busy) -- ticket 1 = locked, 0 = skipped
+//   elastic_mix   (grid)        with the lock: c = centre (peer loads); d = beta (x - c); x <- x - d;
+//                               centre <- c + d (peer stores); the last block fences and releases the lock
+__global__ void elastic_begin_kernel(const __grid_constant__ MixArgs a) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const unsigned long long mine = (unsigned long long)(a.rank + 1);
+  const uint64_t limit = wait_limit(a.wait_ns), t0 = globaltimer_ns();
+  int got = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (ld_acquire_sys_u64(a.gate) == 0ull && atom_cas_sys_u64(a.gate, 0ull, mine) == 0ull) { got = 1; break; }
+    if ((++spins & 15u) == 0u && globaltimer_ns() - t0 > limit) break;
+  }
+  if (!got && a.skipped) atomicAdd(a.skipped, 1u);
+  *a.ticket = got;
+  __threadfence();
+}
+
+__global__ void __launch_bounds__(512) elastic_mix_kernel(const __grid_constant__ MixArgs a) {
+  if (*reinterpret_cast<volatile int*>(a.ticket) != 1) return;
+  const long long n4 = a.n / 4;
+  const float be = a.alpha;
+  float* center = const_cast<float*>(a.pub_peer);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 c = ld_f4(center + i * 4);
+    float4 x = reinterpret_cast<float4*>(a.w)[i];
+    const float4 d = make_float4(be * (x.x - c.x), be * (x.y - c.y), be * (x.z - c.z), be * (x.w - c.w));
+    x = make_float4(x.x - d.x, x.y - d.y, x.z - d.z, x.w - d.w);
+    reinterpret_cast<float4*>(a.w)[i] = x;
+    *reinterpret_cast<float4*>(center + i * 4) = make_float4(c.x + d.x, c.y + d.y, c.z + d.z, c.w + d.w);
+    if (a.w16) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&lo);
+      o.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(a.w16)[i] = o;
+    }
+  }
+  __shared__ int s_last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(a.block_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+  __syncthreads();
+  if (s_last && threadIdx.x == 0) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(a.gate), "l"(0ull) : "memory");   // unlock
+    *a.block_counter = 0u;
+    __threadfence();
+  }
+}
+
 // Cross-GPU barrier as a kernel of one block (orders the kernels before it on every rank's stream against
 // the kernels after it on every other rank's stream).
 struct BarrierArgs {
@@ -520,13 +724,15 @@ struct BarrierArgs {
   uint32_t* epoch_ptr;
   unsigned int* status;
   int rank, world, slot;
+  long long wait_ns;     // limit of the wait for the peers, ns (0: the 3 s default)
 };
 __global__ void barrier_kernel(const __grid_constant__ BarrierArgs a) {
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
   __threadfence_system();
   if (threadIdx.x < a.world) st_release_sys(flag_at(a.flags[threadIdx.x], a.slot, 0, a.rank), epoch);
   int ok = 1;
-  if (threadIdx.x < a.world) ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch) ? 1 : 0;
+  if (threadIdx.x < a.world)
+    ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 0, threadIdx.x), epoch, wait_limit(a.wait_ns)) ? 1 : 0;
   ok = __syncthreads_and(ok);
   if (threadIdx.x == 0) {
     if (!ok) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);
@@ -636,6 +842,48 @@ int rb_elastic_apply(float* center, float* delta, long long n, cudaStream_t st) 
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
   elastic_apply_kernel<<<(int)blocks, 256, 0, st>>>(center, delta, n);
+  return RB_LAUNCH_OK();
+}
+
+int rb_push_begin_p2p(const void* args, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (!a->ticket || (a->peer != a->rank && !a->gate)) return -10;
+  push_begin_kernel<<<1, 32, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_push_add_async_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4 || !a->ticket) return -10;
+  push_add_async_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_fold_begin_p2p(const void* args, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (!a->ticket || !a->gate) return -10;
+  fold_begin_kernel<<<1, 32, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_fold_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4 || !a->ticket) return -10;
+  fold_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_elastic_begin_p2p(const void* args, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (!a->ticket || !a->gate) return -10;
+  elastic_begin_kernel<<<1, 32, 0, st>>>(*a);
+  return RB_LAUNCH_OK();
+}
+
+int rb_elastic_mix_p2p(const void* args, int blocks, cudaStream_t st) {
+  const MixArgs* a = reinterpret_cast<const MixArgs*>(args);
+  if (a->n % 4 || !a->ticket || !a->gate) return -10;
+  elastic_mix_kernel<<<blocks < 1 ? 1 : blocks, 512, 0, st>>>(*a);
   return RB_LAUNCH_OK();
 }
 

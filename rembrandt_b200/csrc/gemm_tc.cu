@@ -36,6 +36,7 @@
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
 #include "common.cuh"
+#include <ctype.h>
 #include <stdlib.h>
 #include <map>
 #include <mutex>
@@ -85,6 +86,36 @@ __device__ __forceinline__ void pixel_coords(const GemmTcParams& p, int pix, int
   h = pp * p.cv_stride + p.cv_lower_h;
 }
 
+// One unit of a CTA's work list: tile (tm, tn) over k-blocks [kb0, kb1). `tail` >= 0 marks a part of a cut item of
+// the last wave (index among the cut items); its sums go to the fp32 workspace instead of D.
+struct WorkItem {
+  int tm, tn, kb0, kb1, tail;
+};
+__device__ __forceinline__ WorkItem decode_work(const GemmTcParams& p, int work, int m_items, int direct,
+                                                int kb_per_split) {
+  WorkItem w;
+  int rem;
+  if (p.tail_items > 0 && work >= direct) {
+    const int w2 = work - direct;
+    const int part = w2 / p.tail_items;
+    w.tail = w2 - part * p.tail_items;
+    rem = direct + w.tail;
+    const int kbs = (p.num_kb + p.tail_split - 1) / p.tail_split;
+    w.kb0 = part * kbs;
+    w.kb1 = min(p.num_kb, w.kb0 + kbs);
+  } else {
+    const int per = m_items * p.n_tiles;
+    const int z = work / per;
+    rem = work - z * per;
+    w.kb0 = z * kb_per_split;
+    w.kb1 = min(p.num_kb, w.kb0 + kb_per_split);
+    w.tail = -1;
+  }
+  w.tn = rem / m_items;
+  w.tm = rem - w.tn * m_items;
+  return w;
+}
+
 __device__ __forceinline__ void load_b(const GemmTcParams& p, uint8_t* sb, uint64_t* bar, int kb, int n0, int b_tap,
                                        int b_c0) {
   const int b_split = p.b_split > 0 ? p.b_split : 1;
@@ -122,6 +153,61 @@ __device__ __forceinline__ void load_b(const GemmTcParams& p, uint8_t* sb, uint6
   }
 }
 
+// The MMAs of one k-block, fully unrolled: MT sub-tiles x KK 16-deep steps (x 2 for a tile wider than 256 columns).
+// The one issuing thread's instruction stream is what bounds the kernel when operands arrive in time (a single extra
+// branch per MMA in this loop cost 44 % on a weight-grad launch), so nothing here is computed per MMA that can be
+// computed per k-block, and only the first MMA into an accumulator carries a predicate.
+template <int KK, int MT, bool WIDE>
+__device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t acc_stride, uint64_t da, uint64_t a_sub,
+                                             uint64_t db, uint32_t a_adv, uint32_t b_adv, uint32_t idesc,
+                                             uint32_t idesc2, uint64_t b_wide_off, bool fresh) {
+#pragma unroll
+  for (int j = 0; j < MT; ++j) {
+    const uint32_t dj = d_tmem + (uint32_t)j * acc_stride;
+    const uint64_t daj = da + (uint64_t)j * a_sub;
+#pragma unroll
+    for (int kk = 0; kk < KK; ++kk) {
+      const uint64_t ak = daj + (uint64_t)(a_adv * kk), bk_ = db + (uint64_t)(b_adv * kk);
+      if (kk == 0) {
+        tc_mma_f16(dj, ak, bk_, idesc, fresh ? 0u : 1u);
+        if (WIDE) tc_mma_f16(dj + 256u, ak, bk_ + b_wide_off, idesc2, fresh ? 0u : 1u);
+      } else {
+        tc_mma_f16_acc(dj, ak, bk_, idesc);
+        if (WIDE) tc_mma_f16_acc(dj + 256u, ak, bk_ + b_wide_off, idesc2);
+      }
+    }
+  }
+}
+
+// What the issuing thread needs for the k-blocks of one work item, fixed for the launch.
+struct IssueCtx {
+  uint32_t ring_u32, tiles_u32, stage_bytes, b_bytes, b_in_stage;   // b_in_stage: offset of B inside a stage
+  uint32_t acc_stride, a_adv, b_adv, idesc, idesc2;
+  uint64_t a_desc0, b_desc0, a_sub, b_wide_off;
+  int stages, b_resident;
+};
+
+// k-blocks [kb0, kb1) of one work item; returns false after a wait that ran out.
+template <int KK, int MT, bool WIDE>
+__device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, unsigned int* status, uint32_t d_tmem,
+                                           int kb0, int kb1, int& s, uint32_t& ph) {
+  for (int kb = kb0; kb < kb1; ++kb) {
+    if (!ctl_wait(ctl, &ctl->full[s], ph, status)) return false;
+    tc_fence_after();
+    const uint32_t sa = c.ring_u32 + (uint32_t)s * c.stage_bytes;
+    const uint32_t sb = c.b_resident ? c.tiles_u32 + (uint32_t)kb * c.b_bytes : sa + c.b_in_stage;
+    // descriptors differ from the templates only in the 14-bit start address (no carry out of it: shared memory
+    // ends below 256 KB)
+    const uint64_t da = c.a_desc0 | (uint64_t)((sa >> 4) & 0x3FFFu);
+    const uint64_t db = c.b_desc0 | (uint64_t)((sb >> 4) & 0x3FFFu);
+    issue_kblock<KK, MT, WIDE>(d_tmem, c.acc_stride, da, c.a_sub, db, c.a_adv, c.b_adv, c.idesc, c.idesc2,
+                               c.b_wide_off, kb == kb0);
+    tc_commit(&ctl->empty[s]);  // stage is free once these MMAs have read it
+    if (++s == c.stages) { s = 0; ph ^= 1u; }
+  }
+  return true;
+}
+
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // tiles start on a 1024-byte boundary (swizzle atoms); control block follows the tiles
@@ -143,7 +229,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   const bool halo = p.a_mode == A_HALO_K;
   const int m_items = halo ? (p.M / (p.cv_P * p.cv_Q)) * p.hl_groups : (p.M + BM * mt - 1) / (BM * mt);
   const int n_tiles = p.n_tiles;
-  const int num_work = m_items * n_tiles * p.split_k;
+  // whole items first, then the parts of the cut items of the last wave (tail cut; never in halo mode)
+  const int direct = m_items * n_tiles - p.tail_items;
+  const int num_work = p.tail_items > 0 ? direct + p.tail_items * p.tail_split : m_items * n_tiles * p.split_k;
   // halo mode: [A ring: hl_a_stages x hl_a_bytes][B ring: stages x b_bytes]
   uint8_t* a_ring = tiles;
   uint8_t* b_ring = tiles + p.hl_a_stages * p.hl_a_bytes;
@@ -170,6 +258,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     tma_prefetch_desc(&p.tm_b);
     tma_prefetch_desc(&p.tm_d);
     if (p.epi == EPI_BF16 && p.mask_src) tma_prefetch_desc(&p.tm_mask);
+    if (p.tail_items > 0) tma_prefetch_desc(&p.tm_ws);
   }
   if (warp == 1) {
     tmem_alloc(&ctl->tmem_base, 512);
@@ -244,13 +333,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       else nload = b_split;
       const uint32_t my_tx = is_a ? (uint32_t)(mt * a_bytes) : (uint32_t)b_bytes;
       for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-        const int z = work / (m_items * n_tiles);
-        const int rem = work - z * (m_items * n_tiles);
-        const int tn = rem / m_items;
-        const int tm = rem - tn * m_items;
+        const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
+        const int tn = it.tn, tm = it.tm, kb0 = it.kb0, kb1 = it.kb1;
         const int m0 = tm * BM * mt;
-        const int kb0 = z * kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + kb_per_split);
         // geometry that is fixed for the work item (every lane keeps what its own load needs)
         // sub-tile of this lane's A load, and which of the sub-tile's boxes it is
         const int aj = (p.a_mode == A_TILED_MN) ? (lane >> 1) : lane / a_split;
@@ -351,7 +436,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     if (lane == 0) {
       const bool a_mn = (p.a_mode == A_TILED_MN);
       const bool b_mn = (p.b_mode == B_TILED_MN || p.b_mode == B_IM2COL_MN);
-      const uint32_t idesc = make_idesc_bf16(BM, (uint32_t)p.bn, a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+      // a tile wider than 256 columns is two MMAs side by side (256 + the rest) that share the A descriptor
+      const uint32_t idesc = make_idesc_bf16(BM, (uint32_t)min(p.bn, 256), a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+      const uint32_t idesc2 = p.bn > 256 ? make_idesc_bf16(BM, (uint32_t)(p.bn - 256), a_mn ? 1u : 0u, b_mn ? 1u : 0u) : 0u;
+      const uint64_t b_wide_off = (uint64_t)((256u * (uint32_t)p.bk * 2u) >> 4);   // K-major B: 256 rows further down
       // K-major: rows of bk*2 bytes, 8-row atoms -> SBO = 8*bk*2; swizzle 128B (bk=64) or 64B (bk=32)
       // MN-major: 64-element (128 B) rows per k, atoms of 8 k -> SBO = 1024, LBO = bk*128 between 64-wide blocks
       const uint32_t k_layout = (p.bk == 64) ? 2u : 4u;
@@ -413,28 +501,37 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           if (++acc == p.acc_bufs) { acc = 0; acc_ph ^= 1u; }
         }
       }
+      // what the unrolled issue code needs, fixed for the launch
+      IssueCtx ic;
+      ic.ring_u32 = smem_u32(ring);
+      ic.tiles_u32 = smem_u32(tiles);
+      ic.stage_bytes = (uint32_t)stage_bytes;
+      ic.b_bytes = (uint32_t)b_bytes;
+      ic.b_in_stage = (uint32_t)(mt * a_bytes);
+      ic.acc_stride = (uint32_t)p.acc_stride;
+      ic.a_adv = a_adv;
+      ic.b_adv = b_adv;
+      ic.idesc = idesc;
+      ic.idesc2 = idesc2;
+      ic.a_desc0 = make_smem_desc(0u, a_lbo, a_sbo, a_lay);
+      ic.b_desc0 = make_smem_desc(0u, b_lbo, b_sbo, b_lay);
+      ic.a_sub = (uint64_t)((uint32_t)a_bytes >> 4);     // next 128-row sub-tile of the stage
+      ic.b_wide_off = b_wide_off;
+      ic.stages = stages;
+      ic.b_resident = p.b_resident;
+      const int issue_kind = (kk_steps == 4 ? 0 : 3) + (idesc2 ? 2 : (mt == 2 ? 1 : 0));
       for (int work = blockIdx.x; work < num_work && ok && !halo; work += gridDim.x) {
-        const int z = work / (m_items * n_tiles);
-        const int kb0 = z * kb_per_split;
-        const int kb1 = min(p.num_kb, kb0 + kb_per_split);
+        const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
         if (!ctl_wait(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * set_cols;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!ctl_wait(ctl, &ctl->full[s], ph, p.status)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(ring + s * stage_bytes);
-          const uint32_t sb = p.b_resident ? smem_u32(tiles + kb * b_bytes) : sa + (uint32_t)(mt * a_bytes);
-          const uint64_t db = make_smem_desc(sb, b_lbo, b_sbo, b_lay);
-          for (int j = 0; j < mt; ++j) {
-            const uint64_t da = make_smem_desc(sa + (uint32_t)(j * a_bytes), a_lbo, a_sbo, a_lay);
-            for (int kk = 0; kk < kk_steps; ++kk) {
-              tc_mma_f16(d_tmem + (uint32_t)(j * p.acc_stride), da + (uint64_t)(a_adv * kk),
-                         db + (uint64_t)(b_adv * kk), idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
-            }
-          }
-          tc_commit(&ctl->empty[s]);  // stage is free once these MMAs have read it
-          if (++s == stages) { s = 0; ph ^= 1u; }
+        switch (issue_kind) {
+          case 0: ok = issue_item<4, 1, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 1: ok = issue_item<4, 2, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 2: ok = issue_item<4, 1, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 3: ok = issue_item<2, 1, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 4: ok = issue_item<2, 2, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          default: ok = issue_item<2, 1, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
         }
         if (!ok) break;
         tc_commit(&ctl->acc_full[acc]);
@@ -455,10 +552,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     uint32_t acc_ph = 0;
     bool ok = true;
     for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
-      const int z = work / (m_items * n_tiles);
-      const int rem = work - z * (m_items * n_tiles);
-      const int tn = rem / m_items;
-      const int tm = rem - tn * m_items;
+      const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
+      const int tn = it.tn, tm = it.tm;
+      const bool tail = it.tail >= 0;
       if (!ctl_wait(ctl, &ctl->acc_full[acc], acc_ph, p.status)) { ok = false; break; }
       tc_fence_after();
       int col0;        // first column of D this tile writes
@@ -487,7 +583,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         const int row0 = tm * BM * mt + j * BM + lane_base;   // first row of this warp's 32-row band
         const uint32_t t_addr =
             tmem_base + (uint32_t)acc * set_cols + (uint32_t)(j * p.acc_stride) + ((uint32_t)lane_base << 16);
-        if (p.epi == EPI_BF16) {
+        if (p.epi == EPI_BF16 && !tail) {
           // 64-column slabs: TMEM -> registers -> bias / ReLU / mask -> swizzled shared memory -> TMA store.
           // Each warp owns a 4 KB slab buffer and issues its own stores, so no cross-warp sync is needed.
           for (int c = col_half * 64; c < p.bn && col0 + c < p.n_store; c += 128) {
@@ -582,9 +678,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           uint32_t v[32];
           tmem_ld_32x32(t_addr + (uint32_t)c, v);
           tmem_ld_wait();
-          if (c >= col_limit || (p.dbg & 1)) continue;
-          int gcol = col0 + c;
-          if (p.b_mode == B_IM2COL_MN && p.wg_taps > 1) {
+          if (!tail && c >= col_limit) continue;
+          int gcol = tail ? c : col0 + c;
+          if (!tail && p.b_mode == B_IM2COL_MN && p.wg_taps > 1) {
             const int t = c / p.wg_cw, cc = c - t * p.wg_cw;
             const int tap = tn * p.wg_taps + t;
             if (tap >= p.wg_ntaps || cc >= p.wg_cpad) continue;
@@ -601,8 +697,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           }
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0 && row0 < p.M) {
-            if (p.epi == EPI_F32_STORE) tma_store_2d(&p.tm_d, stg, gcol, row0);
+          if (lane == 0 && (tail || row0 < p.M)) {
+            // a part of a cut item adds into its rows of the workspace; everything else goes to D
+            if (tail) tma_reduce_add_2d(&p.tm_ws, stg, gcol, (it.tail * mt + j) * BM + lane_base);
+            else if (p.epi == EPI_F32_STORE) tma_store_2d(&p.tm_d, stg, gcol, row0);
             else tma_reduce_add_2d(&p.tm_d, stg, gcol, row0);
             tma_store_commit();
           }
@@ -639,7 +737,10 @@ static EncodeIm2colFn g_encode_im2col = nullptr;
 static int g_num_sms = 0;
 static int g_driver_version = 0;
 
+static void options_from_env();
+
 static int ensure_driver_entry() {
+  options_from_env();
   if (g_encode_tiled && g_encode_im2col) return 0;
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
@@ -735,40 +836,98 @@ static int make_map_nhwc(CUtensorMap* m, const void* ptr, uint64_t C, uint64_t W
   return r == CUDA_SUCCESS ? 0 : -(400 + (int)r);
 }
 
+// ---- options ----------------------------------------------------------------------------------------------------
+// Switches of the planner. Their initial values come from the environment (RB_GEMM_*), read once when the library
+// is first used; afterwards they change only through rb_gemm_set_option (tests, experiments).
+struct GemmOptions {
+  int force_mt = 0;          // RB_GEMM_FORCE_MT: 1 | 2 sub-tiles per item (0 = planner's choice)
+  int force_resident = -1;   // RB_GEMM_FORCE_RESIDENT: 0 | 1
+  int force_halo = -1;       // RB_GEMM_FORCE_HALO: 0 = never, 1 = whenever feasible
+  int force_taps = 0;        // RB_GEMM_FORCE_TAPS: filter taps per weight-grad tile
+  int force_tail = -1;       // RB_GEMM_FORCE_TAIL: 0 = never cut the last wave, 1 = whenever feasible
+  int force_wide = -1;       // RB_GEMM_FORCE_WIDE: 0 = tiles of at most 256 columns, 1 = one wide tile when N <= 512
+  int bk32 = 0;              // RB_GEMM_BK32: keep 32-channel chunks for channel counts such as 96
+  int bn_cap = 256;          // RB_GEMM_BN_CAP: upper bound on the tile width chosen by the planner
+  int a_split = 1;           // RB_GEMM_A_SPLIT / RB_GEMM_B_SPLIT: TMA boxes per K-major tile
+  int b_split = 1;
+  int autotune = 1;          // RB_GEMM_AUTOTUNE: 0 = cost model only, even in tuning mode
+};
+static GemmOptions g_opt;
+static std::once_flag g_opt_once;
+static int g_tune_mode = 0;   // set by rb_gemm_tune_mode: launches of unseen shapes time their candidates
+
+static int* option_slot(const char* name) {
+  struct { const char* name; int* slot; } table[] = {
+      {"force_mt", &g_opt.force_mt}, {"force_resident", &g_opt.force_resident}, {"force_halo", &g_opt.force_halo},
+      {"force_taps", &g_opt.force_taps}, {"force_tail", &g_opt.force_tail}, {"force_wide", &g_opt.force_wide},
+      {"bk32", &g_opt.bk32}, {"bn_cap", &g_opt.bn_cap}, {"a_split", &g_opt.a_split}, {"b_split", &g_opt.b_split},
+      {"autotune", &g_opt.autotune}};
+  for (auto& t : table)
+    if (strcmp(t.name, name) == 0) return t.slot;
+  return nullptr;
+}
+static void options_from_env() {
+  std::call_once(g_opt_once, [] {
+    const char* names[] = {"force_mt", "force_resident", "force_halo", "force_taps", "force_tail", "force_wide",
+                           "bk32", "bn_cap", "a_split", "b_split", "autotune"};
+    for (const char* n : names) {
+      char env[64] = "RB_GEMM_";
+      size_t k = strlen(env);
+      for (const char* c = n; *c && k + 1 < sizeof(env); ++c) env[k++] = (char)toupper((unsigned char)*c);
+      env[k] = 0;
+      const char* e = getenv(env);
+      if (e) *option_slot(n) = atoi(e);
+    }
+  });
+}
+
 // ---- tile-shape planning -----------------------------------------------------------------------------------
 // Cost model in "rows": the kernel is bound by the 128-byte rows it fills into shared memory per k-block
 // (see the header comment), so an item costs about k-blocks x (rows of A + rows of B) plus its epilogue, and a
 // launch costs rounds x item (persistent CTAs, one per SM). The planner picks sub-tiles per item (mt),
-// the reduction split and B residency to minimise that.
+// the reduction split, B residency and whether the last wave is cut along the reduction to minimise that.
 struct Plan {
-  int mt, split, resident;
+  int mt, split, resident, tail;   // tail: parts per cut item of the last wave (0 = no cut)
   double cost;
 };
 
 // Boxes per tile for K-major operands (each box is issued by its own lane). A box must keep whole 8-row swizzle
-// atoms and start on a 1024-byte boundary in shared memory.
-static int pick_box_split(const char* env, int rows, int bk, int dflt) {
-  const char* e = getenv(env);
-  int sp = e ? atoi(e) : dflt;
+// atoms, start on a 1024-byte boundary in shared memory and have at most 256 rows.
+static int pick_box_split(int sp, int rows, int bk) {
+  if (sp < 1) sp = 1;
+  while (rows / sp > 256) sp <<= 1;
   while (sp > 1 && (rows % sp != 0 || (rows / sp) % 8 != 0 || ((rows / sp) * bk * 2) % 1024 != 0)) sp >>= 1;
   return sp < 1 ? 1 : sp;
 }
 
 static bool split_ok(int s, int num_kb) { return s == 1 || (s - 1) * ((num_kb + s - 1) / s) < num_kb; }
 
+static int acc_stride_for(int bn) { return bn > 256 ? 512 : (bn > 128 ? 256 : 128); }
+
+// Parts per cut item for `items` work items on `sms` SMs (0 = cutting does not pay or is not possible): the last
+// wave must be at most half full, every SM gets at most one part, a part keeps at least four k-blocks.
+static int tail_parts(long long items, int sms, int num_kb) {
+  if (items <= sms) return 0;
+  const int rem = (int)(items % sms);
+  if (rem == 0 || rem * 2 > sms) return 0;
+  int s = sms / rem;
+  if (s > num_kb / 4) s = num_kb / 4;
+  if (s > 16) s = 16;
+  while (s > 1 && !split_ok(s, num_kb)) --s;
+  return s >= 2 ? s : 0;
+}
+
 static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights) {
   const int a_bytes = BM * p.bk * 2, b_bytes = p.bn_load * p.bk * 2;
   const double epi_elem = (p.epi == EPI_BF16) ? 1.2 : 1.6;
-  Plan best{1, 1, 0, 1e300};
-  // test hooks: RB_GEMM_FORCE_MT=1|2 and RB_GEMM_FORCE_RESIDENT=0|1 restrict the search (ignored when infeasible)
-  const char* e_mt = getenv("RB_GEMM_FORCE_MT");
-  const char* e_res = getenv("RB_GEMM_FORCE_RESIDENT");
-  const int force_mt = e_mt ? atoi(e_mt) : 0, force_res = e_res ? atoi(e_res) : -1;
+  Plan best{1, 1, 0, 0, 1e300};
+  // the force options restrict the search (ignored when infeasible)
+  const int force_mt = g_opt.force_mt, force_res = g_opt.force_resident;
   for (int pass = 0; pass < 2 && best.cost >= 1e299; ++pass)
   for (int mt = 1; mt <= 2; ++mt) {
     if (pass == 0 && force_mt && mt != force_mt) continue;
-    if (mt == 2 && p.M <= BM) continue;
-    const int acc_stride = p.bn > 128 ? 256 : 128;
+    if (mt == 2 && (p.M <= BM || p.bn > 256)) continue;
+    const int acc_stride = acc_stride_for(p.bn);
     const int acc_bufs = (2 * mt * acc_stride <= 512) ? 2 : 1;
     const int m_items = (p.M + BM * mt - 1) / (BM * mt);
     const long long tiles = (long long)m_items * p.n_tiles;
@@ -789,9 +948,23 @@ static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split,
         const double mainloop = kbs * rows_kb * (p.bk / 64.0);
         const double epi = mt * p.bn * epi_elem;
         const double item = acc_bufs == 2 ? (mainloop > epi ? mainloop : epi) + 0.15 * epi : mainloop + epi;
-        const long long rounds = (tiles * s + g_num_sms - 1) / g_num_sms;
-        const double cost = rounds * item + (res ? (double)p.num_kb * p.bn_load * (p.bk / 64.0) : 0.0);
-        if (cost < best.cost * 0.97) best = Plan{mt, s, res, cost};
+        for (int tail = 0; tail <= 1; ++tail) {
+          int parts = 0;
+          if (tail) {
+            if (p.epi != EPI_BF16 || s != 1 || !p.ws || g_opt.force_tail == 0) continue;
+            parts = tail_parts(tiles, g_num_sms, p.num_kb);
+            if (parts == 0) continue;
+            const long long need = (tiles % g_num_sms) * mt * BM * (long long)p.bn * 4;
+            if (need > p.ws_bytes) continue;
+          } else if (pass == 0 && g_opt.force_tail == 1 && p.epi == EPI_BF16 && s == 1 && p.ws &&
+                     tail_parts(tiles, g_num_sms, p.num_kb) > 0) {
+            continue;
+          }
+          double rounds = (double)((tiles * s + g_num_sms - 1) / g_num_sms);
+          if (parts) rounds = (double)(tiles / g_num_sms) + 1.0 / parts + 0.1;   // + the fix-up pass
+          const double cost = rounds * item + (res ? (double)p.num_kb * p.bn_load * (p.bk / 64.0) : 0.0);
+          if (cost < best.cost * 0.97) best = Plan{mt, s, res, parts, cost};
+        }
       }
     }
   }
@@ -803,8 +976,9 @@ static int apply_plan(GemmTcParams& p, const Plan& pl) {
   p.mt = pl.mt;
   p.split_k = pl.split;
   p.b_resident = pl.resident;
-  p.acc_stride = p.bn > 128 ? 256 : 128;
+  p.acc_stride = acc_stride_for(p.bn);
   p.acc_bufs = (2 * p.mt * p.acc_stride <= 512) ? 2 : 1;
+  if (p.mt * p.acc_stride > 512) return 0;
   const int a_bytes = BM * p.bk * 2, b_bytes = p.bn_load * p.bk * 2;
   const int panel = p.b_resident ? p.num_kb * b_bytes : 0;
   const int stage = p.mt * a_bytes + (p.b_resident ? 0 : b_bytes);
@@ -814,72 +988,183 @@ static int apply_plan(GemmTcParams& p, const Plan& pl) {
   if (p.stages < 2) return 0;
   if (p.mt == 2 && p.M <= BM) return 0;
   const int m_items = (p.M + BM * p.mt - 1) / (BM * p.mt);
-  const long long work = (long long)m_items * p.n_tiles * p.split_k;
+  const long long items = (long long)m_items * p.n_tiles;
+  p.tail_items = 0;
+  p.tail_split = 0;
+  long long work = items * p.split_k;
+  if (pl.tail > 0) {
+    if (p.epi != EPI_BF16 || p.split_k != 1 || !p.ws || items <= g_num_sms) return 0;
+    p.tail_items = (int)(items % g_num_sms);
+    p.tail_split = pl.tail;
+    const long long rows = (long long)p.tail_items * p.mt * BM;
+    if (p.tail_items == 0 || rows * p.bn * 4 > p.ws_bytes || !split_ok(pl.tail, p.num_kb)) return 0;
+    cuuint64_t dims[2] = {(cuuint64_t)p.bn, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)p.bn * 4};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t es[2] = {1, 1};
+    if (g_encode_tiled(&p.tm_ws, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p.ws, dims, strides, box, es,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return 0;
+    work = items - p.tail_items + (long long)p.tail_items * p.tail_split;
+  }
   return work < g_num_sms ? (int)work : g_num_sms;
 }
 
-// Shapes whose output is overwritten (bf16 epilogue: forward and data-grad passes) are tuned by measurement the
-// first time they are seen outside a stream capture: every feasible (sub-tiles per item, resident B) choice is
-// timed on the caller's stream with its real operands (the launches are idempotent) and the fastest is cached.
-// The cost model alone mis-ranks them by up to 30 % (it knows rows filled, not wave quantisation or how much of
-// the epilogue is exposed). RB_GEMM_AUTOTUNE=0 turns this off; the force hooks bypass it.
+// Epilogue of the cut items: D = act(workspace + bias), masked, as bf16; the workspace rows are cleared again so
+// that the next launch that uses the workspace finds zeros. One thread per 8 columns.
+struct TailFixArgs {
+  float* ws;
+  __nv_bfloat16* D;
+  const float* bias;
+  const __nv_bfloat16* mask;
+  long long ldd;
+  int M, bn, rows_per_item, m_items, direct, tail_items, n_valid, n_store, relu;
+};
+__global__ void tail_fix_kernel(const TailFixArgs a) {
+  const int gpr = a.bn / 8;
+  const long long groups = (long long)a.tail_items * a.rows_per_item * gpr;
+  const float act_lo = a.relu ? 0.f : -INFINITY;
+  for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
+       g += (long long)gridDim.x * blockDim.x) {
+    const int c8 = (int)(g % gpr);
+    const long long wr = g / gpr;                    // row of the workspace
+    const int ti = (int)(wr / a.rows_per_item);
+    const int r = (int)(wr - (long long)ti * a.rows_per_item);
+    const int rem = a.direct + ti;
+    const int tn = rem / a.m_items, tm = rem - tn * a.m_items;
+    const long long row = (long long)tm * a.rows_per_item + r;
+    const int col = tn * a.bn + c8 * 8;
+    float4* src = reinterpret_cast<float4*>(a.ws + wr * a.bn + c8 * 8);
+    const float4 v0 = src[0], v1 = src[1];
+    src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+    src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row >= a.M || col >= a.n_store) continue;
+    float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int n = col + e;
+      f[e] = n < a.n_valid ? fmaxf(f[e] + (a.bias ? __ldg(a.bias + n) : 0.f), act_lo) : 0.f;
+    }
+    if (a.mask) {
+      float m[8];
+      load8(a.mask + row * a.ldd + col, m);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (!(m[e] > 0.f)) f[e] = 0.f;
+    }
+    store8(a.D + row * a.ldd + col, f);
+  }
+}
+
+static int run_plan(GemmTcParams p, const Plan& pl, cudaStream_t stream) {
+  const int grid = apply_plan(p, pl);
+  if (grid <= 0) return -3;
+  gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
+  if (p.tail_items > 0) {
+    TailFixArgs f;
+    f.ws = p.ws;
+    f.D = reinterpret_cast<__nv_bfloat16*>(p.D);
+    f.bias = p.bias;
+    f.mask = p.mask_src;
+    f.ldd = p.ldd;
+    f.M = p.M;
+    f.bn = p.bn;
+    f.rows_per_item = p.mt * BM;
+    f.m_items = (p.M + BM * p.mt - 1) / (BM * p.mt);
+    f.direct = f.m_items * p.n_tiles - p.tail_items;
+    f.tail_items = p.tail_items;
+    f.n_valid = p.n_valid;
+    f.n_store = p.n_store;
+    f.relu = p.relu;
+    const long long groups = (long long)p.tail_items * f.rows_per_item * (p.bn / 8);
+    long long blocks = (groups + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    tail_fix_kernel<<<(int)blocks, 256, 0, stream>>>(f);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+}
+
+// Shapes whose output is overwritten (bf16 epilogue: forward and data-grad passes) can be tuned by measurement:
+// in tuning mode (rb_gemm_tune_mode(1), which a network switches on while it runs each of its convolution shapes
+// once on scratch operands at build time) a launch of a shape that has no cached plan times every feasible
+// (sub-tiles per item, resident B, tail cut) choice on the given stream and caches the fastest. The cost model
+// alone mis-ranks them by up to 30 % (it knows rows filled, not how much of the epilogue is exposed). Outside
+// tuning mode a launch never times anything: it takes the cached plan, or the cost model's.
 typedef std::tuple<int, int, int, int, int, int, int, int, int, int> PlanKey;
 static std::map<PlanKey, Plan> g_plan_cache;
 static std::mutex g_plan_mutex;
 
-static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights, cudaStream_t stream) {
-  if (p.M <= 0 || p.n_tiles <= 0 || p.num_kb <= 0) return 0;
-  { const char* e = getenv("RB_GEMM_DBG"); p.dbg = e ? atoi(e) : 0; }
-  Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
-  if (pl.cost >= 1e299) return -3;
-  const char* e_tune = getenv("RB_GEMM_AUTOTUNE");
-  const bool forced = getenv("RB_GEMM_FORCE_MT") || getenv("RB_GEMM_FORCE_RESIDENT");
-  if (p.epi == EPI_BF16 && !forced && !(e_tune && atoi(e_tune) == 0)) {
-    const PlanKey key(p.a_mode, p.b_mode, p.M, p.N, p.num_kb, p.bn, p.bk, p.n_tiles, p.cv_stride, p.mask_src ? 1 : 0);
-    std::lock_guard<std::mutex> lock(g_plan_mutex);
-    auto it = g_plan_cache.find(key);
-    if (it != g_plan_cache.end()) {
-      pl = it->second;
-    } else {
-      cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-      if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
-        cudaEvent_t e0, e1;
-        cudaEventCreate(&e0);
-        cudaEventCreate(&e1);
-        float best_ms = 1e30f;
-        Plan best = pl;
-        for (int mt = 1; mt <= 2; ++mt) {
-          for (int res = 0; res <= 1; ++res) {
-            if (res && (!b_is_weights || p.n_tiles != 1)) continue;
-            GemmTcParams q = p;
-            const Plan cand{mt, 1, res, 0.0};
-            const int grid = apply_plan(q, cand);
-            if (grid <= 0 || (res && q.stages < 3)) continue;
-            float ms = 1e30f;
-            bool okc = true;
-            for (int rep = 0; rep < 3 && okc; ++rep) {
-              cudaEventRecord(e0, stream);
-              gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(q);
-              cudaEventRecord(e1, stream);
-              if (cudaEventSynchronize(e1) != cudaSuccess) { okc = false; break; }
-              float t = 0.f;
-              cudaEventElapsedTime(&t, e0, e1);
-              if (rep > 0 && t < ms) ms = t;   // the first run warms the caches
-            }
-            if (okc && ms < best_ms) { best_ms = ms; best = cand; }
-          }
+static PlanKey plan_key(const GemmTcParams& p) {
+  return PlanKey(p.a_mode, p.b_mode, p.M, p.N, p.num_kb, p.bn, p.bk, p.n_tiles, p.cv_stride, p.mask_src ? 1 : 0);
+}
+
+// Times the candidates of `p` (3 launches each, best of the last 2); returns the best time in ms, or a negative
+// value when nothing could be run.
+static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t stream, Plan* out) {
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  float best_ms = 1e30f;
+  for (int mt = 1; mt <= 2; ++mt) {
+    for (int res = 0; res <= 1; ++res) {
+      if (res && (!b_is_weights || p.n_tiles != 1)) continue;
+      for (int tail = 0; tail <= 1; ++tail) {
+        Plan cand{mt, 1, res, 0, 0.0};
+        if (tail) {
+          if (!p.ws || g_opt.force_tail == 0) continue;
+          const int m_items = (p.M + BM * mt - 1) / (BM * mt);
+          cand.tail = tail_parts((long long)m_items * p.n_tiles, g_num_sms, p.num_kb);
+          if (cand.tail == 0) continue;
         }
-        cudaEventDestroy(e0);
-        cudaEventDestroy(e1);
-        pl = best;
-        g_plan_cache[key] = pl;
+        GemmTcParams q = p;
+        if (apply_plan(q, cand) <= 0 || (res && q.stages < 3)) continue;
+        float ms = 1e30f;
+        bool okc = true;
+        for (int rep = 0; rep < 3 && okc; ++rep) {
+          cudaEventRecord(e0, stream);
+          if (run_plan(p, cand, stream) != 0) { okc = false; break; }
+          cudaEventRecord(e1, stream);
+          if (cudaEventSynchronize(e1) != cudaSuccess) { okc = false; break; }
+          float t = 0.f;
+          cudaEventElapsedTime(&t, e0, e1);
+          if (rep > 0 && t < ms) ms = t;   // the first run warms the caches
+        }
+        if (okc && ms < best_ms) { best_ms = ms; *out = cand; }
       }
     }
   }
-  const int grid = apply_plan(p, pl);
-  if (grid <= 0) return -3;
-  gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  return best_ms < 1e29f ? best_ms : -1.f;
+}
+
+static bool tunable(const GemmTcParams& p, cudaStream_t stream) {
+  if (!g_tune_mode || !g_opt.autotune || p.epi != EPI_BF16) return false;
+  if (g_opt.force_mt || g_opt.force_resident >= 0) return false;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  return cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone;
+}
+
+static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights, cudaStream_t stream) {
+  if (p.M <= 0 || p.n_tiles <= 0 || p.num_kb <= 0) return 0;
+  Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
+  if (pl.cost >= 1e299) return -3;
+  const bool forced = g_opt.force_mt || g_opt.force_resident >= 0 || g_opt.force_tail >= 0;
+  if (p.epi == EPI_BF16 && !forced) {
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    auto it = g_plan_cache.find(plan_key(p));
+    if (it != g_plan_cache.end()) {
+      Plan cached = it->second;
+      if (cached.tail && !p.ws) cached.tail = 0;   // tuned with a workspace, launched without one
+      pl = cached;
+    } else if (tunable(p, stream)) {
+      Plan best = pl;
+      if (tune_plan(p, b_is_weights, stream, &best) > 0.f) pl = best;
+      g_plan_cache[plan_key(p)] = pl;
+    }
+  }
+  return run_plan(p, pl, stream);
 }
 
 static int round_bn(int n, int cap) {
@@ -895,8 +1180,7 @@ static int pick_bn(GemmTcParams& p, int n, int gran, bool allow_split, int fixed
                    Setup setup) {
   int best_bn = 0;
   double best_cost = 1e300;
-  const char* e_cap = getenv("RB_GEMM_BN_CAP");   // experiment hook: upper bound on the tile width
-  const int cap = e_cap ? atoi(e_cap) : 256;
+  const int cap = g_opt.bn_cap > 0 ? g_opt.bn_cap : 256;
   for (int nt = 1; nt <= 4; ++nt) {
     int bn = (n + nt - 1) / nt;
     const int g = (nt > 1 && gran < 64) ? 64 : gran;   // the bf16 epilogue stores 64-column slabs
@@ -911,6 +1195,9 @@ static int pick_bn(GemmTcParams& p, int n, int gran, bool allow_split, int fixed
   return best_bn;
 }
 
+// Tile width chosen by measurement for a convolution shape (key: the plan key with the width left out).
+static std::map<PlanKey, int> g_bn_cache;
+
 }  // namespace rb
 
 using namespace rb;
@@ -924,12 +1211,15 @@ extern "C" {
 // split_k <= 0 lets the library choose; epi 0/1 force split_k = 1.
 int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, long long ldb, int M, int N, int K,
                void* D, long long ldd, int epi, const float* bias, int relu, const void* mask_src, int n_valid,
-               int n_store, int split_k, int bn_cap, unsigned int* status, cudaStream_t stream) {
+               int n_store, int split_k, int bn_cap, float* ws, long long ws_bytes, unsigned int* status,
+               cudaStream_t stream) {
   int rc = ensure_driver_entry();
   if (rc) return rc;
   if ((n_store > 0 ? n_store : N) % 32 != 0 || ldd % 8 != 0) return -11;  // epilogue writes 32-column chunks
   GemmTcParams p;
   memset(&p, 0, sizeof(p));
+  p.ws = ws;
+  p.ws_bytes = ws ? ws_bytes : 0;
   const bool any_mn = a_mn || b_mn;
   p.bk = (!any_mn && (K % 64 != 0) && (K % 32 == 0)) ? 32 : 64;
   if (bn_cap <= 0) bn_cap = 256;
@@ -946,7 +1236,7 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
     rc = make_map_2d(&p.tm_a, A, M, K, lda, 64, p.bk, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
     p.a_mode = A_TILED_K;
-    p.a_split = pick_box_split("RB_GEMM_A_SPLIT", BM, p.bk, 1);
+    p.a_split = pick_box_split(g_opt.a_split, BM, p.bk);
     rc = make_map_2d(&p.tm_a, A, K, M, lda, p.bk, BM / p.a_split, ksw);
   }
   if (rc) return rc;
@@ -955,7 +1245,7 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
     rc = make_map_2d(&p.tm_b, B, N, K, ldb, 64, p.bk, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
     p.b_mode = B_TILED_K;
-    p.b_split = pick_box_split("RB_GEMM_B_SPLIT", p.bn, p.bk, 1);
+    p.b_split = pick_box_split(g_opt.b_split, p.bn, p.bk);
     rc = make_map_2d(&p.tm_b, B, K, N, ldb, p.bk, p.bn / p.b_split, ksw);
   }
   if (rc) return rc;
@@ -988,19 +1278,19 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
 //   base pixel range: lower = -pad_lo, P/Q given by the caller.
 int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, int Kout, int R, int S, int stride,
                      int pad_h, int pad_w, int P, int Q, void* y, long long ldy, const float* bias, int relu,
-                     const void* mask_src, int n_valid, int n_store, unsigned int* status, cudaStream_t stream) {
+                     const void* mask_src, int n_valid, int n_store, float* ws, long long ws_bytes,
+                     unsigned int* status, cudaStream_t stream) {
   int rc = ensure_driver_entry();
   if (rc) return rc;
   GemmTcParams p;
   memset(&p, 0, sizeof(p));
+  p.ws = ws;
+  p.ws_bytes = ws ? ws_bytes : 0;
   // The TMA unit is bound by rows (requests), not bytes: 64-channel (128-byte) rows halve the rows per MMA. A channel
   // count such as 96 therefore runs as two 64-channel chunks whose upper half lies outside the tensor and is
   // zero-filled by the TMA unit (both operands), rather than as three 32-channel chunks: a third more MMA work,
   // a third fewer loads, and the loads are what binds.
-  {
-    const char* e = getenv("RB_GEMM_BK32");   // test hook: 1 = keep 32-channel chunks for such counts
-    p.bk = (Cp % 64 == 0 || (Cp > 64 && !(e && atoi(e) == 1))) ? 64 : 32;
-  }
+  p.bk = (Cp % 64 == 0 || (Cp > 64 && g_opt.bk32 != 1)) ? 64 : 32;   // option bk32: keep 32-channel chunks
   if (Cp % 32 != 0) return -10;
   if ((n_store > 0 ? n_store : Kout) % 32 != 0 || ldy % 8 != 0) return -11;
   const CUtensorMapSwizzle ksw = p.bk == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
@@ -1032,8 +1322,7 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   p.status = status;
   // ---- halo mode (see the header comment): stride 1, more than one filter tap, image no wider than 128
   {
-    const char* e = getenv("RB_GEMM_FORCE_HALO");   // test hook: 0 = never, 1 = whenever feasible
-    const int force = e ? atoi(e) : -1;
+    const int force = g_opt.force_halo;   // 0 = never, 1 = whenever feasible
     if (stride == 1 && R * S > 1 && Q <= 128 && force != 0) {
       int pitch = 8;
       while (pitch < Q) pitch *= 2;
@@ -1082,7 +1371,6 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
         if (mask_src)
           rc = make_map_nhwc(&p.tm_mask, mask_src, p.n_store, Q, P, N, ldy, 64, bw, bh, CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc) return rc;
-        { const char* d = getenv("RB_GEMM_DBG"); p.dbg = d ? atoi(d) : 0; }
         const long long work = (long long)N * groups * p.n_tiles;
         const int grid = work < g_num_sms ? (int)work : g_num_sms;
         gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
@@ -1093,8 +1381,7 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   // upper corner so that the base pixel takes exactly P x Q positions
   const int upper_h = (P - 1) * stride - pad_h - (H - 1);
   const int upper_w = (Q - 1) * stride - pad_w - (W - 1);
-  p.a_split = pick_box_split("RB_GEMM_A_SPLIT", BM, p.bk, 1);
-  p.b_split = pick_box_split("RB_GEMM_B_SPLIT", p.bn, p.bk, 1);
+  p.a_split = pick_box_split(g_opt.a_split, BM, p.bk);
   if (R == 1 && S == 1 && stride == 1 && pad_h == 0 && pad_w == 0 && P == H && Q == W) {
     // a 1 x 1 convolution is a plain GEMM over the pixel rows: tiled loads, which the TMA unit serves 2-3x faster
     // per row than im2col-mode loads
@@ -1104,20 +1391,49 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
     rc = make_map_im2col(&p.tm_a, x, N, H, W, Cp, -pad_h, -pad_w, upper_h, upper_w, stride, p.bk, BM / p.a_split, ksw);
   }
   if (rc) return rc;
-  rc = make_map_3d(&p.tm_b, w, Cp, (uint64_t)R * S, Kout, Cp, (uint64_t)R * S * Cp, p.bk, 1, p.bn / p.b_split, ksw);
-  if (rc) return rc;
-  p.epi = EPI_BF16;
-  p.relu = relu;
-  p.n_valid = n_valid > 0 ? n_valid : Kout;
-  p.n_store = n_store > 0 ? n_store : Kout;
-  p.ldd = ldy;
-  p.D = y;
-  p.bias = bias;
-  p.mask_src = reinterpret_cast<const __nv_bfloat16*>(mask_src);
-  p.status = status;
   rc = make_map_out(&p.tm_d, y, p.n_store, p.M, ldy);
   if (rc) return rc;
   if (mask_src) rc = make_map_out(&p.tm_mask, const_cast<void*>(mask_src), p.n_store, p.M, ldy);
+  if (rc) return rc;
+  // what depends on the tile width: the column tiling and the filter map's box
+  auto set_width = [&](GemmTcParams& q, int bn) -> int {
+    q.bn = q.bn_load = bn;
+    q.n_tiles = (n_cols + bn - 1) / bn;
+    q.b_split = pick_box_split(g_opt.b_split, bn, q.bk);
+    return make_map_3d(&q.tm_b, w, Cp, (uint64_t)R * S, Kout, Cp, (uint64_t)R * S * Cp, q.bk, 1, bn / q.b_split, ksw);
+  };
+  // Between 257 and 512 output columns there is a second candidate: ONE tile as wide as the layer (two MMAs side
+  // by side, one accumulator set, no overlap of epilogue and main loop) instead of two or more narrower tiles
+  // that each load the A operand again. Which is faster is decided by measurement in tuning mode and remembered
+  // per shape; without a measurement the narrower tiles are taken.
+  const int bn_default = p.bn;
+  const int bn_wide = (n_cols > 256 && n_cols <= 512 && g_opt.force_wide != 0 && g_opt.bn_cap >= 256) ? n_cols : 0;
+  int bn_use = bn_default;
+  if (bn_wide) {
+    p.bn = p.n_tiles = 0;
+    const PlanKey wkey = plan_key(p);
+    std::lock_guard<std::mutex> lock(g_plan_mutex);   // released at the end of this block, before `launch` takes it
+    auto it = g_bn_cache.find(wkey);
+    if (g_opt.force_wide == 1) {
+      bn_use = bn_wide;
+    } else if (it != g_bn_cache.end()) {
+      bn_use = it->second;
+    } else if (tunable(p, stream)) {
+      float best_ms = 1e30f;
+      for (int bn : {bn_default, bn_wide}) {
+        GemmTcParams q = p;
+        if (set_width(q, bn)) continue;
+        Plan pl{1, 1, 0, 0, 0.0};
+        const float ms = tune_plan(q, true, stream, &pl);
+        if (ms > 0.f) {
+          g_plan_cache[plan_key(q)] = pl;
+          if (ms < best_ms) { best_ms = ms; bn_use = bn; }
+        }
+      }
+      g_bn_cache[wkey] = bn_use;
+    }
+  }
+  rc = set_width(p, bn_use);
   if (rc) return rc;
   return launch(p, false, 1, true, stream);
 }
@@ -1176,9 +1492,8 @@ int rb_conv_wgrad_tc(const void* x, int N, int H, int W, int Cp, const void* dy,
     const double waste = (double)(p.n_tiles * T) / taps;
     if (pl.cost * waste < best_cost * 0.97) { best_cost = pl.cost * waste; best_bn = T * cw; best_taps = T; }
   }
-  {  // test hook: RB_GEMM_FORCE_TAPS=T takes the T-taps-per-tile candidate when it is feasible
-    const char* e = getenv("RB_GEMM_FORCE_TAPS");
-    const int T = e ? atoi(e) : 0;
+  {  // option force_taps = T takes the T-taps-per-tile candidate when it is feasible
+    const int T = g_opt.force_taps;
     if (T == 1 && best_taps != 1) { best_taps = 1; best_bn = cw > 256 ? 256 : cw; }
     if (T > 1 && T * cw <= 256 && T <= taps) { best_taps = T; best_bn = T * cw; }
   }
@@ -1210,6 +1525,37 @@ int rb_conv_wgrad_tc(const void* x, int N, int H, int W, int Cp, const void* dy,
   if (split_k > p.num_kb) split_k = p.num_kb;
   while (split_k > 1 && !split_ok(split_k, p.num_kb)) --split_k;
   return launch(p, split_k <= 0, split_k > 0 ? split_k : 0, false, stream);
+}
+
+// Planner options by name (see GemmOptions); returns 0, or -1 for an unknown name.
+int rb_gemm_set_option(const char* name, int value) {
+  options_from_env();
+  int* slot = option_slot(name);
+  if (!slot) return -1;
+  *slot = value;
+  return 0;
+}
+
+int rb_gemm_get_option(const char* name, int* value) {
+  options_from_env();
+  int* slot = option_slot(name);
+  if (!slot) return -1;
+  *value = *slot;
+  return 0;
+}
+
+// Tuning mode: while on, a bf16-epilogue launch of a shape without a cached plan times its candidates (it
+// synchronises the stream, so it must not run inside a stream capture) and caches the winner.
+int rb_gemm_tune_mode(int on) {
+  g_tune_mode = on ? 1 : 0;
+  return 0;
+}
+
+int rb_gemm_clear_plans() {
+  std::lock_guard<std::mutex> lock(g_plan_mutex);
+  g_plan_cache.clear();
+  g_bn_cache.clear();
+  return 0;
 }
 
 int rb_num_sms() {

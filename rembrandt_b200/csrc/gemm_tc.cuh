@@ -28,7 +28,7 @@ struct alignas(64) GemmTcParams {
   CUtensorMap tm_d;    // EPI_BF16: output map for the TMA stores of the epilogue (box 64 columns x 32 rows)
   int a_mode, b_mode;
   int M, N;            // extent of D in rows / columns (tiles are clipped against these)
-  int bn;              // tile width  (multiple of 32, <= 256)
+  int bn;              // tile width (multiple of 32); above 256 the tile is two MMAs wide (256 + the rest), mt = 1
   int bn_load;         // rows of B brought in per k-block (= bn; kept separate from the MMA width)
   int bk;              // k-block depth (64 or 32)
   int num_kb;          // k-blocks over the whole reduction
@@ -36,7 +36,7 @@ struct alignas(64) GemmTcParams {
   int stages;
   int mt;              // 128-row sub-tiles per work item (1 or 2): they share one B stage
   int b_resident;      // 1: the whole B panel (all k-blocks) is loaded once per CTA and stays in shared memory
-  int acc_stride;      // TMEM columns between the accumulators of the sub-tiles (128 or 256)
+  int acc_stride;      // TMEM columns between the accumulators of the sub-tiles (128, 256 or 512)
   int acc_bufs;        // accumulator sets in TMEM (2 = epilogue overlaps the next main loop, 1 = no overlap)
   // convolution geometry (im2col operands)
   int cv_P, cv_Q;      // output height / width per image
@@ -70,7 +70,15 @@ struct alignas(64) GemmTcParams {
   const float* bias;               // optional, indexed by column
   const __nv_bfloat16* mask_src;   // optional, same layout as D: D is zeroed where mask_src <= 0
   unsigned int* status;            // error bits (see ptx.cuh)
-  int dbg;                         // timing experiments only: 1 = epilogue skips its global stores
+  // Tail cut (EPI_BF16, split_k = 1): the work items of the last, partly filled wave are cut along the reduction
+  // into `tail_split` parts each, so that every SM gets a share of them instead of a few SMs a whole item. The
+  // parts add their fp32 partial sums into a workspace (TMA reduce-add); `tail_fix_kernel` then applies the
+  // epilogue (bias, activation, mask, bf16) to those items and clears the workspace again.
+  CUtensorMap tm_ws;   // fp32 workspace: [tail_items * mt * 128 rows][bn columns], 32 x 32 boxes
+  float* ws;           // zero on entry, zero again after the fix-up; null = no tail cut possible
+  long long ws_bytes;
+  int tail_items;      // 0 = no tail cut
+  int tail_split;
 };
 
 }  // namespace rb

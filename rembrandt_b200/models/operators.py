@@ -613,6 +613,18 @@ class Conv2dOp(Op):
         super().alloc()
         if self.net.training_capable and self.wants_prev_delta() and self.cfg.conv_stride == 1:
             self.wt16 = torch.zeros((self.cp, self.rs, self.out_cp), dtype=torch.bfloat16, device=self.net.device)
+        if self.net.device.type == "cuda" and not self.direct:
+            self._tune()
+
+    def _tune(self):
+        """Measure the tile plans of this layer's forward and data-grad shapes once, on scratch operands."""
+        h, w, r, s, p = self._geom()
+        n, ko = self.net.batch, self.cfg.out_channels
+        K.tune_conv(n, h, w, self.cp, ko, r, r, s, p, p, self.P, self.Q, self.out_cp, relu=self.has_relu,
+                    has_bias=self.seg_b is not None, n_valid=ko, n_store=self.out_cp)
+        if self.wt16 is not None:
+            K.tune_conv(n, self.P, self.Q, self.out_cp, self.cp, r, r, 1, r - 1 - p, r - 1 - p, h, w, self.cp,
+                        has_mask=self.mask_src() is not None, n_valid=self.in_c, n_store=self.cp)
 
     # geometry the kernels see (the s2d form is a stride-1, pad-0 convolution on the rearranged input)
     def _geom(self):

@@ -50,6 +50,15 @@ class _BnConv:
         self.wt16 = None
         if net.training_capable and need_dx_filters and self.s == 1:
             self.wt16 = torch.zeros((self.cp, self.k * self.k, self.kp), dtype=torch.bfloat16, device=dev)
+        if dev.type == "cuda":
+            # tile plans of the forward and data-grad shapes, measured once on scratch operands
+            K.tune_conv(n, self.h, self.w, self.cp, self.ko, self.k, self.k, self.s, self.p, self.p, self.P, self.Q,
+                        self.kp, n_valid=self.ko, n_store=self.kp)
+            if self.wt16 is not None:
+                for has_mask in (False, True):
+                    K.tune_conv(n, self.P, self.Q, self.kp, self.cp, self.k, self.k, 1, self.k - 1 - self.p,
+                                self.k - 1 - self.p, self.h, self.w, self.cp, has_mask=has_mask, n_valid=self.in_c,
+                                n_store=self.cp)
 
     def v(self, seg, which="params"):
         return self.op.net.seg_view(seg, which)

@@ -44,20 +44,114 @@ def read_status() -> int:
 
 
 # ------------------------------------------------------------------ GEMM / convolution (tcgen05)
+GEMM_WORKSPACE_BYTES = 40 << 20
+_gemm_workspaces: dict = {}
+
+
+def gemm_workspace() -> torch.Tensor:
+    """Zeroed fp32 scratch of the tensor-core kernel for (device, current stream): the partial sums of work items that
+    are cut along the reduction pass through it, and the kernel that finishes those items clears it again. Launches
+    that share a workspace must be ordered on one stream, hence one workspace per stream."""
+    key = (torch.cuda.current_device(), stream_handle())
+    ws = _gemm_workspaces.get(key)
+    if ws is None:
+        ws = _gemm_workspaces[key] = torch.zeros(GEMM_WORKSPACE_BYTES // 4, dtype=torch.float32, device="cuda")
+    return ws
+
+
+def gemm_set_option(name: str, value: int) -> None:
+    """Planner switch of the tensor-core kernel by name (force_mt, force_resident, force_halo, force_taps, force_tail,
+    force_wide, bk32, bn_cap, a_split, b_split, autotune); initial values come from RB_GEMM_<NAME> at first use."""
+    if _native.cuda().rb_gemm_set_option(name.encode(), int(value)) != 0:
+        raise KeyError(name)
+
+
+def gemm_get_option(name: str) -> int:
+    import ctypes as C_
+    v = C_.c_int(0)
+    if _native.cuda().rb_gemm_get_option(name.encode(), C_.byref(v)) != 0:
+        raise KeyError(name)
+    return v.value
+
+
+class gemm_options:
+    """``with gemm_options(force_mt=2, force_resident=0): ...`` sets planner switches and restores them on exit."""
+
+    def __init__(self, **kw):
+        self.kw, self.saved = kw, {}
+
+    def __enter__(self):
+        for k, v in self.kw.items():
+            self.saved[k] = gemm_get_option(k)
+            gemm_set_option(k, v)
+        return self
+
+    def __exit__(self, *exc):
+        for k, v in self.saved.items():
+            gemm_set_option(k, v)
+        return False
+
+
+class gemm_tuning:
+    """While active, a launch of a forward / data-grad shape that has no cached plan times its candidate tile plans
+    (it synchronises the stream: never inside a graph capture) and caches the fastest. A network does this at build
+    time on scratch operands (`tune_conv`); outside this block launches never measure anything."""
+
+    def __enter__(self):
+        _native.cuda().rb_gemm_tune_mode(1)
+        return self
+
+    def __exit__(self, *exc):
+        _native.cuda().rb_gemm_tune_mode(0)
+        return False
+
+
+def gemm_clear_plans() -> None:
+    _native.cuda().rb_gemm_clear_plans()
+
+
 def gemm_tc(a, a_mn, lda, b, b_mn, ldb, M, N, K, d, ldd, epi=EPI_BF16, bias=None, relu=False, mask_src=None,
             n_valid=0, n_store=0, split_k=0, bn_cap=0):
+    ws = gemm_workspace() if epi == EPI_BF16 else None
     rc = _native.cuda().rb_gemm_tc(ptr(a), int(a_mn), lda, ptr(b), int(b_mn), ldb, M, N, K, ptr(d), ldd, epi,
                                    ptr(bias), int(relu), ptr(mask_src), n_valid, n_store, split_k, bn_cap,
+                                   ptr(ws), ws.numel() * 4 if ws is not None else 0,
                                    ptr(status_word()), stream_handle())
     check(rc, "rb_gemm_tc")
 
 
 def conv_fprop_tc(x, N, H, W, Cp, w, Kout, R, S, stride, pad_h, pad_w, P, Q, y, ldy, bias=None, relu=False,
                   mask_src=None, n_valid=0, n_store=0):
+    ws = gemm_workspace()
     rc = _native.cuda().rb_conv_fprop_tc(ptr(x), N, H, W, Cp, ptr(w), Kout, R, S, stride, pad_h, pad_w, P, Q, ptr(y),
                                          ldy, ptr(bias), int(relu), ptr(mask_src), n_valid, n_store,
-                                         ptr(status_word()), stream_handle())
+                                         ptr(ws), ws.numel() * 4, ptr(status_word()), stream_handle())
     check(rc, "rb_conv_fprop_tc")
+
+
+_tuned_convs: set = set()
+
+
+def tune_conv(N, H, W, Cp, Kout, R, S, stride, pad_h, pad_w, P, Q, ldy, relu=False, has_bias=False, has_mask=False,
+              n_valid=0, n_store=0):
+    """Measure the tile plans of one convolution shape (forward form; a stride-1 data-grad is the same call with the
+    roles of input and output exchanged) on scratch operands and cache the winner; later launches of the shape only
+    look the plan up. Idempotent per shape and process."""
+    key = (torch.cuda.current_device(), N, H, W, Cp, Kout, R, S, stride, pad_h, pad_w, P, Q, ldy, bool(has_mask),
+           n_valid, n_store)
+    if key in _tuned_convs:
+        return
+    _tuned_convs.add(key)
+    dev = "cuda"
+    x = torch.zeros((N, H, W, Cp), dtype=torch.bfloat16, device=dev)
+    w = torch.zeros((max(Kout, n_store), R * S, Cp), dtype=torch.bfloat16, device=dev)
+    y = torch.zeros((N * P * Q, ldy), dtype=torch.bfloat16, device=dev)
+    bias = torch.zeros(max(Kout, n_store), dtype=torch.float32, device=dev) if has_bias else None
+    mask = torch.zeros_like(y) if has_mask else None
+    with gemm_tuning():
+        conv_fprop_tc(x, N, H, W, Cp, w, Kout, R, S, stride, pad_h, pad_w, P, Q, y, ldy, bias=bias, relu=relu,
+                      mask_src=mask, n_valid=n_valid, n_store=n_store)
+    torch.cuda.current_stream().synchronize()
 
 
 def conv_wgrad_tc(x, N, H, W, Cp, dy, lddy, Kout, R, S, stride, pad_h, pad_w, P, Q, dw, split_k=0):

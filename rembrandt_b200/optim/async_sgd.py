@@ -2,7 +2,9 @@
 clock, on its own local model (the reference's older ``AsyncSgdOpt``, src/opt/sgd/async.rs, which pre-dates the
 shared ``OptSharedData`` barrier and is no longer compiled there).
 
-Intended for the gossip / elastic backends, whose exchanges tolerate workers that are steps apart. Differences to
+Intended for the gossip / elastic backends, whose exchanges tolerate workers that are steps apart; a backend that has
+a lock-step and an asynchronous form (push gossip, pull gossip, elastic averaging on the kernel backend) must be in
+its asynchronous form, or its own cross-GPU barriers would put the ranks back in step. Differences to
 ``SgdOpt``: no barrier before or after the checkpoint window, no exact synchronisation of the parameters at a
 checkpoint (each rank writes its own parameter files under ``<checkpoint_dir>/rank<r>``), and the displayed training
 statistics are this rank's alone.
@@ -27,18 +29,19 @@ class AsyncSgdOpt(SgdOpt):
     def __init__(self, config, engine, **kw):
         super().__init__(config, engine, **kw)
         self.shared = _LocalStats()
+        if self.world > 1 and getattr(self.comm, "synchronous", False):
+            raise ValueError(f"{self.comm.name} is in its lock-step form (synchronous=True): its exchanges contain "
+                             "cross-GPU barriers, which a barrier-free loop must not run")
 
-    def train(self, train_data, valid_data=None, max_iters=None):
-        comm = self.comm
-        # the barrier calls of the synchronous loop become no-ops for the duration of the run
-        saved = (comm.signal_barrier, comm.wait_barrier, comm.barrier)
-        comm.signal_barrier = lambda: None
-        comm.wait_barrier = lambda: True
-        comm.barrier = lambda: None
-        try:
-            return super().train(train_data, valid_data, max_iters)
-        finally:
-            comm.signal_barrier, comm.wait_barrier, comm.barrier = saved
+    # the loop's own barriers do nothing here; the communication backend is left as it is
+    def _signal_barrier(self):
+        pass
+
+    def _wait_barrier(self) -> bool:
+        return True
+
+    def _barrier(self):
+        pass
 
     def _checkpoint_window(self, t, valid_data, t_start):
         cfg, eng, net = self.cfg, self.engine, self.net

@@ -130,12 +130,16 @@ class _P2PBase:
     def _flag_ptrs(self):
         return self.arena.ptrs("flags")
 
+    # limit of every wait on a peer inside the kernels of this backend, in ns (0 = the kernels' 3 s default)
+    wait_ns = 0
+
     def _barrier_kernel(self, slot, stream):
         a = PK.BarrierArgs()
         _fill_ptrs(a.flags, self._flag_ptrs())
         a.epoch_ptr = self.epochs[slot:].data_ptr()
         a.status = self.status.data_ptr()
         a.rank, a.world, a.slot = self.rank, self.world, slot
+        a.wait_ns = int(self.wait_ns)
         check(PK.fn("rb_barrier_p2p")(C.byref(a), stream.cuda_stream), "rb_barrier_p2p")
 
 
@@ -311,6 +315,7 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         a.one_shot = 1 if (op == 0 and n <= self.one_shot_elems) else 0
         a.op = op
         a.avg_scale = scale if scale is not None else 1.0 / self.world
+        a.wait_ns = int(self.wait_ns)
         if op == 0:
             lr, mu, l2, gs, mode = self._hyper
             a.h.lr, a.h.mu, a.h.l2, a.h.grad_scale, a.h.mode, a.h.phase = lr, mu, l2, gs, mode, 3
@@ -439,6 +444,7 @@ class GossipP2PComm(CommWorker, _P2PBase):
         a.n = flat.numel() // 4 * 4
         a.rank, a.world, a.slot = self.rank, self.world, slot
         a.wait_peer = 1 if self.synchronous else 0
+        a.wait_ns = int(self.wait_ns)
         a.mix_self = 0 if self.mode == "pair" else 1
         a.w_self = 1.0
         a.peer = peers[0]
@@ -505,6 +511,7 @@ class GroupGossipP2PComm(GossipP2PComm):
         a.n = flat.numel() // 4 * 4
         a.rank, a.world, a.slot = self.rank, self.world, slot
         a.wait_peer = 1
+        a.wait_ns = int(self.wait_ns)
         a.w_self = 1.0
         peers = self.group_peers or [self.rank]
         self._phase(a, peers, [1.0 / (k + 2) for k in range(len(peers))], 0, st)
@@ -512,16 +519,27 @@ class GroupGossipP2PComm(GossipP2PComm):
 
 
 class ElasticP2PComm(CommWorker, _P2PBase):
-    """Elastic averaging with the centre in rank 0's memory: clients read it and add their pull to it with
-    peer-to-peer loads and reductions; rank 0 folds the accumulated pulls into the centre."""
+    """Elastic averaging with the centre in rank 0's memory (beta = 0.8 / N, src/worker/elasticserver_dist.rs:249).
+
+    Asynchronous (the default, as in the reference): a client takes the centre's lock word with a compare-and-swap,
+    mixes with the centre as it is at that moment -- x <- x - beta (x - c), c <- c + beta (x - c), read and written
+    through peer memory in one kernel -- and releases the lock. Clients are served one at a time and may be any number
+    of iterations apart; nobody waits for another rank to reach a round. A client that does not get the lock within
+    `lock_wait_ns` gives that exchange up (`skipped_exchanges()` counts them).
+
+    `synchronous=True` is the lock-step form: every client mixes with the same centre snapshot, the pulls are summed
+    into rank 0's accumulator and folded into the centre between two cross-GPU barriers."""
     name = "elastic_p2p"
     graph_safe = False
 
-    def __init__(self, group=None, beta: Optional[float] = None, blocks: int = 96):
+    def __init__(self, group=None, beta: Optional[float] = None, blocks: int = 96, synchronous: bool = False,
+                 lock_wait_ns: int = 200_000_000):
         CommWorker.__init__(self, group)
         self._init_p2p(group, num_slots=8)
         self.beta = beta if beta is not None else 0.8 / max(1, self.world)
         self.blocks = blocks
+        self.synchronous = bool(synchronous)
+        self.lock_wait_ns = int(lock_wait_ns)
         self.net = None
 
     def attach(self, engine):
@@ -529,6 +547,9 @@ class ElasticP2PComm(CommWorker, _P2PBase):
         n = self.net.flat_len
         self.center = self.arena.alloc("center", n, torch.float32)
         self.delta = self.arena.alloc("delta", n, torch.float32)
+        self.lock = self.arena.alloc("lock", 8, torch.int64)
+        self.ticket = torch.zeros(4, dtype=torch.int32, device=self.center.device)
+        self.skipped = torch.zeros(1, dtype=torch.int32, device=self.center.device)
 
     def first_one_way_sync(self, flat):
         if self.world > 1:
@@ -536,6 +557,10 @@ class ElasticP2PComm(CommWorker, _P2PBase):
         self.center.copy_(flat)
         torch.cuda.synchronize()
         dist.barrier(self.group)
+
+    def skipped_exchanges(self) -> int:
+        """Exchanges this rank gave up because the centre stayed locked for longer than `lock_wait_ns`."""
+        return int(self.skipped.item())
 
     def sync_params(self, flat, repeat=False):
         if self.world <= 1:
@@ -547,11 +572,22 @@ class ElasticP2PComm(CommWorker, _P2PBase):
         a.w = flat.data_ptr()
         a.w16 = net.params16.data_ptr() if flat.data_ptr() == net.params.data_ptr() else None
         a.pub_peer = self.arena.ptrs("center")[0]
-        a.acc_target = self.arena.ptrs("delta")[0]
         a.status = self.status.data_ptr()
         a.n = flat.numel() // 4 * 4
         a.rank, a.world = self.rank, self.world
         a.alpha = self.beta
+        if not self.synchronous:
+            a.gate = self.arena.ptrs("lock")[0]
+            a.ticket = self.ticket.data_ptr()
+            a.skipped = self.skipped.data_ptr()
+            a.block_counter = self.counters[4:].data_ptr()
+            a.wait_ns = self.lock_wait_ns
+            check(PK.fn("rb_elastic_begin_p2p")(C.byref(a), st.cuda_stream), "rb_elastic_begin_p2p")
+            check(PK.fn("rb_elastic_mix_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_elastic_mix_p2p")
+            self.bytes_moved += a.n * 8
+            return
+        a.acc_target = self.arena.ptrs("delta")[0]
+        a.wait_ns = int(self.wait_ns)
         check(PK.fn("rb_elastic_pull_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_elastic_pull_p2p")
         self._barrier_kernel(2, st)
         if self.rank == 0:
@@ -571,22 +607,34 @@ class ElasticP2PComm(CommWorker, _P2PBase):
 
 
 class PushGossipP2PComm(CommWorker, _P2PBase):
-    """Push gossip: every rank adds its vector into a random target's accumulator with peer-to-peer reductions;
-    after a barrier each rank keeps (w_self * own + received) / (w_self + count)."""
+    """Push gossip: every rank adds its vector into a random target's accumulator with peer-to-peer reductions and
+    keeps (w_self * own + received) / (w_self + count), w_self = 2 when it drew itself.
+
+    Asynchronous (the default, as in the reference, src/worker/gossip_dist.rs:474-593,883-976): no barrier. A pusher
+    registers at the target's gate word, adds into whichever of the target's two accumulators is open, and counts
+    itself in; at its own exchange a rank closes its open accumulator, waits only for pushes already in flight into it
+    and folds in whatever arrived -- nothing, if nobody pushed (`recv_count == 0`). A push that arrives after the
+    close lands in the other accumulator and is folded one exchange later. Ranks may be any number of iterations apart.
+
+    `synchronous=True` is the lock-step form: push, cross-GPU barrier, fold, barrier."""
     name = "gossip_push_p2p"
     graph_safe = False
 
-    def __init__(self, group=None, seed=(41, 43), blocks: int = 96):
+    def __init__(self, group=None, seed=(41, 43), blocks: int = 96, synchronous: bool = False):
         CommWorker.__init__(self, group)
         self._init_p2p(group, num_slots=8)
         self.rng = XorShift128Plus(seed[0] + 7919 * self.rank, seed[1])
         self.blocks = blocks
+        self.synchronous = bool(synchronous)
         self.net = None
 
     def attach(self, engine):
         self.net = engine.net
-        self.acc = self.arena.alloc("acc", self.net.flat_len, torch.float32)
+        n = self.net.flat_len
+        self.acc = self.arena.alloc("acc", 2 * n, torch.float32)     # two accumulators (the synchronous form uses one)
         self.count = self.arena.alloc("count", ALIGN, torch.float32)
+        self.gate = self.arena.alloc("gate", 8, torch.int64)
+        self.ticket = torch.zeros(4, dtype=torch.int32, device=self.acc.device)
 
     def sync_params(self, flat, repeat=False):
         if self.world <= 1:
@@ -605,6 +653,21 @@ class PushGossipP2PComm(CommWorker, _P2PBase):
         a.n = flat.numel() // 4 * 4
         a.rank, a.world, a.peer = self.rank, self.world, target
         a.w_self = 2.0 if target == self.rank else 1.0
+        a.wait_ns = int(self.wait_ns)
+        if not self.synchronous:
+            a.gate = self.arena.ptrs("gate")[target]
+            a.ticket = self.ticket.data_ptr()
+            check(PK.fn("rb_push_begin_p2p")(C.byref(a), st.cuda_stream), "rb_push_begin_p2p")
+            check(PK.fn("rb_push_add_async_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_push_add_async_p2p")
+            a.gate = self.gate.data_ptr()
+            a.ticket = self.ticket[1:].data_ptr()
+            a.acc_target = self.acc.data_ptr()
+            a.count_target = self.count.data_ptr()
+            a.block_counter = self.counters[5:].data_ptr()
+            check(PK.fn("rb_fold_begin_p2p")(C.byref(a), st.cuda_stream), "rb_fold_begin_p2p")
+            check(PK.fn("rb_fold_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_fold_p2p")
+            self.bytes_moved += a.n * 4
+            return
         check(PK.fn("rb_push_add_p2p")(C.byref(a), self.blocks, st.cuda_stream), "rb_push_add_p2p")
         self._barrier_kernel(2, st)
         a.acc_target = self.acc.data_ptr()

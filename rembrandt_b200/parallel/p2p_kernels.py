@@ -15,6 +15,12 @@ SIGS = {
     "rb_push_finalize": [vp, i32, vp],
     "rb_elastic_pull_p2p": [vp, i32, vp],
     "rb_elastic_apply": [vp, vp, i64, vp],
+    "rb_push_begin_p2p": [vp, vp],
+    "rb_push_add_async_p2p": [vp, i32, vp],
+    "rb_fold_begin_p2p": [vp, vp],
+    "rb_fold_p2p": [vp, i32, vp],
+    "rb_elastic_begin_p2p": [vp, vp],
+    "rb_elastic_mix_p2p": [vp, i32, vp],
     "rb_barrier_p2p": [vp, vp],
     "rb_link_probe": [vp, vp, vp, i64, i32, i32, i32, i32, vp],
 }
@@ -29,19 +35,20 @@ class ArSgdArgs(C.Structure):
                 ("flags", vp * MAX_RANKS), ("stage", vp * MAX_RANKS), ("w", vp), ("v", vp), ("mc_grads", vp),
                 ("mc_w16", vp), ("epoch_ptr", vp), ("block_counter", vp), ("status", vp), ("wait_ok", vp), ("off", i64),
                 ("n", i64), ("decay_len", i64), ("stage_off", i64), ("rank", i32), ("world", i32), ("slot", i32),
-                ("one_shot", i32), ("op", i32), ("zero_grads", i32), ("avg_scale", f32), ("h", SgdHyper)]
+                ("one_shot", i32), ("op", i32), ("zero_grads", i32), ("avg_scale", f32), ("h", SgdHyper), ("wait_ns", i64)]
 
 
 class MixArgs(C.Structure):
     _fields_ = [("flags", vp * MAX_RANKS), ("w", vp), ("w16", vp), ("pub_local", vp), ("pub_peer", vp),
                 ("acc_target", vp), ("count_target", vp), ("epoch_ptr", vp), ("block_counter", vp), ("status", vp),
                 ("n", i64), ("rank", i32), ("world", i32), ("slot", i32), ("peer", i32), ("wait_peer", i32),
-                ("alpha", f32), ("w_self", f32), ("not_last", i32), ("mix_self", i32)]
+                ("alpha", f32), ("w_self", f32), ("not_last", i32), ("mix_self", i32), ("wait_ns", i64), ("gate", vp),
+                ("ticket", vp), ("skipped", vp)]
 
 
 class BarrierArgs(C.Structure):
     _fields_ = [("flags", vp * MAX_RANKS), ("epoch_ptr", vp), ("status", vp), ("rank", i32), ("world", i32),
-                ("slot", i32)]
+                ("slot", i32), ("wait_ns", i64)]
 
 
 _bound = {}

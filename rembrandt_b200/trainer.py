@@ -163,6 +163,16 @@ class SgdOpt:
         raise DeviceWaitTimeout(f"rank {self.rank}: device status {status:#x} at iteration {t}: a bounded wait on a "
                                 f"peer ran out" + (f"; local state written to {saved}" if saved else ""))
 
+    # ---- the checkpoint barrier of the synchronous loop (the barrier-free loop overrides these three)
+    def _signal_barrier(self):
+        self.comm.signal_barrier()
+
+    def _wait_barrier(self) -> bool:
+        return self.comm.wait_barrier()
+
+    def _barrier(self):
+        self.comm.barrier()
+
     def before_step(self, images, labels):
         """Hook run before every batch is fed (used by the distillation optimizer)."""
 
@@ -177,8 +187,8 @@ class SgdOpt:
         with torch.no_grad():
             comm.first_one_way_sync(net.params)
         net.refresh_shadow()
-        comm.signal_barrier()
-        while not comm.wait_barrier():
+        self._signal_barrier()
+        while not self._wait_barrier():
             time.sleep(0.001)
         net.reset_grads()
         chkpt_step = cfg.step_size.at_iter(init_t)
@@ -247,7 +257,7 @@ class SgdOpt:
                     disp_loss = disp_correct = disp_samples = 0.0
 
                 if cfg.checkpoint_iters and t % cfg.checkpoint_iters == 0:
-                    comm.signal_barrier()
+                    self._signal_barrier()
                     self._checkpoint_window(t, valid_data, t_start)
                     chkpt_step = cfg.step_size.at_iter(t)
                 if max_iters and t >= max_iters:
@@ -268,7 +278,7 @@ class SgdOpt:
         eng.flush()
         eng.synchronize()
         self._check_device_status(t)
-        while not comm.wait_barrier():
+        while not self._wait_barrier():
             time.sleep(0.001)
         # a backend that shards the fp32 master (fused all-reduce + SGD) holds only this rank's shard up to date:
         # the snapshot, the state blob and the restore below all need the complete vector
@@ -294,7 +304,7 @@ class SgdOpt:
             net.restore_params()
         if nesterov:
             eng.stepper.nesterov_lookahead(+1.0)
-        comm.barrier()
+        self._barrier()
 
     # ------------------------------------------------------------------ validation
     def validate(self, valid_data: Iterable, num_batches: int, t: int = 0, t_start: Optional[float] = None):

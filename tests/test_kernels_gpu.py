@@ -118,6 +118,8 @@ CONV_CASES = [
     (2, 160, 9, 9, 64, 3, 1, 1),
     (1, 32, 40, 40, 64, 3, 1, 1),     # halo mode: row pitch 64 (two output rows per sub-tile)
     (1, 32, 70, 66, 32, 3, 1, 1),     # halo mode: row pitch 128, non-square
+    (128, 64, 13, 13, 64, 3, 1, 1),   # 169 row tiles on 148 SMs: the 21 of the last wave are cut along the reduction
+    (128, 32, 13, 13, 320, 3, 1, 1),  # the same with one 320-column tile (two MMAs side by side)
 ]
 
 
@@ -132,21 +134,35 @@ def _conv_setup(N, C, H, W, Ko, R, stride, pad, seed=0):
     return Cp, Kp, x, w, b, P, Q
 
 
-@pytest.fixture(params=["auto", "halo", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3"])
-def tile_mode(request, monkeypatch):
+@pytest.fixture(params=["auto", "halo", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3", "tail",
+                        "wide", "wide_tail", "tuned"])
+def tile_mode(request):
     """Force the kernel's tile-shape planner through each of its modes (two sub-tiles per item, resident B,
-    column-shifted halo tiles for stride-1 convolutions)."""
+    column-shifted halo tiles for stride-1 convolutions, the last wave cut along the reduction, one tile as wide as
+    the layer, plans chosen by measurement)."""
     mode = request.param
+    opts = {}
     if mode == "halo":
-        monkeypatch.setenv("RB_GEMM_FORCE_HALO", "1")
+        opts["force_halo"] = 1
     elif mode != "auto":
-        monkeypatch.setenv("RB_GEMM_FORCE_HALO", "0")
-    if mode not in ("auto", "halo"):
-        monkeypatch.setenv("RB_GEMM_FORCE_MT", "2" if "mt2" in mode else "1")
-        monkeypatch.setenv("RB_GEMM_FORCE_RESIDENT", "1" if "resident" in mode else "0")
+        opts["force_halo"] = 0
+    if mode.startswith("mt"):
+        opts["force_mt"] = 2 if "mt2" in mode else 1
+        opts["force_resident"] = 1 if "resident" in mode else 0
         if "taps" in mode:
-            monkeypatch.setenv("RB_GEMM_FORCE_TAPS", mode[-1])
-    return mode
+            opts["force_taps"] = int(mode[-1])
+    if "tail" in mode:
+        opts["force_tail"] = 1
+    if "wide" in mode:
+        opts["force_wide"] = 1
+    if mode == "tuned":
+        K.gemm_clear_plans()
+        with K.gemm_tuning():
+            yield mode
+        K.gemm_clear_plans()
+        return
+    with K.gemm_options(**opts):
+        yield mode
 
 
 @pytest.mark.parametrize("case", CONV_CASES)

@@ -308,6 +308,7 @@ def test_push_gossip_launches_give_the_count_normalised_mean(monkeypatch):
     for r in range(world):
         c, w = _bare(p2p.PushGossipP2PComm, pw, r, world)
         c.rng = XorShift128Plus(41 + 7919 * r, 43)
+        c.synchronous = True
         c.attach(types.SimpleNamespace(net=c.net))
         comms.append(c)
         ws.append(w)
@@ -329,6 +330,196 @@ def test_push_gossip_launches_give_the_count_normalised_mean(monkeypatch):
             assert float(comms[r].acc.abs().sum()) == 0.0 and float(comms[r].count[0]) == 0.0
 
 
+# ---- the asynchronous forms: no barrier launches; every launch runs the moment it is issued ------------------------
+class AsyncWorld(PtrWorld):
+    """Kernels run immediately, in the order the ranks issue them: a sequential schedule of an asynchronous exchange.
+    The stand-ins restate the gate / ticket / lock protocol of the kernels on CPU tensors."""
+
+    def view64(self, ptr):
+        for t in self.tensors:
+            lo = t.data_ptr()
+            if t.dtype == torch.int64 and lo <= ptr < lo + t.numel() * 8:
+                return t.reshape(-1)[(ptr - lo) // 8:]
+        raise KeyError(hex(ptr))
+
+    def view32(self, ptr):
+        for t in self.tensors:
+            lo = t.data_ptr()
+            if t.dtype == torch.int32 and lo <= ptr < lo + t.numel() * 4:
+                return t.reshape(-1)[(ptr - lo) // 4:]
+        raise KeyError(hex(ptr))
+
+    def fn(self, name):
+        def launch(*args):
+            a = args[0]
+            if hasattr(a, "_obj"):
+                a = type(a._obj).from_buffer_copy(a._obj)
+            self.log.append((self.current, name))
+            getattr(self, "_" + name)(a, args[1:])
+            return 0
+        return launch
+
+    def _rb_push_begin_p2p(self, a, rest):
+        buf = -1
+        if a.peer != a.rank:
+            gate = self.view64(a.gate)
+            buf = (int(gate[0]) >> 32) & 1
+            gate[0] += 1 << (16 * buf)
+        self.view32(a.ticket)[0] = buf
+
+    def _rb_push_add_async_p2p(self, a, rest):
+        buf = int(self.view32(a.ticket)[0])
+        if buf < 0:
+            return
+        self.view(a.acc_target)[buf * a.n: (buf + 1) * a.n] += self.view(a.w)[: a.n]
+        self.view(a.count_target)[buf] += 1.0
+        self.view64(a.gate)[0] -= 1 << (16 * buf)
+
+    def _rb_fold_begin_p2p(self, a, rest):
+        gate = self.view64(a.gate)
+        closed = (int(gate[0]) >> 32) & 1
+        gate[0] += 1 << 32
+        assert (int(gate[0]) >> (16 * closed)) & 0xFFFF == 0, "a sequential schedule leaves no push in flight"
+        self.view32(a.ticket)[0] = closed
+
+    def _rb_fold_p2p(self, a, rest):
+        buf = int(self.view32(a.ticket)[0])
+        cnt = float(self.view(a.count_target)[buf])
+        if cnt > 0:
+            w, acc = self.view(a.w)[: a.n], self.view(a.acc_target)[buf * a.n: (buf + 1) * a.n]
+            w.copy_((a.w_self * w + acc) / (a.w_self + cnt))
+            acc.zero_()
+        self.view(a.count_target)[buf] = 0.0
+
+    def _rb_elastic_begin_p2p(self, a, rest):
+        lock = self.view64(a.gate)
+        got = 0
+        if int(lock[0]) == 0:
+            lock[0] = a.rank + 1
+            got = 1
+        else:
+            self.view32(a.skipped)[0] += 1
+        self.view32(a.ticket)[0] = got
+
+    def _rb_elastic_mix_p2p(self, a, rest):
+        if int(self.view32(a.ticket)[0]) != 1:
+            return
+        w, c = self.view(a.w)[: a.n], self.view(a.pub_peer)[: a.n]
+        d = a.alpha * (w - c)
+        w.sub_(d)
+        c.add_(d)
+        self.view64(a.gate)[0] = 0
+
+
+def _bare_async(cls, pw, rank, world):
+    c, w = _bare(cls, pw, rank, world)
+    real_alloc = c.arena.alloc
+
+    def alloc(name, numel, dtype):
+        return pw.reg(real_alloc(name, numel, dtype)) if dtype != torch.float32 else real_alloc(name, numel, dtype)
+    c.arena.alloc = alloc
+    return c, w
+
+
+def test_asynchronous_push_gossip_follows_the_sequential_oracle_with_ranks_steps_apart(monkeypatch):
+    """Rank 0 exchanges three times as often as the others; nobody waits. Oracle: the accumulate / count / fold rules
+    written out per rank (src/worker/gossip_dist.rs:474-593,883-976): a push lands in the target's open accumulator, a
+    fold closes it and keeps (w_self x + received) / (w_self + count), or x itself when nothing arrived."""
+    world, n = 4, 16
+    pw = AsyncWorld(world, n)
+    pw.log = []
+    monkeypatch.setattr(PK, "fn", pw.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    monkeypatch.setattr(torch, "zeros", _registering_zeros(pw, torch.zeros))
+    comms, ws = [], []
+    for r in range(world):
+        c, w = _bare_async(p2p.PushGossipP2PComm, pw, r, world)
+        c.rng = XorShift128Plus(41 + 7919 * r, 43)
+        c.synchronous = False
+        c.attach(types.SimpleNamespace(net=c.net))
+        comms.append(c)
+        ws.append(w)
+    shadows = [XorShift128Plus(41 + 7919 * r, 43) for r in range(world)]
+    torch.manual_seed(50)
+    x = [torch.randn(n) for _ in range(world)]
+    for r in range(world):
+        ws[r].copy_(x[r])
+    acc = [[torch.zeros(n), torch.zeros(n)] for _ in range(world)]
+    cnt = [[0, 0] for _ in range(world)]
+    epoch = [0] * world
+    schedule = [0, 1, 0, 0, 2, 0, 3, 0, 0, 1, 0, 2, 0, 0, 3, 1, 2, 0]
+    empty_folds = 0
+    for r in schedule:
+        pw.current = r
+        comms[r].sync_params(ws[r])
+        t = shadows[r].below(world)
+        if t != r:
+            acc[t][epoch[t] & 1] += x[r]
+            cnt[t][epoch[t] & 1] += 1
+        closed = epoch[r] & 1
+        epoch[r] += 1
+        w_self = 2.0 if t == r else 1.0
+        if cnt[r][closed]:
+            x[r] = (w_self * x[r] + acc[r][closed]) / (w_self + cnt[r][closed])
+            acc[r][closed] = torch.zeros(n)
+            cnt[r][closed] = 0
+        else:
+            empty_folds += 1
+        assert torch.allclose(ws[r], x[r], atol=1e-6), (r, t)
+    assert empty_folds > 0, "the schedule should contain exchanges in which nothing had arrived"
+    assert all(name != "rb_barrier_p2p" for _, name in pw.log), "the asynchronous form launches no barrier"
+
+
+def _registering_zeros(pw, real):
+    """torch.zeros that also registers what it makes with the fake world (the backends' local ticket / counter words)."""
+    def zeros(*a, **k):
+        k.pop("device", None)
+        t = real(*a, **k)
+        if t.dtype in (torch.int32, torch.int64):
+            pw.reg(t)
+        return t
+    return zeros
+
+
+def test_asynchronous_elastic_averaging_serves_clients_one_at_a_time(monkeypatch):
+    """Clients mix with the centre as it is when they get the lock (src/worker/elasticserver_dist.rs:667-715), in any
+    order and any number of times; a client that finds the centre locked gives the exchange up and counts it."""
+    world, n, beta = 3, 16, 0.25
+    pw = AsyncWorld(world, n)
+    pw.log = []
+    monkeypatch.setattr(PK, "fn", pw.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    monkeypatch.setattr(torch, "zeros", _registering_zeros(pw, torch.zeros))
+    comms, ws = [], []
+    for r in range(world):
+        c, w = _bare_async(p2p.ElasticP2PComm, pw, r, world)
+        c.beta, c.synchronous, c.lock_wait_ns = beta, False, 1000
+        c.attach(types.SimpleNamespace(net=c.net))
+        comms.append(c)
+        ws.append(w)
+    torch.manual_seed(60)
+    centre = torch.randn(n)
+    comms[0].center.copy_(centre)
+    x = [torch.randn(n) for _ in range(world)]
+    for r in range(world):
+        ws[r].copy_(x[r])
+    for r in [1, 1, 2, 0, 1, 2, 2, 0]:
+        pw.current = r
+        comms[r].sync_params(ws[r])
+        d = beta * (x[r] - centre)
+        x[r] = x[r] - d
+        centre = centre + d
+        assert torch.allclose(ws[r], x[r], atol=1e-6) and torch.allclose(comms[0].center, centre, atol=1e-6)
+    assert int(comms[0].lock[0]) == 0 and all(c.skipped_exchanges() == 0 for c in comms)
+    # somebody else holds the lock: the exchange is skipped, counted, and changes nothing
+    comms[0].lock[0] = 7
+    pw.current = 2
+    comms[2].sync_params(ws[2])
+    assert torch.allclose(ws[2], x[2], atol=0) and torch.allclose(comms[0].center, centre, atol=1e-6)
+    assert comms[2].skipped_exchanges() == 1 and int(comms[0].lock[0]) == 7
+    assert all(name != "rb_barrier_p2p" for _, name in pw.log)
+
+
 def test_elastic_averaging_launches_move_clients_and_centre_toward_each_other(monkeypatch):
     world, n, beta = 4, 16, 0.2
     pw = PtrWorld(world, n)
@@ -337,7 +528,7 @@ def test_elastic_averaging_launches_move_clients_and_centre_toward_each_other(mo
     comms, ws = [], []
     for r in range(world):
         c, w = _bare(p2p.ElasticP2PComm, pw, r, world)
-        c.beta = beta
+        c.beta, c.synchronous, c.lock_wait_ns = beta, True, 0
         c.attach(types.SimpleNamespace(net=c.net))
         comms.append(c)
         ws.append(w)
