@@ -1,9 +1,10 @@
 """Comparison baseline: the same models and optimizer on stock PyTorch (cuDNN / cuBLAS kernels, DDP over NCCL).
 
 The reference itself (a 2016 Rust crate over cuDNN v4 and MPI) cannot be built offline, so the number to
-beat is this: torch DDP + cuDNN/cuBLAS, bf16 autocast, channels-last activations, SGD momentum 0.9 with
-weight decay 5e-4, 25 MB gradient buckets, same synthetic input shape and batch per GPU. None of the
-framework's own kernels or engine is on this path.
+beat is this: torch DDP + cuDNN/cuBLAS, bf16, channels-last activations, SGD momentum 0.9 with weight decay
+5e-4, 25 MB gradient buckets, same synthetic input shape and batch per GPU -- driven eagerly, or with the whole
+step captured in a CUDA graph, or compiled; the benchmark reports the fastest of the variants it was asked to
+run. None of the framework's own kernels or engine is on this path.
 """
 from __future__ import annotations
 
@@ -106,36 +107,98 @@ MODELS = {"alexnet": (AlexNet, 227, 3, 1000, 227), "nin": (NiN, 224, 3, 1000, 22
 
 
 class TorchBaseline:
-    """One data-parallel replica; `step(images_u8, labels)` does input cast, forward, backward, all-reduce, SGD."""
+    """One data-parallel replica; `step(images_u8, labels)` does input cast, forward, backward, all-reduce, SGD.
 
-    def __init__(self, model="alexnet", batch=128, world=1, rank=0, device="cuda", lr=0.01, momentum=0.9, wd=5e-4):
+    `variant` picks how stock PyTorch is driven, so that the comparison is against its best form, not its slowest:
+
+    * ``eager``    fp32 parameters, bf16 autocast, one kernel launch per operator from Python;
+    * ``graph``    the same step (input cast, forward, backward, DDP all-reduce, fused SGD) captured once in a CUDA
+                   graph and replayed: no launch or Python overhead, like this framework's own engine;
+    * ``bf16_graph`` the module held in bf16 outright (no autocast casts, no fp32 master: less work than this
+                   framework does), channels-last, captured in a CUDA graph;
+    * ``compiled`` ``torch.compile(mode="max-autotune-no-cudagraphs")`` of the network, step captured in a CUDA graph.
+    """
+
+    VARIANTS = ("eager", "graph", "bf16_graph", "compiled")
+
+    def __init__(self, model="alexnet", batch=128, world=1, rank=0, device="cuda", lr=0.01, momentum=0.9, wd=5e-4,
+                 variant="eager"):
         cls, hw, c, k, crop = MODELS[model]
         self.hw, self.c, self.k, self.batch, self.crop = hw, c, k, batch, crop
         self.device = torch.device(device)
+        self.variant = variant
+        self.world = world
         torch.manual_seed(0)
         net = cls().to(self.device).to(memory_format=torch.channels_last)
+        self.pure_bf16 = variant == "bf16_graph"
+        if self.pure_bf16:
+            net = net.to(torch.bfloat16)
+        if variant == "compiled":
+            net = torch.compile(net, mode="max-autotune-no-cudagraphs")
         if world > 1:
             net = torch.nn.parallel.DistributedDataParallel(net, device_ids=[self.device.index], bucket_cap_mb=25,
                                                             gradient_as_bucket_view=True)
         self.net = net
         self.opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=momentum, weight_decay=wd, fused=True)
         self.loss = None
+        self.graph = None
+        self._static_x = self._static_y = None
+        self._stream = None
 
-    def step(self, images_u8, labels):
-        x = images_u8.to(self.device, non_blocking=True)
-        y = labels.to(self.device, non_blocking=True).long()
-        if self.crop < self.hw:   # one random crop offset per batch + flip coin, as torchvision pipelines do per sample
-            oy, ox = (int(v) for v in torch.randint(0, self.hw - self.crop + 1, (2,)))
-            x = x[:, :, oy:oy + self.crop, ox:ox + self.crop]
-            if int(torch.randint(0, 2, (1,))):
-                x = x.flip(-1)
-        x = (x.float() - 127.5) * (1.0 / 73.9)
+    # ---- the step itself (what a graph captures)
+    def _compute(self, x_u8, y):
+        if self.crop < self.hw:
+            if self.graph is not None or self.variant != "eager":
+                o = (self.hw - self.crop) // 2      # a captured step cannot draw on the host: centre crop
+                x_u8 = x_u8[:, :, o:o + self.crop, o:o + self.crop]
+            else:   # one random crop offset per batch + flip coin
+                oy, ox = (int(v) for v in torch.randint(0, self.hw - self.crop + 1, (2,)))
+                x_u8 = x_u8[:, :, oy:oy + self.crop, ox:ox + self.crop]
+                if int(torch.randint(0, 2, (1,))):
+                    x_u8 = x_u8.flip(-1)
+        x = (x_u8.float() - 127.5) * (1.0 / 73.9)
         x = x.contiguous(memory_format=torch.channels_last)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = self.net(x)
+        if self.pure_bf16:
+            out = self.net(x.to(torch.bfloat16))
             loss = F.cross_entropy(out.float(), y)
+        else:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = self.net(x)
+                loss = F.cross_entropy(out.float(), y)
         self.opt.zero_grad(set_to_none=True)
         loss.backward()
         self.opt.step()
-        self.loss = loss
         return loss
+
+    def _capture(self, images_u8, labels):
+        """Warm up on a side stream (DDP needs 11 eager iterations before a capture), then capture one step."""
+        self._static_x = torch.zeros((self.batch, self.c, self.hw, self.hw), dtype=torch.uint8, device=self.device)
+        self._static_y = torch.zeros((self.batch,), dtype=torch.long, device=self.device)
+        self._static_x.copy_(images_u8, non_blocking=True)
+        self._static_y.copy_(labels.long(), non_blocking=True)
+        s = torch.cuda.Stream(self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(11 if self.world > 1 else 3):
+                self._compute(self._static_x, self._static_y)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        self.opt.zero_grad(set_to_none=True)
+        with torch.cuda.graph(g):
+            self._static_loss = self._compute(self._static_x, self._static_y)
+        self.graph = g
+
+    def step(self, images_u8, labels):
+        if self.variant == "eager":
+            x = images_u8.to(self.device, non_blocking=True)
+            y = labels.to(self.device, non_blocking=True).long()
+            self.loss = self._compute(x, y)
+            return self.loss
+        if self.graph is None:
+            self._capture(images_u8, labels)
+        self._static_x.copy_(images_u8, non_blocking=True)
+        self._static_y.copy_(labels, non_blocking=True)
+        self.graph.replay()
+        self.loss = self._static_loss
+        return self.loss

@@ -129,6 +129,14 @@ class Net:
         if not self.is_cuda:
             self.params.requires_grad_(True)
             self.params.grad = self.grads
+        # Small kernels that depend on nothing the main stream is about to produce (bias-gradient column sums, the
+        # re-packing of filters for the data-grad) run on a side stream beside the tensor-core kernels, which leave
+        # DRAM and most of the register file idle; `side` forks, `join_side` joins (both are captured into graphs).
+        self._side = None
+        self._side_dirty = False
+        if self.device.type == "cuda":
+            self._side = torch.cuda.Stream(self.device)
+            self._side_fork, self._side_join = torch.cuda.Event(), torch.cuda.Event()
         if self.is_cuda:
             for op in self.ops:
                 op.alloc()
@@ -244,6 +252,25 @@ class Net:
         with torch.no_grad():
             self.grads.copy_(self.saved_params - self.params)
 
+    # ------------------------------------------------------------------ side stream
+    def side(self, fn):
+        """Run `fn` (kernel launches) on the side stream, ordered after everything issued so far on the current one."""
+        if self._side is None:
+            fn()
+            return
+        self._side_fork.record(torch.cuda.current_stream())
+        self._side.wait_event(self._side_fork)
+        with torch.cuda.stream(self._side):
+            fn()
+        self._side_dirty = True
+
+    def join_side(self):
+        """Make the current stream wait for everything issued on the side stream."""
+        if self._side is not None and self._side_dirty:
+            self._side_join.record(self._side)
+            torch.cuda.current_stream().wait_event(self._side_join)
+            self._side_dirty = False
+
     # ------------------------------------------------------------------ data
     def load_batch(self, images_u8: torch.Tensor, labels: torch.Tensor, weights: Optional[torch.Tensor] = None):
         if self.is_cuda:
@@ -262,6 +289,7 @@ class Net:
             for op in self.ops:
                 with span(op.name):
                     op.forward(train, self.t if t is None else t)
+            self.join_side()
             return None
         t = self.t if t is None else t
         images, labels, weights = self._cpu_batch
@@ -291,7 +319,9 @@ class Net:
                 with span(self.ops[i].name):
                     self.ops[i].backward()
                 if hook is not None:
+                    self.join_side()      # the hook hands this operator's gradients to the exchange
                     hook(i)
+            self.join_side()
             return
         self._cpu_loss.backward()
         self._cpu_loss = None

@@ -642,6 +642,11 @@ class Conv2dOp(Op):
                               ko, self.out_cp, r, r, s, p, p, self.P, self.Q, self.has_relu)
             self._act_forward()
             return
+        if train and self.wt16 is not None:
+            # the data-grad reads the filters transposed and flipped; re-packing them depends on the weights alone,
+            # so it runs beside the forward pass
+            w16 = self.view(self.seg_w, "params16")
+            self.net.side(lambda: K.pack_dgrad_filters(w16, self.wt16, ko, self.out_cp, r * r, self.cp))
         K.conv_fprop_tc(self.prev.out, self.net.batch, h, w, self.cp, self.view(self.seg_w, "params16"), ko, r, r, s,
                         p, p, self.P, self.Q, self.out, self.out_cp,
                         bias=self.view(self.seg_b) if self.seg_b else None, relu=self.has_relu, n_valid=ko,
@@ -654,7 +659,8 @@ class Conv2dOp(Op):
         rows = n * self.P * self.Q
         self._act_backward()
         if self.seg_b:
-            K.colsum(self.dout, rows, self.out_cp, ko, self.view(self.seg_b, "grads"))
+            gb = self.view(self.seg_b, "grads")
+            self.net.side(lambda: K.colsum(self.dout, rows, self.out_cp, ko, gb))     # beside weight- and data-grad
         gw = self.view(self.seg_w, "grads")
         if self.direct:
             K.conv_direct_wgrad(self.prev.out, self.dout, gw, n, h, w, self.cp, ko, self.out_cp, r, r, s, p, p, self.P,
@@ -671,7 +677,6 @@ class Conv2dOp(Op):
                 K.conv_direct_dgrad(self.dout, w16, self.prev.dout, mask, n, h, w, self.cp, ko, self.out_cp, r, r, s,
                                     p, p, self.P, self.Q)
             elif s == 1:
-                K.pack_dgrad_filters(w16, self.wt16, ko, self.out_cp, r * r, self.cp)
                 K.conv_fprop_tc(self.dout, n, self.P, self.Q, self.out_cp, self.wt16, self.cp, r, r, 1, r - 1 - p,
                                 r - 1 - p, h, w, self.prev.dout, self.cp, mask_src=mask, n_valid=self.in_c,
                                 n_store=self.cp)
@@ -847,7 +852,8 @@ class AffineOp(Op):
         n, ko = self.net.batch, self.cfg.out_channels
         self._act_backward()
         if self.seg_b:
-            K.colsum(self.dout, n, self.out_cp, ko, self.view(self.seg_b, "grads"))
+            gb = self.view(self.seg_b, "grads")
+            self.net.side(lambda: K.colsum(self.dout, n, self.out_cp, ko, gb))
         # dW[out][in] += dY^T X : both operands are read "MN-major" straight from their row-major buffers
         # one pass over the batch: overwrite when this is the only micro-batch of the iteration, else accumulate
         epi = K.EPI_F32_ATOMIC if self.net.accumulate else K.EPI_F32_STORE
