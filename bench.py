@@ -266,9 +266,10 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="repeat the timed region of K steps until this much device time has been measured")
     ap.add_argument("--max-repeats", type=int, default=400)
-    ap.add_argument("--baseline-variants", default="eager,graph",
+    ap.add_argument("--baseline-variants", default="auto",
                     help="stock-PyTorch variants timed in the same process (eager, graph, bf16_graph, compiled); the "
-                         "fastest is reported. Empty: no same-lease baseline.")
+                         "fastest is reported. auto = graph,compiled,eager on one GPU (compiling takes about two "
+                         "minutes) and graph,eager on several; none = no same-lease baseline.")
     args = ap.parse_args()
     args.warmup = max(3, args.warmup)
 
@@ -308,7 +309,9 @@ def main():
     host_lbls = [torch.randint(0, classes, (batch,), dtype=torch.int32, generator=gen).pin_memory()
                  for _ in range(pool)]
     sampler_ids = ",".join(str(i) for i in range(world)) if world > 1 else local_rank
-    variants = [v for v in args.baseline_variants.split(",") if v]
+    if args.baseline_variants == "auto":
+        args.baseline_variants = "graph,compiled,eager" if world == 1 else "graph,eager"
+    variants = [v for v in args.baseline_variants.split(",") if v and v != "none"]
 
     def torch_arms():
         """Every requested stock-PyTorch variant, timed here and now; a variant that cannot be built is reported."""

@@ -85,6 +85,93 @@ __global__ void softmax_ce_kernel(const bf16* __restrict__ logits, int B, int K,
   }
 }
 
+// Categorical heads of the second layer generation other than softmax + cross-entropy. Their backward kernels live
+// outside the reference's tree; what is restated here follows from the call sites (src/layer_new.rs:2249-2258
+// `batch_map_softmax_ind_backward(probs, K, B, labels, weights, delta)`, :2703-2738 `batch_blockreduce_sum` of the
+// raw inputs followed by `batch_map_antilogistic_forward(in, K, B, sums, out)` and
+// `batch_map_antilogistic_kl_backward(out, K, B, labels, weights, delta)`, and src/operator/loss.rs:322-333
+// `batch_map_marginalized_softmax_ind_backward(probs, K, B, weights, category_weights, delta)`):
+//   objective 1  softmax indicator: p = softmax(x); the objective is the probability mass on the target,
+//                R = sum_k t_k p_k with t the one-hot label or, marginalised, a weight per category;
+//                loss = 1 - R, delta_j = w p_j (R - t_j)   (for a one-hot target: w p_y (p_j - [j = y]))
+//   objective 2  "antilogistic" + KL: the inputs are non-negative scores normalised by their plain sum,
+//                v_k = x_k / S, S = sum_k x_k (the forward kernel receives exactly that sum);
+//                loss = -log v_y, delta_j = w (1 / S - [j = y] / x_y)
+//   objective 3  "antilogistic" indicator: loss = 1 - v_y, delta_j = w (x_y - [j = y] S) / S^2
+// One warp per sample; masks as in the softmax head; arg-max / accuracy on the normalised values.
+__global__ void categorical_obj_kernel(const bf16* __restrict__ x, int B, int K, int ld, const int* __restrict__ labels,
+                                       const float* __restrict__ weights, float w_scalar, bf16* __restrict__ delta,
+                                       float* __restrict__ probs, float* __restrict__ loss_sum,
+                                       int* __restrict__ correct, int* __restrict__ argmax_out,
+                                       const uint8_t* __restrict__ mask, const float* __restrict__ target_w,
+                                       int objective) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  const bf16* row = x + (long long)b * ld;
+  const uint8_t* mrow = mask ? mask + (long long)b * K : nullptr;
+  const bool soft = objective == 1;
+  float mx = -INFINITY;
+  int am = 0;
+  for (int k = lane; k < K; k += 32) {
+    if (mrow && !mrow[k]) continue;
+    const float v = bf2f(row[k]);
+    if (v > mx) { mx = v; am = k; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, mx, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, am, o);
+    if (ov > mx || (ov == mx && oi < am)) { mx = ov; am = oi; }
+  }
+  // normaliser: sum of exponentials (softmax) or plain sum of the clipped scores
+  float s = 0.f;
+  for (int k = lane; k < K; k += 32)
+    if (!mrow || mrow[k]) s += soft ? __expf(bf2f(row[k]) - mx) : fmaxf(bf2f(row[k]), 0.f);
+  s = warp_sum(s);
+  const float eps = 1e-6f;
+  const float inv = soft ? (s > 0.f ? 1.f / s : 0.f) : 1.f / fmaxf(s, eps);
+  const int y = labels ? labels[b] : -1;
+  const bool live = target_w != nullptr || (y >= 0 && y < K && (!mrow || mrow[y]));
+  const float w = weights ? weights[b] : w_scalar;
+  // mass on the target
+  float r = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    if (mrow && !mrow[k]) continue;
+    const float t = target_w ? target_w[k] : (k == y ? 1.f : 0.f);
+    if (t != 0.f) r += t * (soft ? __expf(bf2f(row[k]) - mx) : fmaxf(bf2f(row[k]), 0.f)) * inv;
+  }
+  r = warp_sum(r);
+  const float xy = (!soft && live && !target_w) ? fmaxf(bf2f(row[y]), eps) : 1.f;
+  if (delta || probs) {
+    for (int k = lane; k < ld; k += 32) {
+      float vk = 0.f;
+      if (k < K && (!mrow || mrow[k])) vk = (soft ? __expf(bf2f(row[k]) - mx) : fmaxf(bf2f(row[k]), 0.f)) * inv;
+      if (probs && k < K) probs[(long long)b * K + k] = vk;
+      if (delta) {
+        float d = 0.f;
+        if (k < K && live && (!mrow || mrow[k])) {
+          const float t = target_w ? target_w[k] : (k == y ? 1.f : 0.f);
+          // scores below zero are clipped (no gradient); a target without any mass gives the KL form no gradient
+          const bool clipped = !soft && bf2f(row[k]) < 0.f;
+          if (objective == 1) d = w * vk * (r - t);
+          else if (clipped) d = 0.f;
+          else if (objective == 2) d = r > eps ? w * (inv - t / xy) : 0.f;
+          else d = w * (r - t) * inv;
+        }
+        delta[(long long)b * ld + k] = f2bf(d);
+      }
+    }
+  }
+  if (lane == 0) {
+    const float lo = !live ? 0.f : (objective == 2 ? -__logf(fmaxf(r, eps)) : 1.f - r);
+    if (argmax_out) argmax_out[b] = am;
+    if (loss_sum && live) atomicAdd(loss_sum, w * lo);
+    if (correct && am == y) atomicAdd(correct, 1);
+  }
+}
+
 // Element-wise regression / binary heads on [B][K] outputs with float targets [B][K]:
 //   mode 0  logistic:  p = sigmoid(x), loss = -(t log p + (1-t) log(1-p)), delta = w (p - t); "correct" counts
 //           samples whose first output lies on the target's side of 0.5
@@ -140,6 +227,18 @@ int rb_softmax_ce(const void* logits, int B, int K, int ld, int L, const int* la
   softmax_ce_kernel<<<(B * L + wpb - 1) / wpb, wpb * 32, 0, st>>>(
       (const bf16*)logits, B, K, ld, L, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, loss_per,
       argmax_out, cat_weights, (const uint8_t*)mask, soft);
+  return RB_LAUNCH_OK();
+}
+
+int rb_categorical_loss(const void* x, int B, int K, int ld, const int* labels, const float* weights, float w_scalar,
+                        void* delta, float* probs, float* loss_sum, int* correct, int* argmax_out, const void* mask,
+                        const float* target_w, int objective, cudaStream_t st) {
+  if (objective < 1 || objective > 3 || K > ld || (!labels && !target_w)) return -10;
+  if (objective != 1 && target_w) return -10;      // the marginalised form exists for the softmax indicator only
+  const int wpb = 4;
+  categorical_obj_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>(
+      (const bf16*)x, B, K, ld, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, argmax_out,
+      (const uint8_t*)mask, target_w, objective);
   return RB_LAUNCH_OK();
 }
 

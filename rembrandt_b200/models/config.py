@@ -270,6 +270,15 @@ class MarginalizedSoftmaxIndLossCfg:
 
 
 @dataclass
+class CategoricalObjLossCfg:
+    """Categorical heads of the second layer generation other than softmax + cross-entropy (src/layer_new.rs:2136
+    SoftmaxIndicatorLossLayer, :2637 AntilogisticKLLossLayer, :2859 AntilogisticIndicatorLossLayer):
+    kind = "softmax_ind" | "antilogistic_kl" | "antilogistic_ind"."""
+    num_categories: int
+    kind: str = "softmax_ind"
+
+
+@dataclass
 class SplitCfg:
     """Fan-out marker for the graph container: the activation is shared, branch deltas are summed."""
     num_out_arms: int = 2
@@ -362,6 +371,10 @@ class SequentialOperatorConfig:
         return self
 
     def marginalized_softmax_ind_loss(self, cfg: MarginalizedSoftmaxIndLossCfg, name="loss"):
+        self.loss_op = NamedOp(name, cfg)
+        return self
+
+    def categorical_obj_loss(self, cfg: "CategoricalObjLossCfg", name="loss"):
         self.loss_op = NamedOp(name, cfg)
         return self
 

@@ -42,6 +42,7 @@ def _op_table():
         C.MarginalizedSoftmaxIndLossCfg: O.MarginalizedSoftmaxIndLossOp,
         C.MultiSoftmaxKLLossCfg: O.MultiSoftmaxKLLossOp,
         C.PointwiseLossCfg: O.PointwiseLossOp,
+        C.CategoricalObjLossCfg: O.CategoricalObjLossOp,
         C.BNormConv2dCfg: R.BNormConv2dOp,
         C.StackResConv2dCfg: R.StackResConv2dOp,
         C.ProjStackResConv2dCfg: R.ProjStackResConv2dOp,

@@ -1261,6 +1261,65 @@ class PointwiseLossOp(SoftmaxKLLossOp):
         return (w * per).sum(), correct, (x[:, 0] > 0).long()
 
 
+class CategoricalObjLossOp(SoftmaxKLLossOp):
+    """Softmax indicator, antilogistic + KL and antilogistic indicator heads (src/layer_new.rs:2136, :2637, :2859).
+
+    The reference's kernels for these heads are not in its tree; the maths is inferred from the call sites and written
+    out in `csrc/softmax_ce.cu` (`categorical_obj_kernel`): the indicator heads maximise the (normalised) mass on the
+    target, loss = 1 - mass; the antilogistic heads normalise non-negative scores by their plain sum instead of a
+    softmax. `set_target_weights` gives the softmax indicator a weight per category in place of the one-hot label
+    (the marginalised form of src/operator/loss.rs:264-407)."""
+
+    KINDS = {"softmax_ind": K.OBJ_SOFTMAX_IND, "antilogistic_kl": K.OBJ_ANTILOGISTIC_KL,
+             "antilogistic_ind": K.OBJ_ANTILOGISTIC_IND}
+
+    def setup(self, net, prev):
+        super().setup(net, prev)
+        if self.cfg.kind not in self.KINDS:
+            raise ValueError(f"unknown categorical objective {self.cfg.kind!r}")
+        self.objective = self.KINDS[self.cfg.kind]
+        self.target_w = None
+
+    def set_target_weights(self, tw):
+        if self.objective != K.OBJ_SOFTMAX_IND:
+            raise ValueError("category weights exist for the softmax indicator head only")
+        self.target_w = None if tw is None else torch.as_tensor(tw, dtype=torch.float32, device=self.net.device)
+
+    def forward(self, train, t):
+        logits, dbuf = self._logits()
+        delta = dbuf if (train and self.prev.dout is not None) else None
+        K.categorical_loss(logits, self.net.batch, self.k, self.ld, self.labels, self.weights, self.net.sample_weight,
+                           delta, self.objective, probs=self.probs, loss_sum=self.loss_sum, correct=self.correct,
+                           argmax_out=self.argmax, mask=self.mask, target_w=self.target_w)
+        if delta is not None:
+            self._scatter_delta()
+
+    def ref_loss(self, logits, labels, weights=None):
+        n = logits.shape[0]
+        x = logits.flatten(1).reshape(n, self.k)
+        labels = labels.long().reshape(-1)
+        live = (labels >= 0) & (labels < self.k)
+        keep = None if self._cpu_mask is None else self._cpu_mask.reshape(n, self.k)
+        if self.objective == K.OBJ_SOFTMAX_IND:
+            v = torch.softmax(x if keep is None else x.masked_fill(~keep, float("-inf")), dim=1)
+        else:
+            pos = x.clamp_min(0.0) if keep is None else x.clamp_min(0.0) * keep
+            v = pos / pos.sum(1, keepdim=True).clamp_min(1e-6)
+        if self.target_w is not None:
+            mass = (v * self.target_w.to(v.device).reshape(1, -1)).sum(1)
+            live = torch.ones_like(live)
+        else:
+            mass = v.gather(1, labels.clamp(0, self.k - 1).reshape(-1, 1)).squeeze(1)
+        per = -torch.log(mass.clamp_min(1e-6)) if self.objective == K.OBJ_ANTILOGISTIC_KL else 1.0 - mass
+        per = torch.where(live, per, torch.zeros_like(per))
+        if getattr(self, "keep_probs", False):
+            self.probs = v.detach()
+        w = weights.reshape(-1) if weights is not None else torch.full_like(per, self.net.sample_weight)
+        masked = x if keep is None else x.masked_fill(~keep, float("-inf"))
+        am = masked.argmax(1)
+        return (w * per).sum(), int((am == labels).sum()), am
+
+
 class MarginalizedSoftmaxIndLossOp(SoftmaxKLLossOp):
     """Softmax head whose gradient is weighted per category (src/operator/loss.rs:264-407)."""
 

@@ -263,6 +263,19 @@ def softmax_ce(logits, B, K, ld, labels, weights, w_scalar, delta, probs=None, l
           "rb_softmax_ce")
 
 
+OBJ_SOFTMAX_IND, OBJ_ANTILOGISTIC_KL, OBJ_ANTILOGISTIC_IND = 1, 2, 3
+
+
+def categorical_loss(x, B, K, ld, labels, weights, w_scalar, delta, objective, probs=None, loss_sum=None, correct=None,
+                     argmax_out=None, mask=None, target_w=None):
+    """Categorical heads other than softmax + cross-entropy (csrc/softmax_ce.cu, `categorical_obj_kernel`):
+    softmax indicator (one-hot label, or `target_w` [K] = a weight per category), antilogistic + KL, antilogistic
+    indicator."""
+    check(_native.cuda().rb_categorical_loss(ptr(x), B, K, ld, ptr(labels), ptr(weights), float(w_scalar), ptr(delta),
+                                             ptr(probs), ptr(loss_sum), ptr(correct), ptr(argmax_out), ptr(mask),
+                                             ptr(target_w), int(objective), stream_handle()), "rb_categorical_loss")
+
+
 def pointwise_loss(x, B, K, ld, target, weights, w_scalar, delta, loss_sum=None, correct=None, mode=0):
     """mode 0: logistic (binary cross-entropy on logits), mode 1: L2; targets float32 [B, K]."""
     check(_native.cuda().rb_pointwise_loss(ptr(x), B, K, ld, ptr(target), ptr(weights), float(w_scalar), ptr(delta),

@@ -255,6 +255,54 @@ def softmax_ce(logits, B, Kc, ld, labels, weights, w_scalar, delta, probs=None, 
         argmax_out.reshape(-1)[:B].copy_(am.int())
 
 
+def categorical_loss(x, B, Kc, ld, labels, weights, w_scalar, delta, objective, probs=None, loss_sum=None, correct=None,
+                     argmax_out=None, mask=None, target_w=None):
+    """Softmax indicator (1), antilogistic + KL (2), antilogistic indicator (3): see csrc/softmax_ce.cu."""
+    z = _rows(x, B, ld)[:, :Kc].float()
+    keep = torch.ones(B, Kc, dtype=torch.bool) if mask is None else mask.reshape(B, Kc) != 0
+    lab = labels.reshape(-1)[:B].long() if labels is not None else torch.full((B,), -1)
+    w = weights.reshape(-1)[:B].float() if weights is not None else torch.full((B,), float(w_scalar))
+    if objective == 1:
+        v = torch.softmax(z.masked_fill(~keep, float("-inf")), 1)
+        inv = None
+    else:
+        pos = z.clamp_min(0.0) * keep
+        s = pos.sum(1, keepdim=True).clamp_min(1e-6)
+        v, inv = pos / s, 1.0 / s
+    if target_w is not None:
+        t = target_w.reshape(1, Kc).float().expand(B, Kc)
+        live = torch.ones(B, dtype=torch.bool)
+    else:
+        live = (lab >= 0) & (lab < Kc)
+        t = torch.zeros(B, Kc)
+        t[live, lab[live]] = 1.0
+        live = live & keep.gather(1, lab.clamp(0, Kc - 1).view(-1, 1)).squeeze(1)
+    r = (t * v * keep).sum(1, keepdim=True)
+    if objective == 1:
+        d = v * (r - t)
+    elif objective == 2:
+        xy = z.gather(1, lab.clamp(0, Kc - 1).view(-1, 1)).clamp_min(1e-6)
+        d = (inv - t / xy) * (r > 1e-6) * (z >= 0)
+    else:
+        d = (r - t) * inv * (z >= 0)
+    d = d * keep * live.view(-1, 1) * w.view(-1, 1)
+    per = -torch.log(r.squeeze(1).clamp_min(1e-6)) if objective == 2 else 1.0 - r.squeeze(1)
+    per = torch.where(live, per, torch.zeros(B))
+    am = z.masked_fill(~keep, float("-inf")).argmax(1)
+    if delta is not None:
+        dm = _rows(delta, B, ld)
+        dm[:, :Kc] = d.to(delta.dtype)
+        dm[:, Kc:] = 0
+    if probs is not None:
+        probs.reshape(-1)[: B * Kc].view(B, Kc).copy_(v)
+    if loss_sum is not None:
+        loss_sum += (w * per).sum()
+    if correct is not None:
+        correct += int((am == lab).sum())
+    if argmax_out is not None:
+        argmax_out.reshape(-1)[:B].copy_(am.int())
+
+
 def pointwise_loss(x, B, Kc, ld, target, weights, w_scalar, delta, loss_sum=None, correct=None, mode=0):
     z = _rows(x, B, ld)[:, :Kc].float()
     t = target.reshape(B, Kc).float()
@@ -435,7 +483,7 @@ EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fw
                                     conv_direct_dgrad, pack_dgrad_filters, zero_s2d_structural, gemm_tc, bias_act,
                                     colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
                                     softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd,
-                                    pointwise_loss, lrn_fwd, lrn_bwd, dropout, var_input_u8, sgd_fused_grid,
+                                    pointwise_loss, categorical_loss, lrn_fwd, lrn_bwd, dropout, var_input_u8, sgd_fused_grid,
                                     axpy_shadow)}
 
 

@@ -8,10 +8,8 @@ from rembrandt_b200.models import descriptor, zoo
 from rembrandt_b200.models import config as C
 from rembrandt_b200.models.net import Net
 
-# directory holding the reference's shipped descriptor files (imagenet_alexnet.model, ...); tests that need them
-# are skipped when it is absent
-EX = os.environ.get("REMBRANDT_EXAMPLES", os.path.join(os.sep, "root", "reference", "examples"))
-have_ref = os.path.isdir(EX)
+# the descriptor files shipped with this repository
+EX = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "examples")
 
 LENET_MODEL = """
 [[layer]]
@@ -77,29 +75,68 @@ def test_inline_descriptor_with_irregularities():
     assert net.params_len == (16 * 25 + 16) + (14 * 14 * 16 * 100 + 100) + (100 * 10 + 10)
 
 
-@pytest.mark.skipif(not have_ref, reason="reference examples not mounted")
-@pytest.mark.parametrize("name,params", [("mnist_lenet", (16 * 25 + 16) + (14 * 14 * 16 * 100 + 100) + 1010),
-                                         ("imagenet_nin", 7595176), ("imagenet_alexnet", None)])
+@pytest.mark.parametrize("name,params", [("mnist_lenet", 431080), ("imagenet_nin", 7595176),
+                                         ("imagenet_alexnet", 62378344)])
 def test_shipped_models_parse(name, params):
     d = descriptor.load_model(f"{EX}/{name}.model", use_crop=False)
     net = Net(d.config, 1, device="cpu")
-    if params is not None:
-        assert net.params_len == params
+    assert net.params_len == params
     if name == "imagenet_alexnet":
-        # ungrouped towers: 96/256/384/384/256 convs, two LRN layers, ReLU on pool layers as written
         convs = [o.cfg.out_channels for o in d.config.hidden_ops if isinstance(o.cfg, C.Conv2dCfg)]
         assert convs == [96, 256, 384, 384, 256]
         assert sum(isinstance(o.cfg, C.LrnCfg) for o in d.config.hidden_ops) == 2
-        pools = [o.cfg for o in d.config.hidden_ops if isinstance(o.cfg, C.Pool2dCfg)]
-        assert [p.act for p in pools] == [C.Act.RECT, C.Act.IDENTITY, C.Act.RECT]
-        assert net.params_len == 62378344
-        assert d.opt.minibatch_size == 64
+        assert [op.out_hwc[0] for op in net.ops if type(op).__name__ == "Pool2dOp"] == [27, 13, 6]
+        assert d.opt.minibatch_size == 128 and d.opt.max_iters == 450000
+        # with the crop the input operator stages 256 x 256 images and cuts 227 x 227 windows
+        dc = descriptor.load_model(f"{EX}/{name}.model").config.input_op.cfg
+        assert dc.in_dims[:2] == (256, 256) and [p.kind for p in dc.preprocs] == ["flip_x", "crop"]
     if name == "imagenet_nin":
         sizes = [op.out_hwc[0] for op in net.ops if type(op).__name__ == "Pool2dOp"]
         assert sizes == [27, 13, 6, 1]                                # ceil-mode pooling, global average
 
 
-@pytest.mark.skipif(not have_ref, reason="reference examples not mounted")
+TWO_TOWER_MODEL = """
+[[layer]]
+name = "data"
+raw_width = 35
+raw_height = 35
+channels = 3
+[[layer]]
+names = ["conv1a", "conv1b"]
+conv_size = 11
+conv_stride = 4
+out_channels = 48
+act_func = "rect"
+[[layer]]
+names = ["pool1a", "pool1b"]
+inputs = ["conv1a", "conv1b"]
+pool_size = 3
+pool_stride = 2
+act_func = "rect"
+[[layer]]
+names = ["norm1a", "norm1b"]
+cross_size = 5
+[[layer]]
+name = "fc"
+inputs = ["norm1a", "norm1b"]
+out_channels = 10
+[[layer]]
+name = "loss"
+num_categories = 10
+"""
+
+
+def test_two_tower_notation_becomes_the_ungrouped_network():
+    """Layers written as towers (`names = [a, b]`, as Krizhevsky's two-GPU AlexNet is usually written down) merge into
+    one layer with the summed channel count; types are inferred from the keys; an activation on a pool layer counts."""
+    d = descriptor.parse_model(TWO_TOWER_MODEL)
+    ops = d.config.hidden_ops
+    assert [type(o.cfg).__name__ for o in ops] == ["Conv2dCfg", "Pool2dCfg", "LrnCfg", "AffineCfg"]
+    assert ops[0].cfg.out_channels == 96 and ops[1].cfg.act == C.Act.RECT and ops[0].name == "conv1"
+    net = Net(d.config, 1, device="cpu")
+    assert net.params_len == (3 * 121 * 96 + 96) + (3 * 3 * 96 * 10 + 10)
+
+
 def test_shipped_data_files_parse():
     m = descriptor.load_data(f"{EX}/mnist.data")
     assert m["train"].source == "mnist" and m["train"].normalize and m["valid"].labels_path.endswith("t10k-labels-idx1-ubyte")

@@ -252,6 +252,31 @@ def test_pointwise_heads_on_the_device_path(monkeypatch, kind):
     _grads_agree(dev, ref)
 
 
+@pytest.mark.parametrize("kind", ["softmax_ind", "antilogistic_kl", "antilogistic_ind"])
+def test_categorical_objective_heads_on_the_device_path(monkeypatch, kind):
+    from rembrandt_b200.models.config import AffineCfg, CategoricalObjLossCfg
+
+    def make():
+        cfg = SequentialOperatorConfig().data3d(Data3dCfg((6, 6, 2), normalize=True))
+        cfg.conv2d(Conv2dCfg(3, 1, 1, 8, Act.RECT, K_), "conv1")
+        # the antilogistic heads normalise non-negative scores: feed them a logistic layer's outputs
+        cfg.affine(AffineCfg(7, Act.LOGISTIC if kind != "softmax_ind" else Act.IDENTITY, K_), "fc")
+        return cfg.categorical_obj_loss(CategoricalObjLossCfg(7, kind))
+
+    dev, ref = _pair(monkeypatch, make)
+    torch.manual_seed(4)
+    x = torch.randint(0, 256, (4, 2, 6, 6), dtype=torch.uint8)
+    y = torch.tensor([1, 6, 0, 3])
+    for n in (dev, ref):
+        n.load_batch(x, y.int() if n is dev else y)
+        n.forward(True)
+        n.backward()
+    dl, dc = dev.read_stats()
+    rl, rc = ref.read_stats()
+    assert abs(dl - rl) < 2e-2 * max(1.0, abs(rl)), (dl, rl)
+    _grads_agree(dev, ref)
+
+
 # ---- random small networks: geometry (odd sizes, strides, paddings, ceil-mode pooling) and channel padding --------
 from hypothesis import HealthCheck, given, settings, strategies as st  # noqa: E402
 

@@ -471,6 +471,48 @@ def test_pointwise_loss(mode):
         assert correct.item() == int(((x[:, 0] > 0) == (t[:, 0] > 0.5)).sum())
 
 
+@pytest.mark.parametrize("objective", [1, 2, 3])
+@pytest.mark.parametrize("marginal", [False, True])
+def test_categorical_objective_heads(objective, marginal):
+    """Softmax indicator (also with a weight per category), antilogistic + KL, antilogistic indicator against
+    autograd of the formulas."""
+    if marginal and objective != 1:
+        pytest.skip("category weights exist for the softmax indicator only")
+    torch.manual_seed(15)
+    B, Kc = 19, 11
+    ld = K.pad_channels(Kc)
+    x = bf(torch.randn(B, Kc, device=DEV) * 2) if objective == 1 else bf(torch.rand(B, Kc, device=DEV) * 3 + 0.05)
+    xi = torch.zeros(B, ld, device=DEV, dtype=torch.bfloat16)
+    xi[:, :Kc] = x.bfloat16()
+    y = torch.randint(0, Kc, (B,), device=DEV, dtype=torch.int32)
+    mask = (torch.rand(B, Kc, device=DEV) > 0.25)
+    mask[torch.arange(B), y.long()] = True
+    tw = torch.rand(Kc, device=DEV) if marginal else None
+    w = 0.2
+    delta = torch.full((B, ld), float("nan"), device=DEV, dtype=torch.bfloat16)
+    probs = torch.full((B, Kc), float("nan"), device=DEV)
+    loss = torch.zeros(1, device=DEV)
+    correct = torch.zeros(1, device=DEV, dtype=torch.int32)
+    am = torch.zeros(B, device=DEV, dtype=torch.int32)
+    K.categorical_loss(xi, B, Kc, ld, y, None, w, delta, objective, probs=probs, loss_sum=loss, correct=correct,
+                       argmax_out=am, mask=mask.to(torch.uint8), target_w=tw)
+    xr = x.clone().requires_grad_()
+    if objective == 1:
+        v = torch.softmax(xr.masked_fill(~mask, float("-inf")), 1)
+    else:
+        pos = xr.clamp_min(0) * mask
+        v = pos / pos.sum(1, keepdim=True)
+    mass = (v * tw).sum(1) if marginal else v[torch.arange(B), y.long()]
+    ref = ((-torch.log(mass) if objective == 2 else 1 - mass) * w).sum()
+    ref_delta = torch.autograd.grad(ref, xr)[0]
+    assert abs(loss.item() - ref.item()) < 2e-3 * max(1.0, abs(ref.item()))
+    close(delta[:, :Kc], ref_delta, atol=3e-3, rtol=2e-2)
+    close(probs, v.detach(), atol=1e-3, rtol=1e-2)
+    assert (delta[:, Kc:].float() == 0).all()
+    first = x.masked_fill(~mask, float("-inf")).argmax(1)
+    assert torch.equal(am.long(), first) and correct.item() == int((first == y.long()).sum())
+
+
 @pytest.mark.parametrize("mode", [0, 1, 2, 3, 4, 5])
 def test_sgd_fused_rules(mode):
     from rembrandt_b200.optim.sgd import reference_step

@@ -234,6 +234,42 @@ def test_pointwise_heads_reference_path(kind):
     assert float(net.grads.abs().sum()) > 0
 
 
+@pytest.mark.parametrize("kind", ["softmax_ind", "antilogistic_kl", "antilogistic_ind"])
+def test_categorical_objective_heads_reference_path(kind):
+    """Softmax indicator and the two antilogistic heads against the formulas written out by hand."""
+    from rembrandt_b200.models import config as C
+    from rembrandt_b200.models.net import Net
+    cfg = C.SequentialOperatorConfig().data3d(C.Data3dCfg((4, 4, 2), normalize=True))
+    cfg.affine(C.AffineCfg(6)).categorical_obj_loss(C.CategoricalObjLossCfg(6, kind))
+    net = Net(cfg, 5, device="cpu")
+    if kind != "softmax_ind":
+        with torch.no_grad():
+            net.params.add_(0.3)      # mostly positive scores, as the antilogistic heads expect
+    x = torch.randint(0, 256, (5, 2, 4, 4), dtype=torch.uint8)
+    y = torch.tensor([0, 3, 5, 1, 2])
+    net.load_batch(x, y)
+    net.forward(True)
+    net.backward()
+    loss, _ = net.read_stats()
+    z = net._cpu_logits.flatten(1)
+    if kind == "softmax_ind":
+        v = torch.softmax(z, 1)
+    else:
+        v = z.clamp_min(0) / z.clamp_min(0).sum(1, keepdim=True).clamp_min(1e-6)
+    mass = v[torch.arange(5), y]
+    want = (-torch.log(mass.clamp_min(1e-6)) if kind == "antilogistic_kl" else 1 - mass).sum() / 5
+    assert abs(loss - float(want)) < 1e-5 * max(1.0, abs(float(want)))
+    assert float(net.grads.abs().sum()) > 0
+    if kind == "softmax_ind":
+        # a weight per category in place of the label: the marginalised form
+        net.loss_op.set_target_weights([0.5, 0.0, 0.25, 0.0, 0.0, 0.25])
+        net.load_batch(x, y)
+        net.forward(True)
+        loss2, _ = net.read_stats()
+        tw = torch.tensor([0.5, 0.0, 0.25, 0.0, 0.0, 0.25])
+        assert abs(loss2 - float((1 - (v * tw).sum(1)).sum() / 5)) < 1e-5
+
+
 def test_softmax_head_sampling_respects_mask_and_temperature():
     from rembrandt_b200.models import config as C
     from rembrandt_b200.models.net import Net
