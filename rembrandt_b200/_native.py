@@ -59,6 +59,7 @@ _CUDA_SIGS = {
     "rb_count_above": [vp, i64, i32, f32, vp, vp],
     # softmax_ce.cu
     "rb_pointwise_loss": [vp, i32, i32, i32, vp, vp, f32, vp, vp, vp, i32, vp],
+    "rb_sample_categories": [vp, i32, i32, i32, vp, f32, u64, u32, vp, vp],
     "rb_categorical_loss": [vp, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, i32, vp],
     "rb_softmax_ce": [vp, i32, i32, i32, i32, vp, vp, f32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp],
     # sgd_fused.cu

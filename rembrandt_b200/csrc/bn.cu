@@ -9,7 +9,10 @@
 
 namespace rb {
 
-// sums[c] += sum x, sums[C+c] += sum x^2 ; optionally of dy and dy*xhat for the backward pass
+// Forward: sums[c] += sum (x - k_c), sums[C+c] += sum (x - k_c)^2 with the shift k_c = x[0][c] (the channel's value in
+// the first row). Shifted sums keep the variance E[(x-k)^2] - E[x-k]^2 free of the cancellation that plain
+// E[x^2] - E[x]^2 suffers when a channel's mean is large against its spread (the shift lies inside the data's range,
+// so both terms are of the order of the variance). Backward: sums of dy and dy * xhat.
 __global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
                                  const float* __restrict__ mean, const float* __restrict__ istd, long long rows, int C,
                                  float* __restrict__ sums, int backward) {
@@ -25,13 +28,19 @@ __global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restr
     if (backward) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) { mu[j] = mean[c0 + j]; is[j] = istd[c0 + j]; }
+    } else {
+      load8(x + c0, mu);   // the shift: row 0 of these channels
     }
     for (long long r = (long long)blockIdx.y * 8 + ty; r < rows; r += (long long)gridDim.y * 8) {
       float v[8];
       load8(x + r * C + c0, v);
       if (!backward) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) { a0[j] += v[j]; a1[j] += v[j] * v[j]; }
+        for (int j = 0; j < 8; ++j) {
+          const float d = v[j] - mu[j];
+          a0[j] += d;
+          a1[j] += d * d;
+        }
       } else {
         float g[8];
         load8(dy + r * C + c0, g);
@@ -64,7 +73,8 @@ __global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restr
 // With a step counter (`step_ptr`, the network's device-side count of training steps) the factor is derived on
 // the device, so that a captured CUDA graph keeps averaging correctly: avg_kind 1 = cumulative 1 / (1 + t),
 // avg_kind 2 = exponential `factor` with 1 at t = 0; avg_kind 0 (or no counter) uses `factor` as given.
-__global__ void bn_finalize_kernel(float* __restrict__ sums, long long rows, int C, float eps, float factor,
+__global__ void bn_finalize_kernel(float* __restrict__ sums, const bf16* __restrict__ x_row0, long long rows, int C,
+                                   float eps, float factor,
                                    float* __restrict__ mean, float* __restrict__ istd, float* __restrict__ run_mean,
                                    float* __restrict__ run_var, int avg_kind = 0,
                                    const unsigned int* __restrict__ step_ptr = nullptr) {
@@ -74,9 +84,10 @@ __global__ void bn_finalize_kernel(float* __restrict__ sums, long long rows, int
     const unsigned int t = *step_ptr;
     factor = avg_kind == 1 ? 1.f / (1.f + (float)t) : (t == 0u ? 1.f : factor);
   }
-  const float m = sums[c] / (float)rows;
-  float var = sums[C + c] / (float)rows - m * m;
+  const float ms = sums[c] / (float)rows;          // mean of the shifted values
+  float var = sums[C + c] / (float)rows - ms * ms;
   var = fmaxf(var, 0.f);
+  const float m = bf2f(x_row0[c]) + ms;
   mean[c] = m;
   istd[c] = rsqrtf(var + eps);
   if (run_mean) {
@@ -191,7 +202,7 @@ int rb_bn_fwd_train(const void* x, long long rows, int C, int c_valid, float* su
   if (gy > 256) gy = 256;
   grid.y = (unsigned)gy;
   bn_reduce_kernel<<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0);
-  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, rows, C, eps, factor, mean, istd, run_mean, run_var,
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, (const bf16*)x, rows, C, eps, factor, mean, istd, run_mean, run_var,
                                                       avg_kind, step_ptr);
   bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, mean, istd, gamma, beta,
                                                                 (const bf16*)residual, (bf16*)y, rows, C, c_valid, relu);
@@ -268,7 +279,8 @@ int rb_bn_fwd_train_noalloc(const void* x, long long rows, int C, int c_valid, f
   if (gy > 256) gy = 256;
   grid.y = (unsigned)gy;
   bn_reduce_kernel<<<grid, 256, 0, stream>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0);
-  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, rows, C, eps, factor, mean, istd, run_mean, run_var);
+  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, stream>>>(sums, (const bf16*)x, rows, C, eps, factor, mean, istd, run_mean,
+                                                          run_var);
   bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, stream>>>((const bf16*)x, mean, istd, gamma, beta,
                                                                     (const bf16*)residual, (bf16*)y, rows, C, c_valid,
                                                                     relu);

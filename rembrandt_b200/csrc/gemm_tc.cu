@@ -851,6 +851,8 @@ struct GemmOptions {
   int a_split = 1;           // RB_GEMM_A_SPLIT / RB_GEMM_B_SPLIT: TMA boxes per K-major tile
   int b_split = 1;
   int autotune = 1;          // RB_GEMM_AUTOTUNE: 0 = cost model only, even in tuning mode
+  int deterministic = 0;     // RB_GEMM_DETERMINISTIC: 1 = no launch lets several CTAs add into the same output element
+                             // (no reduction split, no tail cut), so results are bit-identical from run to run
 };
 static GemmOptions g_opt;
 static std::once_flag g_opt_once;
@@ -861,7 +863,7 @@ static int* option_slot(const char* name) {
       {"force_mt", &g_opt.force_mt}, {"force_resident", &g_opt.force_resident}, {"force_halo", &g_opt.force_halo},
       {"force_taps", &g_opt.force_taps}, {"force_tail", &g_opt.force_tail}, {"force_wide", &g_opt.force_wide},
       {"bk32", &g_opt.bk32}, {"bn_cap", &g_opt.bn_cap}, {"a_split", &g_opt.a_split}, {"b_split", &g_opt.b_split},
-      {"autotune", &g_opt.autotune}};
+      {"autotune", &g_opt.autotune}, {"deterministic", &g_opt.deterministic}};
   for (auto& t : table)
     if (strcmp(t.name, name) == 0) return t.slot;
   return nullptr;
@@ -869,7 +871,7 @@ static int* option_slot(const char* name) {
 static void options_from_env() {
   std::call_once(g_opt_once, [] {
     const char* names[] = {"force_mt", "force_resident", "force_halo", "force_taps", "force_tail", "force_wide",
-                           "bk32", "bn_cap", "a_split", "b_split", "autotune"};
+                           "bk32", "bn_cap", "a_split", "b_split", "autotune", "deterministic"};
     for (const char* n : names) {
       char env[64] = "RB_GEMM_";
       size_t k = strlen(env);
@@ -918,6 +920,10 @@ static int tail_parts(long long items, int sms, int num_kb) {
 }
 
 static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_weights) {
+  if (g_opt.deterministic) {   // one CTA per output tile, its k-blocks in order
+    allow_split = false;
+    fixed_split = 1;
+  }
   const int a_bytes = BM * p.bk * 2, b_bytes = p.bn_load * p.bk * 2;
   const double epi_elem = (p.epi == EPI_BF16) ? 1.2 : 1.6;
   Plan best{1, 1, 0, 0, 1e300};
@@ -951,7 +957,7 @@ static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split,
         for (int tail = 0; tail <= 1; ++tail) {
           int parts = 0;
           if (tail) {
-            if (p.epi != EPI_BF16 || s != 1 || !p.ws || g_opt.force_tail == 0) continue;
+            if (p.epi != EPI_BF16 || s != 1 || !p.ws || g_opt.force_tail == 0 || g_opt.deterministic) continue;
             parts = tail_parts(tiles, g_num_sms, p.num_kb);
             if (parts == 0) continue;
             const long long need = (tiles % g_num_sms) * mt * BM * (long long)p.bn * 4;
@@ -1112,7 +1118,7 @@ static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t st
       for (int tail = 0; tail <= 1; ++tail) {
         Plan cand{mt, 1, res, 0, 0.0};
         if (tail) {
-          if (!p.ws || g_opt.force_tail == 0) continue;
+          if (!p.ws || g_opt.force_tail == 0 || g_opt.deterministic) continue;
           const int m_items = (p.M + BM * mt - 1) / (BM * mt);
           cand.tail = tail_parts((long long)m_items * p.n_tiles, g_num_sms, p.num_kb);
           if (cand.tail == 0) continue;
@@ -1156,7 +1162,7 @@ static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_
     auto it = g_plan_cache.find(plan_key(p));
     if (it != g_plan_cache.end()) {
       Plan cached = it->second;
-      if (cached.tail && !p.ws) cached.tail = 0;   // tuned with a workspace, launched without one
+      if (cached.tail && (!p.ws || g_opt.deterministic)) cached.tail = 0;   // tuned with a workspace, launched without
       pl = cached;
     } else if (tunable(p, stream)) {
       Plan best = pl;

@@ -172,6 +172,52 @@ __global__ void categorical_obj_kernel(const bf16* __restrict__ x, int B, int K,
   }
 }
 
+// Draw one category per sample from softmax(x / temperature) restricted to the admissible categories: the
+// Boltzmann sampling of the first-generation softmax head (src/layer.rs:2456, a prefix-sum CDF kernel followed by a
+// uniform draw). One warp per sample: maximum, normaliser, one Philox uniform per (seed, step, sample), then a
+// running inclusive prefix sum over chunks of 32 categories; the first category whose cumulative mass exceeds the
+// draw wins (the last admissible one if rounding leaves the draw above the total).
+__global__ void sample_categories_kernel(const bf16* __restrict__ x, int B, int K, int ld,
+                                         const uint8_t* __restrict__ mask, float inv_temperature, uint64_t seed,
+                                         uint32_t step, int* __restrict__ out) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (b >= B) return;
+  const bf16* row = x + (long long)b * ld;
+  const uint8_t* mrow = mask ? mask + (long long)b * K : nullptr;
+  float mx = -INFINITY;
+  for (int k = lane; k < K; k += 32)
+    if (!mrow || mrow[k]) mx = fmaxf(mx, bf2f(row[k]) * inv_temperature);
+  mx = warp_max(mx);
+  float se = 0.f;
+  for (int k = lane; k < K; k += 32)
+    if (!mrow || mrow[k]) se += __expf(bf2f(row[k]) * inv_temperature - mx);
+  se = warp_sum(se);
+  uint32_t r4[4];
+  Philox::gen(seed, (uint64_t)b, step, r4);
+  const float target = u32_to_unit(r4[0]) * se;
+  float running = 0.f;
+  int pick = -1, last_ok = -1;
+  for (int k0 = 0; k0 < K && pick < 0; k0 += 32) {
+    const int k = k0 + lane;
+    const bool ok = k < K && (!mrow || mrow[k]);
+    const float e = ok ? __expf(bf2f(row[k]) * inv_temperature - mx) : 0.f;
+    float scan = e;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float up = __shfl_up_sync(0xffffffffu, scan, o);
+      if (lane >= o) scan += up;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, ok && running + scan > target);
+    const unsigned oks = __ballot_sync(0xffffffffu, ok);
+    if (oks) last_ok = k0 + 31 - __clz(oks);
+    if (hit) pick = k0 + __ffs(hit) - 1;
+    running += __shfl_sync(0xffffffffu, scan, 31);
+  }
+  if (lane == 0) out[b] = pick >= 0 ? pick : last_ok;
+}
+
 // Element-wise regression / binary heads on [B][K] outputs with float targets [B][K]:
 //   mode 0  logistic:  p = sigmoid(x), loss = -(t log p + (1-t) log(1-p)), delta = w (p - t); "correct" counts
 //           samples whose first output lies on the target's side of 0.5
@@ -239,6 +285,15 @@ int rb_categorical_loss(const void* x, int B, int K, int ld, const int* labels, 
   categorical_obj_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>(
       (const bf16*)x, B, K, ld, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, argmax_out,
       (const uint8_t*)mask, target_w, objective);
+  return RB_LAUNCH_OK();
+}
+
+int rb_sample_categories(const void* x, int B, int K, int ld, const void* mask, float temperature,
+                         unsigned long long seed, unsigned int step, int* out, cudaStream_t st) {
+  if (K > ld || !(temperature > 0.f)) return -10;
+  const int wpb = 4;
+  sample_categories_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>((const bf16*)x, B, K, ld, (const uint8_t*)mask,
+                                                                    1.f / temperature, seed, step, out);
   return RB_LAUNCH_OK();
 }
 

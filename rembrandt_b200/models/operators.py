@@ -834,10 +834,17 @@ class AffineOp(Op):
 
     @staticmethod
     def _bn_cap(n_cols, m_tiles=1):
-        target = max(1, 148 // m_tiles)
-        bn = (n_cols + target - 1) // target
-        bn = (bn + 63) // 64 * 64
-        return max(64, min(256, bn))
+        """Tile width of the forward / data-grad GEMMs. The batch gives one 128-row tile, so every column tile loads
+        the whole activation panel again: wide tiles keep those re-reads (the larger share of the rows the TMA unit
+        has to fetch) down, and the reduction split spreads the work over the SMs instead."""
+        forced = os.environ.get("RB_FC_BN")
+        if forced:
+            return int(forced)
+        if n_cols >= 2048:
+            return 256
+        if n_cols >= 1024:
+            return 128
+        return 64
 
     def forward(self, train, t):
         n, ko = self.net.batch, self.cfg.out_channels
@@ -1137,11 +1144,24 @@ class SoftmaxKLLossOp(Op):
                                      device=self.net.device)
         self.keep_probs = True
 
-    def sample_categories(self, temperature: float = 1.0, generator=None) -> torch.Tensor:
+    def sample_categories(self, temperature: float = 1.0, generator=None, seed: Optional[int] = None) -> torch.Tensor:
         """Draw one category per sample (head 0) from softmax(logits / temperature), restricted to the admissible
-        categories when a mask is loaded: the Boltzmann sampling of the gen-1 softmax head (src/layer.rs, prefix-sum
-        CDF + uniform draw). Call after `forward`; not on the training hot path (plain torch ops)."""
+        categories when a mask is loaded: the Boltzmann sampling of the gen-1 softmax head (src/layer.rs:2456,
+        prefix-sum CDF + uniform draw). Call after `forward`. On a GPU this is one kernel (per-sample warp, prefix
+        sums, Philox draw keyed by `seed` and the number of draws so far); on CPU `torch.multinomial`."""
         n = self.net.batch
+        if self.net.device.type == "cuda":
+            logits = self.flat if self.spatial else self.prev.out.reshape(n, -1)
+            mask = None
+            if self.mask is not None:
+                mask = self.mask.reshape(n, self.heads, self.k)[:, 0].contiguous()
+            if not hasattr(self, "_sampled"):
+                self._sampled = torch.zeros(n, dtype=torch.int32, device=self.net.device)
+                self._draws = 0
+            self._draws += 1
+            K.sample_categories(logits, n, self.k, logits.shape[1], mask, max(float(temperature), 1e-6),
+                                self.net.dropout_seed if seed is None else seed, self._draws, self._sampled)
+            return self._sampled.long()
         if self.net.is_cuda:
             logits = (self.flat if self.spatial else self.prev.out.reshape(n, -1))[:, : self.k].float()
             mask = None if self.mask is None else self.mask.reshape(n, self.heads, self.k)[:, 0].bool()

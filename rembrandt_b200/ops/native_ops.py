@@ -61,7 +61,7 @@ def gemm_workspace() -> torch.Tensor:
 
 def gemm_set_option(name: str, value: int) -> None:
     """Planner switch of the tensor-core kernel by name (force_mt, force_resident, force_halo, force_taps, force_tail,
-    force_wide, bk32, bn_cap, a_split, b_split, autotune); initial values come from RB_GEMM_<NAME> at first use."""
+    force_wide, bk32, bn_cap, a_split, b_split, autotune, deterministic); initial values come from RB_GEMM_<NAME> at first use."""
     if _native.cuda().rb_gemm_set_option(name.encode(), int(value)) != 0:
         raise KeyError(name)
 
@@ -261,6 +261,13 @@ def softmax_ce(logits, B, K, ld, labels, weights, w_scalar, delta, probs=None, l
                                        ptr(delta), ptr(probs), ptr(loss_sum), ptr(correct), ptr(loss_per),
                                        ptr(argmax_out), ptr(cat_weights), ptr(mask), ptr(soft), stream_handle()),
           "rb_softmax_ce")
+
+
+def sample_categories(x, B, K, ld, mask, temperature, seed, step, out):
+    """out[b] (int32) = one draw from softmax(x[b] / temperature) over the categories whose mask byte is non-zero."""
+    check(_native.cuda().rb_sample_categories(ptr(x), B, K, ld, ptr(mask), float(temperature), int(seed) & (2**64 - 1),
+                                              int(step) & 0xFFFFFFFF, ptr(out), stream_handle()),
+          "rb_sample_categories")
 
 
 OBJ_SOFTMAX_IND, OBJ_ANTILOGISTIC_KL, OBJ_ANTILOGISTIC_IND = 1, 2, 3

@@ -462,22 +462,39 @@ class GossipP2PComm(CommWorker, _P2PBase):
 
 
 class GroupGossipP2PComm(GossipP2PComm):
-    """Hierarchical exchange on the gossip kernels: the mean over this rank's group of `group_size` consecutive ranks,
-    then every rank pulls the group mean of one uniformly random rank and keeps 0.5 * (pulled + own group mean)
-    (the second version of the reference's scheme, src/worker/gossip_pull_allreduce_dist_rdma_v2.rs:327-384).
+    """Hierarchical exchange on the gossip kernels: first the mean over this rank's group of `group_size` consecutive
+    ranks, then gossip between groups.
 
-    Both phases use the publish + mix kernels of the flat gossip: in phase one a rank pulls the snapshots of its group
-    peers as a running mean (pull k with weight 1 / (k + 2)); in phase two it publishes the group mean and pulls one
-    more snapshot with weight 1/2. Every rank runs both phases, so the epochs of the flag protocol stay in step even
-    for a rank that is alone in its group (its phase one is a single mix that lands on itself and changes nothing).
+    version 2 (default; src/worker/gossip_pull_allreduce_dist_rdma_v2.rs:327-384): every rank pulls the group mean of
+    one uniformly random rank and keeps 0.5 * (pulled + own group mean).
+    version 1 (src/worker/gossip_pull_allreduce_dist_rdma.rs:327-402): only the group leaders (first rank of each
+    group) gossip -- a leader pulls the group mean of a uniformly random leader and keeps 0.5 * (pulled + own) unless it
+    drew itself -- and every other rank then takes its leader's result.
+
+    All phases use the publish + mix kernels of the flat gossip: in phase one a rank pulls the snapshots of its group
+    peers as a running mean (pull k with weight 1 / (k + 2)); in the gossip phase it publishes the group mean and pulls
+    one more snapshot with weight 1/2; version 1 adds a phase in which the followers pull their leader's snapshot
+    with weight 1. Every rank runs every phase, so the epochs of the flag protocol stay in step; a rank with nothing
+    to do in a phase issues a mix that lands on itself and changes nothing.
     """
     name = "group_allreduce_gossip_p2p"
 
-    def __init__(self, group=None, group_size: int = 2, seed=(53, 59), blocks: int = 96):
+    def __init__(self, group=None, group_size: int = 2, seed=(53, 59), blocks: int = 96, version: int = 2):
         super().__init__(group, mode="pull", seed=seed, blocks=blocks, synchronous=True)
+        if version not in (1, 2):
+            raise ValueError("version must be 1 or 2")
+        self.version = version
+        self._init_groups(group_size, seed)
+
+    def _init_groups(self, group_size, seed):
         self.group_size = max(1, min(group_size, self.world))
         g0 = self.rank // self.group_size * self.group_size
+        self.leader = g0
+        self.num_groups = (self.world + self.group_size - 1) // self.group_size
         self.group_peers = [r for r in range(g0, min(self.world, g0 + self.group_size)) if r != self.rank]
+        # version 1: a leader's draws come from its own stream, indexed by its position among the leaders (the
+        # stream the library backend gives the leaders' pull gossip)
+        self.leader_rng = XorShift128Plus(seed[0] + 1000003 * (self.rank // self.group_size), seed[1])
 
     def _phase(self, a, peers, weights, mix_self, st):
         a.mix_self = mix_self
@@ -497,7 +514,12 @@ class GroupGossipP2PComm(GossipP2PComm):
         net = self.net
         is_params = flat.data_ptr() == net.params.data_ptr()
         if not (repeat and self._last_peer is not None):
-            self._last_peer = [self.rng.below(self.world)]
+            if self.version == 2:
+                self._last_peer = [self.rng.below(self.world)]
+            elif self.rank == self.leader and self.num_groups > 1:
+                self._last_peer = [self.leader_rng.below(self.num_groups) * self.group_size]
+            else:
+                self._last_peer = [self.rank]
         st = torch.cuda.current_stream()
         a = PK.MixArgs()
         _fill_ptrs(a.flags, self._flag_ptrs())
@@ -515,7 +537,12 @@ class GroupGossipP2PComm(GossipP2PComm):
         a.w_self = 1.0
         peers = self.group_peers or [self.rank]
         self._phase(a, peers, [1.0 / (k + 2) for k in range(len(peers))], 0, st)
-        self._phase(a, self._last_peer, [0.5], 1, st)
+        if self.version == 2:
+            self._phase(a, self._last_peer, [0.5], 1, st)
+            return
+        # version 1: leaders gossip (a self-draw keeps the own group mean: mix_self = 0), then followers copy
+        self._phase(a, self._last_peer, [0.5], 0, st)
+        self._phase(a, [self.leader], [1.0], 0, st)
 
 
 class ElasticP2PComm(CommWorker, _P2PBase):

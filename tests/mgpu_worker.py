@@ -149,8 +149,38 @@ def case_group_gossip(rank, world, group_size):
         dist.barrier()
 
 
+def case_group_gossip_v1(rank, world, group_size):
+    """Leader gossip on the kernels: every rank of a group ends with its leader's result, which is the group mean or,
+    when the leader drew another group, the mean of the two group means."""
+    comm = p2p.GroupGossipP2PComm(group_size=group_size, seed=(53, 59), version=1)
+    net, _ = _param_engine(comm)
+    for rnd in range(4):
+        torch.manual_seed(4000 * rnd + rank)
+        net.params.copy_(torch.randn_like(net.params))
+        everyone = [torch.empty_like(net.params) for _ in range(world)]
+        dist.all_gather(everyone, net.params)
+        comm.sync_params(net.params)
+        torch.cuda.synchronize()
+        assert K.read_status() == 0
+        draws = [torch.zeros(1, dtype=torch.int64, device="cuda") for _ in range(world)]
+        dist.all_gather(draws, torch.tensor([comm._last_peer[0]], device="cuda"))
+        drawn = draws[comm.leader]                  # what this rank's leader drew
+
+        def group_mean(r):
+            g0 = r // group_size * group_size
+            members = range(g0, min(world, g0 + group_size))
+            return sum(everyone[m] for m in members) / len(members)
+
+        d = int(drawn)
+        expect = group_mean(rank) if d == comm.leader else 0.5 * (group_mean(rank) + group_mean(d))
+        n = net.params.numel() // 4 * 4
+        assert torch.allclose(net.params[:n], expect[:n], rtol=1e-5, atol=1e-5), f"round {rnd}"
+        assert torch.equal(net.params16[:n], net.params[:n].bfloat16())
+        dist.barrier()
+
+
 def case_elastic(rank, world):
-    comm = p2p.ElasticP2PComm(beta=0.25)
+    comm = p2p.ElasticP2PComm(beta=0.25, synchronous=True)
     oracle = comm_mod.ElasticComm(beta=0.25)
     net, _ = _param_engine(comm)
     torch.manual_seed(7)
@@ -176,7 +206,7 @@ def case_elastic(rank, world):
 
 
 def case_push(rank, world):
-    comm = p2p.PushGossipP2PComm(seed=(41, 43))
+    comm = p2p.PushGossipP2PComm(seed=(41, 43), synchronous=True)
     oracle = comm_mod.PushGossipComm(seed=(41, 43))
     net, _ = _param_engine(comm)
     for rnd in range(4):
@@ -189,6 +219,104 @@ def case_push(rank, world):
         assert K.read_status() == 0
         n = net.params.numel() // 4 * 4
         assert torch.allclose(net.params[:n], expect[:n], rtol=1e-5, atol=1e-5), f"round {rnd}"
+
+
+def _turns(world, rounds):
+    """A schedule in which rank 0 exchanges three times as often as the others: a list of ranks, one per turn."""
+    turns = []
+    for _ in range(rounds):
+        for r in range(world):
+            turns += [0, r] if r else [0]
+    return turns
+
+
+def case_push_async(rank, world):
+    """Asynchronous push gossip with the ranks any number of exchanges apart: ranks take turns (the others are idle on
+    the host), nobody waits for anybody inside an exchange, and the result equals the sequential restatement of the
+    accumulate / count / fold rules. A turn must also be fast: an exchange that waited for a peer would sit in a wait
+    until its limit."""
+    import time
+    from rembrandt_b200.utils.rng import XorShift128Plus
+    comm = p2p.PushGossipP2PComm(seed=(41, 43))
+    assert not comm.synchronous
+    comm.wait_ns = 20_000_000_000      # a wait on a peer, if there were one, would take 20 s
+    net, _ = _param_engine(comm)
+    torch.manual_seed(900 + rank)
+    net.params.copy_(torch.randn_like(net.params))
+    everyone = [torch.empty_like(net.params) for _ in range(world)]
+    dist.all_gather(everyone, net.params)
+    n = net.params.numel() // 4 * 4
+    x = [e[:n].clone() for e in everyone]
+    acc = [[torch.zeros_like(x[0]), torch.zeros_like(x[0])] for _ in range(world)]
+    cnt = [[0, 0] for _ in range(world)]
+    epoch = [0] * world
+    shadows = [XorShift128Plus(41 + 7919 * r, 43) for r in range(world)]
+    empty = 0
+    for turn, r in enumerate(_turns(world, 4)):
+        if rank == r:
+            t0 = time.time()
+            comm.sync_params(net.params)
+            torch.cuda.synchronize()
+            assert time.time() - t0 < 5.0, "an asynchronous exchange must not wait for a peer"
+        t = shadows[r].below(world)
+        if t != r:
+            acc[t][epoch[t] & 1] += x[r]
+            cnt[t][epoch[t] & 1] += 1
+        closed = epoch[r] & 1
+        epoch[r] += 1
+        w_self = 2.0 if t == r else 1.0
+        if cnt[r][closed]:
+            x[r] = (w_self * x[r] + acc[r][closed]) / (w_self + cnt[r][closed])
+            acc[r][closed].zero_()
+            cnt[r][closed] = 0
+        else:
+            empty += 1
+        dist.barrier()          # host-side turn taking only: the exchange itself contains no barrier
+        assert K.read_status() == 0
+        assert torch.allclose(net.params[:n], x[rank], rtol=1e-5, atol=1e-5), f"turn {turn} (rank {r})"
+    assert torch.equal(net.params16[:n], net.params[:n].bfloat16())
+
+
+def case_elastic_async(rank, world):
+    """Asynchronous elastic averaging: clients take the centre's lock one at a time, in any order and any number of
+    times, and each mixes with the centre as it is then; the lock is free afterwards and nothing was skipped."""
+    comm = p2p.ElasticP2PComm(beta=0.25)
+    assert not comm.synchronous
+    net, _ = _param_engine(comm)
+    torch.manual_seed(7)
+    net.params.copy_(torch.randn_like(net.params))
+    comm.first_one_way_sync(net.params)
+    n = net.params.numel() // 4 * 4
+    centre = net.params[:n].clone()
+    torch.manual_seed(70 + rank)
+    net.params.add_(torch.randn_like(net.params) * 0.1)
+    everyone = [torch.empty_like(net.params) for _ in range(world)]
+    dist.all_gather(everyone, net.params)
+    x = [e[:n].clone() for e in everyone]
+    for turn, r in enumerate(_turns(world, 3)):
+        if rank == r:
+            comm.sync_params(net.params)
+            torch.cuda.synchronize()
+        d = 0.25 * (x[r] - centre)
+        x[r] = x[r] - d
+        centre = centre + d
+        dist.barrier()
+        assert K.read_status() == 0
+        assert torch.allclose(net.params[:n], x[rank], rtol=1e-5, atol=1e-5), f"turn {turn} (rank {r})"
+    if rank == 0:
+        assert torch.allclose(comm.center[:n], centre, rtol=1e-5, atol=1e-5)
+        assert int(comm.lock[0]) == 0
+    assert comm.skipped_exchanges() == 0
+    # all clients at once: the lock serialises them; every exchange either ran alone or was given up and counted
+    before = net.params[:n].clone()
+    comm.sync_params(net.params)
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert K.read_status() == 0
+    moved = not torch.equal(before, net.params[:n])
+    assert moved or comm.skipped_exchanges() == 1
+    if rank == 0:
+        assert int(comm.lock[0]) == 0
 
 
 def main():
@@ -207,20 +335,33 @@ def main():
             case_gossip_pair(rank, world)
         elif case == "pull_rounds":
             case_pull_rounds(rank, world)
+        elif case.startswith("group_gossip_v1"):
+            case_group_gossip_v1(rank, world, int(case.rsplit("_", 1)[1]))
         elif case.startswith("group_gossip"):
             case_group_gossip(rank, world, int(case.rsplit("_", 1)[1]))
         elif case == "elastic":
             case_elastic(rank, world)
         elif case == "push":
             case_push(rank, world)
+        elif case == "push_async":
+            case_push_async(rank, world)
+        elif case == "elastic_async":
+            case_elastic_async(rank, world)
         else:
             raise SystemExit(f"unknown case {case}")
         torch.cuda.synchronize()
         dist.barrier()
         if rank == 0:
             print(f"case {case}: ok on {world} ranks")
-    finally:
-        dist.destroy_process_group()
+    except BaseException:
+        # leave at once: the other ranks may be inside a collective that this rank will never join, and the launcher
+        # ends them as soon as one worker has failed
+        import traceback
+        traceback.print_exc()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(1)
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -259,6 +259,27 @@ def test_conv_wgrad_tc(case, tile_mode):
     close(layout.conv_weight_from_internal(dw2, C, R, R), ref, rtol=2e-2)
 
 
+def test_deterministic_option_makes_weight_gradients_bit_identical():
+    """With the `deterministic` option no two CTAs add into the same element, so two launches on the same operands
+    agree bit for bit (the default splits long reductions over CTAs, whose additions arrive in any order)."""
+    case = (16, 64, 27, 27, 128, 5, 1, 2)
+    N, C, H, W, Ko, R, stride, pad = case
+    Cp, Kp, x, w, b, P, Q = _conv_setup(*case, seed=9)
+    dy = bf(torch.randn(N, Ko, P, Q, device=DEV))
+    xi, dyi = layout.to_nhwc_padded(x, Cp), layout.to_nhwc_padded(dy, Kp)
+    outs = []
+    with K.gemm_options(deterministic=1):
+        for _ in range(3):
+            dw = torch.zeros((Ko, R * R, Cp), device=DEV)
+            K.conv_wgrad_tc(xi, N, H, W, Cp, dyi, Kp, Ko, R, R, stride, pad, pad, P, Q, dw)
+            outs.append(dw)
+    status_ok()
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    wr = w.clone().requires_grad_()
+    ref = torch.autograd.grad(F.conv2d(x, wr, stride=stride, padding=pad), wr, dy)[0]
+    close(layout.conv_weight_from_internal(outs[0], C, R, R), ref, rtol=2e-2)
+
+
 @pytest.mark.parametrize("ks,st,HW", [(11, 4, 67), (7, 2, 31), (5, 2, 20)])
 def test_conv_s2d_first_layer_matches_strided_conv(ks, st, HW):
     """A strided k x k convolution on 3 channels == a stride-1 convolution on the space-to-depth input."""
@@ -471,6 +492,33 @@ def test_pointwise_loss(mode):
         assert correct.item() == int(((x[:, 0] > 0) == (t[:, 0] > 0.5)).sum())
 
 
+def test_sample_categories_follows_the_tempered_masked_softmax():
+    torch.manual_seed(17)
+    B, Kc = 4096, 37
+    ld = K.pad_channels(Kc)
+    row = torch.randn(Kc, device=DEV) * 1.5
+    x = torch.zeros(B, ld, device=DEV, dtype=torch.bfloat16)
+    x[:, :Kc] = row.bfloat16()
+    mask = torch.ones(B, Kc, device=DEV, dtype=torch.uint8)
+    mask[:, ::5] = 0
+    out = torch.full((B,), -7, device=DEV, dtype=torch.int32)
+    counts = torch.zeros(Kc, device=DEV)
+    for step in range(8):
+        K.sample_categories(x, B, Kc, ld, mask, 0.7, 1234, step, out)
+        assert int(out.min()) >= 0 and int(out.max()) < Kc
+        counts += torch.bincount(out.long(), minlength=Kc).float()
+    assert float(counts[::5].sum()) == 0, "a masked category was drawn"
+    p = torch.softmax((row.bfloat16().float() / 0.7).masked_fill(mask[0] == 0, float("-inf")), 0)
+    freq = counts / counts.sum()
+    assert float((freq - p).abs().max()) < 0.01, (freq, p)
+    # the same (seed, step) gives the same draws; another step gives others
+    a = torch.empty_like(out)
+    K.sample_categories(x, B, Kc, ld, mask, 0.7, 1234, 7, a)
+    assert torch.equal(a, out)
+    K.sample_categories(x, B, Kc, ld, mask, 0.7, 1234, 8, a)
+    assert not torch.equal(a, out)
+
+
 @pytest.mark.parametrize("objective", [1, 2, 3])
 @pytest.mark.parametrize("marginal", [False, True])
 def test_categorical_objective_heads(objective, marginal):
@@ -571,6 +619,25 @@ def test_bn_forward_backward():
     close(layout.from_nhwc_padded(dx, C), gx, rtol=5e-2)
     close(dgamma, gg, rtol=5e-2)
     close(dbeta, gb, rtol=5e-2)
+
+
+def test_bn_statistics_of_channels_whose_mean_dwarfs_their_spread():
+    """Channels at 200 +- 0.5 in bf16 (values on a grid of 1): E[x^2] - E[x]^2 in fp32 would lose the variance;
+    the shifted sums keep it."""
+    torch.manual_seed(16)
+    rows, C = 4096, 32
+    x = (200.0 + torch.randn(rows, C, device=DEV) * 0.5).bfloat16()
+    xf = x.float()
+    sums = torch.zeros(2 * C, device=DEV)
+    mean, istd = torch.empty(C, device=DEV), torch.empty(C, device=DEV)
+    rm, rv = torch.zeros(C, device=DEV), torch.ones(C, device=DEV)
+    g, b = torch.ones(C, device=DEV), torch.zeros(C, device=DEV)
+    y = torch.empty(rows, C, device=DEV, dtype=torch.bfloat16)
+    K.bn_fwd_train(x, rows, C, C, sums, 1e-5, 1.0, mean, istd, rm, rv, g, b, None, y, False)
+    var = xf.var(0, unbiased=False)
+    assert torch.allclose(mean, xf.mean(0), rtol=0, atol=1e-3)
+    assert torch.allclose(istd, torch.rsqrt(var + 1e-5), rtol=1e-3)
+    assert torch.allclose(rv, xf.var(0, unbiased=True), rtol=1e-3)
 
 
 def test_input_pipeline_center_crop_and_s2d():

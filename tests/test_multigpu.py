@@ -4,6 +4,7 @@ Each case runs tests/mgpu_worker.py under torch.distributed.run with a time limi
 the peer-to-peer kernels with the same exchange done through NCCL collectives.
 """
 import os
+import signal
 import socket
 import subprocess
 import sys
@@ -22,7 +23,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _run(case, nproc=None, timeout=240):
+def _run(case, nproc=None, timeout=120):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least 2 GPUs")
@@ -30,12 +31,21 @@ def _run(case, nproc=None, timeout=240):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(HERE, "mgpu_worker.py"), case]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout)
-    assert r.returncode == 0, (r.stdout[-3000:] + "\n" + r.stderr[-6000:])
-    assert f"case {case}: ok" in r.stdout
+    # its own session, so that a run that overstays is ended with all of its workers (a launcher killed alone would
+    # leave them on the GPUs)
+    proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, start_new_session=True)
+    try:
+        out, err = proc.communicate(timeout=timeout)
+    except subprocess.TimeoutExpired:
+        os.killpg(proc.pid, signal.SIGKILL)
+        out, err = proc.communicate()
+        raise AssertionError(f"case {case} overstayed {timeout} s\n" + out[-3000:] + "\n" + err[-6000:])
+    assert proc.returncode == 0, (out[-3000:] + "\n" + err[-14000:])
+    assert f"case {case}: ok" in out
 
 
-@pytest.mark.parametrize("case", ["p2p_allreduce", "fused_eager", "fused_graph", "gossip_pair", "pull_rounds", "elastic", "push"])
+@pytest.mark.parametrize("case", ["p2p_allreduce", "fused_eager", "fused_graph", "gossip_pair", "pull_rounds", "elastic", "push",
+                                  "push_async", "elastic_async"])
 def test_p2p_backend(case):
     _run(case)
 

@@ -61,9 +61,8 @@ def _make(rank, world, group_size, seed, fake):
     c.mode, c.alpha, c.blocks, c.synchronous = "pull", 0.5, 8, True
     c.rng = XorShift128Plus(seed[0] + 1000003 * rank, seed[1])
     c._last_peer = None
-    c.group_size = max(1, min(group_size, world))
-    g0 = rank // c.group_size * c.group_size
-    c.group_peers = [r for r in range(g0, min(world, g0 + c.group_size)) if r != rank]
+    c.version = 2
+    c._init_groups(group_size, seed)
     c.net = types.SimpleNamespace(params=fake.w[rank], params16=torch.zeros(1))
     c.pub = torch.zeros(1)
     c.epochs = torch.zeros(4, dtype=torch.int32)
@@ -101,6 +100,44 @@ def test_group_gossip_launch_sequence_gives_group_mean_then_half_pull(monkeypatc
     # the draws are the per-rank streams of the library backend, so both backends pick the same peers
     ref = XorShift128Plus(53 + 1000003 * 1, 59)
     assert [ref.below(world) for _ in range(3)][-1] == comms[1]._last_peer[0]
+
+
+@pytest.mark.parametrize("world,group_size", [(2, 1), (4, 2), (6, 2), (8, 4), (5, 3)])
+def test_leader_gossip_launch_sequence_gives_every_group_its_leaders_result(monkeypatch, world, group_size):
+    """First version of the hierarchical scheme: group mean, gossip among the group leaders only, followers take their
+    leader's result (src/worker/gossip_pull_allreduce_dist_rdma.rs:327-402)."""
+    n = 16
+    fake = FakeWorld(world, n)
+    monkeypatch.setattr(PK, "fn", fake.fn)
+    monkeypatch.setattr(torch.cuda, "current_stream", lambda: types.SimpleNamespace(cuda_stream=0))
+    comms = [_make(r, world, group_size, (53, 59), fake) for r in range(world)]
+    for c in comms:
+        c.version = 1
+    groups = (world + group_size - 1) // group_size
+    shadows = {g: XorShift128Plus(53 + 1000003 * g, 59) for g in range(groups)}
+    mixed = 0
+    for rnd in range(4):
+        torch.manual_seed(70 + rnd)
+        start = [torch.randn(n) for _ in range(world)]
+        for r in range(world):
+            fake.w[r] = start[r].clone()
+            comms[r].net.params = fake.w[r]
+        for r in range(world):
+            fake.current = r
+            comms[r].sync_params(fake.w[r])
+        fake.run()
+
+        def gmean(g):
+            members = range(g * group_size, min(world, (g + 1) * group_size))
+            return sum(start[m] for m in members) / len(members)
+
+        for g in range(groups):
+            drawn = shadows[g].below(groups) if groups > 1 else g
+            want = gmean(g) if drawn == g else 0.5 * (gmean(g) + gmean(drawn))
+            mixed += drawn != g
+            for r in range(g * group_size, min(world, (g + 1) * group_size)):
+                assert torch.allclose(fake.w[r], want, atol=1e-6), (rnd, r, drawn)
+    assert groups == 1 or mixed > 0
 
 
 def test_guard_bands_detect_writes_outside_the_payload(monkeypatch):
