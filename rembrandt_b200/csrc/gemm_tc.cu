@@ -68,6 +68,7 @@ struct SharedCtl {
 };
 
 __device__ __forceinline__ bool ctl_wait(SharedCtl* ctl, uint64_t* bar, uint32_t parity, unsigned int* status) {
+  if (mbar_try_wait(bar, parity)) return true;    // the common case costs one instruction, no read of the abort flag
   if (ctl->abort_flag) return false;
   if (mbar_wait_bounded(bar, parity, WAIT_LIMIT_NS)) return true;
   ctl->abort_flag = 1;
@@ -227,7 +228,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   const int stages = p.stages;
 
   const bool halo = p.a_mode == A_HALO_K;
-  const int m_items = halo ? (p.M / (p.cv_P * p.cv_Q)) * p.hl_groups : (p.M + BM * mt - 1) / (BM * mt);
+  const bool box = p.a_mode == A_BOX_K;
+  const int bx_groups = box ? (p.cv_P + mt * p.bx_rows - 1) / (mt * p.bx_rows) : 1;   // work items per image
+  const int m_items = halo  ? (p.M / (p.cv_P * p.cv_Q)) * p.hl_groups
+                      : box ? (p.M / (p.cv_P * p.cv_Q)) * bx_groups
+                            : (p.M + BM * mt - 1) / (BM * mt);
   const int n_tiles = p.n_tiles;
   // whole items first, then the parts of the cut items of the last wave (tail cut; never in halo mode)
   const int direct = m_items * n_tiles - p.tail_items;
@@ -327,11 +332,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       // loads this warp issues per stage, one lane each
       int nload;
       const int a_split = p.a_split > 0 ? p.a_split : 1, b_split = p.b_split > 0 ? p.b_split : 1;
-      if (is_a) nload = (p.a_mode == A_TILED_MN ? 2 : a_split) * mt;
+      if (is_a) nload = box ? mt : (p.a_mode == A_TILED_MN ? 2 : a_split) * mt;
       else if (p.b_mode == B_TILED_MN) nload = p.bn_load / 64;
       else if (p.b_mode == B_IM2COL_MN) nload = p.wg_taps > 1 ? p.wg_taps * (p.wg_cw / 64) : p.bn_load / 64;
       else nload = b_split;
-      const uint32_t my_tx = is_a ? (uint32_t)(mt * a_bytes) : (uint32_t)b_bytes;
+      const uint32_t my_tx = !is_a ? (uint32_t)b_bytes
+                             : box ? (uint32_t)(mt * p.bx_rows * p.cv_Q * p.bk * 2)   // the boxes bring whole rows only
+                                   : (uint32_t)(mt * a_bytes);
       for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
         const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
         const int tn = it.tn, tm = it.tm, kb0 = it.kb0, kb1 = it.kb1;
@@ -343,6 +350,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         const int a_rows = BM / a_split;
         int a_w = 0, a_h = 0, a_n = 0;
         if (is_a && p.a_mode == A_IM2COL_K && lane < nload) pixel_coords(p, m0 + aj * BM + aq * a_rows, a_w, a_h, a_n);
+        if (is_a && box) {   // lane j loads sub-tile j: image a_n, first output row a_h
+          a_n = tm / bx_groups;
+          a_h = ((tm - a_n * bx_groups) * mt + lane) * p.bx_rows;
+        }
         int b_tap = 0, b_c0 = 0;
         const int n0 = tn * p.bn;
         if (p.b_mode == B_IM2COL_MN) {
@@ -370,6 +381,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
               const int mj = m0 + aj * BM + aq * a_rows;
               if (p.a_mode == A_TILED_K) {
                 tma_load_2d(saj, &p.tm_a, bar, kb * p.bk, mj);
+              } else if (box) {
+                const int tap = kb / p.cv_cchunks;
+                const int cc = kb - tap * p.cv_cchunks;
+                const int r = tap / p.cv_S;
+                const int sx = tap - r * p.cv_S;
+                tma_load_4d(sa + lane * a_bytes, &p.tm_a, bar, cc * p.bk, sx - p.bx_pad_w, a_h + r - p.bx_pad_h, a_n);
               } else if (p.a_mode == A_IM2COL_K) {
                 const int tap = kb / p.cv_cchunks;
                 const int cc = kb - tap * p.cv_cchunks;
@@ -580,7 +597,18 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           h_w = lane_base % p.hl_pitch;
           if (h_p >= p.cv_P || h_w >= p.cv_Q) continue;   // the whole band lies outside the image
         }
-        const int row0 = tm * BM * mt + j * BM + lane_base;   // first row of this warp's 32-row band
+        int row0 = tm * BM * mt + j * BM + lane_base;   // first row of this warp's 32-row band
+        int band_rows = 32;                             // rows of the band that belong to this tile
+        if (box) {
+          // the sub-tile is bx_rows whole output rows of one image: consecutive rows of D, fewer at the image's
+          // lower edge; tile rows past them are computed from stale shared memory and dropped here
+          const int b_n = tm / bx_groups;
+          const int b_p = ((tm - b_n * bx_groups) * mt + j) * p.bx_rows;
+          const int valid = max(0, min(p.bx_rows, p.cv_P - b_p)) * p.cv_Q;
+          band_rows = max(0, min(32, valid - lane_base));
+          row0 = (b_n * p.cv_P + b_p) * p.cv_Q + lane_base;
+          if (band_rows == 0 && !tail) continue;
+        }
         const uint32_t t_addr =
             tmem_base + (uint32_t)acc * set_cols + (uint32_t)(j * p.acc_stride) + ((uint32_t)lane_base << 16);
         if (p.epi == EPI_BF16 && !tail) {
@@ -666,7 +694,19 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0 && (halo || row0 < p.M)) {
+            if (band_rows < 32) {
+              // ragged band (box mode): the rows after the tile's last belong to other tiles, so the valid rows are
+              // copied out by hand, 16 bytes at a time, instead of a 32-row TMA store
+              if (lane < band_rows) {
+                bf16* drow = reinterpret_cast<bf16*>(p.D) + (long long)(row0 + lane) * p.ldd + gcol;
+#pragma unroll
+                for (int ch = 0; ch < 8; ++ch)
+                  if (gcol + ch * 8 < p.n_store)
+                    *reinterpret_cast<uint4*>(drow + ch * 8) =
+                        *reinterpret_cast<const uint4*>(buf + lane * 128 + ((ch ^ (lane & 7)) * 16));
+              }
+              __syncwarp();
+            } else if (lane == 0 && (halo || row0 < p.M)) {
               if (halo) tma_store_4d(&p.tm_d, buf, gcol, h_w, h_p, h_n);
               else tma_store_2d(&p.tm_d, buf, gcol, row0);
               tma_store_commit();
@@ -846,6 +886,7 @@ struct GemmOptions {
   int force_taps = 0;        // RB_GEMM_FORCE_TAPS: filter taps per weight-grad tile
   int force_tail = -1;       // RB_GEMM_FORCE_TAIL: 0 = never cut the last wave, 1 = whenever feasible
   int force_wide = -1;       // RB_GEMM_FORCE_WIDE: 0 = tiles of at most 256 columns, 1 = one wide tile when N <= 512
+  int force_box = -1;        // RB_GEMM_FORCE_BOX: 0 = never load A as tap-shifted boxes, 1 = whenever feasible
   int bk32 = 0;              // RB_GEMM_BK32: keep 32-channel chunks for channel counts such as 96
   int bn_cap = 256;          // RB_GEMM_BN_CAP: upper bound on the tile width chosen by the planner
   int a_split = 1;           // RB_GEMM_A_SPLIT / RB_GEMM_B_SPLIT: TMA boxes per K-major tile
@@ -862,6 +903,7 @@ static int* option_slot(const char* name) {
   struct { const char* name; int* slot; } table[] = {
       {"force_mt", &g_opt.force_mt}, {"force_resident", &g_opt.force_resident}, {"force_halo", &g_opt.force_halo},
       {"force_taps", &g_opt.force_taps}, {"force_tail", &g_opt.force_tail}, {"force_wide", &g_opt.force_wide},
+      {"force_box", &g_opt.force_box},
       {"bk32", &g_opt.bk32}, {"bn_cap", &g_opt.bn_cap}, {"a_split", &g_opt.a_split}, {"b_split", &g_opt.b_split},
       {"autotune", &g_opt.autotune}, {"deterministic", &g_opt.deterministic}};
   for (auto& t : table)
@@ -870,7 +912,7 @@ static int* option_slot(const char* name) {
 }
 static void options_from_env() {
   std::call_once(g_opt_once, [] {
-    const char* names[] = {"force_mt", "force_resident", "force_halo", "force_taps", "force_tail", "force_wide",
+    const char* names[] = {"force_mt", "force_resident", "force_halo", "force_taps", "force_tail", "force_wide", "force_box",
                            "bk32", "bn_cap", "a_split", "b_split", "autotune", "deterministic"};
     for (const char* n : names) {
       char env[64] = "RB_GEMM_";
@@ -906,6 +948,15 @@ static bool split_ok(int s, int num_kb) { return s == 1 || (s - 1) * ((num_kb + 
 
 static int acc_stride_for(int bn) { return bn > 256 ? 512 : (bn > 128 ? 256 : 128); }
 
+// Work items along M for `mt` sub-tiles per item (box mode: whole output rows per sub-tile, per image).
+static int m_items_of(const GemmTcParams& p, int mt) {
+  if (p.a_mode == A_BOX_K) {
+    const int groups = (p.cv_P + mt * p.bx_rows - 1) / (mt * p.bx_rows);
+    return (p.M / (p.cv_P * p.cv_Q)) * groups;
+  }
+  return (p.M + BM * mt - 1) / (BM * mt);
+}
+
 // Parts per cut item for `items` work items on `sms` SMs (0 = cutting does not pay or is not possible): the last
 // wave must be at most half full, every SM gets at most one part, a part keeps at least four k-blocks.
 static int tail_parts(long long items, int sms, int num_kb) {
@@ -933,9 +984,10 @@ static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split,
   for (int mt = 1; mt <= 2; ++mt) {
     if (pass == 0 && force_mt && mt != force_mt) continue;
     if (mt == 2 && (p.M <= BM || p.bn > 256)) continue;
+    if (mt == 2 && p.a_mode == A_BOX_K && p.cv_P <= p.bx_rows) continue;
     const int acc_stride = acc_stride_for(p.bn);
     const int acc_bufs = (2 * mt * acc_stride <= 512) ? 2 : 1;
-    const int m_items = (p.M + BM * mt - 1) / (BM * mt);
+    const int m_items = m_items_of(p, mt);
     const long long tiles = (long long)m_items * p.n_tiles;
     const int max_split = allow_split ? (p.num_kb / 8 > 64 ? 64 : (p.num_kb / 8 < 1 ? 1 : p.num_kb / 8)) : 1;
     for (int s = (fixed_split > 0 ? fixed_split : 1); s <= (fixed_split > 0 ? fixed_split : max_split); ++s) {
@@ -993,7 +1045,8 @@ static int apply_plan(GemmTcParams& p, const Plan& pl) {
   if (p.stages > MAX_STAGES) p.stages = MAX_STAGES;
   if (p.stages < 2) return 0;
   if (p.mt == 2 && p.M <= BM) return 0;
-  const int m_items = (p.M + BM * p.mt - 1) / (BM * p.mt);
+  if (p.mt == 2 && p.a_mode == A_BOX_K && p.cv_P <= p.bx_rows) return 0;
+  const int m_items = m_items_of(p, p.mt);
   const long long items = (long long)m_items * p.n_tiles;
   p.tail_items = 0;
   p.tail_split = 0;
@@ -1026,6 +1079,7 @@ struct TailFixArgs {
   const __nv_bfloat16* mask;
   long long ldd;
   int M, bn, rows_per_item, m_items, direct, tail_items, n_valid, n_store, relu;
+  int box, P, Q, bx_rows, bx_groups, mt;   // box mode: rows of a sub-tile are whole output rows of one image
 };
 __global__ void tail_fix_kernel(const TailFixArgs a) {
   const int gpr = a.bn / 8;
@@ -1039,13 +1093,21 @@ __global__ void tail_fix_kernel(const TailFixArgs a) {
     const int r = (int)(wr - (long long)ti * a.rows_per_item);
     const int rem = a.direct + ti;
     const int tn = rem / a.m_items, tm = rem - tn * a.m_items;
-    const long long row = (long long)tm * a.rows_per_item + r;
+    long long row = (long long)tm * a.rows_per_item + r;
+    bool live = true;
+    if (a.box) {
+      const int j = r / BM, i = r - j * BM;
+      const int n_img = tm / a.bx_groups;
+      const int p_sub = ((tm - n_img * a.bx_groups) * a.mt + j) * a.bx_rows;
+      live = i < max(0, min(a.bx_rows, a.P - p_sub)) * a.Q;
+      row = ((long long)n_img * a.P + p_sub) * a.Q + i;
+    }
     const int col = tn * a.bn + c8 * 8;
     float4* src = reinterpret_cast<float4*>(a.ws + wr * a.bn + c8 * 8);
     const float4 v0 = src[0], v1 = src[1];
     src[0] = make_float4(0.f, 0.f, 0.f, 0.f);
     src[1] = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (row >= a.M || col >= a.n_store) continue;
+    if (!live || row >= a.M || col >= a.n_store) continue;
     float f[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
@@ -1077,7 +1139,13 @@ static int run_plan(GemmTcParams p, const Plan& pl, cudaStream_t stream) {
     f.M = p.M;
     f.bn = p.bn;
     f.rows_per_item = p.mt * BM;
-    f.m_items = (p.M + BM * p.mt - 1) / (BM * p.mt);
+    f.m_items = m_items_of(p, p.mt);
+    f.box = p.a_mode == A_BOX_K ? 1 : 0;
+    f.P = p.cv_P;
+    f.Q = p.cv_Q;
+    f.bx_rows = p.bx_rows;
+    f.bx_groups = f.box ? (p.cv_P + p.mt * p.bx_rows - 1) / (p.mt * p.bx_rows) : 1;
+    f.mt = p.mt;
     f.direct = f.m_items * p.n_tiles - p.tail_items;
     f.tail_items = p.tail_items;
     f.n_valid = p.n_valid;
@@ -1119,8 +1187,7 @@ static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t st
         Plan cand{mt, 1, res, 0, 0.0};
         if (tail) {
           if (!p.ws || g_opt.force_tail == 0 || g_opt.deterministic) continue;
-          const int m_items = (p.M + BM * mt - 1) / (BM * mt);
-          cand.tail = tail_parts((long long)m_items * p.n_tiles, g_num_sms, p.num_kb);
+          cand.tail = tail_parts((long long)m_items_of(p, mt) * p.n_tiles, g_num_sms, p.num_kb);
           if (cand.tail == 0) continue;
         }
         GemmTcParams q = p;
@@ -1388,58 +1455,78 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
   const int upper_h = (P - 1) * stride - pad_h - (H - 1);
   const int upper_w = (Q - 1) * stride - pad_w - (W - 1);
   p.a_split = pick_box_split(g_opt.a_split, BM, p.bk);
-  if (R == 1 && S == 1 && stride == 1 && pad_h == 0 && pad_w == 0 && P == H && Q == W) {
-    // a 1 x 1 convolution is a plain GEMM over the pixel rows: tiled loads, which the TMA unit serves 2-3x faster
-    // per row than im2col-mode loads
-    p.a_mode = A_TILED_K;
-    rc = make_map_2d(&p.tm_a, x, Cp, (uint64_t)p.M, Cp, p.bk, BM / p.a_split, ksw);
-  } else {
-    rc = make_map_im2col(&p.tm_a, x, N, H, W, Cp, -pad_h, -pad_w, upper_h, upper_w, stride, p.bk, BM / p.a_split, ksw);
-  }
-  if (rc) return rc;
+  const bool one_by_one = R == 1 && S == 1 && stride == 1 && pad_h == 0 && pad_w == 0 && P == H && Q == W;
   rc = make_map_out(&p.tm_d, y, p.n_store, p.M, ldy);
   if (rc) return rc;
   if (mask_src) rc = make_map_out(&p.tm_mask, const_cast<void*>(mask_src), p.n_store, p.M, ldy);
   if (rc) return rc;
-  // what depends on the tile width: the column tiling and the filter map's box
-  auto set_width = [&](GemmTcParams& q, int bn) -> int {
+  // How the A operand is loaded (`box` = tap-shifted tiled boxes of whole output rows, else the im2col map, or plain
+  // tiled rows for a 1 x 1 convolution) and what depends on the tile width: column tiling, the filter map's box.
+  auto configure = [&](GemmTcParams& q, int box, int bn) -> int {
+    int e;
+    if (box) {
+      q.a_mode = A_BOX_K;
+      q.a_split = 1;
+      q.bx_rows = BM / Q;
+      q.bx_pad_h = pad_h;
+      q.bx_pad_w = pad_w;
+      e = make_map_nhwc(&q.tm_a, x, Cp, W, H, N, Cp, q.bk, Q, q.bx_rows, ksw);
+    } else if (one_by_one) {
+      // a 1 x 1 convolution is a plain GEMM over the pixel rows: tiled loads, which the TMA unit serves 2-3x
+      // faster per row than im2col-mode loads
+      q.a_mode = A_TILED_K;
+      e = make_map_2d(&q.tm_a, x, Cp, (uint64_t)q.M, Cp, q.bk, BM / q.a_split, ksw);
+    } else {
+      q.a_mode = A_IM2COL_K;
+      e = make_map_im2col(&q.tm_a, x, N, H, W, Cp, -pad_h, -pad_w, upper_h, upper_w, stride, q.bk, BM / q.a_split, ksw);
+    }
+    if (e) return e;
     q.bn = q.bn_load = bn;
     q.n_tiles = (n_cols + bn - 1) / bn;
     q.b_split = pick_box_split(g_opt.b_split, bn, q.bk);
     return make_map_3d(&q.tm_b, w, Cp, (uint64_t)R * S, Kout, Cp, (uint64_t)R * S * Cp, q.bk, 1, bn / q.b_split, ksw);
   };
-  // Between 257 and 512 output columns there is a second candidate: ONE tile as wide as the layer (two MMAs side
-  // by side, one accumulator set, no overlap of epilogue and main loop) instead of two or more narrower tiles
-  // that each load the A operand again. Which is faster is decided by measurement in tuning mode and remembered
-  // per shape; without a measurement the narrower tiles are taken.
+  // Candidates beside the default (im2col loads, tiles of at most 256 columns):
+  //  * between 257 and 512 output columns, ONE tile as wide as the layer (two MMAs side by side, one accumulator
+  //    set, no overlap of epilogue and main loop) instead of narrower tiles that each load the A operand again;
+  //  * for stride-1 convolutions with more than one tap and output rows of at most 128 positions, box loads:
+  //    cheaper per row for the TMA unit, at the price of tile rows that are computed and dropped when Q does not
+  //    divide 128 (and when bx_rows does not divide P).
+  // Which is fastest is decided by measurement in tuning mode and remembered per shape; without a measurement the
+  // default is taken.
   const int bn_default = p.bn;
   const int bn_wide = (n_cols > 256 && n_cols <= 512 && g_opt.force_wide != 0 && g_opt.bn_cap >= 256) ? n_cols : 0;
-  int bn_use = bn_default;
-  if (bn_wide) {
+  const bool box_ok = stride == 1 && R * S > 1 && Q <= BM && g_opt.force_box != 0 && g_opt.force_halo != 1;
+  int use = bn_default;   // low 16 bits: tile width; bit 16: box loads
+  if (bn_wide || box_ok) {
     p.bn = p.n_tiles = 0;
-    const PlanKey wkey = plan_key(p);
+    p.a_mode = A_IM2COL_K;
+    const PlanKey ckey = plan_key(p);
     std::lock_guard<std::mutex> lock(g_plan_mutex);   // released at the end of this block, before `launch` takes it
-    auto it = g_bn_cache.find(wkey);
-    if (g_opt.force_wide == 1) {
-      bn_use = bn_wide;
+    auto it = g_bn_cache.find(ckey);
+    if (g_opt.force_wide == 1 || g_opt.force_box == 1) {
+      use = ((bn_wide && g_opt.force_wide == 1) ? bn_wide : bn_default) | ((box_ok && g_opt.force_box == 1) ? 1 << 16 : 0);
     } else if (it != g_bn_cache.end()) {
-      bn_use = it->second;
+      use = it->second;
     } else if (tunable(p, stream)) {
       float best_ms = 1e30f;
-      for (int bn : {bn_default, bn_wide}) {
-        GemmTcParams q = p;
-        if (set_width(q, bn)) continue;
-        Plan pl{1, 1, 0, 0, 0.0};
-        const float ms = tune_plan(q, true, stream, &pl);
-        if (ms > 0.f) {
-          g_plan_cache[plan_key(q)] = pl;
-          if (ms < best_ms) { best_ms = ms; bn_use = bn; }
+      for (int box = 0; box <= (box_ok ? 1 : 0); ++box) {
+        for (int bn : {bn_default, bn_wide}) {
+          if (bn == 0) continue;
+          GemmTcParams q = p;
+          if (configure(q, box, bn)) continue;
+          Plan pl{1, 1, 0, 0, 0.0};
+          const float ms = tune_plan(q, true, stream, &pl);
+          if (ms > 0.f) {
+            g_plan_cache[plan_key(q)] = pl;
+            if (ms < best_ms) { best_ms = ms; use = bn | (box << 16); }
+          }
         }
       }
-      g_bn_cache[wkey] = bn_use;
+      g_bn_cache[ckey] = use;
     }
   }
-  rc = set_width(p, bn_use);
+  rc = configure(p, (use >> 16) & 1, use & 0xFFFF);
   if (rc) return rc;
   return launch(p, false, 1, true, stream);
 }

@@ -17,7 +17,7 @@
 
 namespace rb {
 
-enum : int { A_TILED_K = 0, A_IM2COL_K = 1, A_TILED_MN = 2, A_HALO_K = 3 };
+enum : int { A_TILED_K = 0, A_IM2COL_K = 1, A_TILED_MN = 2, A_HALO_K = 3, A_BOX_K = 4 };
 enum : int { B_TILED_K = 0, B_TILED_MN = 1, B_IM2COL_MN = 2, B_TILED_K3 = 3 };
 enum : int { EPI_BF16 = 0, EPI_F32_STORE = 1, EPI_F32_ATOMIC = 2 };
 
@@ -60,6 +60,12 @@ struct alignas(64) GemmTcParams {
   int hl_pad_h, hl_pad_w;
   int hl_a_stages;     // A stages in shared memory (each hl_a_bytes apart)
   int hl_a_bytes;
+  // box mode (A_BOX_K, stride-1 convolutions): a sub-tile is bx_rows whole output rows of one image (bx_rows * Q <=
+  // 128 positions, contiguous in the NHWC output); the A operand of filter tap (r, s) is ONE tiled 4-D box of
+  // bx_rows x Q pixels x bk channels whose corner is shifted by the tap (zero fill outside the image), which the TMA
+  // unit serves at the rate of tiled loads instead of the 2-3 times slower im2col mode
+  int bx_rows;
+  int bx_pad_h, bx_pad_w;
   // epilogue
   int epi;
   int relu;            // EPI_BF16: clamp at zero after the bias

@@ -157,6 +157,7 @@ def case_group_gossip_v1(rank, world, group_size):
     for rnd in range(4):
         torch.manual_seed(4000 * rnd + rank)
         net.params.copy_(torch.randn_like(net.params))
+        net.refresh_shadow()       # a leader that draws itself mixes nothing and leaves the compute copy as it is
         everyone = [torch.empty_like(net.params) for _ in range(world)]
         dist.all_gather(everyone, net.params)
         comm.sync_params(net.params)
@@ -243,6 +244,7 @@ def case_push_async(rank, world):
     net, _ = _param_engine(comm)
     torch.manual_seed(900 + rank)
     net.params.copy_(torch.randn_like(net.params))
+    net.refresh_shadow()           # an exchange in which nothing arrived leaves the compute copy as it is
     everyone = [torch.empty_like(net.params) for _ in range(world)]
     dist.all_gather(everyone, net.params)
     n = net.params.numel() // 4 * 4

@@ -120,6 +120,8 @@ CONV_CASES = [
     (1, 32, 70, 66, 32, 3, 1, 1),     # halo mode: row pitch 128, non-square
     (128, 64, 13, 13, 64, 3, 1, 1),   # 169 row tiles on 148 SMs: the 21 of the last wave are cut along the reduction
     (128, 32, 13, 13, 320, 3, 1, 1),  # the same with one 320-column tile (two MMAs side by side)
+    (40, 64, 27, 27, 64, 5, 1, 2),    # box loads: 4 output rows per sub-tile, 280 tiles, ragged last band of each tile
+    (3, 64, 20, 23, 96, 3, 1, 0),     # box loads without padding: output narrower than the input
 ]
 
 
@@ -135,11 +137,11 @@ def _conv_setup(N, C, H, W, Ko, R, stride, pad, seed=0):
 
 
 @pytest.fixture(params=["auto", "halo", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3", "tail",
-                        "wide", "wide_tail", "tuned"])
+                        "wide", "wide_tail", "box", "box_mt2", "box_tail", "box_wide", "tuned"])
 def tile_mode(request):
     """Force the kernel's tile-shape planner through each of its modes (two sub-tiles per item, resident B,
     column-shifted halo tiles for stride-1 convolutions, the last wave cut along the reduction, one tile as wide as
-    the layer, plans chosen by measurement)."""
+    the layer, tap-shifted box loads of whole output rows, plans chosen by measurement)."""
     mode = request.param
     opts = {}
     if mode == "halo":
@@ -151,6 +153,10 @@ def tile_mode(request):
         opts["force_resident"] = 1 if "resident" in mode else 0
         if "taps" in mode:
             opts["force_taps"] = int(mode[-1])
+    if "box" in mode:
+        opts["force_box"] = 1
+        if "mt2" in mode:
+            opts["force_mt"] = 2
     if "tail" in mode:
         opts["force_tail"] = 1
     if "wide" in mode:
