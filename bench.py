@@ -228,9 +228,19 @@ def run_arm(args, impl, variant, world, rank, local_rank, dev, host_imgs, host_l
         time.sleep(0.15)
     t_dev, last_loss = timed_regions(resident_step, finish, args.steps, barrier, stream, world, dev, args.min_seconds,
                                      args.max_repeats)
+    if impl == "ours":
+        engine.time_h2d(True)
     t_e2e, _ = timed_regions(feed_step, finish, args.steps, barrier, stream, world, dev, args.min_seconds,
                              args.max_repeats)
     clocks = sampler.stop() if rank == 0 else None
+    if impl == "ours":
+        # device time of one staging copy, slowest rank: what the host side of the end-to-end path costs per step
+        engine.time_h2d(False)
+        h2d_ms = torch.tensor([engine.h2d_ms() or 0.0], device=dev)
+        if world > 1:
+            dist.all_reduce(h2d_ms, op=dist.ReduceOp.MAX)
+        extra["h2d_copy_ms_slowest_rank"] = round(float(h2d_ms), 4)
+        extra["numa_node"] = args.numa_node
     if impl == "ours":
         extra["gpu_launches"] = engine.launches_per_step * args.steps
         extra["device_status"] = K.read_status()
@@ -266,6 +276,8 @@ def main():
     ap.add_argument("--min-seconds", type=float, default=2.0,
                     help="repeat the timed region of K steps until this much device time has been measured")
     ap.add_argument("--max-repeats", type=int, default=400)
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="do not restrict the rank's host threads to the NUMA node of its GPU")
     ap.add_argument("--baseline-variants", default="auto",
                     help="stock-PyTorch variants timed in the same process (eager, graph, bf16_graph, compiled); the "
                          "fastest is reported. auto = graph,compiled,eager on one GPU (compiling takes about two "
@@ -292,6 +304,11 @@ def main():
         if world == 1 and args.gpus > 1:
             raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N > 1")
     torch.cuda.set_device(local_rank)
+    # the pinned staging batches below are placed on the node of the thread that touches them first: stay on the GPU's
+    args.numa_node = None
+    if not args.no_numa_bind:
+        from rembrandt_b200.utils.numa import bind_to_gpu_node
+        args.numa_node = bind_to_gpu_node(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -362,6 +379,8 @@ def main():
             "timing": spread(main_arm["times_dev"], args.steps, main_arm["clocks"]),
             "e2e": {"value": round(e2e, 1), "unit": "images/s", "ms_per_step": round(med_e2e / args.steps, 4),
                     "h2d_bytes_per_step": main_arm["h2d"], "d2h_bytes_per_step": main_arm["d2h"],
+                    "h2d_copy_ms_slowest_rank": main_arm.get("h2d_copy_ms_slowest_rank"),
+                    "host_threads_bound_to_numa_node": main_arm.get("numa_node"),
                     "timing": spread(main_arm["times_e2e"], args.steps, main_arm["clocks"]),
                     "note": "pinned uint8 batch + int32 labels copied every step; loss read back with a one-step lag"},
             "gpu_launches": main_arm.get("gpu_launches", 0),

@@ -52,7 +52,9 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError("build step failed:\n  " + " ".join(cmd) + "\n" + r.stdout + r.stderr)
 
 
-def build_cuda(force: bool = False, verbose: bool = False) -> Path:
+def build_cuda(force: bool = False, verbose: bool = False, defines: tuple = ()) -> Path:
+    """`defines` (e.g. ("RB_GEMM_PROFILE",)) are passed as -D to every kernel file and force a rebuild; a library
+    built with them should be rebuilt without them afterwards (`python -m rembrandt_b200._build --force`)."""
     LIBDIR.mkdir(exist_ok=True)
     OBJDIR.mkdir(exist_ok=True)
     out = LIBDIR / "librembrandt_cuda.so"
@@ -61,11 +63,12 @@ def build_cuda(force: bool = False, verbose: bool = False) -> Path:
     nvcc = _nvcc()
     jobs = []
     objs = []
+    force = force or bool(defines)
     for src in sources:
         obj = OBJDIR / (src.stem + ".o")
         objs.append(obj)
         if force or _newer(src, obj, headers):
-            cmd = [nvcc, *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            cmd = [nvcc, *NVCC_FLAGS, *(f"-D{d}" for d in defines), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
             if verbose:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)
@@ -98,11 +101,13 @@ def build_host(force: bool = False) -> Path:
     return out
 
 
-def build_all(force: bool = False, verbose: bool = False) -> None:
+def build_all(force: bool = False, verbose: bool = False, defines: tuple = ()) -> None:
     build_host(force)
-    build_cuda(force, verbose)
+    build_cuda(force, verbose, defines)
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    # --profile: the tensor-core kernel counts the cycles its roles spend waiting (read by `bench_conv --roles`)
+    build_all(force="--force" in sys.argv, verbose="-v" in sys.argv,
+              defines=("RB_GEMM_PROFILE",) if "--profile" in sys.argv else ())
     print("built:", *(str(p) for p in sorted(LIBDIR.glob("*.so"))))

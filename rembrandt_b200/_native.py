@@ -34,6 +34,7 @@ _CUDA_SIGS = {
     "rb_gemm_clear_plans": [],
     "rb_conv_wgrad_tc": [vp, i32, i32, i32, i32, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp],
     "rb_num_sms": [],
+    "rb_gemm_role_profile": [vp],
     # conv_direct.cu
     "rb_conv_direct_fwd": [vp, vp, vp, vp] + [i32] * 14 + [vp],
     "rb_conv_direct_dgrad": [vp, vp, vp, vp] + [i32] * 13 + [vp],

@@ -35,7 +35,10 @@ SHAPES = {
 }
 
 
-def run(name, batch, passes, iters, warmup, tune=True):
+PEAK_TFLOPS = 1658.7      # cuBLAS bf16 matmul measured on this pool's B200 (burst); fractions are "of measured"
+
+
+def run(name, batch, passes, iters, warmup, tune=True, roles=False):
     C, H, W, Ko, R, s, p = SHAPES[name]
     Cp, Kp = K.pad_channels(C), K.pad_channels(Ko)
     P, Q = (H + 2 * p - R) // s + 1, (W + 2 * p - R) // s + 1
@@ -69,9 +72,20 @@ def run(name, batch, passes, iters, warmup, tune=True):
             continue
         if name_ == "dgrad" and s != 1:
             continue
+        if roles:
+            fn()
+            K.gemm_role_profile()      # clear: what the tuning and the first launch left
         ms = time_fn(fn, iters, warmup)
         out[name_ + "_ms"] = round(ms, 4)
         out[name_ + "_tflops"] = round(flops / ms / 1e9, 1)
+        out[name_ + "_of_peak"] = round(flops / ms / 1e9 / PEAK_TFLOPS, 3)
+        if roles:
+            c = K.gemm_role_profile()
+            if c and c[4]:
+                out[name_ + "_waiting_pct"] = {"a_producer": round(100.0 * c[0] / c[4], 1),
+                                               "b_producer": round(100.0 * c[1] / c[4], 1),
+                                               "mma_on_operands": round(100.0 * c[2] / c[4], 1),
+                                               "mma_on_epilogue": round(100.0 * c[3] / c[4], 1)}
     torch.cuda.synchronize()
     out["status"] = K.read_status()
     return out
@@ -85,10 +99,14 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-tune", action="store_true", help="take the cost model's tile plans instead of measured ones")
+    ap.add_argument("--roles", action="store_true",
+                    help="also print the share of a CTA's run that each role spends waiting (needs the library built "
+                         "with `python -m rembrandt_b200._build --profile`)")
     args = ap.parse_args(argv)
     names = sorted(SHAPES) if args.shape == "all" else [args.shape]
     for n in names:
-        print(json.dumps(run(n, args.batch, args.passes, args.iters, args.warmup, tune=not args.no_tune)))
+        print(json.dumps(run(n, args.batch, args.passes, args.iters, args.warmup, tune=not args.no_tune,
+                             roles=args.roles)))
 
 
 if __name__ == "__main__":

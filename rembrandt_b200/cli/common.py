@@ -79,6 +79,10 @@ def init_distributed(device: str):
         if device == "cuda":
             local = int(os.environ.get("LOCAL_RANK", "0"))
             torch.cuda.set_device(local)
+            if os.environ.get("RB_NUMA_BIND", "1") == "1":
+                # host threads (loader, pinned staging memory) stay on the NUMA node of this rank's GPU
+                from ..utils.numa import bind_to_gpu_node
+                bind_to_gpu_node(local)
             dist.init_process_group("nccl", device_id=torch.device("cuda", local))
         else:
             dist.init_process_group("gloo")

@@ -159,7 +159,9 @@ __device__ __forceinline__ long long shard_len(long long n, int world) {
 
 __global__ void __launch_bounds__(AR_THREADS, 6) ar_push_kernel(const __grid_constant__ ArSgdArgs a) {
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
-  const int peers = a.world - 1;
+  // one-shot buckets: every rank reduces the whole bucket, and all of them must arrive at the same bits, so the
+  // reducer sums the staged copies of ALL ranks in rank order -- the own copy is staged too (a local store)
+  const int peers = a.one_shot ? a.world : a.world - 1;
   const long long per = a.one_shot ? a.n : shard_len(a.n, a.world);
   const uint32_t per4 = (uint32_t)(per / 4);
   const uint32_t total4 = per4 * (uint32_t)peers;
@@ -261,13 +263,23 @@ __global__ void __launch_bounds__(AR_THREADS, 6) allreduce_sgd_kernel(const __gr
           const int u = (peers <= 3) ? sl / 4 : 0, po = (peers <= 3) ? (sl & 3) : sl;
           const long long i = base + (long long)u * gthreads * 4 + tid4;
           t[sl] = zero;
-          if (po < peers && i < s1) {
+          if (a.one_shot) {
+            // slot = absolute rank (the own staged copy among them): the same operands in the same tree everywhere
+            if (po < a.world && i < s1) t[sl] = ld_f4(stage + (long long)po * per + (i - s0));
+          } else if (po < peers && i < s1) {
             int peer = a.rank + 1 + po;
             if (peer >= a.world) peer -= a.world;
             t[sl] = ld_f4(stage + (long long)peer * per + (i - s0));
           }
         }
-        if (peers <= 3) {
+        if (a.one_shot) {
+          if (peers <= 3) {
+            ga[0] = add4(add4(t[0], t[1]), add4(t[2], t[3]));
+            ga[1] = add4(add4(t[4], t[5]), add4(t[6], t[7]));
+          } else {
+            ga[0] = add4(add4(add4(t[0], t[1]), add4(t[2], t[3])), add4(add4(t[4], t[5]), add4(t[6], t[7])));
+          }
+        } else if (peers <= 3) {
           ga[0] = add4(ga[0], add4(add4(t[0], t[1]), t[2]));
           ga[1] = add4(ga[1], add4(add4(t[4], t[5]), t[6]));
         } else {
@@ -381,7 +393,9 @@ struct MixArgs {
 __global__ void __launch_bounds__(512) publish_kernel(const __grid_constant__ MixArgs a) {
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(a.epoch_ptr) + 1u;
   int ok = 1;
-  if (epoch > 2u && threadIdx.x < a.world && threadIdx.x != a.rank)
+  // (only the lock-step form waits: an asynchronous publisher never waits for a peer; a puller that is two whole
+  // exchanges late may then read a snapshot while it is being replaced, and mixes values of two consecutive ones)
+  if (a.wait_peer && epoch > 2u && threadIdx.x < a.world && threadIdx.x != a.rank)
     ok = wait_epoch(flag_at(a.flags[a.rank], a.slot, 1, threadIdx.x), epoch - 2u, wait_limit(a.wait_ns)) ? 1 : 0;
   ok = __syncthreads_and(ok);
   if (!ok && threadIdx.x == 0) atomicOr(a.status, RB_STATUS_PEER_TIMEOUT);

@@ -76,6 +76,26 @@ __device__ __forceinline__ bool ctl_wait(SharedCtl* ctl, uint64_t* bar, uint32_t
   return false;
 }
 
+// Role profile (built only with -DRB_GEMM_PROFILE, see `python -m rembrandt_b200._build --profile`): cycles that the
+// roles of ONE CTA (block 3) spend waiting, summed over launches -- [0] A producer on a free stage, [1] B producer on
+// a free stage, [2] MMA issuer on a filled stage, [3] MMA issuer on a drained accumulator, [4] the CTA's whole run.
+// A role that hardly waits is the one the others wait for. `rb_gemm_role_profile` reads and clears the counters.
+#ifdef RB_GEMM_PROFILE
+__device__ unsigned long long g_role_cycles[8];
+__device__ __forceinline__ bool ctl_wait_role(SharedCtl* ctl, uint64_t* bar, uint32_t parity, unsigned int* status,
+                                              int slot) {
+  const long long t0 = clock64();
+  const bool r = ctl_wait(ctl, bar, parity, status);
+  if (blockIdx.x == 3) atomicAdd(&g_role_cycles[slot], (unsigned long long)(clock64() - t0));
+  return r;
+}
+#else
+__device__ __forceinline__ bool ctl_wait_role(SharedCtl* ctl, uint64_t* bar, uint32_t parity, unsigned int* status,
+                                              int) {
+  return ctl_wait(ctl, bar, parity, status);
+}
+#endif
+
 // base pixel (w, h, n) of output position `pix` for the im2col tensor maps
 __device__ __forceinline__ void pixel_coords(const GemmTcParams& p, int pix, int& w, int& h, int& n) {
   const int pq = p.cv_P * p.cv_Q;
@@ -193,7 +213,7 @@ template <int KK, int MT, bool WIDE>
 __device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, unsigned int* status, uint32_t d_tmem,
                                            int kb0, int kb1, int& s, uint32_t& ph) {
   for (int kb = kb0; kb < kb1; ++kb) {
-    if (!ctl_wait(ctl, &ctl->full[s], ph, status)) return false;
+    if (!ctl_wait_role(ctl, &ctl->full[s], ph, status, 2)) return false;
     tc_fence_after();
     const uint32_t sa = c.ring_u32 + (uint32_t)s * c.stage_bytes;
     const uint32_t sb = c.b_resident ? c.tiles_u32 + (uint32_t)kb * c.b_bytes : sa + c.b_in_stage;
@@ -210,6 +230,9 @@ __device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, un
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
+#ifdef RB_GEMM_PROFILE
+  const long long t_kernel0 = clock64();
+#endif
   extern __shared__ uint8_t smem_raw[];
   // tiles start on a 1024-byte boundary (swizzle atoms); control block follows the tiles
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -367,7 +390,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         for (int kb = kb0; kb < kb1; ++kb) {
           int w_ok = 1;
           if (lane == 0) {
-            w_ok = ctl_wait(ctl, &ctl->empty[s], ph ^ 1u, p.status) ? 1 : 0;
+            w_ok = ctl_wait_role(ctl, &ctl->empty[s], ph ^ 1u, p.status, is_a ? 0 : 1) ? 1 : 0;
             if (w_ok) mbar_expect_tx(&ctl->full[s], my_tx);
           }
           w_ok = __shfl_sync(0xffffffffu, w_ok, 0);
@@ -539,7 +562,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       const int issue_kind = (kk_steps == 4 ? 0 : 3) + (idesc2 ? 2 : (mt == 2 ? 1 : 0));
       for (int work = blockIdx.x; work < num_work && ok && !halo; work += gridDim.x) {
         const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
-        if (!ctl_wait(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status)) { ok = false; break; }
+        if (!ctl_wait_role(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * set_cols;
         switch (issue_kind) {
@@ -756,6 +779,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 
   tc_fence_before();
   __syncthreads();
+#ifdef RB_GEMM_PROFILE
+  if (blockIdx.x == 3 && threadIdx.x == 0) atomicAdd(&g_role_cycles[4], (unsigned long long)(clock64() - t_kernel0));
+#endif
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -1649,6 +1675,20 @@ int rb_gemm_clear_plans() {
   g_plan_cache.clear();
   g_bn_cache.clear();
   return 0;
+}
+
+// out[0..7]: the role-profile counters (all zero in a build without -DRB_GEMM_PROFILE, returns 1 then); cleared on read.
+int rb_gemm_role_profile(unsigned long long* out) {
+  for (int i = 0; i < 8; ++i) out[i] = 0ull;
+#ifdef RB_GEMM_PROFILE
+  cudaDeviceSynchronize();
+  if (cudaMemcpyFromSymbol(out, g_role_cycles, sizeof(unsigned long long) * 8) != cudaSuccess) return -1;
+  const unsigned long long zeros[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (cudaMemcpyToSymbol(g_role_cycles, zeros, sizeof(zeros)) != cudaSuccess) return -1;
+  return 0;
+#else
+  return 1;
+#endif
 }
 
 int rb_num_sms() {

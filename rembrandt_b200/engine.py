@@ -58,6 +58,9 @@ class StepEngine:
             self._stats_host = [torch.zeros(2, dtype=torch.float32).pin_memory() for _ in range(2)]
             self._stats_ready = [torch.cuda.Event() for _ in range(2)]
             self._lr_dev = None
+            # optional timing of the host-to-device copies (`time_h2d(True)`): pairs of events around each copy
+            self._h2d_timing = False
+            self._h2d_events = []
             if hasattr(self.comm, "attach"):
                 self.comm.attach(self)
 
@@ -79,13 +82,33 @@ class StepEngine:
         s = self._slot
         with torch.cuda.stream(self.copy_stream):
             self.copy_stream.wait_event(self._consumed[s])
+            if self._h2d_timing:
+                t0 = torch.cuda.Event(enable_timing=True)
+                t0.record(self.copy_stream)
             self._stage_imgs[s].copy_(images_u8.reshape(self._stage_imgs[s].shape), non_blocking=True)
             self._stage_lbls[s].copy_(labels.reshape(-1), non_blocking=True)
             if shapes is not None:
                 self._stage_shapes[s].copy_(shapes.reshape(self._stage_shapes[s].shape).int(), non_blocking=True)
             self._copy_done[s].record(self.copy_stream)
+            if self._h2d_timing:
+                t1 = torch.cuda.Event(enable_timing=True)
+                t1.record(self.copy_stream)
+                self._h2d_events.append((t0, t1))
         self._pending = s
         self._slot ^= 1
+
+    def time_h2d(self, on: bool) -> None:
+        """Start (and clear) or stop the device timing of the staging copies that `feed` issues."""
+        self._h2d_timing = bool(on) and self.is_cuda
+        if on:
+            self._h2d_events = []
+
+    def h2d_ms(self) -> Optional[float]:
+        """Mean device time of one staging copy (images + labels) since `time_h2d(True)`; None without samples. The
+        copy stream must have finished them (`synchronize`)."""
+        if not self._h2d_events:
+            return None
+        return sum(a.elapsed_time(b) for a, b in self._h2d_events) / len(self._h2d_events)
 
     def h2d_bytes_per_step(self) -> int:
         if not self.is_cuda:

@@ -106,6 +106,16 @@ class gemm_tuning:
         return False
 
 
+def gemm_role_profile():
+    """Cycles the roles of one CTA of the tensor-core kernel spent waiting since the last call ([A producer, B
+    producer, MMA issuer on operands, MMA issuer on the epilogue, whole run, ...]); None unless the library was built
+    with -DRB_GEMM_PROFILE."""
+    import ctypes as C_
+    buf = (C_.c_ulonglong * 8)()
+    rc = _native.cuda().rb_gemm_role_profile(C_.cast(buf, C_.c_void_p))
+    return list(buf) if rc == 0 else None
+
+
 def gemm_clear_plans() -> None:
     _native.cuda().rb_gemm_clear_plans()
 

@@ -96,7 +96,7 @@ def test_tool_resumes_from_the_latest_state_or_a_given_iteration(tmp_path):
 
 @pytest.mark.parametrize("tool", ["train_mnist", "dist_train_mnist", "train_cifar10", "train_imagenet",
                                   "dist_train_imagenet", "train_gogod", "run_rembrandt", "bench_conv", "bench_gemm",
-                                  "bench_allreduce", "bench_link", "bench_kernels", "bench_ops", "bench_loader", "data_tools",
+                                  "bench_allreduce", "bench_link", "bench_kernels", "bench_ops", "bench_straggler", "bench_loader", "data_tools",
                                   "test_dist"])
 def test_every_tool_imports_and_prints_its_help(tool, capsys):
     import importlib

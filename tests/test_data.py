@@ -414,3 +414,21 @@ def test_jpeg_records_decode_through_the_database_shards(tmp_path):
             wl.append(struct.pack("<i", 40 + i))
     rows = list(VarrayDbShard(str(tmp_path / "d"), str(tmp_path / "l"), codec))
     assert [lab for _, lab in rows] == [40, 41] and np.array_equal(rows[1][0], g3)
+
+
+def test_numa_binding_reads_the_topology_from_sysfs(tmp_path):
+    """The rank-to-NUMA-node binding parses a (fake) sysfs tree; nothing is changed when the topology is unreadable."""
+    import os
+    from rembrandt_b200.utils import numa
+    d = str(tmp_path)
+    os.makedirs(f"{d}/bus/pci/devices/0000:1b:00.0")
+    open(f"{d}/bus/pci/devices/0000:1b:00.0/numa_node", "w").write("1\n")
+    os.makedirs(f"{d}/devices/system/node/node1")
+    open(f"{d}/devices/system/node/node1/cpulist", "w").write("0-1,3\n")
+    assert numa.numa_node_of_bus("0000:1B:00.0", d) == 1
+    assert numa.node_cpus(1, d) == [0, 1, 3]
+    assert numa._parse_cpulist("0-3,8,10-11") == [0, 1, 2, 3, 8, 10, 11]
+    assert numa.numa_node_of_bus("0000:ff:00.0", d) is None and numa.node_cpus(7, d) == []
+    open(f"{d}/bus/pci/devices/0000:1b:00.0/numa_node", "w").write("-1\n")      # single-node machine
+    assert numa.numa_node_of_bus("0000:1b:00.0", d) is None
+    assert numa.bind_to_gpu_node(0, sysfs=str(tmp_path / "absent")) is None

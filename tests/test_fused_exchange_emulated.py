@@ -148,8 +148,8 @@ class World:
         per = n if a.one_shot else _shard_len(n, W)
         g = self._f32(a.grads[r])[a.off:]
         for p in range(W):
-            if p == r:
-                continue
+            if p == r and not a.one_shot:
+                continue            # one-shot buckets stage the own copy too: every rank sums the same slots
             si = 0 if a.one_shot else p * per
             ln = min(per, n - si)
             if ln <= 0:
@@ -166,11 +166,16 @@ class World:
         if s1 <= s0:
             return
         grads = self._f32(a.grads[r])
-        g = grads[a.off + s0: a.off + s1].clone()
         stage = self._f32(a.stage[r])[a.stage_off:]
-        for k in range(1, W):
-            peer = (r + k) % W
-            g += stage[peer * per: peer * per + (s1 - s0)]
+        if a.one_shot:
+            g = torch.zeros(s1 - s0)
+            for src in range(W):        # rank order, the own staged copy among them
+                g += stage[src * per: src * per + (s1 - s0)]
+        else:
+            g = grads[a.off + s0: a.off + s1].clone()
+            for k in range(1, W):
+                peer = (r + k) % W
+                g += stage[peer * per: peer * per + (s1 - s0)]
         lo, hi = a.off + s0, a.off + s1
         if a.op == 1:
             for p in range(W):
