@@ -26,9 +26,14 @@ OBJDIR = CSRC / "build"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
-    "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
+    "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
 ]
+# --use_fast_math (approximate division / square root, flush-to-zero) only where no statistic, normaliser or loss is
+# computed: the tensor-core kernel's epilogue, pooling, data movement. Softmax / cross-entropy, LRN, batch-norm, the
+# optimizer and the exchange kernels that apply it are compiled with IEEE division and square root; where they call
+# an intrinsic such as __expf they do so explicitly.
+PRECISE_SOURCES = {"softmax_ce.cu", "lrn.cu", "bn.cu", "sgd_fused.cu", "comm_p2p.cu"}
 CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-pthread"]
 
 
@@ -68,7 +73,9 @@ def build_cuda(force: bool = False, verbose: bool = False, defines: tuple = ()) 
         obj = OBJDIR / (src.stem + ".o")
         objs.append(obj)
         if force or _newer(src, obj, headers):
-            cmd = [nvcc, *NVCC_FLAGS, *(f"-D{d}" for d in defines), "-I", str(CSRC), "-c", str(src), "-o", str(obj)]
+            fast = [] if src.name in PRECISE_SOURCES else ["--use_fast_math"]
+            cmd = [nvcc, *NVCC_FLAGS, *fast, *(f"-D{d}" for d in defines), "-I", str(CSRC), "-c", str(src), "-o",
+                   str(obj)]
             if verbose:
                 cmd[1:1] = ["-Xptxas", "-v"]
             jobs.append(cmd)

@@ -178,7 +178,7 @@ __device__ __forceinline__ void load_b(const GemmTcParams& p, uint8_t* sb, uint6
 // The one issuing thread's instruction stream is what bounds the kernel when operands arrive in time (a single extra
 // branch per MMA in this loop cost 44 % on a weight-grad launch), so nothing here is computed per MMA that can be
 // computed per k-block, and only the first MMA into an accumulator carries a predicate.
-template <int KK, int MT, bool WIDE>
+template <int KK, int MT, bool WIDE, bool PAIR>
 __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t acc_stride, uint64_t da, uint64_t a_sub,
                                              uint64_t db, uint32_t a_adv, uint32_t b_adv, uint32_t idesc,
                                              uint32_t idesc2, uint64_t b_wide_off, bool fresh) {
@@ -189,7 +189,10 @@ __device__ __forceinline__ void issue_kblock(uint32_t d_tmem, uint32_t acc_strid
 #pragma unroll
     for (int kk = 0; kk < KK; ++kk) {
       const uint64_t ak = daj + (uint64_t)(a_adv * kk), bk_ = db + (uint64_t)(b_adv * kk);
-      if (kk == 0) {
+      if (PAIR) {
+        if (kk == 0) tc_mma2_f16(dj, ak, bk_, idesc, fresh ? 0u : 1u);
+        else tc_mma2_f16_acc(dj, ak, bk_, idesc);
+      } else if (kk == 0) {
         tc_mma_f16(dj, ak, bk_, idesc, fresh ? 0u : 1u);
         if (WIDE) tc_mma_f16(dj + 256u, ak, bk_ + b_wide_off, idesc2, fresh ? 0u : 1u);
       } else {
@@ -209,7 +212,7 @@ struct IssueCtx {
 };
 
 // k-blocks [kb0, kb1) of one work item; returns false after a wait that ran out.
-template <int KK, int MT, bool WIDE>
+template <int KK, int MT, bool WIDE, bool PAIR>
 __device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, unsigned int* status, uint32_t d_tmem,
                                            int kb0, int kb1, int& s, uint32_t& ph) {
   for (int kb = kb0; kb < kb1; ++kb) {
@@ -221,9 +224,11 @@ __device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, un
     // ends below 256 KB)
     const uint64_t da = c.a_desc0 | (uint64_t)((sa >> 4) & 0x3FFFu);
     const uint64_t db = c.b_desc0 | (uint64_t)((sb >> 4) & 0x3FFFu);
-    issue_kblock<KK, MT, WIDE>(d_tmem, c.acc_stride, da, c.a_sub, db, c.a_adv, c.b_adv, c.idesc, c.idesc2,
-                               c.b_wide_off, kb == kb0);
-    tc_commit(&ctl->empty[s]);  // stage is free once these MMAs have read it
+    issue_kblock<KK, MT, WIDE, PAIR>(d_tmem, c.acc_stride, da, c.a_sub, db, c.a_adv, c.b_adv, c.idesc, c.idesc2,
+                                     c.b_wide_off, kb == kb0);
+    // stage is free once these MMAs have read it (in both CTAs of a pair)
+    if (PAIR) tc_commit2_both(&ctl->empty[s]);
+    else tc_commit(&ctl->empty[s]);
     if (++s == c.stages) { s = 0; ph ^= 1u; }
   }
   return true;
@@ -242,6 +247,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // CTA pairs: rank of this CTA in its pair, and the persistent loop runs over pairs
+  const bool pair = p.pair != 0;
+  const uint32_t cta_rank = pair ? cluster_ctarank() : 0u;
+  const int cta_id = pair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int cta_step = pair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+
   const int mt = p.mt;
   const int a_bytes = BM * p.bk * 2;            // one 128-row sub-tile
   const int b_bytes = p.bn_load * p.bk * 2;
@@ -253,9 +264,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   const bool halo = p.a_mode == A_HALO_K;
   const bool box = p.a_mode == A_BOX_K;
   const int bx_groups = box ? (p.cv_P + mt * p.bx_rows - 1) / (mt * p.bx_rows) : 1;   // work items per image
-  const int m_items = halo  ? (p.M / (p.cv_P * p.cv_Q)) * p.hl_groups
+  const int m_units = halo  ? (p.M / (p.cv_P * p.cv_Q)) * p.hl_groups
                       : box ? (p.M / (p.cv_P * p.cv_Q)) * bx_groups
                             : (p.M + BM * mt - 1) / (BM * mt);
+  const int m_items = pair ? (m_units + 1) >> 1 : m_units;   // a pair's item is two CTA-sized units
   const int n_tiles = p.n_tiles;
   // whole items first, then the parts of the cut items of the last wave (tail cut; never in halo mode)
   const int direct = m_items * n_tiles - p.tail_items;
@@ -267,12 +279,13 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
-      mbar_init(&ctl->full[s], (halo || p.b_resident) ? 1 : 2);   // one arrival per producer warp that fills it
+      // one arrival per producer warp that fills it (a pair: both CTAs' producers arrive on the leader's barrier)
+      mbar_init(&ctl->full[s], pair ? 4 : ((halo || p.b_resident) ? 1 : 2));
       mbar_init(&ctl->empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&ctl->acc_full[a], 1);
-      mbar_init(&ctl->acc_empty[a], EPI_WARPS);
+      mbar_init(&ctl->acc_empty[a], pair ? 2 * EPI_WARPS : EPI_WARPS);
     }
     mbar_init(&ctl->b_full, 1);
     for (int a = 0; a < 2; ++a) {
@@ -289,11 +302,17 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     if (p.tail_items > 0) tma_prefetch_desc(&p.tm_ws);
   }
   if (warp == 1) {
-    tmem_alloc(&ctl->tmem_base, 512);
-    tmem_relinquish();
+    if (pair) {
+      tmem_alloc2(&ctl->tmem_base, 512);   // both CTAs of the pair execute this; each gets the same address
+      tmem_relinquish2();
+    } else {
+      tmem_alloc(&ctl->tmem_base, 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (pair) cluster_sync_all();   // the peer's barriers are initialised before anything of ours signals them
   tc_fence_after();
   const uint32_t tmem_base = ctl->tmem_base;
 
@@ -314,7 +333,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       uint64_t* fullb = is_a ? ctl->a_full : ctl->full;
       uint64_t* emptyb = is_a ? ctl->a_empty : ctl->empty;
       if (lane == 0) {
-        for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        for (int work = cta_id; work < num_work && ok; work += cta_step) {
           const int tn = work / m_items;
           const int tm = work - tn * m_items;
           const int n_img = tm / p.hl_groups;
@@ -359,12 +378,15 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       else if (p.b_mode == B_TILED_MN) nload = p.bn_load / 64;
       else if (p.b_mode == B_IM2COL_MN) nload = p.wg_taps > 1 ? p.wg_taps * (p.wg_cw / 64) : p.bn_load / 64;
       else nload = b_split;
+      // a pair counts every load on the leader's `full` barriers
+      const uint32_t full0_leader = pair ? mapa_shared(smem_u32(&ctl->full[0]), 0u) : 0u;
       const uint32_t my_tx = !is_a ? (uint32_t)b_bytes
                              : box ? (uint32_t)(mt * p.bx_rows * p.cv_Q * p.bk * 2)   // the boxes bring whole rows only
                                    : (uint32_t)(mt * a_bytes);
-      for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+      for (int work = cta_id; work < num_work && ok; work += cta_step) {
         const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
-        const int tn = it.tn, tm = it.tm, kb0 = it.kb0, kb1 = it.kb1;
+        const int tn = it.tn, kb0 = it.kb0, kb1 = it.kb1;
+        const int tm = pair ? it.tm * 2 + (int)cta_rank : it.tm;
         const int m0 = tm * BM * mt;
         // geometry that is fixed for the work item (every lane keeps what its own load needs)
         // sub-tile of this lane's A load, and which of the sub-tile's boxes it is
@@ -378,7 +400,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           a_h = ((tm - a_n * bx_groups) * mt + lane) * p.bx_rows;
         }
         int b_tap = 0, b_c0 = 0;
-        const int n0 = tn * p.bn;
+        const int n0 = tn * p.bn + (pair ? (int)cta_rank * p.bn_load : 0);   // a pair's CTA loads its half of the rows
         if (p.b_mode == B_IM2COL_MN) {
           if (p.wg_taps > 1) {
             b_tap = tn * p.wg_taps;
@@ -391,14 +413,39 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           int w_ok = 1;
           if (lane == 0) {
             w_ok = ctl_wait_role(ctl, &ctl->empty[s], ph ^ 1u, p.status, is_a ? 0 : 1) ? 1 : 0;
-            if (w_ok) mbar_expect_tx(&ctl->full[s], my_tx);
+            if (w_ok) {
+              if (pair) mbar_expect_tx_cluster(full0_leader + (uint32_t)s * 8u, my_tx);
+              else mbar_expect_tx(&ctl->full[s], my_tx);
+            }
           }
           w_ok = __shfl_sync(0xffffffffu, w_ok, 0);
           if (!w_ok) { ok = false; break; }
           uint8_t* sa = ring + s * stage_bytes;
           uint8_t* sb = sa + mt * a_bytes;
           uint64_t* bar = &ctl->full[s];
-          if (lane < nload) {
+          if (pair) {
+            // K-major operands only; the bytes are counted on the leader's barrier of this stage
+            const uint32_t bar2 = full0_leader + (uint32_t)s * 8u;
+            if (lane < nload) {
+              const int tap = p.cv_cchunks > 0 ? kb / p.cv_cchunks : 0;   // filter tap (convolution operands)
+              if (is_a) {
+                uint8_t* saj = sa + aj * a_bytes + aq * a_rows * p.bk * 2;
+                if (p.a_mode == A_TILED_K) {
+                  tma2_load_2d(saj, &p.tm_a, bar2, kb * p.bk, m0 + aj * BM + aq * a_rows);
+                } else {   // A_IM2COL_K
+                  const int cc = kb - tap * p.cv_cchunks;
+                  const int r = tap / p.cv_S;
+                  const int sx = tap - r * p.cv_S;
+                  tma2_load_im2col_4d(saj, &p.tm_a, bar2, cc * p.bk, a_w, a_h, a_n, (uint16_t)sx, (uint16_t)r);
+                }
+              } else {
+                const int b_rows = p.bn_load / b_split;
+                uint8_t* sbq = sb + lane * b_rows * p.bk * 2;
+                if (p.b_mode == B_TILED_K) tma2_load_2d(sbq, &p.tm_b, bar2, kb * p.bk, n0 + lane * b_rows);
+                else tma2_load_3d(sbq, &p.tm_b, bar2, (kb - tap * p.cv_cchunks) * p.bk, tap, n0 + lane * b_rows);
+              }
+            }
+          } else if (lane < nload) {
             if (is_a) {
               uint8_t* saj = sa + aj * a_bytes + aq * a_rows * p.bk * 2;
               const int mj = m0 + aj * BM + aq * a_rows;
@@ -454,7 +501,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
           if (++s == stages) { s = 0; ph ^= 1u; }
         }
       }
-      if (!ok && lane == 0) {
+      if (!ok && lane == 0 && pair && cta_rank != 0) {
+        // this CTA's copies complete on the leader's barriers, which cannot be waited on from here: give them time
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+      } else if (!ok && lane == 0) {
         // drain: wait (bounded) until the copies already issued have landed
         const int back = min(issued, stages);
         for (int i = 0; i < back; ++i) {
@@ -473,11 +524,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    if (lane == 0 && cta_rank == 0) {   // of a pair, only the leader issues
       const bool a_mn = (p.a_mode == A_TILED_MN);
       const bool b_mn = (p.b_mode == B_TILED_MN || p.b_mode == B_IM2COL_MN);
       // a tile wider than 256 columns is two MMAs side by side (256 + the rest) that share the A descriptor
-      const uint32_t idesc = make_idesc_bf16(BM, (uint32_t)min(p.bn, 256), a_mn ? 1u : 0u, b_mn ? 1u : 0u);
+      const uint32_t idesc = make_idesc_bf16(pair ? 2 * BM : BM, (uint32_t)min(p.bn, 256), a_mn ? 1u : 0u, b_mn ? 1u : 0u);
       const uint32_t idesc2 = p.bn > 256 ? make_idesc_bf16(BM, (uint32_t)(p.bn - 256), a_mn ? 1u : 0u, b_mn ? 1u : 0u) : 0u;
       const uint64_t b_wide_off = (uint64_t)((256u * (uint32_t)p.bk * 2u) >> 4);   // K-major B: 256 rows further down
       // K-major: rows of bk*2 bytes, 8-row atoms -> SBO = 8*bk*2; swizzle 128B (bk=64) or 64B (bk=32)
@@ -504,7 +555,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         int bs = 0, as = 0;
         uint32_t bph = 0, aph = 0;
         const uint32_t row_bytes = (uint32_t)p.bk * 2u;
-        for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+        for (int work = cta_id; work < num_work && ok; work += cta_step) {
           if (!ctl_wait(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)acc * set_cols;
@@ -559,22 +610,28 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       ic.b_wide_off = b_wide_off;
       ic.stages = stages;
       ic.b_resident = p.b_resident;
-      const int issue_kind = (kk_steps == 4 ? 0 : 3) + (idesc2 ? 2 : (mt == 2 ? 1 : 0));
-      for (int work = blockIdx.x; work < num_work && ok && !halo; work += gridDim.x) {
+      const int issue_kind = (kk_steps == 4 ? 0 : 3) + (idesc2 ? 2 : (mt == 2 ? 1 : 0)) + (pair ? 6 : 0);
+      for (int work = cta_id; work < num_work && ok && !halo; work += cta_step) {
         const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
         if (!ctl_wait_role(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * set_cols;
         switch (issue_kind) {
-          case 0: ok = issue_item<4, 1, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 1: ok = issue_item<4, 2, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 2: ok = issue_item<4, 1, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 3: ok = issue_item<2, 1, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 4: ok = issue_item<2, 2, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          default: ok = issue_item<2, 1, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 0: ok = issue_item<4, 1, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 1: ok = issue_item<4, 2, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 2: ok = issue_item<4, 1, true, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 3: ok = issue_item<2, 1, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 4: ok = issue_item<2, 2, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 5: ok = issue_item<2, 1, true, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 6: ok = issue_item<4, 1, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 7: ok = issue_item<4, 2, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 9: ok = issue_item<2, 1, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 10: ok = issue_item<2, 2, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          default: ok = false; break;   // no wide tiles for pairs (refused on the host)
         }
         if (!ok) break;
-        tc_commit(&ctl->acc_full[acc]);
+        if (pair) tc_commit2_both(&ctl->acc_full[acc]);
+        else tc_commit(&ctl->acc_full[acc]);
         if (++acc == p.acc_bufs) { acc = 0; acc_ph ^= 1u; }
       }
     }
@@ -591,9 +648,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
     int acc = 0;
     uint32_t acc_ph = 0;
     bool ok = true;
-    for (int work = blockIdx.x; work < num_work && ok; work += gridDim.x) {
+    for (int work = cta_id; work < num_work && ok; work += cta_step) {
       const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
-      const int tn = it.tn, tm = it.tm;
+      const int tn = it.tn;
+      const int tm = pair ? it.tm * 2 + (int)cta_rank : it.tm;
       const bool tail = it.tail >= 0;
       if (!ctl_wait(ctl, &ctl->acc_full[acc], acc_ph, p.status)) { ok = false; break; }
       tc_fence_after();
@@ -771,7 +829,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->acc_empty[acc]);
+      if (lane == 0) {
+        // the accumulators of both CTAs of a pair are refilled by the leader: it waits for both epilogues
+        if (pair) mbar_arrive_cluster(mapa_shared(smem_u32(&ctl->acc_empty[acc]), 0u));
+        else mbar_arrive(&ctl->acc_empty[acc]);
+      }
       if (++acc == p.acc_bufs) { acc = 0; acc_ph ^= 1u; }
     }
     if (lane == 0) tma_store_wait_all<0>();   // every output store has completed before the CTA exits
@@ -782,9 +844,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
 #ifdef RB_GEMM_PROFILE
   if (blockIdx.x == 3 && threadIdx.x == 0) atomicAdd(&g_role_cycles[4], (unsigned long long)(clock64() - t_kernel0));
 #endif
+  // a pair frees its TMEM together, after both epilogues have read it and nothing signals a peer's barrier any more
+  if (pair) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    if (pair) tmem_dealloc2(tmem_base, 512);
+    else tmem_dealloc(tmem_base, 512);
   }
 }
 

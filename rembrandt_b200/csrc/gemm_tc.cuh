@@ -85,6 +85,12 @@ struct alignas(64) GemmTcParams {
   long long ws_bytes;
   int tail_items;      // 0 = no tail cut
   int tail_split;
+  // CTA pairs (tcgen05 cta_group::2; K-major operands only): the kernel runs as clusters of two CTAs. A work item
+  // is 2 * mt sub-tiles of 128 rows, CTA r of the pair owns sub-tiles (2 * tm + r) * mt .. + mt: it loads their A
+  // rows, rows [r * bn_load, (r + 1) * bn_load) of the B tile (bn_load = bn / 2), and runs their epilogue from its
+  // own TMEM. The even CTA issues one 256 x bn x 16 MMA where two CTAs alone would issue two 128 x bn x 16 ones,
+  // and each SM reads only half of B from its shared memory.
+  int pair;
 };
 
 }  // namespace rb

@@ -183,10 +183,12 @@ class FusedAllreduceSgdComm(AllreduceComm, _P2PBase):
         net = engine.net
         self.net = net
         self.comm_stream = torch.cuda.Stream(net.device, priority=-1)
-        # consecutive buckets alternate between two streams, so that the push of bucket k+1 (NVLink bound) runs
-        # while bucket k is reduced and applied (HBM bound)
+        # One stream: the buckets run one after another beside the backward pass. Alternating them between two
+        # streams (RB_COMM_STREAMS=2: the push of bucket k+1 beside the reduction of bucket k) measured SLOWER on
+        # AlexNet, 2.05 vs 1.94 ms per step on 2 GPUs and 2.09 vs 1.99 ms on 4: the backward pass's GEMMs then share
+        # the SMs with two exchange kernels instead of one, and they are what the step waits for.
         self.comm_streams = [self.comm_stream]
-        if int(os.environ.get("RB_COMM_STREAMS", "2")) > 1:
+        if int(os.environ.get("RB_COMM_STREAMS", "1")) > 1:
             self.comm_streams.append(torch.cuda.Stream(net.device, priority=-1))
         self._done2 = torch.cuda.Event()
         self._ready = torch.cuda.Event()

@@ -117,6 +117,43 @@ def test_alexnet_and_nin_build_and_step():
     assert Net(zoo.alexnet(), 2, device="cpu").params_len == 62378344
 
 
+def _without_dropout(cfg):
+    for op in cfg.hidden_ops:
+        if isinstance(op.cfg, DropoutCfg):
+            op.cfg.drop_ratio = 0.0     # the host path draws its masks from another generator
+    return cfg
+
+
+@pytest.mark.parametrize("model,hw", [("alexnet", 227), ("nin", 224)])
+def test_flagship_gradients_match_the_reference_path_at_full_shapes(model, hw):
+    """Every tile and tail configuration the benchmark shapes use (11x11 stride 4 over the space-to-depth input,
+    5x5 pad 2, 3x3 pad 1, the 1x1 layers and the global pooling head of NIN, 9216x4096 weights) against the fp32
+    host path, whole network, batch 4, per parameter segment."""
+    fn = getattr(zoo, model)
+    g = Net(_without_dropout(fn(scale=1.0 / 73.9)), 4, device="cuda", seed=(11, 12))
+    c = Net(_without_dropout(fn(scale=1.0 / 73.9)), 4, device="cpu", seed=(11, 12))
+    with torch.no_grad():
+        c.params.copy_(g.params16.float().cpu())
+    torch.manual_seed(3)
+    x = torch.randint(0, 256, (4, 3, hw, hw), dtype=torch.uint8)
+    y = torch.randint(0, 1000, (4,))
+    g.load_batch(x.cuda(), y.cuda().int())
+    c.load_batch(x, y)
+    for net in (g, c):
+        net.forward(True)
+        net.backward()
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    gl, cl = g.read_stats()[0], c.read_stats()[0]
+    assert abs(gl - cl) < 2e-2 * abs(cl), (gl, cl)
+    gg, cg = g.grads.cpu(), c.grads
+    for seg in g.segs:
+        a = gg[seg.offset: seg.offset + seg.numel]
+        b = cg[seg.offset: seg.offset + seg.numel]
+        rel = float((a - b).norm() / b.norm().clamp_min(1e-20))
+        assert rel < 0.1, f"{model} {seg.name}: relative error {rel:.4g}"
+
+
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_overlapped_local_update_equals_single_sweep(use_graph):
     """The per-bucket optimizer step launched from inside backward gives the same parameters (up to the
