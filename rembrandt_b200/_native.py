@@ -35,6 +35,8 @@ _CUDA_SIGS = {
     "rb_conv_wgrad_tc": [vp, i32, i32, i32, i32, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp, i32, vp, vp],
     "rb_num_sms": [],
     "rb_gemm_role_profile": [vp],
+    "rb_gemm_last_launch": [vp],
+    "rb_gemm_last_cuda_error": [],
     # conv_direct.cu
     "rb_conv_direct_fwd": [vp, vp, vp, vp] + [i32] * 14 + [vp],
     "rb_conv_direct_dgrad": [vp, vp, vp, vp] + [i32] * 13 + [vp],
@@ -215,7 +217,17 @@ LAUNCH_COUNT = [0]   # launcher calls made through check(); the benchmark report
 def check(rc: int, what: str) -> None:
     LAUNCH_COUNT[0] += 1
     if rc != 0:
-        raise NativeError(f"{what}: native launcher returned {rc}")
+        detail = ""
+        if rc == -4 and _CUDA is not None:
+            code = _CUDA.rb_gemm_last_cuda_error()
+            if code:
+                detail = f" (CUDA error {code})"
+                try:
+                    import torch
+                    detail = f" (CUDA error {code}: {torch.cuda.cudart().cudaGetErrorString(code)})"
+                except Exception:
+                    pass
+        raise NativeError(f"{what}: native launcher returned {rc}{detail}")
 
 
 def ptr(t):

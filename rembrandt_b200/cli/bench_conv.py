@@ -76,6 +76,7 @@ def run(name, batch, passes, iters, warmup, tune=True, roles=False):
             fn()
             K.gemm_role_profile()      # clear: what the tuning and the first launch left
         ms = time_fn(fn, iters, warmup)
+        out[name_ + "_plan"] = K.gemm_last_launch()
         out[name_ + "_ms"] = round(ms, 4)
         out[name_ + "_tflops"] = round(flops / ms / 1e9, 1)
         out[name_ + "_of_peak"] = round(flops / ms / 1e9 / PEAK_TFLOPS, 3)

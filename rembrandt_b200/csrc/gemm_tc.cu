@@ -234,6 +234,9 @@ __device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, un
   return true;
 }
 
+// PAIR: the instantiation that runs as clusters of two CTAs (p.pair != 0). It is a kernel of its own because a
+// kernel that contains cta_group::2 instructions can only be launched with an even cluster size.
+template <bool PAIR>
 __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
 #ifdef RB_GEMM_PROFILE
   const long long t_kernel0 = clock64();
@@ -248,7 +251,7 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   const int lane = threadIdx.x & 31;
 
   // CTA pairs: rank of this CTA in its pair, and the persistent loop runs over pairs
-  const bool pair = p.pair != 0;
+  constexpr bool pair = PAIR;
   const uint32_t cta_rank = pair ? cluster_ctarank() : 0u;
   const int cta_id = pair ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
   const int cta_step = pair ? (int)(gridDim.x >> 1) : (int)gridDim.x;
@@ -610,24 +613,22 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       ic.b_wide_off = b_wide_off;
       ic.stages = stages;
       ic.b_resident = p.b_resident;
-      const int issue_kind = (kk_steps == 4 ? 0 : 3) + (idesc2 ? 2 : (mt == 2 ? 1 : 0)) + (pair ? 6 : 0);
+      const int issue_kind = (kk_steps == 4 ? 0 : 3) + (idesc2 ? 2 : (mt == 2 ? 1 : 0));
       for (int work = cta_id; work < num_work && ok && !halo; work += cta_step) {
         const WorkItem it = decode_work(p, work, m_items, direct, kb_per_split);
         if (!ctl_wait_role(ctl, &ctl->acc_empty[acc], acc_ph ^ 1u, p.status, 3)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * set_cols;
         switch (issue_kind) {
-          case 0: ok = issue_item<4, 1, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 1: ok = issue_item<4, 2, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 2: ok = issue_item<4, 1, true, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 3: ok = issue_item<2, 1, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 4: ok = issue_item<2, 2, false, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 5: ok = issue_item<2, 1, true, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 6: ok = issue_item<4, 1, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 7: ok = issue_item<4, 2, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 9: ok = issue_item<2, 1, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          case 10: ok = issue_item<2, 2, false, true>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
-          default: ok = false; break;   // no wide tiles for pairs (refused on the host)
+          case 0: ok = issue_item<4, 1, false, PAIR>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 1: ok = issue_item<4, 2, false, PAIR>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 3: ok = issue_item<2, 1, false, PAIR>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          case 4: ok = issue_item<2, 2, false, PAIR>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph); break;
+          default:   // one tile wider than 256 columns: never for pairs (refused on the host)
+            if (PAIR) ok = false;
+            else if (issue_kind == 2) ok = issue_item<4, 1, true, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph);
+            else ok = issue_item<2, 1, true, false>(ic, ctl, p.status, d_tmem, it.kb0, it.kb1, s, ph);
+            break;
         }
         if (!ok) break;
         if (pair) tc_commit2_both(&ctl->acc_full[acc]);
@@ -867,6 +868,7 @@ static EncodeTiledFn g_encode_tiled = nullptr;
 static EncodeIm2colFn g_encode_im2col = nullptr;
 static int g_num_sms = 0;
 static int g_driver_version = 0;
+static int g_pair_clusters = 0;   // clusters of two CTAs of the kernel that the device runs at once (0 = none)
 
 static void options_from_env();
 
@@ -886,9 +888,29 @@ static int ensure_driver_entry() {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev);
   cudaDriverGetVersion(&g_driver_version);
-  if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) !=
-      cudaSuccess)
+  if (cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) !=
+          cudaSuccess ||
+      cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES) !=
+          cudaSuccess)
     return -2;
+  {   // how many CTA pairs fit at once: the persistent loop of pair mode runs exactly that many clusters
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)(g_num_sms / 2 * 2));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2;
+    at.val.clusterDim.y = 1;
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int nc = 0;
+    if (cudaOccupancyMaxActiveClusters(&nc, gemm_tc_kernel<true>, &cfg) != cudaSuccess) nc = 0;
+    cudaGetLastError();   // a refused query must not be taken for a failed launch later
+    g_pair_clusters = nc > g_num_sms / 2 ? g_num_sms / 2 : nc;
+  }
   return 0;
 }
 
@@ -978,6 +1000,7 @@ struct GemmOptions {
   int force_tail = -1;       // RB_GEMM_FORCE_TAIL: 0 = never cut the last wave, 1 = whenever feasible
   int force_wide = -1;       // RB_GEMM_FORCE_WIDE: 0 = tiles of at most 256 columns, 1 = one wide tile when N <= 512
   int force_box = -1;        // RB_GEMM_FORCE_BOX: 0 = never load A as tap-shifted boxes, 1 = whenever feasible
+  int force_pair = -1;       // RB_GEMM_FORCE_PAIR: 0 = never run as CTA pairs (cta_group::2), 1 = whenever feasible
   int bk32 = 0;              // RB_GEMM_BK32: keep 32-channel chunks for channel counts such as 96
   int bn_cap = 256;          // RB_GEMM_BN_CAP: upper bound on the tile width chosen by the planner
   int a_split = 1;           // RB_GEMM_A_SPLIT / RB_GEMM_B_SPLIT: TMA boxes per K-major tile
@@ -994,7 +1017,7 @@ static int* option_slot(const char* name) {
   struct { const char* name; int* slot; } table[] = {
       {"force_mt", &g_opt.force_mt}, {"force_resident", &g_opt.force_resident}, {"force_halo", &g_opt.force_halo},
       {"force_taps", &g_opt.force_taps}, {"force_tail", &g_opt.force_tail}, {"force_wide", &g_opt.force_wide},
-      {"force_box", &g_opt.force_box},
+      {"force_box", &g_opt.force_box}, {"force_pair", &g_opt.force_pair},
       {"bk32", &g_opt.bk32}, {"bn_cap", &g_opt.bn_cap}, {"a_split", &g_opt.a_split}, {"b_split", &g_opt.b_split},
       {"autotune", &g_opt.autotune}, {"deterministic", &g_opt.deterministic}};
   for (auto& t : table)
@@ -1004,7 +1027,7 @@ static int* option_slot(const char* name) {
 static void options_from_env() {
   std::call_once(g_opt_once, [] {
     const char* names[] = {"force_mt", "force_resident", "force_halo", "force_taps", "force_tail", "force_wide", "force_box",
-                           "bk32", "bn_cap", "a_split", "b_split", "autotune", "deterministic"};
+                           "force_pair", "bk32", "bn_cap", "a_split", "b_split", "autotune", "deterministic"};
     for (const char* n : names) {
       char env[64] = "RB_GEMM_";
       size_t k = strlen(env);
@@ -1024,8 +1047,18 @@ static void options_from_env() {
 struct Plan {
   int mt, split, resident, tail;   // tail: parts per cut item of the last wave (0 = no cut)
   double cost;
+  int pair = 0;                    // run as CTA pairs (never with resident B or a tail cut)
 };
 
+// CTA pairs need K-major operands loaded by plain or im2col TMA, a tile of at most 256 columns whose halves are whole
+// boxes of the B map (the map's box is bn / b_split rows, so b_split must be even), and more than one pair's rows.
+static bool pair_ok(const GemmTcParams& p) {
+  if (g_opt.force_pair == 0 || g_pair_clusters <= 0) return false;
+  if (p.a_mode != A_TILED_K && p.a_mode != A_IM2COL_K) return false;
+  if (p.b_mode != B_TILED_K && p.b_mode != B_TILED_K3) return false;
+  if (p.bn > 256 || p.bn % 16 != 0 || p.b_split < 2 || p.b_split % 2 != 0) return false;
+  return p.M > 2 * BM;
+}
 // Boxes per tile for K-major operands (each box is issued by its own lane). A box must keep whole 8-row swizzle
 // atoms, start on a 1024-byte boundary in shared memory and have at most 256 rows.
 static int pick_box_split(int sp, int rows, int bk) {
@@ -1033,6 +1066,16 @@ static int pick_box_split(int sp, int rows, int bk) {
   while (rows / sp > 256) sp <<= 1;
   while (sp > 1 && (rows % sp != 0 || (rows / sp) % 8 != 0 || ((rows / sp) * bk * 2) % 1024 != 0)) sp >>= 1;
   return sp < 1 ? 1 : sp;
+}
+
+// Boxes per B tile such that half a tile is a whole number of boxes whenever the shape allows pairs.
+static int pairable_b_split(int bn, int bk) {
+  int sp = pick_box_split(g_opt.b_split, bn, bk);
+  if (g_opt.force_pair != 0 && sp % 2 != 0 && bn <= 256) {
+    const int sp2 = pick_box_split(sp * 2, bn, bk);
+    if (sp2 % 2 == 0) sp = sp2;
+  }
+  return sp;
 }
 
 static bool split_ok(int s, int num_kb) { return s == 1 || (s - 1) * ((num_kb + s - 1) / s) < num_kb; }
@@ -1045,7 +1088,8 @@ static int m_items_of(const GemmTcParams& p, int mt) {
     const int groups = (p.cv_P + mt * p.bx_rows - 1) / (mt * p.bx_rows);
     return (p.M / (p.cv_P * p.cv_Q)) * groups;
   }
-  return (p.M + BM * mt - 1) / (BM * mt);
+  const int units = (p.M + BM * mt - 1) / (BM * mt);
+  return p.pair ? (units + 1) / 2 : units;
 }
 
 // Parts per cut item for `items` work items on `sms` SMs (0 = cutting does not pay or is not possible): the last
@@ -1125,6 +1169,12 @@ static int apply_plan(GemmTcParams& p, const Plan& pl) {
   p.mt = pl.mt;
   p.split_k = pl.split;
   p.b_resident = pl.resident;
+  if (pl.pair) {
+    if (!pair_ok(p) || pl.resident || pl.tail || p.M <= BM * pl.mt) return 0;
+    p.pair = 1;
+    p.bn_load = p.bn / 2;      // rows of B per CTA
+    p.b_split = p.b_split / 2;
+  }
   p.acc_stride = acc_stride_for(p.bn);
   p.acc_bufs = (2 * p.mt * p.acc_stride <= 512) ? 2 : 1;
   if (p.mt * p.acc_stride > 512) return 0;
@@ -1158,6 +1208,7 @@ static int apply_plan(GemmTcParams& p, const Plan& pl) {
       return 0;
     work = items - p.tail_items + (long long)p.tail_items * p.tail_split;
   }
+  if (p.pair) return 2 * (int)(work < g_pair_clusters ? work : g_pair_clusters);
   return work < g_num_sms ? (int)work : g_num_sms;
 }
 
@@ -1216,10 +1267,39 @@ __global__ void tail_fix_kernel(const TailFixArgs a) {
   }
 }
 
+// What the most recent launch of this process used (for benchmarks and tests; not synchronised between threads):
+// {sub-tiles per item, reduction split, resident B, tail parts, CTA pairs, tile width, A load mode, stages, grid}.
+static int g_last_launch[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+static int g_last_cuda_error = 0;   // what the runtime answered to the last launch that failed
+
 static int run_plan(GemmTcParams p, const Plan& pl, cudaStream_t stream) {
   const int grid = apply_plan(p, pl);
   if (grid <= 0) return -3;
-  gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
+  const int last[9] = {p.mt, p.split_k, p.b_resident, pl.tail, p.pair, p.bn, p.a_mode, p.stages, grid};
+  memcpy(g_last_launch, last, sizeof(last));
+  if (p.pair) {
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2;
+    at.val.clusterDim.y = 1;
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, p);
+    if (e != cudaSuccess) {
+      g_last_cuda_error = (int)e;
+      cudaGetLastError();
+      return -4;
+    }
+  } else {
+    gemm_tc_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
+  }
   if (p.tail_items > 0) {
     TailFixArgs f;
     f.ws = p.ws;
@@ -1247,7 +1327,9 @@ static int run_plan(GemmTcParams p, const Plan& pl, cudaStream_t stream) {
     if (blocks > 148 * 8) blocks = 148 * 8;
     tail_fix_kernel<<<(int)blocks, 256, 0, stream>>>(f);
   }
-  return cudaGetLastError() == cudaSuccess ? 0 : -4;
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) g_last_cuda_error = (int)e;
+  return e == cudaSuccess ? 0 : -4;
 }
 
 // Shapes whose output is overwritten (bf16 epilogue: forward and data-grad passes) can be tuned by measurement:
@@ -1271,11 +1353,13 @@ static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t st
   cudaEventCreate(&e0);
   cudaEventCreate(&e1);
   float best_ms = 1e30f;
+  for (int pr = 0; pr <= (pair_ok(p) ? 1 : 0); ++pr)
   for (int mt = 1; mt <= 2; ++mt) {
-    for (int res = 0; res <= 1; ++res) {
+    for (int res = 0; res <= (pr ? 0 : 1); ++res) {
       if (res && (!b_is_weights || p.n_tiles != 1)) continue;
-      for (int tail = 0; tail <= 1; ++tail) {
+      for (int tail = 0; tail <= (pr ? 0 : 1); ++tail) {
         Plan cand{mt, 1, res, 0, 0.0};
+        cand.pair = pr;
         if (tail) {
           if (!p.ws || g_opt.force_tail == 0 || g_opt.deterministic) continue;
           cand.tail = tail_parts((long long)m_items_of(p, mt) * p.n_tiles, g_num_sms, p.num_kb);
@@ -1294,7 +1378,9 @@ static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t st
           cudaEventElapsedTime(&t, e0, e1);
           if (rep > 0 && t < ms) ms = t;   // the first run warms the caches
         }
-        if (okc && ms < best_ms) { best_ms = ms; *out = cand; }
+        // pairs are timed after every plain plan and must win by 3 %: measured alone they tie to within 2 % on the
+        // layers tried, and inside a training step (other kernels beside them) the plain plans did better
+        if (okc && ms < best_ms * (pr ? 0.97f : 1.0f)) { best_ms = ms; *out = cand; }
       }
     }
   }
@@ -1305,7 +1391,7 @@ static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t st
 
 static bool tunable(const GemmTcParams& p, cudaStream_t stream) {
   if (!g_tune_mode || !g_opt.autotune || p.epi != EPI_BF16) return false;
-  if (g_opt.force_mt || g_opt.force_resident >= 0) return false;
+  if (g_opt.force_mt || g_opt.force_resident >= 0 || g_opt.force_pair == 1) return false;
   cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
   return cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone;
 }
@@ -1314,13 +1400,27 @@ static int launch(GemmTcParams& p, bool allow_split, int fixed_split, bool b_is_
   if (p.M <= 0 || p.n_tiles <= 0 || p.num_kb <= 0) return 0;
   Plan pl = plan_shape(p, allow_split, fixed_split, b_is_weights);
   if (pl.cost >= 1e299) return -3;
-  const bool forced = g_opt.force_mt || g_opt.force_resident >= 0 || g_opt.force_tail >= 0;
+  bool forced = g_opt.force_mt || g_opt.force_resident >= 0 || g_opt.force_tail >= 0;
+  if (g_opt.force_pair == 1 && pair_ok(p)) {   // pairs wherever they are feasible (tests, experiments)
+    for (int mt = g_opt.force_mt ? g_opt.force_mt : 2; mt >= 1; --mt) {
+      Plan pp{mt, pl.split, 0, 0, 0.0};
+      pp.pair = 1;
+      GemmTcParams q = p;
+      if (apply_plan(q, pp) > 0) {
+        pl = pp;
+        forced = true;
+        break;
+      }
+      if (g_opt.force_mt) break;
+    }
+  }
   if (p.epi == EPI_BF16 && !forced) {
     std::lock_guard<std::mutex> lock(g_plan_mutex);
     auto it = g_plan_cache.find(plan_key(p));
     if (it != g_plan_cache.end()) {
       Plan cached = it->second;
       if (cached.tail && (!p.ws || g_opt.deterministic)) cached.tail = 0;   // tuned with a workspace, launched without
+      if (cached.pair && !pair_ok(p)) cached = pl;
       pl = cached;
     } else if (tunable(p, stream)) {
       Plan best = pl;
@@ -1409,7 +1509,7 @@ int rb_gemm_tc(const void* A, int a_mn, long long lda, const void* B, int b_mn, 
     rc = make_map_2d(&p.tm_b, B, N, K, ldb, 64, p.bk, CU_TENSOR_MAP_SWIZZLE_128B);
   } else {
     p.b_mode = B_TILED_K;
-    p.b_split = pick_box_split(g_opt.b_split, p.bn, p.bk);
+    p.b_split = pairable_b_split(p.bn, p.bk);
     rc = make_map_2d(&p.tm_b, B, K, N, ldb, p.bk, p.bn / p.b_split, ksw);
   }
   if (rc) return rc;
@@ -1537,7 +1637,7 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
         if (rc) return rc;
         const long long work = (long long)N * groups * p.n_tiles;
         const int grid = work < g_num_sms ? (int)work : g_num_sms;
-        gemm_tc_kernel<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
+        gemm_tc_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
         return cudaGetLastError() == cudaSuccess ? 0 : -4;
       }
     }
@@ -1574,7 +1674,7 @@ int rb_conv_fprop_tc(const void* x, int N, int H, int W, int Cp, const void* w, 
     if (e) return e;
     q.bn = q.bn_load = bn;
     q.n_tiles = (n_cols + bn - 1) / bn;
-    q.b_split = pick_box_split(g_opt.b_split, bn, q.bk);
+    q.b_split = pairable_b_split(bn, q.bk);
     return make_map_3d(&q.tm_b, w, Cp, (uint64_t)R * S, Kout, Cp, (uint64_t)R * S * Cp, q.bk, 1, bn / q.b_split, ksw);
   };
   // Candidates beside the default (im2col loads, tiles of at most 256 columns):
@@ -1754,6 +1854,15 @@ int rb_gemm_role_profile(unsigned long long* out) {
 #else
   return 1;
 #endif
+}
+
+// Runtime error code of the last launch that failed (a launcher's return value of -4), 0 if none did.
+int rb_gemm_last_cuda_error() { return g_last_cuda_error; }
+
+// out[0..8]: the tile plan of the most recent launch, see g_last_launch.
+int rb_gemm_last_launch(int* out) {
+  memcpy(out, g_last_launch, sizeof(g_last_launch));
+  return 0;
 }
 
 int rb_num_sms() {

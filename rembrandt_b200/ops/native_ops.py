@@ -116,6 +116,15 @@ def gemm_role_profile():
     return list(buf) if rc == 0 else None
 
 
+def gemm_last_launch() -> dict:
+    """Tile plan of the most recent tensor-core launch of this process (after tuning: the plan that won)."""
+    import ctypes as C_
+    buf = (C_.c_int * 9)()
+    _native.cuda().rb_gemm_last_launch(C_.cast(buf, C_.c_void_p))
+    names = ("sub_tiles", "split_k", "resident_b", "tail_parts", "cta_pairs", "tile_width", "a_mode", "stages", "grid")
+    return dict(zip(names, buf))
+
+
 def gemm_clear_plans() -> None:
     _native.cuda().rb_gemm_clear_plans()
 

@@ -137,11 +137,12 @@ def _conv_setup(N, C, H, W, Ko, R, stride, pad, seed=0):
 
 
 @pytest.fixture(params=["auto", "halo", "mt1", "mt2", "mt1_resident", "mt2_resident", "mt1_taps2", "mt2_taps3", "tail",
-                        "wide", "wide_tail", "box", "box_mt2", "box_tail", "box_wide", "tuned"])
+                        "wide", "wide_tail", "box", "box_mt2", "box_tail", "box_wide", "pair", "pair_mt1", "tuned"])
 def tile_mode(request):
     """Force the kernel's tile-shape planner through each of its modes (two sub-tiles per item, resident B,
     column-shifted halo tiles for stride-1 convolutions, the last wave cut along the reduction, one tile as wide as
-    the layer, tap-shifted box loads of whole output rows, plans chosen by measurement)."""
+    the layer, tap-shifted box loads of whole output rows, CTA pairs issuing 256-row MMAs, plans chosen by
+    measurement)."""
     mode = request.param
     opts = {}
     if mode == "halo":
@@ -157,6 +158,10 @@ def tile_mode(request):
         opts["force_box"] = 1
         if "mt2" in mode:
             opts["force_mt"] = 2
+    if "pair" in mode:
+        opts["force_pair"] = 1
+        if "mt1" in mode:
+            opts["force_mt"] = 1
     if "tail" in mode:
         opts["force_tail"] = 1
     if "wide" in mode:
