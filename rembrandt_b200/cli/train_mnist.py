@@ -4,9 +4,11 @@ from ..models import zoo
 from .common import base_parser, run_training
 
 
-def main(argv=None):
-    ap = base_parser(__doc__, batch=64, lr=0.01, momentum="nesterov", l2=5e-4, iters=300, valid_iters=4,
-                     checkpoint_iters=0)
+def main(argv=None, doc=None, **defaults):
+    """`defaults` override the parser's defaults (the data-parallel tool has its own step size and momentum)."""
+    base = dict(batch=64, lr=0.01, momentum="nesterov", l2=5e-4, iters=300, valid_iters=4, checkpoint_iters=0)
+    base.update(defaults)
+    ap = base_parser(doc or __doc__, **base)
     ap.add_argument("--pad", type=int, default=2, help="conv padding (2 as in the reference tool, 0 for the 800-input fc)")
     ap.add_argument("--model", choices=["lenet", "fc1", "fc2"], default="lenet")
     args = ap.parse_args(argv)

@@ -1093,9 +1093,9 @@ static int m_items_of(const GemmTcParams& p, int mt) {
 }
 
 // Parts per cut item for `items` work items on `sms` SMs (0 = cutting does not pay or is not possible): the last
-// wave must be at most half full, every SM gets at most one part, a part keeps at least four k-blocks.
+// wave must be at most half full, every SM gets at most one part, a part keeps at least four k-blocks. A launch with
+// fewer items than half the SMs (small batches, 7 x 7 layers) is one such wave: all of its items are cut.
 static int tail_parts(long long items, int sms, int num_kb) {
-  if (items <= sms) return 0;
   const int rem = (int)(items % sms);
   if (rem == 0 || rem * 2 > sms) return 0;
   int s = sms / rem;
@@ -1193,7 +1193,7 @@ static int apply_plan(GemmTcParams& p, const Plan& pl) {
   p.tail_split = 0;
   long long work = items * p.split_k;
   if (pl.tail > 0) {
-    if (p.epi != EPI_BF16 || p.split_k != 1 || !p.ws || items <= g_num_sms) return 0;
+    if (p.epi != EPI_BF16 || p.split_k != 1 || !p.ws) return 0;
     p.tail_items = (int)(items % g_num_sms);
     p.tail_split = pl.tail;
     const long long rows = (long long)p.tail_items * p.mt * BM;
