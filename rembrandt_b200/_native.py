@@ -49,6 +49,7 @@ _CUDA_SIGS = {
     "rb_lrn_bwd": [vp, vp, vp, vp, i64, i32, i32, f32, f32, f32, vp],
     # elementwise.cu
     "rb_colsum": [vp, i64, i32, i32, vp, vp],
+    "rb_gemv_sparse": [vp, i32, i32, i32, vp, vp, i32, f32, f32, vp, vp],
     "rb_bias_act": [vp, i64, i32, i32, vp, i32, vp, vp, i32, vp],
     "rb_dropout": [vp, vp, vp, i64, f32, u64, u32, vp, vp],
     "rb_relu_mask": [vp, vp, i64, vp],

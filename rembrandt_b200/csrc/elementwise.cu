@@ -189,7 +189,59 @@ static inline int grid_for(long long total, int block) {
 
 using namespace rb;
 
+// y[n] = beta * y[n] + alpha * sum_j val[j] * W(n, ind[j]) for a vector given by its `nnz` non-zero entries: the
+// matrix x sparse-vector product that the reference's tools/bench-cublas.rs:98-115 times for board-game layers whose
+// input is mostly zeros. `transposed` = W stored [k][n] (an entry's weights contiguous: coalesced), else [n][k] (a
+// gather of one element per output and entry). One thread per output; the entries are split over blockIdx.y and the
+// partial sums added with red.add; `y` is scaled by beta in a tiny launch of its own first, which keeps the two
+// phases ordered.
+__global__ void scale_vec_kernel(float* __restrict__ y, int n, float beta) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) y[i] = beta == 0.f ? 0.f : beta * y[i];
+}
+__global__ void gemv_sparse_kernel(const float* __restrict__ w, int n, int k, int transposed,
+                                   const float* __restrict__ val, const int* __restrict__ ind, int nnz, float alpha,
+                                   float* __restrict__ y) {
+  __shared__ float s_val[256];
+  __shared__ int s_ind[256];
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int per = (nnz + gridDim.y - 1) / gridDim.y;
+  const int j0 = blockIdx.y * per, j1 = min(nnz, j0 + per);
+  float acc = 0.f;
+  for (int base = j0; base < j1; base += 256) {
+    const int m = min(256, j1 - base);
+    __syncthreads();
+    if (threadIdx.x < m) {
+      s_val[threadIdx.x] = val[base + threadIdx.x];
+      s_ind[threadIdx.x] = ind[base + threadIdx.x];
+    }
+    __syncthreads();
+    if (i < n) {
+      for (int j = 0; j < m; ++j) {
+        const int c = s_ind[j];
+        if (c >= 0 && c < k) acc += s_val[j] * (transposed ? w[(long long)c * n + i] : w[(long long)i * k + c]);
+      }
+    }
+  }
+  if (i < n && j0 < j1) atomicAdd(y + i, alpha * acc);
+}
+
 extern "C" {
+
+int rb_gemv_sparse(const float* w, int n, int k, int transposed, const float* val, const int* ind, int nnz,
+                   float alpha, float beta, float* y, cudaStream_t st) {
+  if (n <= 0 || k <= 0 || nnz < 0) return -10;
+  const int bx = (n + 255) / 256;
+  scale_vec_kernel<<<bx, 256, 0, st>>>(y, n, beta);
+  if (nnz > 0) {
+    int gy = (148 * 4) / bx;                   // enough blocks for every SM when n is small (361 outputs = 2 blocks)
+    const int max_gy = (nnz + 63) / 64;        // at least 64 entries per block
+    if (gy > max_gy) gy = max_gy;
+    if (gy < 1) gy = 1;
+    gemv_sparse_kernel<<<dim3(bx, gy), 256, 0, st>>>(w, n, k, transposed, val, ind, nnz, alpha, y);
+  }
+  return RB_LAUNCH_OK();
+}
 
 int rb_colsum(const void* x, long long rows, int ld, int cols, float* out, cudaStream_t st) {
   if (ld % 8) return -10;

@@ -205,6 +205,12 @@ def zero_s2d_structural(dw, Kout, R2, Cp, f, cin, ksize):
 
 
 # ------------------------------------------------------------------ memory-bound operators
+def gemv_sparse(w, n, k, transposed, val, ind, nnz, y, alpha=1.0, beta=0.0):
+    """y = beta * y + alpha * W x for x given by `nnz` (value, index) pairs; W fp32 [n][k], or [k][n] if `transposed`."""
+    check(_native.cuda().rb_gemv_sparse(ptr(w), n, k, int(bool(transposed)), ptr(val), ptr(ind), nnz, float(alpha),
+                                        float(beta), ptr(y), stream_handle()), "rb_gemv_sparse")
+
+
 def colsum(x, rows, ld, cols, out):
     check(_native.cuda().rb_colsum(ptr(x), rows, ld, cols, ptr(out), stream_handle()), "rb_colsum")
 

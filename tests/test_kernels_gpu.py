@@ -690,3 +690,26 @@ def test_input_pipeline_random_crop_flip_is_a_crop_of_the_source():
                 if torch.equal(out[n], win) or torch.equal(out[n], win.flip(-1)):
                     found = True
         assert found, f"sample {n} is not a (flipped) crop of its source"
+
+
+@pytest.mark.parametrize("n,k,nnz,transposed", [(361, 2000, 400, True), (361, 2000, 400, False), (2000, 361, 10, True),
+                                                (77, 129, 129, False), (361, 20000, 2000, True)])
+def test_gemv_sparse_matches_dense_product(n, k, nnz, transposed):
+    """Matrix x sparse vector (the board-game layers of tools/bench-cublas.rs) against the dense product in fp32."""
+    torch.manual_seed(31)
+    w = torch.randn(n, k, device=DEV)
+    ind = torch.randperm(k, device=DEV)[:nnz].int()
+    val = torch.randn(nnz, device=DEV)
+    x = torch.zeros(k, device=DEV)
+    x[ind.long()] = val
+    y0 = torch.randn(n, device=DEV)
+    y = y0.clone()
+    wm = w.t().contiguous() if transposed else w
+    K.gemv_sparse(wm, n, k, transposed, val, ind, nnz, y, alpha=0.5, beta=2.0)
+    status_ok()
+    ref = 2.0 * y0 + 0.5 * (w.double() @ x.double()).float()
+    assert torch.allclose(y, ref, rtol=1e-4, atol=1e-3 * float(ref.abs().max()))
+    y = torch.full((n,), float("nan"), device=DEV)
+    K.gemv_sparse(wm, n, k, transposed, val, ind, nnz, y)       # beta = 0 overwrites whatever was there
+    assert torch.allclose(y, (w.double() @ x.double()).float(), rtol=1e-4, atol=1e-3 * float(ref.abs().max()))
+
