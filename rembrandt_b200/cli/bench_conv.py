@@ -32,6 +32,11 @@ SHAPES = {
     "go19_conv1": (16, 19, 19, 16, 5, 1, 2),
     "go19_hidden": (16, 19, 19, 16, 3, 1, 1),
     "go19_res128": (128, 19, 19, 128, 3, 1, 1),
+    # the residual stages of ResNet-18 / 34 (run them with --batch 32, the reference tool's batch)
+    "resnet_stage1": (64, 56, 56, 64, 3, 1, 1),
+    "resnet_stage2": (128, 28, 28, 128, 3, 1, 1),
+    "resnet_stage3": (256, 14, 14, 256, 3, 1, 1),
+    "resnet_stage4": (512, 7, 7, 512, 3, 1, 1),
 }
 
 

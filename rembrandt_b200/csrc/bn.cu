@@ -69,6 +69,86 @@ __global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restr
   }
 }
 
+// The same sums for channel counts of 64, 128 (every power of two up to 2048 that keeps C / 8 <= 256): the block's
+// 256 threads cover (256 / (C / 8)) consecutive rows x all channel groups, so that every lane loads 16 bytes and a
+// block reads whole contiguous rows. The kernel above gives each lane a fixed 8-channel group of a 256-channel slab,
+// which leaves three lanes in four idle at 64 channels -- the widths of a ResNet's first stages, where this reduction
+// was a seventh of the training step.
+__global__ void __launch_bounds__(256) bn_reduce_flat_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy,
+                                                             const bf16* __restrict__ y,
+                                                             const float* __restrict__ mean,
+                                                             const float* __restrict__ istd, long long rows, int C,
+                                                             float* __restrict__ sums, int backward) {
+  __shared__ float red0[2048];
+  __shared__ float red1[2048];
+  const int cg = C >> 3;                 // channel groups per row; divides 256
+  const int rl = 256 / cg;               // rows per pass of the block
+  const int g = threadIdx.x % cg, rr = threadIdx.x / cg;
+  const int c0 = g * 8;
+  float a0[8], a1[8], mu[8], is[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { a0[j] = 0.f; a1[j] = 0.f; is[j] = 1.f; }
+  if (backward) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { mu[j] = mean[c0 + j]; is[j] = istd[c0 + j]; }
+  } else {
+    load8(x + c0, mu);   // the shift: row 0 of these channels
+  }
+  for (long long r = (long long)blockIdx.x * rl + rr; r < rows; r += (long long)gridDim.x * rl) {
+    float v[8];
+    load8(x + r * C + c0, v);
+    if (!backward) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = v[j] - mu[j];
+        a0[j] += d;
+        a1[j] += d * d;
+      }
+    } else {
+      float gr[8];
+      load8(dy + r * C + c0, gr);
+      if (y) {
+        float yy[8];
+        load8(y + r * C + c0, yy);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) if (!(yy[j] > 0.f)) gr[j] = 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { a0[j] += gr[j]; a1[j] += gr[j] * (v[j] - mu[j]) * is[j]; }
+    }
+  }
+  // red[rr][channel]: rl x C = 2048 floats
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { red0[rr * C + c0 + j] = a0[j]; red1[rr * C + c0 + j] = a1[j]; }
+  __syncthreads();
+  for (int c = threadIdx.x; c < C; c += 256) {
+    float s0 = 0.f, s1 = 0.f;
+    for (int k = 0; k < rl; ++k) { s0 += red0[k * C + c]; s1 += red1[k * C + c]; }
+    atomicAdd(sums + c, s0);
+    atomicAdd(sums + C + c, s1);
+  }
+}
+
+// Launches the reduction that fits the channel count (see the two kernels above).
+static void launch_bn_reduce(const bf16* x, const bf16* dy, const bf16* y, const float* mean, const float* istd,
+                             long long rows, int C, float* sums, int backward, cudaStream_t st) {
+  const int cg = C / 8;
+  if (C % 8 == 0 && cg >= 1 && cg <= 256 && 256 % cg == 0) {
+    const int rl = 256 / cg;
+    long long blocks = rows / ((long long)rl * 8);     // about eight rows per thread
+    if (blocks < 1) blocks = 1;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    bn_reduce_flat_kernel<<<(int)blocks, 256, 0, st>>>(x, dy, y, mean, istd, rows, C, sums, backward);
+    return;
+  }
+  dim3 grid((C + 255) / 256, 1);
+  long long gy = rows / 64;
+  if (gy < 1) gy = 1;
+  if (gy > 256) gy = 256;
+  grid.y = (unsigned)gy;
+  bn_reduce_kernel<<<grid, 256, 0, st>>>(x, dy, y, mean, istd, rows, C, sums, backward);
+}
+
 // mean/istd from the sums; running statistics: r = (1-f) r + f batch ; sums re-zeroed.
 // With a step counter (`step_ptr`, the network's device-side count of training steps) the factor is derived on
 // the device, so that a captured CUDA graph keeps averaging correctly: avg_kind 1 = cumulative 1 / (1 + t),
@@ -196,12 +276,7 @@ int rb_bn_fwd_train(const void* x, long long rows, int C, int c_valid, float* su
                     const void* residual, void* y, int relu, int avg_kind, const unsigned int* step_ptr,
                     cudaStream_t st) {
   if (C % 8) return -10;
-  dim3 grid((C + 255) / 256, 1);
-  long long gy = rows / 64;
-  if (gy < 1) gy = 1;
-  if (gy > 256) gy = 256;
-  grid.y = (unsigned)gy;
-  bn_reduce_kernel<<<grid, 256, 0, st>>>((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0);
+  launch_bn_reduce((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0, st);
   bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, (const bf16*)x, rows, C, eps, factor, mean, istd, run_mean, run_var,
                                                       avg_kind, step_ptr);
   bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, mean, istd, gamma, beta,
@@ -225,13 +300,7 @@ int rb_bn_bwd(const void* x, const void* dy, const void* y_relu, long long rows,
               const float* mean, const float* istd, const float* gamma, float* dgamma, float* dbeta, void* dx,
               cudaStream_t st) {
   if (C % 8) return -10;
-  dim3 grid((C + 255) / 256, 1);
-  long long gy = rows / 64;
-  if (gy < 1) gy = 1;
-  if (gy > 256) gy = 256;
-  grid.y = (unsigned)gy;
-  bn_reduce_kernel<<<grid, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (const bf16*)y_relu, mean, istd, rows, C, sums,
-                                         1);
+  launch_bn_reduce((const bf16*)x, (const bf16*)dy, (const bf16*)y_relu, mean, istd, rows, C, sums, 1, st);
   bn_bwd_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, (const bf16*)dy,
                                                                     (const bf16*)y_relu, mean, istd, gamma, sums,
                                                                     (bf16*)dx, rows, C, c_valid);

@@ -1256,8 +1256,21 @@ class PointwiseLossOp(SoftmaxKLLossOp):
         super().alloc()
         self.targets = torch.zeros((self.net.batch, self.k), dtype=torch.float32, device=self.net.device)
 
+    # True: the targets are written by `load_targets` (e.g. a teacher network's activations) and the labels that
+    # arrive with a batch are ignored
+    hold_targets = False
+
     def load_labels(self, labels, non_blocking=True):
+        if self.hold_targets:
+            return
         self.targets.copy_(labels.reshape(self.net.batch, self.k).float(), non_blocking=non_blocking)
+
+    def load_targets(self, targets, non_blocking=True):
+        """Float targets [B, K] from elsewhere than the batch's labels; they stay until the next call."""
+        self.hold_targets = True
+        if not hasattr(self, "targets"):     # host path: no device buffers are allocated
+            self.targets = torch.zeros((self.net.batch, self.k), dtype=torch.float32)
+        self.targets.copy_(targets.reshape(self.net.batch, self.k).float(), non_blocking=non_blocking)
 
     def forward(self, train, t):
         logits, dbuf = self._logits()
@@ -1270,7 +1283,7 @@ class PointwiseLossOp(SoftmaxKLLossOp):
     def ref_loss(self, logits, labels, weights=None):
         n = logits.shape[0]
         x = logits.flatten(1)
-        t = labels.reshape(n, self.k).float()
+        t = self.targets.to(x.device) if self.hold_targets else labels.reshape(n, self.k).float()
         if self.mode == 0:
             per = F.binary_cross_entropy_with_logits(x, t, reduction="none").sum(1)
             correct = int(((x[:, 0] > 0) == (t[:, 0] > 0.5)).sum())

@@ -23,7 +23,10 @@ from .operators import Op, ParamSeg, _draw, conv_out
 class _BnConv:
     """conv (no bias) -> batch norm [-> + residual] [-> ReLU], with its buffers and parameter segments."""
 
-    def __init__(self, op: Op, tag, in_hw, in_c, in_cp, out_c, k, stride, pad, init, mov_avg, eps):
+    def __init__(self, op: Op, tag, in_hw, in_c, in_cp, out_c, k, stride, pad, init, mov_avg, eps, s2d=None):
+        """`s2d` = (f, r2, s2d_hw): the input operator hands over a space-to-depth'd image (a strided first layer on
+        <= 4 channels), on which this convolution is r2 x r2, stride 1, pad 0 over `in_cp` = pad(f * f * in_c)
+        channels; (k, stride, pad) stay the reference geometry (parameters, host path)."""
         self.op, self.tag = op, tag
         self.h, self.w = in_hw
         self.in_c, self.cp = in_c, in_cp
@@ -31,8 +34,16 @@ class _BnConv:
         self.k, self.s, self.p = k, stride, pad
         self.P, self.Q = conv_out(self.h, k, stride, pad), conv_out(self.w, k, stride, pad)
         self.init, self.mov_avg, self.eps = init, mov_avg, eps
+        self.s2d = s2d
+        if s2d is not None:
+            self.f, r2, s2d_hw = s2d
+            # what the kernels see
+            self.gh = self.gw = s2d_hw
+            self.gk, self.gs, self.gp = r2, 1, 0
+        else:
+            self.gh, self.gw, self.gk, self.gs, self.gp = self.h, self.w, k, stride, pad
         n = op.name + "." + tag
-        self.seg_w = ParamSeg(n + ".w", (out_c, k * k, in_cp))
+        self.seg_w = ParamSeg(n + ".w", (out_c, self.gk * self.gk, in_cp))
         self.seg_g = ParamSeg(n + ".scale", (self.kp,), decay=False)
         self.seg_b = ParamSeg(n + ".bias", (self.kp,), decay=False)
         self.seg_rm = ParamSeg(n + ".run_mean", (self.kp,), decay=False, trainable=False)
@@ -48,17 +59,17 @@ class _BnConv:
         self.sums = torch.zeros(2 * self.kp, device=dev)
         self.dconv = torch.zeros_like(self.conv_out) if net.training_capable else None
         self.wt16 = None
-        if net.training_capable and need_dx_filters and self.s == 1:
-            self.wt16 = torch.zeros((self.cp, self.k * self.k, self.kp), dtype=torch.bfloat16, device=dev)
+        if net.training_capable and need_dx_filters and self.gs == 1:
+            self.wt16 = torch.zeros((self.cp, self.gk * self.gk, self.kp), dtype=torch.bfloat16, device=dev)
         if dev.type == "cuda":
             # tile plans of the forward and data-grad shapes, measured once on scratch operands
-            K.tune_conv(n, self.h, self.w, self.cp, self.ko, self.k, self.k, self.s, self.p, self.p, self.P, self.Q,
-                        self.kp, n_valid=self.ko, n_store=self.kp)
+            K.tune_conv(n, self.gh, self.gw, self.cp, self.ko, self.gk, self.gk, self.gs, self.gp, self.gp, self.P,
+                        self.Q, self.kp, n_valid=self.ko, n_store=self.kp)
             if self.wt16 is not None:
                 for has_mask in (False, True):
-                    K.tune_conv(n, self.P, self.Q, self.kp, self.cp, self.k, self.k, 1, self.k - 1 - self.p,
-                                self.k - 1 - self.p, self.h, self.w, self.cp, has_mask=has_mask, n_valid=self.in_c,
-                                n_store=self.cp)
+                    K.tune_conv(n, self.P, self.Q, self.kp, self.cp, self.gk, self.gk, 1, self.gk - 1 - self.gp,
+                                self.gk - 1 - self.gp, self.gh, self.gw, self.cp, has_mask=has_mask,
+                                n_valid=self.in_c, n_store=self.cp)
 
     def v(self, seg, which="params"):
         return self.op.net.seg_view(seg, which)
@@ -66,8 +77,9 @@ class _BnConv:
     def forward(self, x, out, residual, relu, train, t):
         net = self.op.net
         n = net.batch
-        K.conv_fprop_tc(x, n, self.h, self.w, self.cp, self.v(self.seg_w, "params16"), self.ko, self.k, self.k, self.s,
-                        self.p, self.p, self.P, self.Q, self.conv_out, self.kp, n_valid=self.ko, n_store=self.kp)
+        K.conv_fprop_tc(x, n, self.gh, self.gw, self.cp, self.v(self.seg_w, "params16"), self.ko, self.gk, self.gk,
+                        self.gs, self.gp, self.gp, self.P, self.Q, self.conv_out, self.kp, n_valid=self.ko,
+                        n_store=self.kp)
         rows = n * self.P * self.Q
         if train:
             # the factor comes from the device-side step counter, so that graph replays keep averaging correctly
@@ -86,9 +98,15 @@ class _BnConv:
         rows = n * self.P * self.Q
         K.bn_bwd(self.conv_out, dout, y_relu, rows, self.kp, self.ko, self.sums, self.mean, self.istd,
                  self.v(self.seg_g), self.v(self.seg_g, "grads"), self.v(self.seg_b, "grads"), self.dconv)
-        K.conv_wgrad_tc(x, n, self.h, self.w, self.cp, self.dconv, self.kp, self.ko, self.k, self.k, self.s, self.p,
-                        self.p, self.P, self.Q, self.v(self.seg_w, "grads"))
+        gw = self.v(self.seg_w, "grads")
+        K.conv_wgrad_tc(x, n, self.gh, self.gw, self.cp, self.dconv, self.kp, self.ko, self.gk, self.gk, self.gs,
+                        self.gp, self.gp, self.P, self.Q, gw)
+        if self.s2d is not None:
+            # entries of the rearranged filter that no tap of the original filter maps to stay zero
+            K.zero_s2d_structural(gw, self.ko, self.gk, self.cp, self.f, self.in_c, self.k)
         if dx is not None:
+            if self.s2d is not None:
+                raise RuntimeError("a space-to-depth'd convolution is a first layer: it has no input delta")
             w16 = self.v(self.seg_w, "params16")
             if self.s == 1:
                 K.pack_dgrad_filters(w16, self.wt16, self.ko, self.kp, self.k * self.k, self.cp)
@@ -110,9 +128,19 @@ class _BnConv:
                                         self.k, self.s, self.p, self.p, self.P, self.Q)
 
     # ---- parameters
+    def _w_int(self, w_oihw):
+        if self.s2d is not None:
+            return layout.s2d_weight_to_internal(w_oihw, self.f, self.cp)
+        return layout.conv_weight_to_internal(w_oihw, self.cp)
+
+    def _w_ref(self, w_int):
+        if self.s2d is not None:
+            return layout.s2d_weight_from_internal(w_int, self.in_c, self.k, self.f)
+        return layout.conv_weight_from_internal(w_int, self.in_c, self.k, self.k)
+
     def init_params(self, rng):
         w = _draw(self.init, rng, (self.ko, self.in_c, self.k, self.k), self.k * self.k * self.in_c, self.ko)
-        self.v(self.seg_w).copy_(layout.conv_weight_to_internal(w, self.cp))
+        self.v(self.seg_w).copy_(self._w_int(w))
         self.v(self.seg_g).zero_()
         self.v(self.seg_g)[: self.ko] = 1.0
         self.v(self.seg_b).zero_()
@@ -121,7 +149,7 @@ class _BnConv:
         self.v(self.seg_rv)[: self.ko] = 1.0
 
     def encode(self):
-        w = layout.conv_weight_from_internal(self.v(self.seg_w).detach().float().cpu(), self.in_c, self.k, self.k)
+        w = self._w_ref(self.v(self.seg_w).detach().float().cpu())
         out = [(w.reshape(-1), (self.k * self.k * self.in_c, self.ko))]
         for seg in (self.seg_g, self.seg_b, self.seg_rm, self.seg_rv):
             out.append((self.v(seg).detach().float().cpu()[: self.ko].clone(), (1, self.ko)))
@@ -129,14 +157,14 @@ class _BnConv:
 
     def decode(self, arrays):
         w = torch.as_tensor(arrays[0][0]).reshape(self.ko, self.in_c, self.k, self.k)
-        self.v(self.seg_w).copy_(layout.conv_weight_to_internal(w, self.cp))
+        self.v(self.seg_w).copy_(self._w_int(w))
         for seg, (a, _) in zip((self.seg_g, self.seg_b, self.seg_rm, self.seg_rv), arrays[1:5]):
             self.v(seg).zero_()
             self.v(seg)[: self.ko] = torch.as_tensor(a).reshape(-1)
         return 5
 
     def ref(self, x, residual, relu, train, t):
-        w = layout.conv_weight_from_internal(self.v(self.seg_w), self.in_c, self.k, self.k)
+        w = self._w_ref(self.v(self.seg_w))
         y = F.conv2d(x, w, None, stride=self.s, padding=self.p)
         g, b = self.v(self.seg_g)[: self.ko], self.v(self.seg_b)[: self.ko]
         # `.data` views: running statistics are updated in place without touching autograd's version counter
@@ -183,8 +211,17 @@ class BNormConv2dOp(_BlockBase):
         super().setup(net, prev)
         cfg = self.cfg
         h, w, c = prev.out_hwc
+        s2d = None
+        from .operators import DataOp
+        if isinstance(prev, DataOp) and cfg.conv_stride > 1 and c <= 4 and h == w and prev.mode == "nhwc":
+            # a strided first layer on a few channels (the 7 x 7 / 2 stem): the input operator writes the image
+            # space-to-depth'd, and the convolution becomes stride 1 over f * f * c channels instead of a strided
+            # one whose 3 channels are padded to 32 per filter tap
+            f, r2, _out_hw, s2d_hw = layout.s2d_geometry(cfg.conv_size, cfg.conv_stride, h + 2 * cfg.conv_pad)
+            prev.request_s2d(f, s2d_hw, cfg.conv_pad)
+            s2d = (f, r2, s2d_hw)
         self.u = _BnConv(self, "conv", (h, w), c, prev.out_cp, cfg.out_channels, cfg.conv_size, cfg.conv_stride,
-                         cfg.conv_pad, cfg.init_weights, cfg.bnorm_mov_avg, cfg.bnorm_epsilon)
+                         cfg.conv_pad, cfg.init_weights, cfg.bnorm_mov_avg, cfg.bnorm_epsilon, s2d=s2d)
         self.units = (self.u,)
         self.segs = list(self.u.segs)
         self.out_hwc = (self.u.P, self.u.Q, cfg.out_channels)

@@ -103,6 +103,17 @@ def bn_blocks():
     return _head(cfg)
 
 
+def resnet_stem():
+    """A 7 x 7 stride-2 pad-3 normalised first layer on 3 channels: the input arrives space-to-depth'd."""
+    from rembrandt_b200.models.config import BNormConv2dCfg, StackResConv2dCfg
+    cfg = SequentialOperatorConfig().data3d(Data3dCfg((22, 22, 3), normalize=True))
+    cfg.bnorm_conv2d(BNormConv2dCfg(7, 2, 3, 16, Act.RECT, K_), "stem")
+    cfg.pool2d(Pool2dCfg(3, 2, 1, PoolKind.MAX), "pool1")
+    cfg.stack_res_conv2d(StackResConv2dCfg(K_), "res1")
+    cfg.pool2d(Pool2dCfg(6, 1, 0, PoolKind.AVERAGE), "gap")
+    return _head(cfg)
+
+
 def alexnet_like():
     from rembrandt_b200.models.config import DropoutCfg, LrnCfg
     cfg = SequentialOperatorConfig().data3d(Data3dCfg((23, 23, 3), normalize=True))
@@ -122,7 +133,7 @@ def graph_residual():
 
 CASES = {"baseline": (baseline, 10), "strided": (strided, 10), "smooth": (smooth, 10), "low_rank": (low_rank, 10),
          "direct": (direct, 10), "residual": (residual, 10), "flat_input": (flat_input, 10), "go_plain": (go_plain, 361), "go_residual": (go_residual, 361),
-         "bn_blocks": (bn_blocks, 10), "alexnet_like": (alexnet_like, 10), "graph_residual": (graph_residual, 10)}
+         "bn_blocks": (bn_blocks, 10), "resnet_stem": (resnet_stem, 10), "alexnet_like": (alexnet_like, 10), "graph_residual": (graph_residual, 10)}
 
 
 @pytest.mark.parametrize("name", sorted(CASES))

@@ -241,3 +241,53 @@ def test_residual_network_matches_reference_path_and_averages_statistics():
     for seg_g, seg_c in ((stem_g.seg_rm, stem_c.seg_rm), (stem_g.seg_rv, stem_c.seg_rv)):
         a, b = g.seg_view(seg_g).float().cpu(), c.seg_view(seg_c).detach()
         assert torch.allclose(a, b, rtol=5e-2, atol=5e-3), float((a - b).abs().max())
+
+
+def test_strided_normalised_stem_runs_on_the_space_to_depth_input():
+    """A 7 x 7 stride-2 pad-3 batch-normalised first layer (the ResNet stem) against the host path: the device runs
+    it as a 4 x 4 stride-1 convolution on the space-to-depth'd image, with the padding absorbed by the input kernel."""
+    from rembrandt_b200.models.config import BNormConv2dCfg, StackResConv2dCfg
+    k = ParamsInit.kaiming()
+
+    def cfg_fn():
+        return (SequentialOperatorConfig().data3d(Data3dCfg((38, 38, 3), normalize=True))
+                .bnorm_conv2d(BNormConv2dCfg(7, 2, 3, 32, Act.RECT, k), "stem")
+                .pool2d(Pool2dCfg(3, 2, 1, PoolKind.MAX), "pool1")
+                .stack_res_conv2d(StackResConv2dCfg(k), "res1")
+                .pool2d(Pool2dCfg(10, 1, 0, PoolKind.AVERAGE), "gap")
+                .affine(AffineCfg(10, Act.IDENTITY, ParamsInit.xavier()), "fc")
+                .softmax_kl_loss(SoftmaxKLLossCfg(10)))
+
+    g = Net(cfg_fn(), 8, device="cuda", seed=(5, 6))
+    c = Net(cfg_fn(), 8, device="cpu", seed=(5, 6))
+    assert g.hidden_ops[0].u.s2d is not None and g.input_op.mode == "s2d"
+    assert torch.equal(g.params.cpu(), c.params.detach())
+    with torch.no_grad():
+        c.params.copy_(g.params16.float().cpu())
+    torch.manual_seed(2)
+    x = torch.randint(0, 256, (8, 3, 38, 38), dtype=torch.uint8)
+    y = torch.randint(0, 10, (8,))
+    g.load_batch(x.cuda(), y.cuda().int())
+    c.load_batch(x, y)
+    for net in (g, c):
+        net.forward(True)
+        net.backward()
+    torch.cuda.synchronize()
+    assert K.read_status() == 0
+    gl, cl = g.read_stats()[0], c.read_stats()[0]
+    assert abs(gl - cl) < 5e-2 * max(1.0, abs(cl)), (gl, cl)
+    gg, cg = g.grads.cpu(), c.grads
+    for seg in g.segs:
+        if not seg.trainable:
+            continue
+        a, b = gg[seg.offset: seg.offset + seg.numel], cg[seg.offset: seg.offset + seg.numel]
+        rel = float((a - b).norm() / b.norm().clamp_min(1e-12))
+        assert rel < 0.15, f"{seg.name}: relative error {rel:.4g}"
+    # a checkpoint written from the rearranged filter reads back as the 7 x 7 filter of the host path
+    blob_g = g.encode_params()
+    fresh = Net(cfg_fn(), 8, device="cpu", seed=(5, 6))           # the same seed: the same (unrounded) parameters
+    c2 = Net(cfg_fn(), 8, device="cpu", seed=(9, 9))
+    c2.decode_params(blob_g)
+    assert torch.allclose(c2.params, fresh.params.detach(), atol=1e-6)
+    assert len(blob_g) == len(fresh.encode_params())
+

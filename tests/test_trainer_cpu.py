@@ -198,6 +198,51 @@ def test_mimic_training_pulls_student_towards_teacher():
     assert after < 0.5 * before, (before, after)
 
 
+def test_mimic_training_on_activations_fits_a_low_rank_student_to_the_teacher():
+    """The other hand-over of the reference's mimic optimizer: the activations that enter the teacher's loss become
+    the L2 targets of a student (here a low-rank one) that ends in an L2 head."""
+    from rembrandt_b200.api import default_opt
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.config import (Data3dCfg, MimicAffineCfg, PointwiseLossCfg,
+                                              SequentialOperatorConfig)
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.mimic import MimicSgdOpt
+    from rembrandt_b200.parallel.comm import NullComm
+    teacher = Net(zoo.mnist_fc2(hidden=64), 16, device="cpu", seed=(11, 12), training=False)
+    scfg = (SequentialOperatorConfig().data3d(Data3dCfg((28, 28, 1), normalize=True))
+            .mimic_affine(MimicAffineCfg(bottleneck_rank=8, hidden_channels=32, out_channels=10), "m")
+            .pointwise_loss(PointwiseLossCfg(10, "l2")))
+    student = Net(scfg, 16, device="cpu", seed=(21, 22))
+    torch.manual_seed(0)
+    x = torch.randint(0, 256, (16, 1, 28, 28), dtype=torch.uint8)
+    y = torch.randint(0, 10, (16,))
+
+    def gap():
+        outs = []
+        for n in (teacher, student):
+            n.load_batch(x, y)
+            with torch.no_grad():
+                n.forward(False)
+            n.read_stats()
+            outs.append(n._cpu_logits.flatten(1).clone())
+        return float(((outs[0] - outs[1]) ** 2).sum(1).mean())
+
+    cfg = default_opt(16, "null")
+    cfg.max_iters, cfg.display_iters, cfg.checkpoint_iters = 80, 0, 0
+    eng = StepEngine(student, cfg, NullComm(), use_graph=False)
+    eng.set_lr(0.05)
+    opt = MimicSgdOpt(cfg, eng, teacher, target="activations", quiet=True)
+    student.loss_op.load_targets(torch.zeros(16, 10))     # so that the first measurement has targets to ignore
+    before = gap()
+    opt.train([(x, y)] * 80, max_iters=80)
+    after = gap()
+    assert after < 0.5 * before, (before, after)
+    with pytest.raises(ValueError):
+        MimicSgdOpt(cfg, StepEngine(Net(zoo.mnist_fc1(), 16, device="cpu"), cfg, NullComm(), use_graph=False), teacher,
+                    target="activations", quiet=True)
+
+
 def test_async_sgd_opt_checkpoints_locally_without_barriers(tmp_path):
     """The barrier-free loop trains like the synchronous one on a single worker, never calls a barrier, and
     writes its checkpoints under a per-rank directory."""
