@@ -606,9 +606,12 @@ def test_colsum_and_bias_act():
     assert (acc == 0).all()
 
 
-def test_bn_forward_backward():
+@pytest.mark.parametrize("N,C,H", [(4, 64, 5), (6, 128, 9), (3, 512, 7), (5, 96, 6), (2, 320, 8), (33, 64, 12),
+                                   (2, 1024, 4)])
+def test_bn_forward_backward(N, C, H):
+    """Channel counts whose 8-channel groups divide a block (64, 128, 512, 1024) take the reduction that spreads
+    rows over the lanes; 96 and 320 take the slab-per-block one."""
     torch.manual_seed(14)
-    N, C, H = 4, 64, 5
     rows = N * H * H
     x = bf(torch.randn(N, C, H, H, device=DEV) * 2 + 1).requires_grad_()
     gamma = (torch.rand(C, device=DEV) + 0.5).requires_grad_()
