@@ -135,15 +135,25 @@ class TorchBaseline:
             net = net.to(torch.bfloat16)
         if variant == "compiled":
             net = torch.compile(net, mode="max-autotune-no-cudagraphs")
+        self._stream = None
         if world > 1:
-            net = torch.nn.parallel.DistributedDataParallel(net, device_ids=[self.device.index], bucket_cap_mb=25,
-                                                            gradient_as_bucket_view=True)
+            if variant != "eager":
+                # a captured DDP step must never touch the legacy default stream: the wrapper is built, warmed up and
+                # captured on one side stream (its reducer keeps the stream that was current at construction)
+                self._stream = torch.cuda.Stream(self.device)
+                self._stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._stream):
+                    net = torch.nn.parallel.DistributedDataParallel(net, device_ids=[self.device.index],
+                                                                    bucket_cap_mb=25, gradient_as_bucket_view=True)
+                torch.cuda.current_stream().wait_stream(self._stream)
+            else:
+                net = torch.nn.parallel.DistributedDataParallel(net, device_ids=[self.device.index], bucket_cap_mb=25,
+                                                                gradient_as_bucket_view=True)
         self.net = net
         self.opt = torch.optim.SGD(net.parameters(), lr=lr, momentum=momentum, weight_decay=wd, fused=True)
         self.loss = None
         self.graph = None
         self._static_x = self._static_y = None
-        self._stream = None
 
     # ---- the step itself (what a graph captures)
     def _compute(self, x_u8, y):
@@ -176,7 +186,7 @@ class TorchBaseline:
         self._static_y = torch.zeros((self.batch,), dtype=torch.long, device=self.device)
         self._static_x.copy_(images_u8, non_blocking=True)
         self._static_y.copy_(labels.long(), non_blocking=True)
-        s = torch.cuda.Stream(self.device)
+        s = self._stream if self._stream is not None else torch.cuda.Stream(self.device)
         s.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(s):
             for _ in range(11 if self.world > 1 else 3):
@@ -185,7 +195,7 @@ class TorchBaseline:
         torch.cuda.synchronize()
         g = torch.cuda.CUDAGraph()
         self.opt.zero_grad(set_to_none=True)
-        with torch.cuda.graph(g):
+        with torch.cuda.graph(g, stream=s):
             self._static_loss = self._compute(self._static_x, self._static_y)
         self.graph = g
 

@@ -327,7 +327,10 @@ def main():
                  for _ in range(pool)]
     sampler_ids = ",".join(str(i) for i in range(world)) if world > 1 else local_rank
     if args.baseline_variants == "auto":
-        args.baseline_variants = "graph,compiled,eager" if world == 1 else "graph,eager"
+        # several GPUs: eager DDP only. Capturing a DDP step in a CUDA graph is fragile (the autograd engine and the
+        # reducer must stay off the legacy stream), and a variant that fails on a rank ends the run for all of them;
+        # `--baseline-variants graph,eager` asks for it explicitly.
+        args.baseline_variants = "graph,compiled,eager" if world == 1 else "eager"
     variants = [v for v in args.baseline_variants.split(",") if v and v != "none"]
 
     def torch_arms():
@@ -340,7 +343,10 @@ def main():
             except (RuntimeError, ImportError, AttributeError) as e:
                 failed[v] = f"{type(e).__name__}: {str(e)[:160]}"
                 if world > 1:
-                    raise       # ranks must stay in step: a variant that fails on one rank cannot be skipped by it alone
+                    # ranks must stay in step, so nothing more is run after a failure; the line with our own arm's
+                    # numbers (already measured) is still printed, then every rank leaves without further collectives
+                    failed["_stopped_after"] = v
+                    break
         return out, failed
 
     global_batch = batch * world
@@ -410,8 +416,10 @@ def main():
                 out["e2e_vs_baseline_same_lease"] = round(e2e / rate(best["times_e2e"]), 4)
         if base_failed:
             out["baseline_variants_failed"] = base_failed
-        print(json.dumps(out))
+        print(json.dumps(out), flush=True)
     if world > 1:
+        if base_failed.get("_stopped_after"):
+            os._exit(0)      # the process group may hold a half-captured collective: no clean shutdown to be had
         dist.destroy_process_group()
     return 0
 
