@@ -67,6 +67,18 @@ class SyntheticDataSource(DataSource):
             img[:, y0:y0 + band, :] = 255 - img[:, y0:y0 + band, :] // 2
         return img, label
 
+    def as_arrays(self):
+        """All samples as (uint8 [n, C, H, W], int32 [n]), built once: what the native batch loader reads. Without it
+        the training tools would assemble synthetic batches sample by sample in Python, at a tenth of what a GPU eats."""
+        if getattr(self, "_arrays", None) is None:
+            w, h, c = self.dims
+            imgs = np.empty((self.n, c, h, w), dtype=np.uint8)
+            lbls = np.empty(self.n, dtype=np.int32)
+            for i in range(self.n):
+                imgs[i], lbls[i] = self[i]
+            self._arrays = (imgs, lbls)
+        return self._arrays
+
 
 class _Mapped:
     def __init__(self, path):
