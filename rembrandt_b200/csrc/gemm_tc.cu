@@ -1349,39 +1349,49 @@ static PlanKey plan_key(const GemmTcParams& p) {
 // Times the candidates of `p` (3 launches each, best of the last 2); returns the best time in ms, or a negative
 // value when nothing could be run.
 static float tune_plan(const GemmTcParams& p, bool b_is_weights, cudaStream_t stream, Plan* out) {
+  // the candidates: plain plans first (sub-tiles x resident B x tail cut), then CTA pairs
+  Plan cands[12];
+  int n_cands = 0;
+  for (int pr = 0; pr <= (pair_ok(p) ? 1 : 0); ++pr) {
+    for (int mt = 1; mt <= 2; ++mt) {
+      for (int res = 0; res <= (pr ? 0 : 1); ++res) {
+        if (res && (!b_is_weights || p.n_tiles != 1)) continue;
+        for (int tail = 0; tail <= (pr ? 0 : 1); ++tail) {
+          Plan cand{mt, 1, res, 0, 0.0};
+          cand.pair = pr;
+          if (tail) {
+            if (!p.ws || g_opt.force_tail == 0 || g_opt.deterministic) continue;
+            cand.tail = tail_parts((long long)m_items_of(p, mt) * p.n_tiles, g_num_sms, p.num_kb);
+            if (cand.tail == 0) continue;
+          }
+          GemmTcParams q = p;
+          if (apply_plan(q, cand) <= 0 || (res && q.stages < 3)) continue;
+          cands[n_cands++] = cand;
+        }
+      }
+    }
+  }
   cudaEvent_t e0, e1;
   cudaEventCreate(&e0);
   cudaEventCreate(&e1);
   float best_ms = 1e30f;
-  for (int pr = 0; pr <= (pair_ok(p) ? 1 : 0); ++pr)
-  for (int mt = 1; mt <= 2; ++mt) {
-    for (int res = 0; res <= (pr ? 0 : 1); ++res) {
-      if (res && (!b_is_weights || p.n_tiles != 1)) continue;
-      for (int tail = 0; tail <= (pr ? 0 : 1); ++tail) {
-        Plan cand{mt, 1, res, 0, 0.0};
-        cand.pair = pr;
-        if (tail) {
-          if (!p.ws || g_opt.force_tail == 0 || g_opt.deterministic) continue;
-          cand.tail = tail_parts((long long)m_items_of(p, mt) * p.n_tiles, g_num_sms, p.num_kb);
-          if (cand.tail == 0) continue;
-        }
-        GemmTcParams q = p;
-        if (apply_plan(q, cand) <= 0 || (res && q.stages < 3)) continue;
-        float ms = 1e30f;
-        bool okc = true;
-        for (int rep = 0; rep < 3 && okc; ++rep) {
-          cudaEventRecord(e0, stream);
-          if (run_plan(p, cand, stream) != 0) { okc = false; break; }
-          cudaEventRecord(e1, stream);
-          if (cudaEventSynchronize(e1) != cudaSuccess) { okc = false; break; }
-          float t = 0.f;
-          cudaEventElapsedTime(&t, e0, e1);
-          if (rep > 0 && t < ms) ms = t;   // the first run warms the caches
-        }
-        // pairs are timed after every plain plan and must win by 3 %: measured alone they tie to within 2 % on the
-        // layers tried, and inside a training step (other kernels beside them) the plain plans did better
-        if (okc && ms < best_ms * (pr ? 0.97f : 1.0f)) { best_ms = ms; *out = cand; }
-      }
+  for (int c = 0; c < n_cands; ++c) {
+    float ms = 1e30f;
+    bool ok = true;
+    for (int rep = 0; rep < 3 && ok; ++rep) {
+      cudaEventRecord(e0, stream);
+      ok = run_plan(p, cands[c], stream) == 0;
+      cudaEventRecord(e1, stream);
+      ok = ok && cudaEventSynchronize(e1) == cudaSuccess;
+      float t = 0.f;
+      if (ok) cudaEventElapsedTime(&t, e0, e1);
+      if (ok && rep > 0 && t < ms) ms = t;   // the first run warms the caches
+    }
+    // pairs are timed after every plain plan and must win by 3 %: measured alone they tie to within 2 % on the
+    // layers tried, and inside a training step (other kernels beside them) the plain plans did better
+    if (ok && ms < best_ms * (cands[c].pair ? 0.97f : 1.0f)) {
+      best_ms = ms;
+      *out = cands[c];
     }
   }
   cudaEventDestroy(e0);
