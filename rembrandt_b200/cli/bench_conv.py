@@ -91,7 +91,12 @@ def run(name, batch, passes, iters, warmup, tune=True, roles=False):
                 out[name_ + "_waiting_pct"] = {"a_producer": round(100.0 * c[0] / c[4], 1),
                                                "b_producer": round(100.0 * c[1] / c[4], 1),
                                                "mma_on_operands": round(100.0 * c[2] / c[4], 1),
-                                               "mma_on_epilogue": round(100.0 * c[3] / c[4], 1)}
+                                               "mma_on_epilogue": round(100.0 * c[3] / c[4], 1),
+                                               # one epilogue warp: idle; fence + issue of its stores; slabs on
+                                               # their way from TMEM through registers into shared memory
+                                               "epilogue_idle": round(100.0 * c[5] / c[4], 1),
+                                               "epilogue_store_issue": round(100.0 * c[6] / c[4], 1),
+                                               "epilogue_tmem_to_smem": round(100.0 * c[7] / c[4], 1)}
     torch.cuda.synchronize()
     out["status"] = K.read_status()
     return out

@@ -78,7 +78,9 @@ __device__ __forceinline__ bool ctl_wait(SharedCtl* ctl, uint64_t* bar, uint32_t
 
 // Role profile (built only with -DRB_GEMM_PROFILE, see `python -m rembrandt_b200._build --profile`): cycles that the
 // roles of ONE CTA (block 3) spend waiting, summed over launches -- [0] A producer on a free stage, [1] B producer on
-// a free stage, [2] MMA issuer on a filled stage, [3] MMA issuer on a drained accumulator, [4] the CTA's whole run.
+// a free stage, [2] MMA issuer on a filled stage, [3] MMA issuer on a drained accumulator, [4] the CTA's whole run,
+// and for ONE epilogue warp (warp 2) in the bf16 epilogue: [5] waiting for a filled accumulator, [6] proxy fence +
+// issue of the TMA store of a slab, [7] a slab's way from TMEM through registers into shared memory.
 // A role that hardly waits is the one the others wait for. `rb_gemm_role_profile` reads and clears the counters.
 #ifdef RB_GEMM_PROFILE
 __device__ unsigned long long g_role_cycles[8];
@@ -94,6 +96,16 @@ __device__ __forceinline__ bool ctl_wait_role(SharedCtl* ctl, uint64_t* bar, uin
                                               int) {
   return ctl_wait(ctl, bar, parity, status);
 }
+#endif
+
+#ifdef RB_GEMM_PROFILE
+#define RB_PROF_T0(cond) const long long prof_t0_ = (cond) ? clock64() : 0
+#define RB_PROF_ADD(cond, slot) \
+  if ((cond) && blockIdx.x == 3 && (threadIdx.x & 31) == 0) \
+    atomicAdd(&g_role_cycles[slot], (unsigned long long)(clock64() - prof_t0_))
+#else
+#define RB_PROF_T0(cond)
+#define RB_PROF_ADD(cond, slot)
 #endif
 
 // base pixel (w, h, n) of output position `pix` for the im2col tensor maps
@@ -654,7 +666,11 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
       const int tn = it.tn;
       const int tm = pair ? it.tm * 2 + (int)cta_rank : it.tm;
       const bool tail = it.tail >= 0;
-      if (!ctl_wait(ctl, &ctl->acc_full[acc], acc_ph, p.status)) { ok = false; break; }
+      {
+        RB_PROF_T0(warp == 2);
+        if (!ctl_wait(ctl, &ctl->acc_full[acc], acc_ph, p.status)) { ok = false; break; }
+        RB_PROF_ADD(warp == 2, 5);
+      }
       tc_fence_after();
       int col0;        // first column of D this tile writes
       int col_limit;   // tile-local bound on stored columns
@@ -696,7 +712,9 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
         if (p.epi == EPI_BF16 && !tail) {
           // 64-column slabs: TMEM -> registers -> bias / ReLU / mask -> swizzled shared memory -> TMA store.
           // Each warp owns a 4 KB slab buffer and issues its own stores, so no cross-warp sync is needed.
-          for (int c = col_half * 64; c < p.bn && col0 + c < p.n_store; c += 128) {
+          // the two warps of a lane quarter alternate slabs, starting with the other warp on the second sub-tile, so
+          // that a tile with an odd number of slabs (96 columns = a full and a half slab) splits evenly between them
+          for (int c = ((col_half + j) & 1) * 64; c < p.bn && col0 + c < p.n_store; c += 128) {
             uint8_t* buf = stg;
             if (lane == 0) tma_store_wait_read<0>();   // the store that last used this buffer has read it
             __syncwarp();
@@ -720,33 +738,46 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                 mreg[ch] = *reinterpret_cast<const uint4*>(buf + lane * 128 + ((ch ^ (lane & 7)) * 16));
               __syncwarp();
             }
+            RB_PROF_T0(warp == 2);
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
               uint32_t v[32];
-              tmem_ld_32x32(t_addr + (uint32_t)(c + half * 32), v);
-              tmem_ld_wait();
               const int nbase = gcol + half * 32;
+              if (nbase >= p.n_store) continue;            // these columns do not exist in D: the store clips them
               const bool fast = nbase + 32 <= p.n_valid;   // no padded column in this 32-column group
+              tmem_ld_32x32(t_addr + (uint32_t)(c + half * 32), v);
+              // the bias of these 32 columns is fetched while the TMEM read is under way
+              float4 bq[8];
+              if (fast && has_bias) {
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4) bq[q4] = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q4 * 4));
+              }
+              tmem_ld_wait();
+              const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                float f[8];
+                uint4 o;
+                uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+                const uint4 mv = p.mask_src ? mreg[half * 4 + q] : make_uint4(0u, 0u, 0u, 0u);
+                const __nv_bfloat162* m2 = reinterpret_cast<const __nv_bfloat162*>(&mv);
                 if (fast) {
-                  // one warp per scheduler runs this, so instruction count matters: vector bias loads, no
-                  // per-element tests (ReLU is a max against 0 or -inf)
-                  float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
-                  if (has_bias) {
-                    b0 = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q * 8));
-                    b1 = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q * 8 + 4));
+                  // Two epilogue warps share a scheduler, so this is bound by instruction count and dependent-issue
+                  // latency: packed fp32 adds for the bias, one conversion per pair, ReLU and the mask of the
+                  // previous layer's ReLU on the packed bf16 pair (rounding is monotone, so clamping after it gives
+                  // the same bits as clamping before).
+                  const float* bb = reinterpret_cast<const float*>(&bq[q * 2]);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    float x0 = __uint_as_float(v[q * 8 + 2 * e]), x1 = __uint_as_float(v[q * 8 + 2 * e + 1]);
+                    if (has_bias) add2_f32(v[q * 8 + 2 * e], v[q * 8 + 2 * e + 1], bb[2 * e], bb[2 * e + 1], x0, x1);
+                    __nv_bfloat162 h = __floats2bfloat162_rn(x0, x1);
+                    if (p.relu) h = __hmax2(h, zero2);
+                    uint32_t w = *reinterpret_cast<uint32_t*>(&h);
+                    if (p.mask_src) w &= __hgt2_mask(m2[e], zero2);
+                    ow[e] = w;
                   }
-                  f[0] = fmaxf(__uint_as_float(v[q * 8 + 0]) + b0.x, act_lo);
-                  f[1] = fmaxf(__uint_as_float(v[q * 8 + 1]) + b0.y, act_lo);
-                  f[2] = fmaxf(__uint_as_float(v[q * 8 + 2]) + b0.z, act_lo);
-                  f[3] = fmaxf(__uint_as_float(v[q * 8 + 3]) + b0.w, act_lo);
-                  f[4] = fmaxf(__uint_as_float(v[q * 8 + 4]) + b1.x, act_lo);
-                  f[5] = fmaxf(__uint_as_float(v[q * 8 + 5]) + b1.y, act_lo);
-                  f[6] = fmaxf(__uint_as_float(v[q * 8 + 6]) + b1.z, act_lo);
-                  f[7] = fmaxf(__uint_as_float(v[q * 8 + 7]) + b1.w, act_lo);
                 } else {
+                  float f[8];
 #pragma unroll
                   for (int e = 0; e < 8; ++e) {
                     const int n = nbase + q * 8 + e;
@@ -754,26 +785,27 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                     if (n < p.n_valid) x = fmaxf(__uint_as_float(v[q * 8 + e]) + (has_bias ? __ldg(p.bias + n) : 0.f), act_lo);
                     f[e] = x;
                   }
-                }
-                if (p.mask_src) {
-                  const uint4 mv = mreg[half * 4 + q];
-                  const __nv_bfloat162* m2 = reinterpret_cast<const __nv_bfloat162*>(&mv);
+                  if (p.mask_src) {
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float2 mf = __bfloat1622float2(m2[e]);
-                    if (!(mf.x > 0.f)) f[2 * e] = 0.f;
-                    if (!(mf.y > 0.f)) f[2 * e + 1] = 0.f;
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 mf = __bfloat1622float2(m2[e]);
+                      if (!(mf.x > 0.f)) f[2 * e] = 0.f;
+                      if (!(mf.y > 0.f)) f[2 * e + 1] = 0.f;
+                    }
                   }
-                }
-                uint4 o;
-                __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+                  __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                  for (int e = 0; e < 4; ++e) o2[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+                }
                 // 128-byte swizzle: 16-byte chunk index XOR (row mod 8), the layout the store's tensor map expects
                 const int chunk = (half * 4 + q) ^ (lane & 7);
                 *reinterpret_cast<uint4*>(buf + lane * 128 + chunk * 16) = o;
               }
             }
+            RB_PROF_ADD(warp == 2, 7);
+#ifdef RB_GEMM_PROFILE
+            const long long prof_t1_ = clock64();
+#endif
             fence_proxy_async_smem();
             __syncwarp();
             if (band_rows < 32) {
@@ -793,10 +825,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
               else tma_store_2d(&p.tm_d, buf, gcol, row0);
               tma_store_commit();
             }
+#ifdef RB_GEMM_PROFILE
+            if (warp == 2 && blockIdx.x == 3 && lane == 0)
+              atomicAdd(&g_role_cycles[6], (unsigned long long)(clock64() - prof_t1_));
+#endif
           }
           continue;
         }
-        for (int c = col_half * 32; c < p.bn; c += 64) {
+        for (int c = ((col_half + j) & 1) * 32; c < p.bn; c += 64) {
           uint32_t v[32];
           tmem_ld_32x32(t_addr + (uint32_t)c, v);
           tmem_ld_wait();

@@ -294,6 +294,17 @@ __device__ __forceinline__ void tc_commit2_both(uint64_t* bar) {
                : "memory");
 }
 
+// Two fp32 additions in one instruction (sm_100 packed fp32): (a0, a1) + (b0, b1).
+__device__ __forceinline__ void add2_f32(uint32_t a0, uint32_t a1, float b0, float b1, float& r0, float& r1) {
+  asm("{\n\t.reg .b64 a, b, d;\n\t"
+      "mov.b64 a, {%2, %3};\n\t"
+      "mov.b64 b, {%4, %5};\n\t"
+      "add.rn.f32x2 d, a, b;\n\t"
+      "mov.b64 {%0, %1}, d;\n\t}"
+      : "=f"(r0), "=f"(r1)
+      : "r"(a0), "r"(a1), "f"(b0), "f"(b1));
+}
+
 // ---- descriptors ------------------------------------------------------------
 // Shared-memory matrix descriptor (sm_100 format, version field = 1).
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
