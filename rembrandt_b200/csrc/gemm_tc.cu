@@ -1160,7 +1160,10 @@ static Plan plan_shape(const GemmTcParams& p, bool allow_split, int fixed_split,
     const int acc_bufs = (2 * mt * acc_stride <= 512) ? 2 : 1;
     const int m_items = m_items_of(p, mt);
     const long long tiles = (long long)m_items * p.n_tiles;
-    const int max_split = allow_split ? (p.num_kb / 8 > 64 ? 64 : (p.num_kb / 8 < 1 ? 1 : p.num_kb / 8)) : 1;
+    // up to one part per SM (a layer with a single output tile, e.g. the weight-grad of a 1 x 1 convolution on 96
+    // channels, would otherwise leave SMs idle), each part at least eight k-blocks long
+    const int split_cap = g_num_sms > 0 ? g_num_sms : 148;
+    const int max_split = allow_split ? (p.num_kb / 8 > split_cap ? split_cap : (p.num_kb / 8 < 1 ? 1 : p.num_kb / 8)) : 1;
     for (int s = (fixed_split > 0 ? fixed_split : 1); s <= (fixed_split > 0 ? fixed_split : max_split); ++s) {
       if (!split_ok(s, p.num_kb)) continue;
       for (int res = 0; res <= 1; ++res) {
