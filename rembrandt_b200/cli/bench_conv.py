@@ -19,12 +19,15 @@ SHAPES = {
     "alexnet_conv3": (256, 13, 13, 384, 3, 1, 1),
     "alexnet_conv4": (384, 13, 13, 384, 3, 1, 1),
     "alexnet_conv5": (384, 13, 13, 256, 3, 1, 1),
+    "nin_conv1_s2d": (48, 56, 56, 96, 3, 1, 0),       # 11 x 11 stride 4 on 224 x 224 after space-to-depth by 4
     "nin_cccp1": (96, 54, 54, 96, 1, 1, 0),
     "nin_conv2": (96, 27, 27, 256, 5, 1, 2),
     "nin_cccp3": (256, 27, 27, 256, 1, 1, 0),
     "nin_conv3": (256, 13, 13, 384, 3, 1, 1),
     "nin_conv4": (384, 6, 6, 1024, 3, 1, 1),
+    "nin_cccp5": (384, 13, 13, 384, 1, 1, 0),
     "nin_cccp7": (1024, 6, 6, 1024, 1, 1, 0),
+    "nin_cccp8": (1024, 6, 6, 1000, 1, 1, 0),
     # the small board-game shapes the reference's tool also times (tools/bench-cudnn.rs:10-60: 8 x 8 boards at batch
     # 1024, 19 x 19 Go boards at batch 8) and the 128-channel Go layers of tools/train-gogod.rs
     "board8_conv1": (12, 8, 8, 16, 5, 1, 2),
