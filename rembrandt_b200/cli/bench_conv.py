@@ -1,6 +1,7 @@
 """bench-conv: time the implicit-GEMM convolution kernels on given or built-in shapes and report achieved
 TFLOP/s (counterpart of the reference's tools/bench-cudnn.rs, which timed cuDNN on NIN / AlexNet-shaped
-convolutions). Timing uses CUDA events after warm-up; `--pass` selects fprop / dgrad / wgrad.
+convolutions). Timing uses CUDA events around replays of a CUDA graph that holds `--iters` launches (what a layer
+costs inside a captured step; `--eager` launches from the host instead); `--pass` selects fprop / dgrad / wgrad.
 
     python -m rembrandt_b200.cli.bench_conv --shape alexnet_conv2 --batch 128 --pass all
 """
@@ -10,7 +11,7 @@ import json
 import torch
 
 from ..ops import native_ops as K
-from ..utils.timing import time_fn
+from ..utils.timing import time_fn, time_graph
 
 SHAPES = {
     # name: (C, H, W, Kout, R, stride, pad)
@@ -46,7 +47,7 @@ SHAPES = {
 PEAK_TFLOPS = 1658.7      # cuBLAS bf16 matmul measured on this pool's B200 (burst); fractions are "of measured"
 
 
-def run(name, batch, passes, iters, warmup, tune=True, roles=False):
+def run(name, batch, passes, iters, warmup, tune=True, roles=False, eager=False):
     C, H, W, Ko, R, s, p = SHAPES[name]
     Cp, Kp = K.pad_channels(C), K.pad_channels(Ko)
     P, Q = (H + 2 * p - R) // s + 1, (W + 2 * p - R) // s + 1
@@ -83,7 +84,9 @@ def run(name, batch, passes, iters, warmup, tune=True, roles=False):
         if roles:
             fn()
             K.gemm_role_profile()      # clear: what the tuning and the first launch left
-        ms = time_fn(fn, iters, warmup)
+        # replayed from a CUDA graph unless asked otherwise: launched from the host, a kernel shorter than ~20 us is
+        # timed at the host's pace
+        ms = time_fn(fn, iters, warmup) if (eager or roles) else time_graph(fn, iters, warmup)
         out[name_ + "_plan"] = K.gemm_last_launch()
         out[name_ + "_ms"] = round(ms, 4)
         out[name_ + "_tflops"] = round(flops / ms / 1e9, 1)
@@ -113,6 +116,7 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-tune", action="store_true", help="take the cost model's tile plans instead of measured ones")
+    ap.add_argument("--eager", action="store_true", help="launch from the host instead of replaying a captured graph")
     ap.add_argument("--roles", action="store_true",
                     help="also print the share of a CTA's run that each role spends waiting (needs the library built "
                          "with `python -m rembrandt_b200._build --profile`)")
@@ -120,7 +124,7 @@ def main(argv=None):
     names = sorted(SHAPES) if args.shape == "all" else [args.shape]
     for n in names:
         print(json.dumps(run(n, args.batch, args.passes, args.iters, args.warmup, tune=not args.no_tune,
-                             roles=args.roles)))
+                             roles=args.roles, eager=args.eager)))
 
 
 if __name__ == "__main__":

@@ -24,6 +24,34 @@ def time_fn(fn: Callable[[], None], iters: int = 10, warmup: int = 3) -> float:
     return start.elapsed_time(end) / iters
 
 
+def time_graph(fn: Callable[[], None], iters: int = 10, warmup: int = 3, replays: int = 5) -> float:
+    """Mean device milliseconds of `fn` when `iters` calls of it are captured in one CUDA graph and replayed: what a
+    kernel costs inside a captured training step. `time_fn` launches from the host, so for kernels shorter than a
+    launch takes to issue (~10-20 us through Python) it reports the host's pace, not the device's."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for _ in range(iters):
+                fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(replays):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        best = min(best, start.elapsed_time(end) / iters)
+    return best
+
+
 def time_ops(net, iters: int = 5, warmup: int = 2, train: bool = True) -> List[Dict]:
     """Per-operator forward and backward device time in milliseconds."""
     for _ in range(warmup):
