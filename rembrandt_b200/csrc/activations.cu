@@ -6,6 +6,7 @@
 //
 // Activations are bf16 [rows][ld] with `n_valid` live columns; padded columns stay zero (a logistic would turn
 // them into 0.5 and feed the next layer's padded input channels).
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -34,6 +35,7 @@ __device__ __forceinline__ float act_slope(float y, int kind, float param) {
 
 // y = f(y) in place on the live columns
 __global__ void act_fwd_kernel(bf16* __restrict__ y, long long rows, int ld, int n_valid, int kind, float bound) {
+  pdl_prolog();
   const int gpr = ld / 8;
   const long long groups = rows * gpr;
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
@@ -56,6 +58,7 @@ __global__ void act_fwd_kernel(bf16* __restrict__ y, long long rows, int ld, int
 // d *= f'(y) in place
 __global__ void act_bwd_kernel(bf16* __restrict__ d, const bf16* __restrict__ y, long long rows, int ld, int n_valid,
                                int kind, float bound) {
+  pdl_prolog();
   const int gpr = ld / 8;
   const long long groups = rows * gpr;
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
@@ -83,6 +86,7 @@ __device__ __forceinline__ float to_float(bf16 v) { return bf2f(v); }
 template <typename T>
 __global__ void count_above_kernel(const T* __restrict__ x, long long n, float threshold,
                                    unsigned long long* __restrict__ out) {
+  pdl_prolog();
   unsigned int local = 0;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     local += fabsf(to_float(x[i])) > threshold ? 1u : 0u;
@@ -113,22 +117,22 @@ extern "C" {
 
 int rb_act_fwd(void* y, long long rows, int ld, int n_valid, int kind, float bound, cudaStream_t st) {
   if (ld % 8 || kind < ACT_LOGISTIC || kind > ACT_SCALED_LOGISTIC) return -10;
-  act_fwd_kernel<<<act_grid(rows * (ld / 8), 256), 256, 0, st>>>((bf16*)y, rows, ld, n_valid, kind, bound);
+  launch_pdl(act_fwd_kernel, act_grid(rows * (ld / 8), 256), 256, 0, st, (bf16*)y, rows, ld, n_valid, kind, bound);
   return RB_LAUNCH_OK();
 }
 
 int rb_act_bwd(void* d, const void* y, long long rows, int ld, int n_valid, int kind, float bound, cudaStream_t st) {
   if (ld % 8 || kind < ACT_LOGISTIC || kind > ACT_SCALED_LOGISTIC) return -10;
-  act_bwd_kernel<<<act_grid(rows * (ld / 8), 256), 256, 0, st>>>((bf16*)d, (const bf16*)y, rows, ld, n_valid, kind,
-                                                               bound);
+  launch_pdl(act_bwd_kernel, act_grid(rows * (ld / 8), 256), 256, 0, st, (bf16*)d, (const bf16*)y, rows, ld, n_valid,
+             kind, bound);
   return RB_LAUNCH_OK();
 }
 
 int rb_count_above(const void* x, long long n, int is_f32, float threshold, unsigned long long* out, cudaStream_t st) {
   if (is_f32)
-    count_above_kernel<float><<<act_grid(n, 256), 256, 0, st>>>((const float*)x, n, threshold, out);
+    launch_pdl(count_above_kernel<float>, act_grid(n, 256), 256, 0, st, (const float*)x, n, threshold, out);
   else
-    count_above_kernel<bf16><<<act_grid(n, 256), 256, 0, st>>>((const bf16*)x, n, threshold, out);
+    launch_pdl(count_above_kernel<bf16>, act_grid(n, 256), 256, 0, st, (const bf16*)x, n, threshold, out);
   return RB_LAUNCH_OK();
 }
 

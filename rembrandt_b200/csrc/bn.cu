@@ -5,6 +5,7 @@
 // Replaces cuDNN BatchNormalizationForwardTraining/Inference/Backward as used by the reference's
 // BNormConv2d and residual operators, including its "add into a copy of x" residual trick
 // (src/operator/conv.rs:494-535,595-608,1601-1644).
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -16,6 +17,7 @@ namespace rb {
 __global__ void bn_reduce_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, const bf16* __restrict__ y,
                                  const float* __restrict__ mean, const float* __restrict__ istd, long long rows, int C,
                                  float* __restrict__ sums, int backward) {
+  pdl_prolog();
   __shared__ float red0[8][257];
   __shared__ float red1[8][257];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
@@ -79,6 +81,7 @@ __global__ void __launch_bounds__(256) bn_reduce_flat_kernel(const bf16* __restr
                                                              const float* __restrict__ mean,
                                                              const float* __restrict__ istd, long long rows, int C,
                                                              float* __restrict__ sums, int backward) {
+  pdl_prolog();
   __shared__ float red0[2048];
   __shared__ float red1[2048];
   const int cg = C >> 3;                 // channel groups per row; divides 256
@@ -138,7 +141,8 @@ static void launch_bn_reduce(const bf16* x, const bf16* dy, const bf16* y, const
     long long blocks = rows / ((long long)rl * 8);     // about eight rows per thread
     if (blocks < 1) blocks = 1;
     if (blocks > 148 * 4) blocks = 148 * 4;
-    bn_reduce_flat_kernel<<<(int)blocks, 256, 0, st>>>(x, dy, y, mean, istd, rows, C, sums, backward);
+    launch_pdl(bn_reduce_flat_kernel, dim3((unsigned)blocks), dim3(256), 0, st, x, dy, y, mean, istd, rows, C, sums,
+               backward);
     return;
   }
   dim3 grid((C + 255) / 256, 1);
@@ -146,7 +150,7 @@ static void launch_bn_reduce(const bf16* x, const bf16* dy, const bf16* y, const
   if (gy < 1) gy = 1;
   if (gy > 256) gy = 256;
   grid.y = (unsigned)gy;
-  bn_reduce_kernel<<<grid, 256, 0, st>>>(x, dy, y, mean, istd, rows, C, sums, backward);
+  launch_pdl(bn_reduce_kernel, grid, dim3(256), 0, st, x, dy, y, mean, istd, rows, C, sums, backward);
 }
 
 // mean/istd from the sums; running statistics: r = (1-f) r + f batch ; sums re-zeroed.
@@ -158,6 +162,7 @@ __global__ void bn_finalize_kernel(float* __restrict__ sums, const bf16* __restr
                                    float* __restrict__ mean, float* __restrict__ istd, float* __restrict__ run_mean,
                                    float* __restrict__ run_var, int avg_kind = 0,
                                    const unsigned int* __restrict__ step_ptr = nullptr) {
+  pdl_prolog();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   if (step_ptr && avg_kind) {
@@ -180,6 +185,7 @@ __global__ void bn_finalize_kernel(float* __restrict__ sums, const bf16* __restr
 }
 
 __global__ void bn_running_istd_kernel(const float* __restrict__ run_var, float eps, float* __restrict__ istd, int C) {
+  pdl_prolog();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c < C) istd[c] = rsqrtf(run_var[c] + eps);
 }
@@ -188,6 +194,7 @@ __global__ void bn_apply_kernel(const bf16* __restrict__ x, const float* __restr
                                 const float* __restrict__ istd, const float* __restrict__ gamma,
                                 const float* __restrict__ beta, const bf16* __restrict__ residual,
                                 bf16* __restrict__ y, long long rows, int C, int c_valid, int relu) {
+  pdl_prolog();
   const int cv = C / 8;
   const long long total = rows * cv;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -216,6 +223,7 @@ __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __re
                                     const float* __restrict__ mean, const float* __restrict__ istd,
                                     const float* __restrict__ gamma, const float* __restrict__ sums,
                                     bf16* __restrict__ dx, long long rows, int C, int c_valid) {
+  pdl_prolog();
   const int cv = C / 8;
   const long long total = rows * cv;
   const float invm = 1.f / (float)rows;
@@ -247,6 +255,7 @@ __global__ void bn_bwd_apply_kernel(const bf16* __restrict__ x, const bf16* __re
 
 __global__ void bn_grad_accum_kernel(float* __restrict__ sums, float* __restrict__ dgamma, float* __restrict__ dbeta,
                                      int C, int c_valid) {
+  pdl_prolog();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   if (c < c_valid) {
@@ -277,10 +286,10 @@ int rb_bn_fwd_train(const void* x, long long rows, int C, int c_valid, float* su
                     cudaStream_t st) {
   if (C % 8) return -10;
   launch_bn_reduce((const bf16*)x, nullptr, nullptr, nullptr, nullptr, rows, C, sums, 0, st);
-  bn_finalize_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, (const bf16*)x, rows, C, eps, factor, mean, istd, run_mean, run_var,
-                                                      avg_kind, step_ptr);
-  bn_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, mean, istd, gamma, beta,
-                                                                (const bf16*)residual, (bf16*)y, rows, C, c_valid, relu);
+  launch_pdl(bn_finalize_kernel, dim3((C + 127) / 128), dim3(128), 0, st, sums, (const bf16*)x, rows, C, eps, factor,
+             mean, istd, run_mean, run_var, avg_kind, step_ptr);
+  launch_pdl(bn_apply_kernel, dim3(grid_for(rows * (C / 8), 256)), dim3(256), 0, st, (const bf16*)x, mean, istd, gamma,
+             beta, (const bf16*)residual, (bf16*)y, rows, C, c_valid, relu);
   return RB_LAUNCH_OK();
 }
 
@@ -301,10 +310,9 @@ int rb_bn_bwd(const void* x, const void* dy, const void* y_relu, long long rows,
               cudaStream_t st) {
   if (C % 8) return -10;
   launch_bn_reduce((const bf16*)x, (const bf16*)dy, (const bf16*)y_relu, mean, istd, rows, C, sums, 1, st);
-  bn_bwd_apply_kernel<<<grid_for(rows * (C / 8), 256), 256, 0, st>>>((const bf16*)x, (const bf16*)dy,
-                                                                    (const bf16*)y_relu, mean, istd, gamma, sums,
-                                                                    (bf16*)dx, rows, C, c_valid);
-  bn_grad_accum_kernel<<<(C + 127) / 128, 128, 0, st>>>(sums, dgamma, dbeta, C, c_valid);
+  launch_pdl(bn_bwd_apply_kernel, dim3(grid_for(rows * (C / 8), 256)), dim3(256), 0, st, (const bf16*)x,
+             (const bf16*)dy, (const bf16*)y_relu, mean, istd, gamma, sums, (bf16*)dx, rows, C, c_valid);
+  launch_pdl(bn_grad_accum_kernel, dim3((C + 127) / 128), dim3(128), 0, st, sums, dgamma, dbeta, C, c_valid);
   return RB_LAUNCH_OK();
 }
 

@@ -1,5 +1,6 @@
 // Small memory-bound helpers around the tensor-core kernels: bias-gradient column sums,
 // the fp32 -> bf16 epilogue of split-K affine layers, dropout, ReLU masking, filter repacking.
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -8,6 +9,7 @@ namespace rb {
 // gemm of the reference, src/operator/mod.rs:1169,1775-1781)
 __global__ void colsum_kernel(const bf16* __restrict__ x, long long rows, int ld, int cols, float* __restrict__ out,
                               int tpr) {
+  pdl_prolog();
   // tpr threads (8 columns each) per row, 256 / tpr rows per pass: narrow matrices keep all lanes busy
   __shared__ float red[256 * 8];
   const int rpp = 256 / tpr;
@@ -43,6 +45,7 @@ __global__ void colsum_kernel(const bf16* __restrict__ x, long long rows, int ld
 __global__ void bias_act_kernel(float* __restrict__ acc, long long rows, int ld, int n_valid,
                                 const float* __restrict__ bias, int relu, bf16* __restrict__ y,
                                 const bf16* __restrict__ mask_src, int rezero) {
+  pdl_prolog();
   const long long total = rows * (ld / 8);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -81,6 +84,7 @@ __global__ void bias_act_kernel(float* __restrict__ acc, long long rows, int ld,
 __global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, const bf16* __restrict__ mask_src,
                                long long n, float p, uint64_t seed, uint32_t stream,
                                const uint32_t* __restrict__ step_ptr) {
+  pdl_prolog();
   const float scale = 1.f / (1.f - p);
   if (step_ptr) seed += *step_ptr;  // device-side step counter: a captured graph draws a new mask per replay
   const long long groups = n / 8;
@@ -108,6 +112,7 @@ __global__ void dropout_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
 
 // d *= (y > 0) in place
 __global__ void relu_mask_kernel(bf16* __restrict__ d, const bf16* __restrict__ y, long long n) {
+  pdl_prolog();
   const long long groups = n / 8;
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
        g += (long long)gridDim.x * blockDim.x) {
@@ -122,6 +127,7 @@ __global__ void relu_mask_kernel(bf16* __restrict__ d, const bf16* __restrict__ 
 
 // a += b (bf16), optional mask; used to sum branch deltas at fan-out points
 __global__ void add_kernel(bf16* __restrict__ a, const bf16* __restrict__ b, long long n) {
+  pdl_prolog();
   const long long groups = n / 8;
   for (long long g = blockIdx.x * (long long)blockDim.x + threadIdx.x; g < groups;
        g += (long long)gridDim.x * blockDim.x) {
@@ -135,6 +141,7 @@ __global__ void add_kernel(bf16* __restrict__ a, const bf16* __restrict__ b, lon
 }
 
 __global__ void f32_to_bf16_kernel(const float* __restrict__ x, bf16* __restrict__ y, long long n) {
+  pdl_prolog();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     y[i] = f2bf(x[i]);
 }
@@ -143,6 +150,7 @@ __global__ void f32_to_bf16_kernel(const float* __restrict__ x, bf16* __restrict
 // Filters for the data-gradient, which runs as a forward convolution of dY with flipped taps.
 __global__ void pack_dgrad_filters_kernel(const bf16* __restrict__ w, bf16* __restrict__ wt, int Kout, int Kp, int RS,
                                           int Cp) {
+  pdl_prolog();
   const long long total = (long long)Cp * RS * Kp;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -161,6 +169,7 @@ __global__ void pack_dgrad_filters_kernel(const bf16* __restrict__ w, bf16* __re
 // (dy*f + dx)*cin + ci, original row = R2idx*f + dy.
 __global__ void zero_s2d_structural_kernel(float* __restrict__ dw, int Kout, int R2, int Cp, int f, int cin,
                                            int ksize) {
+  pdl_prolog();
   const long long total = (long long)Kout * R2 * R2 * Cp;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
@@ -196,12 +205,14 @@ using namespace rb;
 // partial sums added with red.add; `y` is scaled by beta in a tiny launch of its own first, which keeps the two
 // phases ordered.
 __global__ void scale_vec_kernel(float* __restrict__ y, int n, float beta) {
+  pdl_prolog();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) y[i] = beta == 0.f ? 0.f : beta * y[i];
 }
 __global__ void gemv_sparse_kernel(const float* __restrict__ w, int n, int k, int transposed,
                                    const float* __restrict__ val, const int* __restrict__ ind, int nnz, float alpha,
                                    float* __restrict__ y) {
+  pdl_prolog();
   __shared__ float s_val[256];
   __shared__ int s_ind[256];
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -232,13 +243,13 @@ int rb_gemv_sparse(const float* w, int n, int k, int transposed, const float* va
                    float alpha, float beta, float* y, cudaStream_t st) {
   if (n <= 0 || k <= 0 || nnz < 0) return -10;
   const int bx = (n + 255) / 256;
-  scale_vec_kernel<<<bx, 256, 0, st>>>(y, n, beta);
+  launch_pdl(scale_vec_kernel, bx, 256, 0, st, y, n, beta);
   if (nnz > 0) {
     int gy = (148 * 4) / bx;                   // enough blocks for every SM when n is small (361 outputs = 2 blocks)
     const int max_gy = (nnz + 63) / 64;        // at least 64 entries per block
     if (gy > max_gy) gy = max_gy;
     if (gy < 1) gy = 1;
-    gemv_sparse_kernel<<<dim3(bx, gy), 256, 0, st>>>(w, n, k, transposed, val, ind, nnz, alpha, y);
+    launch_pdl(gemv_sparse_kernel, dim3(bx, gy), 256, 0, st, w, n, k, transposed, val, ind, nnz, alpha, y);
   }
   return RB_LAUNCH_OK();
 }
@@ -254,52 +265,52 @@ int rb_colsum(const void* x, long long rows, int ld, int cols, float* out, cudaS
   const long long cap = (148LL * 8) / grid.x > 1 ? (148LL * 8) / grid.x : 1;
   if (gy > cap) gy = cap;
   grid.y = (unsigned)gy;
-  colsum_kernel<<<grid, 256, 0, st>>>((const bf16*)x, rows, ld, cols, out, tpr);
+  launch_pdl(colsum_kernel, grid, 256, 0, st, (const bf16*)x, rows, ld, cols, out, tpr);
   return RB_LAUNCH_OK();
 }
 
 int rb_bias_act(float* acc, long long rows, int ld, int n_valid, const float* bias, int relu, void* y,
                 const void* mask_src, int rezero, cudaStream_t st) {
   if (ld % 8) return -10;
-  bias_act_kernel<<<grid_for(rows * (ld / 8), 256), 256, 0, st>>>(acc, rows, ld, n_valid, bias, relu, (bf16*)y,
-                                                                 (const bf16*)mask_src, rezero);
+  launch_pdl(bias_act_kernel, grid_for(rows * (ld / 8), 256), 256, 0, st, acc, rows, ld, n_valid, bias, relu, (bf16*)y,
+             (const bf16*)mask_src, rezero);
   return RB_LAUNCH_OK();
 }
 
 int rb_dropout(const void* x, void* y, const void* mask_src, long long n, float p, unsigned long long seed,
                unsigned int stream_id, const unsigned int* step_ptr, cudaStream_t st) {
   if (n % 8) return -10;
-  dropout_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (const bf16*)mask_src, n, p, seed,
-                                                      stream_id, step_ptr);
+  launch_pdl(dropout_kernel, grid_for(n / 8, 256), 256, 0, st, (const bf16*)x, (bf16*)y, (const bf16*)mask_src, n, p,
+             seed, stream_id, step_ptr);
   return RB_LAUNCH_OK();
 }
 
 int rb_relu_mask(void* d, const void* y, long long n, cudaStream_t st) {
   if (n % 8) return -10;
-  relu_mask_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((bf16*)d, (const bf16*)y, n);
+  launch_pdl(relu_mask_kernel, grid_for(n / 8, 256), 256, 0, st, (bf16*)d, (const bf16*)y, n);
   return RB_LAUNCH_OK();
 }
 
 int rb_add_bf16(void* a, const void* b, long long n, cudaStream_t st) {
   if (n % 8) return -10;
-  add_kernel<<<grid_for(n / 8, 256), 256, 0, st>>>((bf16*)a, (const bf16*)b, n);
+  launch_pdl(add_kernel, grid_for(n / 8, 256), 256, 0, st, (bf16*)a, (const bf16*)b, n);
   return RB_LAUNCH_OK();
 }
 
 int rb_f32_to_bf16(const float* x, void* y, long long n, cudaStream_t st) {
-  f32_to_bf16_kernel<<<grid_for(n, 256), 256, 0, st>>>(x, (bf16*)y, n);
+  launch_pdl(f32_to_bf16_kernel, grid_for(n, 256), 256, 0, st, x, (bf16*)y, n);
   return RB_LAUNCH_OK();
 }
 
 int rb_pack_dgrad_filters(const void* w, void* wt, int Kout, int Kp, int RS, int Cp, cudaStream_t st) {
-  pack_dgrad_filters_kernel<<<grid_for((long long)Cp * RS * Kp, 256), 256, 0, st>>>((const bf16*)w, (bf16*)wt, Kout,
-                                                                                   Kp, RS, Cp);
+  launch_pdl(pack_dgrad_filters_kernel, grid_for((long long)Cp * RS * Kp, 256), 256, 0, st, (const bf16*)w, (bf16*)wt,
+             Kout, Kp, RS, Cp);
   return RB_LAUNCH_OK();
 }
 
 int rb_zero_s2d_structural(float* dw, int Kout, int R2, int Cp, int f, int cin, int ksize, cudaStream_t st) {
-  zero_s2d_structural_kernel<<<grid_for((long long)Kout * R2 * R2 * Cp, 256), 256, 0, st>>>(dw, Kout, R2, Cp, f, cin,
-                                                                                           ksize);
+  launch_pdl(zero_s2d_structural_kernel, grid_for((long long)Kout * R2 * R2 * Cp, 256), 256, 0, st, dw, Kout, R2, Cp,
+             f, cin, ksize);
   return RB_LAUNCH_OK();
 }
 

@@ -36,6 +36,7 @@
 #include "gemm_tc.cuh"
 #include "ptx.cuh"
 #include "common.cuh"
+#include "launch.cuh"
 #include <ctype.h>
 #include <stdlib.h>
 #include <map>
@@ -46,6 +47,13 @@ namespace rb {
 
 constexpr int BM = 128;
 constexpr int GEMM_THREADS = 352;   // A-producer warp, MMA warp, 8 epilogue warps, B-producer warp
+// Register budget: 352 threads x 144 registers leave 14.8 K of the SM's 64 K registers free, which is what one
+// 128-thread block of the exchange kernels (80 registers per thread, 10 K) needs to run beside a resident CTA of this
+// kernel. Above 155 registers those blocks no longer fit and the gradient exchange stops overlapping the backward
+// pass (measured: 2.29 instead of 1.98 ms per AlexNet step on 2 GPUs); tests/test_register_budget.py keeps watch.
+// Registers are handed out to whole warps, four warps at a time: the CTA's 11 warps take 12 x 32 x 144 = 55296, and
+// the 10240 left are exactly the four warps x 80 registers of an exchange block. Hence the hard cap.
+constexpr int GEMM_MAX_REGS = 144;
 constexpr int PRODUCER_B_WARP = 10;
 constexpr int EPI_WARPS = 8;
 constexpr int MAX_STAGES = 8;
@@ -249,7 +257,7 @@ __device__ __forceinline__ bool issue_item(const IssueCtx& c, SharedCtl* ctl, un
 // PAIR: the instantiation that runs as clusters of two CTAs (p.pair != 0). It is a kernel of its own because a
 // kernel that contains cta_group::2 instructions can only be launched with an even cluster size.
 template <bool PAIR>
-__global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
+__global__ void __maxnreg__(GEMM_MAX_REGS) gemm_tc_kernel(const __grid_constant__ GemmTcParams p) {
 #ifdef RB_GEMM_PROFILE
   const long long t_kernel0 = clock64();
 #endif
@@ -329,6 +337,12 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
   __syncthreads();
   if (pair) cluster_sync_all();   // the peer's barriers are initialised before anything of ours signals them
   tc_fence_after();
+  // Programmatic dependent launch (option `pdl`): everything above touched only this CTA's own shared memory, TMEM
+  // and the launch parameters, so it may run while the kernels before this one on the stream are still finishing;
+  // nothing below (operands, bias, mask, output, workspace) is touched before they have completed and flushed.
+  // Without the launch attribute both instructions do nothing.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const uint32_t tmem_base = ctl->tmem_base;
 
   if (warp == 0 || warp == PRODUCER_B_WARP) {
@@ -746,12 +760,6 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
               if (nbase >= p.n_store) continue;            // these columns do not exist in D: the store clips them
               const bool fast = nbase + 32 <= p.n_valid;   // no padded column in this 32-column group
               tmem_ld_32x32(t_addr + (uint32_t)(c + half * 32), v);
-              // the bias of these 32 columns is fetched while the TMEM read is under way
-              float4 bq[8];
-              if (fast && has_bias) {
-#pragma unroll
-                for (int q4 = 0; q4 < 8; ++q4) bq[q4] = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q4 * 4));
-              }
               tmem_ld_wait();
               const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
 #pragma unroll
@@ -765,7 +773,14 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1) gemm_tc_kernel(const __grid_c
                   // latency: packed fp32 adds for the bias, one conversion per pair, ReLU and the mask of the
                   // previous layer's ReLU on the packed bf16 pair (rounding is monotone, so clamping after it gives
                   // the same bits as clamping before).
-                  const float* bb = reinterpret_cast<const float*>(&bq[q * 2]);
+                  // (the bias is fetched eight columns at a time: holding all 32 columns' worth in registers put the
+                  // kernel over its register budget)
+                  float4 bq[2];
+                  if (has_bias) {
+                    bq[0] = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q * 8));
+                    bq[1] = __ldg(reinterpret_cast<const float4*>(p.bias + nbase + q * 8 + 4));
+                  }
+                  const float* bb = reinterpret_cast<const float*>(&bq[0]);
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
                     float x0 = __uint_as_float(v[q * 8 + 2 * e]), x1 = __uint_as_float(v[q * 8 + 2 * e + 1]);
@@ -1037,6 +1052,10 @@ struct GemmOptions {
   int force_wide = -1;       // RB_GEMM_FORCE_WIDE: 0 = tiles of at most 256 columns, 1 = one wide tile when N <= 512
   int force_box = -1;        // RB_GEMM_FORCE_BOX: 0 = never load A as tap-shifted boxes, 1 = whenever feasible
   int force_pair = -1;       // RB_GEMM_FORCE_PAIR: 0 = never run as CTA pairs (cta_group::2), 1 = whenever feasible
+  int pdl = 2;               // RB_GEMM_PDL: programmatic stream serialization (blocks become resident while the kernel
+                             // before them finishes; see launch.cuh): 0 = off, 1 = this kernel only, 2 = every kernel
+                             // of a step. Beside exchange kernels on other streams use at most 1: the waiting blocks
+                             // of elementwise kernels fill the SMs' thread slots and the exchange kernels starve.
   int bk32 = 0;              // RB_GEMM_BK32: keep 32-channel chunks for channel counts such as 96
   int bn_cap = 256;          // RB_GEMM_BN_CAP: upper bound on the tile width chosen by the planner
   int a_split = 1;           // RB_GEMM_A_SPLIT / RB_GEMM_B_SPLIT: TMA boxes per K-major tile
@@ -1053,7 +1072,7 @@ static int* option_slot(const char* name) {
   struct { const char* name; int* slot; } table[] = {
       {"force_mt", &g_opt.force_mt}, {"force_resident", &g_opt.force_resident}, {"force_halo", &g_opt.force_halo},
       {"force_taps", &g_opt.force_taps}, {"force_tail", &g_opt.force_tail}, {"force_wide", &g_opt.force_wide},
-      {"force_box", &g_opt.force_box}, {"force_pair", &g_opt.force_pair},
+      {"force_box", &g_opt.force_box}, {"force_pair", &g_opt.force_pair}, {"pdl", &g_opt.pdl},
       {"bk32", &g_opt.bk32}, {"bn_cap", &g_opt.bn_cap}, {"a_split", &g_opt.a_split}, {"b_split", &g_opt.b_split},
       {"autotune", &g_opt.autotune}, {"deterministic", &g_opt.deterministic}};
   for (auto& t : table)
@@ -1063,7 +1082,7 @@ static int* option_slot(const char* name) {
 static void options_from_env() {
   std::call_once(g_opt_once, [] {
     const char* names[] = {"force_mt", "force_resident", "force_halo", "force_taps", "force_tail", "force_wide", "force_box",
-                           "force_pair", "bk32", "bn_cap", "a_split", "b_split", "autotune", "deterministic"};
+                           "force_pair", "pdl", "bk32", "bn_cap", "a_split", "b_split", "autotune", "deterministic"};
     for (const char* n : names) {
       char env[64] = "RB_GEMM_";
       size_t k = strlen(env);
@@ -1073,6 +1092,11 @@ static void options_from_env() {
       if (e) *option_slot(n) = atoi(e);
     }
   });
+}
+
+int pdl_enabled() {
+  options_from_env();
+  return g_opt.pdl >= 2 ? 1 : 0;
 }
 
 // ---- tile-shape planning -----------------------------------------------------------------------------------
@@ -1263,6 +1287,7 @@ struct TailFixArgs {
   int box, P, Q, bx_rows, bx_groups, mt;   // box mode: rows of a sub-tile are whole output rows of one image
 };
 __global__ void tail_fix_kernel(const TailFixArgs a) {
+  pdl_prolog();
   const int gpr = a.bn / 8;
   const long long groups = (long long)a.tail_items * a.rows_per_item * gpr;
   const float act_lo = a.relu ? 0.f : -INFINITY;
@@ -1316,28 +1341,36 @@ static int run_plan(GemmTcParams p, const Plan& pl, cudaStream_t stream) {
   if (grid <= 0) return -3;
   const int last[9] = {p.mt, p.split_k, p.b_resident, pl.tail, p.pair, p.bn, p.a_mode, p.stages, grid};
   memcpy(g_last_launch, last, sizeof(last));
-  if (p.pair) {
+  {
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(GEMM_THREADS);
     cfg.dynamicSmemBytes = GEMM_SMEM_BYTES;
     cfg.stream = stream;
-    cudaLaunchAttribute at;
-    at.id = cudaLaunchAttributeClusterDimension;
-    at.val.clusterDim.x = 2;
-    at.val.clusterDim.y = 1;
-    at.val.clusterDim.z = 1;
-    cfg.attrs = &at;
-    cfg.numAttrs = 1;
-    const cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, p);
+    cudaLaunchAttribute at[2];
+    int n_at = 0;
+    if (p.pair) {
+      at[n_at].id = cudaLaunchAttributeClusterDimension;
+      at[n_at].val.clusterDim.x = 2;
+      at[n_at].val.clusterDim.y = 1;
+      at[n_at].val.clusterDim.z = 1;
+      ++n_at;
+    }
+    if (g_opt.pdl >= 1) {   // the kernel's prologue may overlap the end of the work before it on the stream
+      at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[n_at].val.programmaticStreamSerializationAllowed = 1;
+      ++n_at;
+    }
+    cfg.attrs = n_at ? at : nullptr;
+    cfg.numAttrs = (unsigned)n_at;
+    const cudaError_t e = p.pair ? cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, p)
+                                 : cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, p);
     if (e != cudaSuccess) {
       g_last_cuda_error = (int)e;
       cudaGetLastError();
       return -4;
     }
-  } else {
-    gemm_tc_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, stream>>>(p);
   }
   if (p.tail_items > 0) {
     TailFixArgs f;
@@ -1364,7 +1397,7 @@ static int run_plan(GemmTcParams p, const Plan& pl, cudaStream_t stream) {
     const long long groups = (long long)p.tail_items * f.rows_per_item * (p.bn / 8);
     long long blocks = (groups + 255) / 256;
     if (blocks > 148 * 8) blocks = 148 * 8;
-    tail_fix_kernel<<<(int)blocks, 256, 0, stream>>>(f);
+    launch_pdl(tail_fix_kernel, (int)blocks, 256, 0, stream, f);
   }
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) g_last_cuda_error = (int)e;

@@ -10,6 +10,7 @@
 // Space-to-depth by f (used for strided first layers): output pixel (Y,X) holds the f*f*C values of
 // source pixels (Y*f+dy, X*f+dx), channel = (dy*f+dx)*C + c, so an s-strided k x k convolution becomes
 // a stride-1 ceil(k/f) x ceil(k/f) convolution on f*f*C channels.
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -63,6 +64,7 @@ __device__ __forceinline__ void sample_draw(const InputArgs& a, int n, int& oy, 
 }
 
 __global__ void input_kernel(InputArgs a) {
+  pdl_prolog();
   const int groups = a.Cp / 8;
   const long long total = (long long)a.N * a.OH * a.OW * groups;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -106,6 +108,7 @@ __global__ void input_kernel(InputArgs a) {
 // coalesced byte loads, converted (scale, mean, lighting shift, crop / flip / zero padding) into shared memory
 // as floats, then written out as 16-byte channel groups. The per-sample random draw is computed once per block.
 __global__ void __launch_bounds__(256) input_rows_kernel(InputArgs a) {
+  pdl_prolog();
   extern __shared__ float srow[];  // [f][C][seg_w]
   __shared__ int s_draw[3];
   __shared__ float s_shift[3];
@@ -209,6 +212,7 @@ __global__ void __launch_bounds__(256) input_rows_kernel(InputArgs a) {
 // Synthetic N(0,1) activations (bf16, padded channels zero) and uniform labels, generated on the device.
 __global__ void synth_normal_kernel(bf16* __restrict__ dst, long long pixels, int C, int Cp, uint64_t seed,
                                     uint32_t step) {
+  pdl_prolog();
   const long long total = pixels * Cp;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total / 4;
        i += (long long)gridDim.x * blockDim.x) {
@@ -229,6 +233,7 @@ __global__ void synth_normal_kernel(bf16* __restrict__ dst, long long pixels, in
 }
 
 __global__ void synth_labels_kernel(int* __restrict__ labels, int n, int classes, uint64_t seed, uint32_t step) {
+  pdl_prolog();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   uint32_t r[4];
@@ -264,9 +269,9 @@ int rb_input_u8(const void* src, const float* mean, void* dst, int N, int C, int
   if (blocks < 1) blocks = 1;
   const size_t row_smem = (size_t)f * C * OW * f * sizeof(float);
   if (row_smem <= 40 * 1024 && Cp <= 512 && (long long)N * OH < 0x7FFFFFFF) {
-    input_rows_kernel<<<N * OH, 256, row_smem, st>>>(a);
+    launch_pdl(input_rows_kernel, N * OH, 256, row_smem, st, a);
   } else {
-    input_kernel<<<(int)blocks, 256, 0, st>>>(a);
+    launch_pdl(input_kernel, (int)blocks, 256, 0, st, a);
   }
   return RB_LAUNCH_OK();
 }
@@ -277,12 +282,12 @@ int rb_synth_normal(void* dst, long long pixels, int C, int Cp, unsigned long lo
   long long blocks = (pixels * Cp / 4 + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
-  synth_normal_kernel<<<(int)blocks, 256, 0, st>>>((bf16*)dst, pixels, C, Cp, seed, step);
+  launch_pdl(synth_normal_kernel, (int)blocks, 256, 0, st, (bf16*)dst, pixels, C, Cp, seed, step);
   return RB_LAUNCH_OK();
 }
 
 int rb_synth_labels(int* labels, int n, int classes, unsigned long long seed, unsigned int step, cudaStream_t st) {
-  synth_labels_kernel<<<(n + 255) / 256, 256, 0, st>>>(labels, n, classes, seed, step);
+  launch_pdl(synth_labels_kernel, (n + 255) / 256, 256, 0, st, labels, n, classes, seed, step);
   return RB_LAUNCH_OK();
 }
 

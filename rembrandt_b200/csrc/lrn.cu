@@ -5,6 +5,7 @@
 // examples/imagenet_alexnet.model:30-36) but leaves it a pass-through stub (src/layer.rs:1846-1899);
 // this is the real operator. One thread owns one pixel's channel chunk; the channel vector sits in
 // shared memory so window sums are cheap.
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -13,6 +14,7 @@ constexpr int LRN_PIX = 8;  // pixels per block
 
 __global__ void lrn_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, long long pixels, int C, int size,
                                float alpha_eff, float beta, float kconst) {
+  pdl_prolog();
   extern __shared__ float sm[];  // LRN_PIX * C squares
   const int half_lo = size / 2, half_hi = (size - 1) / 2;
   const long long pix0 = (long long)blockIdx.x * LRN_PIX;
@@ -40,6 +42,7 @@ __global__ void lrn_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y,
 __global__ void lrn_bwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ dx,
                                const bf16* __restrict__ mask_src, long long pixels, int C, int size, float alpha_eff,
                                float beta, float kconst) {
+  pdl_prolog();
   extern __shared__ float sm[];  // per pixel: x[C], s[C], t[C] = dy*y/s
   const int half_lo = size / 2, half_hi = (size - 1) / 2;
   const long long pix0 = (long long)blockIdx.x * LRN_PIX;
@@ -107,6 +110,7 @@ __device__ __forceinline__ void load24(const bf16* base, long long chunk, int cv
 template <int SIZE>
 __global__ void lrn_fwd_vec_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, unsigned int chunks, int cv,
                                    float alpha_eff, float beta, float kconst) {
+  pdl_prolog();
   constexpr int LO = SIZE / 2, HI = (SIZE - 1) / 2;
   for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += gridDim.x * blockDim.x) {
     const int c8 = (int)(i % (unsigned)cv);
@@ -131,6 +135,7 @@ template <int SIZE>
 __global__ void lrn_bwd_vec_kernel(const bf16* __restrict__ x, const bf16* __restrict__ dy, bf16* __restrict__ dx,
                                    const bf16* __restrict__ mask_src, unsigned int chunks, int cv, float alpha_eff,
                                    float beta, float kconst) {
+  pdl_prolog();
   constexpr int LO = SIZE / 2, HI = (SIZE - 1) / 2;
   static_assert(LO + HI <= 8, "window too wide for the register path");
   for (unsigned int i = blockIdx.x * blockDim.x + threadIdx.x; i < chunks; i += gridDim.x * blockDim.x) {
@@ -181,11 +186,11 @@ static int launch_lrn_vec(const void* x, const void* dy, void* out, const void* 
   if (blocks > 148 * 16) blocks = 148 * 16;
   if (blocks < 1) blocks = 1;
   if (backward)
-    lrn_bwd_vec_kernel<SIZE><<<blocks, 256, 0, st>>>((const bf16*)x, (const bf16*)dy, (bf16*)out,
-                                                     (const bf16*)mask_src, chunks, C / 8, alpha_eff, beta, kconst);
+    launch_pdl(lrn_bwd_vec_kernel<SIZE>, blocks, 256, 0, st, (const bf16*)x, (const bf16*)dy, (bf16*)out,
+               (const bf16*)mask_src, chunks, C / 8, alpha_eff, beta, kconst);
   else
-    lrn_fwd_vec_kernel<SIZE><<<blocks, 256, 0, st>>>((const bf16*)x, (bf16*)out, chunks, C / 8, alpha_eff, beta,
-                                                     kconst);
+    launch_pdl(lrn_fwd_vec_kernel<SIZE>, blocks, 256, 0, st, (const bf16*)x, (bf16*)out, chunks, C / 8, alpha_eff,
+               beta, kconst);
   return RB_LAUNCH_OK();
 }
 
@@ -216,7 +221,8 @@ int rb_lrn_fwd(const void* x, void* y, long long pixels, int C, int size, float 
   const int blocks = (int)((pixels + LRN_PIX - 1) / LRN_PIX);
   const size_t smem = (size_t)LRN_PIX * C * sizeof(float);
   if (smem > 48 * 1024) return -10;
-  lrn_fwd_kernel<<<blocks, 256, smem, st>>>((const bf16*)x, (bf16*)y, pixels, C, size, alpha_eff, beta, kconst);
+  launch_pdl(lrn_fwd_kernel, blocks, 256, smem, st, (const bf16*)x, (bf16*)y, pixels, C, size, alpha_eff, beta,
+             kconst);
   return RB_LAUNCH_OK();
 }
 
@@ -227,8 +233,8 @@ int rb_lrn_bwd(const void* x, const void* dy, void* dx, const void* mask_src, lo
   const int blocks = (int)((pixels + LRN_PIX - 1) / LRN_PIX);
   const size_t smem = (size_t)3 * LRN_PIX * C * sizeof(float);
   if (smem > 48 * 1024) return -10;
-  lrn_bwd_kernel<<<blocks, 256, smem, st>>>((const bf16*)x, (const bf16*)dy, (bf16*)dx, (const bf16*)mask_src, pixels,
-                                            C, size, alpha_eff, beta, kconst);
+  launch_pdl(lrn_bwd_kernel, blocks, 256, smem, st, (const bf16*)x, (const bf16*)dy, (bf16*)dx, (const bf16*)mask_src,
+             pixels, C, size, alpha_eff, beta, kconst);
   return RB_LAUNCH_OK();
 }
 

@@ -4,6 +4,7 @@
 // full window size (padding counted), as cuDNN's AverageCountIncludingPadding does
 // (src/operator/mod.rs:2053-2066). Max pooling records the window offset of the (first) maximum in
 // one byte per output so that the backward pass is an exact gather with no atomics.
+#include "launch.cuh"
 #include <cstdlib>
 
 #include "common.cuh"
@@ -13,6 +14,7 @@ namespace rb {
 template <typename IT>
 __global__ void maxpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, uint8_t* __restrict__ idx, int N,
                                    int H, int W, int C, int P, int Q, int k, int stride, int pad, int relu) {
+  pdl_prolog();
   const int cv = C / 8;
   const IT total = (IT)N * P * Q * cv;
   for (IT i = (IT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IT)gridDim.x * blockDim.x) {
@@ -57,6 +59,7 @@ template <typename IT>
 __global__ void maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* __restrict__ idx, bf16* __restrict__ dx,
                                    const bf16* __restrict__ mask_src, int N, int H, int W, int C, int P, int Q,
                                    int k, int stride, int pad) {
+  pdl_prolog();
   const int cv = C / 8;
   const IT total = (IT)N * H * W * cv;
   for (IT i = (IT)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (IT)gridDim.x * blockDim.x) {
@@ -104,6 +107,7 @@ __global__ void maxpool_bwd_kernel(const bf16* __restrict__ dy, const uint8_t* _
 template <typename IT>
 __global__ void avgpool_fwd_kernel(const bf16* __restrict__ x, bf16* __restrict__ y, int N, int H, int W, int C, int P,
                                    int Q, int k, int stride, int pad, int relu) {
+  pdl_prolog();
   const int cv = C / 8;
   const IT total = (IT)N * P * Q * cv;
   const float inv = 1.f / (float)(k * k);
@@ -143,6 +147,7 @@ template <typename IT>
 __global__ void avgpool_bwd_kernel(const bf16* __restrict__ dy, const bf16* __restrict__ y_relu,
                                    bf16* __restrict__ dx, const bf16* __restrict__ mask_src, int N, int H, int W,
                                    int C, int P, int Q, int k, int stride, int pad) {
+  pdl_prolog();
   const int cv = C / 8;
   const IT total = (IT)N * H * W * cv;
   const float inv = 1.f / (float)(k * k);
@@ -202,6 +207,7 @@ __global__ void __launch_bounds__(256) maxpool_fwd_rows_kernel(const bf16* __res
                                                                uint8_t* __restrict__ idx, int H, int W, int C, int P,
                                                                int Q, int k_rt, int stride_rt, int pad, int relu,
                                                                uint32_t cv_magic) {
+  pdl_prolog();
   const int k = KK ? KK : k_rt, stride = SS ? SS : stride_rt;
   const int cv = C / 8;
   const int n = blockIdx.x / P, p = blockIdx.x - n * P;
@@ -267,6 +273,7 @@ __global__ void __launch_bounds__(256) maxpool_bwd_rows_kernel(const bf16* __res
                                                                const bf16* __restrict__ mask_src, int H, int W, int C,
                                                                int P, int Q, int k_rt, int stride_rt, int pad,
                                                                uint32_t cv_magic) {
+  pdl_prolog();
   const int k = KK ? KK : k_rt, stride = SS ? SS : stride_rt;
   const int cv = C / 8;
   const int n = blockIdx.x / H, h = blockIdx.x - n * H;
@@ -328,29 +335,31 @@ int rb_pool_fwd(const void* x, void* y, void* idx, int N, int H, int W, int C, i
   if (C % 8) return -10;
   const long long total = (long long)N * P * Q * (C / 8);
   const bool small = (long long)N * (H > P ? H : P) * (W > Q ? W : Q) * C < 0x7FFFFFFFll;  // 32-bit index math
-#define RB_POOL_FWD(IT)                                                                                              \
-  if (is_max)                                                                                                        \
-    maxpool_fwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, \
-                                                                P, Q, k, stride, pad, relu);                         \
-  else                                                                                                               \
-    avgpool_fwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)x, (bf16*)y, N, H, W, C, P, Q, k,       \
-                                                                stride, pad, relu);
+  // generic kernels with 32- or 64-bit index arithmetic
+  auto generic = [&](auto maxk, auto avgk) {
+    if (is_max)
+      launch_pdl(maxk, grid_for(total, 256), 256, 0, st, (const bf16*)x, (bf16*)y, (uint8_t*)idx, N, H, W, C, P, Q, k,
+                 stride, pad, relu);
+    else
+      launch_pdl(avgk, grid_for(total, 256), 256, 0, st, (const bf16*)x, (bf16*)y, N, H, W, C, P, Q, k, stride, pad,
+                 relu);
+  };
   const int cv = C / 8;
   if (is_max && small && !getenv("RB_POOL_GENERIC") && Q * cv >= 64 && Q * cv < 65536 && (long long)N * P < 0x7FFFFFFF) {
     const int threads = Q * cv >= 256 ? 256 : (Q * cv + 31) / 32 * 32;
     const uint32_t magic = (uint32_t)((0x100000000ull + cv - 1) / cv);
-#define RB_FWD_ROWS(KK, SS)                                                                                \
-  maxpool_fwd_rows_kernel<KK, SS><<<N * P, threads, 0, st>>>((const bf16*)x, (bf16*)y, (uint8_t*)idx, H, W, C, P, Q, \
-                                                            k, stride, pad, relu, magic)
-    if (k == 3 && stride == 2) RB_FWD_ROWS(3, 2);
-    else if (k == 2 && stride == 2) RB_FWD_ROWS(2, 2);
-    else if (k == 3 && stride == 1) RB_FWD_ROWS(3, 1);
-    else RB_FWD_ROWS(0, 0);
-#undef RB_FWD_ROWS
+    auto rows = [&](auto kern) {
+      launch_pdl(kern, N * P, threads, 0, st, (const bf16*)x, (bf16*)y, (uint8_t*)idx, H, W, C, P, Q, k, stride, pad,
+                 relu, magic);
+    };
+    if (k == 3 && stride == 2) rows(maxpool_fwd_rows_kernel<3, 2>);
+    else if (k == 2 && stride == 2) rows(maxpool_fwd_rows_kernel<2, 2>);
+    else if (k == 3 && stride == 1) rows(maxpool_fwd_rows_kernel<3, 1>);
+    else rows(maxpool_fwd_rows_kernel<0, 0>);
     return RB_LAUNCH_OK();
   }
-  if (small) { RB_POOL_FWD(unsigned int) } else { RB_POOL_FWD(long long) }
-#undef RB_POOL_FWD
+  if (small) generic(maxpool_fwd_kernel<unsigned int>, avgpool_fwd_kernel<unsigned int>);
+  else generic(maxpool_fwd_kernel<long long>, avgpool_fwd_kernel<long long>);
   return RB_LAUNCH_OK();
 }
 
@@ -359,32 +368,30 @@ int rb_pool_bwd(const void* dy, const void* idx, const void* y_relu, void* dx, c
   if (C % 8) return -10;
   const long long total = (long long)N * H * W * (C / 8);
   const bool small = (long long)N * (H > P ? H : P) * (W > Q ? W : Q) * C < 0x7FFFFFFFll;
-#define RB_POOL_BWD(IT)                                                                                               \
-  if (is_max)                                                                                                         \
-    maxpool_bwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const uint8_t*)idx, (bf16*)dx,      \
-                                                                (const bf16*)mask_src, N, H, W, C, P, Q, k, stride,   \
-                                                                pad);                                                 \
-  else                                                                                                                \
-    avgpool_bwd_kernel<IT><<<grid_for(total, 256), 256, 0, st>>>((const bf16*)dy, (const bf16*)y_relu, (bf16*)dx,      \
-                                                                (const bf16*)mask_src, N, H, W, C, P, Q, k, stride,   \
-                                                                pad);
+  auto generic = [&](auto maxk, auto avgk) {
+    if (is_max)
+      launch_pdl(maxk, grid_for(total, 256), 256, 0, st, (const bf16*)dy, (const uint8_t*)idx, (bf16*)dx,
+                 (const bf16*)mask_src, N, H, W, C, P, Q, k, stride, pad);
+    else
+      launch_pdl(avgk, grid_for(total, 256), 256, 0, st, (const bf16*)dy, (const bf16*)y_relu, (bf16*)dx,
+                 (const bf16*)mask_src, N, H, W, C, P, Q, k, stride, pad);
+  };
   const int cv = C / 8;
   if (is_max && small && !getenv("RB_POOL_GENERIC") && W * cv >= 64 && W * cv < 65536 && (long long)N * H < 0x7FFFFFFF) {
     const int threads = W * cv >= 256 ? 256 : (W * cv + 31) / 32 * 32;
     const uint32_t magic = (uint32_t)((0x100000000ull + cv - 1) / cv);
-#define RB_BWD_ROWS(KK, SS)                                                                              \
-  maxpool_bwd_rows_kernel<KK, SS><<<N * H, threads, 0, st>>>((const bf16*)dy, (const uint8_t*)idx, (bf16*)dx,       \
-                                                            (const bf16*)mask_src, H, W, C, P, Q, k, stride, pad, \
-                                                            magic)
-    if (k == 3 && stride == 2) RB_BWD_ROWS(3, 2);
-    else if (k == 2 && stride == 2) RB_BWD_ROWS(2, 2);
-    else if (k == 3 && stride == 1) RB_BWD_ROWS(3, 1);
-    else RB_BWD_ROWS(0, 0);
-#undef RB_BWD_ROWS
+    auto rows = [&](auto kern) {
+      launch_pdl(kern, N * H, threads, 0, st, (const bf16*)dy, (const uint8_t*)idx, (bf16*)dx, (const bf16*)mask_src,
+                 H, W, C, P, Q, k, stride, pad, magic);
+    };
+    if (k == 3 && stride == 2) rows(maxpool_bwd_rows_kernel<3, 2>);
+    else if (k == 2 && stride == 2) rows(maxpool_bwd_rows_kernel<2, 2>);
+    else if (k == 3 && stride == 1) rows(maxpool_bwd_rows_kernel<3, 1>);
+    else rows(maxpool_bwd_rows_kernel<0, 0>);
     return RB_LAUNCH_OK();
   }
-  if (small) { RB_POOL_BWD(unsigned int) } else { RB_POOL_BWD(long long) }
-#undef RB_POOL_BWD
+  if (small) generic(maxpool_bwd_kernel<unsigned int>, avgpool_bwd_kernel<unsigned int>);
+  else generic(maxpool_bwd_kernel<long long>, avgpool_bwd_kernel<long long>);
   return RB_LAUNCH_OK();
 }
 

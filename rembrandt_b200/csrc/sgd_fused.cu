@@ -4,6 +4,7 @@
 // update_params / reset, src/operator/mod.rs:1178-1363 and src/opt/sgd/new.rs:358-495).
 //
 // The rules themselves are in sgd_rules.cuh.
+#include "launch.cuh"
 #include "common.cuh"
 #include "sgd_rules.cuh"
 
@@ -18,6 +19,7 @@ struct SgdArgs : SgdHyper {
 };
 
 __global__ void sgd_fused_kernel(SgdArgs a) {
+  pdl_prolog();
   const long long n4 = a.n / 4;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
        i += (long long)gridDim.x * blockDim.x) {
@@ -54,6 +56,7 @@ __global__ void sgd_fused_kernel(SgdArgs a) {
 // w += s * v (Nesterov look-ahead bookkeeping before the first step), refreshing the bf16 copy.
 __global__ void axpy_shadow_kernel(float* __restrict__ w, const float* __restrict__ v, bf16* __restrict__ w16,
                                    long long n, float s) {
+  pdl_prolog();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     float x = w[i];
     if (v) x += s * v[i];
@@ -64,6 +67,7 @@ __global__ void axpy_shadow_kernel(float* __restrict__ w, const float* __restric
 
 // y = a*x + b*y on fp32 ranges (exact averaging, elastic mixes on one device, snapshots)
 __global__ void axpby_kernel(const float* __restrict__ x, float* __restrict__ y, long long n, float a, float b) {
+  pdl_prolog();
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
     y[i] = a * x[i] + b * y[i];
 }
@@ -83,7 +87,7 @@ int rb_sgd_fused(float* w, float* g, float* v, void* w16, long long n, float lr,
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  sgd_fused_kernel<<<(int)blocks, 256, 0, st>>>(a);
+  launch_pdl(sgd_fused_kernel, (int)blocks, 256, 0, st, a);
   return RB_LAUNCH_OK();
 }
 
@@ -98,7 +102,7 @@ int rb_sgd_fused_grid(float* w, float* g, float* v, void* w16, long long n, floa
   a.w = w; a.g = g; a.v = v; a.w16 = (bf16*)w16; a.n = n;
   const long long need = (n / 4 + threads - 1) / threads;
   if (need < blocks) blocks = need < 1 ? 1 : (int)need;
-  sgd_fused_kernel<<<blocks, threads, 0, st>>>(a);
+  launch_pdl(sgd_fused_kernel, blocks, threads, 0, st, a);
   return RB_LAUNCH_OK();
 }
 
@@ -106,7 +110,7 @@ int rb_axpy_shadow(float* w, const float* v, void* w16, long long n, float s, cu
   if (n <= 0) return 0;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  axpy_shadow_kernel<<<(int)blocks, 256, 0, st>>>(w, v, (bf16*)w16, n, s);
+  launch_pdl(axpy_shadow_kernel, (int)blocks, 256, 0, st, w, v, (bf16*)w16, n, s);
   return RB_LAUNCH_OK();
 }
 
@@ -114,7 +118,7 @@ int rb_axpby(const float* x, float* y, long long n, float a, float b, cudaStream
   if (n <= 0) return 0;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  axpby_kernel<<<(int)blocks, 256, 0, st>>>(x, y, n, a, b);
+  launch_pdl(axpby_kernel, (int)blocks, 256, 0, st, x, y, n, a, b);
   return RB_LAUNCH_OK();
 }
 

@@ -3,6 +3,7 @@
 // Replaces the reference's cuDNN softmax + batch_map_softmax_kl_backward + batch_map_softmax_kl_loss1 +
 // batch_blockreduce_sum + batch_blockreduce_argmax sequence (src/operator/loss.rs:118-237), without its
 // K <= 1024 and B <= 1024 limits.
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -20,6 +21,7 @@ __global__ void softmax_ce_kernel(const bf16* __restrict__ logits, int B, int K,
                                   int* __restrict__ correct, float* __restrict__ loss_per, int* __restrict__ argmax_out,
                                   const float* __restrict__ cat_weights, const uint8_t* __restrict__ mask,
                                   const float* __restrict__ soft) {
+  pdl_prolog();
   const int warps_per_block = blockDim.x >> 5;
   const int r = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -105,6 +107,7 @@ __global__ void categorical_obj_kernel(const bf16* __restrict__ x, int B, int K,
                                        int* __restrict__ correct, int* __restrict__ argmax_out,
                                        const uint8_t* __restrict__ mask, const float* __restrict__ target_w,
                                        int objective) {
+  pdl_prolog();
   const int warps_per_block = blockDim.x >> 5;
   const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -180,6 +183,7 @@ __global__ void categorical_obj_kernel(const bf16* __restrict__ x, int B, int K,
 __global__ void sample_categories_kernel(const bf16* __restrict__ x, int B, int K, int ld,
                                          const uint8_t* __restrict__ mask, float inv_temperature, uint64_t seed,
                                          uint32_t step, int* __restrict__ out) {
+  pdl_prolog();
   const int warps_per_block = blockDim.x >> 5;
   const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -226,6 +230,7 @@ __global__ void sample_categories_kernel(const bf16* __restrict__ x, int B, int 
 __global__ void pointwise_loss_kernel(const bf16* __restrict__ x, int B, int K, int ld, const float* __restrict__ target,
                                       const float* __restrict__ weights, float w_scalar, bf16* __restrict__ delta,
                                       float* __restrict__ loss_sum, int* __restrict__ correct, int mode) {
+  pdl_prolog();
   const int warps_per_block = blockDim.x >> 5;
   const int b = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -270,9 +275,9 @@ int rb_softmax_ce(const void* logits, int B, int K, int ld, int L, const int* la
                   int* argmax_out, const float* cat_weights, const void* mask, const float* soft, cudaStream_t st) {
   if (L < 1 || (long long)L * K > ld) return -10;
   const int wpb = 4;
-  softmax_ce_kernel<<<(B * L + wpb - 1) / wpb, wpb * 32, 0, st>>>(
-      (const bf16*)logits, B, K, ld, L, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, loss_per,
-      argmax_out, cat_weights, (const uint8_t*)mask, soft);
+  launch_pdl(softmax_ce_kernel, (B * L + wpb - 1) / wpb, wpb * 32, 0, st, (const bf16*)logits, B, K, ld, L, labels,
+             weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, loss_per, argmax_out, cat_weights,
+             (const uint8_t*)mask, soft);
   return RB_LAUNCH_OK();
 }
 
@@ -282,9 +287,8 @@ int rb_categorical_loss(const void* x, int B, int K, int ld, const int* labels, 
   if (objective < 1 || objective > 3 || K > ld || (!labels && !target_w)) return -10;
   if (objective != 1 && target_w) return -10;      // the marginalised form exists for the softmax indicator only
   const int wpb = 4;
-  categorical_obj_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>(
-      (const bf16*)x, B, K, ld, labels, weights, w_scalar, (bf16*)delta, probs, loss_sum, correct, argmax_out,
-      (const uint8_t*)mask, target_w, objective);
+  launch_pdl(categorical_obj_kernel, (B + wpb - 1) / wpb, wpb * 32, 0, st, (const bf16*)x, B, K, ld, labels, weights,
+             w_scalar, (bf16*)delta, probs, loss_sum, correct, argmax_out, (const uint8_t*)mask, target_w, objective);
   return RB_LAUNCH_OK();
 }
 
@@ -292,8 +296,8 @@ int rb_sample_categories(const void* x, int B, int K, int ld, const void* mask, 
                          unsigned long long seed, unsigned int step, int* out, cudaStream_t st) {
   if (K > ld || !(temperature > 0.f)) return -10;
   const int wpb = 4;
-  sample_categories_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>((const bf16*)x, B, K, ld, (const uint8_t*)mask,
-                                                                    1.f / temperature, seed, step, out);
+  launch_pdl(sample_categories_kernel, (B + wpb - 1) / wpb, wpb * 32, 0, st, (const bf16*)x, B, K, ld,
+             (const uint8_t*)mask, 1.f / temperature, seed, step, out);
   return RB_LAUNCH_OK();
 }
 
@@ -301,8 +305,8 @@ int rb_pointwise_loss(const void* x, int B, int K, int ld, const float* target, 
                       void* delta, float* loss_sum, int* correct, int mode, cudaStream_t st) {
   if (mode < 0 || mode > 1 || K > ld) return -10;
   const int wpb = 4;
-  pointwise_loss_kernel<<<(B + wpb - 1) / wpb, wpb * 32, 0, st>>>((const bf16*)x, B, K, ld, target, weights, w_scalar,
-                                                                 (bf16*)delta, loss_sum, correct, mode);
+  launch_pdl(pointwise_loss_kernel, (B + wpb - 1) / wpb, wpb * 32, 0, st, (const bf16*)x, B, K, ld, target, weights,
+             w_scalar, (bf16*)delta, loss_sum, correct, mode);
   return RB_LAUNCH_OK();
 }
 

@@ -10,6 +10,7 @@
 // Source layout: sample n starts at src + n * in_stride and holds C planes of h x w bytes (x fastest), with
 // (w, h) = shapes[n]. Taps outside the source image are clamped to its border; crop windows that reach outside the
 // rescaled image (source too small) read zeros there.
+#include "launch.cuh"
 #include "common.cuh"
 
 namespace rb {
@@ -43,6 +44,7 @@ __device__ __forceinline__ void catmull_rom(float t, float (&w)[4]) {
 }
 
 __global__ void __launch_bounds__(256) var_input_kernel(const __grid_constant__ VarInputArgs a) {
+  pdl_prolog();
   const long long total = (long long)a.N * a.crop_h * a.crop_w;
   const uint32_t step = a.step + (a.step_ptr ? *a.step_ptr : 0u);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
@@ -167,7 +169,7 @@ int rb_var_input_u8(const void* src, const int* shapes, void* dst, int* draws, l
   long long blocks = (total + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
   if (blocks < 1) blocks = 1;
-  var_input_kernel<<<(int)blocks, 256, 0, st>>>(a);
+  launch_pdl(var_input_kernel, (int)blocks, 256, 0, st, a);
   return RB_LAUNCH_OK();
 }
 

@@ -473,6 +473,10 @@ def axpy_shadow(w, v, w16, n, s):
         w16[:n].copy_(w[:n])
 
 
+def gemm_set_option(name, value):
+    """Planner switches do nothing on the emulated path."""
+
+
 def _unsupported(name):
     def fn(*a, **k):
         raise NotImplementedError(f"kernel front {name} has no CPU stand-in")
@@ -484,7 +488,7 @@ EMULATED = {f.__name__: f for f in (conv_fprop_tc, conv_wgrad_tc, conv_direct_fw
                                     colsum, relu_mask, add_bf16, f32_to_bf16, act_fwd, act_bwd, pool_fwd, pool_bwd,
                                     softmax_ce, input_u8, sgd_fused, bn_fwd_train, bn_fwd_infer, bn_bwd,
                                     pointwise_loss, categorical_loss, lrn_fwd, lrn_bwd, dropout, var_input_u8, sgd_fused_grid,
-                                    axpy_shadow)}
+                                    axpy_shadow, gemm_set_option)}
 
 
 def install(monkeypatch):
