@@ -51,7 +51,8 @@ def base_parser(desc, **defaults):
                     help="exchange backend: auto (fused_allreduce_sgd on GPUs, allreduce on CPU ranks) | kernel backends "
                          "fused_allreduce_sgd, gossip_p2p, gossip_pull_p2p, gossip_push_p2p, group_allreduce_gossip_p2p, "
                          "elastic_p2p | library backends allreduce, gossip_pair, gossip_pull, gossip_push, "
-                         "group_allreduce_gossip, elastic | null")
+                         "group_allreduce_gossip, elastic, and on CPU ranks their asynchronous forms gossip_push_async, "
+                         "elastic_async | null")
     ap.add_argument("--sync-order", choices=sorted(ORDERS), default=None)
     ap.add_argument("--comm-interval", type=int, default=1)
     ap.add_argument("--step-ref", choices=["local", "checkpoint"], default="local",
@@ -193,6 +194,7 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
     history = sgd.train(_repeat(train_iter), valid_iter, max_iters=args.iters)
     if valid_iter is not None and args.valid_iters:
         sgd.validate(valid_iter, args.valid_iters, engine.iter)
+    worker.close()
     if dist.is_initialized():
         dist.barrier()
         dist.destroy_process_group()

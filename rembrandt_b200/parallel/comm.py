@@ -18,10 +18,12 @@ backend                     reference component
 ``PullGossipComm``          pull from uniformly random peers, ``num_rounds``, ``repeat``
                             (worker/gossip_pull_dist_rdma.rs:517-589)
 ``PushGossipComm``          push to a uniformly random target, count-normalised mean
-                            (worker/gossip_dist.rs:883-976)
+                            (worker/gossip_dist.rs:883-976); ``asynchronous=True``: a receiving thread
+                            accumulates whatever arrives, nobody waits (worker/gossip_dist.rs:474-593)
 ``GroupAllreduceGossipComm``group all-reduce + pull gossip between groups (gossip_pull_allreduce_dist_rdma*.rs)
 ``ElasticComm``             elastic averaging against a centre held by rank 0, beta = 0.8/N
-                            (worker/elasticserver_dist.rs:249-255,711-715)
+                            (worker/elasticserver_dist.rs:249-255,711-715); ``asynchronous=True``: a serving
+                            thread on rank 0 handles one client at a time, in the order they ask
 ==========================  ================================================================================
 
 The backends in this file use ``torch.distributed`` collectives (gloo on CPU ranks, NCCL on GPUs); they define
@@ -30,8 +32,9 @@ one CUDA kernel live in ``parallel/p2p.py`` and subclass these.
 """
 from __future__ import annotations
 
+import threading
 from dataclasses import dataclass
-from typing import List, Optional, Sequence
+from typing import Callable, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -121,6 +124,10 @@ class CommWorker:
 
     def wait_barrier(self) -> bool:
         return True
+
+    def close(self) -> None:
+        """Stop background threads and drain messages in flight. Collective: every rank calls it once, after its
+        last exchange. Nothing to do for the lock-step backends."""
 
 
 class NullComm(CommWorker):
@@ -344,19 +351,143 @@ class PullGossipComm(CommWorker):
     allreduce_average = CommWorker.exact_sync
 
 
+class _NoLock:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+_NO_LOCK = _NoLock()
+
+
+class _Inbox(threading.Thread):
+    """Background receiver of the asynchronous library backends: the reference's passive thread
+    (worker/gossip_dist.rs:474-593, worker/elasticserver_dist.rs:249-255).
+
+    It blocks in a receive from ANY rank on a process group of its own (so its traffic never meets the main
+    thread's collectives), hands every message of `n` floats to `on_message(sender, payload)`, and ends after it
+    has seen one closing message from each of the `world - 1` peers. Messages of one sender arrive in the order
+    sent, so by then everything that sender pushed earlier has been handled. The last element of a message is
+    its kind: >= 0 data, < 0 closing."""
+
+    def __init__(self, group, world: int, n: int, dtype, on_message: Callable[[int, torch.Tensor], None]):
+        super().__init__(daemon=True, name="rb-comm-inbox")
+        self.group, self.world, self.n, self.on_message = group, world, n, on_message
+        self.buf = torch.empty(n + 1, dtype=dtype)
+        self.error: Optional[BaseException] = None
+
+    def run(self):
+        closed = 0
+        try:
+            while closed < self.world - 1:
+                sender = dist.recv(self.buf, group=self.group)
+                if float(self.buf[self.n]) < 0:
+                    closed += 1
+                else:
+                    self.on_message(dist.get_group_rank(self.group, sender), self.buf[:self.n])
+        except BaseException as e:      # surfaced by the owner's next call
+            self.error = e
+
+
+def _async_group(group):
+    """A gloo group over the same ranks for one-sided style traffic. Receiving from any source exists in gloo only;
+    on GPUs the asynchronous exchanges are the kernel backends of ``parallel/p2p.py``."""
+    if dist.get_backend(group) != "gloo":
+        raise ValueError("the asynchronous library backends need gloo (CPU ranks); on GPUs use the kernel "
+                         "backends gossip_push_p2p / elastic_p2p, which are asynchronous by default")
+    ranks = dist.get_process_group_ranks(group) if group is not None else list(range(dist.get_world_size()))
+    return dist.new_group(ranks, backend="gloo")
+
+
 class PushGossipComm(CommWorker):
     """Each rank pushes its vector to a uniformly random target; a rank that received k vectors keeps
-    (w_self * own + sum received) / (w_self + k) with w_self = 2 if it targeted itself, else 1."""
+    (w_self * own + sum received) / (w_self + k) with w_self = 2 if it targeted itself, else 1.
+
+    Lock-step by default: the ranks agree on the round's targets and every push of a round is folded in that
+    round. ``asynchronous=True`` is the reference's form (worker/gossip_dist.rs:474-593, 883-976): a background
+    thread adds whatever arrives, from whichever rank, into an accumulator and counts it; an exchange pushes to
+    its target and folds in what has arrived since the last one (possibly nothing). No rank waits for another.
+    It needs gloo and a `close()` by every rank at the end."""
     name = "gossip_push"
 
-    def __init__(self, group=None, seed=(41, 43)):
+    def __init__(self, group=None, seed=(41, 43), asynchronous: bool = False):
         super().__init__(group)
         self.rng = XorShift128Plus(seed[0] + 7919 * self.rank, seed[1])
         self._global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+        self.asynchronous = bool(asynchronous) and self.world > 1
+        self.synchronous = not self.asynchronous
+        self.folded = 0               # vectors folded in so far (asynchronous form)
+        self._inbox = None
+        if self.asynchronous:
+            self._pg = _async_group(group)
+            self._lock = threading.Lock()
+            self._acc, self._count, self._msg = None, 0, None
 
+    # ---- asynchronous form
+    def _on_push(self, sender: int, payload: torch.Tensor) -> None:
+        with self._lock:
+            self._acc.add_(payload)
+            self._count += 1
+
+    def _start(self, flat: torch.Tensor) -> None:
+        n = flat.numel()
+        self._acc = torch.zeros(n, dtype=flat.dtype)
+        self._msg = torch.empty(n + 1, dtype=flat.dtype)
+        self._inbox = _Inbox(self._pg, self.world, n, flat.dtype, self._on_push)
+        self._inbox.start()
+
+    def _sync_async(self, flat: torch.Tensor) -> None:
+        if self._inbox is None:
+            self._start(flat)
+        if self._inbox.error is not None:
+            raise RuntimeError("push gossip: the receiving thread stopped") from self._inbox.error
+        n = flat.numel()
+        target = self.rng.below(self.world)
+        if target != self.rank:
+            self._msg[:n].copy_(flat.reshape(-1))
+            self._msg[n] = 1.0
+            dist.send(self._msg, dist.get_global_rank(self._pg, target), group=self._pg)
+        w_self = 2.0 if target == self.rank else 1.0
+        with self._lock:
+            k = self._count
+            if k:
+                flat.mul_(w_self).add_(self._acc.view_as(flat)).div_(w_self + k)
+                self._acc.zero_()
+                self._count = 0
+        self.folded += k
+        self.bytes_moved += n * 4
+
+    def close(self) -> None:
+        if not self.asynchronous or self._inbox is None:
+            return
+        self._msg[self._msg.numel() - 1] = -1.0
+        for r in range(self.world):
+            if r != self.rank:
+                dist.send(self._msg, dist.get_global_rank(self._pg, r), group=self._pg)
+        self._inbox.join()
+        self._inbox = None
+
+    def first_one_way_sync(self, flat: torch.Tensor) -> None:
+        """Asynchronous form: start listening before any rank can push (every rank calls this before training)."""
+        if self.asynchronous and self._inbox is None:
+            self._start(flat)
+            dist.barrier(group=self.group)
+
+    def pending(self) -> int:
+        """Vectors that have arrived and are not folded in yet (asynchronous form)."""
+        if not self.asynchronous or self._acc is None:
+            return 0
+        with self._lock:
+            return self._count
+
+    # ---- lock-step form
     def sync_params(self, flat, repeat=False):
         if self.world <= 1:
             return
+        if self.asynchronous:
+            return self._sync_async(flat)
         target = self.rng.below(self.world)
         targets = [None] * self.world
         dist.all_gather_object(targets, target, group=self.group)
@@ -428,24 +559,87 @@ class GroupAllreduceGossipComm(CommWorker):
 
 class ElasticComm(CommWorker):
     """Elastic averaging SGD: the centre variable lives on rank 0. On each exchange a client reads the centre,
-    both move toward each other:  centre += beta (x - centre_read),  x = (1-beta) x + beta centre_read."""
+    both move toward each other:  centre += beta (x - centre_read),  x = (1-beta) x + beta centre_read.
+
+    Lock-step by default (every client mixes with the same centre snapshot of the round). ``asynchronous=True``
+    is the reference's server (worker/elasticserver_dist.rs:249-255, 667-715): a thread on rank 0 takes one
+    client's vector at a time, from whichever client asks, answers with the centre as it is then and moves the
+    centre toward that client; no client waits for another. `request_log` on rank 0 lists the clients in the
+    order served, which makes a run replayable. It needs gloo and a `close()` by every rank at the end."""
     name = "elastic"
 
-    def __init__(self, group=None, beta: Optional[float] = None):
+    def __init__(self, group=None, beta: Optional[float] = None, asynchronous: bool = False):
         super().__init__(group)
         self.beta = beta if beta is not None else 0.8 / max(1, self.world)
         self.center = None
+        self.asynchronous = bool(asynchronous) and self.world > 1
+        self.synchronous = not self.asynchronous
+        self.request_log: List[int] = []
+        self._inbox = None
+        if self.asynchronous:
+            self._pg = _async_group(group)
+            self._lock = threading.Lock()
+            self._msg = None
 
     def first_one_way_sync(self, flat):
         """Rank 0's parameters become the centre; every rank starts from it."""
         if self.world > 1:
             dist.broadcast(flat, 0, group=self.group)
+        if self.asynchronous and self.rank != 0 and self._msg is None:
+            self._msg = torch.zeros(flat.numel() + 1, dtype=flat.dtype)
         if self.rank == 0:
             self.center = flat.clone()
+            if self.asynchronous and self._inbox is None:
+                self._inbox = _Inbox(self._pg, self.world, flat.numel(), flat.dtype, self._serve)
+                self._inbox.start()
 
+    # ---- asynchronous form
+    def _mix_center(self, client: int, x: torch.Tensor) -> torch.Tensor:
+        """Serve one client under the lock: returns the centre as read, then moves it toward `x`."""
+        with self._lock:
+            read = self.center.reshape(-1).clone()
+            self.center.reshape(-1).add_(x.reshape(-1) - read, alpha=self.beta)
+            self.request_log.append(client)
+        return read
+
+    def _serve(self, client: int, payload: torch.Tensor) -> None:
+        read = self._mix_center(client, payload)
+        dist.send(read, dist.get_global_rank(self._pg, client), group=self._pg, tag=1)
+
+    def _sync_async(self, flat: torch.Tensor) -> None:
+        n = flat.numel()
+        if self.rank == 0:
+            if self._inbox is not None and self._inbox.error is not None:
+                raise RuntimeError("elastic averaging: the serving thread stopped") from self._inbox.error
+            read = self._mix_center(0, flat)
+        else:
+            self._msg[:n].copy_(flat.reshape(-1))
+            self._msg[n] = 1.0
+            root = dist.get_global_rank(self._pg, 0)
+            dist.send(self._msg, root, group=self._pg)
+            read = torch.empty(n, dtype=flat.dtype)
+            dist.recv(read, root, group=self._pg, tag=1)
+        flat.mul_(1.0 - self.beta).add_(read.view_as(flat), alpha=self.beta)
+        self.bytes_moved += n * 8
+
+    def close(self) -> None:
+        if not self.asynchronous:
+            return
+        if self.rank != 0:
+            if self._msg is None:
+                return                      # first_one_way_sync never ran: no server is listening
+            self._msg[self._msg.numel() - 1] = -1.0
+            dist.send(self._msg, dist.get_global_rank(self._pg, 0), group=self._pg)
+        elif self._inbox is not None:
+            self._inbox.join()
+            self._inbox = None
+
+    # ---- lock-step form
     def sync_params(self, flat, repeat=False):
         if self.world <= 1:
             return
+        if self.asynchronous:
+            return self._sync_async(flat)
         # every client mixes with the same centre snapshot; the centre receives the sum of the pulls
         center = self.center.clone() if self.rank == 0 else torch.empty_like(flat)
         dist.broadcast(center, 0, group=self.group)
@@ -461,7 +655,8 @@ class ElasticComm(CommWorker):
         if self.world <= 1:
             return
         if self.rank == 0:
-            flat.copy_(self.center)
+            with (self._lock if self.asynchronous else _NO_LOCK):
+                flat.copy_(self.center)
         dist.broadcast(flat, 0, group=self.group)
 
     allreduce_average = CommWorker.exact_sync
@@ -478,6 +673,9 @@ def make_comm(name: str, **kw) -> CommWorker:
     if name == "fused_allreduce_sgd" or name.endswith("_p2p"):
         from . import p2p
         return p2p.make(name, **kw)
+    if name in ("gossip_push_async", "elastic_async"):
+        # the asynchronous forms of the two library backends that have one (gloo ranks only)
+        return table[name[:-len("_async")]](asynchronous=True, **kw)
     if name not in table:
         raise ValueError(f"unknown comm backend {name!r}")
     return table[name](**kw) if name != "null" else NullComm()

@@ -100,6 +100,122 @@ def elastic(rank, world):
     assert torch.allclose(y, center, atol=1e-6)    # exact sync broadcasts the centre
 
 
+def _wait_for(cond, seconds=20.0):
+    t_end = time.time() + seconds
+    while not cond():
+        assert time.time() < t_end, "condition not reached in time"
+        time.sleep(0.002)
+
+
+def push_gossip_async_one_at_a_time(rank, world):
+    """Asynchronous push gossip with one rank exchanging at a time, so that what each exchange folds in is known:
+    every rank replays all ranks' draws, pushes and folds and compares its own vector after each of its exchanges."""
+    c = C.PushGossipComm(seed=(41, 43), asynchronous=True)
+    x = _vec(rank)
+    c.first_one_way_sync(x)
+    shadows = [XorShift128Plus(41 + 7919 * r, 43) for r in range(world)]
+    xs = _all(world)
+    inbox = [[] for _ in range(world)]
+    folded = [0] * world
+    for rnd in range(4 * world):
+        a = rnd % world
+        target = shadows[a].below(world)
+        if target != a:
+            inbox[target].append(xs[a].clone())
+        if rank == a:
+            _wait_for(lambda: c.pending() == len(inbox[a]))     # the earlier pushes to this rank have all arrived
+            c.sync_params(x)
+        w_self = 2.0 if target == a else 1.0
+        if inbox[a]:
+            xs[a] = (w_self * xs[a] + sum(inbox[a])) / (w_self + len(inbox[a]))
+            folded[a] += len(inbox[a])
+            inbox[a] = []
+        if rank == a:
+            assert torch.allclose(x, xs[a], atol=1e-6), f"exchange {rnd}"
+            assert c.folded == folded[a]
+        dist.barrier()
+    c.close()
+    assert c.pending() == len(inbox[rank])                      # close() returns once every push has arrived
+
+
+def push_gossip_async_nobody_waits(rank, world):
+    """Free-running asynchronous push gossip with a rank that sleeps 50 ms before each of its exchanges: the other
+    ranks finish their exchanges in a fraction of the sleeper's time, vectors stay convex combinations of the
+    initial ones, and after close() every pushed vector is accounted for (folded or still pending)."""
+    rounds, nap = 24, 0.05
+    c = C.PushGossipComm(seed=(5, 11), asynchronous=True)
+    x = torch.full((1031,), float(rank))
+    c.first_one_way_sync(x)
+    t0 = time.time()
+    for _ in range(rounds):
+        if rank == 1:
+            time.sleep(nap)
+        c.sync_params(x)
+        assert float(x.min()) >= -1e-5 and float(x.max()) <= world - 1 + 1e-5
+    mine = time.time() - t0
+    c.close()
+    shadows = [XorShift128Plus(5 + 7919 * r, 11) for r in range(world)]
+    pushed_here = sum(1 for r in range(world) if r != rank for _ in range(rounds) if shadows[r].below(world) == rank)
+    assert c.folded + c.pending() == pushed_here
+    if rank != 1:
+        assert mine < 0.5 * rounds * nap, f"rank {rank} took {mine:.2f} s: it waited for the sleeping rank"
+
+
+def elastic_async_replay(rank, world):
+    """Asynchronous elastic averaging, free-running: rank 0's log of the order in which clients were served,
+    replayed sequentially, reproduces the centre and every client's vector."""
+    rounds = 6
+    c = C.ElasticComm(asynchronous=True)
+    beta = c.beta
+    x = _vec(rank)
+    c.first_one_way_sync(x)
+    for k in range(rounds):
+        x += 0.1 * _vec(rank, rnd=20 + k)
+        if rank == 2:
+            time.sleep(0.01)
+        c.sync_params(x)
+    c.close()
+    finals = [torch.zeros_like(x) for _ in range(world)]
+    dist.all_gather(finals, x)
+    if rank == 0:
+        log = c.request_log
+        assert sorted(log) == sorted(list(range(world)) * rounds)
+        center = _vec(0)
+        xs = [center.clone() for _ in range(world)]
+        served = [0] * world
+        for client in log:
+            xs[client] = xs[client] + 0.1 * _vec(client, rnd=20 + served[client])
+            served[client] += 1
+            read = center.clone()
+            center = center + beta * (xs[client] - read)
+            xs[client] = (1 - beta) * xs[client] + beta * read
+        assert torch.allclose(c.center, center, atol=1e-5)
+        for r in range(world):
+            assert torch.allclose(finals[r], xs[r], atol=1e-5), f"client {r}"
+    y = torch.zeros_like(x)
+    c.exact_sync(y)                                             # still a plain broadcast of the centre
+    ref = [torch.zeros_like(y) for _ in range(world)]
+    dist.all_gather(ref, y)
+    assert all(torch.equal(ref[0], t) for t in ref)
+
+
+def elastic_async_slow_client(rank, world):
+    """A client that sleeps between its exchanges does not slow the others down."""
+    rounds, nap = 20, 0.05
+    c = C.ElasticComm(asynchronous=True)
+    x = _vec(rank)
+    c.first_one_way_sync(x)
+    t0 = time.time()
+    for _ in range(rounds):
+        if rank == 1:
+            time.sleep(nap)
+        c.sync_params(x)
+    mine = time.time() - t0
+    c.close()
+    if rank != 1:
+        assert mine < 0.5 * rounds * nap, f"rank {rank} took {mine:.2f} s"
+
+
 def hierarchical(rank, world):
     c = C.GroupAllreduceGossipComm(group_size=2, seed=(53, 59))
     x = _vec(rank)
@@ -326,6 +442,51 @@ def _rule_and_order(rank, world, mode_value, order_value, interval=1, accum=1):
     err = np.abs(got - w[rank]).max()
     assert err < 5e-5, (f"{mode.name} x {order.name} (interval {interval}, {accum} batches per iteration): rank {rank} "
                         f"differs from the restatement by {err:.3g}")
+
+
+def barrier_free_loop_with_async_exchanges(rank, world, directory, backend):
+    """The barrier-free optimizer loop over an asynchronous library exchange: ranks run different numbers of
+    iterations per second (rank 1 naps), nobody waits, every rank checkpoints into its own directory, and the
+    replicas end closer to each other than independent runs would."""
+    import os
+
+    from rembrandt_b200.data import BatchIter, RandomSampleDataIter, SyntheticDataSource, partition_shard
+    from rembrandt_b200.engine import StepEngine
+    from rembrandt_b200.models import zoo
+    from rembrandt_b200.models.net import Net
+    from rembrandt_b200.optim.async_sgd import AsyncSgdOpt
+    from rembrandt_b200.optim.sgd import Momentum, SgdOptConfig, StepSizeSchedule, SyncOrder
+
+    src = SyntheticDataSource(256, (28, 28, 1), 10, seed=1, separable=True)
+    comm = C.make_comm(backend)
+    assert comm.asynchronous and not comm.synchronous
+    order = SyncOrder.STEP_THEN_SYNC_PARAMS if "gossip" in backend else SyncOrder.SYNC_PARAMS_THEN_STEP
+    opt = SgdOptConfig(minibatch_size=16, step_size=StepSizeSchedule.constant(0.05), momentum=Momentum.UPDATE, mu=0.9,
+                       l2_reg_coef=1e-4, sync_order=order, display_iters=4, checkpoint_iters=6, save_iters=6,
+                       valid_iters=0, checkpoint_dir=directory)
+    net = Net(zoo.mnist_fc1(), 16, device="cpu", seed=(3, 4), minibatch_size=16)
+    sgd = AsyncSgdOpt(opt, StepEngine(net, opt, comm), quiet=True)
+    train = BatchIter(RandomSampleDataIter(partition_shard(src, rank, world), seed=(9 + rank, 9)), 16, src.dims)
+
+    def forever():
+        while True:
+            for b in train:
+                if rank == 1:
+                    time.sleep(0.02)
+                yield b
+    t0 = time.time()
+    sgd.train(forever(), None, max_iters=12)
+    mine = time.time() - t0
+    sgd.trace.close()
+    comm.close()
+    assert os.path.exists(os.path.join(directory, f"rank{rank}", "params.t_12.blob"))
+    times = [torch.zeros(1, dtype=torch.float64) for _ in range(world)]
+    dist.all_gather(times, torch.tensor([mine], dtype=torch.float64))
+    if rank == 0:
+        assert float(times[1]) >= 12 * 0.02
+    finals = [torch.empty_like(net.params.detach()) for _ in range(world)]
+    dist.all_gather(finals, net.params.detach().clone())
+    assert all(torch.isfinite(f).all() for f in finals)
 
 
 def gossip_training_loop(rank, world, directory):

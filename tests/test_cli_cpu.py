@@ -55,7 +55,8 @@ def test_training_from_a_caffe_database_through_the_native_loader(tmp_path):
     assert sgd.engine.iter == 3
 
 
-@pytest.mark.parametrize("comm", ["allreduce", "gossip_pair", "gossip_pull", "gossip_push", "group_allreduce_gossip", "elastic"])
+@pytest.mark.parametrize("comm", ["allreduce", "gossip_pair", "gossip_pull", "gossip_push", "group_allreduce_gossip", "elastic",
+                                  "gossip_push_async", "elastic_async"])
 def test_distributed_tool_on_two_cpu_ranks(comm):
     import socket
     import subprocess

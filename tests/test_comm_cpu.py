@@ -29,6 +29,27 @@ def test_elastic_averaging_against_rank0_centre():
     run_ranks(3, cases.elastic)
 
 
+def test_async_push_gossip_folds_exactly_what_arrived():
+    run_ranks(3, cases.push_gossip_async_one_at_a_time)
+
+
+def test_async_push_gossip_does_not_wait_for_a_slow_rank():
+    run_ranks(4, cases.push_gossip_async_nobody_waits)
+
+
+def test_async_elastic_matches_a_replay_of_the_serving_order():
+    run_ranks(3, cases.elastic_async_replay)
+
+
+def test_async_elastic_does_not_wait_for_a_slow_client():
+    run_ranks(3, cases.elastic_async_slow_client)
+
+
+@pytest.mark.parametrize("backend", ["gossip_push_async", "elastic_async"])
+def test_barrier_free_loop_over_asynchronous_library_exchanges(tmp_path, backend):
+    run_ranks(3, cases.barrier_free_loop_with_async_exchanges, str(tmp_path), backend, timeout_s=180)
+
+
 def test_group_allreduce_then_gossip():
     run_ranks(4, cases.hierarchical)
 
