@@ -288,10 +288,11 @@ def main():
     if args.impl == "reference":
         # The reference is a Rust-nightly-2016 crate whose GPU runtime lives in 17 sibling crates that are not
         # in its tree; pip cannot install it and there is no Rust toolchain here.
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "peterhj/rembrandt is a Rust crate (no Python packaging, cargo/rustc absent, 17 path "
-                          "dependencies and cuDNN v4 missing): `pip install --target baseline/_ref` finds nothing to "
-                          "build; compare against --impl torch_ddp instead"}))
+        if int(os.environ.get("RANK", "0")) == 0:      # one line per job, also under a multi-rank launcher
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "peterhj/rembrandt is a Rust crate (no Python packaging, cargo/rustc absent, 17 path "
+                              "dependencies and cuDNN v4 missing): `pip install --target baseline/_ref` finds nothing "
+                              "to build; compare against --impl torch_ddp instead"}))
         return 0
 
     import torch
