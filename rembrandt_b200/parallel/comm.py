@@ -32,6 +32,7 @@ one CUDA kernel live in ``parallel/p2p.py`` and subclass these.
 """
 from __future__ import annotations
 
+import os
 import threading
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Sequence
@@ -189,8 +190,10 @@ class LocalOverlapComm(NullComm):
     graph_safe = True
     overlap_single = True
 
-    def __init__(self, bucket_bytes: int = 32 << 20, min_bucket_bytes: int = 4 << 20, blocks: int = 296):
+    def __init__(self, bucket_bytes: int = 32 << 20, min_bucket_bytes: int = 4 << 20, blocks: Optional[int] = None):
         super().__init__()
+        if blocks is None:
+            blocks = int(os.environ.get("RB_OVERLAP_BLOCKS", "296"))
         self.bucket_elems = bucket_bytes // 4 // 64 * 64
         self.min_bucket_elems = min_bucket_bytes // 4
         self.blocks = blocks
