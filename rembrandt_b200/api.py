@@ -6,8 +6,6 @@ engine) for a named model; ``build_net`` gives just the network. With more than 
 """
 from __future__ import annotations
 
-import os
-
 from typing import Optional
 
 import numpy as np

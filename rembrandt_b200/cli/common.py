@@ -13,7 +13,7 @@ import torch
 import torch.distributed as dist
 
 from ..data import (AsyncPoolDataIter, AsyncQueueDataIter, BatchIter, RaggedBatchIter, RandomIndexIter, CyclicSampleDataIter, RandomSampleDataIter, SyntheticDataSource,
-                    compute_mean, open_data_file, open_split, partition_shard)
+                    open_data_file, open_split, partition_shard)
 from ..engine import StepEngine
 from ..models.net import Net
 from ..optim.sgd import (CheckpointBehavior, InitBehavior, Momentum, SgdOptConfig, StepSizeReference, StepSizeSchedule,

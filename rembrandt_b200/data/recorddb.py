@@ -16,7 +16,7 @@ from __future__ import annotations
 import mmap
 import os
 import struct
-from typing import Iterator, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 

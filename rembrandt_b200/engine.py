@@ -20,7 +20,7 @@ from typing import Optional, Tuple
 import torch
 
 from .models.net import Net
-from .optim.sgd import Momentum, SgdOptConfig, SyncOrder
+from .optim.sgd import SgdOptConfig, SyncOrder
 from .optim.stepper import SgdStepper
 from .ops import native_ops as K
 from .parallel.comm import CommWorker, NullComm

@@ -16,7 +16,6 @@ import torch.nn.functional as F
 from ..ops import layout
 from ..ops import native_ops as K
 from ..ops.native_ops import pad_channels
-from . import config as C
 from .operators import Op, ParamSeg, _draw, conv_out
 
 

@@ -11,7 +11,6 @@ import enum
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
-import torch
 
 
 class Momentum(enum.IntEnum):
