@@ -191,7 +191,7 @@ def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None
         from ..utils.report import ReportServer
         report = ReportServer(port=args.report_port)
     sgd = SgdOpt(opt, engine, ExperimentConfig(args.straggler_ranks, args.straggler_max_delay_ms), report=report)
-    history = sgd.train(_repeat(train_iter), valid_iter, max_iters=args.iters)
+    sgd.train(_repeat(train_iter), valid_iter, max_iters=args.iters)
     if valid_iter is not None and args.valid_iters:
         sgd.validate(valid_iter, args.valid_iters, engine.iter)
     worker.close()

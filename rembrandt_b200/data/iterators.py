@@ -258,7 +258,6 @@ class AsyncPoolDataIter:
         tasks: "queue.Queue" = queue.Queue(self.window)
         results = {}
         cond = threading.Condition()
-        failure: List[BaseException] = []
 
         def work():
             while True:
