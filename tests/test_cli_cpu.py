@@ -72,6 +72,29 @@ def test_distributed_tool_on_two_cpu_ranks(comm):
     assert "iter 4 " in r.stderr
 
 
+def test_straggler_tool_on_three_cpu_ranks_shows_who_waits():
+    """Lock-step push gossip: everybody pays the sleeping rank's delay. Asynchronous: only the sleeper does."""
+    import json
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), "-m", "rembrandt_b200.cli.bench_straggler", "--device", "cpu", "--batch", "8",
+           "--comm", "gossip_push", "--both", "--delay-ms", "60", "--steps", "8", "--warmup", "2"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=400, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    by = {(row["synchronous"], row["delay_ms"] > 0): row for row in rows}
+    assert len(by) == 4
+    lock, free = by[(True, True)], by[(False, True)]
+    assert min(lock["ms_per_step_by_rank"]) >= 60.0                       # every rank waits for the sleeper
+    assert free["ms_per_step_by_rank"][1] >= 60.0                         # the sleeper itself
+    assert free["ms_per_step_of_the_other_ranks"] < lock["ms_per_step_of_the_other_ranks"] - 30.0
+
+
 def test_variable_size_template_through_the_imagenet_tool(monkeypatch):
     from rembrandt_b200.cli import train_imagenet
     from rembrandt_b200.models import zoo
