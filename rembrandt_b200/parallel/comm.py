@@ -401,7 +401,13 @@ def _async_group(group):
         raise ValueError("the asynchronous library backends need gloo (CPU ranks); on GPUs use the kernel "
                          "backends gossip_push_p2p / elastic_p2p, which are asynchronous by default")
     ranks = dist.get_process_group_ranks(group) if group is not None else list(range(dist.get_world_size()))
-    return dist.new_group(ranks, backend="gloo")
+    timeout = None
+    try:    # same time limit as the group it shadows, so that a peer that died ends a receive with an error there too
+        pg = group if group is not None else dist.distributed_c10d._get_default_group()
+        timeout = pg._get_backend(torch.device("cpu")).options._timeout
+    except (AttributeError, RuntimeError):
+        pass
+    return dist.new_group(ranks, backend="gloo", timeout=timeout)
 
 
 class PushGossipComm(CommWorker):
@@ -470,7 +476,9 @@ class PushGossipComm(CommWorker):
             if r != self.rank:
                 dist.send(self._msg, dist.get_global_rank(self._pg, r), group=self._pg)
         self._inbox.join()
-        self._inbox = None
+        error, self._inbox = self._inbox.error, None
+        if error is not None:
+            raise RuntimeError("push gossip: a peer never sent its closing message") from error
 
     def first_one_way_sync(self, flat: torch.Tensor) -> None:
         """Asynchronous form: start listening before any rank can push (every rank calls this before training)."""
@@ -635,7 +643,9 @@ class ElasticComm(CommWorker):
             dist.send(self._msg, dist.get_global_rank(self._pg, 0), group=self._pg)
         elif self._inbox is not None:
             self._inbox.join()
-            self._inbox = None
+            error, self._inbox = self._inbox.error, None
+            if error is not None:
+                raise RuntimeError("elastic averaging: a client never sent its closing message") from error
 
     # ---- lock-step form
     def sync_params(self, flat, repeat=False):

@@ -262,6 +262,19 @@ def rank_raises_before_collective(rank, world):
     C.AllreduceComm().allreduce_average(x)         # the survivors' collective must end with an error, not hang
 
 
+def async_rank_leaves_without_closing(rank, world):
+    """Asynchronous push gossip: rank 1 raises after a few exchanges and never sends its closing message. The
+    others keep exchanging (nobody waits for it), and their close() ends with an error, not a hang."""
+    c = C.PushGossipComm(seed=(7, 9), asynchronous=True)
+    x = _vec(rank)
+    c.first_one_way_sync(x)
+    for k in range(6):
+        if rank == 1 and k == 3:
+            raise RuntimeError("injected failure on rank 1")
+        c.sync_params(x)
+    c.close()      # survivors: the receive from the dead rank ends with a reset connection or the group's time limit
+
+
 def rank_never_joins(rank, world):
     if rank == world - 1:
         time.sleep(6)                              # misses the collective; the process-group timeout is shorter

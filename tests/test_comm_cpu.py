@@ -70,6 +70,13 @@ def test_a_rank_that_raises_ends_the_others_with_an_error_not_a_hang():
     assert all(c != 0 for c in codes), "survivors must see the failure (connection reset or timeout)"
 
 
+def test_async_exchange_survivors_see_a_rank_that_left_without_closing():
+    codes, msgs = run_ranks(3, cases.async_rank_leaves_without_closing, timeout_s=8, expect_failure=True)
+    assert all(c is not None for c in codes), "a rank hung"
+    assert codes[1] != 0 and any("injected failure" in m for _, m in msgs)
+    assert all(c != 0 for c in codes), "survivors must see the failure when they close"
+
+
 def test_a_rank_that_never_joins_times_the_collective_out():
     codes, msgs = run_ranks(3, cases.rank_never_joins, timeout_s=3, expect_failure=True)
     assert all(c is not None for c in codes), "a rank hung"
