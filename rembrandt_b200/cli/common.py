@@ -70,13 +70,37 @@ def base_parser(desc, **defaults):
     ap.add_argument("--straggler-ranks", type=int, nargs="*", default=[])
     ap.add_argument("--straggler-max-delay-ms", type=int, default=0)
     ap.add_argument("--report-port", type=int, default=0, help="serve a live loss report on this port")
+    add_rendezvous_args(ap)
     return ap
 
 
-def init_distributed(device: str):
+def add_rendezvous_args(ap):
+    ap.add_argument("--rendezvous-dir", default=os.environ.get("RB_RENDEZVOUS_DIR"),
+                    help="meet the other ranks through a file in this shared directory instead of a launcher's "
+                         "environment (the reference's directory-based worker, src/worker/gossip_dist_dir.rs): start "
+                         "every rank by hand with --rank R --world-size N")
+    ap.add_argument("--rank", type=int, default=None)
+    ap.add_argument("--world-size", type=int, default=None)
+
+
+def init_distributed(device: str, args=None):
+    """Join the process group. Under `torch.distributed.run` the launcher's environment says who we are; with
+    `--rendezvous-dir` the ranks are started by hand and meet through a file in a directory that all of them see."""
+    shared = getattr(args, "rendezvous_dir", None)
+    if shared and getattr(args, "world_size", None):
+        os.environ["WORLD_SIZE"] = str(args.world_size)
+        os.environ["RANK"] = str(args.rank or 0)
+        if "LOCAL_RANK" not in os.environ:
+            per_node = torch.cuda.device_count() if device == "cuda" else 0
+            os.environ["LOCAL_RANK"] = str((args.rank or 0) % per_node if per_node else 0)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1 and not dist.is_initialized():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        how = {}
+        if shared:
+            os.makedirs(shared, exist_ok=True)
+            how = {"init_method": "file://" + os.path.join(os.path.abspath(shared), "rendezvous"),
+                   "rank": int(os.environ["RANK"]), "world_size": world}
         if device == "cuda":
             local = int(os.environ.get("LOCAL_RANK", "0"))
             torch.cuda.set_device(local)
@@ -84,9 +108,9 @@ def init_distributed(device: str):
                 # host threads (loader, pinned staging memory) stay on the NUMA node of this rank's GPU
                 from ..utils.numa import bind_to_gpu_node
                 bind_to_gpu_node(local)
-            dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist.init_process_group("nccl", device_id=torch.device("cuda", local), **how)
         else:
-            dist.init_process_group("gloo")
+            dist.init_process_group("gloo", **how)
     rank = dist.get_rank() if dist.is_initialized() else 0
     return rank, world
 
@@ -108,7 +132,7 @@ def default_order(comm_name):
 
 
 def run_training(args, model_cfg, schedule: StepSizeSchedule = None, source=None, valid_source=None):
-    rank, world = init_distributed(args.device)
+    rank, world = init_distributed(args.device, args)
     device = torch.device(args.device, int(os.environ.get("LOCAL_RANK", "0")) if args.device == "cuda" else None) \
         if args.device == "cuda" else torch.device("cpu")
     worker = make_comm(args.comm, args.device, world)

@@ -3,20 +3,22 @@ initialises MPI and prints rank and size). Every rank joins the process group, a
 sees; exit status 0 means the launcher, the rendezvous and one collective work.
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m rembrandt_b200.cli.test_dist
+    python -m rembrandt_b200.cli.test_dist --rendezvous-dir /shared/run1 --rank R --world-size N     # one per rank, by hand
 """
 import argparse
 
 import torch
 import torch.distributed as dist
 
-from .common import init_distributed
+from .common import add_rendezvous_args, init_distributed
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--device", default="cuda" if torch.cuda.is_available() else "cpu")
+    add_rendezvous_args(ap)
     args = ap.parse_args(argv)
-    rank, world = init_distributed(args.device)
+    rank, world = init_distributed(args.device, args)
     total = torch.tensor([float(rank)], device="cuda" if args.device == "cuda" and world > 1 else "cpu")
     if world > 1:
         dist.all_reduce(total)

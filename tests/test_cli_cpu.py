@@ -72,6 +72,29 @@ def test_distributed_tool_on_two_cpu_ranks(comm):
     assert "iter 4 " in r.stderr
 
 
+def test_ranks_started_by_hand_meet_through_a_shared_directory(tmp_path):
+    """No launcher: every rank is its own command with --rendezvous-dir / --rank / --world-size; a training tool
+    takes the same flags."""
+    import subprocess
+    import sys
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR", "MASTER_PORT")}
+
+    def start(module, extra, d):
+        return [subprocess.Popen([sys.executable, "-m", module, "--device", "cpu", "--rendezvous-dir", d,
+                                  "--rank", str(r), "--world-size", "2", *extra], cwd=ROOT, env=env,
+                                 stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=240) + (p.returncode,) for p in start("rembrandt_b200.cli.test_dist", [], str(tmp_path / "a"))]
+    assert all(rc == 0 for _, _, rc in outs), outs
+    assert sorted(o.strip().splitlines()[-1][:11] for o, _, _ in outs) == ["rank 0 of 2", "rank 1 of 2"]
+    tiny = [a for a in TINY if a not in ("--device", "cpu")]
+    outs = [p.communicate(timeout=300) + (p.returncode,)
+            for p in start("rembrandt_b200.cli.dist_train_mnist",
+                           [*tiny, "--model", "fc1", "--comm", "gossip_pair", "--iters", "4", "--display-iters", "2",
+                            "--valid-iters", "0"], str(tmp_path / "b"))]
+    assert all(rc == 0 for _, _, rc in outs), [e[-3000:] for _, e, _ in outs]
+    assert any("iter 4 " in e for _, e, _ in outs)                      # rank 0 prints the progress lines
+
+
 def test_straggler_tool_on_three_cpu_ranks_shows_who_waits():
     """Lock-step push gossip: everybody pays the sleeping rank's delay. Asynchronous: only the sleeper does."""
     import json
